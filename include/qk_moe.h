@@ -1,0 +1,244 @@
+/* qk_moe.h — C ABI of the B200 (sm_100a) quantized MoE feed-forward path.
+ *
+ * This is the boundary a qk engine binds instead of its per-layer MoE / GEMV
+ * shader dispatches.  It keeps the conventions of the engine ABI
+ * (reference include/qk.h:18-29): an opaque handle, an open call that returns
+ * NULL and fills a NUL-terminated error string, every other call returning 0
+ * (or a non-negative count) on success and a negative code on failure, the
+ * caller owning every output buffer, inputs copied at upload, and ALL calls on
+ * one context made from a single thread (reference include/qk.h:3-7).
+ *
+ * Differences a caller must know:
+ *   - calls that launch GPU work are asynchronous on the context's CUDA
+ *     stream; qkm_sync() (or a *_host call, which synchronises itself) makes
+ *     results visible;
+ *   - there is no CPU fallback: without a CUDA device qkm_open fails.
+ *
+ * Buffer layouts are the reference's (file:line under the reference tree):
+ *   x        [T][n_embd] f32                       shaders/moe_logits.comp:12
+ *   logits   [T][n_expert] f32                     shaders/moe_logits.comp:13
+ *   sel      qkm_sel[T], 160 B each                shaders/moe_select.comp:15
+ *   h        [T][n_used+1][n_ff] f32, slot n_used = shared expert
+ *                                                  shaders/moe_gateup_iq3.comp:42
+ *   y, y2    [T][n_embd] f32                       shaders/moe_down_iq4.comp:29
+ *   offsets  [n_expert+1] u32, pairs [T*n_used] u32 = (token<<4)|slot
+ *                                                  shaders/moe_group_pairs.comp:24-50
+ *   contrib  [T][n_used][n_embd] f32               shaders/moe_down_iq4_grouped.comp
+ * Weight tensors are raw ggml blocks (reference src/quants.h:52-119), row-major
+ * [n_expert][rows][K/blk] exactly as they sit in a GGUF file.
+ */
+#ifndef QK_MOE_H
+#define QK_MOE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define QKM_API
+#else
+#define QKM_API __attribute__((visibility("default")))
+#endif
+
+/* ggml tensor type ids (reference src/gguf.h:17-21). */
+enum {
+    QKM_TYPE_F32 = 0,
+    QKM_TYPE_F16 = 1,
+    QKM_TYPE_Q8_0 = 8,
+    QKM_TYPE_Q6_K = 14,
+    QKM_TYPE_IQ3_XXS = 18,
+    QKM_TYPE_IQ4_XS = 23
+};
+
+/* Error codes (negative).  -1..-5 keep the meaning they have in the reference
+ * engine (src/main.cpp:5447-5453, :5530). */
+enum {
+    QKM_OK = 0,
+    QKM_ERR_ARG = -1,      /* NULL handle / bad argument                    */
+    QKM_ERR_BUSY = -2,     /* layer not uploaded / context in wrong state    */
+    QKM_ERR_BOUNDS = -3,   /* size beyond the limits given at open           */
+    QKM_ERR_TYPE = -4,     /* unsupported ggml type for this operand         */
+    QKM_ERR_MODE = -5,     /* call not valid in this mode (e.g. EP not set)  */
+    QKM_ERR_CUDA = -6,     /* a CUDA runtime call failed; see qkm_last_error */
+    QKM_ERR_TIMEOUT = -7   /* a bounded device-side wait gave up             */
+};
+
+/* Selection record, one per token (reference shaders/moe_select.comp:15 and
+ * shaders/moe_route_select.comp:17-23: the fused variant uses the first pad
+ * word as its arrival counter).  ids are in descending-logit order; w is the
+ * softmax over the selected logits only; w_shared = sigmoid(gate_inp_shexp.x). */
+typedef struct qkm_sel {
+    uint32_t ids[16];
+    float    w[16];
+    float    w_shared;
+    uint32_t route_done;
+    float    pad[6];
+} qkm_sel;
+
+/* The 4xu32 push constant every MoE shader receives (src/main.cpp:4202). */
+typedef struct qkm_dims {
+    uint32_t n_embd;   /* hidden width, multiple of 256                      */
+    uint32_t n_ff;     /* expert FFN width, multiple of 256 (main.cpp:3620)  */
+    uint32_t n_expert; /* 1..512 (main.cpp:955)                              */
+    uint32_t n_used;   /* 1..16, <= n_expert (main.cpp:1298)                 */
+} qkm_dims;
+
+typedef struct qkm_config {
+    qkm_dims dims;
+    uint32_t n_layer;     /* number of layer slots that can be uploaded, >= 1 */
+    uint32_t max_tokens;  /* largest T any call will pass, >= 1               */
+    int32_t  device;      /* CUDA device ordinal; -1 = current device         */
+    uint32_t flags;       /* QKM_FLAG_*                                       */
+    /* Expert parallel view (0/0 = all experts local).  Experts
+     * [expert_first, expert_first+expert_count) are resident on this GPU. */
+    uint32_t expert_first;
+    uint32_t expert_count;
+} qkm_config;
+
+enum {
+    QKM_FLAG_NONE = 0
+};
+
+/* One layer's eight MoE tensors (the set loadMoeT reads, src/main.cpp:1265-1308).
+ * Pointers are HOST pointers for qkm_upload_layer and DEVICE pointers when the
+ * struct is filled by qkm_layer_device_ptrs.  With an expert-parallel view the
+ * three *_exps tensors hold only the resident experts, first resident expert
+ * first. */
+typedef struct qkm_layer_weights {
+    uint32_t router_type;   /* QKM_TYPE_F32 (reference) or QKM_TYPE_F16        */
+    uint32_t gateup_type;   /* QKM_TYPE_IQ3_XXS or QKM_TYPE_IQ4_XS             */
+    uint32_t down_type;     /* QKM_TYPE_IQ4_XS or QKM_TYPE_Q6_K                */
+    uint32_t reserved;
+    const void  *router;          /* ffn_gate_inp        [n_expert][n_embd]      */
+    const float *gate_inp_shexp;  /* ffn_gate_inp_shexp  [n_embd] f32            */
+    const void  *gate_exps;       /* ffn_gate_exps       [n_expert][n_ff][n_embd] */
+    const void  *up_exps;         /* ffn_up_exps         [n_expert][n_ff][n_embd] */
+    const void  *down_exps;       /* ffn_down_exps       [n_expert][n_embd][n_ff] */
+    const void  *gate_shexp;      /* ffn_gate_shexp      [n_ff][n_embd] Q8_0      */
+    const void  *up_shexp;        /* ffn_up_shexp        [n_ff][n_embd] Q8_0      */
+    const void  *down_shexp;      /* ffn_down_shexp      [n_embd][n_ff] Q8_0      */
+} qkm_layer_weights;
+
+typedef struct qkm_ctx qkm_ctx;
+
+/* ---- lifecycle (shape of qk_open/qk_close, include/qk.h:26-29) ---------- */
+QKM_API qkm_ctx *qkm_open(const qkm_config *cfg, char *err, size_t err_len);
+QKM_API void     qkm_close(qkm_ctx *c);
+QKM_API const char *qkm_last_error(const qkm_ctx *c);
+QKM_API const char *qkm_version(void);
+
+/* getters (include/qk.h:31-36 style) */
+QKM_API uint32_t qkm_n_embd(const qkm_ctx *c);
+QKM_API uint32_t qkm_n_ff(const qkm_ctx *c);
+QKM_API uint32_t qkm_n_expert(const qkm_ctx *c);
+QKM_API uint32_t qkm_n_used(const qkm_ctx *c);
+QKM_API uint32_t qkm_n_layer(const qkm_ctx *c);
+QKM_API uint32_t qkm_max_tokens(const qkm_ctx *c);
+/* bytes per row of ne0 elements of a ggml type, 0 if unsupported
+ * (ggmlRowBytes, src/gguf.h:36-46) */
+QKM_API size_t   qkm_row_bytes(uint32_t type, uint64_t ne0);
+
+/* Stream the context launches on (a cudaStream_t passed as void*; NULL = the
+ * legacy default stream).  qkm_sync waits for it. */
+QKM_API int qkm_set_stream(qkm_ctx *c, void *cuda_stream);
+QKM_API int qkm_sync(qkm_ctx *c);
+/* Number of kernels this context has launched since open (bench accounting). */
+QKM_API uint64_t qkm_launch_count(const qkm_ctx *c);
+
+/* Plain device memory for callers that do not link the CUDA runtime. */
+QKM_API void *qkm_dev_alloc(qkm_ctx *c, size_t bytes);
+QKM_API int   qkm_dev_free(qkm_ctx *c, void *p);
+QKM_API int   qkm_h2d(qkm_ctx *c, void *dst_dev, const void *src_host, size_t bytes);
+QKM_API int   qkm_d2h(qkm_ctx *c, void *dst_host, const void *src_dev, size_t bytes);
+
+/* ---- weights ------------------------------------------------------------ */
+/* Copy one layer's tensors to the GPU (replaces the per-layer upload in
+ * qk_engine::open, src/main.cpp:4031-4067).  The caller keeps ownership. */
+QKM_API int qkm_upload_layer(qkm_ctx *c, uint32_t layer, const qkm_layer_weights *host);
+/* Device addresses of an uploaded layer, for the op-level calls below. */
+QKM_API int qkm_layer_device_ptrs(const qkm_ctx *c, uint32_t layer, qkm_layer_weights *out);
+
+/* ---- op-level entry points: one per reference shader group ---------------
+ * All pointers are DEVICE pointers.  n_tokens is the reference's grid-z. */
+
+/* moe_logits.comp:18-36 / moe_logits_gemm.comp:34-73 */
+QKM_API int qkm_moe_logits(qkm_ctx *c, uint32_t router_type, const void *router,
+                           const float *x, float *logits, uint32_t n_tokens);
+/* moe_select.comp:24-76 / moe_select_256.comp:31-96: top-n_used of the given
+ * f32 logits (non-finite -> -3.4e38, lowest id wins ties), softmax over the
+ * selected, w_shared. */
+QKM_API int qkm_moe_select(qkm_ctx *c, const float *logits, const float *gate_inp_shexp,
+                           const float *x, qkm_sel *sel, uint32_t n_tokens);
+/* moe_route_select.comp:41-130 (+_hier): logits and selection in one call.
+ * This is the path the fused layer calls use: candidates near the selection
+ * boundary are re-evaluated in f64 so ids equal an f64-accumulating CPU router
+ * (src/main.cpp:1320-1341). */
+QKM_API int qkm_moe_route_select(qkm_ctx *c, uint32_t router_type, const void *router,
+                                 const float *gate_inp_shexp, const float *x,
+                                 qkm_sel *sel, uint32_t n_tokens);
+/* moe_group_pairs.comp:19-50 */
+QKM_API int qkm_moe_group_pairs(qkm_ctx *c, const qkm_sel *sel, uint32_t n_tokens,
+                                uint32_t *offsets, uint32_t *pairs);
+/* moe_gateup_iq3.comp:34-106 / moe_gateup_iq4.comp (+_rowtile): token-major */
+QKM_API int qkm_moe_gateup(qkm_ctx *c, uint32_t type, const void *gate_exps,
+                           const void *up_exps, const float *x, const qkm_sel *sel,
+                           float *h, uint32_t n_tokens);
+/* moe_gateup_iq3_grouped*.comp: expert-major over offsets/pairs */
+QKM_API int qkm_moe_gateup_grouped(qkm_ctx *c, uint32_t type, const void *gate_exps,
+                                   const void *up_exps, const float *x,
+                                   const uint32_t *offsets, const uint32_t *pairs,
+                                   float *h, uint32_t n_tokens);
+/* moe_gateup_q8.comp:30-62 (+_64, _coopmat): shared expert -> h[t][n_used][:] */
+QKM_API int qkm_moe_shared_gateup(qkm_ctx *c, const void *gate_shexp, const void *up_shexp,
+                                  const float *x, float *h, uint32_t n_tokens);
+/* moe_down_iq4.comp:35-81 / moe_down_q6k.comp:33-84: token-major weighted sum */
+QKM_API int qkm_moe_down(qkm_ctx *c, uint32_t type, const void *down_exps, const float *h,
+                         const qkm_sel *sel, float *y, uint32_t n_tokens);
+/* moe_down_{iq4,q6k}_grouped*.comp: expert-major, per-(token,slot) contributions */
+QKM_API int qkm_moe_down_grouped(qkm_ctx *c, uint32_t type, const void *down_exps,
+                                 const float *h, const qkm_sel *sel,
+                                 const uint32_t *offsets, const uint32_t *pairs,
+                                 float *contrib, uint32_t n_tokens);
+/* moe_down_q8b.comp:31-57 (+_32, moe_down_q8_coopmat.comp) */
+QKM_API int qkm_moe_shared_down(qkm_ctx *c, const void *down_shexp, const float *h,
+                                const qkm_sel *sel, float *y2, uint32_t n_tokens);
+/* gemv_{f16,q8_0,q6_k,iq4_xs,iq3_xxs}.comp; n = grid-z batch (gemv_q8_0.comp:31-32):
+ * y[n][M] = W[M][K] . x[n][K] */
+QKM_API int qkm_gemv(qkm_ctx *c, uint32_t type, const void *W, const float *x, float *y,
+                     uint32_t M, uint32_t K, uint32_t n);
+/* dequant_row_* (src/quants.h:70-165) on the GPU: the bit-exactness probe. */
+QKM_API int qkm_dequant(qkm_ctx *c, uint32_t type, const void *blocks, float *y,
+                        uint64_t n_elems);
+
+/* ---- fused layer calls --------------------------------------------------- */
+/* Decode sequence of one layer (src/main.cpp:4375-4404) for T tokens/slots:
+ * router -> top-k -> routed gate/up + shared gate/up -> routed + shared down,
+ * y = sum_s w_s*down_s + w_shared*down_shared.  x, y: device [T][n_embd]. */
+QKM_API int qkm_moe_decode(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
+                           float *y);
+/* Batched-prefill sequence (src/main.cpp:5050-5198): grouped by expert, expert
+ * GEMMs on the tensor cores with bf16 operands and f32 accumulation. */
+QKM_API int qkm_moe_prefill(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
+                            float *y);
+/* Same two calls with HOST buffers: copies x in, runs, copies y out, syncs.
+ * mode 0 = decode path, 1 = prefill path. */
+QKM_API int qkm_moe_forward_host(qkm_ctx *c, uint32_t layer, int mode, const float *x_host,
+                                 uint32_t n_tokens, float *y_host);
+/* Decode through layers [0, n_layer) in sequence, feeding each layer the same
+ * per-layer input rows x[l] (device [n_layer][T][n_embd]); y likewise. */
+QKM_API int qkm_moe_decode_stack(qkm_ctx *c, uint32_t layer_first, uint32_t layer_count,
+                                 const float *x, uint32_t n_tokens, float *y);
+/* Selection records of the last fused call (device -> host copy, syncs). */
+QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
+/* Device address of the context's selection / h scratch of the last fused call. */
+QKM_API const qkm_sel *qkm_sel_device(const qkm_ctx *c);
+QKM_API const float   *qkm_h_device(const qkm_ctx *c);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* QK_MOE_H */

@@ -1,0 +1,273 @@
+"""ctypes binding of include/qk_moe.h (libqkmoe.so) and a thin host-side mirror
+of the reference engine's per-layer MoE interface.
+
+There is no CPU path here: if the CUDA library is missing or no B200 is
+present, loading or opening fails with an error.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import synth
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libqkmoe.so")
+
+OK, ERR_ARG, ERR_BUSY, ERR_BOUNDS, ERR_TYPE, ERR_MODE, ERR_CUDA, ERR_TIMEOUT = 0, -1, -2, -3, -4, -5, -6, -7
+
+
+class Dims(C.Structure):
+    _fields_ = [("n_embd", C.c_uint32), ("n_ff", C.c_uint32), ("n_expert", C.c_uint32), ("n_used", C.c_uint32)]
+
+
+class Config(C.Structure):
+    _fields_ = [("dims", Dims), ("n_layer", C.c_uint32), ("max_tokens", C.c_uint32), ("device", C.c_int32),
+                ("flags", C.c_uint32), ("expert_first", C.c_uint32), ("expert_count", C.c_uint32)]
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [("router_type", C.c_uint32), ("gateup_type", C.c_uint32), ("down_type", C.c_uint32),
+                ("reserved", C.c_uint32), ("router", C.c_void_p), ("gate_inp_shexp", C.c_void_p),
+                ("gate_exps", C.c_void_p), ("up_exps", C.c_void_p), ("down_exps", C.c_void_p),
+                ("gate_shexp", C.c_void_p), ("up_shexp", C.c_void_p), ("down_shexp", C.c_void_p)]
+
+
+SEL_DTYPE = np.dtype([("ids", np.uint32, 16), ("w", np.float32, 16), ("w_shared", np.float32),
+                      ("route_done", np.uint32), ("pad", np.float32, 6)])
+assert SEL_DTYPE.itemsize == 160
+
+_VP, _U32, _U64, _I, _SZ = C.c_void_p, C.c_uint32, C.c_uint64, C.c_int, C.c_size_t
+
+# name -> (restype, argtypes); every symbol include/qk_moe.h declares
+SIGNATURES = {
+    "qkm_open": (_VP, [C.POINTER(Config), C.c_char_p, _SZ]),
+    "qkm_close": (None, [_VP]),
+    "qkm_last_error": (C.c_char_p, [_VP]),
+    "qkm_version": (C.c_char_p, []),
+    "qkm_n_embd": (_U32, [_VP]), "qkm_n_ff": (_U32, [_VP]), "qkm_n_expert": (_U32, [_VP]),
+    "qkm_n_used": (_U32, [_VP]), "qkm_n_layer": (_U32, [_VP]), "qkm_max_tokens": (_U32, [_VP]),
+    "qkm_row_bytes": (_SZ, [_U32, _U64]),
+    "qkm_set_stream": (_I, [_VP, _VP]),
+    "qkm_sync": (_I, [_VP]),
+    "qkm_launch_count": (_U64, [_VP]),
+    "qkm_dev_alloc": (_VP, [_VP, _SZ]),
+    "qkm_dev_free": (_I, [_VP, _VP]),
+    "qkm_h2d": (_I, [_VP, _VP, _VP, _SZ]),
+    "qkm_d2h": (_I, [_VP, _VP, _VP, _SZ]),
+    "qkm_upload_layer": (_I, [_VP, _U32, C.POINTER(LayerWeights)]),
+    "qkm_layer_device_ptrs": (_I, [_VP, _U32, C.POINTER(LayerWeights)]),
+    "qkm_moe_logits": (_I, [_VP, _U32, _VP, _VP, _VP, _U32]),
+    "qkm_moe_select": (_I, [_VP, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_moe_route_select": (_I, [_VP, _U32, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_moe_group_pairs": (_I, [_VP, _VP, _U32, _VP, _VP]),
+    "qkm_moe_gateup": (_I, [_VP, _U32, _VP, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_moe_gateup_grouped": (_I, [_VP, _U32, _VP, _VP, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_moe_shared_gateup": (_I, [_VP, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_moe_down": (_I, [_VP, _U32, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_moe_down_grouped": (_I, [_VP, _U32, _VP, _VP, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_moe_shared_down": (_I, [_VP, _VP, _VP, _VP, _VP, _U32]),
+    "qkm_gemv": (_I, [_VP, _U32, _VP, _VP, _VP, _U32, _U32, _U32]),
+    "qkm_dequant": (_I, [_VP, _U32, _VP, _VP, _U64]),
+    "qkm_moe_decode": (_I, [_VP, _U32, _VP, _U32, _VP]),
+    "qkm_moe_prefill": (_I, [_VP, _U32, _VP, _U32, _VP]),
+    "qkm_moe_forward_host": (_I, [_VP, _U32, _I, _VP, _U32, _VP]),
+    "qkm_moe_decode_stack": (_I, [_VP, _U32, _U32, _VP, _U32, _VP]),
+    "qkm_last_sel": (_I, [_VP, _VP, _U32]),
+    "qkm_sel_device": (_VP, [_VP]),
+    "qkm_h_device": (_VP, [_VP]),
+}
+
+_lib = None
+
+
+def load_library(path: str = LIB_PATH) -> C.CDLL:
+    """dlopen libqkmoe.so and declare every entry point.  Raises if it is missing."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(path):
+        raise RuntimeError(f"{path} not found: build it with `python qwen-kernel_b200/build.py` "
+                           "(there is no CPU fallback)")
+    lib = C.CDLL(path)
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the library lacks a declared symbol
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+class QkmError(RuntimeError):
+    def __init__(self, code, msg):
+        super().__init__(f"qkm error {code}: {msg}")
+        self.code = code
+
+
+class DevBuf:
+    """Device memory owned through the C ABI (no torch needed)."""
+
+    def __init__(self, ctx: "Context", nbytes: int):
+        self.ctx, self.nbytes = ctx, int(nbytes)
+        self.ptr = ctx.lib.qkm_dev_alloc(ctx.h, max(self.nbytes, 1))
+        if not self.ptr:
+            raise QkmError(ERR_CUDA, ctx.last_error())
+
+    def upload(self, arr: np.ndarray) -> "DevBuf":
+        arr = np.ascontiguousarray(arr)
+        assert arr.nbytes <= self.nbytes
+        self.ctx.check(self.ctx.lib.qkm_h2d(self.ctx.h, self.ptr, arr.ctypes.data, arr.nbytes))
+        return self
+
+    def download(self, dtype, shape) -> np.ndarray:
+        out = np.empty(shape, dtype)
+        assert out.nbytes <= self.nbytes
+        self.ctx.check(self.ctx.lib.qkm_d2h(self.ctx.h, out.ctypes.data, self.ptr, out.nbytes))
+        return out
+
+    def free(self):
+        if self.ptr and self.ctx.h:
+            self.ctx.lib.qkm_dev_free(self.ctx.h, self.ptr)
+        self.ptr = None
+
+
+def _p(x):
+    """Device pointer of a DevBuf / torch tensor / int."""
+    if x is None:
+        return None
+    if isinstance(x, DevBuf):
+        return x.ptr
+    if hasattr(x, "data_ptr"):
+        return x.data_ptr()
+    return int(x)
+
+
+class Context:
+    """One GPU context (one host thread; calls are asynchronous on its stream)."""
+
+    def __init__(self, dims: synth.Dims = None, n_layer=1, max_tokens=16, device=-1, expert_first=0,
+                 expert_count=0):
+        self.lib = load_library()
+        dims = dims or synth.Dims()
+        self.dims = dims
+        cfg = Config(Dims(dims.n_embd, dims.n_ff, dims.n_expert, dims.n_used), n_layer, max_tokens, device, 0,
+                     expert_first, expert_count)
+        err = C.create_string_buffer(512)
+        self.h = self.lib.qkm_open(C.byref(cfg), err, len(err))
+        if not self.h:
+            raise QkmError(ERR_CUDA, err.value.decode())
+        self.n_layer, self.max_tokens = n_layer, max_tokens
+        self.layer_types = {}
+
+    # -- plumbing
+    def close(self):
+        if self.h:
+            self.lib.qkm_close(self.h)
+            self.h = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *a):
+        self.close()
+
+    def last_error(self) -> str:
+        return self.lib.qkm_last_error(self.h).decode()
+
+    def check(self, rc: int) -> int:
+        if rc < 0:
+            raise QkmError(rc, self.last_error())
+        return rc
+
+    def set_stream(self, cuda_stream: int):
+        self.check(self.lib.qkm_set_stream(self.h, cuda_stream))
+
+    def sync(self):
+        self.check(self.lib.qkm_sync(self.h))
+
+    def launch_count(self) -> int:
+        return int(self.lib.qkm_launch_count(self.h))
+
+    def alloc(self, nbytes: int) -> DevBuf:
+        return DevBuf(self, nbytes)
+
+    def to_device(self, arr: np.ndarray) -> DevBuf:
+        arr = np.ascontiguousarray(arr)
+        return DevBuf(self, arr.nbytes).upload(arr)
+
+    # -- weights
+    def upload_layer(self, layer_idx: int, layer: synth.Layer):
+        w = LayerWeights()
+        w.router_type, w.gateup_type, w.down_type = layer.router_type, layer.gateup_type, layer.down_type
+        (w.router, w.gate_inp_shexp, w.gate_exps, w.up_exps, w.down_exps, w.gate_shexp, w.up_shexp,
+         w.down_shexp) = [t.ctypes.data for t in layer.tensors()]
+        self.check(self.lib.qkm_upload_layer(self.h, layer_idx, C.byref(w)))
+        self.layer_types[layer_idx] = (layer.router_type, layer.gateup_type, layer.down_type)
+
+    def layer_ptrs(self, layer_idx: int) -> LayerWeights:
+        w = LayerWeights()
+        self.check(self.lib.qkm_layer_device_ptrs(self.h, layer_idx, C.byref(w)))
+        return w
+
+    # -- op level (device pointers)
+    def moe_logits(self, router_type, router, x, logits, n):
+        self.check(self.lib.qkm_moe_logits(self.h, router_type, _p(router), _p(x), _p(logits), n))
+
+    def moe_select(self, logits, gis, x, sel, n):
+        self.check(self.lib.qkm_moe_select(self.h, _p(logits), _p(gis), _p(x), _p(sel), n))
+
+    def moe_route_select(self, router_type, router, gis, x, sel, n):
+        self.check(self.lib.qkm_moe_route_select(self.h, router_type, _p(router), _p(gis), _p(x), _p(sel), n))
+
+    def moe_group_pairs(self, sel, n, offsets, pairs):
+        self.check(self.lib.qkm_moe_group_pairs(self.h, _p(sel), n, _p(offsets), _p(pairs)))
+
+    def moe_gateup(self, ttype, gate, up, x, sel, h, n):
+        self.check(self.lib.qkm_moe_gateup(self.h, ttype, _p(gate), _p(up), _p(x), _p(sel), _p(h), n))
+
+    def moe_gateup_grouped(self, ttype, gate, up, x, offsets, pairs, h, n):
+        self.check(self.lib.qkm_moe_gateup_grouped(self.h, ttype, _p(gate), _p(up), _p(x), _p(offsets),
+                                                   _p(pairs), _p(h), n))
+
+    def moe_shared_gateup(self, gate, up, x, h, n):
+        self.check(self.lib.qkm_moe_shared_gateup(self.h, _p(gate), _p(up), _p(x), _p(h), n))
+
+    def moe_down(self, ttype, down, h, sel, y, n):
+        self.check(self.lib.qkm_moe_down(self.h, ttype, _p(down), _p(h), _p(sel), _p(y), n))
+
+    def moe_down_grouped(self, ttype, down, h, sel, offsets, pairs, contrib, n):
+        self.check(self.lib.qkm_moe_down_grouped(self.h, ttype, _p(down), _p(h), _p(sel), _p(offsets),
+                                                 _p(pairs), _p(contrib), n))
+
+    def moe_shared_down(self, down, h, sel, y2, n):
+        self.check(self.lib.qkm_moe_shared_down(self.h, _p(down), _p(h), _p(sel), _p(y2), n))
+
+    def gemv(self, ttype, W, x, y, M, K, n=1):
+        self.check(self.lib.qkm_gemv(self.h, ttype, _p(W), _p(x), _p(y), M, K, n))
+
+    def dequant(self, ttype, blocks, y, n_elems):
+        self.check(self.lib.qkm_dequant(self.h, ttype, _p(blocks), _p(y), n_elems))
+
+    # -- fused
+    def moe_decode(self, layer_idx, x, n, y):
+        self.check(self.lib.qkm_moe_decode(self.h, layer_idx, _p(x), n, _p(y)))
+
+    def moe_prefill(self, layer_idx, x, n, y):
+        self.check(self.lib.qkm_moe_prefill(self.h, layer_idx, _p(x), n, _p(y)))
+
+    def moe_decode_stack(self, first, count, x, n, y):
+        self.check(self.lib.qkm_moe_decode_stack(self.h, first, count, _p(x), n, _p(y)))
+
+    def moe_forward_host(self, layer_idx, x: np.ndarray, mode=0) -> np.ndarray:
+        """Host in, host out (copies inside): the call an engine with host-resident
+        activations makes.  mode 0 = decode path, 1 = prefill path."""
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, self.dims.n_embd)
+        y = np.empty_like(x)
+        self.check(self.lib.qkm_moe_forward_host(self.h, layer_idx, mode, x.ctypes.data, x.shape[0], y.ctypes.data))
+        return y
+
+    def last_sel(self, n) -> np.ndarray:
+        sel = np.zeros(n, SEL_DTYPE)
+        self.check(self.lib.qkm_last_sel(self.h, sel.ctypes.data, n))
+        return sel

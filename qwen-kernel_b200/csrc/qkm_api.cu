@@ -1,0 +1,438 @@
+// The C ABI of include/qk_moe.h: context, weight upload, op-level entry points and
+// the fused per-layer sequences.  Host-side C++; every kernel lives in the other
+// translation units and is reached through qkm_kernels.h.
+//
+// The call sequences mirror the reference engine's dispatch order: decode
+// src/main.cpp:4375-4404, batched prefill src/main.cpp:5050-5198.
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <vector>
+
+#include "qkm_common.cuh"
+#include "qkm_kernels.h"
+
+using namespace qkm;
+
+struct qkm_layer_dev {
+    bool uploaded = false;
+    qkm_layer_weights w{};  // device pointers
+    void* allocs[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+};
+
+struct qkm_ctx {
+    qkm_config cfg{};
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    uint64_t launches = 0;
+    char err[512] = {0};
+    std::vector<qkm_layer_dev> layers;
+    uint32_t efirst = 0, ecount = 0;  // resident experts (ecount == n_expert when unsharded)
+    // scratch, sized for max_tokens
+    qkm_sel* sel = nullptr;
+    float* h = nullptr;
+    void* route_scratch = nullptr;
+    uint32_t* offsets = nullptr;
+    uint32_t* pairs = nullptr;
+    float* contrib = nullptr;  // allocated on first use
+    float* y2 = nullptr;
+    float* x_stage = nullptr;
+    float* y_stage = nullptr;
+    Launch L() { return Launch{stream, &launches}; }
+};
+
+namespace {
+
+int fail(qkm_ctx* c, int code, const char* fmt, ...) {
+    if (c) {
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(c->err, sizeof c->err, fmt, ap);
+        va_end(ap);
+    }
+    return code;
+}
+
+#define QKM_CUDA(c, call)                                                                       \
+    do {                                                                                        \
+        cudaError_t e_ = (call);                                                                \
+        if (e_ != cudaSuccess)                                                                  \
+            return fail((c), QKM_ERR_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), \
+                        __FILE__, __LINE__);                                                    \
+    } while (0)
+
+bool dims_ok(const qkm_dims& d) {
+    // limits the reference enforces: src/main.cpp:955, :1298, :3620-3621
+    return d.n_embd >= 256 && d.n_embd % 256 == 0 && d.n_ff >= 256 && d.n_ff % 256 == 0 &&
+           d.n_expert >= 1 && d.n_expert <= 512 && d.n_used >= 1 && d.n_used <= 16 &&
+           d.n_used <= d.n_expert;
+}
+
+size_t tensor_bytes(const qkm_ctx* c, int idx, const qkm_layer_weights& w) {
+    const qkm_dims& d = c->cfg.dims;
+    const size_t ne = c->ecount;
+    switch (idx) {
+        case 0: return (size_t)d.n_expert * row_bytes(w.router_type, d.n_embd);
+        case 1: return (size_t)d.n_embd * 4;
+        case 2: case 3: return ne * d.n_ff * row_bytes(w.gateup_type, d.n_embd);
+        case 4: return ne * d.n_embd * row_bytes(w.down_type, d.n_ff);
+        case 5: case 6: return (size_t)d.n_ff * row_bytes(QKM_TYPE_Q8_0, d.n_embd);
+        case 7: return (size_t)d.n_embd * row_bytes(QKM_TYPE_Q8_0, d.n_ff);
+    }
+    return 0;
+}
+
+int check_tokens(qkm_ctx* c, uint32_t n) {
+    if (!c) return QKM_ERR_ARG;
+    if (n > c->cfg.max_tokens) return fail(c, QKM_ERR_BOUNDS, "n_tokens %u exceeds max_tokens %u", n, c->cfg.max_tokens);
+    return QKM_OK;
+}
+
+int layer_ready(qkm_ctx* c, uint32_t layer) {
+    if (!c) return QKM_ERR_ARG;
+    if (layer >= c->cfg.n_layer) return fail(c, QKM_ERR_BOUNDS, "layer %u out of range (n_layer %u)", layer, c->cfg.n_layer);
+    if (!c->layers[layer].uploaded) return fail(c, QKM_ERR_BUSY, "layer %u has no weights uploaded", layer);
+    return QKM_OK;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- lifecycle
+
+extern "C" QKM_API const char* qkm_version(void) { return "qk-moe-b200 0.1 (sm_100a)"; }
+
+extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t err_len) {
+    auto bail = [&](const char* msg, const char* detail) -> qkm_ctx* {
+        if (err && err_len) snprintf(err, err_len, "%s%s%s", msg, detail ? ": " : "", detail ? detail : "");
+        return nullptr;
+    };
+    if (!cfg) return bail("qkm_open: NULL config", nullptr);
+    if (!dims_ok(cfg->dims)) return bail("qkm_open: unsupported dims (n_embd,n_ff multiples of 256; n_expert<=512; n_used<=16)", nullptr);
+    if (cfg->n_layer < 1 || cfg->max_tokens < 1) return bail("qkm_open: n_layer and max_tokens must be >= 1", nullptr);
+    if (cfg->max_tokens >= (1u << 28)) return bail("qkm_open: max_tokens too large for the pair encoding", nullptr);
+    uint32_t efirst = cfg->expert_first, ecount = cfg->expert_count;
+    if (ecount == 0) { efirst = 0; ecount = cfg->dims.n_expert; }
+    if ((uint64_t)efirst + ecount > cfg->dims.n_expert) return bail("qkm_open: expert range exceeds n_expert", nullptr);
+
+    int ndev = 0;
+    cudaError_t e = cudaGetDeviceCount(&ndev);
+    if (e != cudaSuccess || ndev == 0) return bail("qkm_open: no CUDA device (this library has no CPU path)", cudaGetErrorString(e));
+    int dev = cfg->device;
+    if (dev < 0) { if (cudaGetDevice(&dev) != cudaSuccess) dev = 0; }
+    if (dev >= ndev) return bail("qkm_open: device ordinal out of range", nullptr);
+    if ((e = cudaSetDevice(dev)) != cudaSuccess) return bail("qkm_open: cudaSetDevice", cudaGetErrorString(e));
+    cudaDeviceProp prop{};
+    if ((e = cudaGetDeviceProperties(&prop, dev)) != cudaSuccess) return bail("qkm_open: cudaGetDeviceProperties", cudaGetErrorString(e));
+    if (prop.major != 10) return bail("qkm_open: kernels are built for sm_100a only; device is", prop.name);
+
+    qkm_ctx* c = new (std::nothrow) qkm_ctx();
+    if (!c) return bail("qkm_open: out of host memory", nullptr);
+    c->cfg = *cfg;
+    c->device = dev;
+    c->efirst = efirst;
+    c->ecount = ecount;
+    c->layers.resize(cfg->n_layer);
+    const qkm_dims& d = cfg->dims;
+    const size_t T = cfg->max_tokens;
+    struct { void** p; size_t bytes; } allocs[] = {
+        {(void**)&c->sel, T * sizeof(qkm_sel)},
+        {(void**)&c->h, T * (d.n_used + 1) * d.n_ff * sizeof(float)},
+        {(void**)&c->route_scratch, route_scratch_bytes((uint32_t)T, d.n_expert)},
+        {(void**)&c->offsets, (d.n_expert + 1) * sizeof(uint32_t)},
+        {(void**)&c->pairs, T * d.n_used * sizeof(uint32_t)},
+        {(void**)&c->y2, T * d.n_embd * sizeof(float)},
+        {(void**)&c->x_stage, T * d.n_embd * sizeof(float)},
+        {(void**)&c->y_stage, T * d.n_embd * sizeof(float)},
+    };
+    for (auto& a : allocs) {
+        if ((e = cudaMalloc(a.p, a.bytes)) != cudaSuccess) {
+            bail("qkm_open: cudaMalloc of scratch", cudaGetErrorString(e));
+            qkm_close(c);
+            return nullptr;
+        }
+    }
+    if (err && err_len) err[0] = 0;
+    return c;
+}
+
+extern "C" QKM_API void qkm_close(qkm_ctx* c) {
+    if (!c) return;
+    cudaSetDevice(c->device);
+    cudaDeviceSynchronize();
+    for (auto& l : c->layers)
+        for (void* p : l.allocs) if (p) cudaFree(p);
+    void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage};
+    for (void* p : scratch) if (p) cudaFree(p);
+    delete c;
+}
+
+extern "C" QKM_API const char* qkm_last_error(const qkm_ctx* c) { return c ? c->err : "NULL context"; }
+extern "C" QKM_API uint32_t qkm_n_embd(const qkm_ctx* c) { return c ? c->cfg.dims.n_embd : 0; }
+extern "C" QKM_API uint32_t qkm_n_ff(const qkm_ctx* c) { return c ? c->cfg.dims.n_ff : 0; }
+extern "C" QKM_API uint32_t qkm_n_expert(const qkm_ctx* c) { return c ? c->cfg.dims.n_expert : 0; }
+extern "C" QKM_API uint32_t qkm_n_used(const qkm_ctx* c) { return c ? c->cfg.dims.n_used : 0; }
+extern "C" QKM_API uint32_t qkm_n_layer(const qkm_ctx* c) { return c ? c->cfg.n_layer : 0; }
+extern "C" QKM_API uint32_t qkm_max_tokens(const qkm_ctx* c) { return c ? c->cfg.max_tokens : 0; }
+extern "C" QKM_API size_t qkm_row_bytes(uint32_t type, uint64_t ne0) {
+    const uint32_t be = block_elems(type);
+    if (be == 0 || ne0 % be) return 0;
+    return row_bytes(type, ne0);
+}
+
+extern "C" QKM_API int qkm_set_stream(qkm_ctx* c, void* s) {
+    if (!c) return QKM_ERR_ARG;
+    c->stream = (cudaStream_t)s;
+    return QKM_OK;
+}
+extern "C" QKM_API int qkm_sync(qkm_ctx* c) {
+    if (!c) return QKM_ERR_ARG;
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    return QKM_OK;
+}
+extern "C" QKM_API uint64_t qkm_launch_count(const qkm_ctx* c) { return c ? c->launches : 0; }
+
+extern "C" QKM_API void* qkm_dev_alloc(qkm_ctx* c, size_t bytes) {
+    if (!c) return nullptr;
+    void* p = nullptr;
+    cudaSetDevice(c->device);
+    cudaError_t e = cudaMalloc(&p, bytes ? bytes : 1);
+    if (e != cudaSuccess) { fail(c, QKM_ERR_CUDA, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e)); return nullptr; }
+    return p;
+}
+extern "C" QKM_API int qkm_dev_free(qkm_ctx* c, void* p) {
+    if (!c) return QKM_ERR_ARG;
+    QKM_CUDA(c, cudaFree(p));
+    return QKM_OK;
+}
+extern "C" QKM_API int qkm_h2d(qkm_ctx* c, void* dst, const void* src, size_t bytes) {
+    if (!c || (!dst && bytes) || (!src && bytes)) return QKM_ERR_ARG;
+    QKM_CUDA(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, c->stream));
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    return QKM_OK;
+}
+extern "C" QKM_API int qkm_d2h(qkm_ctx* c, void* dst, const void* src, size_t bytes) {
+    if (!c || (!dst && bytes) || (!src && bytes)) return QKM_ERR_ARG;
+    QKM_CUDA(c, cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, c->stream));
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    return QKM_OK;
+}
+
+// ---------------------------------------------------------------- weights
+
+extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_layer_weights* w) {
+    if (!c || !w) return QKM_ERR_ARG;
+    if (layer >= c->cfg.n_layer) return fail(c, QKM_ERR_BOUNDS, "layer %u out of range", layer);
+    // the types loadMoeT accepts (src/main.cpp:1283-1291), plus an F16 router
+    if (w->router_type != QKM_TYPE_F32 && w->router_type != QKM_TYPE_F16)
+        return fail(c, QKM_ERR_TYPE, "router type %u unsupported (F32 or F16)", w->router_type);
+    if (w->gateup_type != QKM_TYPE_IQ3_XXS && w->gateup_type != QKM_TYPE_IQ4_XS)
+        return fail(c, QKM_ERR_TYPE, "gate/up type %u unsupported (IQ3_XXS or IQ4_XS)", w->gateup_type);
+    if (w->down_type != QKM_TYPE_IQ4_XS && w->down_type != QKM_TYPE_Q6_K)
+        return fail(c, QKM_ERR_TYPE, "down type %u unsupported (IQ4_XS or Q6_K)", w->down_type);
+    const void* src[8] = {w->router, w->gate_inp_shexp, w->gate_exps, w->up_exps, w->down_exps,
+                          w->gate_shexp, w->up_shexp, w->down_shexp};
+    for (const void* p : src) if (!p) return fail(c, QKM_ERR_ARG, "layer %u: NULL tensor pointer", layer);
+    QKM_CUDA(c, cudaSetDevice(c->device));
+    qkm_layer_dev& l = c->layers[layer];
+    for (int i = 0; i < 8; ++i) {
+        const size_t bytes = tensor_bytes(c, i, *w);
+        if (l.allocs[i]) { QKM_CUDA(c, cudaFree(l.allocs[i])); l.allocs[i] = nullptr; }
+        // 256 spare bytes: streaming kernels may read a few bytes past a tensor's end
+        QKM_CUDA(c, cudaMalloc(&l.allocs[i], bytes + 256));
+        QKM_CUDA(c, cudaMemcpyAsync(l.allocs[i], src[i], bytes, cudaMemcpyHostToDevice, c->stream));
+        QKM_CUDA(c, cudaMemsetAsync((uint8_t*)l.allocs[i] + bytes, 0, 256, c->stream));
+    }
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    l.w = *w;
+    l.w.router = l.allocs[0];
+    l.w.gate_inp_shexp = (const float*)l.allocs[1];
+    l.w.gate_exps = l.allocs[2];
+    l.w.up_exps = l.allocs[3];
+    l.w.down_exps = l.allocs[4];
+    l.w.gate_shexp = l.allocs[5];
+    l.w.up_shexp = l.allocs[6];
+    l.w.down_shexp = l.allocs[7];
+    l.uploaded = true;
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_layer_device_ptrs(const qkm_ctx* c, uint32_t layer, qkm_layer_weights* out) {
+    if (!c || !out) return QKM_ERR_ARG;
+    if (layer >= c->cfg.n_layer) return QKM_ERR_BOUNDS;
+    if (!c->layers[layer].uploaded) return QKM_ERR_BUSY;
+    *out = c->layers[layer].w;
+    return QKM_OK;
+}
+
+// ---------------------------------------------------------------- op-level entry points
+
+#define QKM_LAUNCH(c, call)                                                                          \
+    do {                                                                                             \
+        cudaError_t e_ = (call);                                                                     \
+        if (e_ == cudaErrorInvalidValue) return fail((c), QKM_ERR_TYPE, "%s: unsupported type or shape", #call); \
+        if (e_ != cudaSuccess) return fail((c), QKM_ERR_CUDA, "%s: %s", #call, cudaGetErrorString(e_)); \
+    } while (0)
+
+extern "C" QKM_API int qkm_moe_logits(qkm_ctx* c, uint32_t router_type, const void* router, const float* x,
+                                      float* logits, uint32_t n) {
+    if (!c || !router || !x || !logits) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_logits(c->L(), c->cfg.dims, router_type, router, x, logits, nullptr, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_select(qkm_ctx* c, const float* logits, const float* gis, const float* x,
+                                      qkm_sel* sel, uint32_t n) {
+    if (!c || !logits || !gis || !x || !sel) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_select(c->L(), c->cfg.dims, logits, gis, x, sel, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_route_select(qkm_ctx* c, uint32_t router_type, const void* router,
+                                            const float* gis, const float* x, qkm_sel* sel, uint32_t n) {
+    if (!c || !router || !gis || !x || !sel) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    if (router_type != QKM_TYPE_F32 && router_type != QKM_TYPE_F16) return fail(c, QKM_ERR_TYPE, "router type %u", router_type);
+    QKM_LAUNCH(c, launch_route_select(c->L(), c->cfg.dims, router_type, router, gis, x, sel, n, c->route_scratch));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_group_pairs(qkm_ctx* c, const qkm_sel* sel, uint32_t n, uint32_t* offsets,
+                                           uint32_t* pairs) {
+    if (!c || !sel || !offsets || !pairs) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_group_pairs(c->L(), c->cfg.dims, sel, n, offsets, pairs, c->efirst, c->ecount));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_gateup(qkm_ctx* c, uint32_t type, const void* gate, const void* up,
+                                      const float* x, const qkm_sel* sel, float* h, uint32_t n) {
+    if (!c || !gate || !up || !x || !sel || !h) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_gateup_tokens(c->L(), c->cfg.dims, type, gate, up, x, sel, h, n, c->efirst, c->ecount));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_gateup_grouped(qkm_ctx* c, uint32_t type, const void* gate, const void* up,
+                                              const float* x, const uint32_t* offsets, const uint32_t* pairs,
+                                              float* h, uint32_t n) {
+    if (!c || !gate || !up || !x || !offsets || !pairs || !h) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_gateup_pairs(c->L(), c->cfg.dims, type, gate, up, x, offsets, pairs, h, n, c->efirst, c->ecount));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_shared_gateup(qkm_ctx* c, const void* gate, const void* up, const float* x,
+                                             float* h, uint32_t n) {
+    if (!c || !gate || !up || !x || !h) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_shared_gateup(c->L(), c->cfg.dims, gate, up, x, h, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_down(qkm_ctx* c, uint32_t type, const void* down, const float* h,
+                                    const qkm_sel* sel, float* y, uint32_t n) {
+    if (!c || !down || !h || !sel || !y) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_down_tokens(c->L(), c->cfg.dims, type, down, h, sel, y, n, c->efirst, c->ecount, nullptr));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_down_grouped(qkm_ctx* c, uint32_t type, const void* down, const float* h,
+                                            const qkm_sel* sel, const uint32_t* offsets, const uint32_t* pairs,
+                                            float* contrib, uint32_t n) {
+    if (!c || !down || !h || !sel || !offsets || !pairs || !contrib) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_down_pairs(c->L(), c->cfg.dims, type, down, h, sel, offsets, pairs, contrib, n, c->efirst, c->ecount));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_shared_down(qkm_ctx* c, const void* down, const float* h, const qkm_sel* sel,
+                                           float* y2, uint32_t n) {
+    if (!c || !down || !h || !sel || !y2) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_shared_down(c->L(), c->cfg.dims, down, h, sel, y2, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_gemv(qkm_ctx* c, uint32_t type, const void* W, const float* x, float* y,
+                                uint32_t M, uint32_t K, uint32_t n) {
+    if (!c || !W || !x || !y) return QKM_ERR_ARG;
+    const uint32_t be = block_elems(type);
+    if (be == 0) return fail(c, QKM_ERR_TYPE, "qkm_gemv: type %u unsupported", type);
+    if (K == 0 || K % be || K % 8) return fail(c, QKM_ERR_ARG, "qkm_gemv: K=%u must be a multiple of the block size %u and of 8", K, be);
+    if (n > 65535) return fail(c, QKM_ERR_BOUNDS, "qkm_gemv: n=%u exceeds 65535", n);
+    QKM_LAUNCH(c, launch_gemv(c->L(), type, W, x, y, M, K, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_dequant(qkm_ctx* c, uint32_t type, const void* blocks, float* y, uint64_t n_elems) {
+    if (!c || !blocks || !y) return QKM_ERR_ARG;
+    const uint32_t be = block_elems(type);
+    if (be == 0) return fail(c, QKM_ERR_TYPE, "qkm_dequant: type %u unsupported", type);
+    if (n_elems % be || n_elems % 8) return fail(c, QKM_ERR_ARG, "qkm_dequant: n_elems must be whole blocks and a multiple of 8");
+    QKM_LAUNCH(c, launch_dequant(c->L(), type, blocks, y, n_elems));
+    return QKM_OK;
+}
+
+// ---------------------------------------------------------------- fused layer calls
+
+extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, float* y) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (!x || !y) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    const qkm_layer_weights& w = c->layers[layer].w;
+    const qkm_dims& d = c->cfg.dims;
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch));
+    QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
+    QKM_LAUNCH(c, launch_gateup_tokens(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, x, c->sel, c->h, n, c->efirst, c->ecount));
+    QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, float* y) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (!x || !y) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    const qkm_layer_weights& w = c->layers[layer].w;
+    const qkm_dims& d = c->cfg.dims;
+    if (!c->contrib) {
+        QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
+    }
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch));
+    QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
+    QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
+    QKM_LAUNCH(c, launch_gateup_pairs(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, x, c->offsets, c->pairs, c->h, n, c->efirst, c->ecount));
+    QKM_CUDA(c, cudaMemsetAsync(c->contrib, 0, (size_t)n * d.n_used * d.n_embd * sizeof(float), c->stream));
+    QKM_LAUNCH(c, launch_down_pairs(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, c->offsets, c->pairs, c->contrib, n, c->efirst, c->ecount));
+    QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, c->sel, c->y2, n));
+    QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, c->y2, y, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_forward_host(qkm_ctx* c, uint32_t layer, int mode, const float* x_host,
+                                            uint32_t n, float* y_host) {
+    if (!c || !x_host || !y_host) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    const size_t bytes = (size_t)n * c->cfg.dims.n_embd * sizeof(float);
+    QKM_CUDA(c, cudaMemcpyAsync(c->x_stage, x_host, bytes, cudaMemcpyHostToDevice, c->stream));
+    const int rc = mode == 0 ? qkm_moe_decode(c, layer, c->x_stage, n, c->y_stage)
+                             : qkm_moe_prefill(c, layer, c->x_stage, n, c->y_stage);
+    if (rc) return rc;
+    QKM_CUDA(c, cudaMemcpyAsync(y_host, c->y_stage, bytes, cudaMemcpyDeviceToHost, c->stream));
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t count, const float* x,
+                                            uint32_t n, float* y) {
+    if (!c || !x || !y) return QKM_ERR_ARG;
+    if ((uint64_t)first + count > c->cfg.n_layer) return fail(c, QKM_ERR_BOUNDS, "layers [%u,%u) out of range", first, first + count);
+    const size_t stride = (size_t)n * c->cfg.dims.n_embd;
+    for (uint32_t l = 0; l < count; ++l)
+        if (int rc = qkm_moe_decode(c, first + l, x + l * stride, n, y + l * stride)) return rc;
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_last_sel(qkm_ctx* c, qkm_sel* sel_host, uint32_t n) {
+    if (!c || !sel_host) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    return qkm_d2h(c, sel_host, c->sel, (size_t)n * sizeof(qkm_sel));
+}
+extern "C" QKM_API const qkm_sel* qkm_sel_device(const qkm_ctx* c) { return c ? c->sel : nullptr; }
+extern "C" QKM_API const float* qkm_h_device(const qkm_ctx* c) { return c ? c->h : nullptr; }

@@ -1,0 +1,102 @@
+"""Whole-layer parity through the fused C-ABI calls, against the oracle and the golden
+fixtures: ids positional-exact, weights 1e-4 (the reference's gate, src/main.cpp:1191-1194)
+and tighter, outputs 1e-5 (f32 decode path) row-scaled relative, argmax of every output
+row unchanged."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL_F32 = 1e-5
+
+
+def check_layer(syn, got_y, got_sel, ref, n_used, tol=TOL_F32):
+    assert np.array_equal(got_sel["ids"][:, :n_used], ref["sel"]["ids"][:, :n_used])
+    np.testing.assert_allclose(got_sel["w"][:, :n_used], ref["sel"]["w"][:, :n_used], rtol=1e-5, atol=1e-7)
+    np.testing.assert_allclose(got_sel["w_shared"], ref["sel"]["w_shared"], rtol=1e-6)
+    assert syn.rel_err_rows(got_y, ref["y"]) < tol
+    assert syn.rel_err_reference(got_y, ref["y"]) < 1e-2
+    assert np.array_equal(np.argmax(got_y, axis=1), np.argmax(ref["y"], axis=1))
+
+
+@pytest.mark.parametrize("tag", ["a", "b"])
+def test_golden_small_layer(pkg, syn, golden, tag):
+    g = golden(f"moe_small_{tag}.npz")
+    rt, gt, dt = (int(v) for v in g["types"])
+    dims = syn.Dims(*(int(v) for v in g["dims"]))
+    layer = syn.make_layer(dims, seed=1234, layer=3, router_type=rt, gateup_type=gt, down_type=dt)
+    with pkg.Context(dims, n_layer=1, max_tokens=4, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        for mode in (0, 1):
+            y = ctx.moe_forward_host(0, g["x"], mode=mode)
+            sel = ctx.last_sel(3)
+            assert np.array_equal(sel["ids"], g["ids"])
+            np.testing.assert_allclose(sel["w"], g["w"], rtol=1e-5, atol=1e-7)
+            assert syn.rel_err_rows(y, g["y"]) < (TOL_F32 if mode == 0 else 2e-2)
+
+
+@pytest.mark.parametrize("router_type,gt,dt", [(1, 18, 23), (0, 18, 14), (0, 23, 23)])
+@pytest.mark.parametrize("T", [1, 5])
+def test_decode_full_size_layer(pkg, orc, syn, router_type, gt, dt, T):
+    """Bench configuration 0: 2048 / 512 / 256 experts / top-8."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=42, router_type=router_type, gateup_type=gt, down_type=dt)
+    x = syn.random_x(T, dims.n_embd, seed=43)
+    ref = orc.moe_layer(layer, x, threads=8)
+    with pkg.Context(dims, n_layer=1, max_tokens=8, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        y = ctx.moe_forward_host(0, x, mode=0)
+        check_layer(syn, y, ctx.last_sel(T), ref, 8)
+        # determinism: a second run is bit-identical
+        y2 = ctx.moe_forward_host(0, x, mode=0)
+        assert np.array_equal(y, y2)
+
+
+def test_decode_stack_and_errors(pkg, orc, syn):
+    dims = syn.Dims(n_embd=512, n_ff=256, n_expert=16, n_used=4)
+    T, L = 6, 3
+    layers = [syn.make_layer(dims, seed=50, layer=l) for l in range(L)]
+    x = np.stack([syn.random_x(T, dims.n_embd, seed=60 + l) for l in range(L)])
+    with pkg.Context(dims, n_layer=L, max_tokens=T, device=0) as ctx:
+        with pytest.raises(pkg.QkmError) as ei:      # nothing uploaded yet
+            ctx.moe_forward_host(0, x[0])
+        assert ei.value.code == -2
+        for l in range(L):
+            ctx.upload_layer(l, layers[l])
+        d_x, d_y = ctx.to_device(x), ctx.alloc(x.nbytes)
+        ctx.moe_decode_stack(0, L, d_x, T, d_y)
+        y = d_y.download(np.float32, x.shape)
+        for l in range(L):
+            ref = orc.moe_layer(layers[l], x[l])
+            assert syn.rel_err_rows(y[l], ref["y"]) < TOL_F32
+        with pytest.raises(pkg.QkmError) as ei:      # more tokens than the context was opened for
+            ctx.moe_decode(0, d_x, T + 1, d_y)
+        assert ei.value.code == -3
+        with pytest.raises(pkg.QkmError):
+            ctx.moe_decode(L, d_x, 1, d_y)
+        assert ctx.launch_count() > 0
+
+
+def test_expert_parallel_view_partial_sums(pkg, orc, syn):
+    """A context that holds experts [4,8) only returns that shard's partial sum."""
+    dims = syn.Dims(n_embd=512, n_ff=256, n_expert=8, n_used=3)
+    T = 7
+    layer = syn.make_layer(dims, seed=70)
+    x = syn.random_x(T, dims.n_embd, seed=71)
+    full = orc.moe_layer(layer, x)
+    total = np.zeros_like(full["y"])
+    for first in (0, 4):
+        shard = layer.expert_slice(first, 4)
+        with pkg.Context(dims, n_layer=1, max_tokens=T, device=0, expert_first=first, expert_count=4) as ctx:
+            ctx.upload_layer(0, shard)
+            w = ctx.layer_ptrs(0)
+            d_x, d_sel = ctx.to_device(x), ctx.to_device(full["sel"])
+            d_h, d_y = ctx.to_device(np.zeros(T * 4 * 256, np.float32)), ctx.alloc(T * 512 * 4)
+            ctx.moe_gateup(shard.gateup_type, w.gate_exps, w.up_exps, d_x, d_sel, d_h, T)
+            ctx.moe_down(shard.down_type, w.down_exps, d_h, d_sel, d_y, T)
+            part = d_y.download(np.float32, (T, 512))
+            want = orc.moe_layer(shard, x, sel_in=full["sel"], with_shared=False)["y"]
+            assert syn.rel_err_rows(part, want) < TOL_F32
+            total += part
+    routed = orc.moe_layer(layer, x, sel_in=full["sel"], with_shared=False)["y"]
+    assert syn.rel_err_rows(total, routed) < TOL_F32
