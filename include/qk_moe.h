@@ -231,6 +231,10 @@ QKM_API int qkm_moe_forward_host(qkm_ctx *c, uint32_t layer, int mode, const flo
  * per-layer input rows x[l] (device [n_layer][T][n_embd]); y likewise. */
 QKM_API int qkm_moe_decode_stack(qkm_ctx *c, uint32_t layer_first, uint32_t layer_count,
                                  const float *x, uint32_t n_tokens, float *y);
+/* The same with HOST buffers [layer_count][T][n_embd]: one copy in, the stack, one
+ * copy out, then a stream synchronise.  Pinned host memory makes the copies async. */
+QKM_API int qkm_moe_decode_stack_host(qkm_ctx *c, uint32_t layer_first, uint32_t layer_count,
+                                      const float *x_host, uint32_t n_tokens, float *y_host);
 /* Selection records of the last fused call (device -> host copy, syncs). */
 QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 /* Device address of the context's selection / h scratch of the last fused call. */

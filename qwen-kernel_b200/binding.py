@@ -75,6 +75,7 @@ SIGNATURES = {
     "qkm_moe_prefill": (_I, [_VP, _U32, _VP, _U32, _VP]),
     "qkm_moe_forward_host": (_I, [_VP, _U32, _I, _VP, _U32, _VP]),
     "qkm_moe_decode_stack": (_I, [_VP, _U32, _U32, _VP, _U32, _VP]),
+    "qkm_moe_decode_stack_host": (_I, [_VP, _U32, _U32, _VP, _U32, _VP]),
     "qkm_last_sel": (_I, [_VP, _VP, _U32]),
     "qkm_sel_device": (_VP, [_VP]),
     "qkm_h_device": (_VP, [_VP]),
@@ -258,6 +259,10 @@ class Context:
 
     def moe_decode_stack(self, first, count, x, n, y):
         self.check(self.lib.qkm_moe_decode_stack(self.h, first, count, _p(x), n, _p(y)))
+
+    def moe_decode_stack_host(self, first, count, x_host_ptr, n, y_host_ptr):
+        """x/y: host addresses (ints) of [count][n][n_embd] f32, ideally pinned."""
+        self.check(self.lib.qkm_moe_decode_stack_host(self.h, first, count, x_host_ptr, n, y_host_ptr))
 
     def moe_forward_host(self, layer_idx, x: np.ndarray, mode=0) -> np.ndarray:
         """Host in, host out (copies inside): the call an engine with host-resident

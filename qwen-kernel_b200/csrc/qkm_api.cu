@@ -41,6 +41,8 @@ struct qkm_ctx {
     float* y2 = nullptr;
     float* x_stage = nullptr;
     float* y_stage = nullptr;
+    float* stack_x = nullptr;  // [n_layer][max_tokens][n_embd], allocated on first use
+    float* stack_y = nullptr;
     Launch L() { return Launch{stream, &launches}; }
 };
 
@@ -164,7 +166,8 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     cudaDeviceSynchronize();
     for (auto& l : c->layers)
         for (void* p : l.allocs) if (p) cudaFree(p);
-    void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage};
+    void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
+                       c->stack_x, c->stack_y};
     for (void* p : scratch) if (p) cudaFree(p);
     delete c;
 }
@@ -426,6 +429,24 @@ extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t
     const size_t stride = (size_t)n * c->cfg.dims.n_embd;
     for (uint32_t l = 0; l < count; ++l)
         if (int rc = qkm_moe_decode(c, first + l, x + l * stride, n, y + l * stride)) return rc;
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_decode_stack_host(qkm_ctx* c, uint32_t first, uint32_t count,
+                                                 const float* x_host, uint32_t n, float* y_host) {
+    if (!c || !x_host || !y_host) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    if ((uint64_t)first + count > c->cfg.n_layer) return fail(c, QKM_ERR_BOUNDS, "layers [%u,%u) out of range", first, first + count);
+    if (!c->stack_x) {
+        const size_t cap = (size_t)c->cfg.n_layer * c->cfg.max_tokens * c->cfg.dims.n_embd * sizeof(float);
+        QKM_CUDA(c, cudaMalloc((void**)&c->stack_x, cap));
+        QKM_CUDA(c, cudaMalloc((void**)&c->stack_y, cap));
+    }
+    const size_t bytes = (size_t)count * n * c->cfg.dims.n_embd * sizeof(float);
+    QKM_CUDA(c, cudaMemcpyAsync(c->stack_x, x_host, bytes, cudaMemcpyHostToDevice, c->stream));
+    if (int rc = qkm_moe_decode_stack(c, first, count, c->stack_x, n, c->stack_y)) return rc;
+    QKM_CUDA(c, cudaMemcpyAsync(y_host, c->stack_y, bytes, cudaMemcpyDeviceToHost, c->stream));
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
     return QKM_OK;
 }
 

@@ -190,7 +190,6 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     __shared__ uint32_t s_cand[kMaxCand];
     __shared__ double s_val[kMaxCand];
     __shared__ uint32_t s_ncand;
-    __shared__ float s_thresh;
     const uint32_t t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const float* xt = x + (size_t)t * d.n_embd;
     const float* lt = logits + (size_t)t * d.n_expert;
@@ -231,10 +230,10 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     // Doubled for safety, and doubled again because two logits are compared.
     const float eps = (float)(d.n_embd / 32 + 6) * 5.9604645e-8f * sqrtf(r2) * sqrtf(x2);
     const float thresh = kth - 4.0f * eps;
-    if (tid == 0) s_thresh = thresh;
 
     // candidates: every expert at or above the threshold
-    const bool c0 = id0 < d.n_expert && l0 >= thresh, c1 = id1 < d.n_expert && l1 >= thresh;
+    // (written as !(l < thresh) so a NaN threshold - NaN in x - admits every expert)
+    const bool c0 = id0 < d.n_expert && !(l0 < thresh), c1 = id1 < d.n_expert && !(l1 < thresh);
     if (c0) { const uint32_t p = atomicAdd(&s_ncand, 1u); if (p < kMaxCand) s_cand[p] = id0; }
     if (c1) { const uint32_t p = atomicAdd(&s_ncand, 1u); if (p < kMaxCand) s_cand[p] = id1; }
     __syncthreads();
@@ -243,7 +242,7 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     // Too many near-ties (or non-finite input: everything sits at the floor): fall
     // back to evaluating experts in id order, kMaxCand at a time is not enough, so
     // take the exact route of ranking ALL experts in f64 through the global pass below.
-    const bool all = ncand_raw > kMaxCand;
+    const bool all = ncand_raw > kMaxCand || ncand_raw < d.n_used;
     const uint32_t total = all ? d.n_expert : ncand_raw;
 
     // f64 re-evaluation.  In the `all` case values stream through s_val in chunks and

@@ -106,9 +106,12 @@ def test_moe_layer_properties(orc, syn):
     # expert-parallel partial sums add up to the whole layer
     parts = [orc.moe_layer(layer.expert_slice(f, 4), x, sel_in=sel, with_shared=(f == 0))["y"] for f in (0, 4)]
     assert syn.rel_err_rows(parts[0] + parts[1], out["y"]) < 1e-6
-    # contributions fold back to the routed sum
-    shared_only = orc.moe_layer(layer.expert_slice(0, 0) if False else layer, x, sel_in=sel)["y"]
-    assert shared_only.shape == out["y"].shape
+    # per-slot contributions fold back to the routed sum (slot order)
+    r = orc.moe_layer(layer, x, sel_in=sel, with_shared=False, want_contrib=True)
+    fold = np.zeros_like(r["y"])
+    for s in range(dims.n_used):
+        fold += r["contrib"][:, s]
+    assert np.array_equal(fold, r["y"])
     # multi-threaded run is identical
     out_mt = orc.moe_layer(layer, x, threads=4)
     assert np.array_equal(out_mt["y"], out["y"])
