@@ -260,54 +260,32 @@ def run_decode(args, pkg, syn):
 
 
 def time_kernels(ctx, pkg, syn, torch, dev, stream, L, S, x_dev, distinct, dims, reps=5):
-    """Average duration of each kernel class over all layers (one launch per layer per
-    pass), from CUDA events on the launching stream, with its algorithmic bytes."""
-    sel = torch.empty(L * S * 160, dtype=torch.uint8, device=dev)
-    h = torch.zeros(L, S, dims.n_used + 1, dims.n_ff, device=dev)
-    y = torch.empty(L, S, dims.n_embd, device=dev)
-    ptrs = [ctx.layer_ptrs(l) for l in range(L)]
+    """Average duration of every stage of the fused decode sequence (one launch per layer
+    per pass), from CUDA events recorded on the launching stream between the stages
+    (qkm_profile_*), with the algorithmic weight bytes each stage touches."""
     rb = syn.row_bytes
-    gu_bytes = 2 * dims.n_ff * rb(syn.IQ3_XXS, dims.n_embd)
-    dn_bytes = dims.n_embd * rb(syn.IQ4_XS, dims.n_ff)
-    sh_gu = 2 * dims.n_ff * rb(syn.Q8_0, dims.n_embd)
-    sh_dn = dims.n_embd * rb(syn.Q8_0, dims.n_ff)
-    router_b = dims.n_expert * rb(syn.F16, dims.n_embd) + dims.n_embd * 4
     mean_u = float(np.mean(distinct))
-
-    def sel_ptr(l):
-        return sel.data_ptr() + l * S * 160
-
-    def route(l):
-        ctx.moe_route_select(syn.F16, ptrs[l].router, ptrs[l].gate_inp_shexp, x_dev[l], sel_ptr(l), S)
-
-    def shared_gu(l):
-        ctx.moe_shared_gateup(ptrs[l].gate_shexp, ptrs[l].up_shexp, x_dev[l], h[l], S)
-
-    def gateup(l):
-        ctx.moe_gateup(syn.IQ3_XXS, ptrs[l].gate_exps, ptrs[l].up_exps, x_dev[l], sel_ptr(l), h[l], S)
-
-    def down(l):
-        ctx.moe_down(syn.IQ4_XS, ptrs[l].down_exps, h[l], sel_ptr(l), y[l], S)
-
-    def shared_dn(l):
-        ctx.moe_shared_down(ptrs[l].down_shexp, h[l], sel_ptr(l), y[l], S)
-
-    out = {}
-    for name, fn, nbytes in (("route_select", route, router_b), ("shared_gateup", shared_gu, sh_gu),
-                             ("routed_gateup", gateup, mean_u * gu_bytes), ("routed_down", down, mean_u * dn_bytes),
-                             ("shared_down", shared_dn, sh_dn)):
+    stage_bytes = {
+        "moe.route": dims.n_expert * rb(syn.F16, dims.n_embd) + dims.n_embd * 4,
+        "moe.shared_gu": 2 * dims.n_ff * rb(syn.Q8_0, dims.n_embd),
+        "moe.gu": mean_u * 2 * dims.n_ff * rb(syn.IQ3_XXS, dims.n_embd),
+        "moe.dn": mean_u * dims.n_embd * rb(syn.IQ4_XS, dims.n_ff),
+        "moe.shared_dn": dims.n_embd * rb(syn.Q8_0, dims.n_ff),
+    }
+    y = torch.empty(S, dims.n_embd, device=dev)
+    ctx.profile_enable(True)
+    acc = {}
+    for _ in range(reps):
         for l in range(L):
-            fn(l)
-        torch.cuda.synchronize(dev)
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
-        for _ in range(reps):
-            for l in range(L):
-                fn(l)
-        e1.record(stream)
-        torch.cuda.synchronize(dev)
-        ms = e0.elapsed_time(e1) / (reps * L)
-        out[name] = {"name": name, "ms_per_layer": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9}
+            ctx.moe_decode(l, x_dev[l], S, y)
+            for k, v in ctx.profile_read().items():
+                acc[k] = acc.get(k, 0.0) + v
+    ctx.profile_enable(False)
+    out = {}
+    for k, v in acc.items():
+        ms = v / (reps * L)
+        nbytes = stage_bytes.get(k, 0)
+        out[k] = {"name": k, "ms_per_layer": ms, "bytes_per_launch": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9 if ms > 0 else 0.0}
     return out
 
 

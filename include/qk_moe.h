@@ -235,6 +235,14 @@ QKM_API int qkm_moe_decode_stack(qkm_ctx *c, uint32_t layer_first, uint32_t laye
  * copy out, then a stream synchronise.  Pinned host memory makes the copies async. */
 QKM_API int qkm_moe_decode_stack_host(qkm_ctx *c, uint32_t layer_first, uint32_t layer_count,
                                       const float *x_host, uint32_t n_tokens, float *y_host);
+/* Per-stage device timing of the fused calls (the reference's QK_STEP_PROF,
+ * src/main.cpp:4173-4185, :4591-4632: a timestamp after every stage of the decode
+ * sequence, reported per label).  While enabled, qkm_moe_decode / qkm_moe_prefill
+ * record a CUDA event on the context's stream after each stage; qkm_profile_read
+ * synchronises and returns, for the LAST fused call, the number of stages, their
+ * labels (16 bytes each, NUL-terminated) and their durations in milliseconds. */
+QKM_API int qkm_profile_enable(qkm_ctx *c, int on);
+QKM_API int qkm_profile_read(qkm_ctx *c, char *labels, float *ms, uint32_t max_stages);
 /* Selection records of the last fused call (device -> host copy, syncs). */
 QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 /* Device address of the context's selection / h scratch of the last fused call. */

@@ -76,6 +76,8 @@ SIGNATURES = {
     "qkm_moe_forward_host": (_I, [_VP, _U32, _I, _VP, _U32, _VP]),
     "qkm_moe_decode_stack": (_I, [_VP, _U32, _U32, _VP, _U32, _VP]),
     "qkm_moe_decode_stack_host": (_I, [_VP, _U32, _U32, _VP, _U32, _VP]),
+    "qkm_profile_enable": (_I, [_VP, _I]),
+    "qkm_profile_read": (_I, [_VP, _VP, _VP, _U32]),
     "qkm_last_sel": (_I, [_VP, _VP, _U32]),
     "qkm_sel_device": (_VP, [_VP]),
     "qkm_h_device": (_VP, [_VP]),
@@ -271,6 +273,16 @@ class Context:
         y = np.empty_like(x)
         self.check(self.lib.qkm_moe_forward_host(self.h, layer_idx, mode, x.ctypes.data, x.shape[0], y.ctypes.data))
         return y
+
+    def profile_enable(self, on=True):
+        self.check(self.lib.qkm_profile_enable(self.h, int(on)))
+
+    def profile_read(self) -> dict:
+        """Stage label -> milliseconds of the last fused call (synchronises)."""
+        labels = C.create_string_buffer(16 * 16)
+        ms = (C.c_float * 16)()
+        n = self.check(self.lib.qkm_profile_read(self.h, labels, ms, 16))
+        return {labels.raw[16 * i:16 * i + 16].split(b"\0")[0].decode(): float(ms[i]) for i in range(n)}
 
     def last_sel(self, n) -> np.ndarray:
         sel = np.zeros(n, SEL_DTYPE)

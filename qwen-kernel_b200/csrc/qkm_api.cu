@@ -19,8 +19,11 @@ using namespace qkm;
 
 struct qkm_layer_dev {
     bool uploaded = false;
-    qkm_layer_weights w{};  // device pointers
+    qkm_layer_weights w{};  // device pointers, raw ggml layout
     void* allocs[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    // tile-ordered copies for the streaming kernels (NULL where the type has none)
+    void* tiles[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+    bool stream_ok = false;  // routed gate/up and down both have tiles
 };
 
 struct qkm_ctx {
@@ -43,6 +46,32 @@ struct qkm_ctx {
     float* y_stage = nullptr;
     float* stack_x = nullptr;  // [n_layer][max_tokens][n_embd], allocated on first use
     float* stack_y = nullptr;
+    // streaming path scratch
+    int n_sms = 0;
+    int8_t* xplanes = nullptr;        // [max_tokens][4][n_embd]
+    float* xscale = nullptr;          // [max_tokens]
+    void* hpieces = nullptr;          // [max_tokens*n_used][3][n_ff] bf16
+    StreamItem* items_gu = nullptr;
+    StreamItem* items_dn = nullptr;
+    uint32_t* n_items = nullptr;      // [0] gate/up, [1] down
+    uint32_t* status = nullptr;       // kernel status word (device)
+    uint32_t* status_host = nullptr;  // pinned mirror
+    bool shapes_stream_ok = false;
+    // per-stage profiling of the fused calls
+    static constexpr int kMaxStages = 16;
+    bool profiling = false;
+    cudaEvent_t prof_ev[kMaxStages + 1] = {};
+    char prof_label[kMaxStages][16] = {};
+    int prof_n = 0;
+    void prof_begin() {
+        prof_n = 0;
+        if (profiling) cudaEventRecord(prof_ev[0], stream);
+    }
+    void prof_mark(const char* label) {
+        if (!profiling || prof_n >= kMaxStages) return;
+        snprintf(prof_label[prof_n], 16, "%s", label);
+        cudaEventRecord(prof_ev[++prof_n], stream);
+    }
     Launch L() { return Launch{stream, &launches}; }
 };
 
@@ -156,6 +185,40 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
             return nullptr;
         }
     }
+    c->n_sms = prop.multiProcessorCount;
+    // Streaming kernels: column blocks per row must be a power of two in [2,16] (one warp
+    // each), rows must split into whole items, and all experts must be resident.
+    auto pow2_2_16 = [](uint32_t v) { return v >= 2 && v <= 16 && (v & (v - 1)) == 0; };
+    c->shapes_stream_ok = pow2_2_16(d.n_embd / 256) && pow2_2_16(d.n_ff / 256) &&
+                          d.n_ff % gateup_stream_rows_per_item() == 0 &&
+                          d.n_embd % down_stream_rows_per_item() == 0 && ecount == d.n_expert;
+    if (c->shapes_stream_ok) {
+        const size_t max_groups = (T * d.n_used + 1) / 2 + d.n_expert;  // token pairs per expert, rounded up
+        struct { void** p; size_t bytes; } more[] = {
+            {(void**)&c->xplanes, T * 4 * d.n_embd},
+            {(void**)&c->xscale, T * sizeof(float)},
+            {(void**)&c->hpieces, T * d.n_used * 3 * d.n_ff * 2},
+            {(void**)&c->items_gu, max_groups * (d.n_ff / gateup_stream_rows_per_item()) * sizeof(StreamItem)},
+            {(void**)&c->items_dn, max_groups * (d.n_embd / down_stream_rows_per_item()) * sizeof(StreamItem)},
+            {(void**)&c->n_items, 2 * sizeof(uint32_t)},
+            {(void**)&c->contrib, T * d.n_used * d.n_embd * sizeof(float)},
+        };
+        for (auto& a : more) {
+            if ((e = cudaMalloc(a.p, a.bytes)) != cudaSuccess) {
+                bail("qkm_open: cudaMalloc of streaming scratch", cudaGetErrorString(e));
+                qkm_close(c);
+                return nullptr;
+            }
+        }
+    }
+    if ((e = cudaMalloc((void**)&c->status, sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMemset(c->status, 0, sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMallocHost((void**)&c->status_host, sizeof(uint32_t))) != cudaSuccess) {
+        bail("qkm_open: status word", cudaGetErrorString(e));
+        qkm_close(c);
+        return nullptr;
+    }
+    *c->status_host = 0;
     if (err && err_len) err[0] = 0;
     return c;
 }
@@ -164,11 +227,16 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     if (!c) return;
     cudaSetDevice(c->device);
     cudaDeviceSynchronize();
-    for (auto& l : c->layers)
+    for (auto& l : c->layers) {
         for (void* p : l.allocs) if (p) cudaFree(p);
+        for (void* p : l.tiles) if (p) cudaFree(p);
+    }
     void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
-                       c->stack_x, c->stack_y};
+                       c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
+                       c->n_items, c->status};
     for (void* p : scratch) if (p) cudaFree(p);
+    if (c->status_host) cudaFreeHost(c->status_host);
+    for (cudaEvent_t ev : c->prof_ev) if (ev) cudaEventDestroy(ev);
     delete c;
 }
 
@@ -190,10 +258,22 @@ extern "C" QKM_API int qkm_set_stream(qkm_ctx* c, void* s) {
     c->stream = (cudaStream_t)s;
     return QKM_OK;
 }
+// Copies the kernels' status word back after a synchronise; a bounded device-side wait
+// that gave up (or a broken layout assumption) surfaces here as an error code.
+static int check_status(qkm_ctx* c) {
+    QKM_CUDA(c, cudaMemcpyAsync(c->status_host, c->status, sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    if (*c->status_host != 0) {
+        const uint32_t st = *c->status_host;
+        cudaMemsetAsync(c->status, 0, sizeof(uint32_t), c->stream);
+        return fail(c, QKM_ERR_TIMEOUT, "a kernel reported status %u (1 = bounded wait gave up, 2 = shared-memory layout)", st);
+    }
+    return QKM_OK;
+}
+
 extern "C" QKM_API int qkm_sync(qkm_ctx* c) {
     if (!c) return QKM_ERR_ARG;
-    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
-    return QKM_OK;
+    return check_status(c);
 }
 extern "C" QKM_API uint64_t qkm_launch_count(const qkm_ctx* c) { return c ? c->launches : 0; }
 
@@ -247,6 +327,25 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
         QKM_CUDA(c, cudaMalloc(&l.allocs[i], bytes + 256));
         QKM_CUDA(c, cudaMemcpyAsync(l.allocs[i], src[i], bytes, cudaMemcpyHostToDevice, c->stream));
         QKM_CUDA(c, cudaMemsetAsync((uint8_t*)l.allocs[i] + bytes, 0, 256, c->stream));
+    }
+    // tile-ordered copies for the streaming kernels (same bytes, re-ordered on the device)
+    for (void*& p : l.tiles) { if (p) { QKM_CUDA(c, cudaFree(p)); p = nullptr; } }
+    l.stream_ok = false;
+    if (c->shapes_stream_ok) {
+        const qkm_dims& d = c->cfg.dims;
+        struct { int idx; uint32_t type, mats, rows, K; } plan[] = {
+            {2, w->gateup_type, c->ecount, d.n_ff, d.n_embd}, {3, w->gateup_type, c->ecount, d.n_ff, d.n_embd},
+            {4, w->down_type, c->ecount, d.n_embd, d.n_ff},
+        };
+        bool ok = w->gateup_type == QKM_TYPE_IQ3_XXS && w->down_type == QKM_TYPE_IQ4_XS;
+        for (auto& t : plan) {
+            if (!ok) break;
+            const size_t bytes = tensor_bytes(c, t.idx, *w);
+            QKM_CUDA(c, cudaMalloc(&l.tiles[t.idx], bytes + 256));
+            cudaError_t e = launch_repack(c->L(), t.type, l.allocs[t.idx], l.tiles[t.idx], t.mats, t.rows, t.K);
+            if (e != cudaSuccess) return fail(c, QKM_ERR_CUDA, "repack: %s", cudaGetErrorString(e));
+        }
+        l.stream_ok = ok;
     }
     QKM_CUDA(c, cudaStreamSynchronize(c->stream));
     l.w = *w;
@@ -379,12 +478,39 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     if (int rc = layer_ready(c, layer)) return rc;
     if (!x || !y) return QKM_ERR_ARG;
     if (int rc = check_tokens(c, n)) return rc;
-    const qkm_layer_weights& w = c->layers[layer].w;
+    const qkm_layer_dev& ld = c->layers[layer];
+    const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
+    c->prof_begin();
     QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch));
+    c->prof_mark("moe.route");
+    if (!ld.stream_ok) {  // generic kernels on the raw layout
+        QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
+        c->prof_mark("moe.shared_gu");
+        QKM_LAUNCH(c, launch_gateup_tokens(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, x, c->sel, c->h, n, c->efirst, c->ecount));
+        c->prof_mark("moe.gu");
+        QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));
+        c->prof_mark("moe.dn");
+        return QKM_OK;
+    }
+    QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
+    QKM_LAUNCH(c, launch_plan_items(c->L(), c->offsets, c->ecount, d.n_ff / gateup_stream_rows_per_item(), 2, c->items_gu, c->n_items));
+    QKM_LAUNCH(c, launch_plan_items(c->L(), c->offsets, c->ecount, d.n_embd / down_stream_rows_per_item(), 2, c->items_dn, c->n_items + 1));
+    c->prof_mark("moe.pairs");
+    QKM_LAUNCH(c, launch_encode_digits(c->L(), x, c->xplanes, c->xscale, n, d.n_embd));
+    c->prof_mark("moe.encode");
     QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
-    QKM_LAUNCH(c, launch_gateup_tokens(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, x, c->sel, c->h, n, c->efirst, c->ecount));
-    QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));
+    c->prof_mark("moe.shared_gu");
+    QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xplanes, c->xscale, c->pairs,
+                                       c->items_gu, c->n_items, c->h, c->hpieces, (uint32_t)c->n_sms, c->status));
+    c->prof_mark("moe.gu");
+    QKM_LAUNCH(c, launch_down_stream(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->pairs, c->items_dn,
+                                     c->n_items + 1, c->contrib, (uint32_t)c->n_sms, c->status));
+    c->prof_mark("moe.dn");
+    QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, c->sel, c->y2, n));
+    c->prof_mark("moe.shared_dn");
+    QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, c->y2, y, n));
+    c->prof_mark("moe.fold");
     return QKM_OK;
 }
 
@@ -418,8 +544,7 @@ extern "C" QKM_API int qkm_moe_forward_host(qkm_ctx* c, uint32_t layer, int mode
                              : qkm_moe_prefill(c, layer, c->x_stage, n, c->y_stage);
     if (rc) return rc;
     QKM_CUDA(c, cudaMemcpyAsync(y_host, c->y_stage, bytes, cudaMemcpyDeviceToHost, c->stream));
-    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
-    return QKM_OK;
+    return check_status(c);
 }
 
 extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t count, const float* x,
@@ -446,8 +571,28 @@ extern "C" QKM_API int qkm_moe_decode_stack_host(qkm_ctx* c, uint32_t first, uin
     QKM_CUDA(c, cudaMemcpyAsync(c->stack_x, x_host, bytes, cudaMemcpyHostToDevice, c->stream));
     if (int rc = qkm_moe_decode_stack(c, first, count, c->stack_x, n, c->stack_y)) return rc;
     QKM_CUDA(c, cudaMemcpyAsync(y_host, c->stack_y, bytes, cudaMemcpyDeviceToHost, c->stream));
-    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    return check_status(c);
+}
+
+extern "C" QKM_API int qkm_profile_enable(qkm_ctx* c, int on) {
+    if (!c) return QKM_ERR_ARG;
+    if (on && !c->prof_ev[0])
+        for (cudaEvent_t& ev : c->prof_ev) QKM_CUDA(c, cudaEventCreate(&ev));
+    c->profiling = on != 0;
+    c->prof_n = 0;
     return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_profile_read(qkm_ctx* c, char* labels, float* ms, uint32_t max_stages) {
+    if (!c || !labels || !ms) return QKM_ERR_ARG;
+    if (!c->profiling) return fail(c, QKM_ERR_MODE, "profiling is not enabled");
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    const int n = c->prof_n < (int)max_stages ? c->prof_n : (int)max_stages;
+    for (int i = 0; i < n; ++i) {
+        memcpy(labels + 16 * i, c->prof_label[i], 16);
+        QKM_CUDA(c, cudaEventElapsedTime(&ms[i], c->prof_ev[i], c->prof_ev[i + 1]));
+    }
+    return n;
 }
 
 extern "C" QKM_API int qkm_last_sel(qkm_ctx* c, qkm_sel* sel_host, uint32_t n) {

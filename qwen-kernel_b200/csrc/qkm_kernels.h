@@ -17,6 +17,35 @@ struct Launch {
     void count(int n = 1) const { if (launches) *launches += (uint64_t)n; }
 };
 
+// One unit of work of a streaming kernel: an expert, a chunk of its rows and up to
+// tok_per_item of the tokens routed to it (pairs[pair_off .. pair_off + ntok)).
+struct StreamItem {
+    uint16_t expert;   // resident-expert index
+    uint8_t chunk;     // row chunk within the expert's matrix
+    uint8_t ntok;
+    uint32_t pair_off;
+};
+
+// ---- qkm_repack.cu : raw ggml -> tile layout (same bytes, see qkm_tiles.cuh)
+cudaError_t launch_repack(const Launch& L, uint32_t type, const void* raw, void* out, uint32_t n_mats,
+                          uint32_t rows, uint32_t K);
+
+// ---- qkm_decode_gateup.cu / qkm_decode_down.cu : streaming kernels for small token counts
+cudaError_t launch_encode_digits(const Launch& L, const float* x, int8_t* planes, float* scale,
+                                 uint32_t n_rows, uint32_t K);
+cudaError_t launch_plan_items(const Launch& L, const uint32_t* offsets, uint32_t n_expert_local,
+                              uint32_t n_chunks, uint32_t tok_per_item, StreamItem* items, uint32_t* n_items);
+cudaError_t launch_gateup_stream(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
+                                 const void* up_tiles, const int8_t* xplanes, const float* xscale,
+                                 const uint32_t* pairs, const StreamItem* items, const uint32_t* n_items,
+                                 float* h, void* hpieces, uint32_t n_sms, uint32_t* status);
+cudaError_t launch_down_stream(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles,
+                               const void* hpieces, const qkm_sel* sel, const uint32_t* pairs,
+                               const StreamItem* items, const uint32_t* n_items, float* contrib,
+                               uint32_t n_sms, uint32_t* status);
+uint32_t gateup_stream_rows_per_item();
+uint32_t down_stream_rows_per_item();
+
 // ---- qkm_gemv.cu
 cudaError_t launch_dequant(const Launch& L, uint32_t type, const void* blocks, float* y, uint64_t n_elems);
 cudaError_t launch_gemv(const Launch& L, uint32_t type, const void* W, const float* x, float* y,
