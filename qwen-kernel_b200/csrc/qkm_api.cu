@@ -53,7 +53,11 @@ struct qkm_ctx {
     void* hpieces = nullptr;          // [max_tokens*n_used][3][n_ff] bf16
     StreamItem* items_gu = nullptr;
     StreamItem* items_dn = nullptr;
-    uint32_t* n_items = nullptr;      // [0] gate/up, [1] down
+    StreamItem* items_sh_gu = nullptr;
+    StreamItem* items_sh_dn = nullptr;
+    uint32_t* n_items = nullptr;      // [0] gate/up, [1] down, [2] shared gate/up, [3] shared down
+    float* contrib_s = nullptr;       // [max_tokens][n_used+1][n_embd]
+    uint32_t* arrivals = nullptr;     // [max_tokens][n_embd / unit rows]
     uint32_t* status = nullptr;       // kernel status word (device)
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
@@ -173,7 +177,7 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
         {(void**)&c->h, T * (d.n_used + 1) * d.n_ff * sizeof(float)},
         {(void**)&c->route_scratch, route_scratch_bytes((uint32_t)T, d.n_expert)},
         {(void**)&c->offsets, (d.n_expert + 1) * sizeof(uint32_t)},
-        {(void**)&c->pairs, T * d.n_used * sizeof(uint32_t)},
+        {(void**)&c->pairs, T * (d.n_used + 1) * sizeof(uint32_t)},
         {(void**)&c->y2, T * d.n_embd * sizeof(float)},
         {(void**)&c->x_stage, T * d.n_embd * sizeof(float)},
         {(void**)&c->y_stage, T * d.n_embd * sizeof(float)},
@@ -189,19 +193,24 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
     // Streaming kernels: column blocks per row must be a power of two in [2,16] (one warp
     // each), rows must split into whole items, and all experts must be resident.
     auto pow2_2_16 = [](uint32_t v) { return v >= 2 && v <= 16 && (v & (v - 1)) == 0; };
-    c->shapes_stream_ok = pow2_2_16(d.n_embd / 256) && pow2_2_16(d.n_ff / 256) &&
+    c->shapes_stream_ok = pow2_2_16(d.n_embd / 256) && d.n_embd / 256 <= 8 && pow2_2_16(d.n_ff / 256) && d.n_used <= 15 &&
                           d.n_ff % gateup_stream_rows_per_item() == 0 &&
                           d.n_embd % down_stream_rows_per_item() == 0 && ecount == d.n_expert;
     if (c->shapes_stream_ok) {
         const size_t max_groups = (T * d.n_used + 1) / 2 + d.n_expert;  // token pairs per expert, rounded up
+        const size_t sh_groups = (T + 1) / 2;
+        const size_t chunks_gu = d.n_ff / gateup_stream_rows_per_item(), chunks_dn = d.n_embd / down_stream_rows_per_item();
         struct { void** p; size_t bytes; } more[] = {
             {(void**)&c->xplanes, T * 4 * d.n_embd},
             {(void**)&c->xscale, T * sizeof(float)},
-            {(void**)&c->hpieces, T * d.n_used * 3 * d.n_ff * 2},
-            {(void**)&c->items_gu, max_groups * (d.n_ff / gateup_stream_rows_per_item()) * sizeof(StreamItem)},
-            {(void**)&c->items_dn, max_groups * (d.n_embd / down_stream_rows_per_item()) * sizeof(StreamItem)},
-            {(void**)&c->n_items, 2 * sizeof(uint32_t)},
-            {(void**)&c->contrib, T * d.n_used * d.n_embd * sizeof(float)},
+            {(void**)&c->hpieces, T * (d.n_used + 1) * 3 * d.n_ff * 2},
+            {(void**)&c->items_gu, max_groups * chunks_gu * sizeof(StreamItem)},
+            {(void**)&c->items_dn, max_groups * chunks_dn * sizeof(StreamItem)},
+            {(void**)&c->items_sh_gu, sh_groups * chunks_gu * sizeof(StreamItem)},
+            {(void**)&c->items_sh_dn, sh_groups * chunks_dn * sizeof(StreamItem)},
+            {(void**)&c->n_items, 4 * sizeof(uint32_t)},
+            {(void**)&c->contrib_s, T * (d.n_used + 1) * d.n_embd * sizeof(float)},
+            {(void**)&c->arrivals, T * (d.n_embd / down_stream_unit_rows()) * sizeof(uint32_t)},
         };
         for (auto& a : more) {
             if ((e = cudaMalloc(a.p, a.bytes)) != cudaSuccess) {
@@ -210,6 +219,7 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
                 return nullptr;
             }
         }
+        cudaMemset(c->arrivals, 0, T * (d.n_embd / down_stream_unit_rows()) * sizeof(uint32_t));
     }
     if ((e = cudaMalloc((void**)&c->status, sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMemset(c->status, 0, sizeof(uint32_t))) != cudaSuccess ||
@@ -233,7 +243,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     }
     void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
-                       c->n_items, c->status};
+                       c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status};
     for (void* p : scratch) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     for (cudaEvent_t ev : c->prof_ev) if (ev) cudaEventDestroy(ev);
@@ -336,6 +346,8 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
         struct { int idx; uint32_t type, mats, rows, K; } plan[] = {
             {2, w->gateup_type, c->ecount, d.n_ff, d.n_embd}, {3, w->gateup_type, c->ecount, d.n_ff, d.n_embd},
             {4, w->down_type, c->ecount, d.n_embd, d.n_ff},
+            {5, QKM_TYPE_Q8_0, 1, d.n_ff, d.n_embd}, {6, QKM_TYPE_Q8_0, 1, d.n_ff, d.n_embd},
+            {7, QKM_TYPE_Q8_0, 1, d.n_embd, d.n_ff},
         };
         bool ok = w->gateup_type == QKM_TYPE_IQ3_XXS && w->down_type == QKM_TYPE_IQ4_XS;
         for (auto& t : plan) {
@@ -482,7 +494,8 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     c->prof_begin();
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch));
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch,
+                                      ld.stream_ok ? c->xplanes : nullptr, ld.stream_ok ? c->xscale : nullptr));
     c->prof_mark("moe.route");
     if (!ld.stream_ok) {  // generic kernels on the raw layout
         QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
@@ -493,24 +506,23 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         c->prof_mark("moe.dn");
         return QKM_OK;
     }
-    QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
-    QKM_LAUNCH(c, launch_plan_items(c->L(), c->offsets, c->ecount, d.n_ff / gateup_stream_rows_per_item(), 2, c->items_gu, c->n_items));
-    QKM_LAUNCH(c, launch_plan_items(c->L(), c->offsets, c->ecount, d.n_embd / down_stream_rows_per_item(), 2, c->items_dn, c->n_items + 1));
+    QKM_LAUNCH(c, launch_group_plan(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount, c->items_gu,
+                                    d.n_ff / gateup_stream_rows_per_item(), c->items_dn,
+                                    d.n_embd / down_stream_rows_per_item(), c->items_sh_gu, c->items_sh_dn, 2, c->n_items));
     c->prof_mark("moe.pairs");
-    QKM_LAUNCH(c, launch_encode_digits(c->L(), x, c->xplanes, c->xscale, n, d.n_embd));
-    c->prof_mark("moe.encode");
-    QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
+    const uint32_t nb = (uint32_t)c->n_sms;
+    QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xplanes, c->xscale, c->pairs,
+                                       c->items_sh_gu, c->n_items + 2, c->h, c->hpieces, nb, c->status));
     c->prof_mark("moe.shared_gu");
     QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xplanes, c->xscale, c->pairs,
-                                       c->items_gu, c->n_items, c->h, c->hpieces, (uint32_t)c->n_sms, c->status));
+                                       c->items_gu, c->n_items, c->h, c->hpieces, nb, c->status));
     c->prof_mark("moe.gu");
     QKM_LAUNCH(c, launch_down_stream(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->pairs, c->items_dn,
-                                     c->n_items + 1, c->contrib, (uint32_t)c->n_sms, c->status));
+                                     c->n_items + 1, c->contrib_s, y, c->arrivals, nb, c->status));
     c->prof_mark("moe.dn");
-    QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, c->sel, c->y2, n));
+    QKM_LAUNCH(c, launch_down_stream(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, c->sel, c->pairs, c->items_sh_dn,
+                                     c->n_items + 3, c->contrib_s, y, c->arrivals, nb, c->status));
     c->prof_mark("moe.shared_dn");
-    QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, c->y2, y, n));
-    c->prof_mark("moe.fold");
     return QKM_OK;
 }
 

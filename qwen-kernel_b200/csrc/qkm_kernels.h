@@ -33,16 +33,16 @@ cudaError_t launch_repack(const Launch& L, uint32_t type, const void* raw, void*
 // ---- qkm_decode_gateup.cu / qkm_decode_down.cu : streaming kernels for small token counts
 cudaError_t launch_encode_digits(const Launch& L, const float* x, int8_t* planes, float* scale,
                                  uint32_t n_rows, uint32_t K);
-cudaError_t launch_plan_items(const Launch& L, const uint32_t* offsets, uint32_t n_expert_local,
-                              uint32_t n_chunks, uint32_t tok_per_item, StreamItem* items, uint32_t* n_items);
 cudaError_t launch_gateup_stream(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                                  const void* up_tiles, const int8_t* xplanes, const float* xscale,
                                  const uint32_t* pairs, const StreamItem* items, const uint32_t* n_items,
-                                 float* h, void* hpieces, uint32_t n_sms, uint32_t* status);
+                                 float* h, void* hpieces, uint32_t n_blocks, uint32_t* status);
+// contrib [T][n_used+1][n_embd]; arrivals [T][n_embd/unit rows] zero before the first call
 cudaError_t launch_down_stream(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles,
                                const void* hpieces, const qkm_sel* sel, const uint32_t* pairs,
-                               const StreamItem* items, const uint32_t* n_items, float* contrib,
-                               uint32_t n_sms, uint32_t* status);
+                               const StreamItem* items, const uint32_t* n_items, float* contrib, float* y,
+                               uint32_t* arrivals, uint32_t n_blocks, uint32_t* status);
+uint32_t down_stream_unit_rows();
 uint32_t gateup_stream_rows_per_item();
 uint32_t down_stream_rows_per_item();
 
@@ -60,10 +60,17 @@ cudaError_t launch_select(const Launch& L, const qkm_dims& d, const float* logit
                           const float* x, qkm_sel* sel, uint32_t n_tokens);
 cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t router_type,
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
-                                uint32_t n_tokens, void* scratch);
+                                uint32_t n_tokens, void* scratch, int8_t* xplanes = nullptr,
+                                float* xscale = nullptr);
 cudaError_t launch_group_pairs(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                                uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,
                                uint32_t expert_count);
+// group_pairs plus, in the same launch, the work lists of the streaming kernels
+cudaError_t launch_group_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
+                              uint32_t* offsets, uint32_t* pairs, uint32_t expert_first, uint32_t expert_count,
+                              StreamItem* items_gu, uint32_t chunks_gu, StreamItem* items_dn,
+                              uint32_t chunks_dn, StreamItem* items_sh_gu, StreamItem* items_sh_dn,
+                              uint32_t tok_per_item, uint32_t* n_items);
 
 // ---- qkm_moe_simple.cu : one warp per output element, raw ggml layout
 cudaError_t launch_gateup_tokens(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate,
@@ -83,8 +90,10 @@ cudaError_t launch_down_pairs(const Launch& L, const qkm_dims& d, uint32_t type,
                               const float* h, const qkm_sel* sel, const uint32_t* offsets,
                               const uint32_t* pairs, float* contrib, uint32_t n_tokens,
                               uint32_t expert_first, uint32_t expert_count);
+// y2 = w_shared * shared down; with contrib != NULL: y2 = sum_s contrib[.][s][.] + that
 cudaError_t launch_shared_down(const Launch& L, const qkm_dims& d, const void* down, const float* h,
-                               const qkm_sel* sel, float* y2, uint32_t n_tokens);
+                               const qkm_sel* sel, float* y2, uint32_t n_tokens,
+                               const float* contrib = nullptr);
 // y[t][o] = sum over slots (in order) of contrib[t][s][o], plus y2[t][o] when y2 != NULL
 cudaError_t launch_fold_contrib(const Launch& L, const qkm_dims& d, const float* contrib, const float* y2,
                                 float* y, uint32_t n_tokens);

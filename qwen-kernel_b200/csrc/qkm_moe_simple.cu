@@ -242,9 +242,12 @@ cudaError_t launch_down_pairs(const Launch& L, const qkm_dims& d, uint32_t type,
 }
 
 // ---- shared down: y2[t][o] = w_shared * (DS[o] . h[t][n_used]) ------------------------------------------------
+// With `contrib` the routed per-slot contributions are folded in, slots in order, then the
+// shared term: the sum add_rms3_grouped.comp:22-27 forms.
 __global__ void __launch_bounds__(256)
 shared_down_kernel(const uint8_t* __restrict__ down, const float* __restrict__ h,
-                   const qkm_sel* __restrict__ sel, float* __restrict__ y2, qkm_dims d) {
+                   const qkm_sel* __restrict__ sel, float* __restrict__ y2, qkm_dims d,
+                   const float* __restrict__ contrib) {
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t o = blockIdx.x * 8u + (threadIdx.x >> 5);
     const uint32_t t = blockIdx.y;
@@ -252,14 +255,23 @@ shared_down_kernel(const uint8_t* __restrict__ down, const float* __restrict__ h
     float part = row_dot<QKM_TYPE_Q8_0>(down + (size_t)o * row_bytes(QKM_TYPE_Q8_0, d.n_ff),
                                         h + ((size_t)t * (d.n_used + 1) + d.n_used) * d.n_ff, d.n_ff, lane);
     part = warp_sum(part);
-    if (lane == 0) y2[(size_t)t * d.n_embd + o] = sel[t].w_shared * part;
+    if (lane == 0) {
+        const float shared = sel[t].w_shared * part;
+        if (contrib != nullptr) {
+            float v = 0.f;
+            for (uint32_t s = 0; s < d.n_used; ++s) v += contrib[((size_t)t * d.n_used + s) * d.n_embd + o];
+            y2[(size_t)t * d.n_embd + o] = v + shared;
+        } else {
+            y2[(size_t)t * d.n_embd + o] = shared;
+        }
+    }
 }
 
 cudaError_t launch_shared_down(const Launch& L, const qkm_dims& d, const void* down, const float* h,
-                               const qkm_sel* sel, float* y2, uint32_t n_tokens) {
+                               const qkm_sel* sel, float* y2, uint32_t n_tokens, const float* contrib) {
     if (n_tokens == 0) return cudaSuccess;
     const dim3 grid((d.n_embd + 7) / 8, n_tokens);
-    shared_down_kernel<<<grid, 256, 0, L.stream>>>((const uint8_t*)down, h, sel, y2, d);
+    shared_down_kernel<<<grid, 256, 0, L.stream>>>((const uint8_t*)down, h, sel, y2, d, contrib);
     L.count();
     return cudaGetLastError();
 }

@@ -19,37 +19,54 @@
 
 #include "qkm_common.cuh"
 #include "qkm_kernels.h"
+#include "qkm_stream.cuh"
 
 namespace qkm {
 
 static constexpr float kFloor = -3.4e38f;
 
-// ---- logits: one warp per (expert, token) ---------------------------------------------
-// Also writes |router row|^2 (needed for the error bound) when row_norm2 != NULL.
+// ---- logits: one warp per expert row, kTokPerWarp tokens per pass ---------------------------
+// Each lane adds its K/32 products in a fixed order (8-element units lane, lane+32, ...)
+// and the lanes meet in a 5-level tree: the order the error bound of the refined
+// selection assumes.  Also writes |router row|^2 when row_norm2 != NULL.
+static constexpr int kTokPerWarp = 4;
+
 template <int TYPE>
 __global__ void __launch_bounds__(256)
 logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, float* __restrict__ logits,
-              float* __restrict__ row_norm2, uint32_t n_expert, uint32_t K) {
+              float* __restrict__ row_norm2, uint32_t n_expert, uint32_t K, uint32_t n_tokens) {
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t e = blockIdx.x * 8u + warp;
-    const uint32_t t = blockIdx.y;
+    const uint32_t t0 = blockIdx.y * kTokPerWarp;
     if (e >= n_expert) return;
     const uint8_t* row = router + (size_t)e * row_bytes(TYPE, K);
-    const float* xt = x + (size_t)t * K;
-    float acc = 0.f, nrm = 0.f;
+    float acc[kTokPerWarp], nrm = 0.f;
+#pragma unroll
+    for (int j = 0; j < kTokPerWarp; ++j) acc[j] = 0.f;
     for (uint32_t u = lane; u < K / 8; u += 32) {
         float w[8];
         dequant8<TYPE>(row, u * 8, w);
-        const float4 a = *reinterpret_cast<const float4*>(xt + u * 8);
-        const float4 b = *reinterpret_cast<const float4*>(xt + u * 8 + 4);
-        acc += w[0] * a.x; acc += w[1] * a.y; acc += w[2] * a.z; acc += w[3] * a.w;
-        acc += w[4] * b.x; acc += w[5] * b.y; acc += w[6] * b.z; acc += w[7] * b.w;
 #pragma unroll
         for (int i = 0; i < 8; ++i) nrm += w[i] * w[i];
+#pragma unroll
+        for (int j = 0; j < kTokPerWarp; ++j) {
+            if (t0 + j < n_tokens) {
+                const float* xt = x + (size_t)(t0 + j) * K + u * 8;
+                const float4 a = *reinterpret_cast<const float4*>(xt);
+                const float4 b = *reinterpret_cast<const float4*>(xt + 4);
+                float s = acc[j];
+                s += w[0] * a.x; s += w[1] * a.y; s += w[2] * a.z; s += w[3] * a.w;
+                s += w[4] * b.x; s += w[5] * b.y; s += w[6] * b.z; s += w[7] * b.w;
+                acc[j] = s;
+            }
+        }
     }
-    acc = warp_sum(acc);
-    if (lane == 0) logits[(size_t)t * n_expert + e] = acc;
-    if (row_norm2 != nullptr && t == 0) {
+#pragma unroll
+    for (int j = 0; j < kTokPerWarp; ++j) {
+        const float v = warp_sum(acc[j]);
+        if (lane == 0 && t0 + j < n_tokens) logits[(size_t)(t0 + j) * n_expert + e] = v;
+    }
+    if (row_norm2 != nullptr && blockIdx.y == 0) {
         nrm = warp_sum(nrm);
         if (lane == 0) row_norm2[e] = nrm;
     }
@@ -58,12 +75,12 @@ logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, f
 cudaError_t launch_logits(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
                           const float* x, float* logits, float* row_norm2, uint32_t n_tokens) {
     if (n_tokens == 0) return cudaSuccess;
-    const dim3 grid((d.n_expert + 7) / 8, n_tokens);
+    const dim3 grid((d.n_expert + 7) / 8, (n_tokens + kTokPerWarp - 1) / kTokPerWarp);
     const uint8_t* r = (const uint8_t*)router;
     if (router_type == QKM_TYPE_F32)
-        logits_kernel<QKM_TYPE_F32><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd);
+        logits_kernel<QKM_TYPE_F32><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd, n_tokens);
     else if (router_type == QKM_TYPE_F16)
-        logits_kernel<QKM_TYPE_F16><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd);
+        logits_kernel<QKM_TYPE_F16><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd, n_tokens);
     else
         return cudaErrorInvalidValue;
     L.count();
@@ -183,7 +200,8 @@ template <int TYPE>
 __global__ void __launch_bounds__(256)
 refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict__ logits,
                      const float* __restrict__ row_norm2, const float* __restrict__ gis,
-                     const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d) {
+                     const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d,
+                     int8_t* __restrict__ xplanes, float* __restrict__ xscale) {
     __shared__ unsigned long long s_warp[8];
     __shared__ double s_red[8];
     __shared__ float s_f[8];
@@ -199,6 +217,12 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     const uint32_t pid0 = id0 < d.n_expert ? id0 : 0xFFFFFFFEu;
     const uint32_t pid1 = id1 < d.n_expert ? id1 : 0xFFFFFFFEu;
 
+    // the streaming expert kernels read x as int8 digit planes: encode it here, where the
+    // row is being read anyway
+    if (xplanes != nullptr) {
+        __shared__ float s_max[8];
+        block_encode_digits(xt, xplanes + (size_t)t * 4 * d.n_embd, xscale + t, d.n_embd, s_max);
+    }
     // |x|^2 and max |row|^2 for the error bound
     float xs = 0.f, rn = 0.f;
     for (uint32_t k = tid; k < d.n_embd; k += 256) xs += xt[k] * xt[k];
@@ -311,7 +335,7 @@ size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert) {
 
 cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t router_type,
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
-                                uint32_t n_tokens, void* scratch) {
+                                uint32_t n_tokens, void* scratch, int8_t* xplanes, float* xscale) {
     if (n_tokens == 0) return cudaSuccess;
     float* logits = (float*)scratch;
     float* norm2 = logits + (size_t)n_tokens * d.n_expert;
@@ -319,9 +343,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
     if (e != cudaSuccess) return e;
     const uint8_t* r = (const uint8_t*)router;
     if (router_type == QKM_TYPE_F32)
-        refine_select_kernel<QKM_TYPE_F32><<<n_tokens, 256, 0, L.stream>>>(r, logits, norm2, gis, x, sel, d);
+        refine_select_kernel<QKM_TYPE_F32><<<n_tokens, 256, 0, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
     else
-        refine_select_kernel<QKM_TYPE_F16><<<n_tokens, 256, 0, L.stream>>>(r, logits, norm2, gis, x, sel, d);
+        refine_select_kernel<QKM_TYPE_F16><<<n_tokens, 256, 0, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
     L.count();
     return cudaGetLastError();
 }
@@ -331,16 +355,33 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
 // ascending (token, slot) order (the reference leaves the order unspecified,
 // moe_group_pairs.comp:3-5).  With an expert-parallel view only resident experts
 // get ranges, indexed from 0.
-__global__ void __launch_bounds__(256)
+//
+// When `plan` is given the same launch also cuts the work of the streaming kernels into
+// items: for each expert with pairs, its tokens in groups of `tok_per_item`, times the
+// row chunks of the gate/up matrices (items_gu) and of the down matrix (items_dn).
+// The shared expert gets its own lists: every token is a "pair" (token, slot n_used)
+// stored after the routed pairs, in groups of tok_per_item.
+struct PlanArgs {
+    StreamItem* items_gu;
+    StreamItem* items_dn;
+    StreamItem* items_sh_gu;
+    StreamItem* items_sh_dn;
+    uint32_t* n_items;   // [0] routed gate/up, [1] routed down, [2] shared gate/up, [3] shared down
+    uint32_t chunks_gu, chunks_dn, tok_per_item;
+};
+
+__global__ void __launch_bounds__(512)
 group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t n_expert, uint32_t n_used,
                    uint32_t expert_first, uint32_t expert_count, uint32_t n_chunks,
-                   uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs) {
-    extern __shared__ uint32_t s_cnt[];  // [n_chunks][expert_count], then totals [expert_count]
+                   uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, PlanArgs plan) {
+    extern __shared__ __align__(8) uint32_t s_dyn[];  // scan [512 x u64], counters [n_chunks][expert_count], totals
+    uint32_t* s_scan = s_dyn;
+    uint32_t* s_cnt = s_dyn + 1024;
     uint32_t* s_tot = s_cnt + (size_t)n_chunks * expert_count;
     const uint32_t tid = threadIdx.x;
     const uint32_t np = n_tokens * n_used;
     const uint32_t chunk = (np + n_chunks - 1) / n_chunks;
-    for (uint32_t i = tid; i < n_chunks * expert_count; i += 256) s_cnt[i] = 0;
+    for (uint32_t i = tid; i < n_chunks * expert_count; i += 512) s_cnt[i] = 0;
     __syncthreads();
     const uint32_t p0 = tid * chunk, p1 = min(np, p0 + chunk);
     if (tid < n_chunks) {
@@ -351,7 +392,7 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
         }
     }
     __syncthreads();
-    for (uint32_t e = tid; e < expert_count; e += 256) {
+    for (uint32_t e = tid; e < expert_count; e += 512) {
         uint32_t run = 0;
         for (uint32_t c = 0; c < n_chunks; ++c) {
             const uint32_t v = s_cnt[(size_t)c * expert_count + e];
@@ -361,15 +402,53 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
         s_tot[e] = run;
     }
     __syncthreads();
-    if (tid == 0) {
-        uint32_t off = 0;
-        for (uint32_t e = 0; e < expert_count; ++e) {
-            const uint32_t v = s_tot[e];
-            s_tot[e] = off;
-            offsets[e] = off;
-            off += v;
+    // exclusive scan of the per-expert totals (expert_count <= 512: one element per thread)
+    const uint32_t mine = tid < expert_count ? s_tot[tid] : 0u;
+    const uint32_t groups = plan.n_items ? (mine + plan.tok_per_item - 1) / plan.tok_per_item : 0u;
+    {
+        // two scans at once: pair counts in the low half, token groups in the high half
+        unsigned long long v = (unsigned long long)mine | ((unsigned long long)groups << 32);
+        unsigned long long* s64 = reinterpret_cast<unsigned long long*>(s_scan);
+        s64[tid] = v;
+        __syncthreads();
+        for (uint32_t o = 1; o < 512; o <<= 1) {
+            const unsigned long long add = tid >= o ? s64[tid - o] : 0ull;
+            __syncthreads();
+            s64[tid] += add;
+            __syncthreads();
         }
-        offsets[expert_count] = off;
+        const unsigned long long incl = s64[tid];
+        const uint32_t off = (uint32_t)(incl & 0xFFFFFFFFull) - mine;
+        const uint32_t g0 = (uint32_t)(incl >> 32) - groups;
+        if (tid < expert_count) { offsets[tid] = off; s_tot[tid] = off; }
+        if (tid == 511) offsets[expert_count] = (uint32_t)(incl & 0xFFFFFFFFull);
+        if (plan.n_items) {
+            if (tid == 511) {
+                plan.n_items[0] = (uint32_t)(incl >> 32) * plan.chunks_gu;
+                plan.n_items[1] = (uint32_t)(incl >> 32) * plan.chunks_dn;
+            }
+            for (uint32_t gi = 0; gi < groups; ++gi) {
+                StreamItem it;
+                it.expert = (uint16_t)tid;
+                it.ntok = (uint8_t)min(plan.tok_per_item, mine - gi * plan.tok_per_item);
+                it.pair_off = off + gi * plan.tok_per_item;
+                for (uint32_t c = 0; c < plan.chunks_gu; ++c) { it.chunk = (uint8_t)c; plan.items_gu[(size_t)(g0 + gi) * plan.chunks_gu + c] = it; }
+                for (uint32_t c = 0; c < plan.chunks_dn; ++c) { it.chunk = (uint8_t)c; plan.items_dn[(size_t)(g0 + gi) * plan.chunks_dn + c] = it; }
+            }
+        }
+    }
+    if (plan.n_items && plan.items_sh_gu) {
+        const uint32_t sh_groups = (n_tokens + plan.tok_per_item - 1) / plan.tok_per_item;
+        for (uint32_t t = tid; t < n_tokens; t += 512) pairs[np + t] = (t << 4) | n_used;
+        for (uint32_t gi = tid; gi < sh_groups; gi += 512) {
+            StreamItem it;
+            it.expert = 0;
+            it.ntok = (uint8_t)min(plan.tok_per_item, n_tokens - gi * plan.tok_per_item);
+            it.pair_off = np + gi * plan.tok_per_item;
+            for (uint32_t c = 0; c < plan.chunks_gu; ++c) { it.chunk = (uint8_t)c; plan.items_sh_gu[(size_t)gi * plan.chunks_gu + c] = it; }
+            for (uint32_t c = 0; c < plan.chunks_dn; ++c) { it.chunk = (uint8_t)c; plan.items_sh_dn[(size_t)gi * plan.chunks_dn + c] = it; }
+        }
+        if (tid == 0) { plan.n_items[2] = sh_groups * plan.chunks_gu; plan.n_items[3] = sh_groups * plan.chunks_dn; }
     }
     __syncthreads();
     if (tid < n_chunks) {
@@ -384,26 +463,41 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
     }
 }
 
+static cudaError_t group_pairs_launch(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
+                                      uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,
+                                      uint32_t expert_count, const PlanArgs& plan) {
+    if (expert_count == 0) { expert_first = 0; expert_count = d.n_expert; }
+    if (expert_count > 512) return cudaErrorInvalidValue;
+    // one chunk of pairs per thread: enough chunks to spread the pairs, no more counters
+    // than 32768 words of shared memory hold
+    const uint32_t np = n_tokens * d.n_used;
+    uint32_t n_chunks = 32768u / expert_count;
+    if (n_chunks > 512) n_chunks = 512;
+    const uint32_t want = (np + 7) / 8;
+    if (n_chunks > want) n_chunks = want ? want : 1;
+    const size_t smem = ((size_t)n_chunks * expert_count + expert_count + 2 * 512) * sizeof(uint32_t);
+    cudaError_t e = cudaFuncSetAttribute(group_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)((32768 + 512 + 1024) * sizeof(uint32_t)));
+    if (e != cudaSuccess) return e;
+    group_pairs_kernel<<<1, 512, smem, L.stream>>>(sel, n_tokens, d.n_expert, d.n_used, expert_first,
+                                                   expert_count, n_chunks, offsets, pairs, plan);
+    L.count();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_group_pairs(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                                uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,
                                uint32_t expert_count) {
-    if (expert_count == 0) { expert_first = 0; expert_count = d.n_expert; }
-    // 32768 counters of shared memory: as many chunks (threads) as fit, at most 256
-    uint32_t n_chunks = 32768u / expert_count;
-    if (n_chunks > 256) n_chunks = 256;
-    if (n_chunks == 0) return cudaErrorInvalidValue;
-    const size_t smem = ((size_t)n_chunks * expert_count + expert_count) * sizeof(uint32_t);
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(group_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             (int)((32768 + 512) * sizeof(uint32_t)));
-        if (e != cudaSuccess) return e;
-        configured = true;
-    }
-    group_pairs_kernel<<<1, 256, smem, L.stream>>>(sel, n_tokens, d.n_expert, d.n_used, expert_first,
-                                                   expert_count, n_chunks, offsets, pairs);
-    L.count();
-    return cudaGetLastError();
+    return group_pairs_launch(L, d, sel, n_tokens, offsets, pairs, expert_first, expert_count, PlanArgs{});
+}
+
+cudaError_t launch_group_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
+                              uint32_t* offsets, uint32_t* pairs, uint32_t expert_first, uint32_t expert_count,
+                              StreamItem* items_gu, uint32_t chunks_gu, StreamItem* items_dn,
+                              uint32_t chunks_dn, StreamItem* items_sh_gu, StreamItem* items_sh_dn,
+                              uint32_t tok_per_item, uint32_t* n_items) {
+    PlanArgs plan{items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, chunks_gu, chunks_dn, tok_per_item};
+    return group_pairs_launch(L, d, sel, n_tokens, offsets, pairs, expert_first, expert_count, plan);
 }
 
 }  // namespace qkm

@@ -104,6 +104,42 @@ __device__ __forceinline__ uint32_t digits4(int v) {
     const int d2 = ((v + 64) & 127) - 64; v = (v - d2) >> 7;
     return (uint32_t)(d0 & 255) | ((uint32_t)(d1 & 255) << 8) | ((uint32_t)(d2 & 255) << 16) | ((uint32_t)(v & 255) << 24);
 }
+// Encodes one row x[K] into digit planes, called by all 256 threads of a block.
+// Plane layout per row: [kb = k/256][digit 0..3][256], so the four planes of one
+// 256-column block are 1 KB of consecutive memory.  scale receives 2^-p; a row that
+// holds NaN/Inf gets all-zero planes and a NaN scale (its outputs become NaN).
+__device__ __forceinline__ void block_encode_digits(const float* __restrict__ xt, int8_t* __restrict__ pl,
+                                                    float* __restrict__ scale, uint32_t K, float* s_max /*[8]*/) {
+    const uint32_t tid = threadIdx.x;
+    float m = 0.f;
+    bool bad = false;
+    for (uint32_t k = tid; k < K; k += 256) {
+        const float v = xt[k];
+        bad |= !(fabsf(v) <= 3.0e38f);
+        m = fmaxf(m, fabsf(v));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    if ((tid & 31u) == 0) s_max[tid >> 5] = m;
+    __syncthreads();
+    m = s_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, s_max[w]);
+    const int p = digit_exponent(m);
+    const float up = ldexpf(1.0f, p);
+    for (uint32_t k = tid; k < K; k += 256) {
+        const uint32_t dgt = any_bad ? 0u : digits4(__float2int_rn(xt[k] * up));
+        int8_t* q = pl + (size_t)(k >> 8) * 1024 + (k & 255u);
+        q[0] = (int8_t)(dgt & 255u);
+        q[256] = (int8_t)((dgt >> 8) & 255u);
+        q[512] = (int8_t)((dgt >> 16) & 255u);
+        q[768] = (int8_t)(dgt >> 24);
+    }
+    if (tid == 0) *scale = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
+    __syncthreads();
+}
+
 // three bf16 pieces whose sum is x exactly (24 significant bits)
 __device__ __forceinline__ void bf16_pieces(float x, __nv_bfloat16& p0, __nv_bfloat16& p1, __nv_bfloat16& p2) {
     p0 = __float2bfloat16_rn(x);
