@@ -164,7 +164,8 @@ def run_decode(args, pkg, syn):
         raise SystemExit("expert-parallel decode is launched through --workload ep (not built into this path yet)")
 
     ctx = pkg.Context(dims, n_layer=L, max_tokens=S, device=local_rank)
-    stream = torch.cuda.current_stream(dev)
+    stream = torch.cuda.Stream(dev)   # a real stream: the stack is replayed as a CUDA graph
+    torch.cuda.set_stream(stream)
     ctx.set_stream(stream.cuda_stream)
     orc_mod = entry.oracle_module()
     orc = orc_mod.Oracle()

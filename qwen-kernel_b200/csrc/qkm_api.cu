@@ -61,6 +61,10 @@ struct qkm_ctx {
     uint32_t* status = nullptr;       // kernel status word (device)
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
+    // the decode stack as a CUDA graph: captured on first use for a given argument set
+    cudaGraphExec_t stack_graph = nullptr;
+    struct { uint32_t first, count, n; const float* x; float* y; cudaStream_t stream; } stack_key{};
+    uint64_t stack_graph_launches = 0;
     // per-stage profiling of the fused calls
     static constexpr int kMaxStages = 16;
     bool profiling = false;
@@ -246,6 +250,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status};
     for (void* p : scratch) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
+    if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
     for (cudaEvent_t ev : c->prof_ev) if (ev) cudaEventDestroy(ev);
     delete c;
 }
@@ -329,6 +334,7 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
                           w->gate_shexp, w->up_shexp, w->down_shexp};
     for (const void* p : src) if (!p) return fail(c, QKM_ERR_ARG, "layer %u: NULL tensor pointer", layer);
     QKM_CUDA(c, cudaSetDevice(c->device));
+    if (c->stack_graph) { cudaGraphExecDestroy(c->stack_graph); c->stack_graph = nullptr; }
     qkm_layer_dev& l = c->layers[layer];
     for (int i = 0; i < 8; ++i) {
         const size_t bytes = tensor_bytes(c, i, *w);
@@ -471,7 +477,7 @@ extern "C" QKM_API int qkm_gemv(qkm_ctx* c, uint32_t type, const void* W, const 
     if (be == 0) return fail(c, QKM_ERR_TYPE, "qkm_gemv: type %u unsupported", type);
     if (K == 0 || K % be || K % 8) return fail(c, QKM_ERR_ARG, "qkm_gemv: K=%u must be a multiple of the block size %u and of 8", K, be);
     if (n > 65535) return fail(c, QKM_ERR_BOUNDS, "qkm_gemv: n=%u exceeds 65535", n);
-    QKM_LAUNCH(c, launch_gemv(c->L(), type, W, x, y, M, K, n));
+    QKM_LAUNCH(c, launch_gemv_stream(c->L(), type, W, x, y, M, K, n, (uint32_t)c->n_sms, c->status));
     return QKM_OK;
 }
 
@@ -517,12 +523,11 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xplanes, c->xscale, c->pairs,
                                        c->items_gu, c->n_items, c->h, c->hpieces, nb, c->status));
     c->prof_mark("moe.gu");
-    QKM_LAUNCH(c, launch_down_stream(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->pairs, c->items_dn,
-                                     c->n_items + 1, c->contrib_s, y, c->arrivals, nb, c->status));
-    c->prof_mark("moe.dn");
     QKM_LAUNCH(c, launch_down_stream(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, c->sel, c->pairs, c->items_sh_dn,
-                                     c->n_items + 3, c->contrib_s, y, c->arrivals, nb, c->status));
+                                     c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));
     c->prof_mark("moe.shared_dn");
+    QKM_LAUNCH(c, launch_down_tok(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->y2, y, n, nb, c->status));
+    c->prof_mark("moe.dn");
     return QKM_OK;
 }
 
@@ -559,13 +564,56 @@ extern "C" QKM_API int qkm_moe_forward_host(qkm_ctx* c, uint32_t layer, int mode
     return check_status(c);
 }
 
+static int decode_stack_eager(qkm_ctx* c, uint32_t first, uint32_t count, const float* x, uint32_t n, float* y) {
+    const size_t stride = (size_t)n * c->cfg.dims.n_embd;
+    for (uint32_t l = 0; l < count; ++l)
+        if (int rc = qkm_moe_decode(c, first + l, x + l * stride, n, y + l * stride)) return rc;
+    return QKM_OK;
+}
+
+// The per-layer launches of the stack are captured into a CUDA graph the first time an
+// argument set is seen and replayed afterwards (a launch-bound inner loop: each layer is a
+// handful of short kernels).  Capture needs a real stream: on the legacy default stream,
+// while profiling, or after an upload, the launches are issued one by one.
 extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t count, const float* x,
                                             uint32_t n, float* y) {
     if (!c || !x || !y) return QKM_ERR_ARG;
     if ((uint64_t)first + count > c->cfg.n_layer) return fail(c, QKM_ERR_BOUNDS, "layers [%u,%u) out of range", first, first + count);
-    const size_t stride = (size_t)n * c->cfg.dims.n_embd;
+    if (int rc = check_tokens(c, n)) return rc;
     for (uint32_t l = 0; l < count; ++l)
-        if (int rc = qkm_moe_decode(c, first + l, x + l * stride, n, y + l * stride)) return rc;
+        if (int rc = layer_ready(c, first + l)) return rc;
+    if (c->stream == nullptr || c->profiling || count < 2) return decode_stack_eager(c, first, count, x, n, y);
+    auto& k = c->stack_key;
+    const bool same = c->stack_graph && k.first == first && k.count == count && k.n == n && k.x == x && k.y == y &&
+                      k.stream == c->stream;
+    if (!same) {
+        if (c->stack_graph) { cudaGraphExecDestroy(c->stack_graph); c->stack_graph = nullptr; }
+        const uint64_t before = c->launches;
+        if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
+            cudaGetLastError();
+            return decode_stack_eager(c, first, count, x, n, y);
+        }
+        const int rc = decode_stack_eager(c, first, count, x, n, y);
+        cudaGraph_t graph = nullptr;
+        const cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
+        c->stack_graph_launches = c->launches - before;
+        c->launches = before;
+        if (rc != QKM_OK || e != cudaSuccess || !graph) {
+            if (graph) cudaGraphDestroy(graph);
+            cudaGetLastError();
+            return rc != QKM_OK ? rc : decode_stack_eager(c, first, count, x, n, y);
+        }
+        const cudaError_t ei = cudaGraphInstantiate(&c->stack_graph, graph, 0);
+        cudaGraphDestroy(graph);
+        if (ei != cudaSuccess) {
+            c->stack_graph = nullptr;
+            cudaGetLastError();
+            return decode_stack_eager(c, first, count, x, n, y);
+        }
+        k.first = first; k.count = count; k.n = n; k.x = x; k.y = y; k.stream = c->stream;
+    }
+    QKM_CUDA(c, cudaGraphLaunch(c->stack_graph, c->stream));
+    c->launches += c->stack_graph_launches;
     return QKM_OK;
 }
 

@@ -128,7 +128,8 @@ down_stream_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __res
             loaded_pair_off = it.pair_off; loaded_ntok = it.ntok;
             const uint32_t ts = g >> 2, piece = g & 3u;
             if (ts < it.ntok && piece < 3) {
-                const __nv_bfloat16* src = hpieces + ((size_t)(it.pair_off + ts) * 3 + piece) * d.n_ff +
+                const uint32_t pr = pairs[it.pair_off + ts];
+                const __nv_bfloat16* src = hpieces + ((size_t)((pr >> 4) * n_slots + (pr & 15u)) * 3 + piece) * d.n_ff +
                                            ((size_t)(8 * kb) * 4 + t) * 8;
 #pragma unroll
                 for (int sb = 0; sb < 8; ++sb) {
@@ -245,28 +246,35 @@ down_stream_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __res
                 for (uint32_t w = 0; w < KB; ++w) sum += red[(team * KB + w) * dn::kRedFloats + row * 2 + ts];
                 const uint32_t pr = pairs[it.pair_off + ts], tok = pr >> 4, slot = pr & 15u;
                 const float wgt = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
-                contrib[((size_t)tok * n_slots + slot) * d.n_embd + row0 + row] = wgt * sum;
+                if (arrivals != nullptr) contrib[((size_t)tok * n_slots + slot) * d.n_embd + row0 + row] = wgt * sum;
+                else y[(size_t)tok * d.n_embd + row0 + row] = wgt * sum;   // single-slot use: y is this slot's term
             }
         }
-        __threadfence();
-        asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(team_threads) : "memory");
-        if (lt < it.ntok) {
-            const uint32_t tok = pairs[it.pair_off + lt] >> 4;
-            const uint32_t old = atomicAdd(&arrivals[(size_t)tok * units_per_row + unit_idx], 1u);
-            const bool last = old + 1 == n_slots;
-            if (last) arrivals[(size_t)tok * units_per_row + unit_idx] = 0;  // ready for the next call
-            flags[team * 2 + lt] = last ? 1u : 0u;
-        }
-        asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(team_threads) : "memory");
-        for (uint32_t ts = 0; ts < it.ntok; ++ts) {
-            if (flags[team * 2 + ts] == 0) continue;
+        if (arrivals != nullptr) {
             __threadfence();
-            const uint32_t tok = pairs[it.pair_off + ts] >> 4;
-            for (uint32_t row = lt; row < dn::kUnitRows; row += team_threads) {
-                const float* cp = contrib + (size_t)tok * n_slots * d.n_embd + row0 + row;
-                float v = 0.f;
-                for (uint32_t s = 0; s < d.n_used; ++s) v += __ldcg(cp + (size_t)s * d.n_embd);
-                y[(size_t)tok * d.n_embd + row0 + row] = v + __ldcg(cp + (size_t)d.n_used * d.n_embd);
+            asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(team_threads) : "memory");
+            if (lt < it.ntok) {
+                const uint32_t tok = pairs[it.pair_off + lt] >> 4;
+                const uint32_t old = atomicAdd(&arrivals[(size_t)tok * units_per_row + unit_idx], 1u);
+                const bool last = old + 1 == n_slots;
+                if (last) arrivals[(size_t)tok * units_per_row + unit_idx] = 0;  // ready for the next call
+                flags[team * 2 + lt] = last ? 1u : 0u;
+            }
+            asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(team_threads) : "memory");
+            for (uint32_t ts = 0; ts < it.ntok; ++ts) {
+                if (flags[team * 2 + ts] == 0) continue;
+                __threadfence();
+                const uint32_t tok = pairs[it.pair_off + ts] >> 4;
+                for (uint32_t row = lt; row < dn::kUnitRows; row += team_threads) {
+                    const float* cp = contrib + (size_t)tok * n_slots * d.n_embd + row0 + row;
+                    float part[16];
+#pragma unroll
+                    for (int s = 0; s < 16; ++s) part[s] = (uint32_t)s < n_slots ? __ldcg(cp + (size_t)s * d.n_embd) : 0.f;
+                    float v = 0.f;
+#pragma unroll
+                    for (int s = 0; s < 16; ++s) v += part[s];  // slots in order, the shared expert last
+                    y[(size_t)tok * d.n_embd + row0 + row] = v;
+                }
             }
         }
         asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(team_threads) : "memory");

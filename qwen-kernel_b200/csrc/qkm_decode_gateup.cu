@@ -291,12 +291,12 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
                 const uint32_t pr = pairs[it.pair_off + ts], tok = pr >> 4, slot = pr & 15u;
                 const uint32_t r_ff = it.chunk * gu::kRowsPerItem + (unit % gu::kUnitsPerItem) * (16 * gu::kUnitTiles) + row;
                 h[((size_t)tok * (d.n_used + 1) + slot) * d.n_ff + r_ff] = hv;
-                // bf16 pieces in the down kernel's B-operand order: [pair][piece][sub-block][t][8]
+                // bf16 pieces in the down kernels' B-operand order: [token][slot][piece][sub-block][t][8]
                 // with the 8 = elements (4t, 16+4t, 4t+1, 17+4t, 4t+2, 18+4t, 4t+3, 19+4t)
                 __nv_bfloat16 p0, p1, p2;
                 bf16_pieces(hv, p0, p1, p2);
                 const uint32_t e32 = r_ff & 31u, tt = (e32 & 15u) >> 2, pos = 2 * (e32 & 3u) + (e32 >> 4);
-                const size_t o = (((size_t)(it.pair_off + ts) * 3) * (d.n_ff / 32) + (r_ff >> 5)) * 32 + tt * 8 + pos;
+                const size_t o = (((size_t)(tok * (d.n_used + 1) + slot) * 3) * (d.n_ff / 32) + (r_ff >> 5)) * 32 + tt * 8 + pos;
                 hpieces[o] = p0; hpieces[o + d.n_ff] = p1; hpieces[o + 2 * (size_t)d.n_ff] = p2;
             }
         }

@@ -43,6 +43,10 @@ cudaError_t launch_down_stream(const Launch& L, const qkm_dims& d, uint32_t type
                                const StreamItem* items, const uint32_t* n_items, float* contrib, float* y,
                                uint32_t* arrivals, uint32_t n_blocks, uint32_t* status);
 uint32_t down_stream_unit_rows();
+// token-major routed down: y[t] = sum_s w_s * D[ids_s].h[t][s] + y2[t] (y2 may be NULL)
+cudaError_t launch_down_tok(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles,
+                            const void* hpieces, const qkm_sel* sel, const float* y2, float* y,
+                            uint32_t n_tokens, uint32_t n_blocks, uint32_t* status);
 uint32_t gateup_stream_rows_per_item();
 uint32_t down_stream_rows_per_item();
 
@@ -50,6 +54,10 @@ uint32_t down_stream_rows_per_item();
 cudaError_t launch_dequant(const Launch& L, uint32_t type, const void* blocks, float* y, uint64_t n_elems);
 cudaError_t launch_gemv(const Launch& L, uint32_t type, const void* W, const float* x, float* y,
                         uint32_t M, uint32_t K, uint32_t n);
+
+// streamed form (bulk-copy ring) with the generic kernel for tail rows / unaligned tensors
+cudaError_t launch_gemv_stream(const Launch& L, uint32_t type, const void* W, const float* x, float* y,
+                               uint32_t M, uint32_t K, uint32_t n, uint32_t n_sms, uint32_t* status);
 
 // ---- qkm_route.cu
 // Scratch the refined router needs: n_tokens * n_expert f32 logits + n_expert f32 row norms.

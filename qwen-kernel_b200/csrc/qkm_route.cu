@@ -25,57 +25,85 @@ namespace qkm {
 
 static constexpr float kFloor = -3.4e38f;
 
-// ---- logits: one warp per expert row, kTokPerWarp tokens per pass ---------------------------
-// Each lane adds its K/32 products in a fixed order (8-element units lane, lane+32, ...)
-// and the lanes meet in a 5-level tree: the order the error bound of the refined
+// ---- logits: two expert rows per block, four warps (column quarters) per row ----------------
+// Every lane owns at most kMaxUnits 8-element units of its quarter, loads them and the
+// matching x values of kTokPerBlock tokens up front (one memory round trip), adds its
+// products in a fixed order, then the lanes meet in a 5-level tree and the four quarters
+// in shared memory: fewer sequential additions than the error bound of the refined
 // selection assumes.  Also writes |router row|^2 when row_norm2 != NULL.
-static constexpr int kTokPerWarp = 4;
+static constexpr int kTokPerBlock = 4;
+static constexpr int kMaxUnits = 2;  // K <= 2048 in one pass; longer rows loop
 
 template <int TYPE>
 __global__ void __launch_bounds__(256)
 logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, float* __restrict__ logits,
               float* __restrict__ row_norm2, uint32_t n_expert, uint32_t K, uint32_t n_tokens) {
+    __shared__ float s_part[8][kTokPerBlock + 1];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
-    const uint32_t e = blockIdx.x * 8u + warp;
-    const uint32_t t0 = blockIdx.y * kTokPerWarp;
-    if (e >= n_expert) return;
-    const uint8_t* row = router + (size_t)e * row_bytes(TYPE, K);
-    float acc[kTokPerWarp], nrm = 0.f;
+    const uint32_t e = blockIdx.x * 2u + (warp >> 2), quarter = warp & 3u;
+    const uint32_t t0 = blockIdx.y * kTokPerBlock;
+    const uint32_t units_q = K / 32;  // units per quarter
+    float acc[kTokPerBlock], nrm = 0.f;
 #pragma unroll
-    for (int j = 0; j < kTokPerWarp; ++j) acc[j] = 0.f;
-    for (uint32_t u = lane; u < K / 8; u += 32) {
-        float w[8];
-        dequant8<TYPE>(row, u * 8, w);
+    for (int j = 0; j < kTokPerBlock; ++j) acc[j] = 0.f;
+    if (e < n_expert) {
+        const uint8_t* row = router + (size_t)e * row_bytes(TYPE, K);
+        for (uint32_t u0 = lane; u0 < units_q; u0 += 32 * kMaxUnits) {
+            float w[kMaxUnits][8];
+            float4 xa[kMaxUnits][kTokPerBlock], xb[kMaxUnits][kTokPerBlock];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) nrm += w[i] * w[i];
+            for (int i = 0; i < kMaxUnits; ++i) {
+                const uint32_t u = u0 + 32 * i;
+                if (u < units_q) {
+                    const uint32_t k = (quarter * units_q + u) * 8;
+                    dequant8<TYPE>(row, k, w[i]);
 #pragma unroll
-        for (int j = 0; j < kTokPerWarp; ++j) {
-            if (t0 + j < n_tokens) {
-                const float* xt = x + (size_t)(t0 + j) * K + u * 8;
-                const float4 a = *reinterpret_cast<const float4*>(xt);
-                const float4 b = *reinterpret_cast<const float4*>(xt + 4);
-                float s = acc[j];
-                s += w[0] * a.x; s += w[1] * a.y; s += w[2] * a.z; s += w[3] * a.w;
-                s += w[4] * b.x; s += w[5] * b.y; s += w[6] * b.z; s += w[7] * b.w;
-                acc[j] = s;
+                    for (int j = 0; j < kTokPerBlock; ++j) {
+                        const uint32_t tt = min(t0 + j, n_tokens - 1);
+                        const float* xt = x + (size_t)tt * K + k;
+                        xa[i][j] = *reinterpret_cast<const float4*>(xt);
+                        xb[i][j] = *reinterpret_cast<const float4*>(xt + 4);
+                    }
+                }
+            }
+#pragma unroll
+            for (int i = 0; i < kMaxUnits; ++i) {
+                if (u0 + 32 * i < units_q) {
+#pragma unroll
+                    for (int q = 0; q < 8; ++q) nrm += w[i][q] * w[i][q];
+#pragma unroll
+                    for (int j = 0; j < kTokPerBlock; ++j) {
+                        float s = acc[j];
+                        s += w[i][0] * xa[i][j].x; s += w[i][1] * xa[i][j].y; s += w[i][2] * xa[i][j].z; s += w[i][3] * xa[i][j].w;
+                        s += w[i][4] * xb[i][j].x; s += w[i][5] * xb[i][j].y; s += w[i][6] * xb[i][j].z; s += w[i][7] * xb[i][j].w;
+                        acc[j] = s;
+                    }
+                }
             }
         }
     }
 #pragma unroll
-    for (int j = 0; j < kTokPerWarp; ++j) {
+    for (int j = 0; j < kTokPerBlock; ++j) {
         const float v = warp_sum(acc[j]);
-        if (lane == 0 && t0 + j < n_tokens) logits[(size_t)(t0 + j) * n_expert + e] = v;
+        if (lane == 0) s_part[warp][j] = v;
     }
-    if (row_norm2 != nullptr && blockIdx.y == 0) {
-        nrm = warp_sum(nrm);
-        if (lane == 0) row_norm2[e] = nrm;
+    nrm = warp_sum(nrm);
+    if (lane == 0) s_part[warp][kTokPerBlock] = nrm;
+    __syncthreads();
+    if (quarter == 0 && e < n_expert && lane <= kTokPerBlock) {
+        const float v = ((s_part[warp][lane] + s_part[warp + 1][lane]) + s_part[warp + 2][lane]) + s_part[warp + 3][lane];
+        if (lane < kTokPerBlock) {
+            if (t0 + lane < n_tokens) logits[(size_t)(t0 + lane) * n_expert + e] = v;
+        } else if (row_norm2 != nullptr && blockIdx.y == 0) {
+            row_norm2[e] = v;
+        }
     }
 }
 
 cudaError_t launch_logits(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
                           const float* x, float* logits, float* row_norm2, uint32_t n_tokens) {
     if (n_tokens == 0) return cudaSuccess;
-    const dim3 grid((d.n_expert + 7) / 8, (n_tokens + kTokPerWarp - 1) / kTokPerWarp);
+    const dim3 grid((d.n_expert + 1) / 2, (n_tokens + kTokPerBlock - 1) / kTokPerBlock);
     const uint8_t* r = (const uint8_t*)router;
     if (router_type == QKM_TYPE_F32)
         logits_kernel<QKM_TYPE_F32><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd, n_tokens);
@@ -217,26 +245,54 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     const uint32_t pid0 = id0 < d.n_expert ? id0 : 0xFFFFFFFEu;
     const uint32_t pid1 = id1 < d.n_expert ? id1 : 0xFFFFFFFEu;
 
-    // the streaming expert kernels read x as int8 digit planes: encode it here, where the
-    // row is being read anyway
-    if (xplanes != nullptr) {
-        __shared__ float s_max[8];
-        block_encode_digits(xt, xplanes + (size_t)t * 4 * d.n_embd, xscale + t, d.n_embd, s_max);
+    // One pass over the row: stage it in shared memory and gather everything that needs
+    // it - |x|^2 and max|x| (error bound, digit exponent), the shared-gate dot in f64 -
+    // together with max |router row|^2, so all global loads of this phase are in flight at once.
+    extern __shared__ float s_x[];  // n_embd floats
+    float xs = 0.f, xm = 0.f, rn = 0.f;
+    double dsg = 0.0;
+    bool bad = false;
+    for (uint32_t k = tid; k < d.n_embd; k += 256) {
+        const float v = xt[k], gv = gis[k];
+        s_x[k] = v;
+        xs += v * v;
+        xm = fmaxf(xm, fabsf(v));
+        bad |= !(fabsf(v) <= 3.0e38f);
+        dsg += (double)gv * (double)v;
     }
-    // |x|^2 and max |row|^2 for the error bound
-    float xs = 0.f, rn = 0.f;
-    for (uint32_t k = tid; k < d.n_embd; k += 256) xs += xt[k] * xt[k];
     if (id0 < d.n_expert) rn = row_norm2[id0];
     if (id1 < d.n_expert) rn = fmaxf(rn, row_norm2[id1]);
     xs = warp_sum(xs);
+    dsg = warp_sum(dsg);
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) rn = fmaxf(rn, __shfl_xor_sync(0xFFFFFFFFu, rn, o));
-    if (lane == 0) { s_f[warp] = xs; s_red[warp] = (double)rn; }
+    for (int o = 16; o > 0; o >>= 1) {
+        rn = fmaxf(rn, __shfl_xor_sync(0xFFFFFFFFu, rn, o));
+        xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
+    }
+    __shared__ float s_rn[8], s_xm[8];
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    if (lane == 0) { s_f[warp] = xs; s_red[warp] = dsg; s_rn[warp] = rn; s_xm[warp] = xm; }
     if (tid == 0) s_ncand = 0;
     __syncthreads();
-    float x2 = 0.f, r2 = 0.f;
+    float x2 = 0.f, r2 = 0.f, xmax = 0.f;
+    double sg = 0.0;
 #pragma unroll
-    for (int w = 0; w < 8; ++w) { x2 += s_f[w]; r2 = fmaxf(r2, (float)s_red[w]); }
+    for (int w = 0; w < 8; ++w) { x2 += s_f[w]; sg += s_red[w]; r2 = fmaxf(r2, s_rn[w]); xmax = fmaxf(xmax, s_xm[w]); }
+    // the streaming expert kernels read x as int8 digit planes ([kb][digit][256] per row)
+    if (xplanes != nullptr) {
+        const int p = digit_exponent(xmax);
+        const float up = ldexpf(1.0f, p);
+        int8_t* pl = xplanes + (size_t)t * 4 * d.n_embd;
+        for (uint32_t k = tid; k < d.n_embd; k += 256) {
+            const uint32_t dgt = any_bad ? 0u : digits4(__float2int_rn(s_x[k] * up));
+            int8_t* q = pl + (size_t)(k >> 8) * 1024 + (k & 255u);
+            q[0] = (int8_t)(dgt & 255u);
+            q[256] = (int8_t)((dgt >> 8) & 255u);
+            q[512] = (int8_t)((dgt >> 16) & 255u);
+            q[768] = (int8_t)(dgt >> 24);
+        }
+        if (tid == 0) xscale[t] = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
+    }
 
     // k-th largest f32 logit
     float v0 = l0, v1 = l1, kth = kFloor;
@@ -283,11 +339,12 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
             const uint32_t e = all ? base + c : s_cand[c];
             const uint8_t* row = router + (size_t)e * rb;
             double acc = 0.0;
+#pragma unroll 4
             for (uint32_t u = lane; u < d.n_embd / 8; u += 32) {
                 float w[8];
                 dequant8<TYPE>(row, u * 8, w);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc += (double)w[i] * (double)xt[u * 8 + i];
+                for (int i = 0; i < 8; ++i) acc += (double)w[i] * (double)s_x[u * 8 + i];
             }
             acc = warp_sum(acc);
             if (lane == 0) {
@@ -314,7 +371,7 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
             s_nbest = nb;
         }
     }
-    const double sg = block_dot_f64(gis, xt, d.n_embd, s_red);
+    __syncthreads();
     if (tid == 0) {
         double w[16], sum = 0.0;
         for (uint32_t i = 0; i < d.n_used; ++i) { w[i] = exp(s_best_val[i] - s_best_val[0]); sum += w[i]; }
@@ -343,9 +400,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
     if (e != cudaSuccess) return e;
     const uint8_t* r = (const uint8_t*)router;
     if (router_type == QKM_TYPE_F32)
-        refine_select_kernel<QKM_TYPE_F32><<<n_tokens, 256, 0, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
+        refine_select_kernel<QKM_TYPE_F32><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
     else
-        refine_select_kernel<QKM_TYPE_F16><<<n_tokens, 256, 0, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
+        refine_select_kernel<QKM_TYPE_F16><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
     L.count();
     return cudaGetLastError();
 }
@@ -376,7 +433,7 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
                    uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, PlanArgs plan) {
     extern __shared__ __align__(8) uint32_t s_dyn[];  // scan [512 x u64], counters [n_chunks][expert_count], totals
     uint32_t* s_scan = s_dyn;
-    uint32_t* s_cnt = s_dyn + 1024;
+    uint32_t* s_cnt = s_dyn + 1152;
     uint32_t* s_tot = s_cnt + (size_t)n_chunks * expert_count;
     const uint32_t tid = threadIdx.x;
     const uint32_t np = n_tokens * n_used;
@@ -409,23 +466,38 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
         // two scans at once: pair counts in the low half, token groups in the high half
         unsigned long long v = (unsigned long long)mine | ((unsigned long long)groups << 32);
         unsigned long long* s64 = reinterpret_cast<unsigned long long*>(s_scan);
-        s64[tid] = v;
-        __syncthreads();
-        for (uint32_t o = 1; o < 512; o <<= 1) {
-            const unsigned long long add = tid >= o ? s64[tid - o] : 0ull;
-            __syncthreads();
-            s64[tid] += add;
-            __syncthreads();
+        // inclusive scan over 512 threads: shuffles inside each warp, then the 16 warp totals
+        const uint32_t lane = tid & 31u, wrp = tid >> 5;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const unsigned long long up = __shfl_up_sync(0xFFFFFFFFu, v, o);
+            if (lane >= (uint32_t)o) v += up;
         }
-        const unsigned long long incl = s64[tid];
+        if (lane == 31) s64[wrp] = v;
+        __syncthreads();
+        if (wrp == 0) {
+            unsigned long long w = lane < 16 ? s64[lane] : 0ull;
+#pragma unroll
+            for (int o = 1; o < 16; o <<= 1) {
+                const unsigned long long up = __shfl_up_sync(0xFFFFFFFFu, w, o);
+                if (lane >= (uint32_t)o) w += up;
+            }
+            if (lane < 16) s64[16 + lane] = w;  // inclusive totals of warps 0..lane
+        }
+        __syncthreads();
+        if (wrp > 0) v += s64[16 + wrp - 1];
+        s64[32 + tid] = v;
+        __syncthreads();
+        const unsigned long long incl = v;
+        const unsigned long long last_incl = s64[32 + 511];
         const uint32_t off = (uint32_t)(incl & 0xFFFFFFFFull) - mine;
         const uint32_t g0 = (uint32_t)(incl >> 32) - groups;
         if (tid < expert_count) { offsets[tid] = off; s_tot[tid] = off; }
-        if (tid == 511) offsets[expert_count] = (uint32_t)(incl & 0xFFFFFFFFull);
+        if (tid == 511) offsets[expert_count] = (uint32_t)(last_incl & 0xFFFFFFFFull);
         if (plan.n_items) {
             if (tid == 511) {
-                plan.n_items[0] = (uint32_t)(incl >> 32) * plan.chunks_gu;
-                plan.n_items[1] = (uint32_t)(incl >> 32) * plan.chunks_dn;
+                plan.n_items[0] = (uint32_t)(last_incl >> 32) * plan.chunks_gu;
+                plan.n_items[1] = (uint32_t)(last_incl >> 32) * plan.chunks_dn;
             }
             for (uint32_t gi = 0; gi < groups; ++gi) {
                 StreamItem it;
@@ -475,9 +547,9 @@ static cudaError_t group_pairs_launch(const Launch& L, const qkm_dims& d, const 
     if (n_chunks > 512) n_chunks = 512;
     const uint32_t want = (np + 7) / 8;
     if (n_chunks > want) n_chunks = want ? want : 1;
-    const size_t smem = ((size_t)n_chunks * expert_count + expert_count + 2 * 512) * sizeof(uint32_t);
+    const size_t smem = ((size_t)n_chunks * expert_count + expert_count + 1152) * sizeof(uint32_t);
     cudaError_t e = cudaFuncSetAttribute(group_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)((32768 + 512 + 1024) * sizeof(uint32_t)));
+                                         (int)((32768 + 512 + 1152) * sizeof(uint32_t)));
     if (e != cudaSuccess) return e;
     group_pairs_kernel<<<1, 512, smem, L.stream>>>(sel, n_tokens, d.n_expert, d.n_used, expert_first,
                                                    expert_count, n_chunks, offsets, pairs, plan);
