@@ -61,6 +61,9 @@ struct qkm_ctx {
     uint32_t* status = nullptr;       // kernel status word (device)
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
+    // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
+    cudaStream_t side = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     // the decode stack as a CUDA graph: captured on first use for a given argument set
     cudaGraphExec_t stack_graph = nullptr;
     struct { uint32_t first, count, n; const float* x; float* y; cudaStream_t stream; } stack_key{};
@@ -233,6 +236,13 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
         return nullptr;
     }
     *c->status_host = 0;
+    if (cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        bail("qkm_open: side stream", nullptr);
+        qkm_close(c);
+        return nullptr;
+    }
     if (err && err_len) err[0] = 0;
     return c;
 }
@@ -251,6 +261,9 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     for (void* p : scratch) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
+    if (c->ev_fork) cudaEventDestroy(c->ev_fork);
+    if (c->ev_join) cudaEventDestroy(c->ev_join);
+    if (c->side) cudaStreamDestroy(c->side);
     for (cudaEvent_t ev : c->prof_ev) if (ev) cudaEventDestroy(ev);
     delete c;
 }
@@ -512,20 +525,35 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         c->prof_mark("moe.dn");
         return QKM_OK;
     }
+    const uint32_t nb = (uint32_t)c->n_sms;
+    // Shared expert: depends on x (digit planes) only, so it runs on the side stream while
+    // the main stream groups pairs and streams the routed gate/up; they meet before the
+    // routed down kernel, which adds y2.  (Sequential while profiling.)
+    const bool fork = !c->profiling;
+    Launch S{fork ? c->side : c->stream, &c->launches};
+    if (fork) {
+        QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
+        QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+    }
+    // the shared lists depend on n only; the grouping kernel writes them, so the side
+    // stream keeps its own copies, refreshed here (tiny) - see launch_shared_plan
+    QKM_LAUNCH(c, launch_shared_plan(S, d, n, c->pairs, c->items_sh_gu, d.n_ff / gateup_stream_rows_per_item(),
+                                     c->items_sh_dn, d.n_embd / down_stream_rows_per_item(), 2, c->n_items + 2));
+    QKM_LAUNCH(c, launch_gateup_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xplanes, c->xscale, c->pairs,
+                                       c->items_sh_gu, c->n_items + 2, c->h, c->hpieces, nb, c->status));
+    if (!fork) c->prof_mark("moe.shared_gu");
+    QKM_LAUNCH(c, launch_down_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, c->sel, c->pairs, c->items_sh_dn,
+                                     c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));
+    if (!fork) c->prof_mark("moe.shared_dn");
+    if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     QKM_LAUNCH(c, launch_group_plan(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount, c->items_gu,
                                     d.n_ff / gateup_stream_rows_per_item(), c->items_dn,
-                                    d.n_embd / down_stream_rows_per_item(), c->items_sh_gu, c->items_sh_dn, 2, c->n_items));
+                                    d.n_embd / down_stream_rows_per_item(), nullptr, nullptr, 2, c->n_items));
     c->prof_mark("moe.pairs");
-    const uint32_t nb = (uint32_t)c->n_sms;
-    QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xplanes, c->xscale, c->pairs,
-                                       c->items_sh_gu, c->n_items + 2, c->h, c->hpieces, nb, c->status));
-    c->prof_mark("moe.shared_gu");
     QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xplanes, c->xscale, c->pairs,
                                        c->items_gu, c->n_items, c->h, c->hpieces, nb, c->status));
     c->prof_mark("moe.gu");
-    QKM_LAUNCH(c, launch_down_stream(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, c->sel, c->pairs, c->items_sh_dn,
-                                     c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));
-    c->prof_mark("moe.shared_dn");
+    if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     QKM_LAUNCH(c, launch_down_tok(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->y2, y, n, nb, c->status));
     c->prof_mark("moe.dn");
     return QKM_OK;

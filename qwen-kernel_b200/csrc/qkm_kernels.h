@@ -80,6 +80,11 @@ cudaError_t launch_group_plan(const Launch& L, const qkm_dims& d, const qkm_sel*
                               uint32_t chunks_dn, StreamItem* items_sh_gu, StreamItem* items_sh_dn,
                               uint32_t tok_per_item, uint32_t* n_items);
 
+// shared-expert work lists: n_items[0] gate/up, n_items[1] down; pairs[n_tokens*n_used + t] = (t<<4)|n_used
+cudaError_t launch_shared_plan(const Launch& L, const qkm_dims& d, uint32_t n_tokens, uint32_t* pairs,
+                               StreamItem* items_gu, uint32_t chunks_gu, StreamItem* items_dn,
+                               uint32_t chunks_dn, uint32_t tok_per_item, uint32_t* n_items);
+
 // ---- qkm_moe_simple.cu : one warp per output element, raw ggml layout
 cudaError_t launch_gateup_tokens(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate,
                                  const void* up, const float* x, const qkm_sel* sel, float* h,

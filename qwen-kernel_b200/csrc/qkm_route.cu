@@ -294,17 +294,39 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
         if (tid == 0) xscale[t] = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
     }
 
-    // k-th largest f32 logit
-    float v0 = l0, v1 = l1, kth = kFloor;
-    for (uint32_t i = 0; i < d.n_used; ++i) {
-        const unsigned long long k = block_argmax(v0, pid0, v1, pid1, s_warp);
-        const uint32_t id = 0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull);
-        uint32_t b = (uint32_t)(k >> 32);
-        b = (b & 0x80000000u) ? (b & 0x7FFFFFFFu) : ~b;
-        kth = __uint_as_float(b);
-        if (id == id0) v0 = kFloor;
-        if (id == id1) v1 = kFloor;
+    // k-th largest f32 logit: warp 0 alone ranks the (sanitised) logits, 16 per lane, with
+    // shuffles only - no block-wide barrier per round
+    __shared__ float s_log[512];
+    __shared__ float s_kth;
+    s_log[id0] = l0;
+    s_log[id1] = l1;
+    __syncthreads();
+    if (warp == 0) {
+        float v[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = s_log[lane + 32 * j];
+        float kth_w = kFloor;
+        for (uint32_t i = 0; i < d.n_used; ++i) {
+            unsigned long long best = 0ull;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+                const uint32_t id = lane + 32 * j;
+                const unsigned long long k = rank_key(v[j], id < d.n_expert ? id : 0xFFFFFFFEu);
+                best = k > best ? k : best;
+            }
+            best = warp_max_u64(best);
+            const uint32_t id = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
+            uint32_t bb = (uint32_t)(best >> 32);
+            bb = (bb & 0x80000000u) ? (bb & 0x7FFFFFFFu) : ~bb;
+            kth_w = __uint_as_float(bb);
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (id == lane + 32 * j) v[j] = kFloor;
+        }
+        if (lane == 0) s_kth = kth_w;
     }
+    __syncthreads();
+    const float kth = s_kth;
     // Error bound of one f32 logit: each lane adds K/32 products in sequence, then a
     // 5-level tree; |err| <= (K/32 + 6) * 2^-24 * sum|w_k x_k| <= that * |w| * |x|.
     // Doubled for safety, and doubled again because two logits are compared.
@@ -372,17 +394,22 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
         }
     }
     __syncthreads();
-    if (tid == 0) {
-        double w[16], sum = 0.0;
-        for (uint32_t i = 0; i < d.n_used; ++i) { w[i] = exp(s_best_val[i] - s_best_val[0]); sum += w[i]; }
-        for (uint32_t i = 0; i < 16; ++i) {
-            sel[t].ids[i] = i < d.n_used ? min(s_best_id[i], d.n_expert - 1) : 0u;
-            sel[t].w[i] = i < d.n_used ? (float)(w[i] / sum) : 0.f;
-        }
-        sel[t].w_shared = (float)(1.0 / (1.0 + exp(-sg)));
-        sel[t].route_done = 0;
+    if (warp == 0) {
+        // lane i < n_used: softmax term of pick i; lane 16: the shared gate
+        double wv = 0.0;
+        if (lane < d.n_used) wv = exp(s_best_val[lane] - s_best_val[0]);
+        double sum = wv;
 #pragma unroll
-        for (int i = 0; i < 6; ++i) sel[t].pad[i] = 0.f;
+        for (int o = 8; o > 0; o >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, o);  // lanes 0..15
+        if (lane < 16) {
+            sel[t].ids[lane] = lane < d.n_used ? min(s_best_id[lane], d.n_expert - 1) : 0u;
+            sel[t].w[lane] = lane < d.n_used ? (float)(wv / sum) : 0.f;
+        } else if (lane == 16) {
+            sel[t].w_shared = (float)(1.0 / (1.0 + exp(-sg)));
+            sel[t].route_done = 0;
+        } else if (lane < 23) {
+            sel[t].pad[lane - 17] = 0.f;
+        }
     }
 }
 
@@ -429,7 +456,7 @@ struct PlanArgs {
 
 __global__ void __launch_bounds__(512)
 group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t n_expert, uint32_t n_used,
-                   uint32_t expert_first, uint32_t expert_count, uint32_t n_chunks,
+                   uint32_t expert_first, uint32_t expert_count, uint32_t n_chunks, uint32_t stage_ids,
                    uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, PlanArgs plan) {
     extern __shared__ __align__(8) uint32_t s_dyn[];  // scan [512 x u64], counters [n_chunks][expert_count], totals
     uint32_t* s_scan = s_dyn;
@@ -439,12 +466,24 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
     const uint32_t np = n_tokens * n_used;
     const uint32_t chunk = (np + n_chunks - 1) / n_chunks;
     for (uint32_t i = tid; i < n_chunks * expert_count; i += 512) s_cnt[i] = 0;
+    // small inputs: fetch every id once, all loads in flight together, and walk them from
+    // shared memory afterwards
+    uint32_t* s_ids = s_tot + expert_count;
+    if (stage_ids)
+        for (uint32_t p = tid; p < np; p += 512) {
+            const uint32_t t = p / n_used, s = p - t * n_used;
+            s_ids[p] = min(sel[t].ids[s], n_expert - 1) - expert_first;  // wraps when below
+        }
     __syncthreads();
+    auto local_expert = [&](uint32_t p) -> uint32_t {
+        if (stage_ids) return s_ids[p];
+        const uint32_t t = p / n_used, s = p - t * n_used;
+        return min(sel[t].ids[s], n_expert - 1) - expert_first;
+    };
     const uint32_t p0 = tid * chunk, p1 = min(np, p0 + chunk);
     if (tid < n_chunks) {
         for (uint32_t p = p0; p < p1; ++p) {
-            const uint32_t t = p / n_used, s = p - t * n_used;
-            const uint32_t e = min(sel[t].ids[s], n_expert - 1) - expert_first;  // wraps when below
+            const uint32_t e = local_expert(p);
             if (e < expert_count) s_cnt[(size_t)tid * expert_count + e]++;
         }
     }
@@ -526,7 +565,7 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
     if (tid < n_chunks) {
         for (uint32_t p = p0; p < p1; ++p) {
             const uint32_t t = p / n_used, s = p - t * n_used;
-            const uint32_t e = min(sel[t].ids[s], n_expert - 1) - expert_first;
+            const uint32_t e = local_expert(p);
             if (e < expert_count) {
                 const uint32_t dst = s_tot[e] + s_cnt[(size_t)tid * expert_count + e]++;
                 pairs[dst] = (t << 4) | s;
@@ -547,12 +586,43 @@ static cudaError_t group_pairs_launch(const Launch& L, const qkm_dims& d, const 
     if (n_chunks > 512) n_chunks = 512;
     const uint32_t want = (np + 7) / 8;
     if (n_chunks > want) n_chunks = want ? want : 1;
-    const size_t smem = ((size_t)n_chunks * expert_count + expert_count + 1152) * sizeof(uint32_t);
+    const uint32_t stage_ids = np <= 8192 ? 1u : 0u;
+    const size_t smem = ((size_t)n_chunks * expert_count + expert_count + 1152 + (stage_ids ? np : 0)) * sizeof(uint32_t);
     cudaError_t e = cudaFuncSetAttribute(group_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)((32768 + 512 + 1152) * sizeof(uint32_t)));
+                                         (int)((32768 + 512 + 1152 + 8192) * sizeof(uint32_t)));
     if (e != cudaSuccess) return e;
     group_pairs_kernel<<<1, 512, smem, L.stream>>>(sel, n_tokens, d.n_expert, d.n_used, expert_first,
-                                                   expert_count, n_chunks, offsets, pairs, plan);
+                                                   expert_count, n_chunks, stage_ids, offsets, pairs, plan);
+    L.count();
+    return cudaGetLastError();
+}
+
+// Work lists of the shared expert: every token is a "pair" (token, slot n_used) stored
+// after the routed pairs, in groups of tok_per_item.  Depends on n_tokens only.
+__global__ void shared_plan_kernel(uint32_t n_tokens, uint32_t n_used, uint32_t* __restrict__ pairs,
+                                   StreamItem* __restrict__ items_gu, uint32_t chunks_gu,
+                                   StreamItem* __restrict__ items_dn, uint32_t chunks_dn,
+                                   uint32_t tok_per_item, uint32_t* __restrict__ n_items) {
+    const uint32_t np = n_tokens * n_used, tid = threadIdx.x;
+    const uint32_t groups = (n_tokens + tok_per_item - 1) / tok_per_item;
+    for (uint32_t t = tid; t < n_tokens; t += blockDim.x) pairs[np + t] = (t << 4) | n_used;
+    for (uint32_t gi = tid; gi < groups; gi += blockDim.x) {
+        StreamItem it;
+        it.expert = 0;
+        it.ntok = (uint8_t)min(tok_per_item, n_tokens - gi * tok_per_item);
+        it.pair_off = np + gi * tok_per_item;
+        for (uint32_t c = 0; c < chunks_gu; ++c) { it.chunk = (uint8_t)c; items_gu[(size_t)gi * chunks_gu + c] = it; }
+        for (uint32_t c = 0; c < chunks_dn; ++c) { it.chunk = (uint8_t)c; items_dn[(size_t)gi * chunks_dn + c] = it; }
+    }
+    if (tid == 0) { n_items[0] = groups * chunks_gu; n_items[1] = groups * chunks_dn; }
+}
+
+cudaError_t launch_shared_plan(const Launch& L, const qkm_dims& d, uint32_t n_tokens, uint32_t* pairs,
+                               StreamItem* items_gu, uint32_t chunks_gu, StreamItem* items_dn,
+                               uint32_t chunks_dn, uint32_t tok_per_item, uint32_t* n_items) {
+    if (n_tokens == 0) return cudaSuccess;
+    shared_plan_kernel<<<1, 256, 0, L.stream>>>(n_tokens, d.n_used, pairs, items_gu, chunks_gu, items_dn, chunks_dn,
+                                                tok_per_item, n_items);
     L.count();
     return cudaGetLastError();
 }
