@@ -222,7 +222,10 @@ cudaError_t launch_select(const Launch& L, const qkm_dims& d, const float* logit
 }
 
 // ---- refined selection: f32 ranking, f64 re-evaluation of the boundary ---------------------
-static constexpr int kMaxCand = 64;
+// One block per token.  Ranking is done by counting: every thread counts how many experts
+// precede its own in the order (value descending, id ascending), which needs no rounds of
+// block-wide argmax and no serial insertion.
+static constexpr int kMaxCand = 128;
 
 template <int TYPE>
 __global__ void __launch_bounds__(256)
@@ -230,25 +233,31 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
                      const float* __restrict__ row_norm2, const float* __restrict__ gis,
                      const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d,
                      int8_t* __restrict__ xplanes, float* __restrict__ xscale) {
-    __shared__ unsigned long long s_warp[8];
+    extern __shared__ float s_x[];  // n_embd floats
+    __shared__ double s_val[512];   // f64 logit of every candidate, -inf elsewhere
+    __shared__ float s_log[512];
     __shared__ double s_red[8];
-    __shared__ float s_f[8];
+    __shared__ float s_f[8], s_rn[8], s_xm[8];
     __shared__ uint32_t s_cand[kMaxCand];
-    __shared__ double s_val[kMaxCand];
     __shared__ uint32_t s_ncand;
+    __shared__ float s_kth;
+    __shared__ uint32_t s_best_id[16];
+    __shared__ double s_best_val[16];
     const uint32_t t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const float* xt = x + (size_t)t * d.n_embd;
     const float* lt = logits + (size_t)t * d.n_expert;
     const uint32_t id0 = tid, id1 = tid + 256u;
-    const float l0 = id0 < d.n_expert ? sane(lt[id0]) : kFloor;
-    const float l1 = id1 < d.n_expert ? sane(lt[id1]) : kFloor;
-    const uint32_t pid0 = id0 < d.n_expert ? id0 : 0xFFFFFFFEu;
-    const uint32_t pid1 = id1 < d.n_expert ? id1 : 0xFFFFFFFEu;
+    const float l0 = (id0 < d.n_expert ? sane(lt[id0]) : kFloor) + 0.0f;  // + 0: -0 and +0 tie
+    const float l1 = (id1 < d.n_expert ? sane(lt[id1]) : kFloor) + 0.0f;
+    s_log[id0] = l0;
+    s_log[id1] = l1;
+    const double ninf = -__longlong_as_double(0x7FF0000000000000ll);
+    s_val[id0] = ninf;
+    s_val[id1] = ninf;
 
     // One pass over the row: stage it in shared memory and gather everything that needs
     // it - |x|^2 and max|x| (error bound, digit exponent), the shared-gate dot in f64 -
     // together with max |router row|^2, so all global loads of this phase are in flight at once.
-    extern __shared__ float s_x[];  // n_embd floats
     float xs = 0.f, xm = 0.f, rn = 0.f;
     double dsg = 0.0;
     bool bad = false;
@@ -269,7 +278,6 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
         rn = fmaxf(rn, __shfl_xor_sync(0xFFFFFFFFu, rn, o));
         xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
     }
-    __shared__ float s_rn[8], s_xm[8];
     const int any_bad = __syncthreads_or(bad ? 1 : 0);
     if (lane == 0) { s_f[warp] = xs; s_red[warp] = dsg; s_rn[warp] = rn; s_xm[warp] = xm; }
     if (tid == 0) s_ncand = 0;
@@ -294,103 +302,68 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
         if (tid == 0) xscale[t] = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
     }
 
-    // k-th largest f32 logit: warp 0 alone ranks the (sanitised) logits, 16 per lane, with
-    // shuffles only - no block-wide barrier per round
-    __shared__ float s_log[512];
-    __shared__ float s_kth;
-    s_log[id0] = l0;
-    s_log[id1] = l1;
-    __syncthreads();
-    if (warp == 0) {
-        float v[16];
-#pragma unroll
-        for (int j = 0; j < 16; ++j) v[j] = s_log[lane + 32 * j];
-        float kth_w = kFloor;
-        for (uint32_t i = 0; i < d.n_used; ++i) {
-            unsigned long long best = 0ull;
-#pragma unroll
-            for (int j = 0; j < 16; ++j) {
-                const uint32_t id = lane + 32 * j;
-                const unsigned long long k = rank_key(v[j], id < d.n_expert ? id : 0xFFFFFFFEu);
-                best = k > best ? k : best;
-            }
-            best = warp_max_u64(best);
-            const uint32_t id = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
-            uint32_t bb = (uint32_t)(best >> 32);
-            bb = (bb & 0x80000000u) ? (bb & 0x7FFFFFFFu) : ~bb;
-            kth_w = __uint_as_float(bb);
-#pragma unroll
-            for (int j = 0; j < 16; ++j)
-                if (id == lane + 32 * j) v[j] = kFloor;
+    // k-th largest f32 logit: the expert that exactly n_used-1 others precede
+    {
+        uint32_t c0 = 0, c1 = 0;
+        for (uint32_t j = 0; j < d.n_expert; ++j) {
+            const float vj = s_log[j];
+            c0 += (vj > l0 || (vj == l0 && j < id0)) ? 1u : 0u;
+            c1 += (vj > l1 || (vj == l1 && j < id1)) ? 1u : 0u;
         }
-        if (lane == 0) s_kth = kth_w;
+        if (id0 < d.n_expert && c0 == d.n_used - 1) s_kth = l0;
+        if (id1 < d.n_expert && c1 == d.n_used - 1) s_kth = l1;
     }
     __syncthreads();
     const float kth = s_kth;
-    // Error bound of one f32 logit: each lane adds K/32 products in sequence, then a
-    // 5-level tree; |err| <= (K/32 + 6) * 2^-24 * sum|w_k x_k| <= that * |w| * |x|.
+    // Error bound of one f32 logit: each lane adds at most K/32 products in sequence, then
+    // trees; |err| <= (K/32 + 8) * 2^-24 * sum|w_k x_k| <= that * |w| * |x|.
     // Doubled for safety, and doubled again because two logits are compared.
-    const float eps = (float)(d.n_embd / 32 + 6) * 5.9604645e-8f * sqrtf(r2) * sqrtf(x2);
+    const float eps = (float)(d.n_embd / 32 + 8) * 5.9604645e-8f * sqrtf(r2) * sqrtf(x2);
     const float thresh = kth - 4.0f * eps;
-
     // candidates: every expert at or above the threshold
     // (written as !(l < thresh) so a NaN threshold - NaN in x - admits every expert)
-    const bool c0 = id0 < d.n_expert && !(l0 < thresh), c1 = id1 < d.n_expert && !(l1 < thresh);
-    if (c0) { const uint32_t p = atomicAdd(&s_ncand, 1u); if (p < kMaxCand) s_cand[p] = id0; }
-    if (c1) { const uint32_t p = atomicAdd(&s_ncand, 1u); if (p < kMaxCand) s_cand[p] = id1; }
+    const bool k0 = id0 < d.n_expert && !(l0 < thresh), k1 = id1 < d.n_expert && !(l1 < thresh);
+    if (k0) { const uint32_t p = atomicAdd(&s_ncand, 1u); if (p < kMaxCand) s_cand[p] = id0; }
+    if (k1) { const uint32_t p = atomicAdd(&s_ncand, 1u); if (p < kMaxCand) s_cand[p] = id1; }
     __syncthreads();
-    const uint32_t ncand_raw = s_ncand;
-    __syncthreads();
-    // Too many near-ties (or non-finite input: everything sits at the floor): fall
-    // back to evaluating experts in id order, kMaxCand at a time is not enough, so
-    // take the exact route of ranking ALL experts in f64 through the global pass below.
-    const bool all = ncand_raw > kMaxCand || ncand_raw < d.n_used;
-    const uint32_t total = all ? d.n_expert : ncand_raw;
+    const uint32_t ncand = s_ncand;
+    // too many near-ties (or non-finite input: everything at the floor): evaluate all experts
+    const bool all = ncand > kMaxCand || ncand < d.n_used;
+    const uint32_t total = all ? d.n_expert : ncand;
 
-    // f64 re-evaluation.  In the `all` case values stream through s_val in chunks and
-    // a running top-k (ids, values) is kept by thread 0.
-    __shared__ uint32_t s_best_id[16];
-    __shared__ double s_best_val[16];
-    __shared__ uint32_t s_nbest;
-    if (tid == 0) s_nbest = 0;
+    // f64 re-evaluation, one warp per candidate, four independent partial sums per lane
     const size_t rb = row_bytes(TYPE, d.n_embd);
-    for (uint32_t base = 0; base < total; base += kMaxCand) {
-        const uint32_t n = min((uint32_t)kMaxCand, total - base);
-        __syncthreads();
-        for (uint32_t c = warp; c < n; c += 8) {
-            const uint32_t e = all ? base + c : s_cand[c];
-            const uint8_t* row = router + (size_t)e * rb;
-            double acc = 0.0;
+    for (uint32_t c = warp; c < total; c += 8) {
+        const uint32_t e = all ? c : s_cand[c];
+        const uint8_t* row = router + (size_t)e * rb;
+        double a0 = 0.0, a1 = 0.0, a2 = 0.0, a3 = 0.0;
 #pragma unroll 4
-            for (uint32_t u = lane; u < d.n_embd / 8; u += 32) {
-                float w[8];
-                dequant8<TYPE>(row, u * 8, w);
-#pragma unroll
-                for (int i = 0; i < 8; ++i) acc += (double)w[i] * (double)s_x[u * 8 + i];
-            }
-            acc = warp_sum(acc);
-            if (lane == 0) {
-                s_val[c] = (isnan(acc) || isinf(acc)) ? (double)kFloor : acc;
-                if (all) s_cand[c] = e;
-            }
+        for (uint32_t u = lane; u < d.n_embd / 8; u += 32) {
+            float w[8];
+            dequant8<TYPE>(row, u * 8, w);
+            const float* xv = s_x + u * 8;
+            a0 += (double)w[0] * (double)xv[0]; a1 += (double)w[1] * (double)xv[1];
+            a2 += (double)w[2] * (double)xv[2]; a3 += (double)w[3] * (double)xv[3];
+            a0 += (double)w[4] * (double)xv[4]; a1 += (double)w[5] * (double)xv[5];
+            a2 += (double)w[6] * (double)xv[6]; a3 += (double)w[7] * (double)xv[7];
         }
-        __syncthreads();
-        if (tid == 0) {
-            // merge this chunk into the running top-k: (value desc, id asc)
-            uint32_t nb = s_nbest;
-            for (uint32_t c = 0; c < n; ++c) {
-                const double v = s_val[c];
-                const uint32_t e = s_cand[c];
-                uint32_t pos = nb;
-                while (pos > 0 && (s_best_val[pos - 1] < v || (s_best_val[pos - 1] == v && s_best_id[pos - 1] > e))) --pos;
-                if (pos >= d.n_used) continue;
-                const uint32_t last = nb < d.n_used ? nb : d.n_used - 1;
-                for (uint32_t j = last; j > pos; --j) { s_best_val[j] = s_best_val[j - 1]; s_best_id[j] = s_best_id[j - 1]; }
-                s_best_val[pos] = v;
-                s_best_id[pos] = e;
-                if (nb < d.n_used) ++nb;
+        const double acc = warp_sum((a0 + a1) + (a2 + a3));
+        if (lane == 0) s_val[e] = (isnan(acc) || isinf(acc)) ? (double)kFloor : acc;
+    }
+    __syncthreads();
+    // final order among the candidates: (f64 value descending, id ascending)
+    {
+        const double v0 = s_val[id0], v1 = s_val[id1];
+        const bool m0 = v0 > ninf, m1 = v1 > ninf;
+        if (m0 || m1) {
+            uint32_t c0 = 0, c1 = 0;
+            for (uint32_t j = 0; j < d.n_expert; ++j) {
+                const double vj = s_val[j];
+                c0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
+                c1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
             }
-            s_nbest = nb;
+            if (m0 && c0 < d.n_used) { s_best_id[c0] = id0; s_best_val[c0] = v0; }
+            if (m1 && c1 < d.n_used) { s_best_id[c1] = id1; s_best_val[c1] = v1; }
         }
     }
     __syncthreads();
