@@ -61,6 +61,12 @@ struct qkm_ctx {
     uint32_t* status = nullptr;       // kernel status word (device)
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
+    // prefill (tcgen05) scratch, allocated on first use
+    void* xb = nullptr;               // [max_tokens][n_embd] f16, rows scaled by powers of two (xscale undoes it)
+    void* hb = nullptr;               // [max_tokens*(n_used+1)][n_ff] bf16
+    float* contrib_p = nullptr;       // [max_tokens*(n_used+1)][n_embd]
+    MmaItem* mma_items[4] = {nullptr, nullptr, nullptr, nullptr};  // gate/up, down, shared gate/up, shared down
+    uint32_t* pos_of = nullptr;       // [max_tokens*(n_used+1)]
     // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
@@ -257,7 +263,9 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     }
     void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
-                       c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status};
+                       c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status,
+                       c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
+                       c->pos_of};
     for (void* p : scratch) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
@@ -559,11 +567,9 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     return QKM_OK;
 }
 
-extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, float* y) {
-    if (int rc = layer_ready(c, layer)) return rc;
-    if (!x || !y) return QKM_ERR_ARG;
-    if (int rc = check_tokens(c, n)) return rc;
-    const qkm_layer_weights& w = c->layers[layer].w;
+// Generic prefill sequence on the raw layout (any supported shape and type).
+static int prefill_generic(qkm_ctx* c, const qkm_layer_dev& ld, const float* x, uint32_t n, float* y) {
+    const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     if (!c->contrib) {
         QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
@@ -576,6 +582,56 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     QKM_LAUNCH(c, launch_down_pairs(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, c->offsets, c->pairs, c->contrib, n, c->efirst, c->ecount));
     QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, c->sel, c->y2, n));
     QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, c->y2, y, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, float* y) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (!x || !y) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    const qkm_layer_dev& ld = c->layers[layer];
+    const qkm_layer_weights& w = ld.w;
+    const qkm_dims& d = c->cfg.dims;
+    if (!ld.stream_ok || n == 0) return prefill_generic(c, ld, x, n, y);
+    // tensor-core path: tokens grouped by expert, expert GEMMs on tcgen05 with bf16 operands
+    const size_t T = c->cfg.max_tokens, rows = T * (d.n_used + 1);
+    const uint32_t NT = prefill_pairs_per_block();
+    const uint32_t rt_gu = d.n_ff / 128, rt_dn = d.n_embd / 128;
+    const size_t max_tiles = d.n_expert + (T * d.n_used + NT - 1) / NT, max_sh = (T + NT - 1) / NT;
+    if (!c->xb) {
+        QKM_CUDA(c, cudaMalloc(&c->xb, T * d.n_embd * 2));
+        QKM_CUDA(c, cudaMalloc(&c->hb, rows * d.n_ff * 2));
+        QKM_CUDA(c, cudaMalloc((void**)&c->contrib_p, rows * d.n_embd * sizeof(float)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[0], max_tiles * rt_gu * sizeof(MmaItem)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[1], max_tiles * rt_dn * sizeof(MmaItem)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[2], max_sh * rt_gu * sizeof(MmaItem)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[3], max_sh * rt_dn * sizeof(MmaItem)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->pos_of, rows * sizeof(uint32_t)));
+    }
+    const uint32_t tiles_now = d.n_expert < n * d.n_used ? d.n_expert + (n * d.n_used + NT - 1) / NT : n * d.n_used;
+    const uint32_t sh_now = (n + NT - 1) / NT;
+    c->prof_begin();
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch));
+    c->prof_mark("moe.route");
+    QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
+    QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n, c->mma_items[0], c->mma_items[1],
+                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of));
+    QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
+    c->prof_mark("moe.pairs");
+    QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
+                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status));
+    c->prof_mark("moe.gu");
+    QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
+                                    c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status));
+    c->prof_mark("moe.shared_gu");
+    QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, c->sel, c->pairs, c->mma_items[1],
+                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status));
+    c->prof_mark("moe.dn");
+    QKM_LAUNCH(c, launch_down_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
+                                  c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
+    c->prof_mark("moe.shared_dn");
+    QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, y, n));
+    c->prof_mark("moe.fold");
     return QKM_OK;
 }
 

@@ -26,6 +26,32 @@ struct StreamItem {
     uint32_t pair_off;
 };
 
+// One block of the prefill GEMMs: an expert, a 128-row tile of its matrix and up to 128
+// of its pairs (pairs[pair_off .. pair_off + n)).
+struct MmaItem {
+    uint16_t expert;
+    uint16_t rt;
+    uint32_t pair_off;
+    uint32_t n;
+};
+
+// ---- qkm_prefill.cu : tcgen05 expert GEMMs for batched prefill
+uint32_t prefill_pairs_per_block();
+// x rows as f16 scaled per row by a power of two (inv_scale[row] undoes it)
+cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float* inv_scale, uint32_t n_rows, uint32_t K);
+cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
+                            uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
+                            MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of);
+cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
+                              const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
+                              const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
+                              uint32_t* status);
+cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
+                            const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
+                            uint32_t max_items, float* contrib, uint32_t* status);
+cudaError_t launch_fold_pairs(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,
+                              float* y, uint32_t n_tokens);
+
 // ---- qkm_repack.cu : raw ggml -> tile layout (same bytes, see qkm_tiles.cuh)
 cudaError_t launch_repack(const Launch& L, uint32_t type, const void* raw, void* out, uint32_t n_mats,
                           uint32_t rows, uint32_t K);

@@ -1,0 +1,526 @@
+// Batched prefill of the expert GEMMs on the 5th-generation tensor cores (tcgen05 + TMEM).
+//
+// Replaces moe_gateup_iq3_grouped_coopmat.comp / moe_gateup_q8_coopmat.comp (gate/up +
+// SwiGLU), moe_down_{iq4}_grouped_coopmat.comp / moe_down_q8_coopmat.comp (down) and the
+// slot-order fold of add_rms3_grouped.comp:22-27.
+//
+// Tokens are grouped by expert (moe_group_pairs).  One block owns (expert, 128 weight
+// rows, up to 128 of the expert's pairs).  Weights are the M = 128 operand: every k-step
+// the block's threads dequantise 128 x 64 weights from the tile-ordered quant blocks to
+// bf16 (single rounding of the exact f32 value) straight into the 128-byte-swizzled
+// K-major shared-memory layout, gather the matching 64 columns of the pairs' activation
+// rows (bf16) as the N operand, and one thread issues tcgen05.mma (kind::f16, bf16 inputs,
+// f32 accumulators in tensor memory).  Three shared-memory stages let dequantisation of
+// the next k-steps overlap the asynchronous MMAs; a stage is recycled when the commit of
+// the MMAs that read it arrives on its mbarrier.  All waits are bounded.
+//
+// Operand types: the gate/up GEMM runs on f16 operands (11-bit significands; x is scaled
+// per token by a power of two into f16 range and unscaled in the epilogue), the down GEMM
+// on bf16 operands (the hidden rows need bf16's exponent range).  With bf16 on both GEMMs
+// the worst element of a 2048-wide output row sits at the 2e-2 tolerance; f16 on the first
+// GEMM leaves a 3x margin at the same tensor-core rate.
+//
+// gate/up: two accumulators (gate rows, up rows) share the B operand; the epilogue reads
+//          both from TMEM, applies SwiGLU and stores h as bf16 [pair][n_ff] (the down
+//          GEMM's N operand) and as f32 in the reference's h layout.
+// down:    epilogue multiplies by the routing weight after the full K reduction
+//          (moe_down_iq4_grouped_coopmat.comp:160-161) and stores contrib[pair][n_embd];
+//          the fold adds a token's slots in order, then the shared expert.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "qkm_kernels.h"
+#include "qkm_stream.cuh"
+#include "qkm_tiles.cuh"
+#include "qkm_umma.cuh"
+
+namespace qkm {
+
+namespace pf {
+constexpr int kThreads = 256;
+constexpr int kStages = 3;
+constexpr int kNT = 128;                       // pairs per block (N tile)
+constexpr int kTileBytes = 128 * 128;          // 128 rows x 64 bf16
+constexpr int kGridReplicas = 8;
+}  // namespace pf
+
+// ---- x -> f16 rows, each scaled by a power of two so that max|x| lands in [2^13, 2^14) -----------
+__global__ void __launch_bounds__(256)
+to_f16_rows_kernel(const float* __restrict__ x, __half* __restrict__ xh, float* __restrict__ inv_scale, uint32_t K) {
+    __shared__ float s_max[8];
+    const uint32_t t = blockIdx.x, tid = threadIdx.x;
+    const float* xt = x + (size_t)t * K;
+    float m = 0.f;
+    for (uint32_t k = tid; k < K; k += 256) m = fmaxf(m, fabsf(xt[k]));
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if ((tid & 31u) == 0) s_max[tid >> 5] = m;
+    __syncthreads();
+    m = s_max[0];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) m = fmaxf(m, s_max[w]);
+    int p = 0;
+    if (m > 0.f && m <= 3.0e38f) { int e; frexpf(m, &e); p = 14 - e; }  // m * 2^p in [2^13, 2^14)
+    const float up = ldexpf(1.0f, p);
+    for (uint32_t k = tid * 2; k < K; k += 512) {
+        const float2 v = *reinterpret_cast<const float2*>(xt + k);
+        *reinterpret_cast<__half2*>(xh + (size_t)t * K + k) = __floats2half2_rn(v.x * up, v.y * up);
+    }
+    if (tid == 0) inv_scale[t] = ldexpf(1.0f, -p);
+}
+
+// ---- work list ------------------------------------------------------------------------------------------
+// For every expert with pairs: its pairs in tiles of kNT, times the 128-row tiles of the
+// gate/up matrices (items_gu) and of the down matrix (items_dn).  Index n_expert_local is
+// the shared expert: its "pairs" are all tokens, stored after the routed pairs.
+// Also pos_of[t * (n_used+1) + s] = position of pair (t, s) in the grouped order.
+__global__ void __launch_bounds__(512)
+mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, uint32_t n_expert_local,
+                uint32_t n_tokens, uint32_t n_used, uint32_t rt_gu, uint32_t rt_dn,
+                MmaItem* __restrict__ items_gu, MmaItem* __restrict__ items_dn, MmaItem* __restrict__ items_sh_gu,
+                MmaItem* __restrict__ items_sh_dn, uint32_t* __restrict__ n_items, uint32_t* __restrict__ pos_of) {
+    __shared__ uint32_t s_scan[512];
+    const uint32_t e = threadIdx.x;
+    const uint32_t np = offsets[n_expert_local];
+    uint32_t tiles = 0, p0 = 0, n = 0;
+    if (e < n_expert_local) { p0 = offsets[e]; n = offsets[e + 1] - p0; tiles = (n + pf::kNT - 1) / pf::kNT; }
+    s_scan[e] = tiles;
+    __syncthreads();
+    for (uint32_t o = 1; o < 512; o <<= 1) {
+        const uint32_t v = e >= o ? s_scan[e - o] : 0;
+        __syncthreads();
+        s_scan[e] += v;
+        __syncthreads();
+    }
+    const uint32_t first = s_scan[e] - tiles;
+    for (uint32_t ti = 0; ti < tiles; ++ti) {
+        MmaItem it;
+        it.expert = (uint16_t)e;
+        it.pair_off = p0 + ti * pf::kNT;
+        it.n = min((uint32_t)pf::kNT, n - ti * pf::kNT);
+        for (uint32_t r = 0; r < rt_gu; ++r) { it.rt = (uint16_t)r; items_gu[(size_t)(first + ti) * rt_gu + r] = it; }
+        for (uint32_t r = 0; r < rt_dn; ++r) { it.rt = (uint16_t)r; items_dn[(size_t)(first + ti) * rt_dn + r] = it; }
+    }
+    const uint32_t sh_tiles = (n_tokens + pf::kNT - 1) / pf::kNT;
+    for (uint32_t ti = e; ti < sh_tiles; ti += 512) {
+        MmaItem it;
+        it.expert = 0;
+        it.pair_off = np + ti * pf::kNT;
+        it.n = min((uint32_t)pf::kNT, n_tokens - ti * pf::kNT);
+        for (uint32_t r = 0; r < rt_gu; ++r) { it.rt = (uint16_t)r; items_sh_gu[(size_t)ti * rt_gu + r] = it; }
+        for (uint32_t r = 0; r < rt_dn; ++r) { it.rt = (uint16_t)r; items_sh_dn[(size_t)ti * rt_dn + r] = it; }
+    }
+    if (e == 511) {
+        n_items[0] = s_scan[511] * rt_gu; n_items[1] = s_scan[511] * rt_dn;
+        n_items[2] = sh_tiles * rt_gu;    n_items[3] = sh_tiles * rt_dn;
+    }
+    for (uint32_t p = e; p < np; p += 512) {
+        const uint32_t pr = pairs[p];
+        pos_of[(pr >> 4) * (n_used + 1) + (pr & 15u)] = p;
+    }
+    for (uint32_t t = e; t < n_tokens; t += 512) {
+        pairs[np + t] = (t << 4) | n_used;
+        pos_of[t * (n_used + 1) + n_used] = np + t;
+    }
+}
+
+// ---- operand producers ----------------------------------------------------------------------------------
+// Each fills, for one weight row and one 64-column k-step, the row's eight 16-byte chunks
+// of the swizzled A tile.  `tile` points at the row's 16-row tile of the tile-ordered
+// tensor (qkm_tiles.cuh), r16 is the row inside it, q = k-step within the 256-column block.
+
+template <bool F16>
+__device__ __forceinline__ uint32_t pack16(float a, float b) {
+    if (F16) { __half2 v = __floats2half2_rn(a, b); return *reinterpret_cast<uint32_t*>(&v); }
+    __nv_bfloat162 v = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) { return pack16<false>(a, b); }
+
+__device__ __forceinline__ void produce_iq3(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
+                                            const float4* __restrict__ s_grid, uint32_t lane, uint8_t* a_tile,
+                                            uint32_t row) {
+    const uint32_t g = r16 & 7u, hf = r16 >> 3;
+    const uint2 aux2 = *reinterpret_cast<const uint2*>(tile + 1024 + 32 * r16 + 8 * q);
+    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + 1536 + 2 * r16));
+    uint32_t idxw[4];
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+        idxw[t] = *reinterpret_cast<const uint32_t*>(tile + hf * 512 + (4 * g + t) * 16 + 4 * q);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {          // sub-block 2q + j
+        const uint32_t aux = j ? aux2.y : aux2.x;
+        const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {      // 8-element group t -> chunk 4j + t
+            const uint32_t pr = (idxw[t] >> (16 * j)) & 0xFFFFu;
+            const float4 m0 = s_grid[(pr & 0xFFu) * pf::kGridReplicas + (lane & 7u)];
+            const float4 m1 = s_grid[(pr >> 8) * pf::kGridReplicas + (lane & 7u)];
+            const uint32_t sg = signs8((aux >> (7 * t)) & 127u);
+            uint4 o;
+            o.x = pack16<true>(db * m0.x, db * m0.y) ^ (((sg & 1u) << 15) | ((sg & 2u) << 30));
+            o.y = pack16<true>(db * m0.z, db * m0.w) ^ (((sg & 4u) << 13) | ((sg & 8u) << 28));
+            o.z = pack16<true>(db * m1.x, db * m1.y) ^ (((sg & 16u) << 11) | ((sg & 32u) << 26));
+            o.w = pack16<true>(db * m1.z, db * m1.w) ^ (((sg & 64u) << 9) | ((sg & 128u) << 24));
+            *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + t)) = o;
+        }
+    }
+}
+
+__device__ __forceinline__ void produce_iq4(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
+                                            const float* __restrict__ s_kv, uint32_t lane, uint8_t* a_tile,
+                                            uint32_t row) {
+    const uint32_t g = r16 & 7u, hf = r16 >> 3;
+    const uint2 hd = *reinterpret_cast<const uint2*>(tile + 16 * g + 8 * hf);  // d | scales_h << 16, scales_l
+    const float d = f16_bits_to_f32(hd.x & 0xFFFFu);
+    const uint32_t sh = hd.x >> 16;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const uint32_t sb = 2 * q + j;
+        const int ls = (int)(((hd.y >> (4 * sb)) & 0xFu) | (((sh >> (2 * sb)) & 3u) << 4)) - 32;
+        const float dl = d * (float)ls;
+        // the sub-block's 16 quant bytes: word t sits in lane slot (g, t) of chunk 2*hf + sb/4
+        uint32_t w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            w[t] = *reinterpret_cast<const uint32_t*>(tile + 128 + ((2 * hf + (sb >> 2)) * 32 + 4 * g + t) * 16 + 4 * (sb & 3u));
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {      // elements 8p .. 8p+7 of the sub-block -> chunk 4j + p
+            const uint32_t lo = w[2 * (p & 1)], hi = w[2 * (p & 1) + 1];
+            const uint32_t sft = (p >> 1) * 4;   // low nibbles for elements < 16, high nibbles above
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                v[i] = dl * s_kv[((lo >> (8 * i + sft)) & 15u) * 32 + lane];
+                v[4 + i] = dl * s_kv[((hi >> (8 * i + sft)) & 15u) * 32 + lane];
+            }
+            uint4 o;
+            o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
+            o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+            *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + p)) = o;
+        }
+    }
+}
+
+template <bool F16>
+__device__ __forceinline__ void produce_q8(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
+                                           uint8_t* a_tile, uint32_t row) {
+    const uint32_t g = r16 & 7u, hf = r16 >> 3;
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+        const uint32_t blk = 2 * q + j;
+        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + 2 * (16 * blk + r16)));
+        // lane slot (g, t): qs[4t..4t+3] then qs[16+4t..16+4t+3]
+        uint2 w[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+            w[t] = *reinterpret_cast<const uint2*>(tile + 256 + ((blk * 2 + hf) * 32 + 4 * g + t) * 8);
+#pragma unroll
+        for (int p = 0; p < 4; ++p) {      // elements 8p..8p+7: words (2(p&1), 2(p&1)+1), .x below 16, .y above
+            const uint32_t a = (p >> 1) ? w[2 * (p & 1)].y : w[2 * (p & 1)].x;
+            const uint32_t b = (p >> 1) ? w[2 * (p & 1) + 1].y : w[2 * (p & 1) + 1].x;
+            uint4 o;
+            o.x = pack16<F16>(d * (float)(int8_t)(a & 0xFF), d * (float)(int8_t)((a >> 8) & 0xFF));
+            o.y = pack16<F16>(d * (float)(int8_t)((a >> 16) & 0xFF), d * (float)(int8_t)(a >> 24));
+            o.z = pack16<F16>(d * (float)(int8_t)(b & 0xFF), d * (float)(int8_t)((b >> 8) & 0xFF));
+            o.w = pack16<F16>(d * (float)(int8_t)((b >> 16) & 0xFF), d * (float)(int8_t)(b >> 24));
+            *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + p)) = o;
+        }
+    }
+}
+
+// N operand: rows [0, n_mma) of the block's pairs, 64 columns at k0; rows >= n are zero.
+// `src_row(i)` returns the bf16 row of pair i.
+template <class RowFn>
+__device__ __forceinline__ void produce_b(uint8_t* b_tile, uint32_t n, uint32_t n_mma, uint32_t k0, RowFn src_row) {
+    for (uint32_t qd = threadIdx.x; qd < n_mma * 8; qd += pf::kThreads) {
+        const uint32_t row = qd >> 3, c = qd & 7u;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < n) v = *reinterpret_cast<const uint4*>(src_row(row) + k0 + 8 * c);
+        *reinterpret_cast<uint4*>(b_tile + umma::sw128_chunk(row, c)) = v;
+    }
+}
+
+// ---- gate/up + SwiGLU ------------------------------------------------------------------------------------
+// FMT: QKM_TYPE_IQ3_XXS (routed experts) or QKM_TYPE_Q8_0 (shared expert).
+template <int FMT>
+__global__ void __launch_bounds__(pf::kThreads, 1)
+gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restrict__ up_tiles,
+                  const __half* __restrict__ xb, const float* __restrict__ x_inv_scale,
+                  const uint32_t* __restrict__ pairs, const MmaItem* __restrict__ items,
+                  const uint32_t* __restrict__ n_items_ptr, float* __restrict__ h,
+                  __nv_bfloat16* __restrict__ hb, qkm_dims d, uint32_t* __restrict__ status) {
+    if (blockIdx.x >= *n_items_ptr) return;
+    constexpr int kTile = FMT == QKM_TYPE_IQ3_XXS ? kTileIq3 : kTileQ8;
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    __shared__ __align__(8) unsigned long long s_bar[pf::kStages + 1];
+    __shared__ uint32_t s_tmem;
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    float4* s_grid = reinterpret_cast<float4*>(smem + pf::kStages * 3 * pf::kTileBytes);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const MmaItem it = items[blockIdx.x];
+    const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
+    const uint32_t KB = d.n_embd / 256, RT16 = d.n_ff / 16, KS = d.n_embd / 64;
+
+    if (FMT == QKM_TYPE_IQ3_XXS)
+        for (uint32_t i = tid; i < 256 * pf::kGridReplicas; i += pf::kThreads) {
+            const uint32_t gw = c_iq3_grid[i / pf::kGridReplicas];
+            s_grid[i] = make_float4((float)(gw & 255u), (float)((gw >> 8) & 255u), (float)((gw >> 16) & 255u), (float)(gw >> 24));
+        }
+    if (tid == 0) {
+        for (int s = 0; s <= pf::kStages; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), 256); umma::tmem_relinquish(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    const uint32_t idesc = umma::instr_desc_f16(n_mma);
+    bool timed_out = false;
+
+    // producer role of this thread: row r of the gate (threads 0..127) or up (128..255) tile
+    const uint32_t r = tid & 127u, mat = tid >> 7;
+    const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
+    const uint8_t* wt = (mat ? up_tiles : gate_tiles) + (size_t)it.expert * KB * RT16 * kTile;
+
+    for (uint32_t ks = 0; ks < KS; ++ks) {
+        const uint32_t stage = ks % pf::kStages;
+        if (ks >= (uint32_t)pf::kStages)
+            if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
+        uint8_t* st = smem + stage * 3 * pf::kTileBytes;
+        const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
+        if (FMT == QKM_TYPE_IQ3_XXS) produce_iq3(tile, r16, ks & 3u, s_grid, lane, st + mat * pf::kTileBytes, r);
+        else produce_q8<true>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+        produce_b(st + 2 * pf::kTileBytes, n, n_mma, ks * 64,
+                  [&](uint32_t i) { return xb + (size_t)(pairs[it.pair_off + i] >> 4) * d.n_embd; });
+        umma::fence_smem_to_async();
+        __syncthreads();
+        if (tid == 0) {
+            umma::fence_after_sync();
+            const uint32_t a_g = smem_addr(st), a_u = a_g + pf::kTileBytes, b = a_g + 2 * pf::kTileBytes;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool acc = (ks | (uint32_t)j) != 0;
+                umma::mma_bf16_ss(tmem, umma::smem_desc(a_g + 32 * j), umma::smem_desc(b + 32 * j), idesc, acc);
+                umma::mma_bf16_ss(tmem + 128, umma::smem_desc(a_u + 32 * j), umma::smem_desc(b + 32 * j), idesc, acc);
+            }
+            umma::commit(smem_addr(&s_bar[stage]));
+            if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[pf::kStages]));
+        }
+    }
+    if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages]), 0)) timed_out = true;
+    umma::fence_after_sync();
+
+    // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) and every other 16-column block
+    {
+        const uint32_t lg = warp & 3u, row = 32 * lg + lane;
+        const uint32_t r_ff = it.rt * 128u + row;
+        for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += 2) {
+            uint32_t vg[16], vu[16];
+            umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, vg);
+            umma::tmem_ld16(tmem + ((32 * lg) << 16) + 128 + cb * 16, vu);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t col = cb * 16 + i;
+                if (col < n) {
+                    const uint32_t pos = it.pair_off + col, pr = pairs[pos];
+                    const float us = x_inv_scale[pr >> 4];   // undo the per-token power-of-two scale of x
+                    const float hv = swiglu(__uint_as_float(vg[i]) * us, __uint_as_float(vu[i]) * us);
+                    hb[(size_t)pos * d.n_ff + r_ff] = __float2bfloat16_rn(hv);
+                    h[((size_t)(pr >> 4) * (d.n_used + 1) + (pr & 15u)) * d.n_ff + r_ff] = hv;
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 256);
+    if (timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+}
+
+// ---- down -------------------------------------------------------------------------------------------------
+// FMT: QKM_TYPE_IQ4_XS (routed) or QKM_TYPE_Q8_0 (shared).  contrib[pair position][n_embd].
+template <int FMT>
+__global__ void __launch_bounds__(pf::kThreads, 1)
+down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restrict__ hb,
+                const qkm_sel* __restrict__ sel, const uint32_t* __restrict__ pairs,
+                const MmaItem* __restrict__ items, const uint32_t* __restrict__ n_items_ptr,
+                float* __restrict__ contrib, qkm_dims d, uint32_t* __restrict__ status) {
+    if (blockIdx.x >= *n_items_ptr) return;
+    constexpr int kTile = FMT == QKM_TYPE_IQ4_XS ? kTileIq4 : kTileQ8;
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    __shared__ __align__(8) unsigned long long s_bar[pf::kStages + 1];
+    __shared__ uint32_t s_tmem;
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    float* s_kv = reinterpret_cast<float*>(smem + pf::kStages * 2 * pf::kTileBytes);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const MmaItem it = items[blockIdx.x];
+    const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
+    const uint32_t KB = d.n_ff / 256, RT16 = d.n_embd / 16, KS = d.n_ff / 64;
+
+    if (FMT == QKM_TYPE_IQ4_XS)
+        for (uint32_t i = tid; i < 16 * 32; i += pf::kThreads) s_kv[i] = (float)c_iq4_values[i >> 5];
+    if (tid == 0) {
+        for (int s = 0; s <= pf::kStages; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), 128); umma::tmem_relinquish(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    const uint32_t idesc = umma::instr_desc_bf16(n_mma);
+    bool timed_out = false;
+
+    // producer role: threads 0..127 write the A rows, all threads help with B
+    const uint32_t r = tid & 127u;
+    const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
+    const uint8_t* wt = tiles + (size_t)it.expert * KB * RT16 * kTile;
+
+    for (uint32_t ks = 0; ks < KS; ++ks) {
+        const uint32_t stage = ks % pf::kStages;
+        if (ks >= (uint32_t)pf::kStages)
+            if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
+        uint8_t* st = smem + stage * 2 * pf::kTileBytes;
+        if (tid < 128) {
+            const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
+            if (FMT == QKM_TYPE_IQ4_XS) produce_iq4(tile, r16, ks & 3u, s_kv, lane, st, r);
+            else produce_q8<false>(tile, r16, ks & 3u, st, r);
+        }
+        produce_b(st + pf::kTileBytes, n, n_mma, ks * 64,
+                  [&](uint32_t i) { return hb + (size_t)(it.pair_off + i) * d.n_ff; });
+        umma::fence_smem_to_async();
+        __syncthreads();
+        if (tid == 0) {
+            umma::fence_after_sync();
+            const uint32_t a = smem_addr(st), b = a + pf::kTileBytes;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                umma::mma_bf16_ss(tmem, umma::smem_desc(a + 32 * j), umma::smem_desc(b + 32 * j), idesc, (ks | (uint32_t)j) != 0);
+            umma::commit(smem_addr(&s_bar[stage]));
+            if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[pf::kStages]));
+        }
+    }
+    if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages]), 0)) timed_out = true;
+    umma::fence_after_sync();
+    {
+        const uint32_t lg = warp & 3u, row = 32 * lg + lane;
+        const uint32_t o = it.rt * 128u + row;
+        for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += 2) {
+            uint32_t v[16];
+            umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, v);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t col = cb * 16 + i;
+                if (col < n) {
+                    const uint32_t pos = it.pair_off + col, pr = pairs[pos], tok = pr >> 4, slot = pr & 15u;
+                    const float wgt = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
+                    // routing weight after the full K reduction
+                    contrib[(size_t)pos * d.n_embd + o] = wgt * __uint_as_float(v[i]);
+                }
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 128);
+    if (timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+}
+
+// ---- fold: y[t] = sum over slots (in order) of contrib[pos(t,s)], then the shared expert -----------------
+__global__ void fold_pairs_kernel(const float* __restrict__ contrib, const uint32_t* __restrict__ pos_of,
+                                  float* __restrict__ y, uint32_t n_used, uint32_t n_embd) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (o >= n_embd) return;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t s = 0; s <= n_used; ++s) {
+        const float4 c = *reinterpret_cast<const float4*>(contrib + (size_t)pos_of[t * (n_used + 1) + s] * n_embd + o);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+    }
+    *reinterpret_cast<float4*>(y + (size_t)t * n_embd + o) = v;
+}
+
+// ---- launchers ---------------------------------------------------------------------------------------------
+uint32_t prefill_pairs_per_block() { return pf::kNT; }
+
+cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float* inv_scale, uint32_t n_rows, uint32_t K) {
+    if (n_rows == 0) return cudaSuccess;
+    to_f16_rows_kernel<<<n_rows, 256, 0, L.stream>>>(x, (__half*)xh, inv_scale, K);
+    L.count();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
+                            uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
+                            MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of) {
+    if (n_expert_local > 512) return cudaErrorInvalidValue;
+    mma_plan_kernel<<<1, 512, 0, L.stream>>>(offsets, pairs, n_expert_local, n_tokens, d.n_used, d.n_ff / 128,
+                                             d.n_embd / 128, items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, pos_of);
+    L.count();
+    return cudaGetLastError();
+}
+
+template <int FMT>
+static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
+                                     const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
+                                     const uint32_t* n_items, uint32_t max_items, float* h, void* hb, uint32_t* status) {
+    const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 256 * pf::kGridReplicas * 16 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(gateup_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    gateup_mma_kernel<FMT><<<max_items, pf::kThreads, smem, L.stream>>>(
+        (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, (const __half*)xb, x_inv_scale, pairs, items, n_items, h,
+        (__nv_bfloat16*)hb, d, status);
+    L.count();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
+                              const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
+                              const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
+                              uint32_t* status) {
+    if (max_items == 0) return cudaSuccess;
+    if (type == QKM_TYPE_IQ3_XXS)
+        return gateup_mma_launch<QKM_TYPE_IQ3_XXS>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
+    if (type == QKM_TYPE_Q8_0)
+        return gateup_mma_launch<QKM_TYPE_Q8_0>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
+    return cudaErrorInvalidValue;
+}
+
+template <int FMT>
+static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const void* tiles, const void* hb,
+                                   const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items,
+                                   const uint32_t* n_items, uint32_t max_items, float* contrib, uint32_t* status) {
+    const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + 16 * 32 * 4 + 1024;
+    cudaError_t e = cudaFuncSetAttribute(down_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    down_mma_kernel<FMT><<<max_items, pf::kThreads, smem, L.stream>>>(
+        (const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items, n_items, contrib, d, status);
+    L.count();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
+                            const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
+                            uint32_t max_items, float* contrib, uint32_t* status) {
+    if (max_items == 0) return cudaSuccess;
+    if (type == QKM_TYPE_IQ4_XS)
+        return down_mma_launch<QKM_TYPE_IQ4_XS>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status);
+    if (type == QKM_TYPE_Q8_0)
+        return down_mma_launch<QKM_TYPE_Q8_0>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status);
+    return cudaErrorInvalidValue;
+}
+
+cudaError_t launch_fold_pairs(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,
+                              float* y, uint32_t n_tokens) {
+    if (n_tokens == 0) return cudaSuccess;
+    const dim3 grid((d.n_embd / 4 + 255) / 256, n_tokens);
+    fold_pairs_kernel<<<grid, 256, 0, L.stream>>>(contrib, pos_of, y, d.n_used, d.n_embd);
+    L.count();
+    return cudaGetLastError();
+}
+
+}  // namespace qkm

@@ -1,0 +1,64 @@
+"""Batched prefill through the tensor-core path (bf16 operands, f32 accumulation) against the
+f64-accumulating oracle.  Tolerance: 2e-2 on the row-scaled relative error, expert ids exact,
+argmax of every output row unchanged (where the reference itself is not a near-tie)."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 2e-2
+
+
+def run_prefill(pkg, orc, syn, dims, layer, x, tol=TOL_BF16):
+    T = x.shape[0]
+    ref = orc.moe_layer(layer, x, threads=orc.hardware_threads(), want_h=True)
+    with pkg.Context(dims, n_layer=1, max_tokens=max(T, 1), device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        y = ctx.moe_forward_host(0, x, mode=1)
+        sel = ctx.last_sel(T)
+        y_again = ctx.moe_forward_host(0, x, mode=1)
+    assert np.array_equal(sel["ids"][:, :dims.n_used], ref["sel"]["ids"][:, :dims.n_used])
+    err = syn.rel_err_rows(y, ref["y"])
+    assert err < tol, err
+    # argmax of every output row is unchanged wherever the reference's lead over the
+    # runner-up is larger than twice the tolerated error (a closer call is a tie at this precision)
+    r = ref["y"].astype(np.float64)
+    top2 = np.sort(r, axis=1)[:, -2:]
+    rms = np.sqrt(np.mean(r * r, axis=1))
+    clear = (top2[:, 1] - top2[:, 0]) > 2 * tol * np.maximum(rms, np.abs(top2[:, 1]))
+    assert np.array_equal(np.argmax(y, axis=1)[clear], np.argmax(r, axis=1)[clear])
+    assert np.array_equal(y, y_again)   # deterministic
+    return err
+
+
+@pytest.mark.parametrize("T", [1, 17, 130, 300])
+def test_prefill_full_size(pkg, orc, syn, T):
+    """Bench configuration 3 shapes (2048 / 512 / 256 experts / top-8) at small chunk sizes."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=42)
+    x = syn.random_x(T, dims.n_embd, seed=77)
+    run_prefill(pkg, orc, syn, dims, layer, x)
+
+
+def test_prefill_hot_expert(pkg, orc, syn):
+    """Every token routed to the same experts: more pairs than one block holds (N tiles > 1)."""
+    dims = syn.Dims(n_embd=1024, n_ff=512, n_expert=16, n_used=4)
+    layer = syn.make_layer(dims, seed=5, router_type=syn.F32)
+    r = layer.router.view(np.float32).reshape(16, 1024).copy()
+    r[3] *= 40.0; r[7] *= 30.0                      # experts 3 and 7 dominate for most tokens
+    layer.router = r.reshape(-1).view(np.uint8)
+    x = syn.random_x(150, dims.n_embd, seed=6)
+    x[:, :] = np.abs(x) * np.sign(r[3])[None, :] * 0.5 + x * 0.5   # push tokens towards expert 3
+    run_prefill(pkg, orc, syn, dims, layer, x)
+
+
+def test_prefill_matches_decode_path(pkg, syn):
+    """The two fused paths agree to bf16 accuracy on the same inputs."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=8)
+    x = syn.random_x(24, dims.n_embd, seed=9)
+    with pkg.Context(dims, n_layer=1, max_tokens=24, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        yd = ctx.moe_forward_host(0, x, mode=0)
+        yp = ctx.moe_forward_host(0, x, mode=1)
+    assert syn.rel_err_rows(yp, yd) < TOL_BF16
