@@ -618,18 +618,27 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
                                   c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of));
     QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
     c->prof_mark("moe.pairs");
+    // the shared expert's two GEMMs (few, long blocks) run beside the routed ones
+    const bool fork = !c->profiling;
+    Launch S{fork ? c->side : c->stream, &c->launches};
+    if (fork) {
+        QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
+        QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+    }
+    QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
+                                    c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status));
+    if (!fork) c->prof_mark("moe.shared_gu");
+    QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
+                                  c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
+    if (!fork) c->prof_mark("moe.shared_dn");
+    if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
                                     c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status));
     c->prof_mark("moe.gu");
-    QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
-                                    c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status));
-    c->prof_mark("moe.shared_gu");
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, c->sel, c->pairs, c->mma_items[1],
                                   c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status));
     c->prof_mark("moe.dn");
-    QKM_LAUNCH(c, launch_down_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
-                                  c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
-    c->prof_mark("moe.shared_dn");
+    if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, y, n));
     c->prof_mark("moe.fold");
     return QKM_OK;

@@ -10,9 +10,12 @@
 // bf16 (single rounding of the exact f32 value) straight into the 128-byte-swizzled
 // K-major shared-memory layout, gather the matching 64 columns of the pairs' activation
 // rows (bf16) as the N operand, and one thread issues tcgen05.mma (kind::f16, bf16 inputs,
-// f32 accumulators in tensor memory).  Three shared-memory stages let dequantisation of
-// the next k-steps overlap the asynchronous MMAs; a stage is recycled when the commit of
-// the MMAs that read it arrives on its mbarrier.  All waits are bounded.
+// f32 accumulators in tensor memory).  Two shared-memory stages (two blocks per SM) let dequantisation of
+// the next k-steps overlap the asynchronous MMAs.  Eight warps produce operands and later
+// run the epilogue; a ninth warp only issues MMAs: producers arrive on a stage's "full"
+// mbarrier, the issuer waits for it, issues the k-step's MMAs and commits them to the
+// stage's "empty" mbarrier, which the producers wait on before refilling the stage.
+// All waits are bounded.
 //
 // Operand types: the gate/up GEMM runs on f16 operands (11-bit significands; x is scaled
 // per token by a power of two into f16 range and unscaled in the epilogue), the down GEMM
@@ -37,11 +40,13 @@
 namespace qkm {
 
 namespace pf {
-constexpr int kThreads = 256;
-constexpr int kStages = 3;
+constexpr int kThreads = 256;                  // producer/epilogue threads; one more warp issues the MMAs
+constexpr int kBlock = kThreads + 32;
+constexpr int kStages = 2;
 constexpr int kNT = 128;                       // pairs per block (N tile)
 constexpr int kTileBytes = 128 * 128;          // 128 rows x 64 bf16
-constexpr int kGridReplicas = 8;
+constexpr int kGridReplicas = 4;
+constexpr int kSignReplicas = 2;
 }  // namespace pf
 
 // ---- x -> f16 rows, each scaled by a power of two so that max|x| lands in [2^13, 2^14) -----------
@@ -137,36 +142,61 @@ __device__ __forceinline__ uint32_t pack16(float a, float b) {
 }
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) { return pack16<false>(a, b); }
 
-__device__ __forceinline__ void produce_iq3(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
-                                            const float4* __restrict__ s_grid, uint32_t lane, uint8_t* a_tile,
-                                            uint32_t row) {
+// IQ3_XXS raw bytes of one thread's row.  The index pairs are fetched once per 256-column
+// block with full 16-byte loads (every fetched sector is used); the two aux words and the
+// scale per k-step.
+struct Iq3Idx { uint4 t[4]; };                       // group t: index pairs of sub-blocks 0..7
+struct Iq3Raw { uint32_t idxw[4]; uint2 aux2; uint32_t dbits; };
+
+__device__ __forceinline__ Iq3Idx load_iq3_idx(const uint8_t* __restrict__ tile, uint32_t r16) {
     const uint32_t g = r16 & 7u, hf = r16 >> 3;
-    const uint2 aux2 = *reinterpret_cast<const uint2*>(tile + 1024 + 32 * r16 + 8 * q);
-    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + 1536 + 2 * r16));
-    uint32_t idxw[4];
+    Iq3Idx r;
 #pragma unroll
-    for (int t = 0; t < 4; ++t)
-        idxw[t] = *reinterpret_cast<const uint32_t*>(tile + hf * 512 + (4 * g + t) * 16 + 4 * q);
+    for (int t = 0; t < 4; ++t) r.t[t] = *reinterpret_cast<const uint4*>(tile + hf * 512 + (4 * g + t) * 16);
+    return r;
+}
+__device__ __forceinline__ Iq3Raw load_iq3(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q, const Iq3Idx& ix) {
+    Iq3Raw r;
+    r.aux2 = *reinterpret_cast<const uint2*>(tile + 1024 + 32 * r16 + 8 * q);
+    r.dbits = *reinterpret_cast<const uint16_t*>(tile + 1536 + 2 * r16);
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {
+        const uint32_t w[4] = {ix.t[t].x, ix.t[t].y, ix.t[t].z, ix.t[t].w};
+        r.idxw[t] = q == 0 ? w[0] : q == 1 ? w[1] : q == 2 ? w[2] : w[3];
+    }
+    return r;
+}
+
+// Dequantise to f16: a table gives the four magnitudes of a grid entry as two f16 pairs,
+// another the four sign masks of a 7-bit sign code; one packed multiply by the sub-block
+// scale (f16) and one XOR per pair.  Two roundings of 2^-12 each.
+//   s_gridh: [256][kGridReplicas] uint2      s_sign: [128][kSignReplicas] uint4
+__device__ __forceinline__ void produce_iq3(const Iq3Raw& raw, const uint2* __restrict__ s_gridh,
+                                            const uint4* __restrict__ s_sign, uint32_t lane, uint8_t* a_tile,
+                                            uint32_t row) {
+    const float d = f16_bits_to_f32(raw.dbits);
 #pragma unroll
     for (int j = 0; j < 2; ++j) {          // sub-block 2q + j
-        const uint32_t aux = j ? aux2.y : aux2.x;
-        const float db = d * (0.5f + (float)(aux >> 28)) * 0.5f;
+        const uint32_t aux = j ? raw.aux2.y : raw.aux2.x;
+        const __half2 db2 = __float2half2_rn(d * (0.5f + (float)(aux >> 28)) * 0.5f);
 #pragma unroll
         for (int t = 0; t < 4; ++t) {      // 8-element group t -> chunk 4j + t
-            const uint32_t pr = (idxw[t] >> (16 * j)) & 0xFFFFu;
-            const float4 m0 = s_grid[(pr & 0xFFu) * pf::kGridReplicas + (lane & 7u)];
-            const float4 m1 = s_grid[(pr >> 8) * pf::kGridReplicas + (lane & 7u)];
-            const uint32_t sg = signs8((aux >> (7 * t)) & 127u);
+            const uint32_t pr = (raw.idxw[t] >> (16 * j)) & 0xFFFFu;
+            const uint2 g0 = s_gridh[(pr & 0xFFu) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
+            const uint2 g1 = s_gridh[(pr >> 8) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
+            const uint4 sm = s_sign[((aux >> (7 * t)) & 127u) * pf::kSignReplicas + (lane & (pf::kSignReplicas - 1))];
             uint4 o;
-            o.x = pack16<true>(db * m0.x, db * m0.y) ^ (((sg & 1u) << 15) | ((sg & 2u) << 30));
-            o.y = pack16<true>(db * m0.z, db * m0.w) ^ (((sg & 4u) << 13) | ((sg & 8u) << 28));
-            o.z = pack16<true>(db * m1.x, db * m1.y) ^ (((sg & 16u) << 11) | ((sg & 32u) << 26));
-            o.w = pack16<true>(db * m1.z, db * m1.w) ^ (((sg & 64u) << 9) | ((sg & 128u) << 24));
+            __half2 v;
+            v = __hmul2(*reinterpret_cast<const __half2*>(&g0.x), db2); o.x = *reinterpret_cast<uint32_t*>(&v) ^ sm.x;
+            v = __hmul2(*reinterpret_cast<const __half2*>(&g0.y), db2); o.y = *reinterpret_cast<uint32_t*>(&v) ^ sm.y;
+            v = __hmul2(*reinterpret_cast<const __half2*>(&g1.x), db2); o.z = *reinterpret_cast<uint32_t*>(&v) ^ sm.z;
+            v = __hmul2(*reinterpret_cast<const __half2*>(&g1.y), db2); o.w = *reinterpret_cast<uint32_t*>(&v) ^ sm.w;
             *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + t)) = o;
         }
     }
 }
 
+template <int J0, int J1>
 __device__ __forceinline__ void produce_iq4(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
                                             const float* __restrict__ s_kv, uint32_t lane, uint8_t* a_tile,
                                             uint32_t row) {
@@ -175,7 +205,7 @@ __device__ __forceinline__ void produce_iq4(const uint8_t* __restrict__ tile, ui
     const float d = f16_bits_to_f32(hd.x & 0xFFFFu);
     const uint32_t sh = hd.x >> 16;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = J0; j < J1; ++j) {
         const uint32_t sb = 2 * q + j;
         const int ls = (int)(((hd.y >> (4 * sb)) & 0xFu) | (((sh >> (2 * sb)) & 3u) << 4)) - 32;
         const float dl = d * (float)ls;
@@ -202,12 +232,12 @@ __device__ __forceinline__ void produce_iq4(const uint8_t* __restrict__ tile, ui
     }
 }
 
-template <bool F16>
+template <bool F16, int J0, int J1>
 __device__ __forceinline__ void produce_q8(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
                                            uint8_t* a_tile, uint32_t row) {
     const uint32_t g = r16 & 7u, hf = r16 >> 3;
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {
+    for (int j = J0; j < J1; ++j) {
         const uint32_t blk = 2 * q + j;
         const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + 2 * (16 * blk + r16)));
         // lane slot (g, t): qs[4t..4t+3] then qs[16+4t..16+4t+3]
@@ -230,21 +260,34 @@ __device__ __forceinline__ void produce_q8(const uint8_t* __restrict__ tile, uin
 }
 
 // N operand: rows [0, n_mma) of the block's pairs, 64 columns at k0; rows >= n are zero.
-// `src_row(i)` returns the bf16 row of pair i.
-template <class RowFn>
-__device__ __forceinline__ void produce_b(uint8_t* b_tile, uint32_t n, uint32_t n_mma, uint32_t k0, RowFn src_row) {
-    for (uint32_t qd = threadIdx.x; qd < n_mma * 8; qd += pf::kThreads) {
-        const uint32_t row = qd >> 3, c = qd & 7u;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < n) v = *reinterpret_cast<const uint4*>(src_row(row) + k0 + 8 * c);
-        *reinterpret_cast<uint4*>(b_tile + umma::sw128_chunk(row, c)) = v;
+// Split in two so the global loads of the next k-step can be in flight during this one:
+// fetch_b reads this thread's (at most 4) 16-byte chunks, store_b writes them swizzled.
+// `row_ptr[i]` is the activation row of pair i (element type: 2 bytes).
+struct BRegs { uint4 v[4]; };
+
+template <class T>
+__device__ __forceinline__ BRegs fetch_b(const T* const* row_ptr, uint32_t n, uint32_t n_mma, uint32_t k0) {
+    BRegs b;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t qd = threadIdx.x + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
+        b.v[i] = make_uint4(0, 0, 0, 0);
+        if (qd < n_mma * 8 && row < n) b.v[i] = *reinterpret_cast<const uint4*>(row_ptr[row] + k0 + 8 * c);
+    }
+    return b;
+}
+__device__ __forceinline__ void store_b(uint8_t* b_tile, const BRegs& b, uint32_t n_mma) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t qd = threadIdx.x + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
+        if (qd < n_mma * 8) *reinterpret_cast<uint4*>(b_tile + umma::sw128_chunk(row, c)) = b.v[i];
     }
 }
 
 // ---- gate/up + SwiGLU ------------------------------------------------------------------------------------
 // FMT: QKM_TYPE_IQ3_XXS (routed experts) or QKM_TYPE_Q8_0 (shared expert).
 template <int FMT>
-__global__ void __launch_bounds__(pf::kThreads, 1)
+__global__ void __launch_bounds__(pf::kBlock, 2)
 gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restrict__ up_tiles,
                   const __half* __restrict__ xb, const float* __restrict__ x_inv_scale,
                   const uint32_t* __restrict__ pairs, const MmaItem* __restrict__ items,
@@ -253,22 +296,35 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     if (blockIdx.x >= *n_items_ptr) return;
     constexpr int kTile = FMT == QKM_TYPE_IQ3_XXS ? kTileIq3 : kTileQ8;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
-    __shared__ __align__(8) unsigned long long s_bar[pf::kStages + 1];
+    __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    float4* s_grid = reinterpret_cast<float4*>(smem + pf::kStages * 3 * pf::kTileBytes);
+    uint2* s_gridh = reinterpret_cast<uint2*>(smem + pf::kStages * 3 * pf::kTileBytes);
+    uint4* s_sign = reinterpret_cast<uint4*>(s_gridh + 256 * pf::kGridReplicas);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const MmaItem it = items[blockIdx.x];
     const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
     const uint32_t KB = d.n_embd / 256, RT16 = d.n_ff / 16, KS = d.n_embd / 64;
 
-    if (FMT == QKM_TYPE_IQ3_XXS)
+    if (FMT == QKM_TYPE_IQ3_XXS) {
         for (uint32_t i = tid; i < 256 * pf::kGridReplicas; i += pf::kThreads) {
             const uint32_t gw = c_iq3_grid[i / pf::kGridReplicas];
-            s_grid[i] = make_float4((float)(gw & 255u), (float)((gw >> 8) & 255u), (float)((gw >> 16) & 255u), (float)(gw >> 24));
+            __half2 lo = __floats2half2_rn((float)(gw & 255u), (float)((gw >> 8) & 255u));
+            __half2 hi = __floats2half2_rn((float)((gw >> 16) & 255u), (float)(gw >> 24));
+            s_gridh[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
         }
+        for (uint32_t i = tid; i < 128 * pf::kSignReplicas; i += pf::kThreads) {
+            const uint32_t sg = signs8(i / pf::kSignReplicas);
+            s_sign[i] = make_uint4(((sg & 1u) << 15) | ((sg & 2u) << 30), ((sg & 4u) << 13) | ((sg & 8u) << 28),
+                                   ((sg & 16u) << 11) | ((sg & 32u) << 26), ((sg & 64u) << 9) | ((sg & 128u) << 24));
+        }
+    }
     if (tid == 0) {
-        for (int s = 0; s <= pf::kStages; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
+        for (int s = 0; s < pf::kStages; ++s) {
+            mbar_init(smem_addr(&s_bar[s]), 1);                            // empty: one commit
+            mbar_init(smem_addr(&s_bar[pf::kStages + s]), pf::kThreads);   // full: every producer thread
+        }
+        mbar_init(smem_addr(&s_bar[2 * pf::kStages]), 1);
         mbar_fence_init();
     }
     if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), 256); umma::tmem_relinquish(); }
@@ -284,32 +340,61 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
     const uint8_t* wt = (mat ? up_tiles : gate_tiles) + (size_t)it.expert * KB * RT16 * kTile;
 
+    // activation rows of this block's pairs (one dependent load less per k-step)
+    __shared__ const __half* s_row[pf::kNT];
+    for (uint32_t i = tid; i < n; i += pf::kBlock) s_row[i] = xb + (size_t)(pairs[it.pair_off + i] >> 4) * d.n_embd;
+    __syncthreads();
+    if (tid >= pf::kThreads) {
+        // ---- MMA issuer warp
+        if (lane == 0) {
+            for (uint32_t ks = 0; ks < KS; ++ks) {
+                const uint32_t stage = ks % pf::kStages;
+                if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages + stage]), (ks / pf::kStages) & 1u)) timed_out = true;
+                umma::fence_after_sync();
+                const uint32_t a_g = smem_addr(smem + stage * 3 * pf::kTileBytes), a_u = a_g + pf::kTileBytes, b = a_g + 2 * pf::kTileBytes;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const bool acc = (ks | (uint32_t)j) != 0;
+                    umma::mma_f16_ss(tmem, umma::smem_desc(a_g + 32 * j), umma::smem_desc(b + 32 * j), idesc, acc);
+                    umma::mma_f16_ss(tmem + 128, umma::smem_desc(a_u + 32 * j), umma::smem_desc(b + 32 * j), idesc, acc);
+                }
+                umma::commit(smem_addr(&s_bar[stage]));
+                if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[2 * pf::kStages]));
+            }
+        }
+    } else {
+    // ---- producer warps
+    Iq3Raw raw{};   // this thread's quant bytes of the current k-step, fetched one step ahead
+    Iq3Idx ix{};    // index pairs of the current 256-column block
+    if (FMT == QKM_TYPE_IQ3_XXS) {
+        ix = load_iq3_idx(wt + (size_t)rt16 * kTile, r16);
+        raw = load_iq3(wt + (size_t)rt16 * kTile, r16, 0, ix);
+    }
+    BRegs breg = fetch_b(s_row, n, n_mma, 0);
     for (uint32_t ks = 0; ks < KS; ++ks) {
         const uint32_t stage = ks % pf::kStages;
+        Iq3Raw next{};
+        BRegs bnext{};
+        if (ks + 1 < KS) {
+            if (FMT == QKM_TYPE_IQ3_XXS) {
+                const uint8_t* ntile = wt + ((size_t)((ks + 1) >> 2) * RT16 + rt16) * kTile;
+                if (((ks + 1) & 3u) == 0) ix = load_iq3_idx(ntile, r16);
+                next = load_iq3(ntile, r16, (ks + 1) & 3u, ix);
+            }
+            bnext = fetch_b(s_row, n, n_mma, (ks + 1) * 64);
+        }
         if (ks >= (uint32_t)pf::kStages)
             if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
         uint8_t* st = smem + stage * 3 * pf::kTileBytes;
         const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-        if (FMT == QKM_TYPE_IQ3_XXS) produce_iq3(tile, r16, ks & 3u, s_grid, lane, st + mat * pf::kTileBytes, r);
-        else produce_q8<true>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
-        produce_b(st + 2 * pf::kTileBytes, n, n_mma, ks * 64,
-                  [&](uint32_t i) { return xb + (size_t)(pairs[it.pair_off + i] >> 4) * d.n_embd; });
+        if (FMT == QKM_TYPE_IQ3_XXS) { produce_iq3(raw, s_gridh, s_sign, lane, st + mat * pf::kTileBytes, r); raw = next; }
+        else produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+        store_b(st + 2 * pf::kTileBytes, breg, n_mma);
+        breg = bnext;
         umma::fence_smem_to_async();
-        __syncthreads();
-        if (tid == 0) {
-            umma::fence_after_sync();
-            const uint32_t a_g = smem_addr(st), a_u = a_g + pf::kTileBytes, b = a_g + 2 * pf::kTileBytes;
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const bool acc = (ks | (uint32_t)j) != 0;
-                umma::mma_bf16_ss(tmem, umma::smem_desc(a_g + 32 * j), umma::smem_desc(b + 32 * j), idesc, acc);
-                umma::mma_bf16_ss(tmem + 128, umma::smem_desc(a_u + 32 * j), umma::smem_desc(b + 32 * j), idesc, acc);
-            }
-            umma::commit(smem_addr(&s_bar[stage]));
-            if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[pf::kStages]));
-        }
+        mbar_arrive(smem_addr(&s_bar[pf::kStages + stage]));
     }
-    if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages]), 0)) timed_out = true;
+    if (!mbar_wait_bounded(smem_addr(&s_bar[2 * pf::kStages]), 0)) timed_out = true;
     umma::fence_after_sync();
 
     // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) and every other 16-column block
@@ -334,6 +419,7 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
             }
         }
     }
+    }  // producer / epilogue warps
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
@@ -343,7 +429,7 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
 // ---- down -------------------------------------------------------------------------------------------------
 // FMT: QKM_TYPE_IQ4_XS (routed) or QKM_TYPE_Q8_0 (shared).  contrib[pair position][n_embd].
 template <int FMT>
-__global__ void __launch_bounds__(pf::kThreads, 1)
+__global__ void __launch_bounds__(pf::kBlock, 2)
 down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restrict__ hb,
                 const qkm_sel* __restrict__ sel, const uint32_t* __restrict__ pairs,
                 const MmaItem* __restrict__ items, const uint32_t* __restrict__ n_items_ptr,
@@ -351,7 +437,7 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     if (blockIdx.x >= *n_items_ptr) return;
     constexpr int kTile = FMT == QKM_TYPE_IQ4_XS ? kTileIq4 : kTileQ8;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
-    __shared__ __align__(8) unsigned long long s_bar[pf::kStages + 1];
+    __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     float* s_kv = reinterpret_cast<float*>(smem + pf::kStages * 2 * pf::kTileBytes);
@@ -363,7 +449,11 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     if (FMT == QKM_TYPE_IQ4_XS)
         for (uint32_t i = tid; i < 16 * 32; i += pf::kThreads) s_kv[i] = (float)c_iq4_values[i >> 5];
     if (tid == 0) {
-        for (int s = 0; s <= pf::kStages; ++s) mbar_init(smem_addr(&s_bar[s]), 1);
+        for (int s = 0; s < pf::kStages; ++s) {
+            mbar_init(smem_addr(&s_bar[s]), 1);                            // empty: one commit
+            mbar_init(smem_addr(&s_bar[pf::kStages + s]), pf::kThreads);   // full: every producer thread
+        }
+        mbar_init(smem_addr(&s_bar[2 * pf::kStages]), 1);
         mbar_fence_init();
     }
     if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), 128); umma::tmem_relinquish(); }
@@ -374,36 +464,55 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     const uint32_t idesc = umma::instr_desc_bf16(n_mma);
     bool timed_out = false;
 
-    // producer role: threads 0..127 write the A rows, all threads help with B
+    // producer role: thread -> row (tid & 127), 32-column half (tid >> 7) of the A tile; all threads help with B
     const uint32_t r = tid & 127u;
     const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
     const uint8_t* wt = tiles + (size_t)it.expert * KB * RT16 * kTile;
 
+    __shared__ const __nv_bfloat16* s_row[pf::kNT];
+    for (uint32_t i = tid; i < n; i += pf::kBlock) s_row[i] = hb + (size_t)(it.pair_off + i) * d.n_ff;
+    __syncthreads();
+    if (tid >= pf::kThreads) {
+        // ---- MMA issuer warp
+        if (lane == 0) {
+            for (uint32_t ks = 0; ks < KS; ++ks) {
+                const uint32_t stage = ks % pf::kStages;
+                if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages + stage]), (ks / pf::kStages) & 1u)) timed_out = true;
+                umma::fence_after_sync();
+                const uint32_t a = smem_addr(smem + stage * 2 * pf::kTileBytes), b = a + pf::kTileBytes;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    umma::mma_f16_ss(tmem, umma::smem_desc(a + 32 * j), umma::smem_desc(b + 32 * j), idesc, (ks | (uint32_t)j) != 0);
+                umma::commit(smem_addr(&s_bar[stage]));
+                if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[2 * pf::kStages]));
+            }
+        }
+    } else {
+    // ---- producer warps
+    BRegs breg = fetch_b(s_row, n, n_mma, 0);
     for (uint32_t ks = 0; ks < KS; ++ks) {
         const uint32_t stage = ks % pf::kStages;
+        BRegs bnext{};
+        if (ks + 1 < KS) bnext = fetch_b(s_row, n, n_mma, (ks + 1) * 64);
         if (ks >= (uint32_t)pf::kStages)
             if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
         uint8_t* st = smem + stage * 2 * pf::kTileBytes;
-        if (tid < 128) {
+        {
             const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-            if (FMT == QKM_TYPE_IQ4_XS) produce_iq4(tile, r16, ks & 3u, s_kv, lane, st, r);
-            else produce_q8<false>(tile, r16, ks & 3u, st, r);
+            if (tid < 128) {
+                if (FMT == QKM_TYPE_IQ4_XS) produce_iq4<0, 1>(tile, r16, ks & 3u, s_kv, lane, st, r);
+                else produce_q8<false, 0, 1>(tile, r16, ks & 3u, st, r);
+            } else {
+                if (FMT == QKM_TYPE_IQ4_XS) produce_iq4<1, 2>(tile, r16, ks & 3u, s_kv, lane, st, r);
+                else produce_q8<false, 1, 2>(tile, r16, ks & 3u, st, r);
+            }
         }
-        produce_b(st + pf::kTileBytes, n, n_mma, ks * 64,
-                  [&](uint32_t i) { return hb + (size_t)(it.pair_off + i) * d.n_ff; });
+        store_b(st + pf::kTileBytes, breg, n_mma);
+        breg = bnext;
         umma::fence_smem_to_async();
-        __syncthreads();
-        if (tid == 0) {
-            umma::fence_after_sync();
-            const uint32_t a = smem_addr(st), b = a + pf::kTileBytes;
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-                umma::mma_bf16_ss(tmem, umma::smem_desc(a + 32 * j), umma::smem_desc(b + 32 * j), idesc, (ks | (uint32_t)j) != 0);
-            umma::commit(smem_addr(&s_bar[stage]));
-            if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[pf::kStages]));
-        }
+        mbar_arrive(smem_addr(&s_bar[pf::kStages + stage]));
     }
-    if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages]), 0)) timed_out = true;
+    if (!mbar_wait_bounded(smem_addr(&s_bar[2 * pf::kStages]), 0)) timed_out = true;
     umma::fence_after_sync();
     {
         const uint32_t lg = warp & 3u, row = 32 * lg + lane;
@@ -424,6 +533,7 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
             }
         }
     }
+    }  // producer / epilogue warps
     umma::fence_before_sync();
     __syncthreads();
     if (warp == 0) umma::tmem_dealloc(tmem, 128);
@@ -468,10 +578,10 @@ template <int FMT>
 static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
                                      const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
                                      const uint32_t* n_items, uint32_t max_items, float* h, void* hb, uint32_t* status) {
-    const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 256 * pf::kGridReplicas * 16 + 1024;
+    const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 256 * pf::kGridReplicas * 8 + 128 * pf::kSignReplicas * 16 + 1024;
     cudaError_t e = cudaFuncSetAttribute(gateup_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gateup_mma_kernel<FMT><<<max_items, pf::kThreads, smem, L.stream>>>(
+    gateup_mma_kernel<FMT><<<max_items, pf::kBlock, smem, L.stream>>>(
         (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, (const __half*)xb, x_inv_scale, pairs, items, n_items, h,
         (__nv_bfloat16*)hb, d, status);
     L.count();
@@ -497,7 +607,7 @@ static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const voi
     const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + 16 * 32 * 4 + 1024;
     cudaError_t e = cudaFuncSetAttribute(down_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    down_mma_kernel<FMT><<<max_items, pf::kThreads, smem, L.stream>>>(
+    down_mma_kernel<FMT><<<max_items, pf::kBlock, smem, L.stream>>>(
         (const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items, n_items, contrib, d, status);
     L.count();
     return cudaGetLastError();

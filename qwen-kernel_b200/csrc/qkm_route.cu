@@ -115,6 +115,90 @@ cudaError_t launch_logits(const Launch& L, const qkm_dims& d, uint32_t router_ty
     return cudaGetLastError();
 }
 
+// ---- logits for many tokens: 64 x 64 output tiles, f32 FMA -------------------------------------
+// logits[t][e] = sum_k x[t][k] * w[e][k], k ascending in one chain per output (the refined
+// selection is told the chain length).  Operands are staged through shared memory 16
+// columns at a time; each thread owns a 4 x 4 block of outputs.
+template <int TYPE>
+__global__ void __launch_bounds__(256)
+logits_gemm_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, float* __restrict__ logits,
+                   uint32_t n_expert, uint32_t K, uint32_t n_tokens) {
+    __shared__ __align__(16) float s_xt[16][64 + 4];   // [k][token]
+    __shared__ __align__(16) float s_wt[16][64 + 4];   // [k][expert]
+    const uint32_t tid = threadIdx.x, tx = tid & 15u, ty = tid >> 4;
+    const uint32_t e0 = blockIdx.x * 64, t0 = blockIdx.y * 64;
+    const size_t rb = row_bytes(TYPE, K);
+    float acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+    // loader role: thread -> (row = tid / 4, 4 columns at (tid % 4) * 4) of both operand tiles
+    const uint32_t lr = tid >> 2, lc = (tid & 3u) * 4;
+    auto fetch = [&](uint32_t k0, float4& xv, float4& wv) {
+        xv = make_float4(0.f, 0.f, 0.f, 0.f); wv = xv;
+        if (t0 + lr < n_tokens) xv = *reinterpret_cast<const float4*>(x + (size_t)(t0 + lr) * K + k0 + lc);
+        if (e0 + lr < n_expert) {
+            const uint8_t* row = router + (size_t)(e0 + lr) * rb;
+            if (TYPE == QKM_TYPE_F32) {
+                wv = *reinterpret_cast<const float4*>(row + (size_t)(k0 + lc) * 4);
+            } else {
+                const uint2 hv = *reinterpret_cast<const uint2*>(row + (size_t)(k0 + lc) * 2);
+                wv = make_float4(f16_bits_to_f32(hv.x & 0xFFFFu), f16_bits_to_f32(hv.x >> 16),
+                                 f16_bits_to_f32(hv.y & 0xFFFFu), f16_bits_to_f32(hv.y >> 16));
+            }
+        }
+    };
+    float4 xv, wv;
+    fetch(0, xv, wv);
+    for (uint32_t k0 = 0; k0 < K; k0 += 16) {
+        __syncthreads();
+        s_xt[lc + 0][lr] = xv.x; s_xt[lc + 1][lr] = xv.y; s_xt[lc + 2][lr] = xv.z; s_xt[lc + 3][lr] = xv.w;
+        s_wt[lc + 0][lr] = wv.x; s_wt[lc + 1][lr] = wv.y; s_wt[lc + 2][lr] = wv.z; s_wt[lc + 3][lr] = wv.w;
+        __syncthreads();
+        if (k0 + 16 < K) fetch(k0 + 16, xv, wv);   // next tile's loads fly during this tile's math
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float4 a = *reinterpret_cast<const float4*>(&s_xt[k][ty * 4]);
+            const float4 b = *reinterpret_cast<const float4*>(&s_wt[k][tx * 4]);
+            const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int i = 0; i < 4; ++i)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) acc[i][j] += av[i] * bv[j];
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t t = t0 + ty * 4 + i;
+        if (t < n_tokens) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const uint32_t e = e0 + tx * 4 + j;
+                if (e < n_expert) logits[(size_t)t * n_expert + e] = acc[i][j];
+            }
+        }
+    }
+}
+
+// |router row|^2, one warp per row
+template <int TYPE>
+__global__ void __launch_bounds__(256)
+row_norm2_kernel(const uint8_t* __restrict__ router, float* __restrict__ row_norm2, uint32_t n_expert, uint32_t K) {
+    const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (e >= n_expert) return;
+    const uint8_t* row = router + (size_t)e * row_bytes(TYPE, K);
+    float nrm = 0.f;
+    for (uint32_t u = lane; u < K / 8; u += 32) {
+        float w[8];
+        dequant8<TYPE>(row, u * 8, w);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) nrm += w[i] * w[i];
+    }
+    nrm = warp_sum(nrm);
+    if (lane == 0) row_norm2[e] = nrm;
+}
+
 // ---- helpers for block-wide (value, lowest id) argmax --------------------------------------
 // Key orders by value first; among equal values the smaller id gives the larger key.
 __device__ __forceinline__ unsigned long long rank_key(float v, uint32_t id) {
@@ -232,7 +316,7 @@ __global__ void __launch_bounds__(256)
 refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict__ logits,
                      const float* __restrict__ row_norm2, const float* __restrict__ gis,
                      const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d,
-                     int8_t* __restrict__ xplanes, float* __restrict__ xscale) {
+                     int8_t* __restrict__ xplanes, float* __restrict__ xscale, float eps_terms) {
     extern __shared__ float s_x[];  // n_embd floats
     __shared__ double s_val[512];   // f64 logit of every candidate, -inf elsewhere
     __shared__ float s_log[512];
@@ -315,10 +399,10 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     }
     __syncthreads();
     const float kth = s_kth;
-    // Error bound of one f32 logit: each lane adds at most K/32 products in sequence, then
-    // trees; |err| <= (K/32 + 8) * 2^-24 * sum|w_k x_k| <= that * |w| * |x|.
+    // Error bound of one f32 logit whose longest chain of additions has eps_terms links:
+    // |err| <= eps_terms * 2^-24 * sum|w_k x_k| <= that * |w| * |x|.
     // Doubled for safety, and doubled again because two logits are compared.
-    const float eps = (float)(d.n_embd / 32 + 8) * 5.9604645e-8f * sqrtf(r2) * sqrtf(x2);
+    const float eps = eps_terms * 5.9604645e-8f * sqrtf(r2) * sqrtf(x2);
     const float thresh = kth - 4.0f * eps;
     // candidates: every expert at or above the threshold
     // (written as !(l < thresh) so a NaN threshold - NaN in x - admits every expert)
@@ -394,15 +478,33 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
                                 uint32_t n_tokens, void* scratch, int8_t* xplanes, float* xscale) {
     if (n_tokens == 0) return cudaSuccess;
+    if (router_type != QKM_TYPE_F32 && router_type != QKM_TYPE_F16) return cudaErrorInvalidValue;
     float* logits = (float*)scratch;
     float* norm2 = logits + (size_t)n_tokens * d.n_expert;
-    cudaError_t e = launch_logits(L, d, router_type, router, x, logits, norm2, n_tokens);
-    if (e != cudaSuccess) return e;
     const uint8_t* r = (const uint8_t*)router;
+    float eps_terms;
+    if (n_tokens >= 1024) {   // many tokens: tiled GEMM, one chain of n_embd additions per logit
+        const dim3 grid((d.n_expert + 63) / 64, (n_tokens + 63) / 64);
+        if (router_type == QKM_TYPE_F32) {
+            row_norm2_kernel<QKM_TYPE_F32><<<(d.n_expert + 7) / 8, 256, 0, L.stream>>>(r, norm2, d.n_expert, d.n_embd);
+            logits_gemm_kernel<QKM_TYPE_F32><<<grid, 256, 0, L.stream>>>(r, x, logits, d.n_expert, d.n_embd, n_tokens);
+        } else {
+            row_norm2_kernel<QKM_TYPE_F16><<<(d.n_expert + 7) / 8, 256, 0, L.stream>>>(r, norm2, d.n_expert, d.n_embd);
+            logits_gemm_kernel<QKM_TYPE_F16><<<grid, 256, 0, L.stream>>>(r, x, logits, d.n_expert, d.n_embd, n_tokens);
+        }
+        L.count(2);
+        cudaError_t e = cudaGetLastError();
+        if (e != cudaSuccess) return e;
+        eps_terms = (float)d.n_embd + 8.f;
+    } else {
+        cudaError_t e = launch_logits(L, d, router_type, router, x, logits, norm2, n_tokens);
+        if (e != cudaSuccess) return e;
+        eps_terms = (float)(d.n_embd / 32 + 8);
+    }
     if (router_type == QKM_TYPE_F32)
-        refine_select_kernel<QKM_TYPE_F32><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
+        refine_select_kernel<QKM_TYPE_F32><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
     else
-        refine_select_kernel<QKM_TYPE_F16><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale);
+        refine_select_kernel<QKM_TYPE_F16><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
     L.count();
     return cudaGetLastError();
 }
