@@ -249,6 +249,30 @@ QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 QKM_API const qkm_sel *qkm_sel_device(const qkm_ctx *c);
 QKM_API const float   *qkm_h_device(const qkm_ctx *c);
 
+/* Router logits + selection WITHOUT any device allocation and without a context.
+ * NO COUNTERPART IN THE REFERENCE: it exists for hosts that may not take memory from
+ * the driver while they run (a server that already owns all free HBM through its own
+ * pool, a latency-bound loop in which an allocation may stall the device, a plugin in
+ * a process with externally accounted memory).  Same arithmetic and results as
+ * qkm_moe_route_select.  Scratch is a fixed array inside the library image, one per
+ * device, shared by all calls on that device:
+ *   - limits: n_tokens * n_expert <= QKM_STATIC_ROUTE_MAX_LOGITS and
+ *     n_expert <= QKM_STATIC_ROUTE_MAX_EXPERTS; larger calls return QKM_ERR_ARG and
+ *     write the reason to `err`;
+ *   - nothing in the array needs to start at zero (each call writes all it reads);
+ *   - calls that overlap in time on one device race on the array: keep them on one
+ *     stream or order them with events;
+ *   - the first call on a device looks up the array's address (and lets the runtime
+ *     initialise the device if the process has not used it): make it during start-up,
+ *     before any stream capture.
+ * `stream` is a cudaStream_t (NULL = default stream); all pointers are device memory. */
+#define QKM_STATIC_ROUTE_MAX_LOGITS  32768u
+#define QKM_STATIC_ROUTE_MAX_EXPERTS 512u
+QKM_API int qkm_route_select_static(int device, void *stream, const qkm_dims *dims,
+                                    uint32_t router_type, const void *router,
+                                    const float *gate_inp_shexp, const float *x, qkm_sel *sel,
+                                    uint32_t n_tokens, char *err, size_t err_len);
+
 #ifdef __cplusplus
 }
 #endif

@@ -81,6 +81,7 @@ SIGNATURES = {
     "qkm_last_sel": (_I, [_VP, _VP, _U32]),
     "qkm_sel_device": (_VP, [_VP]),
     "qkm_h_device": (_VP, [_VP]),
+    "qkm_route_select_static": (_I, [_I, _VP, C.POINTER(Dims), _U32, _VP, _VP, _VP, _VP, _U32, C.c_char_p, _SZ]),
 }
 
 _lib = None
