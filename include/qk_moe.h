@@ -249,6 +249,36 @@ QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 QKM_API const qkm_sel *qkm_sel_device(const qkm_ctx *c);
 QKM_API const float   *qkm_h_device(const qkm_ctx *c);
 
+/* ---- expert parallel (one context per GPU; no counterpart in the reference, which is
+ * single-GPU: the arithmetic per (token, expert) is that of src/main.cpp:1351-1369) -------
+ * Rank r of n_ranks is a context opened with expert_first = r * n_expert / n_ranks and
+ * expert_count = n_expert / n_ranks; router and shared-expert weights are replicated, the
+ * three *_exps tensors hold the shard.  Tokens are data-parallel.  Per layer and rank:
+ *
+ *   qkm_ep_dispatch        route the n local tokens; for every rank that owns at least one
+ *                          of a token's experts, one row of xsend (the token's x) and of
+ *                          selsend (its selection record), rank by rank, ascending token
+ *                          within a rank.  counts_host[r] = rows for rank r.  Blocks until
+ *                          the counts are on the host.  xsend / selsend must hold
+ *                          n * min(n_ranks, n_used) rows.
+ *   (caller)               all-to-all-v of xsend and selsend by counts -> xrecv, selrecv
+ *   qkm_ep_shared          shared expert of the local tokens; overlaps the exchange
+ *   qkm_ep_expert_forward  resident experts over the n_recv received rows: partial[i] =
+ *                          sum over the slots of row i whose expert is resident of
+ *                          w_slot * down(silu(gate x) * up x); n_recv <= max_tokens
+ *   (caller)               all-to-all-v of partial back (the reverse split) -> back, which
+ *                          then has one row per row of xsend, in the same order
+ *   qkm_ep_combine         y[t] = shared(t) + sum of t's rows of back in rank order
+ */
+QKM_API int qkm_ep_dispatch(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
+                            uint32_t n_ranks, float *xsend, qkm_sel *selsend,
+                            uint32_t *counts_host);
+QKM_API int qkm_ep_shared(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens);
+QKM_API int qkm_ep_expert_forward(qkm_ctx *c, uint32_t layer, const float *xrecv,
+                                  const qkm_sel *selrecv, uint32_t n_recv, float *partial);
+QKM_API int qkm_ep_combine(qkm_ctx *c, uint32_t n_tokens, uint32_t n_ranks, const float *back,
+                           float *y);
+
 /* Router logits + selection WITHOUT any device allocation and without a context.
  * NO COUNTERPART IN THE REFERENCE: it exists for hosts that may not take memory from
  * the driver while they run (a server that already owns all free HBM through its own

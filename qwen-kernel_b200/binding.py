@@ -81,6 +81,10 @@ SIGNATURES = {
     "qkm_last_sel": (_I, [_VP, _VP, _U32]),
     "qkm_sel_device": (_VP, [_VP]),
     "qkm_h_device": (_VP, [_VP]),
+    "qkm_ep_dispatch": (_I, [_VP, _U32, _VP, _U32, _U32, _VP, _VP, _VP]),
+    "qkm_ep_shared": (_I, [_VP, _U32, _VP, _U32]),
+    "qkm_ep_expert_forward": (_I, [_VP, _U32, _VP, _VP, _U32, _VP]),
+    "qkm_ep_combine": (_I, [_VP, _U32, _U32, _VP, _VP]),
     "qkm_route_select_static": (_I, [_I, _VP, C.POINTER(Dims), _U32, _VP, _VP, _VP, _VP, _U32, C.c_char_p, _SZ]),
 }
 
@@ -274,6 +278,22 @@ class Context:
         y = np.empty_like(x)
         self.check(self.lib.qkm_moe_forward_host(self.h, layer_idx, mode, x.ctypes.data, x.shape[0], y.ctypes.data))
         return y
+
+    # -- expert parallel (this context is one shard; see include/qk_moe.h)
+    def ep_dispatch(self, layer_idx, x, n, n_ranks, xsend, selsend) -> list:
+        """Routes the n local tokens and packs the rows each rank needs; returns rows per rank."""
+        counts = (C.c_uint32 * n_ranks)()
+        self.check(self.lib.qkm_ep_dispatch(self.h, layer_idx, _p(x), n, n_ranks, _p(xsend), _p(selsend), counts))
+        return list(counts)
+
+    def ep_shared(self, layer_idx, x, n):
+        self.check(self.lib.qkm_ep_shared(self.h, layer_idx, _p(x), n))
+
+    def ep_expert_forward(self, layer_idx, xrecv, selrecv, n_recv, partial):
+        self.check(self.lib.qkm_ep_expert_forward(self.h, layer_idx, _p(xrecv), _p(selrecv), n_recv, _p(partial)))
+
+    def ep_combine(self, n, n_ranks, back, y):
+        self.check(self.lib.qkm_ep_combine(self.h, n, n_ranks, _p(back), _p(y)))
 
     def profile_enable(self, on=True):
         self.check(self.lib.qkm_profile_enable(self.h, int(on)))

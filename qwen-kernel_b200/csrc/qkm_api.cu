@@ -23,7 +23,8 @@ struct qkm_layer_dev {
     void* allocs[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     // tile-ordered copies for the streaming kernels (NULL where the type has none)
     void* tiles[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
-    bool stream_ok = false;  // routed gate/up and down both have tiles
+    bool tiles_ok = false;   // routed gate/up and down both have tiles
+    bool stream_ok = false;  // tiles, and every expert resident: the fused decode / prefill sequences apply
 };
 
 struct qkm_ctx {
@@ -67,6 +68,12 @@ struct qkm_ctx {
     float* contrib_p = nullptr;       // [max_tokens*(n_used+1)][n_embd]
     MmaItem* mma_items[4] = {nullptr, nullptr, nullptr, nullptr};  // gate/up, down, shared gate/up, shared down
     uint32_t* pos_of = nullptr;       // [max_tokens*(n_used+1)]
+    // expert-parallel exchange plan of the last qkm_ep_dispatch, allocated on first use
+    uint32_t ep_ranks = 0;
+    uint32_t* ep_counts = nullptr;       // [n_ranks + 1] rows per destination rank, then their sum
+    uint32_t* ep_counts_host = nullptr;  // pinned mirror
+    uint32_t* ep_send_tok = nullptr;     // [max_tokens * min(n_ranks, n_used)]
+    uint32_t* ep_send_pos = nullptr;     // [max_tokens][n_ranks]
     // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
@@ -204,11 +211,12 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
     }
     c->n_sms = prop.multiProcessorCount;
     // Streaming kernels: column blocks per row must be a power of two in [2,16] (one warp
-    // each), rows must split into whole items, and all experts must be resident.
+    // each) and rows must split into whole items.  (The fused decode / prefill sequences
+    // also need every expert resident; a sharded context uses the tiles through qkm_ep_*.)
     auto pow2_2_16 = [](uint32_t v) { return v >= 2 && v <= 16 && (v & (v - 1)) == 0; };
     c->shapes_stream_ok = pow2_2_16(d.n_embd / 256) && d.n_embd / 256 <= 8 && pow2_2_16(d.n_ff / 256) && d.n_used <= 15 &&
                           d.n_ff % gateup_stream_rows_per_item() == 0 &&
-                          d.n_embd % down_stream_rows_per_item() == 0 && ecount == d.n_expert;
+                          d.n_embd % down_stream_rows_per_item() == 0;
     if (c->shapes_stream_ok) {
         const size_t max_groups = (T * d.n_used + 1) / 2 + d.n_expert;  // token pairs per expert, rounded up
         const size_t sh_groups = (T + 1) / 2;
@@ -265,9 +273,10 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
-                       c->pos_of};
+                       c->pos_of, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
+    if (c->ep_counts_host) cudaFreeHost(c->ep_counts_host);
     if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->ev_join) cudaEventDestroy(c->ev_join);
@@ -367,7 +376,7 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
     }
     // tile-ordered copies for the streaming kernels (same bytes, re-ordered on the device)
     for (void*& p : l.tiles) { if (p) { QKM_CUDA(c, cudaFree(p)); p = nullptr; } }
-    l.stream_ok = false;
+    l.stream_ok = l.tiles_ok = false;
     if (c->shapes_stream_ok) {
         const qkm_dims& d = c->cfg.dims;
         struct { int idx; uint32_t type, mats, rows, K; } plan[] = {
@@ -384,7 +393,8 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
             cudaError_t e = launch_repack(c->L(), t.type, l.allocs[t.idx], l.tiles[t.idx], t.mats, t.rows, t.K);
             if (e != cudaSuccess) return fail(c, QKM_ERR_CUDA, "repack: %s", cudaGetErrorString(e));
         }
-        l.stream_ok = ok;
+        l.tiles_ok = ok;
+        l.stream_ok = ok && c->ecount == c->cfg.dims.n_expert;
     }
     QKM_CUDA(c, cudaStreamSynchronize(c->stream));
     l.w = *w;
@@ -585,6 +595,25 @@ static int prefill_generic(qkm_ctx* c, const qkm_layer_dev& ld, const float* x, 
     return QKM_OK;
 }
 
+// Scratch of the tensor-core (tcgen05) sequences, allocated on first use.
+static int ensure_prefill_scratch(qkm_ctx* c) {
+    if (c->xb) return QKM_OK;
+    const qkm_dims& d = c->cfg.dims;
+    const size_t T = c->cfg.max_tokens, rows = T * (d.n_used + 1);
+    const uint32_t NT = prefill_pairs_per_block();
+    const uint32_t rt_gu = d.n_ff / 128, rt_dn = d.n_embd / 128;
+    const size_t max_tiles = d.n_expert + (T * d.n_used + NT - 1) / NT, max_sh = (T + NT - 1) / NT;
+    QKM_CUDA(c, cudaMalloc(&c->xb, T * d.n_embd * 2));
+    QKM_CUDA(c, cudaMalloc(&c->hb, rows * d.n_ff * 2));
+    QKM_CUDA(c, cudaMalloc((void**)&c->contrib_p, rows * d.n_embd * sizeof(float)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[0], max_tiles * rt_gu * sizeof(MmaItem)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[1], max_tiles * rt_dn * sizeof(MmaItem)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[2], max_sh * rt_gu * sizeof(MmaItem)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[3], max_sh * rt_dn * sizeof(MmaItem)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->pos_of, rows * sizeof(uint32_t)));
+    return QKM_OK;
+}
+
 extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, float* y) {
     if (int rc = layer_ready(c, layer)) return rc;
     if (!x || !y) return QKM_ERR_ARG;
@@ -594,20 +623,9 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     const qkm_dims& d = c->cfg.dims;
     if (!ld.stream_ok || n == 0) return prefill_generic(c, ld, x, n, y);
     // tensor-core path: tokens grouped by expert, expert GEMMs on tcgen05 with bf16 operands
-    const size_t T = c->cfg.max_tokens, rows = T * (d.n_used + 1);
     const uint32_t NT = prefill_pairs_per_block();
     const uint32_t rt_gu = d.n_ff / 128, rt_dn = d.n_embd / 128;
-    const size_t max_tiles = d.n_expert + (T * d.n_used + NT - 1) / NT, max_sh = (T + NT - 1) / NT;
-    if (!c->xb) {
-        QKM_CUDA(c, cudaMalloc(&c->xb, T * d.n_embd * 2));
-        QKM_CUDA(c, cudaMalloc(&c->hb, rows * d.n_ff * 2));
-        QKM_CUDA(c, cudaMalloc((void**)&c->contrib_p, rows * d.n_embd * sizeof(float)));
-        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[0], max_tiles * rt_gu * sizeof(MmaItem)));
-        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[1], max_tiles * rt_dn * sizeof(MmaItem)));
-        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[2], max_sh * rt_gu * sizeof(MmaItem)));
-        QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[3], max_sh * rt_dn * sizeof(MmaItem)));
-        QKM_CUDA(c, cudaMalloc((void**)&c->pos_of, rows * sizeof(uint32_t)));
-    }
+    if (int rc = ensure_prefill_scratch(c)) return rc;
     const uint32_t tiles_now = d.n_expert < n * d.n_used ? d.n_expert + (n * d.n_used + NT - 1) / NT : n * d.n_used;
     const uint32_t sh_now = (n + NT - 1) / NT;
     c->prof_begin();
@@ -755,3 +773,133 @@ extern "C" QKM_API int qkm_last_sel(qkm_ctx* c, qkm_sel* sel_host, uint32_t n) {
 }
 extern "C" QKM_API const qkm_sel* qkm_sel_device(const qkm_ctx* c) { return c ? c->sel : nullptr; }
 extern "C" QKM_API const float* qkm_h_device(const qkm_ctx* c) { return c ? c->h : nullptr; }
+
+// ---------------------------------------------------------------- expert parallel
+// One context per GPU, opened with expert_first/expert_count naming its shard.  Per layer:
+//   qkm_ep_dispatch  : route the local tokens, decide which rows go to which rank, pack them
+//   (host: all-to-all of the rows and their selection records)
+//   qkm_ep_shared    : the shared expert of the local tokens (runs while the rows travel)
+//   qkm_ep_expert_forward : resident experts over the received rows -> one partial row each
+//   (host: all-to-all of the partial rows back)
+//   qkm_ep_combine   : y = shared + partials, summed in rank order
+// The reference has no multi-GPU path; the sequence keeps its single-GPU arithmetic
+// (src/main.cpp:1316-1387) and only changes the order in which a token's slots are summed.
+
+static int ep_check(qkm_ctx* c, uint32_t n_ranks) {
+    const qkm_dims& d = c->cfg.dims;
+    if (n_ranks == 0 || n_ranks > 64 || d.n_expert % n_ranks) return fail(c, QKM_ERR_ARG, "n_ranks %u does not divide n_expert %u", n_ranks, d.n_expert);
+    if (c->ecount != d.n_expert / n_ranks || c->efirst % c->ecount)
+        return fail(c, QKM_ERR_MODE, "context holds experts [%u,%u): not one of %u equal shards", c->efirst, c->efirst + c->ecount, n_ranks);
+    if (c->ep_ranks != n_ranks) {
+        if (c->ep_counts) { cudaFree(c->ep_counts); cudaFree(c->ep_send_tok); cudaFree(c->ep_send_pos); cudaFreeHost(c->ep_counts_host); }
+        c->ep_counts = c->ep_send_tok = c->ep_send_pos = c->ep_counts_host = nullptr;
+        c->ep_ranks = 0;
+        const size_t T = c->cfg.max_tokens, fan = n_ranks < d.n_used ? n_ranks : d.n_used;
+        QKM_CUDA(c, cudaMalloc((void**)&c->ep_counts, (n_ranks + 1) * sizeof(uint32_t)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->ep_send_tok, T * fan * sizeof(uint32_t)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->ep_send_pos, T * n_ranks * sizeof(uint32_t)));
+        QKM_CUDA(c, cudaMallocHost((void**)&c->ep_counts_host, (n_ranks + 1) * sizeof(uint32_t)));
+        c->ep_ranks = n_ranks;
+    }
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_dispatch(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t n_ranks,
+                                       float* xsend, qkm_sel* selsend, uint32_t* counts_host) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (!x || !xsend || !selsend || !counts_host) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    if (int rc = ep_check(c, n_ranks)) return rc;
+    const qkm_layer_dev& ld = c->layers[layer];
+    const qkm_layer_weights& w = ld.w;
+    const qkm_dims& d = c->cfg.dims;
+    const bool planes = ld.tiles_ok && n <= 64;   // the streamed shared-expert kernels read digit planes
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch,
+                                      planes ? c->xplanes : nullptr, planes ? c->xscale : nullptr));
+    QKM_LAUNCH(c, launch_ep_plan(c->L(), d, c->sel, n, n_ranks, c->ep_counts, c->ep_send_tok, c->ep_send_pos));
+    const uint32_t fan = n_ranks < d.n_used ? n_ranks : d.n_used;
+    QKM_LAUNCH(c, launch_ep_pack(c->L(), d, x, c->sel, c->ep_send_tok, c->ep_counts + n_ranks, n * fan, xsend, selsend));
+    QKM_CUDA(c, cudaMemcpyAsync(c->ep_counts_host, c->ep_counts, (n_ranks + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
+    QKM_CUDA(c, cudaStreamSynchronize(c->stream));
+    memcpy(counts_host, c->ep_counts_host, n_ranks * sizeof(uint32_t));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_shared(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (!x) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    if (n == 0) return QKM_OK;
+    const qkm_layer_dev& ld = c->layers[layer];
+    const qkm_layer_weights& w = ld.w;
+    const qkm_dims& d = c->cfg.dims;
+    if (!ld.tiles_ok) {
+        QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
+        QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, c->sel, c->y2, n));
+        return QKM_OK;
+    }
+    if (n <= 64) {   // streamed kernels of the decode sequence (digit planes written by qkm_ep_dispatch)
+        const uint32_t nb = (uint32_t)c->n_sms;
+        QKM_LAUNCH(c, launch_shared_plan(c->L(), d, n, c->pairs, c->items_sh_gu, d.n_ff / gateup_stream_rows_per_item(),
+                                         c->items_sh_dn, d.n_embd / down_stream_rows_per_item(), 2, c->n_items + 2));
+        QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xplanes, c->xscale, c->pairs,
+                                           c->items_sh_gu, c->n_items + 2, c->h, c->hpieces, nb, c->status));
+        QKM_LAUNCH(c, launch_down_stream(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, c->sel, c->pairs, c->items_sh_dn,
+                                         c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));
+        return QKM_OK;
+    }
+    // tensor-core kernels with an empty routed list: only the shared expert's tiles
+    if (int rc = ensure_prefill_scratch(c)) return rc;
+    const uint32_t NT = prefill_pairs_per_block(), sh_now = (n + NT - 1) / NT;
+    QKM_CUDA(c, cudaMemsetAsync(c->offsets, 0, sizeof(uint32_t), c->stream));
+    QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, 0, n, c->mma_items[0], c->mma_items[1], c->mma_items[2],
+                                  c->mma_items[3], c->n_items, c->pos_of, true));
+    QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
+    QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
+                                    c->n_items + 2, sh_now * (d.n_ff / 128), c->h, c->hb, c->status));
+    QKM_LAUNCH(c, launch_down_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
+                                  c->n_items + 3, sh_now * (d.n_embd / 128), c->contrib_p, c->status));
+    QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, c->y2, n));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_expert_forward(qkm_ctx* c, uint32_t layer, const float* xrecv, const qkm_sel* selrecv,
+                                             uint32_t n_recv, float* partial) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (n_recv == 0) return QKM_OK;
+    if (!xrecv || !selrecv || !partial) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n_recv)) return rc;
+    const qkm_layer_dev& ld = c->layers[layer];
+    const qkm_layer_weights& w = ld.w;
+    const qkm_dims& d = c->cfg.dims;
+    QKM_LAUNCH(c, launch_group_pairs(c->L(), d, selrecv, n_recv, c->offsets, c->pairs, c->efirst, c->ecount));
+    if (!ld.tiles_ok) {   // generic kernels on the raw layout
+        if (!c->contrib) QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
+        QKM_LAUNCH(c, launch_gateup_pairs(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, xrecv, c->offsets, c->pairs, c->h, n_recv, c->efirst, c->ecount));
+        QKM_CUDA(c, cudaMemsetAsync(c->contrib, 0, (size_t)n_recv * d.n_used * d.n_embd * sizeof(float), c->stream));
+        QKM_LAUNCH(c, launch_down_pairs(c->L(), d, w.down_type, w.down_exps, c->h, selrecv, c->offsets, c->pairs, c->contrib, n_recv, c->efirst, c->ecount));
+        QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, nullptr, partial, n_recv));
+        return QKM_OK;
+    }
+    if (int rc = ensure_prefill_scratch(c)) return rc;
+    const uint32_t NT = prefill_pairs_per_block();
+    const uint32_t np_max = n_recv * d.n_used;
+    const uint32_t tiles_now = c->ecount < np_max ? c->ecount + (np_max + NT - 1) / NT : np_max;
+    QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n_recv, c->mma_items[0], c->mma_items[1],
+                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of, false));
+    QKM_LAUNCH(c, launch_to_f16_rows(c->L(), xrecv, c->xb, c->xscale, n_recv, d.n_embd));
+    QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
+                                    c->n_items, tiles_now * (d.n_ff / 128), c->h, c->hb, c->status));
+    QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
+                                  c->n_items + 1, tiles_now * (d.n_embd / 128), c->contrib_p, c->status));
+    QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, partial, n_recv));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_combine(qkm_ctx* c, uint32_t n, uint32_t n_ranks, const float* back, float* y) {
+    if (!c || !y || (!back && n)) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    if (c->ep_ranks != n_ranks || !c->ep_send_pos) return fail(c, QKM_ERR_MODE, "qkm_ep_combine without a matching qkm_ep_dispatch");
+    QKM_LAUNCH(c, launch_ep_combine(c->L(), c->cfg.dims, back, c->ep_send_pos, c->y2, y, n, n_ranks));
+    return QKM_OK;
+}

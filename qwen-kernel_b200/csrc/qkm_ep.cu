@@ -1,0 +1,135 @@
+// Expert-parallel exchange helpers: which of this GPU's tokens go to which peer, packing
+// the rows to send, and summing the partial results that come back.
+//
+// Experts are sharded contiguously: rank r of G owns experts [r * n_expert / G, (r + 1) * n_expert / G).
+// A token is sent ONCE to every rank that owns at least one of its selected experts (not
+// once per expert), together with its selection record; the receiving rank runs its resident
+// experts over the received rows and returns one weighted partial row per received token.
+// The all-to-all itself is the host's (NCCL); these kernels only prepare and consume its
+// buffers, so nothing here waits on another GPU.
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "qkm_kernels.h"
+
+namespace qkm {
+
+namespace {
+
+constexpr uint32_t kInvalid = 0xFFFFFFFFu;
+constexpr int kPlanThreads = 1024;
+
+// One block.  counts[r] = tokens sent to rank r; send_tok = those tokens, rank by rank, each
+// rank's in ascending token order; send_pos[t][r] = row of token t in the send order for
+// rank r (kInvalid if t needs nothing from r).  total[0] = sum of counts.
+__global__ void __launch_bounds__(kPlanThreads)
+ep_plan_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t n_used, uint32_t experts_per_rank,
+               uint32_t n_ranks, uint32_t* __restrict__ counts, uint32_t* __restrict__ send_tok,
+               uint32_t* __restrict__ send_pos) {
+    __shared__ uint32_t s_warp[kPlanThreads / 32];
+    __shared__ uint32_t s_base;
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    if (tid == 0) s_base = 0;
+    __syncthreads();
+    for (uint32_t r = 0; r < n_ranks; ++r) {
+        uint32_t rank_count = 0;
+        for (uint32_t t0 = 0; t0 < n_tokens; t0 += kPlanThreads) {
+            const uint32_t t = t0 + tid;
+            bool need = false;
+            if (t < n_tokens)
+                for (uint32_t s = 0; s < n_used; ++s) need |= (sel[t].ids[s] / experts_per_rank) == r;
+            const uint32_t bal = __ballot_sync(0xFFFFFFFFu, need);
+            if (lane == 0) s_warp[warp] = __popc(bal);
+            __syncthreads();
+            uint32_t before = 0, all = 0;
+            for (uint32_t w = 0; w < kPlanThreads / 32; ++w) {
+                const uint32_t c = s_warp[w];
+                if (w < warp) before += c;
+                all += c;
+            }
+            const uint32_t base = s_base;
+            if (t < n_tokens) {
+                if (need) {
+                    const uint32_t pos = base + rank_count + before + __popc(bal & ((1u << lane) - 1u));
+                    send_tok[pos] = t;
+                    send_pos[(size_t)t * n_ranks + r] = pos;
+                } else {
+                    send_pos[(size_t)t * n_ranks + r] = kInvalid;
+                }
+            }
+            rank_count += all;
+            __syncthreads();
+        }
+        if (tid == 0) { counts[r] = rank_count; s_base += rank_count; }
+        __syncthreads();
+    }
+    if (tid == 0) counts[n_ranks] = s_base;
+}
+
+// One block per send row (blocks past the total leave): x row and selection record.
+__global__ void __launch_bounds__(256)
+ep_pack_kernel(const float* __restrict__ x, const qkm_sel* __restrict__ sel, const uint32_t* __restrict__ send_tok,
+               const uint32_t* __restrict__ total, float* __restrict__ xsend, qkm_sel* __restrict__ selsend,
+               uint32_t n_embd) {
+    const uint32_t p = blockIdx.x;
+    if (p >= *total) return;
+    const uint32_t t = send_tok[p];
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)t * n_embd);
+    float4* dst = reinterpret_cast<float4*>(xsend + (size_t)p * n_embd);
+    for (uint32_t i = threadIdx.x; i < n_embd / 4; i += blockDim.x) dst[i] = src[i];
+    const uint32_t* ss = reinterpret_cast<const uint32_t*>(sel + t);
+    uint32_t* sd = reinterpret_cast<uint32_t*>(selsend + p);
+    if (threadIdx.x < sizeof(qkm_sel) / 4) sd[threadIdx.x] = ss[threadIdx.x];
+}
+
+// y[t] = y2[t] + sum over ranks, in rank order, of the partial row that rank returned for t
+__global__ void __launch_bounds__(256)
+ep_combine_kernel(const float* __restrict__ back, const uint32_t* __restrict__ send_pos,
+                  const float* __restrict__ y2, float* __restrict__ y, uint32_t n_ranks, uint32_t n_embd) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (o >= n_embd) return;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t r = 0; r < n_ranks; ++r) {
+        const uint32_t p = send_pos[(size_t)t * n_ranks + r];
+        if (p == kInvalid) continue;
+        const float4 c = *reinterpret_cast<const float4*>(back + (size_t)p * n_embd + o);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+    }
+    if (y2) {
+        const float4 c = *reinterpret_cast<const float4*>(y2 + (size_t)t * n_embd + o);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+    }
+    *reinterpret_cast<float4*>(y + (size_t)t * n_embd + o) = v;
+}
+
+}  // namespace
+
+cudaError_t launch_ep_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens, uint32_t n_ranks,
+                           uint32_t* counts, uint32_t* send_tok, uint32_t* send_pos) {
+    if (n_ranks == 0 || d.n_expert % n_ranks) return cudaErrorInvalidValue;
+    ep_plan_kernel<<<1, kPlanThreads, 0, L.stream>>>(sel, n_tokens, d.n_used, d.n_expert / n_ranks, n_ranks, counts,
+                                                     send_tok, send_pos);
+    L.count();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pack(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel,
+                           const uint32_t* send_tok, const uint32_t* total, uint32_t max_rows, float* xsend,
+                           qkm_sel* selsend) {
+    if (max_rows == 0) return cudaSuccess;
+    ep_pack_kernel<<<max_rows, 256, 0, L.stream>>>(x, sel, send_tok, total, xsend, selsend, d.n_embd);
+    L.count();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_combine(const Launch& L, const qkm_dims& d, const float* back, const uint32_t* send_pos,
+                              const float* y2, float* y, uint32_t n_tokens, uint32_t n_ranks) {
+    if (n_tokens == 0) return cudaSuccess;
+    const dim3 grid((d.n_embd / 4 + 255) / 256, n_tokens);
+    ep_combine_kernel<<<grid, 256, 0, L.stream>>>(back, send_pos, y2, y, n_ranks, d.n_embd);
+    L.count();
+    return cudaGetLastError();
+}
+
+}  // namespace qkm

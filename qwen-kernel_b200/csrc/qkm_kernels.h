@@ -41,7 +41,8 @@ uint32_t prefill_pairs_per_block();
 cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float* inv_scale, uint32_t n_rows, uint32_t K);
 cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
                             uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
-                            MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of);
+                            MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of,
+                            bool with_shared = true);
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
@@ -136,5 +137,16 @@ cudaError_t launch_shared_down(const Launch& L, const qkm_dims& d, const void* d
 // y[t][o] = sum over slots (in order) of contrib[t][s][o], plus y2[t][o] when y2 != NULL
 cudaError_t launch_fold_contrib(const Launch& L, const qkm_dims& d, const float* contrib, const float* y2,
                                 float* y, uint32_t n_tokens);
+
+// ---- expert-parallel exchange helpers (qkm_ep.cu) --------------------------------------------
+// counts[0..n_ranks) rows per destination rank and counts[n_ranks] their sum; send_tok the
+// tokens in send order; send_pos[t][r] the row of token t among the rows sent (to rank r).
+cudaError_t launch_ep_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens, uint32_t n_ranks,
+                           uint32_t* counts, uint32_t* send_tok, uint32_t* send_pos);
+cudaError_t launch_ep_pack(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel,
+                           const uint32_t* send_tok, const uint32_t* total, uint32_t max_rows, float* xsend,
+                           qkm_sel* selsend);
+cudaError_t launch_ep_combine(const Launch& L, const qkm_dims& d, const float* back, const uint32_t* send_pos,
+                              const float* y2, float* y, uint32_t n_tokens, uint32_t n_ranks);
 
 }  // namespace qkm

@@ -78,15 +78,18 @@ to_f16_rows_kernel(const float* __restrict__ x, __half* __restrict__ xh, float* 
 // For every expert with pairs: its pairs in tiles of kNT, times the 128-row tiles of the
 // gate/up matrices (items_gu) and of the down matrix (items_dn).  Index n_expert_local is
 // the shared expert: its "pairs" are all tokens, stored after the routed pairs.
-// Also pos_of[t * (n_used+1) + s] = position of pair (t, s) in the grouped order.
+// Also pos_of[t * (n_used+1) + s] = position of pair (t, s) in the grouped order, or
+// 0xFFFFFFFF when the pair is not in the lists (its expert lives on another GPU, or the
+// shared expert is left out with with_shared == 0).
 __global__ void __launch_bounds__(512)
 mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, uint32_t n_expert_local,
-                uint32_t n_tokens, uint32_t n_used, uint32_t rt_gu, uint32_t rt_dn,
+                uint32_t n_tokens, uint32_t n_used, uint32_t rt_gu, uint32_t rt_dn, uint32_t with_shared,
                 MmaItem* __restrict__ items_gu, MmaItem* __restrict__ items_dn, MmaItem* __restrict__ items_sh_gu,
                 MmaItem* __restrict__ items_sh_dn, uint32_t* __restrict__ n_items, uint32_t* __restrict__ pos_of) {
     __shared__ uint32_t s_scan[512];
     const uint32_t e = threadIdx.x;
     const uint32_t np = offsets[n_expert_local];
+    for (uint32_t i = e; i < n_tokens * (n_used + 1); i += 512) pos_of[i] = 0xFFFFFFFFu;
     uint32_t tiles = 0, p0 = 0, n = 0;
     if (e < n_expert_local) { p0 = offsets[e]; n = offsets[e + 1] - p0; tiles = (n + pf::kNT - 1) / pf::kNT; }
     s_scan[e] = tiles;
@@ -106,7 +109,7 @@ mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pai
         for (uint32_t r = 0; r < rt_gu; ++r) { it.rt = (uint16_t)r; items_gu[(size_t)(first + ti) * rt_gu + r] = it; }
         for (uint32_t r = 0; r < rt_dn; ++r) { it.rt = (uint16_t)r; items_dn[(size_t)(first + ti) * rt_dn + r] = it; }
     }
-    const uint32_t sh_tiles = (n_tokens + pf::kNT - 1) / pf::kNT;
+    const uint32_t sh_tiles = with_shared ? (n_tokens + pf::kNT - 1) / pf::kNT : 0;
     for (uint32_t ti = e; ti < sh_tiles; ti += 512) {
         MmaItem it;
         it.expert = 0;
@@ -123,7 +126,7 @@ mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pai
         const uint32_t pr = pairs[p];
         pos_of[(pr >> 4) * (n_used + 1) + (pr & 15u)] = p;
     }
-    for (uint32_t t = e; t < n_tokens; t += 512) {
+    for (uint32_t t = e; t < (with_shared ? n_tokens : 0u); t += 512) {
         pairs[np + t] = (t << 4) | n_used;
         pos_of[t * (n_used + 1) + n_used] = np + t;
     }
@@ -548,7 +551,9 @@ __global__ void fold_pairs_kernel(const float* __restrict__ contrib, const uint3
     if (o >= n_embd) return;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t s = 0; s <= n_used; ++s) {
-        const float4 c = *reinterpret_cast<const float4*>(contrib + (size_t)pos_of[t * (n_used + 1) + s] * n_embd + o);
+        const uint32_t p = pos_of[t * (n_used + 1) + s];
+        if (p == 0xFFFFFFFFu) continue;
+        const float4 c = *reinterpret_cast<const float4*>(contrib + (size_t)p * n_embd + o);
         v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
     }
     *reinterpret_cast<float4*>(y + (size_t)t * n_embd + o) = v;
@@ -566,10 +571,11 @@ cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float*
 
 cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
                             uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
-                            MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of) {
+                            MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of,
+                            bool with_shared) {
     if (n_expert_local > 512) return cudaErrorInvalidValue;
     mma_plan_kernel<<<1, 512, 0, L.stream>>>(offsets, pairs, n_expert_local, n_tokens, d.n_used, d.n_ff / 128,
-                                             d.n_embd / 128, items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, pos_of);
+                                             d.n_embd / 128, with_shared ? 1u : 0u, items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, pos_of);
     L.count();
     return cudaGetLastError();
 }

@@ -1,0 +1,74 @@
+"""Expert-parallel MoE layer across the GPUs of one node: one process per GPU, experts
+sharded contiguously (rank r of G owns experts [r*E/G, (r+1)*E/G)), tokens data-parallel,
+one all-to-all each way per layer.
+
+The reference engine is single-GPU; what is kept from it is the per-(token, expert)
+arithmetic (src/main.cpp:1351-1369) and the buffer formats (the 160-byte selection record,
+f32 rows).  A token's row travels once to every rank that owns at least one of its selected
+experts; that rank returns one partial row, already weighted and summed over its experts.
+
+The engine object does the compute on this rank's device: `qwen_kernel_b200.Context` opened
+with this rank's expert range (its `ep_*` methods call the C ABI's `qkm_ep_*`).  The
+exchange is `torch.distributed.all_to_all_single` with split sizes: NCCL over NVLink between
+GPUs; tests run the same code over gloo with an engine that computes on the CPU.
+"""
+from __future__ import annotations
+
+import torch
+import torch.distributed as dist
+
+SEL_BYTES = 160
+
+
+def shard_range(n_expert: int, rank: int, world: int):
+    """(expert_first, expert_count) of `rank`: equal contiguous shards."""
+    if n_expert % world:
+        raise ValueError(f"n_expert {n_expert} is not divisible by {world} ranks")
+    per = n_expert // world
+    return rank * per, per
+
+
+class ExpertParallel:
+    """Runs MoE layers over a process group.  All buffers are allocated once."""
+
+    def __init__(self, engine, n_embd: int, n_used: int, max_local_tokens: int, max_recv_rows: int,
+                 device, group=None):
+        self.engine, self.group = engine, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.n_embd, self.device = n_embd, device
+        fan = min(self.world, n_used)
+        send_rows = max_local_tokens * fan
+        self.max_local, self.max_recv = max_local_tokens, max_recv_rows
+        f32, u8 = torch.float32, torch.uint8
+        self.xsend = torch.empty((send_rows, n_embd), dtype=f32, device=device)
+        self.selsend = torch.empty((send_rows, SEL_BYTES), dtype=u8, device=device)
+        self.back = torch.empty((send_rows, n_embd), dtype=f32, device=device)
+        self.xrecv = torch.empty((max_recv_rows, n_embd), dtype=f32, device=device)
+        self.selrecv = torch.empty((max_recv_rows, SEL_BYTES), dtype=u8, device=device)
+        self.partial = torch.empty((max_recv_rows, n_embd), dtype=f32, device=device)
+        self.counts_dev = torch.empty(self.world, dtype=torch.int64, device=device)
+        self.rcounts_dev = torch.empty(self.world, dtype=torch.int64, device=device)
+        self.last_counts = None
+
+    def forward(self, layer: int, x: torch.Tensor, n: int, y: torch.Tensor) -> None:
+        """y[:n] = MoE layer `layer` of the n local rows x[:n] (all ranks call this together)."""
+        if n > self.max_local:
+            raise ValueError(f"{n} local tokens exceed the {self.max_local} this object was sized for")
+        eng, W = self.engine, self.world
+        send = eng.ep_dispatch(layer, x, n, W, self.xsend, self.selsend)
+        # how many rows each peer sends here
+        self.counts_dev.copy_(torch.tensor(send, dtype=torch.int64), non_blocking=False)
+        dist.all_to_all_single(self.rcounts_dev, self.counts_dev, group=self.group)
+        recv = [int(v) for v in self.rcounts_dev.tolist()]
+        n_send, n_recv = sum(send), sum(recv)
+        if n_recv > self.max_recv:
+            raise RuntimeError(f"rank {self.rank}: {n_recv} rows arrive but buffers hold {self.max_recv}")
+        self.last_counts = (send, recv)
+        w1 = dist.all_to_all_single(self.xrecv[:n_recv], self.xsend[:n_send], recv, send, group=self.group, async_op=True)
+        w2 = dist.all_to_all_single(self.selrecv[:n_recv], self.selsend[:n_send], recv, send, group=self.group, async_op=True)
+        eng.ep_shared(layer, x, n)          # overlaps the exchange
+        w1.wait()
+        w2.wait()
+        eng.ep_expert_forward(layer, self.xrecv, self.selrecv, n_recv, self.partial)
+        dist.all_to_all_single(self.back[:n_send], self.partial[:n_recv], send, recv, group=self.group)
+        eng.ep_combine(n, W, self.back, y)

@@ -1,0 +1,127 @@
+"""Expert-parallel entry points (qkm_ep_*) on one GPU: G sharded contexts stand in for G
+ranks, the all-to-all is done by copying rows between their buffers on the host.  No
+kernel waits on another, so running the ranks one after the other is safe on one device.
+
+Tolerance: the expert GEMMs run on the tensor cores (bf16/f16 operands), so outputs are held
+to the prefill tolerance 2e-2 (row-scaled) against the f64 oracle; ids, send order and split
+sizes are exact.  Shapes without tiles take the f32 kernels and are held to 1e-5."""
+import numpy as np
+import pytest
+
+from ep_cpu_engine import plan_send
+
+pytestmark = pytest.mark.gpu
+
+TOL_BF16 = 2e-2
+TOL_F32 = 1e-5
+
+
+def run_ep(pkg, orc, syn, dims, layer, x_parts, G, tol):
+    from qwen_kernel_b200 import SEL_DTYPE
+    per = dims.n_expert // G
+    fan = min(G, dims.n_used)
+    T_all = sum(p.shape[0] for p in x_parts)
+    ctxs = []
+    for r in range(G):
+        c = pkg.Context(dims, n_layer=1, max_tokens=max(T_all, 1), device=0, expert_first=r * per, expert_count=per)
+        c.upload_layer(0, layer.expert_slice(r * per, per))
+        ctxs.append(c)
+    E = dims.n_embd
+    st = []
+    # phase 1: dispatch on every rank
+    for r, (c, xp) in enumerate(zip(ctxs, x_parts)):
+        n = xp.shape[0]
+        d_x = c.to_device(xp) if n else c.alloc(16)
+        d_xs, d_ss = c.alloc(max(n * fan, 1) * E * 4), c.alloc(max(n * fan, 1) * 160)
+        counts = c.ep_dispatch(0, d_x, n, G, d_xs, d_ss)
+        sel = c.last_sel(n) if n else np.zeros(0, SEL_DTYPE)
+        want_sel, _ = orc.route(layer, xp) if n else (sel, None)
+        assert np.array_equal(sel["ids"], want_sel["ids"])
+        want_counts, send_tok, _ = plan_send(sel["ids"], dims.n_used, per, G)
+        assert counts == want_counts
+        k = sum(counts)
+        xs = d_xs.download(np.float32, (k, E)) if k else np.zeros((0, E), np.float32)
+        ss = d_ss.download(np.uint8, (k, 160)) if k else np.zeros((0, 160), np.uint8)
+        assert np.array_equal(xs, xp[send_tok])
+        assert np.array_equal(ss.reshape(-1).view(SEL_DTYPE)["ids"], sel["ids"][send_tok])
+        c.ep_shared(0, d_x, n)
+        st.append(dict(n=n, d_x=d_x, counts=counts, xs=xs, ss=ss, bufs=[d_x, d_xs, d_ss]))
+    # phase 2: "all-to-all" on the host, expert forward on every rank
+    partials = []
+    for r, c in enumerate(ctxs):
+        chunks_x, chunks_s = [], []
+        for src in range(G):
+            off = sum(st[src]["counts"][:r])
+            cnt = st[src]["counts"][r]
+            chunks_x.append(st[src]["xs"][off:off + cnt])
+            chunks_s.append(st[src]["ss"][off:off + cnt])
+        xr, sr = np.concatenate(chunks_x), np.concatenate(chunks_s)
+        n_recv = xr.shape[0]
+        if n_recv:
+            d_xr, d_sr, d_p = c.to_device(xr), c.to_device(sr), c.alloc(n_recv * E * 4)
+            c.ep_expert_forward(0, d_xr, d_sr, n_recv, d_p)
+            partials.append(d_p.download(np.float32, (n_recv, E)))
+            for b in (d_xr, d_sr, d_p):
+                b.free()
+        else:
+            partials.append(np.zeros((0, E), np.float32))
+    # phase 3: rows travel back, combine
+    worst = 0.0
+    for r, c in enumerate(ctxs):
+        s = st[r]
+        back = []
+        for dst in range(G):   # rows this rank sent to dst come back in the same order
+            off = sum(st[src]["counts"][dst] for src in range(r))
+            back.append(partials[dst][off:off + s["counts"][dst]])
+        back = np.concatenate(back) if back else np.zeros((0, E), np.float32)
+        n = s["n"]
+        if n:
+            d_b = c.to_device(back) if back.shape[0] else c.alloc(16)
+            d_y = c.alloc(n * E * 4)
+            c.ep_combine(n, G, d_b, d_y)
+            y = d_y.download(np.float32, (n, E))
+            want = orc.moe_layer(layer, x_parts[r], threads=orc.hardware_threads())["y"]
+            worst = max(worst, syn.rel_err_rows(y, want))
+            d_b.free(); d_y.free()
+        for b in s["bufs"]:
+            b.free()
+    for c in ctxs:
+        c.close()
+    assert worst < tol, worst
+    return worst
+
+
+@pytest.mark.parametrize("G,T", [(2, 24), (4, 40), (8, 200), (2, 200)])
+def test_ep_full_size_shapes(pkg, orc, syn, G, T):
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=42)
+    x = syn.random_x(T, dims.n_embd, seed=61)
+    cuts = np.linspace(0, T, G + 1).astype(int)
+    cuts[1] = min(T, cuts[1] + 3)                       # uneven shares
+    parts = [x[cuts[r]:cuts[r + 1]] for r in range(G)]
+    run_ep(pkg, orc, syn, dims, layer, parts, G, TOL_BF16)
+
+
+def test_ep_rank_without_tokens(pkg, orc, syn):
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=43)
+    x = syn.random_x(5, dims.n_embd, seed=62)
+    run_ep(pkg, orc, syn, dims, layer, [x, x[:0]], 2, TOL_BF16)
+
+
+def test_ep_generic_kernels_f32(pkg, orc, syn):
+    """Q6_K down has no tile layout: the f32 kernels serve the shard, 1e-5 applies."""
+    dims = syn.Dims(n_embd=512, n_ff=256, n_expert=8, n_used=2)
+    layer = syn.make_layer(dims, seed=44, down_type=syn.Q6_K)
+    x = syn.random_x(10, dims.n_embd, seed=63)
+    run_ep(pkg, orc, syn, dims, layer, [x[:6], x[6:]], 2, TOL_F32)
+
+
+def test_ep_rejects_wrong_shard(pkg, syn):
+    dims = syn.Dims()
+    with pkg.Context(dims, n_layer=1, max_tokens=4, device=0, expert_first=0, expert_count=64) as c:
+        c.upload_layer(0, syn.make_layer(dims, seed=45).expert_slice(0, 64))
+        d = c.alloc(1 << 16)
+        with pytest.raises(pkg.QkmError):
+            c.ep_dispatch(0, d, 1, 8, d, d)      # 64 experts is a 4-way shard, not 8
+        d.free()
