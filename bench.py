@@ -2,19 +2,26 @@
 """Benchmark of the quantized MoE feed-forward path on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
-                    [--workload decode|prefill|gemv] [--layers L] [--slots S] [--tokens T]
+                    [--layers L] [--slots S] [--sub-layers P] [--no-sub]
+    (N > 1: python -m torch.distributed.run --nproc-per-node N ... bench.py --gpus N ...)
 
-One JSON line on stdout (rank 0).  The default workload is the decode
-configuration: a stack of 40 MoE layers (2048 / 512 / 256 experts / top-8, F16
-router, IQ3_XXS gate+up, IQ4_XS down, Q8_0 shared expert, per-layer seeds), 16
-concurrent slots with independent N(0,1) hidden rows per layer.  A step is one
-pass of the 16 rows through the 40 layers; value = tokens / second through the
-stack.  Weights are seeded synthetic ggml blocks (no model file is needed).
+One JSON line on stdout (rank 0).  The headline workload is the decode configuration: a
+stack of 40 MoE layers (2048 / 512 / 256 experts / top-8, F16 router, IQ3_XXS gate+up,
+IQ4_XS down, Q8_0 shared expert, per-layer seeds), 16 concurrent slots per GPU with
+independent N(0,1) hidden rows per layer.  A step is one pass of the rows through the 40
+layers; value = tokens / second through the stack, summed over the GPUs (each GPU holds
+the whole stack and decodes its own slots: weak scaling, no collective).  Weights are
+seeded synthetic ggml blocks (no model file is needed).
 
-Timing: W >= 3 untimed steps, then K steps between two CUDA events on the
-launching stream, bracketed by barrier + synchronize; max over ranks.  The
-working set of a step (about 40 x 143 MB of weights) is far larger than the
-126 MB L2, so every step streams its weights from HBM.
+Sub-objects of the same line: "prefill" - batched prefill of one layer at several chunk
+sizes on the tensor cores (1 GPU), or the expert-parallel layer with experts sharded over
+the N GPUs and NCCL all-to-all dispatch / combine (N > 1, strong scaling); "gemv" - the
+dense dequant-GEMV sweep (1 GPU).
+
+Timing: W >= 3 untimed steps, then K steps between two CUDA events on the launching
+stream, bracketed by barrier + synchronize; max over ranks.  The working set of a step
+(40 x ~140 MB of weights for decode, 8 rotating layers for prefill, > 250 MB of matrix
+copies for GEMV) is larger than the 126 MB L2, so every step streams its weights from HBM.
 """
 from __future__ import annotations
 
@@ -149,115 +156,305 @@ def decode_config(args, n_slots):
 
 # ------------------------------------------------------------------ GPU arm
 
-def run_decode(args, pkg, syn):
+class Ranks:
+    """Process-group plumbing: one rank per GPU under torchrun, a single process otherwise."""
+
+    def __init__(self, torch):
+        self.torch = torch
+        self.rank, self.local_rank, self.world = dist_env()
+        self.dev = torch.device("cuda", self.local_rank)
+        torch.cuda.set_device(self.dev)
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("nccl", device_id=self.dev)
+            self.dist = dist
+
+    def barrier(self):
+        if self.dist:
+            self.dist.barrier()
+        self.torch.cuda.synchronize(self.dev)
+
+    def max_over_ranks(self, v: float) -> float:
+        if not self.dist:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def sum_over_ranks(self, v: float) -> float:
+        if not self.dist:
+            return v
+        t = self.torch.tensor([v], dtype=self.torch.float64, device=self.dev)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return float(t.item())
+
+    def close(self):
+        if self.dist:
+            self.dist.barrier()
+            self.dist.destroy_process_group()
+
+
+def timed(torch, R: Ranks, stream, fn, steps: int, warmup: int) -> float:
+    """ms per step: warm-up, barrier + synchronize, CUDA events on the launching stream
+    around exactly `steps` calls, barrier + synchronize, max over ranks."""
+    for _ in range(warmup):
+        fn()
+    R.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    R.barrier()
+    return R.max_over_ranks(e0.elapsed_time(e1) / steps)
+
+
+def run_ours(args, pkg, syn):
     import torch
-    rank, local_rank, world = dist_env()
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    dev = torch.device("cuda", local_rank)
-    torch.cuda.set_device(dev)
+    R = Ranks(torch)
+    dev, world, rank = R.dev, R.world, R.rank
     dims = syn.Dims()
     L, S = args.layers, args.slots
-    if world > 1:
-        raise SystemExit("expert-parallel decode is launched through --workload ep (not built into this path yet)")
-
-    ctx = pkg.Context(dims, n_layer=L, max_tokens=S, device=local_rank)
-    stream = torch.cuda.Stream(dev)   # a real stream: the stack is replayed as a CUDA graph
-    torch.cuda.set_stream(stream)
-    ctx.set_stream(stream.cuda_stream)
     orc_mod = entry.oracle_module()
     orc = orc_mod.Oracle()
-    distinct, x_all = [], np.empty((L, S, dims.n_embd), np.float32)
-    layer0 = None
+    peaks = measured_peaks()
+
+    # ---- weights: every rank holds the whole stack (14 GB of 180): decode slots are
+    # independent sequences, so ranks are replicas for this workload and no collective is
+    # on its data path.  The expert-parallel workloads below shard the experts instead.
+    ctx = pkg.Context(dims, n_layer=L, max_tokens=S, device=R.local_rank)
+    stream = torch.cuda.Stream(dev)   # a real stream: the stack is replayed as a CUDA graph
+    ctx.set_stream(stream.cuda_stream)
+    layers_keep = []
+    x_all = np.empty((L, S, dims.n_embd), np.float32)
     for l in range(L):
         layer = syn.make_layer(dims, SEED_W, l, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)
         ctx.upload_layer(l, layer)
-        x_all[l] = syn.random_x(S, dims.n_embd, SEED_X + l)
-        if l == 0:
-            layer0 = layer
-    x_dev = torch.from_numpy(x_all).to(dev)
-    y_dev = torch.empty_like(x_dev)
+        x_all[l] = syn.random_x(S, dims.n_embd, SEED_X + 1000 * rank + l)
+        if l < args.sub_layers:
+            layers_keep.append(layer)
+    with torch.cuda.stream(stream):
+        x_dev = torch.from_numpy(x_all).to(dev)
+        y_dev = torch.empty_like(x_dev)
     x_pin = torch.from_numpy(x_all).pin_memory()
     y_pin = torch.empty_like(x_pin).pin_memory()
 
     def step():
         ctx.moe_decode_stack(0, L, x_dev, S, y_dev)
 
-    def barrier():
-        torch.cuda.synchronize(dev)
-
     # correctness of what is being timed: layer 0 against the oracle
-    step(); barrier()
-    ref0 = orc.moe_layer(layer0, x_all[0], threads=orc.hardware_threads())
+    step(); R.barrier()
+    ref0 = orc.moe_layer(layers_keep[0], x_all[0], threads=orc.hardware_threads())
     err0 = syn.rel_err_rows(y_dev[0].cpu().numpy(), ref0["y"])
     assert err0 < 1e-5, f"layer 0 output error {err0}"
 
     # distinct experts per layer (for the algorithmic byte count), from the device's own routing
+    distinct = []
     for l in range(L):
         ctx.moe_decode(l, x_dev[l], S, y_dev[l])
         ids = ctx.last_sel(S)["ids"][:, :dims.n_used]
         distinct.append(len(np.unique(ids)))
     bytes_step = sum(syn.layer_touched_bytes(dims, syn.F16, syn.IQ3_XXS, syn.IQ4_XS, u) for u in distinct)
 
-    for _ in range(max(args.warmup, 3)):
+    W = max(args.warmup, 3)
+    for _ in range(W):
         step()
-    barrier()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(R.local_rank)
+    R.barrier()
     sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     n0 = ctx.launch_count()
-    barrier()
-    e0.record(stream)
-    for _ in range(args.steps):
-        step()
-    e1.record(stream)
-    barrier()
+    ms = timed(torch, R, stream, step, args.steps, 0)
     launches = ctx.launch_count() - n0
     clocks = sampler.stop()
-    ms = e0.elapsed_time(e1) / args.steps
-    value = S / (ms * 1e-3)
+    value = world * S / (ms * 1e-3)
+    bytes_all = R.sum_over_ranks(float(bytes_step))
 
-    # end to end: pinned host rows in, host rows out, every step
+    # end to end: pinned host rows in, host rows out, every step (wall clock, max over ranks)
     for _ in range(2):
         ctx.moe_decode_stack_host(0, L, x_pin.data_ptr(), S, y_pin.data_ptr())
+    R.barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         ctx.moe_decode_stack_host(0, L, x_pin.data_ptr(), S, y_pin.data_ptr())
-    e2e_s = (time.perf_counter() - t0) / args.steps
+    e2e_s = R.max_over_ranks((time.perf_counter() - t0) / args.steps)
     assert np.array_equal(y_pin[0].numpy(), y_dev[0].cpu().numpy())
 
-    # per-kernel timing of the dominant kernels over the same inputs (CUDA events, this stream)
-    kern = time_kernels(ctx, pkg, syn, torch, dev, stream, L, S, x_dev, distinct, dims)
-    peaks = measured_peaks()
-    dom = max(kern.values(), key=lambda k: k["ms_per_layer"])
-    roof = {"bound": "hbm", "kernel": dom["name"], "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
-            "frac": dom["gbs"] / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth",
-            "frac_of_nominal_8TBs": dom["gbs"] / 8000.0, "traffic": None,
-            "bytes_per_launch": dom["bytes_per_launch"], "ms_per_launch": dom["ms_per_layer"]}
-
-    threads = orc.hardware_threads() or 1
-    cpu_sec_layer = cpu_moe_sample(syn, orc_mod, dims, S, 2, threads, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)
-    cpu_val = S / (cpu_sec_layer * L)
     line = {
-        "metric": "moe_decode_tok_s", "value": value, "unit": "tok/s", "n_gpus": 1, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": decode_config(args, S),
-        "hbm": {"algorithmic_bytes_per_step": bytes_step, "gbs": bytes_step / (ms * 1e-3) / 1e9,
-                "frac_of_measured_copy": bytes_step / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                "frac_of_nominal_8TBs": bytes_step / (ms * 1e-3) / 8e12,
+        "metric": "moe_decode_tok_s", "value": value, "unit": "tok/s", "n_gpus": world, "steps": args.steps,
+        "warmup": W, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic", "config": decode_config(args, S * world),
+        "hbm": {"algorithmic_bytes_per_step": bytes_all, "gbs": bytes_all / (ms * 1e-3) / 1e9,
+                "gbs_per_gpu": bytes_all / world / (ms * 1e-3) / 1e9,
+                "frac_of_measured_copy": bytes_all / world / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                "frac_of_nominal_8TBs": bytes_all / world / (ms * 1e-3) / 8e12,
                 "distinct_experts_per_layer_mean": float(np.mean(distinct))},
         "us_per_layer": ms * 1e3 / L,
-        "roofline": roof, "kernels": kern,
-        "cpu_baseline": {"value": cpu_val, "unit": "tok/s", "cores": threads, "kind": "port",
-                         "sample": f"2 of {L} layers x {S} rows on the host cores, scaled by layers"},
-        "e2e": {"value": S / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(x_pin.numel() * 4),
-                "d2h_bytes_per_step": int(y_pin.numel() * 4), "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": int(launches), "clocks": clocks, "parity": {"layer0_rel_err": err0},
+        "e2e": {"value": world * S / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(x_pin.numel() * 4) * world,
+                "d2h_bytes_per_step": int(y_pin.numel() * 4) * world, "ms_per_step": e2e_s * 1e3},
+        "gpu_launches": int(launches) * world, "clocks": clocks, "parity": {"layer0_rel_err": err0},
     }
-    print(json.dumps(line), flush=True)
+    line["config"]["parallelism"] = "1 GPU" if world == 1 else f"{world} replicas of the stack, {S} slots each, no collective"
+
+    # per-kernel timing of the dominant kernels over the same inputs (CUDA events, this stream)
+    if rank == 0:
+        kern = time_kernels(ctx, pkg, syn, torch, dev, stream, L, S, x_dev, distinct, dims)
+        dom = max(kern.values(), key=lambda k: k["ms_per_layer"])
+        line["roofline"] = {
+            "bound": "hbm", "kernel": dom["name"], "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
+            "frac": dom["gbs"] / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth",
+            "frac_of_nominal_8TBs": dom["gbs"] / 8000.0, "traffic": NCU_TRAFFIC.get(dom["name"]),
+            "bytes_per_launch": dom["bytes_per_launch"], "ms_per_launch": dom["ms_per_layer"]}
+        line["kernels"] = kern
+        threads = orc.hardware_threads() or 1
+        if world == 1:
+            cpu_sec_layer = cpu_moe_sample(syn, orc_mod, dims, S, 2, threads, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)
+            line["cpu_baseline"] = {"value": S / (cpu_sec_layer * L), "unit": "tok/s", "cores": threads, "kind": "port",
+                                    "sample": f"2 of {L} layers x {S} rows on the host cores, scaled by layers"}
+    R.barrier()
     ctx.close()
+    del x_dev, y_dev
+    torch.cuda.empty_cache()
+
+    # ---- the other configurations, as sub-objects of the same line
+    if not args.no_sub:
+        line["prefill"] = run_prefill_or_ep(args, pkg, syn, torch, R, orc, layers_keep, peaks)
+        if world == 1:
+            line["gemv"] = run_gemv_sweep(args, pkg, syn, torch, R, orc, peaks)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    R.close()
+
+
+# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of
+# the decode stages on this workload; the captures are summarised under profiles/.
+NCU_TRAFFIC = {}
+
+PREFILL_CHUNKS = (128, 256, 512, 2048, 4096)
+TENSOR_FLOPS_PER_TOKEN = 56_623_104   # routed 8 x (gate, up, down) + shared expert, 2 x MACs
+
+
+def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
+    """1 GPU: batched prefill (tcgen05 expert GEMMs) at several chunk sizes, rotating over
+    `len(layers)` distinct layers so weights come from HBM.  N GPUs: the same token counts
+    split over the ranks, experts sharded, rows exchanged by all-to-all (strong scaling)."""
+    dims = syn.Dims()
+    dev, world, rank = R.dev, R.world, R.rank
+    PL = len(layers)
+    Tmax = max(PREFILL_CHUNKS)
+    per = dims.n_expert // world
+    ctx = pkg.Context(dims, n_layer=PL, max_tokens=Tmax, device=R.local_rank,
+                      expert_first=rank * per if world > 1 else 0, expert_count=per if world > 1 else 0)
+    for l, layer in enumerate(layers):
+        ctx.upload_layer(l, layer.expert_slice(rank * per, per) if world > 1 else layer)
+    stream = torch.cuda.current_stream(dev)
+    n_max = Tmax // world
+    x_np = np.stack([syn.random_x(n_max, dims.n_embd, SEED_X + 77 + 1000 * rank + l) for l in range(PL)])
+    x = torch.from_numpy(x_np).to(dev)
+    y = torch.empty_like(x)
+    ep = None
+    if world > 1:
+        from qwen_kernel_b200.expert_parallel import ExpertParallel
+        ep = ExpertParallel(ctx, dims.n_embd, dims.n_used, max_local_tokens=n_max, max_recv_rows=Tmax, device=dev)
+    out = {"layers_rotated": PL, "chunks": {}}
+    steps, warm = max(3, args.steps // 4), 3
+    for T in PREFILL_CHUNKS:
+        n = T // world
+        if n == 0:
+            continue
+
+        def step():
+            for l in range(PL):
+                if ep:
+                    ep.forward(l, x[l], n, y[l])
+                else:
+                    ctx.moe_prefill(l, x[l], n, y[l])
+
+        step(); R.barrier()
+        k = min(n, 8)
+        want = orc.moe_layer(layers[0], x_np[0, :k], threads=orc.hardware_threads())["y"]
+        err = syn.rel_err_rows(y[0, :k].cpu().numpy(), want)
+        assert err < 2e-2, f"prefill T={T}: error {err}"
+        n0 = ctx.launch_count()
+        ms = timed(torch, R, stream, step, steps, warm) / PL     # per layer
+        entry_ = {"us_per_layer": ms * 1e3, "tok_s": T / (ms * 1e-3), "rel_err_vs_oracle": R.max_over_ranks(err),
+                  "tensor_tflops": T * TENSOR_FLOPS_PER_TOKEN / (ms * 1e-3) / 1e12,
+                  "launches_per_layer": (ctx.launch_count() - n0) / ((steps + warm) * PL)}
+        entry_["frac_of_measured_bf16_burst"] = entry_["tensor_tflops"] / peaks["bf16_tflops"]
+        if ep:
+            send, recv = ep.last_counts
+            off = sum(send) - send[rank]
+            entry_["rows_sent_off_gpu_per_rank"] = off
+            entry_["nvlink_bytes_per_rank_per_layer"] = off * (dims.n_embd * 4 + 160) + off * dims.n_embd * 4
+        out["chunks"][str(T)] = entry_
+    if world == 1:
+        ctx.profile_enable(True)
+        T = 2048
+        acc = {}
+        for l in range(PL):
+            ctx.moe_prefill(l, x[l], T, y[l])
+            for kk, v in ctx.profile_read().items():
+                acc[kk] = acc.get(kk, 0.0) + v * 1e3 / PL
+        ctx.profile_enable(False)
+        out["stages_us_at_2048"] = acc
+        gu = acc.get("moe.gu", 0.0)
+        if gu > 0:
+            fl = T * dims.n_used * 2 * 2 * dims.n_ff * dims.n_embd
+            out["roofline"] = {"bound": "tensor", "kernel": "gateup_mma_kernel<IQ3_XXS> at 2048 tokens",
+                               "achieved": fl / (gu * 1e-6) / 1e12, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
+                               "frac": fl / (gu * 1e-6) / 1e12 / peaks["bf16_tflops"],
+                               "peak_source": peaks["source"] + " cuBLAS bf16 burst", "traffic": None}
+    out["workload"] = ("moe_prefill: one layer, chunks of T tokens, tcgen05 expert GEMMs" if world == 1 else
+                       f"expert-parallel moe layer: T tokens over {world} GPUs ({per} experts each), all-to-all over NVLink")
+    out["scaling"] = "strong"
+    R.barrier()
+    ctx.close()
+    return out
+
+
+GEMV_SHAPES = ((4096, 2048), (2048, 4096), (8192, 2048))
+
+
+def run_gemv_sweep(args, pkg, syn, torch, R: Ranks, orc, peaks):
+    """Dense dequant-GEMV, batch 1, per format and shape.  Each case rotates over enough
+    copies of the matrix (distinct addresses) that a pass reads more than twice the L2."""
+    dev = R.dev
+    ctx = pkg.Context(syn.Dims(), n_layer=1, max_tokens=1, device=R.local_rank)
+    stream = torch.cuda.current_stream(dev)
+    cases = [(t, m, k) for (m, k) in GEMV_SHAPES for t in (syn.Q8_0, syn.Q6_K, syn.IQ4_XS, syn.IQ3_XXS, syn.F16)]
+    cases.append((syn.Q6_K, 151936, 2048))
+    names = {syn.Q8_0: "q8_0", syn.Q6_K: "q6_k", syn.IQ4_XS: "iq4_xs", syn.IQ3_XXS: "iq3_xxs", syn.F16: "f16"}
+    out = {}
+    for t, M, K in cases:
+        W = syn.random_blocks(t, M, K, SEED_W + 5, "gemv")
+        nbytes = W.nbytes
+        stride = (nbytes + 255) // 256 * 256
+        copies = max(1, min(64, -(-300_000_000 // stride)))
+        buf = torch.zeros(copies * stride + 256, dtype=torch.uint8, device=dev)
+        w_dev = torch.from_numpy(W).to(dev)
+        for c in range(copies):
+            buf[c * stride:c * stride + nbytes] = w_dev
+        xv = syn.random_x(1, K, SEED_X + 9)
+        x = torch.from_numpy(xv).to(dev)
+        y = torch.empty(M, dtype=torch.float32, device=dev)
+        base = buf.data_ptr()
+
+        def step():
+            for c in range(copies):
+                ctx.gemv(t, base + c * stride, x, y, M, K, 1)
+
+        step(); R.barrier()
+        if M <= 8192:
+            want = orc.gemv(t, W, xv.reshape(-1), M, K, threads=orc.hardware_threads())
+            err = syn.rel_err_rows(y.cpu().numpy().reshape(1, -1), want.reshape(1, -1))
+            assert err < 1e-5, f"gemv {names[t]} {M}x{K}: error {err}"
+        ms = timed(torch, R, stream, step, 5, 3) / copies
+        gb = syn.gemv_bytes(t, M, K)
+        out[f"{names[t]}_{M}x{K}"] = {"us": ms * 1e3, "gbs": gb / (ms * 1e-3) / 1e9,
+                                      "frac_of_measured_copy": gb / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "copies": copies}
+        del buf, w_dev
+    ctx.close()
+    return out
 
 
 def time_kernels(ctx, pkg, syn, torch, dev, stream, L, S, x_dev, distinct, dims, reps=5):
@@ -296,19 +493,18 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "gemv"])
     ap.add_argument("--layers", type=int, default=40)
-    ap.add_argument("--slots", type=int, default=16)
-    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--slots", type=int, default=16, help="decode slots per GPU")
+    ap.add_argument("--sub-layers", type=int, default=8, help="distinct layers the prefill / expert-parallel cases rotate over")
+    ap.add_argument("--no-sub", action="store_true", help="only the headline decode workload")
     args = ap.parse_args()
+    args.sub_layers = max(1, min(args.sub_layers, args.layers))
     pkg = entry.package()
     syn = pkg.synth
     if args.impl == "reference":
         return run_reference_arm(args, syn)
     pkg.load_library()  # fails loudly if the CUDA library was not built
-    if args.workload == "decode":
-        return run_decode(args, pkg, syn)
-    raise SystemExit(f"workload {args.workload} not available yet")
+    return run_ours(args, pkg, syn)
 
 
 if __name__ == "__main__":
