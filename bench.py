@@ -423,7 +423,9 @@ def run_gemv_sweep(args, pkg, syn, torch, R: Ranks, orc, peaks):
     copies of the matrix (distinct addresses) that a pass reads more than twice the L2."""
     dev = R.dev
     ctx = pkg.Context(syn.Dims(), n_layer=1, max_tokens=1, device=R.local_rank)
-    stream = torch.cuda.current_stream(dev)
+    stream = torch.cuda.Stream(dev)   # a real stream: each pass over the copies is replayed as a CUDA graph
+    ctx.set_stream(stream.cuda_stream)
+    torch.cuda.set_stream(stream)
     cases = [(t, m, k) for (m, k) in GEMV_SHAPES for t in (syn.Q8_0, syn.Q6_K, syn.IQ4_XS, syn.IQ3_XXS, syn.F16)]
     cases.append((syn.Q6_K, 151936, 2048))
     names = {syn.Q8_0: "q8_0", syn.Q6_K: "q6_k", syn.IQ4_XS: "iq4_xs", syn.IQ3_XXS: "iq3_xxs", syn.F16: "f16"}
@@ -451,11 +453,16 @@ def run_gemv_sweep(args, pkg, syn, torch, R: Ranks, orc, peaks):
             want = orc.gemv(t, W, xv.reshape(-1), M, K, threads=orc.hardware_threads())
             err = syn.rel_err_rows(y.cpu().numpy().reshape(1, -1), want.reshape(1, -1))
             assert err < 1e-5, f"gemv {names[t]} {M}x{K}: error {err}"
-        ms = timed(torch, R, stream, step, 5, 3) / copies
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        ms = timed(torch, R, stream, graph.replay, 5, 3) / copies
+        del graph
         gb = syn.gemv_bytes(t, M, K)
         out[f"{names[t]}_{M}x{K}"] = {"us": ms * 1e3, "gbs": gb / (ms * 1e-3) / 1e9,
                                       "frac_of_measured_copy": gb / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "copies": copies}
         del buf, w_dev
+    torch.cuda.set_stream(torch.cuda.default_stream(dev))
     ctx.close()
     return out
 
