@@ -39,6 +39,7 @@ struct qkm_ctx {
     qkm_sel* sel = nullptr;
     float* h = nullptr;
     void* route_scratch = nullptr;
+    size_t route_scratch_bytes = 0;
     uint32_t* offsets = nullptr;
     uint32_t* pairs = nullptr;
     float* contrib = nullptr;  // allocated on first use
@@ -192,10 +193,11 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
     c->layers.resize(cfg->n_layer);
     const qkm_dims& d = cfg->dims;
     const size_t T = cfg->max_tokens;
+    c->route_scratch_bytes = qkm::route_scratch_bytes((uint32_t)T, d.n_expert);
     struct { void** p; size_t bytes; } allocs[] = {
         {(void**)&c->sel, T * sizeof(qkm_sel)},
         {(void**)&c->h, T * (d.n_used + 1) * d.n_ff * sizeof(float)},
-        {(void**)&c->route_scratch, route_scratch_bytes((uint32_t)T, d.n_expert)},
+        {(void**)&c->route_scratch, qkm::route_scratch_bytes((uint32_t)T, d.n_expert)},
         {(void**)&c->offsets, (d.n_expert + 1) * sizeof(uint32_t)},
         {(void**)&c->pairs, T * (d.n_used + 1) * sizeof(uint32_t)},
         {(void**)&c->y2, T * d.n_embd * sizeof(float)},
@@ -446,7 +448,7 @@ extern "C" QKM_API int qkm_moe_route_select(qkm_ctx* c, uint32_t router_type, co
     if (!c || !router || !gis || !x || !sel) return QKM_ERR_ARG;
     if (int rc = check_tokens(c, n)) return rc;
     if (router_type != QKM_TYPE_F32 && router_type != QKM_TYPE_F16) return fail(c, QKM_ERR_TYPE, "router type %u", router_type);
-    QKM_LAUNCH(c, launch_route_select(c->L(), c->cfg.dims, router_type, router, gis, x, sel, n, c->route_scratch));
+    QKM_LAUNCH(c, launch_route_select(c->L(), c->cfg.dims, router_type, router, gis, x, sel, n, c->route_scratch, c->route_scratch_bytes));
     return QKM_OK;
 }
 
@@ -531,7 +533,7 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     c->prof_begin();
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch,
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
                                       ld.stream_ok ? c->xplanes : nullptr, ld.stream_ok ? c->xscale : nullptr));
     c->prof_mark("moe.route");
     if (!ld.stream_ok) {  // generic kernels on the raw layout
@@ -584,7 +586,7 @@ static int prefill_generic(qkm_ctx* c, const qkm_layer_dev& ld, const float* x, 
     if (!c->contrib) {
         QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
     }
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch));
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes));
     QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
     QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
     QKM_LAUNCH(c, launch_gateup_pairs(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, x, c->offsets, c->pairs, c->h, n, c->efirst, c->ecount));
@@ -629,7 +631,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     const uint32_t tiles_now = d.n_expert < n * d.n_used ? d.n_expert + (n * d.n_used + NT - 1) / NT : n * d.n_used;
     const uint32_t sh_now = (n + NT - 1) / NT;
     c->prof_begin();
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch));
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes));
     c->prof_mark("moe.route");
     QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
     QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n, c->mma_items[0], c->mma_items[1],
@@ -814,7 +816,7 @@ extern "C" QKM_API int qkm_ep_dispatch(qkm_ctx* c, uint32_t layer, const float* 
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     const bool planes = ld.tiles_ok && n <= 64;   // the streamed shared-expert kernels read digit planes
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch,
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
                                       planes ? c->xplanes : nullptr, planes ? c->xscale : nullptr));
     QKM_LAUNCH(c, launch_ep_plan(c->L(), d, c->sel, n, n_ranks, c->ep_counts, c->ep_send_tok, c->ep_send_pos));
     const uint32_t fan = n_ranks < d.n_used ? n_ranks : d.n_used;

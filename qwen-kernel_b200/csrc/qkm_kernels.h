@@ -87,7 +87,8 @@ cudaError_t launch_gemv_stream(const Launch& L, uint32_t type, const void* W, co
                                uint32_t M, uint32_t K, uint32_t n, uint32_t n_sms, uint32_t* status);
 
 // ---- qkm_route.cu
-// Scratch the refined router needs: n_tokens * n_expert f32 logits + n_expert f32 row norms.
+// Scratch the refined router needs: n_tokens * n_expert f32 logits + n_expert f32 row norms,
+// or n_tokens * n_expert f64 logits for the small batches that are ranked in f64 directly.
 size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert);
 cudaError_t launch_logits(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
                           const float* x, float* logits, float* row_norm2, uint32_t n_tokens);
@@ -95,7 +96,7 @@ cudaError_t launch_select(const Launch& L, const qkm_dims& d, const float* logit
                           const float* x, qkm_sel* sel, uint32_t n_tokens);
 cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t router_type,
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
-                                uint32_t n_tokens, void* scratch, int8_t* xplanes = nullptr,
+                                uint32_t n_tokens, void* scratch, size_t scratch_bytes, int8_t* xplanes = nullptr,
                                 float* xscale = nullptr);
 cudaError_t launch_group_pairs(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                                uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,

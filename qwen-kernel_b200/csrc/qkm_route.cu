@@ -34,18 +34,21 @@ static constexpr float kFloor = -3.4e38f;
 static constexpr int kTokPerBlock = 4;
 static constexpr int kMaxUnits = 2;  // K <= 2048 in one pass; longer rows loop
 
-template <int TYPE>
+// With ACC = double the logits are those of an f64-accumulating router outright (the f64
+// pipe does the 2 * K * n_expert flops of a decode batch in well under a microsecond), and
+// the selection needs no error bound or re-evaluation.
+template <int TYPE, typename ACC>
 __global__ void __launch_bounds__(256)
-logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, float* __restrict__ logits,
+logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, ACC* __restrict__ logits,
               float* __restrict__ row_norm2, uint32_t n_expert, uint32_t K, uint32_t n_tokens) {
-    __shared__ float s_part[8][kTokPerBlock + 1];
+    __shared__ ACC s_part[8][kTokPerBlock + 1];
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t e = blockIdx.x * 2u + (warp >> 2), quarter = warp & 3u;
     const uint32_t t0 = blockIdx.y * kTokPerBlock;
     const uint32_t units_q = K / 32;  // units per quarter
-    float acc[kTokPerBlock], nrm = 0.f;
+    ACC acc[kTokPerBlock], nrm = 0;
 #pragma unroll
-    for (int j = 0; j < kTokPerBlock; ++j) acc[j] = 0.f;
+    for (int j = 0; j < kTokPerBlock; ++j) acc[j] = 0;
     if (e < n_expert) {
         const uint8_t* row = router + (size_t)e * row_bytes(TYPE, K);
         for (uint32_t u0 = lane; u0 < units_q; u0 += 32 * kMaxUnits) {
@@ -70,12 +73,14 @@ logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, f
             for (int i = 0; i < kMaxUnits; ++i) {
                 if (u0 + 32 * i < units_q) {
 #pragma unroll
-                    for (int q = 0; q < 8; ++q) nrm += w[i][q] * w[i][q];
+                    for (int q = 0; q < 8; ++q) nrm += (ACC)(w[i][q] * w[i][q]);
 #pragma unroll
                     for (int j = 0; j < kTokPerBlock; ++j) {
-                        float s = acc[j];
-                        s += w[i][0] * xa[i][j].x; s += w[i][1] * xa[i][j].y; s += w[i][2] * xa[i][j].z; s += w[i][3] * xa[i][j].w;
-                        s += w[i][4] * xb[i][j].x; s += w[i][5] * xb[i][j].y; s += w[i][6] * xb[i][j].z; s += w[i][7] * xb[i][j].w;
+                        ACC s = acc[j];
+                        s += (ACC)w[i][0] * (ACC)xa[i][j].x; s += (ACC)w[i][1] * (ACC)xa[i][j].y;
+                        s += (ACC)w[i][2] * (ACC)xa[i][j].z; s += (ACC)w[i][3] * (ACC)xa[i][j].w;
+                        s += (ACC)w[i][4] * (ACC)xb[i][j].x; s += (ACC)w[i][5] * (ACC)xb[i][j].y;
+                        s += (ACC)w[i][6] * (ACC)xb[i][j].z; s += (ACC)w[i][7] * (ACC)xb[i][j].w;
                         acc[j] = s;
                     }
                 }
@@ -84,18 +89,18 @@ logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, f
     }
 #pragma unroll
     for (int j = 0; j < kTokPerBlock; ++j) {
-        const float v = warp_sum(acc[j]);
+        const ACC v = warp_sum(acc[j]);
         if (lane == 0) s_part[warp][j] = v;
     }
     nrm = warp_sum(nrm);
     if (lane == 0) s_part[warp][kTokPerBlock] = nrm;
     __syncthreads();
     if (quarter == 0 && e < n_expert && lane <= kTokPerBlock) {
-        const float v = ((s_part[warp][lane] + s_part[warp + 1][lane]) + s_part[warp + 2][lane]) + s_part[warp + 3][lane];
+        const ACC v = ((s_part[warp][lane] + s_part[warp + 1][lane]) + s_part[warp + 2][lane]) + s_part[warp + 3][lane];
         if (lane < kTokPerBlock) {
             if (t0 + lane < n_tokens) logits[(size_t)(t0 + lane) * n_expert + e] = v;
         } else if (row_norm2 != nullptr && blockIdx.y == 0) {
-            row_norm2[e] = v;
+            row_norm2[e] = (float)v;
         }
     }
 }
@@ -106,11 +111,23 @@ cudaError_t launch_logits(const Launch& L, const qkm_dims& d, uint32_t router_ty
     const dim3 grid((d.n_expert + 1) / 2, (n_tokens + kTokPerBlock - 1) / kTokPerBlock);
     const uint8_t* r = (const uint8_t*)router;
     if (router_type == QKM_TYPE_F32)
-        logits_kernel<QKM_TYPE_F32><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd, n_tokens);
+        logits_kernel<QKM_TYPE_F32, float><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd, n_tokens);
     else if (router_type == QKM_TYPE_F16)
-        logits_kernel<QKM_TYPE_F16><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd, n_tokens);
+        logits_kernel<QKM_TYPE_F16, float><<<grid, 256, 0, L.stream>>>(r, x, logits, row_norm2, d.n_expert, d.n_embd, n_tokens);
     else
         return cudaErrorInvalidValue;
+    L.count();
+    return cudaGetLastError();
+}
+
+static cudaError_t launch_logits64(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
+                                   const float* x, double* logits, uint32_t n_tokens) {
+    const dim3 grid((d.n_expert + 1) / 2, (n_tokens + kTokPerBlock - 1) / kTokPerBlock);
+    const uint8_t* r = (const uint8_t*)router;
+    if (router_type == QKM_TYPE_F32)
+        logits_kernel<QKM_TYPE_F32, double><<<grid, 256, 0, L.stream>>>(r, x, logits, nullptr, d.n_expert, d.n_embd, n_tokens);
+    else
+        logits_kernel<QKM_TYPE_F16, double><<<grid, 256, 0, L.stream>>>(r, x, logits, nullptr, d.n_expert, d.n_embd, n_tokens);
     L.count();
     return cudaGetLastError();
 }
@@ -311,9 +328,11 @@ cudaError_t launch_select(const Launch& L, const qkm_dims& d, const float* logit
 // block-wide argmax and no serial insertion.
 static constexpr int kMaxCand = 128;
 
-template <int TYPE>
+// EXACT: `logits_any` holds f64 logits of an f64-accumulating kernel; they are ranked as they
+// are (no bound, no candidates).  Otherwise it holds f32 logits and the boundary is re-evaluated.
+template <int TYPE, bool EXACT>
 __global__ void __launch_bounds__(256)
-refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict__ logits,
+refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict__ logits_any,
                      const float* __restrict__ row_norm2, const float* __restrict__ gis,
                      const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d,
                      int8_t* __restrict__ xplanes, float* __restrict__ xscale, float eps_terms) {
@@ -329,15 +348,25 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     __shared__ double s_best_val[16];
     const uint32_t t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const float* xt = x + (size_t)t * d.n_embd;
-    const float* lt = logits + (size_t)t * d.n_expert;
     const uint32_t id0 = tid, id1 = tid + 256u;
-    const float l0 = (id0 < d.n_expert ? sane(lt[id0]) : kFloor) + 0.0f;  // + 0: -0 and +0 tie
-    const float l1 = (id1 < d.n_expert ? sane(lt[id1]) : kFloor) + 0.0f;
-    s_log[id0] = l0;
-    s_log[id1] = l1;
     const double ninf = -__longlong_as_double(0x7FF0000000000000ll);
-    s_val[id0] = ninf;
-    s_val[id1] = ninf;
+    float l0 = kFloor, l1 = kFloor;
+    if (EXACT) {
+        const double* lt = reinterpret_cast<const double*>(logits_any) + (size_t)t * d.n_expert;
+        double v0 = ninf, v1 = ninf;
+        if (id0 < d.n_expert) { v0 = lt[id0]; if (isnan(v0) || isinf(v0)) v0 = (double)kFloor; }
+        if (id1 < d.n_expert) { v1 = lt[id1]; if (isnan(v1) || isinf(v1)) v1 = (double)kFloor; }
+        s_val[id0] = v0;
+        s_val[id1] = v1;
+    } else {
+        const float* lt = reinterpret_cast<const float*>(logits_any) + (size_t)t * d.n_expert;
+        l0 = (id0 < d.n_expert ? sane(lt[id0]) : kFloor) + 0.0f;  // + 0: -0 and +0 tie
+        l1 = (id1 < d.n_expert ? sane(lt[id1]) : kFloor) + 0.0f;
+        s_log[id0] = l0;
+        s_log[id1] = l1;
+        s_val[id0] = ninf;
+        s_val[id1] = ninf;
+    }
 
     // One pass over the row: stage it in shared memory and gather everything that needs
     // it - |x|^2 and max|x| (error bound, digit exponent), the shared-gate dot in f64 -
@@ -353,8 +382,10 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
         bad |= !(fabsf(v) <= 3.0e38f);
         dsg += (double)gv * (double)v;
     }
-    if (id0 < d.n_expert) rn = row_norm2[id0];
-    if (id1 < d.n_expert) rn = fmaxf(rn, row_norm2[id1]);
+    if (!EXACT) {
+        if (id0 < d.n_expert) rn = row_norm2[id0];
+        if (id1 < d.n_expert) rn = fmaxf(rn, row_norm2[id1]);
+    }
     xs = warp_sum(xs);
     dsg = warp_sum(dsg);
 #pragma unroll
@@ -386,6 +417,7 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
         if (tid == 0) xscale[t] = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
     }
 
+    if (!EXACT) {
     // k-th largest f32 logit: the expert that exactly n_used-1 others precede
     {
         uint32_t c0 = 0, c1 = 0;
@@ -434,6 +466,7 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
         const double acc = warp_sum((a0 + a1) + (a2 + a3));
         if (lane == 0) s_val[e] = (isnan(acc) || isinf(acc)) ? (double)kFloor : acc;
     }
+    }  // !EXACT
     __syncthreads();
     // final order among the candidates: (f64 value descending, id ascending)
     {
@@ -470,15 +503,32 @@ refine_select_kernel(const uint8_t* __restrict__ router, const float* __restrict
     }
 }
 
+static constexpr uint32_t kExactMaxTokens = 64;   // decode-sized batches rank f64 logits directly
+
 size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert) {
-    return ((size_t)n_tokens * n_expert + n_expert) * sizeof(float);
+    const size_t f32_path = ((size_t)n_tokens * n_expert + n_expert) * sizeof(float);
+    const size_t f64_path = (size_t)(n_tokens < kExactMaxTokens ? n_tokens : kExactMaxTokens) * n_expert * sizeof(double);
+    return f32_path > f64_path ? f32_path : f64_path;
 }
 
 cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t router_type,
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
-                                uint32_t n_tokens, void* scratch, int8_t* xplanes, float* xscale) {
+                                uint32_t n_tokens, void* scratch, size_t scratch_bytes, int8_t* xplanes, float* xscale) {
     if (n_tokens == 0) return cudaSuccess;
     if (router_type != QKM_TYPE_F32 && router_type != QKM_TYPE_F16) return cudaErrorInvalidValue;
+    if (n_tokens <= kExactMaxTokens && (size_t)n_tokens * d.n_expert * sizeof(double) <= scratch_bytes) {
+        // small batch: f64 logits, ranked as they are
+        double* l64 = (double*)scratch;
+        cudaError_t e = launch_logits64(L, d, router_type, router, x, l64, n_tokens);
+        if (e != cudaSuccess) return e;
+        if (router_type == QKM_TYPE_F32)
+            refine_select_kernel<QKM_TYPE_F32, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f);
+        else
+            refine_select_kernel<QKM_TYPE_F16, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f);
+        L.count();
+        return cudaGetLastError();
+    }
+    if (((size_t)n_tokens * d.n_expert + d.n_expert) * sizeof(float) > scratch_bytes) return cudaErrorInvalidValue;
     float* logits = (float*)scratch;
     float* norm2 = logits + (size_t)n_tokens * d.n_expert;
     const uint8_t* r = (const uint8_t*)router;
@@ -502,9 +552,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         eps_terms = (float)(d.n_embd / 32 + 8);
     }
     if (router_type == QKM_TYPE_F32)
-        refine_select_kernel<QKM_TYPE_F32><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
+        refine_select_kernel<QKM_TYPE_F32, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
     else
-        refine_select_kernel<QKM_TYPE_F16><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
+        refine_select_kernel<QKM_TYPE_F16, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
     L.count();
     return cudaGetLastError();
 }

@@ -99,7 +99,7 @@ extern "C" QKM_API int qkm_route_select_static(int device, void* stream, const q
         rc = QKM_ERR_CUDA;
     } else {
         const qkm::Launch L{(cudaStream_t)stream, nullptr};
-        e = qkm::launch_route_select(L, *dims, router_type, router, gate_inp_shexp, x, sel, n_tokens, scratch);
+        e = qkm::launch_route_select(L, *dims, router_type, router, gate_inp_shexp, x, sel, n_tokens, scratch, kScratchFloats * sizeof(float));
         if (e != cudaSuccess) {
             put_error(err, err_len, "launch failed", cudaGetErrorString(e));
             rc = QKM_ERR_CUDA;
