@@ -45,8 +45,7 @@ constexpr int kBlock = kThreads + 32;
 constexpr int kStages = 2;
 constexpr int kNT = 128;                       // pairs per block (N tile)
 constexpr int kTileBytes = 128 * 128;          // 128 rows x 64 bf16
-constexpr int kGridReplicas = 4;
-constexpr int kSignReplicas = 2;
+constexpr int kGridReplicas = 8;
 }  // namespace pf
 
 // ---- x -> f16 rows, each scaled by a power of two so that max|x| lands in [2^13, 2^14) -----------
@@ -173,63 +172,96 @@ __device__ __forceinline__ Iq3Raw load_iq3(const uint8_t* __restrict__ tile, uin
 // Dequantise to f16: a table gives the four magnitudes of a grid entry as two f16 pairs,
 // another the four sign masks of a 7-bit sign code; one packed multiply by the sub-block
 // scale (f16) and one XOR per pair.  Two roundings of 2^-12 each.
-//   s_gridh: [256][kGridReplicas] uint2      s_sign: [128][kSignReplicas] uint4
-__device__ __forceinline__ void produce_iq3(const Iq3Raw& raw, const uint2* __restrict__ s_gridh,
-                                            const uint4* __restrict__ s_sign, uint32_t lane, uint8_t* a_tile,
+//   s_grid: [256][kGridReplicas] u32 (four magnitudes)     s_sign: [128] sign bytes (code | parity << 7)
+__device__ __forceinline__ void produce_iq3(const Iq3Raw& raw, const uint32_t* __restrict__ s_grid,
+                                            const uint8_t* __restrict__ s_sign, uint32_t lane, uint8_t* a_tile,
                                             uint32_t row) {
     const float d = f16_bits_to_f32(raw.dbits);
 #pragma unroll
     for (int j = 0; j < 2; ++j) {          // sub-block 2q + j
         const uint32_t aux = j ? raw.aux2.y : raw.aux2.x;
         const __half2 db2 = __float2half2_rn(d * (0.5f + (float)(aux >> 28)) * 0.5f);
+        const __half2 nb2 = __hmul2(db2, __float2half2_rn(-1024.f));
 #pragma unroll
         for (int t = 0; t < 4; ++t) {      // 8-element group t -> chunk 4j + t
             const uint32_t pr = (raw.idxw[t] >> (16 * j)) & 0xFFFFu;
-            const uint2 g0 = s_gridh[(pr & 0xFFu) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
-            const uint2 g1 = s_gridh[(pr >> 8) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
-            const uint4 sm = s_sign[((aux >> (7 * t)) & 127u) * pf::kSignReplicas + (lane & (pf::kSignReplicas - 1))];
+            // four u8 magnitudes per grid word; byte b becomes the f16 1024 + b by placing it under
+            // the exponent byte 0x64, and one fused multiply-add scales it and removes the 1024
+            const uint32_t g0 = s_grid[(pr & 0xFFu) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
+            const uint32_t g1 = s_grid[(pr >> 8) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
+            // sign byte of the 7-bit code (128-byte table: one word per bank, never a conflict),
+            // then bit i -> bit 7 of byte i by one multiply (the partial products do not overlap)
+            const uint32_t s8 = s_sign[(aux >> (7 * t)) & 127u];
+            const uint32_t m_lo = ((s8 & 0xFu) * 0x10204080u) & 0x80808080u;
+            const uint32_t m_hi = ((s8 >> 4) * 0x10204080u) & 0x80808080u;
             uint4 o;
             __half2 v;
-            v = __hmul2(*reinterpret_cast<const __half2*>(&g0.x), db2); o.x = *reinterpret_cast<uint32_t*>(&v) ^ sm.x;
-            v = __hmul2(*reinterpret_cast<const __half2*>(&g0.y), db2); o.y = *reinterpret_cast<uint32_t*>(&v) ^ sm.y;
-            v = __hmul2(*reinterpret_cast<const __half2*>(&g1.x), db2); o.z = *reinterpret_cast<uint32_t*>(&v) ^ sm.z;
-            v = __hmul2(*reinterpret_cast<const __half2*>(&g1.y), db2); o.w = *reinterpret_cast<uint32_t*>(&v) ^ sm.w;
+            uint32_t h;
+            h = __byte_perm(g0, 0x64646464u, 0x5140); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
+            o.x = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_lo, 0u, 0x1404);
+            h = __byte_perm(g0, 0x64646464u, 0x7362); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
+            o.y = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_lo, 0u, 0x3424);
+            h = __byte_perm(g1, 0x64646464u, 0x5140); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
+            o.z = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_hi, 0u, 0x1404);
+            h = __byte_perm(g1, 0x64646464u, 0x7362); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
+            o.w = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_hi, 0u, 0x3424);
             *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + t)) = o;
         }
     }
 }
 
-template <int J0, int J1>
-__device__ __forceinline__ void produce_iq4(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
-                                            const float* __restrict__ s_kv, uint32_t lane, uint8_t* a_tile,
-                                            uint32_t row) {
-    const uint32_t g = r16 & 7u, hf = r16 >> 3;
-    const uint2 hd = *reinterpret_cast<const uint2*>(tile + 16 * g + 8 * hf);  // d | scales_h << 16, scales_l
+// IQ4_XS: a quant byte holds two weights 16 columns apart (low and high nibble).  The table
+// maps a byte to both values as a bf16 pair; it is replicated per lane ([256][32] words, lane
+// = bank) so lookups never conflict.  s_pair_lane already points at this lane's column.
+// The sub-block scale is applied in two bf16 pieces (hi + lo), so the stored weight carries
+// one bf16 rounding of the exact product, as before.
+// the bytes one thread needs for (row, k-step, 32-column half j): fetched one k-step ahead
+struct Iq4Raw { uint2 hd; uint32_t w[4]; };
+__device__ __forceinline__ Iq4Raw load_iq4(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q, uint32_t j) {
+    const uint32_t g = r16 & 7u, hf = r16 >> 3, sb = 2 * q + j;
+    Iq4Raw r;
+    r.hd = *reinterpret_cast<const uint2*>(tile + 16 * g + 8 * hf);  // d | scales_h << 16, scales_l
+    // the sub-block's 16 quant bytes: word t sits in lane slot (g, t) of chunk 2*hf + sb/4
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+        r.w[t] = *reinterpret_cast<const uint32_t*>(tile + 128 + ((2 * hf + (sb >> 2)) * 32 + 4 * g + t) * 16 + 4 * (sb & 3u));
+    return r;
+}
+
+__device__ __forceinline__ void produce_iq4(const Iq4Raw& raw, uint32_t q, uint32_t j,
+                                            const uint8_t* __restrict__ s_pair_lane, uint8_t* a_tile, uint32_t row) {
+    const uint2 hd = raw.hd;
     const float d = f16_bits_to_f32(hd.x & 0xFFFFu);
     const uint32_t sh = hd.x >> 16;
-#pragma unroll
-    for (int j = J0; j < J1; ++j) {
+    {
         const uint32_t sb = 2 * q + j;
         const int ls = (int)(((hd.y >> (4 * sb)) & 0xFu) | (((sh >> (2 * sb)) & 3u) << 4)) - 32;
         const float dl = d * (float)ls;
-        // the sub-block's 16 quant bytes: word t sits in lane slot (g, t) of chunk 2*hf + sb/4
-        uint32_t w[4];
+        const __nv_bfloat16 dhi = __float2bfloat16_rn(dl);
+        const __nv_bfloat162 s_hi = __bfloat162bfloat162(dhi);
+        const __nv_bfloat162 s_lo = __bfloat162bfloat162(__float2bfloat16_rn(dl - __bfloat162float(dhi)));
+        const uint32_t* w = raw.w;
+        uint32_t lo[8], hi[8];   // bf16 pairs: columns 2i, 2i+1 of the low-nibble half / of the high-nibble half
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
-            w[t] = *reinterpret_cast<const uint32_t*>(tile + 128 + ((2 * hf + (sb >> 2)) * 32 + 4 * g + t) * 16 + 4 * (sb & 3u));
+        for (int t = 0; t < 4; ++t) {
+            const uint32_t l0 = *reinterpret_cast<const uint32_t*>(s_pair_lane + ((w[t] << 7) & 0x7F80u));
+            const uint32_t l1 = *reinterpret_cast<const uint32_t*>(s_pair_lane + ((w[t] >> 1) & 0x7F80u));
+            const uint32_t l2 = *reinterpret_cast<const uint32_t*>(s_pair_lane + ((w[t] >> 9) & 0x7F80u));
+            const uint32_t l3 = *reinterpret_cast<const uint32_t*>(s_pair_lane + ((w[t] >> 17) & 0x7F80u));
+            lo[2 * t] = __byte_perm(l0, l1, 0x5410); lo[2 * t + 1] = __byte_perm(l2, l3, 0x5410);
+            hi[2 * t] = __byte_perm(l0, l1, 0x7632); hi[2 * t + 1] = __byte_perm(l2, l3, 0x7632);
+        }
+        auto scale = [&](uint32_t x) -> uint32_t {
+            const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&x);
+            const __nv_bfloat162 r = __hfma2(v, s_hi, __hmul2(v, s_lo));
+            return *reinterpret_cast<const uint32_t*>(&r);
+        };
 #pragma unroll
         for (int p = 0; p < 4; ++p) {      // elements 8p .. 8p+7 of the sub-block -> chunk 4j + p
-            const uint32_t lo = w[2 * (p & 1)], hi = w[2 * (p & 1) + 1];
-            const uint32_t sft = (p >> 1) * 4;   // low nibbles for elements < 16, high nibbles above
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                v[i] = dl * s_kv[((lo >> (8 * i + sft)) & 15u) * 32 + lane];
-                v[4 + i] = dl * s_kv[((hi >> (8 * i + sft)) & 15u) * 32 + lane];
-            }
+            const uint32_t* src = (p >> 1) ? hi : lo;
+            const int o4 = 4 * (p & 1);
             uint4 o;
-            o.x = pack_bf16(v[0], v[1]); o.y = pack_bf16(v[2], v[3]);
-            o.z = pack_bf16(v[4], v[5]); o.w = pack_bf16(v[6], v[7]);
+            o.x = scale(src[o4]); o.y = scale(src[o4 + 1]); o.z = scale(src[o4 + 2]); o.w = scale(src[o4 + 3]);
             *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + p)) = o;
         }
     }
@@ -302,25 +334,16 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    uint2* s_gridh = reinterpret_cast<uint2*>(smem + pf::kStages * 3 * pf::kTileBytes);
-    uint4* s_sign = reinterpret_cast<uint4*>(s_gridh + 256 * pf::kGridReplicas);
+    uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + pf::kStages * 3 * pf::kTileBytes);
+    uint8_t* s_sign = reinterpret_cast<uint8_t*>(s_grid + 256 * pf::kGridReplicas);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const MmaItem it = items[blockIdx.x];
     const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
     const uint32_t KB = d.n_embd / 256, RT16 = d.n_ff / 16, KS = d.n_embd / 64;
 
     if (FMT == QKM_TYPE_IQ3_XXS) {
-        for (uint32_t i = tid; i < 256 * pf::kGridReplicas; i += pf::kThreads) {
-            const uint32_t gw = c_iq3_grid[i / pf::kGridReplicas];
-            __half2 lo = __floats2half2_rn((float)(gw & 255u), (float)((gw >> 8) & 255u));
-            __half2 hi = __floats2half2_rn((float)((gw >> 16) & 255u), (float)(gw >> 24));
-            s_gridh[i] = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-        }
-        for (uint32_t i = tid; i < 128 * pf::kSignReplicas; i += pf::kThreads) {
-            const uint32_t sg = signs8(i / pf::kSignReplicas);
-            s_sign[i] = make_uint4(((sg & 1u) << 15) | ((sg & 2u) << 30), ((sg & 4u) << 13) | ((sg & 8u) << 28),
-                                   ((sg & 16u) << 11) | ((sg & 32u) << 26), ((sg & 64u) << 9) | ((sg & 128u) << 24));
-        }
+        for (uint32_t i = tid; i < 256 * pf::kGridReplicas; i += pf::kThreads) s_grid[i] = c_iq3_grid[i / pf::kGridReplicas];
+        if (tid < 128) s_sign[tid] = (uint8_t)signs8(tid);
     }
     if (tid == 0) {
         for (int s = 0; s < pf::kStages; ++s) {
@@ -344,8 +367,17 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     const uint8_t* wt = (mat ? up_tiles : gate_tiles) + (size_t)it.expert * KB * RT16 * kTile;
 
     // activation rows of this block's pairs (one dependent load less per k-step)
+    // per column (pair) of this block: its x row, the scale that undoes the row's power-of-two
+    // scaling, and where its h row goes in the [token][slot] layout
     __shared__ const __half* s_row[pf::kNT];
-    for (uint32_t i = tid; i < n; i += pf::kBlock) s_row[i] = xb + (size_t)(pairs[it.pair_off + i] >> 4) * d.n_embd;
+    __shared__ float s_inv[pf::kNT];
+    __shared__ uint32_t s_hrow[pf::kNT];
+    for (uint32_t i = tid; i < n; i += pf::kBlock) {
+        const uint32_t pr = pairs[it.pair_off + i], tok = pr >> 4;
+        s_row[i] = xb + (size_t)tok * d.n_embd;
+        s_inv[i] = x_inv_scale[tok];
+        s_hrow[i] = tok * (d.n_used + 1) + (pr & 15u);
+    }
     __syncthreads();
     if (tid >= pf::kThreads) {
         // ---- MMA issuer warp
@@ -390,7 +422,7 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
             if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
         uint8_t* st = smem + stage * 3 * pf::kTileBytes;
         const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-        if (FMT == QKM_TYPE_IQ3_XXS) { produce_iq3(raw, s_gridh, s_sign, lane, st + mat * pf::kTileBytes, r); raw = next; }
+        if (FMT == QKM_TYPE_IQ3_XXS) { produce_iq3(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r); raw = next; }
         else produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
         store_b(st + 2 * pf::kTileBytes, breg, n_mma);
         breg = bnext;
@@ -413,11 +445,10 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
             for (int i = 0; i < 16; ++i) {
                 const uint32_t col = cb * 16 + i;
                 if (col < n) {
-                    const uint32_t pos = it.pair_off + col, pr = pairs[pos];
-                    const float us = x_inv_scale[pr >> 4];   // undo the per-token power-of-two scale of x
+                    const float us = s_inv[col];   // undo the per-token power-of-two scale of x
                     const float hv = swiglu(__uint_as_float(vg[i]) * us, __uint_as_float(vu[i]) * us);
-                    hb[(size_t)pos * d.n_ff + r_ff] = __float2bfloat16_rn(hv);
-                    h[((size_t)(pr >> 4) * (d.n_used + 1) + (pr & 15u)) * d.n_ff + r_ff] = hv;
+                    hb[(size_t)(it.pair_off + col) * d.n_ff + r_ff] = __float2bfloat16_rn(hv);
+                    h[(size_t)s_hrow[col] * d.n_ff + r_ff] = hv;
                 }
             }
         }
@@ -436,21 +467,26 @@ __global__ void __launch_bounds__(pf::kBlock, 2)
 down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restrict__ hb,
                 const qkm_sel* __restrict__ sel, const uint32_t* __restrict__ pairs,
                 const MmaItem* __restrict__ items, const uint32_t* __restrict__ n_items_ptr,
-                float* __restrict__ contrib, qkm_dims d, uint32_t* __restrict__ status) {
-    if (blockIdx.x >= *n_items_ptr) return;
+                float* __restrict__ contrib, qkm_dims d, uint32_t row_tiles, uint32_t* __restrict__ status) {
+    if (blockIdx.x * row_tiles >= *n_items_ptr) return;
     constexpr int kTile = FMT == QKM_TYPE_IQ4_XS ? kTileIq4 : kTileQ8;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    float* s_kv = reinterpret_cast<float*>(smem + pf::kStages * 2 * pf::kTileBytes);
+    uint32_t* s_pair = reinterpret_cast<uint32_t*>(smem + pf::kStages * 2 * pf::kTileBytes);   // [256][32], IQ4_XS only
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
-    const MmaItem it = items[blockIdx.x];
+    const MmaItem it = items[blockIdx.x * row_tiles];   // items of one (expert, pair tile) are consecutive row tiles
     const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
     const uint32_t KB = d.n_ff / 256, RT16 = d.n_embd / 16, KS = d.n_ff / 64;
 
     if (FMT == QKM_TYPE_IQ4_XS)
-        for (uint32_t i = tid; i < 16 * 32; i += pf::kThreads) s_kv[i] = (float)c_iq4_values[i >> 5];
+        for (uint32_t i = tid; i < 256 * 32; i += pf::kThreads) {
+            const uint32_t b = i >> 5;
+            const __nv_bfloat162 v = __floats2bfloat162_rn((float)c_iq4_values[b & 15u], (float)c_iq4_values[b >> 4]);
+            s_pair[i] = *reinterpret_cast<const uint32_t*>(&v);
+        }
+    const uint8_t* s_pair_lane = reinterpret_cast<const uint8_t*>(s_pair + lane);
     if (tid == 0) {
         for (int s = 0; s < pf::kStages; ++s) {
             mbar_init(smem_addr(&s_bar[s]), 1);                            // empty: one commit
@@ -469,18 +505,25 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
 
     // producer role: thread -> row (tid & 127), 32-column half (tid >> 7) of the A tile; all threads help with B
     const uint32_t r = tid & 127u;
-    const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
     const uint8_t* wt = tiles + (size_t)it.expert * KB * RT16 * kTile;
 
+    // per column (pair) of this block: its h row and its routing weight
     __shared__ const __nv_bfloat16* s_row[pf::kNT];
-    for (uint32_t i = tid; i < n; i += pf::kBlock) s_row[i] = hb + (size_t)(it.pair_off + i) * d.n_ff;
+    __shared__ float s_wgt[pf::kNT];
+    for (uint32_t i = tid; i < n; i += pf::kBlock) {
+        s_row[i] = hb + (size_t)(it.pair_off + i) * d.n_ff;
+        const uint32_t pr = pairs[it.pair_off + i], tok = pr >> 4, slot = pr & 15u;
+        s_wgt[i] = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
+    }
     __syncthreads();
+    // The block walks `row_tiles` consecutive 128-row tiles of the same expert and pairs: tables,
+    // barriers and tensor memory are set up once; gs counts k-steps across the tiles.
     if (tid >= pf::kThreads) {
         // ---- MMA issuer warp
         if (lane == 0) {
-            for (uint32_t ks = 0; ks < KS; ++ks) {
-                const uint32_t stage = ks % pf::kStages;
-                if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages + stage]), (ks / pf::kStages) & 1u)) timed_out = true;
+            for (uint32_t gs = 0; gs < row_tiles * KS; ++gs) {
+                const uint32_t stage = gs % pf::kStages, ks = gs % KS;
+                if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages + stage]), (gs / pf::kStages) & 1u)) timed_out = true;
                 umma::fence_after_sync();
                 const uint32_t a = smem_addr(smem + stage * 2 * pf::kTileBytes), b = a + pf::kTileBytes;
 #pragma unroll
@@ -492,34 +535,42 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
         }
     } else {
     // ---- producer warps
+    const uint32_t jhalf = tid >> 7;   // which 32-column half of the k-step this thread expands
+    for (uint32_t sub = 0; sub < row_tiles; ++sub) {
+    const uint32_t rowidx = (it.rt + sub) * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
     BRegs breg = fetch_b(s_row, n, n_mma, 0);
+    Iq4Raw raw{};
+    if (FMT == QKM_TYPE_IQ4_XS) raw = load_iq4(wt + (size_t)rt16 * kTile, r16, 0, jhalf);
     for (uint32_t ks = 0; ks < KS; ++ks) {
-        const uint32_t stage = ks % pf::kStages;
+        const uint32_t gs = sub * KS + ks, stage = gs % pf::kStages;
         BRegs bnext{};
-        if (ks + 1 < KS) bnext = fetch_b(s_row, n, n_mma, (ks + 1) * 64);
-        if (ks >= (uint32_t)pf::kStages)
-            if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
+        Iq4Raw next{};
+        if (ks + 1 < KS) {
+            bnext = fetch_b(s_row, n, n_mma, (ks + 1) * 64);
+            if (FMT == QKM_TYPE_IQ4_XS)
+                next = load_iq4(wt + ((size_t)((ks + 1) >> 2) * RT16 + rt16) * kTile, r16, (ks + 1) & 3u, jhalf);
+        }
+        if (gs >= (uint32_t)pf::kStages)
+            if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((gs / pf::kStages) - 1) & 1u)) timed_out = true;
         uint8_t* st = smem + stage * 2 * pf::kTileBytes;
-        {
+        if (FMT == QKM_TYPE_IQ4_XS) {
+            produce_iq4(raw, ks & 3u, jhalf, s_pair_lane, st, r);
+            raw = next;
+        } else {
             const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-            if (tid < 128) {
-                if (FMT == QKM_TYPE_IQ4_XS) produce_iq4<0, 1>(tile, r16, ks & 3u, s_kv, lane, st, r);
-                else produce_q8<false, 0, 1>(tile, r16, ks & 3u, st, r);
-            } else {
-                if (FMT == QKM_TYPE_IQ4_XS) produce_iq4<1, 2>(tile, r16, ks & 3u, s_kv, lane, st, r);
-                else produce_q8<false, 1, 2>(tile, r16, ks & 3u, st, r);
-            }
+            if (tid < 128) produce_q8<false, 0, 1>(tile, r16, ks & 3u, st, r);
+            else produce_q8<false, 1, 2>(tile, r16, ks & 3u, st, r);
         }
         store_b(st + pf::kTileBytes, breg, n_mma);
         breg = bnext;
         umma::fence_smem_to_async();
         mbar_arrive(smem_addr(&s_bar[pf::kStages + stage]));
     }
-    if (!mbar_wait_bounded(smem_addr(&s_bar[2 * pf::kStages]), 0)) timed_out = true;
+    if (!mbar_wait_bounded(smem_addr(&s_bar[2 * pf::kStages]), sub & 1u)) timed_out = true;
     umma::fence_after_sync();
     {
         const uint32_t lg = warp & 3u, row = 32 * lg + lane;
-        const uint32_t o = it.rt * 128u + row;
+        const uint32_t o = (it.rt + sub) * 128u + row;
         for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += 2) {
             uint32_t v[16];
             umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, v);
@@ -527,15 +578,13 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 const uint32_t col = cb * 16 + i;
-                if (col < n) {
-                    const uint32_t pos = it.pair_off + col, pr = pairs[pos], tok = pr >> 4, slot = pr & 15u;
-                    const float wgt = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
-                    // routing weight after the full K reduction
-                    contrib[(size_t)pos * d.n_embd + o] = wgt * __uint_as_float(v[i]);
-                }
+                // routing weight after the full K reduction
+                if (col < n) contrib[(size_t)(it.pair_off + col) * d.n_embd + o] = s_wgt[col] * __uint_as_float(v[i]);
             }
         }
     }
+    umma::fence_before_sync();   // the accumulator is read out before the next tile's first MMA overwrites it
+    }  // row tiles
     }  // producer / epilogue warps
     umma::fence_before_sync();
     __syncthreads();
@@ -584,7 +633,7 @@ template <int FMT>
 static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
                                      const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
                                      const uint32_t* n_items, uint32_t max_items, float* h, void* hb, uint32_t* status) {
-    const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 256 * pf::kGridReplicas * 8 + 128 * pf::kSignReplicas * 16 + 1024;
+    const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 256 * pf::kGridReplicas * 4 + 128 + 1024;
     cudaError_t e = cudaFuncSetAttribute(gateup_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     gateup_mma_kernel<FMT><<<max_items, pf::kBlock, smem, L.stream>>>(
@@ -610,11 +659,14 @@ template <int FMT>
 static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const void* tiles, const void* hb,
                                    const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items,
                                    const uint32_t* n_items, uint32_t max_items, float* contrib, uint32_t* status) {
-    const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + 16 * 32 * 4 + 1024;
+    const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + (FMT == QKM_TYPE_IQ4_XS ? 256 * 32 * 4 : 0) + 1024;
     cudaError_t e = cudaFuncSetAttribute(down_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    down_mma_kernel<FMT><<<max_items, pf::kBlock, smem, L.stream>>>(
-        (const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items, n_items, contrib, d, status);
+    // routed experts: four row tiles per block (set-up amortised); the shared expert has few blocks, one each
+    uint32_t row_tiles = FMT == QKM_TYPE_IQ4_XS ? 4u : 1u;
+    while (row_tiles > 1 && (d.n_embd / 128) % row_tiles) row_tiles >>= 1;
+    down_mma_kernel<FMT><<<(max_items + row_tiles - 1) / row_tiles, pf::kBlock, smem, L.stream>>>(
+        (const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items, n_items, contrib, d, row_tiles, status);
     L.count();
     return cudaGetLastError();
 }
