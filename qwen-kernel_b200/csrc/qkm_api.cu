@@ -631,12 +631,13 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     const uint32_t tiles_now = d.n_expert < n * d.n_used ? d.n_expert + (n * d.n_used + NT - 1) / NT : n * d.n_used;
     const uint32_t sh_now = (n + NT - 1) / NT;
     c->prof_begin();
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes));
+    QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
+                                      nullptr, nullptr, c->xb, c->xscale, c->status));
     c->prof_mark("moe.route");
     QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
     QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n, c->mma_items[0], c->mma_items[1],
                                   c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of));
-    QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
     c->prof_mark("moe.pairs");
     // the shared expert's two GEMMs (few, long blocks) run beside the routed ones
     const bool fork = !c->profiling;
@@ -816,8 +817,14 @@ extern "C" QKM_API int qkm_ep_dispatch(qkm_ctx* c, uint32_t layer, const float* 
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     const bool planes = ld.tiles_ok && n <= 64;   // the streamed shared-expert kernels read digit planes
+    const bool tc = ld.tiles_ok && n >= 128;      // tensor-core logits from f16 rows
+    if (tc) {
+        if (int rc = ensure_prefill_scratch(c)) return rc;
+        QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
+    }
     QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
-                                      planes ? c->xplanes : nullptr, planes ? c->xscale : nullptr));
+                                      planes ? c->xplanes : nullptr, planes ? c->xscale : nullptr, tc ? c->xb : nullptr,
+                                      tc ? c->xscale : nullptr, c->status));
     QKM_LAUNCH(c, launch_ep_plan(c->L(), d, c->sel, n, n_ranks, c->ep_counts, c->ep_send_tok, c->ep_send_pos));
     const uint32_t fan = n_ranks < d.n_used ? n_ranks : d.n_used;
     QKM_LAUNCH(c, launch_ep_pack(c->L(), d, x, c->sel, c->ep_send_tok, c->ep_counts + n_ranks, n * fan, xsend, selsend));

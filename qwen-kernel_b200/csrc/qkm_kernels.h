@@ -97,7 +97,13 @@ cudaError_t launch_select(const Launch& L, const qkm_dims& d, const float* logit
 cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t router_type,
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
                                 uint32_t n_tokens, void* scratch, size_t scratch_bytes, int8_t* xplanes = nullptr,
-                                float* xscale = nullptr);
+                                float* xscale = nullptr, const void* x_f16 = nullptr, const float* x_f16_inv = nullptr,
+                                uint32_t* status = nullptr);
+// f32 logits from f16 operands on the tensor cores (x_f16 / x_inv_scale as written by launch_to_f16_rows);
+// |error| <= 2^-9 * |router row| * |x|.  Needs n_expert % 128 == 0 and n_embd <= 4096.
+cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
+                              const void* x_f16, const float* x_inv_scale, float* logits, uint32_t n_tokens,
+                              uint32_t* status);
 cudaError_t launch_group_pairs(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                                uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,
                                uint32_t expert_count);

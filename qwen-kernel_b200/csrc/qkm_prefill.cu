@@ -592,6 +592,136 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     if (timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
+// ---- router logits on the tensor cores -----------------------------------------------------------------
+// logits[t][e] = router[e] . x[t] with f16 operands (the router as stored when it is F16, rounded
+// from F32 otherwise; x rows as written by to_f16_rows_kernel) and f32 accumulation in tensor
+// memory.  These logits only pre-select: the selection kernel re-evaluates every expert within
+// its error bound of the k-th in f64, so the bound has to hold, not the last bits.
+// Error per logit <= (2^-11 [x rounding] + 2^-11 [router rounding] + K * 2^-22 [accumulation])
+// * |w| * |x|, below 2^-9 * |w| * |x| for K <= 4096.
+// Block = 128 experts (M) x up to 128 tokens (N); 256 producer threads copy both operand tiles
+// into the swizzled layout, the ninth warp issues the MMAs.
+struct LgRegs { uint4 a[4], b[4]; };
+
+template <int TYPE>
+__device__ __forceinline__ void lg_fetch(LgRegs& r, const uint8_t* __restrict__ router, const __half* __restrict__ xh,
+                                         uint32_t e0, uint32_t t0, uint32_t n, uint32_t n_mma, uint32_t K, uint32_t k0) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const uint32_t qd = threadIdx.x + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
+        if (TYPE == QKM_TYPE_F16) {
+            r.a[i] = *reinterpret_cast<const uint4*>(router + ((size_t)(e0 + row) * K + k0 + 8 * c) * 2);
+        } else {
+            const float4* p = reinterpret_cast<const float4*>(router + ((size_t)(e0 + row) * K + k0 + 8 * c) * 4);
+            const float4 lo = p[0], hi = p[1];
+            r.a[i] = make_uint4(pack16<true>(lo.x, lo.y), pack16<true>(lo.z, lo.w), pack16<true>(hi.x, hi.y), pack16<true>(hi.z, hi.w));
+        }
+        r.b[i] = make_uint4(0, 0, 0, 0);
+        if (qd < n_mma * 8 && row < n) r.b[i] = *reinterpret_cast<const uint4*>(xh + (size_t)(t0 + row) * K + k0 + 8 * c);
+    }
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(pf::kBlock, 2)
+logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__ xh, const float* __restrict__ x_inv_scale,
+                  float* __restrict__ logits, uint32_t n_expert, uint32_t K, uint32_t n_tokens, uint32_t* __restrict__ status) {
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
+    __shared__ uint32_t s_tmem;
+    uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    const uint32_t t0 = blockIdx.x * 128u, e0 = blockIdx.y * 128u;
+    const uint32_t n = min(128u, n_tokens - t0), n_mma = (n + 15u) & ~15u, KS = K / 64;
+    if (tid == 0) {
+        for (int s = 0; s < pf::kStages; ++s) {
+            mbar_init(smem_addr(&s_bar[s]), 1);
+            mbar_init(smem_addr(&s_bar[pf::kStages + s]), pf::kThreads);
+        }
+        mbar_init(smem_addr(&s_bar[2 * pf::kStages]), 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), 128); umma::tmem_relinquish(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    const uint32_t tmem = s_tmem;
+    const uint32_t idesc = umma::instr_desc_f16(n_mma);
+    bool timed_out = false;
+    if (tid >= pf::kThreads) {
+        if (lane == 0) {
+            for (uint32_t ks = 0; ks < KS; ++ks) {
+                const uint32_t stage = ks % pf::kStages;
+                if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages + stage]), (ks / pf::kStages) & 1u)) timed_out = true;
+                umma::fence_after_sync();
+                const uint32_t a = smem_addr(smem + stage * 2 * pf::kTileBytes), b = a + pf::kTileBytes;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    umma::mma_f16_ss(tmem, umma::smem_desc(a + 32 * j), umma::smem_desc(b + 32 * j), idesc, (ks | (uint32_t)j) != 0);
+                umma::commit(smem_addr(&s_bar[stage]));
+                if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[2 * pf::kStages]));
+            }
+        }
+    } else {
+        LgRegs cur;
+        lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K, 0);
+        for (uint32_t ks = 0; ks < KS; ++ks) {
+            const uint32_t stage = ks % pf::kStages;
+            if (ks >= (uint32_t)pf::kStages)
+                if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
+            uint8_t* st = smem + stage * 2 * pf::kTileBytes;
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t qd = tid + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
+                *reinterpret_cast<uint4*>(st + umma::sw128_chunk(row, c)) = cur.a[i];
+                if (qd < n_mma * 8) *reinterpret_cast<uint4*>(st + pf::kTileBytes + umma::sw128_chunk(row, c)) = cur.b[i];
+            }
+            umma::fence_smem_to_async();
+            mbar_arrive(smem_addr(&s_bar[pf::kStages + stage]));
+            if (ks + 1 < KS) lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K, (ks + 1) * 64);
+        }
+        if (!mbar_wait_bounded(smem_addr(&s_bar[2 * pf::kStages]), 0)) timed_out = true;
+        umma::fence_after_sync();
+        const uint32_t lg = warp & 3u, e = e0 + 32 * lg + lane;
+        for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += 2) {
+            uint32_t v[16];
+            umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, v);
+            umma::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t col = cb * 16 + i;
+                if (col < n) logits[(size_t)(t0 + col) * n_expert + e] = __uint_as_float(v[i]) * x_inv_scale[t0 + col];
+            }
+        }
+    }
+    umma::fence_before_sync();
+    __syncthreads();
+    if (warp == 0) umma::tmem_dealloc(tmem, 128);
+    if (timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+}
+
+cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
+                              const void* x_f16, const float* x_inv_scale, float* logits, uint32_t n_tokens,
+                              uint32_t* status) {
+    if (n_tokens == 0) return cudaSuccess;
+    if (d.n_expert % 128 || d.n_embd % 64 || d.n_embd > 4096) return cudaErrorInvalidValue;
+    const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + 1024;
+    const dim3 grid((n_tokens + 127) / 128, d.n_expert / 128);
+    cudaError_t e;
+    if (router_type == QKM_TYPE_F16) {
+        e = cudaFuncSetAttribute(logits_mma_kernel<QKM_TYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        logits_mma_kernel<QKM_TYPE_F16><<<grid, pf::kBlock, smem, L.stream>>>((const uint8_t*)router, (const __half*)x_f16, x_inv_scale, logits, d.n_expert, d.n_embd, n_tokens, status);
+    } else if (router_type == QKM_TYPE_F32) {
+        e = cudaFuncSetAttribute(logits_mma_kernel<QKM_TYPE_F32>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return e;
+        logits_mma_kernel<QKM_TYPE_F32><<<grid, pf::kBlock, smem, L.stream>>>((const uint8_t*)router, (const __half*)x_f16, x_inv_scale, logits, d.n_expert, d.n_embd, n_tokens, status);
+    } else {
+        return cudaErrorInvalidValue;
+    }
+    L.count();
+    return cudaGetLastError();
+}
+
 // ---- fold: y[t] = sum over slots (in order) of contrib[pos(t,s)], then the shared expert -----------------
 __global__ void fold_pairs_kernel(const float* __restrict__ contrib, const uint32_t* __restrict__ pos_of,
                                   float* __restrict__ y, uint32_t n_used, uint32_t n_embd) {

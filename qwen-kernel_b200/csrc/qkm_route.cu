@@ -335,10 +335,10 @@ __global__ void __launch_bounds__(256)
 refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict__ logits_any,
                      const float* __restrict__ row_norm2, const float* __restrict__ gis,
                      const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d,
-                     int8_t* __restrict__ xplanes, float* __restrict__ xscale, float eps_terms) {
+                     int8_t* __restrict__ xplanes, float* __restrict__ xscale, float eps_terms, float eps_abs) {
     extern __shared__ float s_x[];  // n_embd floats
     __shared__ double s_val[512];   // f64 logit of every candidate, -inf elsewhere
-    __shared__ float s_log[512];
+    __shared__ __align__(16) float s_log[512];
     __shared__ double s_red[8];
     __shared__ float s_f[8], s_rn[8], s_xm[8];
     __shared__ uint32_t s_cand[kMaxCand];
@@ -417,24 +417,37 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
         if (tid == 0) xscale[t] = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
     }
 
+    bool listed_all = true;     // every expert holds an f64 value (s_val)
+    uint32_t n_listed = 0;      // else: the candidates s_cand[0 .. n_listed)
     if (!EXACT) {
     // k-th largest f32 logit: the expert that exactly n_used-1 others precede
     {
+        // four logits per shared-memory load (n_expert is padded to 512 with the floor value)
+        const uint32_t n4 = (d.n_expert + 3u) & ~3u;
+        const bool two = d.n_expert > 256;       // the second expert of a thread exists only then
         uint32_t c0 = 0, c1 = 0;
-        for (uint32_t j = 0; j < d.n_expert; ++j) {
-            const float vj = s_log[j];
-            c0 += (vj > l0 || (vj == l0 && j < id0)) ? 1u : 0u;
-            c1 += (vj > l1 || (vj == l1 && j < id1)) ? 1u : 0u;
+        for (uint32_t j = 0; j < n4; j += 4) {
+            const float4 v = *reinterpret_cast<const float4*>(s_log + j);
+            c0 += (v.x > l0 || (v.x == l0 && j < id0)) ? 1u : 0u;
+            c0 += (v.y > l0 || (v.y == l0 && j + 1 < id0)) ? 1u : 0u;
+            c0 += (v.z > l0 || (v.z == l0 && j + 2 < id0)) ? 1u : 0u;
+            c0 += (v.w > l0 || (v.w == l0 && j + 3 < id0)) ? 1u : 0u;
+            if (two) {
+                c1 += (v.x > l1 || (v.x == l1 && j < id1)) ? 1u : 0u;
+                c1 += (v.y > l1 || (v.y == l1 && j + 1 < id1)) ? 1u : 0u;
+                c1 += (v.z > l1 || (v.z == l1 && j + 2 < id1)) ? 1u : 0u;
+                c1 += (v.w > l1 || (v.w == l1 && j + 3 < id1)) ? 1u : 0u;
+            }
         }
         if (id0 < d.n_expert && c0 == d.n_used - 1) s_kth = l0;
-        if (id1 < d.n_expert && c1 == d.n_used - 1) s_kth = l1;
+        if (two && id1 < d.n_expert && c1 == d.n_used - 1) s_kth = l1;
     }
     __syncthreads();
     const float kth = s_kth;
     // Error bound of one f32 logit whose longest chain of additions has eps_terms links:
     // |err| <= eps_terms * 2^-24 * sum|w_k x_k| <= that * |w| * |x|.
     // Doubled for safety, and doubled again because two logits are compared.
-    const float eps = eps_terms * 5.9604645e-8f * sqrtf(r2) * sqrtf(x2);
+    const float eps = 5.9604645e-8f * (eps_terms * sqrtf(r2) + eps_abs) * sqrtf(x2);
     const float thresh = kth - 4.0f * eps;
     // candidates: every expert at or above the threshold
     // (written as !(l < thresh) so a NaN threshold - NaN in x - admits every expert)
@@ -446,6 +459,8 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
     // too many near-ties (or non-finite input: everything at the floor): evaluate all experts
     const bool all = ncand > kMaxCand || ncand < d.n_used;
     const uint32_t total = all ? d.n_expert : ncand;
+    listed_all = all;
+    n_listed = ncand;
 
     // f64 re-evaluation, one warp per candidate, four independent partial sums per lane
     const size_t rb = row_bytes(TYPE, d.n_embd);
@@ -474,10 +489,19 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
         const bool m0 = v0 > ninf, m1 = v1 > ninf;
         if (m0 || m1) {
             uint32_t c0 = 0, c1 = 0;
-            for (uint32_t j = 0; j < d.n_expert; ++j) {
-                const double vj = s_val[j];
-                c0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
-                c1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
+            if (EXACT || listed_all) {
+                for (uint32_t j = 0; j < d.n_expert; ++j) {
+                    const double vj = s_val[j];
+                    c0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
+                    c1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
+                }
+            } else {   // only the listed candidates hold values
+                for (uint32_t q = 0; q < n_listed; ++q) {
+                    const uint32_t j = s_cand[q];
+                    const double vj = s_val[j];
+                    c0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
+                    c1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
+                }
             }
             if (m0 && c0 < d.n_used) { s_best_id[c0] = id0; s_best_val[c0] = v0; }
             if (m1 && c1 < d.n_used) { s_best_id[c1] = id1; s_best_val[c1] = v1; }
@@ -513,7 +537,8 @@ size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert) {
 
 cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t router_type,
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
-                                uint32_t n_tokens, void* scratch, size_t scratch_bytes, int8_t* xplanes, float* xscale) {
+                                uint32_t n_tokens, void* scratch, size_t scratch_bytes, int8_t* xplanes, float* xscale,
+                                const void* x_f16, const float* x_f16_inv, uint32_t* status) {
     if (n_tokens == 0) return cudaSuccess;
     if (router_type != QKM_TYPE_F32 && router_type != QKM_TYPE_F16) return cudaErrorInvalidValue;
     if (n_tokens <= kExactMaxTokens && (size_t)n_tokens * d.n_expert * sizeof(double) <= scratch_bytes) {
@@ -522,9 +547,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         cudaError_t e = launch_logits64(L, d, router_type, router, x, l64, n_tokens);
         if (e != cudaSuccess) return e;
         if (router_type == QKM_TYPE_F32)
-            refine_select_kernel<QKM_TYPE_F32, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f);
+            refine_select_kernel<QKM_TYPE_F32, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f);
         else
-            refine_select_kernel<QKM_TYPE_F16, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f);
+            refine_select_kernel<QKM_TYPE_F16, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f);
         L.count();
         return cudaGetLastError();
     }
@@ -532,8 +557,19 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
     float* logits = (float*)scratch;
     float* norm2 = logits + (size_t)n_tokens * d.n_expert;
     const uint8_t* r = (const uint8_t*)router;
-    float eps_terms;
-    if (n_tokens >= 1024) {   // many tokens: tiled GEMM, one chain of n_embd additions per logit
+    float eps_terms, eps_abs = 0.f;
+    if (x_f16 && x_f16_inv && status && n_tokens >= 128 && d.n_expert % 128 == 0 && d.n_embd <= 4096) {
+        // tensor cores, f16 operands: |error| <= 2^-9 |w| |x|, plus the flush of tiny router values
+        if (router_type == QKM_TYPE_F32)
+            row_norm2_kernel<QKM_TYPE_F32><<<(d.n_expert + 7) / 8, 256, 0, L.stream>>>(r, norm2, d.n_expert, d.n_embd);
+        else
+            row_norm2_kernel<QKM_TYPE_F16><<<(d.n_expert + 7) / 8, 256, 0, L.stream>>>(r, norm2, d.n_expert, d.n_embd);
+        L.count();
+        cudaError_t e = launch_logits_mma(L, d, router_type, router, x_f16, x_f16_inv, logits, n_tokens, status);
+        if (e != cudaSuccess) return e;
+        eps_terms = 32768.f;                       // 2^-9 / 2^-24
+        eps_abs = 2.f * sqrtf((float)d.n_embd);    // 2^-25 per router element that f16 flushes
+    } else if (n_tokens >= 1024) {   // many tokens: tiled GEMM, one chain of n_embd additions per logit
         const dim3 grid((d.n_expert + 63) / 64, (n_tokens + 63) / 64);
         if (router_type == QKM_TYPE_F32) {
             row_norm2_kernel<QKM_TYPE_F32><<<(d.n_expert + 7) / 8, 256, 0, L.stream>>>(r, norm2, d.n_expert, d.n_embd);
@@ -552,9 +588,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         eps_terms = (float)(d.n_embd / 32 + 8);
     }
     if (router_type == QKM_TYPE_F32)
-        refine_select_kernel<QKM_TYPE_F32, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
+        refine_select_kernel<QKM_TYPE_F32, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs);
     else
-        refine_select_kernel<QKM_TYPE_F16, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms);
+        refine_select_kernel<QKM_TYPE_F16, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs);
     L.count();
     return cudaGetLastError();
 }
