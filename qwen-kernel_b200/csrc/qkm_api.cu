@@ -69,6 +69,7 @@ struct qkm_ctx {
     float* contrib_p = nullptr;       // [max_tokens*(n_used+1)][n_embd]
     MmaItem* mma_items[4] = {nullptr, nullptr, nullptr, nullptr};  // gate/up, down, shared gate/up, shared down
     uint32_t* pos_of = nullptr;       // [max_tokens*(n_used+1)]
+    uint32_t* group_hist = nullptr;   // scratch of the multi-block grouping
     // expert-parallel exchange plan of the last qkm_ep_dispatch, allocated on first use
     uint32_t ep_ranks = 0;
     uint32_t* ep_counts = nullptr;       // [n_ranks + 1] rows per destination rank, then their sum
@@ -275,7 +276,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
-                       c->pos_of, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
+                       c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->ep_counts_host) cudaFreeHost(c->ep_counts_host);
@@ -613,6 +614,7 @@ static int ensure_prefill_scratch(qkm_ctx* c) {
     QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[2], max_sh * rt_gu * sizeof(MmaItem)));
     QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[3], max_sh * rt_dn * sizeof(MmaItem)));
     QKM_CUDA(c, cudaMalloc((void**)&c->pos_of, rows * sizeof(uint32_t)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->group_hist, group_wide_scratch_bytes((uint32_t)T, d.n_used, c->ecount)));
     return QKM_OK;
 }
 
@@ -635,9 +637,9 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
                                       nullptr, nullptr, c->xb, c->xscale, c->status));
     c->prof_mark("moe.route");
-    QKM_LAUNCH(c, launch_group_pairs(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount));
+    QKM_LAUNCH(c, launch_group_pairs_wide(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount, c->group_hist, c->pos_of));
     QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n, c->mma_items[0], c->mma_items[1],
-                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of));
+                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of, true, true));
     c->prof_mark("moe.pairs");
     // the shared expert's two GEMMs (few, long blocks) run beside the routed ones
     const bool fork = !c->profiling;
@@ -881,8 +883,8 @@ extern "C" QKM_API int qkm_ep_expert_forward(qkm_ctx* c, uint32_t layer, const f
     const qkm_layer_dev& ld = c->layers[layer];
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
-    QKM_LAUNCH(c, launch_group_pairs(c->L(), d, selrecv, n_recv, c->offsets, c->pairs, c->efirst, c->ecount));
     if (!ld.tiles_ok) {   // generic kernels on the raw layout
+        QKM_LAUNCH(c, launch_group_pairs(c->L(), d, selrecv, n_recv, c->offsets, c->pairs, c->efirst, c->ecount));
         if (!c->contrib) QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
         QKM_LAUNCH(c, launch_gateup_pairs(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, xrecv, c->offsets, c->pairs, c->h, n_recv, c->efirst, c->ecount));
         QKM_CUDA(c, cudaMemsetAsync(c->contrib, 0, (size_t)n_recv * d.n_used * d.n_embd * sizeof(float), c->stream));
@@ -894,8 +896,9 @@ extern "C" QKM_API int qkm_ep_expert_forward(qkm_ctx* c, uint32_t layer, const f
     const uint32_t NT = prefill_pairs_per_block();
     const uint32_t np_max = n_recv * d.n_used;
     const uint32_t tiles_now = c->ecount < np_max ? c->ecount + (np_max + NT - 1) / NT : np_max;
+    QKM_LAUNCH(c, launch_group_pairs_wide(c->L(), d, selrecv, n_recv, c->offsets, c->pairs, c->efirst, c->ecount, c->group_hist, c->pos_of));
     QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n_recv, c->mma_items[0], c->mma_items[1],
-                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of, false));
+                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of, false, true));
     QKM_LAUNCH(c, launch_to_f16_rows(c->L(), xrecv, c->xb, c->xscale, n_recv, d.n_embd));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
                                     c->n_items, tiles_now * (d.n_ff / 128), c->h, c->hb, c->status));

@@ -42,7 +42,7 @@ cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float*
 cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
                             uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
                             MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of,
-                            bool with_shared = true);
+                            bool with_shared = true, bool routed_pos_done = false);
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
@@ -107,6 +107,13 @@ cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t route
 cudaError_t launch_group_pairs(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                                uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,
                                uint32_t expert_count);
+// The same grouping spread over many blocks (large batches).  `hist` is scratch of
+// group_wide_scratch_bytes(); pos_of (optional) gets, for every (token, slot), the position of
+// the pair in `pairs`, or 0xFFFFFFFF when its expert is not resident.
+size_t group_wide_scratch_bytes(uint32_t n_tokens, uint32_t n_used, uint32_t expert_count);
+cudaError_t launch_group_pairs_wide(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
+                                    uint32_t* offsets, uint32_t* pairs, uint32_t expert_first, uint32_t expert_count,
+                                    uint32_t* hist, uint32_t* pos_of);
 // group_pairs plus, in the same launch, the work lists of the streaming kernels
 cudaError_t launch_group_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                               uint32_t* offsets, uint32_t* pairs, uint32_t expert_first, uint32_t expert_count,

@@ -83,12 +83,14 @@ to_f16_rows_kernel(const float* __restrict__ x, __half* __restrict__ xh, float* 
 __global__ void __launch_bounds__(512)
 mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, uint32_t n_expert_local,
                 uint32_t n_tokens, uint32_t n_used, uint32_t rt_gu, uint32_t rt_dn, uint32_t with_shared,
+                uint32_t routed_pos_done,
                 MmaItem* __restrict__ items_gu, MmaItem* __restrict__ items_dn, MmaItem* __restrict__ items_sh_gu,
                 MmaItem* __restrict__ items_sh_dn, uint32_t* __restrict__ n_items, uint32_t* __restrict__ pos_of) {
     __shared__ uint32_t s_scan[512];
     const uint32_t e = threadIdx.x;
     const uint32_t np = offsets[n_expert_local];
-    for (uint32_t i = e; i < n_tokens * (n_used + 1); i += 512) pos_of[i] = 0xFFFFFFFFu;
+    if (!routed_pos_done)   // else the grouping kernels have written every routed (token, slot) entry
+        for (uint32_t i = e; i < n_tokens * (n_used + 1); i += 512) pos_of[i] = 0xFFFFFFFFu;
     uint32_t tiles = 0, p0 = 0, n = 0;
     if (e < n_expert_local) { p0 = offsets[e]; n = offsets[e + 1] - p0; tiles = (n + pf::kNT - 1) / pf::kNT; }
     s_scan[e] = tiles;
@@ -121,13 +123,14 @@ mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pai
         n_items[0] = s_scan[511] * rt_gu; n_items[1] = s_scan[511] * rt_dn;
         n_items[2] = sh_tiles * rt_gu;    n_items[3] = sh_tiles * rt_dn;
     }
-    for (uint32_t p = e; p < np; p += 512) {
-        const uint32_t pr = pairs[p];
-        pos_of[(pr >> 4) * (n_used + 1) + (pr & 15u)] = p;
-    }
-    for (uint32_t t = e; t < (with_shared ? n_tokens : 0u); t += 512) {
-        pairs[np + t] = (t << 4) | n_used;
-        pos_of[t * (n_used + 1) + n_used] = np + t;
+    if (!routed_pos_done)
+        for (uint32_t p = e; p < np; p += 512) {
+            const uint32_t pr = pairs[p];
+            pos_of[(pr >> 4) * (n_used + 1) + (pr & 15u)] = p;
+        }
+    for (uint32_t t = e; t < n_tokens; t += 512) {
+        if (with_shared) pairs[np + t] = (t << 4) | n_used;
+        pos_of[t * (n_used + 1) + n_used] = with_shared ? np + t : 0xFFFFFFFFu;
     }
 }
 
@@ -751,10 +754,10 @@ cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float*
 cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
                             uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
                             MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of,
-                            bool with_shared) {
+                            bool with_shared, bool routed_pos_done) {
     if (n_expert_local > 512) return cudaErrorInvalidValue;
     mma_plan_kernel<<<1, 512, 0, L.stream>>>(offsets, pairs, n_expert_local, n_tokens, d.n_used, d.n_ff / 128,
-                                             d.n_embd / 128, with_shared ? 1u : 0u, items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, pos_of);
+                                             d.n_embd / 128, with_shared ? 1u : 0u, routed_pos_done ? 1u : 0u, items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, pos_of);
     L.count();
     return cudaGetLastError();
 }

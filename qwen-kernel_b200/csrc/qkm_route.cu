@@ -788,6 +788,132 @@ cudaError_t launch_shared_plan(const Launch& L, const qkm_dims& d, uint32_t n_to
     return cudaGetLastError();
 }
 
+// ---- pair grouping for large batches: three launches over many blocks ---------------------------
+// The pairs (token-major, slot-minor) are cut into runs of 128, one per warp.  (1) every warp
+// counts its run per expert; (2) one block turns the counts into start positions (scan over the
+// runs per expert, then over the experts); (3) every warp places its pairs: position = expert
+// start + start of the run within the expert + rank within the run, which keeps each expert's
+// pairs in ascending (token, slot) order without atomics on global memory.
+namespace gw {
+constexpr uint32_t kRun = 128;        // pairs per warp
+constexpr uint32_t kWarps = 16;       // warps per block
+constexpr uint32_t kInvalid = 0xFFFFFFFFu;
+}  // namespace gw
+
+__device__ __forceinline__ uint32_t gw_local_expert(const qkm_sel* __restrict__ sel, uint32_t p, uint32_t n_used,
+                                                    uint32_t n_expert, uint32_t expert_first) {
+    const uint32_t t = p / n_used, s = p - t * n_used;
+    return min(sel[t].ids[s], n_expert - 1) - expert_first;   // wraps above expert_count when below the range
+}
+
+__global__ void __launch_bounds__(gw::kWarps * 32)
+group_count_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used, uint32_t n_expert,
+                   uint32_t expert_first, uint32_t expert_count, uint32_t* __restrict__ hist) {
+    extern __shared__ uint32_t s_cnt[];   // [kWarps][expert_count]
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t run = blockIdx.x * gw::kWarps + warp;
+    uint32_t* mine = s_cnt + (size_t)warp * expert_count;
+    for (uint32_t e = lane; e < expert_count; e += 32) mine[e] = 0;
+    __syncwarp();
+    const uint32_t p0 = run * gw::kRun;
+    for (uint32_t i = 0; i < gw::kRun; i += 32) {
+        const uint32_t p = p0 + i + lane;
+        if (p < np) {
+            const uint32_t e = gw_local_expert(sel, p, n_used, n_expert, expert_first);
+            if (e < expert_count) atomicAdd(&mine[e], 1u);
+        }
+    }
+    __syncwarp();
+    if (p0 < np)
+        for (uint32_t e = lane; e < expert_count; e += 32) hist[(size_t)run * expert_count + e] = mine[e];
+}
+
+__global__ void __launch_bounds__(512)
+group_scan_kernel(uint32_t* __restrict__ hist, uint32_t n_runs, uint32_t expert_count, uint32_t* __restrict__ offsets) {
+    __shared__ uint32_t s_scan[512];
+    const uint32_t e = threadIdx.x;
+    uint32_t total = 0;
+    if (e < expert_count)
+        for (uint32_t r = 0; r < n_runs; ++r) {
+            const uint32_t v = hist[(size_t)r * expert_count + e];
+            hist[(size_t)r * expert_count + e] = total;
+            total += v;
+        }
+    s_scan[e] = total;
+    __syncthreads();
+    for (uint32_t o = 1; o < 512; o <<= 1) {
+        const uint32_t v = e >= o ? s_scan[e - o] : 0;
+        __syncthreads();
+        s_scan[e] += v;
+        __syncthreads();
+    }
+    if (e < expert_count) offsets[e] = s_scan[e] - total;
+    if (e == 511) offsets[expert_count] = s_scan[511];
+}
+
+__global__ void __launch_bounds__(gw::kWarps * 32)
+group_place_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used, uint32_t n_expert,
+                   uint32_t expert_first, uint32_t expert_count, const uint32_t* __restrict__ hist,
+                   const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, uint32_t* __restrict__ pos_of) {
+    extern __shared__ uint32_t s_cnt[];   // [kWarps][expert_count]: pairs of the run placed so far, per expert
+    const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
+    const uint32_t run = blockIdx.x * gw::kWarps + warp;
+    uint32_t* mine = s_cnt + (size_t)warp * expert_count;
+    for (uint32_t e = lane; e < expert_count; e += 32) mine[e] = 0;
+    __syncwarp();
+    const uint32_t p0 = run * gw::kRun;
+    for (uint32_t i = 0; i < gw::kRun; i += 32) {
+        const uint32_t p = p0 + i + lane;
+        uint32_t e = gw::kInvalid;
+        if (p < np) {
+            e = gw_local_expert(sel, p, n_used, n_expert, expert_first);
+            if (e >= expert_count) e = gw::kInvalid;
+        }
+        // lanes with the same expert: rank by lane, the lowest lane keeps the run's counter
+        const uint32_t same = __match_any_sync(0xFFFFFFFFu, e);
+        const uint32_t rank = __popc(same & ((1u << lane) - 1u));
+        const uint32_t leader = __ffs(same) - 1;
+        uint32_t before = 0;
+        if (e != gw::kInvalid && lane == leader) { before = mine[e]; mine[e] = before + __popc(same); }
+        before = __shfl_sync(0xFFFFFFFFu, before, leader);
+        __syncwarp();
+        if (p < np) {
+            const uint32_t t = p / n_used, s = p - t * n_used;
+            uint32_t pos = gw::kInvalid;
+            if (e != gw::kInvalid) {
+                pos = offsets[e] + hist[(size_t)run * expert_count + e] + before + rank;
+                pairs[pos] = (t << 4) | s;
+            }
+            if (pos_of) pos_of[t * (n_used + 1) + s] = pos;
+        }
+    }
+}
+
+size_t group_wide_scratch_bytes(uint32_t n_tokens, uint32_t n_used, uint32_t expert_count) {
+    const size_t runs = ((size_t)n_tokens * n_used + gw::kRun - 1) / gw::kRun;
+    return (runs + gw::kWarps) * expert_count * sizeof(uint32_t);
+}
+
+cudaError_t launch_group_pairs_wide(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
+                                    uint32_t* offsets, uint32_t* pairs, uint32_t expert_first, uint32_t expert_count,
+                                    uint32_t* hist, uint32_t* pos_of) {
+    if (expert_count == 0) { expert_first = 0; expert_count = d.n_expert; }
+    if (expert_count > 512) return cudaErrorInvalidValue;
+    const uint32_t np = n_tokens * d.n_used;
+    const uint32_t n_runs = (np + gw::kRun - 1) / gw::kRun, blocks = (n_runs + gw::kWarps - 1) / gw::kWarps;
+    const size_t smem = (size_t)gw::kWarps * expert_count * sizeof(uint32_t);
+    if (np == 0) {
+        cudaError_t e = cudaMemsetAsync(offsets, 0, (expert_count + 1) * sizeof(uint32_t), L.stream);
+        return e;
+    }
+    group_count_kernel<<<blocks, gw::kWarps * 32, smem, L.stream>>>(sel, np, d.n_used, d.n_expert, expert_first, expert_count, hist);
+    group_scan_kernel<<<1, 512, 0, L.stream>>>(hist, n_runs, expert_count, offsets);
+    group_place_kernel<<<blocks, gw::kWarps * 32, smem, L.stream>>>(sel, np, d.n_used, d.n_expert, expert_first, expert_count,
+                                                                      hist, offsets, pairs, pos_of);
+    L.count(3);
+    return cudaGetLastError();
+}
+
 cudaError_t launch_group_pairs(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                                uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,
                                uint32_t expert_count) {
