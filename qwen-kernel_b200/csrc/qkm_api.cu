@@ -61,6 +61,7 @@ struct qkm_ctx {
     float* contrib_s = nullptr;       // [max_tokens][n_used+1][n_embd]
     uint32_t* arrivals = nullptr;     // [max_tokens][n_embd / unit rows]
     uint32_t* status = nullptr;       // kernel status word (device)
+    uint32_t* route_counter = nullptr; // ticket counter of the selection kernel's grouping tail (device, stays zero)
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
     // prefill (tcgen05) scratch, allocated on first use
@@ -78,7 +79,7 @@ struct qkm_ctx {
     uint32_t* ep_send_pos = nullptr;     // [max_tokens][n_ranks]
     // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
     cudaStream_t side = nullptr;
-    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_planes = nullptr;
     // the decode stack as a CUDA graph: captured on first use for a given argument set
     cudaGraphExec_t stack_graph = nullptr;
     struct { uint32_t first, count, n; const float* x; float* y; cudaStream_t stream; } stack_key{};
@@ -247,6 +248,8 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
     }
     if ((e = cudaMalloc((void**)&c->status, sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMemset(c->status, 0, sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMalloc((void**)&c->route_counter, sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMemset(c->route_counter, 0, sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMallocHost((void**)&c->status_host, sizeof(uint32_t))) != cudaSuccess) {
         bail("qkm_open: status word", cudaGetErrorString(e));
         qkm_close(c);
@@ -255,7 +258,8 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
     *c->status_host = 0;
     if (cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
-        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess) {
+        cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
+        cudaEventCreateWithFlags(&c->ev_planes, cudaEventDisableTiming) != cudaSuccess) {
         bail("qkm_open: side stream", nullptr);
         qkm_close(c);
         return nullptr;
@@ -274,7 +278,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     }
     void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
-                       c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status,
+                       c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
@@ -283,6 +287,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->ev_join) cudaEventDestroy(c->ev_join);
+    if (c->ev_planes) cudaEventDestroy(c->ev_planes);
     if (c->side) cudaStreamDestroy(c->side);
     for (cudaEvent_t ev : c->prof_ev) if (ev) cudaEventDestroy(ev);
     delete c;
@@ -534,10 +539,9 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     c->prof_begin();
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
-                                      ld.stream_ok ? c->xplanes : nullptr, ld.stream_ok ? c->xscale : nullptr));
-    c->prof_mark("moe.route");
     if (!ld.stream_ok) {  // generic kernels on the raw layout
+        QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes));
+        c->prof_mark("moe.route");
         QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
         c->prof_mark("moe.shared_gu");
         QKM_LAUNCH(c, launch_gateup_tokens(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, x, c->sel, c->h, n, c->efirst, c->ecount));
@@ -547,30 +551,42 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         return QKM_OK;
     }
     const uint32_t nb = (uint32_t)c->n_sms;
-    // Shared expert: depends on x (digit planes) only, so it runs on the side stream while
-    // the main stream groups pairs and streams the routed gate/up; they meet before the
-    // routed down kernel, which adds y2.  (Sequential while profiling.)
+    // Shared expert: depends on x only (as digit planes), so the whole of it - planes, gate/up,
+    // down - runs on the side stream from the start of the layer, beside the router.  The main
+    // stream needs the planes before the routed gate/up (ev_planes) and y2 before the routed
+    // down kernel (ev_join).  (Sequential while profiling.)
     const bool fork = !c->profiling;
     Launch S{fork ? c->side : c->stream, &c->launches};
     if (fork) {
         QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     }
-    // the shared lists depend on n only; the grouping kernel writes them, so the side
-    // stream keeps its own copies, refreshed here (tiny) - see launch_shared_plan
+    QKM_LAUNCH(c, launch_xplanes(S, x, n, d.n_embd, c->xplanes, c->xscale));
+    if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_planes, c->side));
     QKM_LAUNCH(c, launch_shared_plan(S, d, n, c->pairs, c->items_sh_gu, d.n_ff / gateup_stream_rows_per_item(),
                                      c->items_sh_dn, d.n_embd / down_stream_rows_per_item(), 2, c->n_items + 2));
     QKM_LAUNCH(c, launch_gateup_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xplanes, c->xscale, c->pairs,
                                        c->items_sh_gu, c->n_items + 2, c->h, c->hpieces, nb, c->status));
     if (!fork) c->prof_mark("moe.shared_gu");
-    QKM_LAUNCH(c, launch_down_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, c->sel, c->pairs, c->items_sh_dn,
-                                     c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));
+    QKM_LAUNCH(c, launch_down_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, nullptr, c->pairs, c->items_sh_dn,
+                                     c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));   // unweighted: w_shared is applied by the routed down kernel
     if (!fork) c->prof_mark("moe.shared_dn");
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
-    QKM_LAUNCH(c, launch_group_plan(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount, c->items_gu,
-                                    d.n_ff / gateup_stream_rows_per_item(), c->items_dn,
-                                    d.n_embd / down_stream_rows_per_item(), nullptr, nullptr, 2, c->n_items));
-    c->prof_mark("moe.pairs");
+    // Router.  Decode-sized batches: the selection kernel's last block also groups the pairs and
+    // cuts the work lists; otherwise a grouping launch follows.
+    const bool fused_plan = route_select_plans(d, n, c->route_scratch_bytes);
+    const RoutePlan rplan{c->route_counter, c->offsets, c->pairs, c->items_gu, c->items_dn, c->n_items,
+                          d.n_ff / gateup_stream_rows_per_item(), d.n_embd / down_stream_rows_per_item(), 2, c->efirst, c->ecount};
+    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
+                                      nullptr, nullptr, nullptr, nullptr, nullptr, fused_plan ? &rplan : nullptr));
+    c->prof_mark("moe.route");
+    if (!fused_plan) {
+        QKM_LAUNCH(c, launch_group_plan(c->L(), d, c->sel, n, c->offsets, c->pairs, c->efirst, c->ecount, c->items_gu,
+                                        d.n_ff / gateup_stream_rows_per_item(), c->items_dn,
+                                        d.n_embd / down_stream_rows_per_item(), nullptr, nullptr, 2, c->n_items));
+        c->prof_mark("moe.pairs");
+    }
+    if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_planes, 0));
     QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xplanes, c->xscale, c->pairs,
                                        c->items_gu, c->n_items, c->h, c->hpieces, nb, c->status));
     c->prof_mark("moe.gu");

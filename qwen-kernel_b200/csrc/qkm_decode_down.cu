@@ -245,7 +245,8 @@ down_stream_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __res
                 float sum = 0.f;
                 for (uint32_t w = 0; w < KB; ++w) sum += red[(team * KB + w) * dn::kRedFloats + row * 2 + ts];
                 const uint32_t pr = pairs[it.pair_off + ts], tok = pr >> 4, slot = pr & 15u;
-                const float wgt = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
+                // sel == NULL: the caller applies the weight (lets this kernel run before the routing is known)
+                const float wgt = sel == nullptr ? 1.f : (slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared);
                 if (arrivals != nullptr) contrib[((size_t)tok * n_slots + slot) * d.n_embd + row0 + row] = wgt * sum;
                 else y[(size_t)tok * d.n_embd + row0 + row] = wgt * sum;   // single-slot use: y is this slot's term
             }

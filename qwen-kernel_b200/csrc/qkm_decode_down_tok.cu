@@ -1,4 +1,4 @@
-// Streaming routed down projection, token major: y[t] = sum_s w_s * D[ids_s] . h[t][s] + y2[t].
+// Streaming routed down projection, token major: y[t] = sum_s w_s * D[ids_s] . h[t][s] + w_shared * y2[t].
 //
 // Replaces moe_down_iq4.comp together with the final "routed + shared" add.  A unit of
 // work is (token, 16 output rows): the team that owns it walks the token's n_used experts
@@ -175,7 +175,8 @@ down_tok_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __re
             float sum = 0.f;
             for (uint32_t w = 0; w < KB; ++w) sum += red[(team * KB + w) * 16 + lt];
             const size_t o = (size_t)tok * d.n_embd + rt * 16 + lt;
-            y[o] = sum + (y2 != nullptr ? y2[o] : 0.f);
+            // y2 holds the shared expert's down projection without its gate weight
+            y[o] = sum + (y2 != nullptr ? sel[tok].w_shared * y2[o] : 0.f);
         }
         asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(team_threads) : "memory");
     }

@@ -87,6 +87,23 @@ cudaError_t launch_gemv_stream(const Launch& L, uint32_t type, const void* W, co
                                uint32_t M, uint32_t K, uint32_t n, uint32_t n_sms, uint32_t* status);
 
 // ---- qkm_route.cu
+// x rows as int8 digit planes + per-row scale (the selection kernel can write the same).
+cudaError_t launch_xplanes(const Launch& L, const float* x, uint32_t n_tokens, uint32_t n_embd, int8_t* xplanes, float* xscale);
+// Optional tail of launch_route_select for decode-sized batches (<= 64 tokens, <= 1024 pairs,
+// f64-logit path): the selection kernel's last block also groups the pairs and cuts the
+// streaming kernels' work lists (what launch_group_plan does), saving a launch.  `counter` is a
+// zero-initialised device word the kernel leaves at zero.  route_select_plans() tells whether
+// a call with these sizes takes that path.
+struct RoutePlan {
+    uint32_t* counter;
+    uint32_t* offsets;
+    uint32_t* pairs;
+    StreamItem* items_gu;
+    StreamItem* items_dn;
+    uint32_t* n_items;
+    uint32_t chunks_gu, chunks_dn, tok_per_item, expert_first, expert_count;
+};
+bool route_select_plans(const qkm_dims& d, uint32_t n_tokens, size_t scratch_bytes);
 // Scratch the refined router needs: n_tokens * n_expert f32 logits + n_expert f32 row norms,
 // or n_tokens * n_expert f64 logits for the small batches that are ranked in f64 directly.
 size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert);
@@ -98,7 +115,7 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
                                 uint32_t n_tokens, void* scratch, size_t scratch_bytes, int8_t* xplanes = nullptr,
                                 float* xscale = nullptr, const void* x_f16 = nullptr, const float* x_f16_inv = nullptr,
-                                uint32_t* status = nullptr);
+                                uint32_t* status = nullptr, const RoutePlan* plan = nullptr);
 // f32 logits from f16 operands on the tensor cores (x_f16 / x_inv_scale as written by launch_to_f16_rows);
 // |error| <= 2^-9 * |router row| * |x|.  Needs n_expert % 128 == 0 and n_embd <= 4096.
 cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,

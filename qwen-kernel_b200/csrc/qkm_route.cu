@@ -322,6 +322,140 @@ cudaError_t launch_select(const Launch& L, const qkm_dims& d, const float* logit
     return cudaGetLastError();
 }
 
+// ---- x rows as int8 digit planes (what the streaming expert kernels read) ---------------------
+// One block per row: x * 2^p rounded to 28 bits, split into four balanced base-128 digits,
+// layout [k-block][digit][256]; xscale = 2^-p.  A row with a non-finite value gets zero digits
+// and a NaN scale.  (The selection kernel can write the same planes; doing it here lets the
+// shared expert start before the routing is known.)
+__global__ void __launch_bounds__(256)
+xplanes_kernel(const float* __restrict__ x, uint32_t n_embd, int8_t* __restrict__ xplanes, float* __restrict__ xscale) {
+    __shared__ float s_xm[8];
+    const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
+    const float* xt = x + (size_t)t * n_embd;
+    float v[16];   // n_embd <= 4096
+    float xm = 0.f;
+    bool bad = false;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t k = tid + 256 * i;
+        v[i] = k < n_embd ? xt[k] : 0.f;
+        xm = fmaxf(xm, fabsf(v[i]));
+        bad |= !(fabsf(v[i]) <= 3.0e38f);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
+    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    if (lane == 0) s_xm[warp] = xm;
+    __syncthreads();
+    float xmax = 0.f;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) xmax = fmaxf(xmax, s_xm[w]);
+    const int p = digit_exponent(xmax);
+    const float up = ldexpf(1.0f, p);
+    int8_t* pl = xplanes + (size_t)t * 4 * n_embd;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const uint32_t k = tid + 256 * i;
+        if (k < n_embd) {
+            const uint32_t dgt = any_bad ? 0u : digits4(__float2int_rn(v[i] * up));
+            int8_t* q = pl + (size_t)(k >> 8) * 1024 + (k & 255u);
+            q[0] = (int8_t)(dgt & 255u);
+            q[256] = (int8_t)((dgt >> 8) & 255u);
+            q[512] = (int8_t)((dgt >> 16) & 255u);
+            q[768] = (int8_t)(dgt >> 24);
+        }
+    }
+    if (tid == 0) xscale[t] = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
+}
+
+cudaError_t launch_xplanes(const Launch& L, const float* x, uint32_t n_tokens, uint32_t n_embd, int8_t* xplanes, float* xscale) {
+    if (n_tokens == 0) return cudaSuccess;
+    if (n_embd > 4096) return cudaErrorInvalidValue;
+    xplanes_kernel<<<n_tokens, 256, 0, L.stream>>>(x, n_embd, xplanes, xscale);
+    L.count();
+    return cudaGetLastError();
+}
+
+// ---- grouping of a decode-sized batch inside the selection kernel ------------------------------
+// The block that finishes its token last (a ticket counter tells it) groups the pairs of all
+// tokens and cuts the work list of the streaming kernels, which saves a launch on the layer's
+// critical path.  At most 1024 pairs; same result as group_pairs_kernel.
+struct GroupTail {
+    uint32_t* counter;       // NULL: no grouping here
+    uint32_t* offsets;
+    uint32_t* pairs;
+    StreamItem* items_gu;
+    StreamItem* items_dn;
+    uint32_t* n_items;       // [0] gate/up items, [1] down items
+    uint32_t chunks_gu, chunks_dn, tok_per_item, n_tokens, expert_first, expert_count;
+};
+static constexpr uint32_t kTailMaxPairs = 1024;
+
+__device__ void group_small_block(const qkm_sel* __restrict__ sel, uint32_t n_expert, uint32_t n_used, const GroupTail& g) {
+    __shared__ uint16_t s_e[kTailMaxPairs];
+    __shared__ uint32_t s_cnt[512], s_off[512];
+    __shared__ unsigned long long s_wsum[8];
+    const uint32_t tid = threadIdx.x, lane = tid & 31u, wrp = tid >> 5;
+    const uint32_t np = g.n_tokens * n_used;
+    for (uint32_t e = tid; e < 512; e += 256) s_cnt[e] = 0;
+    for (uint32_t p = tid; p < np; p += 256) {
+        const uint32_t t = p / n_used, s = p - t * n_used;
+        const uint32_t e = min(__ldcg(&sel[t].ids[s]), n_expert - 1) - g.expert_first;
+        s_e[p] = (uint16_t)(e < g.expert_count ? e : 0xFFFFu);
+    }
+    __syncthreads();
+    for (uint32_t p = tid; p < np; p += 256)
+        if (s_e[p] != 0xFFFFu) atomicAdd(&s_cnt[s_e[p]], 1u);
+    __syncthreads();
+    // exclusive scan over the experts, two per thread; pair counts low, token groups high
+    const uint32_t c0 = s_cnt[2 * tid], c1 = s_cnt[2 * tid + 1];
+    const uint32_t g0n = (c0 + g.tok_per_item - 1) / g.tok_per_item, g1n = (c1 + g.tok_per_item - 1) / g.tok_per_item;
+    unsigned long long v = (unsigned long long)(c0 + c1) | ((unsigned long long)(g0n + g1n) << 32);
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const unsigned long long up = __shfl_up_sync(0xFFFFFFFFu, v, o);
+        if (lane >= (uint32_t)o) v += up;
+    }
+    if (lane == 31) s_wsum[wrp] = v;
+    __syncthreads();
+    unsigned long long base = 0, total = 0;
+    for (uint32_t w = 0; w < 8; ++w) { if (w < wrp) base += s_wsum[w]; total += s_wsum[w]; }
+    const unsigned long long excl = base + v - ((unsigned long long)(c0 + c1) | ((unsigned long long)(g0n + g1n) << 32));
+    const uint32_t off0 = (uint32_t)(excl & 0xFFFFFFFFull), grp0 = (uint32_t)(excl >> 32);
+    s_off[2 * tid] = off0;
+    s_off[2 * tid + 1] = off0 + c0;
+    if (2 * tid < g.expert_count) g.offsets[2 * tid] = off0;
+    if (2 * tid + 1 < g.expert_count) g.offsets[2 * tid + 1] = off0 + c0;
+    if (tid == 0) {
+        g.offsets[g.expert_count] = (uint32_t)(total & 0xFFFFFFFFull);
+        g.n_items[0] = (uint32_t)(total >> 32) * g.chunks_gu;
+        g.n_items[1] = (uint32_t)(total >> 32) * g.chunks_dn;
+    }
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+        const uint32_t e = 2 * tid + k, cnt = k ? c1 : c0, off = k ? off0 + c0 : off0, gfirst = k ? grp0 + g0n : grp0;
+        const uint32_t groups = k ? g1n : g0n;
+        for (uint32_t gi = 0; gi < groups; ++gi) {
+            StreamItem it;
+            it.expert = (uint16_t)e;
+            it.ntok = (uint8_t)min(g.tok_per_item, cnt - gi * g.tok_per_item);
+            it.pair_off = off + gi * g.tok_per_item;
+            for (uint32_t c = 0; c < g.chunks_gu; ++c) { it.chunk = (uint8_t)c; g.items_gu[(size_t)(gfirst + gi) * g.chunks_gu + c] = it; }
+            for (uint32_t c = 0; c < g.chunks_dn; ++c) { it.chunk = (uint8_t)c; g.items_dn[(size_t)(gfirst + gi) * g.chunks_dn + c] = it; }
+        }
+    }
+    __syncthreads();
+    // place: rank among the earlier pairs of the same expert keeps (token, slot) order
+    for (uint32_t p = tid; p < np; p += 256) {
+        const uint32_t e = s_e[p];
+        if (e == 0xFFFFu) continue;
+        uint32_t rank = 0;
+        for (uint32_t q = 0; q < p; ++q) rank += s_e[q] == e ? 1u : 0u;
+        const uint32_t t = p / n_used, s = p - t * n_used;
+        g.pairs[s_off[e] + rank] = (t << 4) | s;
+    }
+}
+
 // ---- refined selection: f32 ranking, f64 re-evaluation of the boundary ---------------------
 // One block per token.  Ranking is done by counting: every thread counts how many experts
 // precede its own in the order (value descending, id ascending), which needs no rounds of
@@ -335,9 +469,10 @@ __global__ void __launch_bounds__(256)
 refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict__ logits_any,
                      const float* __restrict__ row_norm2, const float* __restrict__ gis,
                      const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d,
-                     int8_t* __restrict__ xplanes, float* __restrict__ xscale, float eps_terms, float eps_abs) {
+                     int8_t* __restrict__ xplanes, float* __restrict__ xscale, float eps_terms, float eps_abs,
+                     GroupTail tail) {
     extern __shared__ float s_x[];  // n_embd floats
-    __shared__ double s_val[512];   // f64 logit of every candidate, -inf elsewhere
+    __shared__ __align__(16) double s_val[512];   // f64 logit of every candidate, -inf elsewhere
     __shared__ __align__(16) float s_log[512];
     __shared__ double s_red[8];
     __shared__ float s_f[8], s_rn[8], s_xm[8];
@@ -490,10 +625,22 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
         if (m0 || m1) {
             uint32_t c0 = 0, c1 = 0;
             if (EXACT || listed_all) {
-                for (uint32_t j = 0; j < d.n_expert; ++j) {
-                    const double vj = s_val[j];
-                    c0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
-                    c1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
+                // two values per shared-memory load (entries past n_expert hold -inf and never count)
+                const uint32_t n2 = (d.n_expert + 1u) & ~1u;
+                if (d.n_expert <= 256) {
+                    for (uint32_t j = 0; j < n2; j += 2) {
+                        const double2 vj = *reinterpret_cast<const double2*>(s_val + j);
+                        c0 += (vj.x > v0 || (vj.x == v0 && j < id0)) ? 1u : 0u;
+                        c0 += (vj.y > v0 || (vj.y == v0 && j + 1 < id0)) ? 1u : 0u;
+                    }
+                } else {
+                    for (uint32_t j = 0; j < n2; j += 2) {
+                        const double2 vj = *reinterpret_cast<const double2*>(s_val + j);
+                        c0 += (vj.x > v0 || (vj.x == v0 && j < id0)) ? 1u : 0u;
+                        c0 += (vj.y > v0 || (vj.y == v0 && j + 1 < id0)) ? 1u : 0u;
+                        c1 += (vj.x > v1 || (vj.x == v1 && j < id1)) ? 1u : 0u;
+                        c1 += (vj.y > v1 || (vj.y == v1 && j + 1 < id1)) ? 1u : 0u;
+                    }
                 }
             } else {   // only the listed candidates hold values
                 for (uint32_t q = 0; q < n_listed; ++q) {
@@ -525,9 +672,26 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
             sel[t].pad[lane - 17] = 0.f;
         }
     }
+    if (tail.counter != nullptr) {
+        __shared__ uint32_t s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) s_last = atomicAdd(tail.counter, 1u) == gridDim.x - 1 ? 1u : 0u;
+        __syncthreads();
+        if (s_last) {
+            if (tid == 0) *tail.counter = 0;   // ready for the next launch
+            __threadfence();
+            group_small_block(sel, d.n_expert, d.n_used, tail);
+        }
+    }
 }
 
 static constexpr uint32_t kExactMaxTokens = 64;   // decode-sized batches rank f64 logits directly
+
+bool route_select_plans(const qkm_dims& d, uint32_t n_tokens, size_t scratch_bytes) {
+    return n_tokens > 0 && n_tokens <= kExactMaxTokens && n_tokens * d.n_used <= kTailMaxPairs &&
+           (size_t)n_tokens * d.n_expert * sizeof(double) <= scratch_bytes;
+}
 
 size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert) {
     const size_t f32_path = ((size_t)n_tokens * n_expert + n_expert) * sizeof(float);
@@ -538,8 +702,15 @@ size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert) {
 cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t router_type,
                                 const void* router, const float* gis, const float* x, qkm_sel* sel,
                                 uint32_t n_tokens, void* scratch, size_t scratch_bytes, int8_t* xplanes, float* xscale,
-                                const void* x_f16, const float* x_f16_inv, uint32_t* status) {
+                                const void* x_f16, const float* x_f16_inv, uint32_t* status, const RoutePlan* plan) {
     if (n_tokens == 0) return cudaSuccess;
+    GroupTail tail{};
+    if (plan && plan->counter && n_tokens <= kExactMaxTokens && n_tokens * d.n_used <= kTailMaxPairs) {
+        uint32_t ef = plan->expert_first, ec = plan->expert_count;
+        if (ec == 0) { ef = 0; ec = d.n_expert; }
+        tail = GroupTail{plan->counter, plan->offsets, plan->pairs, plan->items_gu, plan->items_dn, plan->n_items,
+                         plan->chunks_gu, plan->chunks_dn, plan->tok_per_item, n_tokens, ef, ec};
+    }
     if (router_type != QKM_TYPE_F32 && router_type != QKM_TYPE_F16) return cudaErrorInvalidValue;
     if (n_tokens <= kExactMaxTokens && (size_t)n_tokens * d.n_expert * sizeof(double) <= scratch_bytes) {
         // small batch: f64 logits, ranked as they are
@@ -547,9 +718,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         cudaError_t e = launch_logits64(L, d, router_type, router, x, l64, n_tokens);
         if (e != cudaSuccess) return e;
         if (router_type == QKM_TYPE_F32)
-            refine_select_kernel<QKM_TYPE_F32, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f);
+            refine_select_kernel<QKM_TYPE_F32, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
         else
-            refine_select_kernel<QKM_TYPE_F16, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f);
+            refine_select_kernel<QKM_TYPE_F16, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
         L.count();
         return cudaGetLastError();
     }
@@ -588,9 +759,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         eps_terms = (float)(d.n_embd / 32 + 8);
     }
     if (router_type == QKM_TYPE_F32)
-        refine_select_kernel<QKM_TYPE_F32, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs);
+        refine_select_kernel<QKM_TYPE_F32, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs, GroupTail{});
     else
-        refine_select_kernel<QKM_TYPE_F16, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs);
+        refine_select_kernel<QKM_TYPE_F16, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs, GroupTail{});
     L.count();
     return cudaGetLastError();
 }
