@@ -273,6 +273,11 @@ QKM_API const float   *qkm_h_device(const qkm_ctx *c);
 QKM_API int qkm_ep_dispatch(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
                             uint32_t n_ranks, float *xsend, qkm_sel *selsend,
                             uint32_t *counts_host);
+/* As qkm_ep_dispatch, but asynchronous: counts_dev (DEVICE memory, n_ranks 32-bit words)
+ * receives the row counts on the context's stream; nothing is copied to the host. */
+QKM_API int qkm_ep_dispatch_dev(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
+                                uint32_t n_ranks, float *xsend, qkm_sel *selsend,
+                                uint32_t *counts_dev);
 QKM_API int qkm_ep_shared(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens);
 QKM_API int qkm_ep_expert_forward(qkm_ctx *c, uint32_t layer, const float *xrecv,
                                   const qkm_sel *selrecv, uint32_t n_recv, float *partial);

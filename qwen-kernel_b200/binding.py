@@ -82,6 +82,7 @@ SIGNATURES = {
     "qkm_sel_device": (_VP, [_VP]),
     "qkm_h_device": (_VP, [_VP]),
     "qkm_ep_dispatch": (_I, [_VP, _U32, _VP, _U32, _U32, _VP, _VP, _VP]),
+    "qkm_ep_dispatch_dev": (_I, [_VP, _U32, _VP, _U32, _U32, _VP, _VP, _VP]),
     "qkm_ep_shared": (_I, [_VP, _U32, _VP, _U32]),
     "qkm_ep_expert_forward": (_I, [_VP, _U32, _VP, _VP, _U32, _VP]),
     "qkm_ep_combine": (_I, [_VP, _U32, _U32, _VP, _VP]),
@@ -285,6 +286,10 @@ class Context:
         counts = (C.c_uint32 * n_ranks)()
         self.check(self.lib.qkm_ep_dispatch(self.h, layer_idx, _p(x), n, n_ranks, _p(xsend), _p(selsend), counts))
         return list(counts)
+
+    def ep_dispatch_dev(self, layer_idx, x, n, n_ranks, xsend, selsend, counts_dev):
+        """Asynchronous form: counts_dev is a device int32 tensor of n_ranks entries."""
+        self.check(self.lib.qkm_ep_dispatch_dev(self.h, layer_idx, _p(x), n, n_ranks, _p(xsend), _p(selsend), _p(counts_dev)))
 
     def ep_shared(self, layer_idx, x, n):
         self.check(self.lib.qkm_ep_shared(self.h, layer_idx, _p(x), n))

@@ -825,10 +825,10 @@ static int ep_check(qkm_ctx* c, uint32_t n_ranks) {
     return QKM_OK;
 }
 
-extern "C" QKM_API int qkm_ep_dispatch(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t n_ranks,
-                                       float* xsend, qkm_sel* selsend, uint32_t* counts_host) {
+static int ep_dispatch_launch(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t n_ranks,
+                              float* xsend, qkm_sel* selsend) {
     if (int rc = layer_ready(c, layer)) return rc;
-    if (!x || !xsend || !selsend || !counts_host) return QKM_ERR_ARG;
+    if (!x || !xsend || !selsend) return QKM_ERR_ARG;
     if (int rc = check_tokens(c, n)) return rc;
     if (int rc = ep_check(c, n_ranks)) return rc;
     const qkm_layer_dev& ld = c->layers[layer];
@@ -846,9 +846,26 @@ extern "C" QKM_API int qkm_ep_dispatch(qkm_ctx* c, uint32_t layer, const float* 
     QKM_LAUNCH(c, launch_ep_plan(c->L(), d, c->sel, n, n_ranks, c->ep_counts, c->ep_send_tok, c->ep_send_pos));
     const uint32_t fan = n_ranks < d.n_used ? n_ranks : d.n_used;
     QKM_LAUNCH(c, launch_ep_pack(c->L(), d, x, c->sel, c->ep_send_tok, c->ep_counts + n_ranks, n * fan, xsend, selsend));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_dispatch(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t n_ranks,
+                                       float* xsend, qkm_sel* selsend, uint32_t* counts_host) {
+    if (!counts_host) return QKM_ERR_ARG;
+    if (int rc = ep_dispatch_launch(c, layer, x, n, n_ranks, xsend, selsend)) return rc;
     QKM_CUDA(c, cudaMemcpyAsync(c->ep_counts_host, c->ep_counts, (n_ranks + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost, c->stream));
     QKM_CUDA(c, cudaStreamSynchronize(c->stream));
     memcpy(counts_host, c->ep_counts_host, n_ranks * sizeof(uint32_t));
+    return QKM_OK;
+}
+
+// The same without touching the host: the row counts go to a device buffer of the caller
+// (n_ranks 32-bit words), so they can feed the collective that exchanges them directly.
+extern "C" QKM_API int qkm_ep_dispatch_dev(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t n_ranks,
+                                           float* xsend, qkm_sel* selsend, uint32_t* counts_dev) {
+    if (!counts_dev) return QKM_ERR_ARG;
+    if (int rc = ep_dispatch_launch(c, layer, x, n, n_ranks, xsend, selsend)) return rc;
+    QKM_CUDA(c, cudaMemcpyAsync(counts_dev, c->ep_counts, n_ranks * sizeof(uint32_t), cudaMemcpyDeviceToDevice, c->stream));
     return QKM_OK;
 }
 

@@ -46,8 +46,7 @@ class ExpertParallel:
         self.xrecv = torch.empty((max_recv_rows, n_embd), dtype=f32, device=device)
         self.selrecv = torch.empty((max_recv_rows, SEL_BYTES), dtype=u8, device=device)
         self.partial = torch.empty((max_recv_rows, n_embd), dtype=f32, device=device)
-        self.counts_dev = torch.empty(self.world, dtype=torch.int64, device=device)
-        self.rcounts_dev = torch.empty(self.world, dtype=torch.int64, device=device)
+        self.counts_dev = torch.zeros(2 * self.world, dtype=torch.int32, device=device)   # sent | received
         self.last_counts = None
 
     def forward(self, layer: int, x: torch.Tensor, n: int, y: torch.Tensor) -> None:
@@ -55,11 +54,11 @@ class ExpertParallel:
         if n > self.max_local:
             raise ValueError(f"{n} local tokens exceed the {self.max_local} this object was sized for")
         eng, W = self.engine, self.world
-        send = eng.ep_dispatch(layer, x, n, W, self.xsend, self.selsend)
-        # how many rows each peer sends here
-        self.counts_dev.copy_(torch.tensor(send, dtype=torch.int64), non_blocking=False)
-        dist.all_to_all_single(self.rcounts_dev, self.counts_dev, group=self.group)
-        recv = [int(v) for v in self.rcounts_dev.tolist()]
+        # rows per destination stay on the device, are exchanged, and come to the host once
+        eng.ep_dispatch_dev(layer, x, n, W, self.xsend, self.selsend, self.counts_dev[:W])
+        dist.all_to_all_single(self.counts_dev[W:], self.counts_dev[:W], group=self.group)
+        both = [int(v) for v in self.counts_dev.tolist()]
+        send, recv = both[:W], both[W:]
         n_send, n_recv = sum(send), sum(recv)
         if n_recv > self.max_recv:
             raise RuntimeError(f"rank {self.rank}: {n_recv} rows arrive but buffers hold {self.max_recv}")

@@ -41,6 +41,10 @@ class OracleEngine:
         selsend.numpy()[:k] = self.sel[send_tok].view(np.uint8).reshape(k, 160)
         return counts
 
+    def ep_dispatch_dev(self, layer, x, n, n_ranks, xsend, selsend, counts_dev):
+        counts = self.ep_dispatch(layer, x, n, n_ranks, xsend, selsend)
+        counts_dev.numpy()[:] = np.asarray(counts, np.int32)
+
     def ep_shared(self, layer, x, n):
         # shared expert only: a selection whose experts all live outside the one-expert slice
         d = self.dims

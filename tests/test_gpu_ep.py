@@ -44,6 +44,11 @@ def run_ep(pkg, orc, syn, dims, layer, x_parts, G, tol):
         ss = d_ss.download(np.uint8, (k, 160)) if k else np.zeros((0, 160), np.uint8)
         assert np.array_equal(xs, xp[send_tok])
         assert np.array_equal(ss.reshape(-1).view(SEL_DTYPE)["ids"], sel["ids"][send_tok])
+        # the asynchronous form leaves the same counts in device memory
+        d_cnt = c.alloc(4 * G)
+        c.ep_dispatch_dev(0, d_x, n, G, d_xs, d_ss, d_cnt)
+        assert d_cnt.download(np.uint32, G).tolist() == counts
+        d_cnt.free()
         c.ep_shared(0, d_x, n)
         st.append(dict(n=n, d_x=d_x, counts=counts, xs=xs, ss=ss, bufs=[d_x, d_xs, d_ss]))
     # phase 2: "all-to-all" on the host, expert forward on every rank
