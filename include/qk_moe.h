@@ -137,6 +137,8 @@ QKM_API uint32_t qkm_n_expert(const qkm_ctx *c);
 QKM_API uint32_t qkm_n_used(const qkm_ctx *c);
 QKM_API uint32_t qkm_n_layer(const qkm_ctx *c);
 QKM_API uint32_t qkm_max_tokens(const qkm_ctx *c);
+/* resident experts [first, first + count) of this context (all of them when unsharded) */
+QKM_API void     qkm_expert_range(const qkm_ctx *c, uint32_t *first, uint32_t *count);
 /* bytes per row of ne0 elements of a ggml type, 0 if unsupported
  * (ggmlRowBytes, src/gguf.h:36-46) */
 QKM_API size_t   qkm_row_bytes(uint32_t type, uint64_t ne0);
@@ -248,6 +250,46 @@ QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 /* Device address of the context's selection / h scratch of the last fused call. */
 QKM_API const qkm_sel *qkm_sel_device(const qkm_ctx *c);
 QKM_API const float   *qkm_h_device(const qkm_ctx *c);
+
+/* ---- GGUF files (src/gguf.h:54-198; tensor set and checks of loadMoeT, src/main.cpp:1265-1308)
+ * Read-only, memory-mapped; a split model is opened by its first shard
+ * ("<prefix>-00001-of-000NN.gguf").  Every length in the file is bounds-checked; failures
+ * return NULL / a negative code with a message, they never abort. */
+typedef struct qkm_gguf qkm_gguf;
+QKM_API qkm_gguf *qkm_gguf_open(const char *path, char *err, size_t err_len);
+QKM_API void      qkm_gguf_close(qkm_gguf *g);
+QKM_API const char *qkm_gguf_last_error(const qkm_gguf *g);
+QKM_API uint64_t  qkm_gguf_tensor_count(const qkm_gguf *g);
+/* tensor by name: ggml type, ne[4], pointer into the mapping, bytes left in its shard */
+QKM_API int qkm_gguf_find(const qkm_gguf *g, const char *name, uint32_t *type, uint64_t ne[4],
+                          const void **data, uint64_t *nbytes);
+QKM_API uint64_t qkm_gguf_kv_u64(const qkm_gguf *g, const char *key, uint64_t def);
+QKM_API int qkm_gguf_kv_str(const qkm_gguf *g, const char *key, char *out, size_t out_len);
+/* the eight blk.<layer>.ffn_* tensors, validated: dims for qkm_open, host pointers for
+ * qkm_upload_layer */
+QKM_API int qkm_gguf_moe_layer(qkm_gguf *g, uint32_t layer, qkm_dims *dims, qkm_layer_weights *w);
+/* file layer -> context layer; a sharded context takes its slice of the expert tensors */
+QKM_API int qkm_upload_layer_gguf(qkm_ctx *c, uint32_t layer, qkm_gguf *g, uint32_t file_layer);
+
+/* ---- layer entry / tail around the MoE block ------------------------------------------
+ * add_rmsnorm.comp:22-40: y = a + b, xn = y * w / sqrt(mean(y^2) + eps); rows of n f32. */
+QKM_API int qkm_add_rmsnorm(qkm_ctx *c, const float *a, const float *b, const float *w, float *y,
+                            float *xn, uint32_t n_rows, uint32_t n, float eps);
+/* add_rms3.comp:23-41: s = a + b + c2 (residual + routed + shared), xn = rmsnorm(s) * w */
+QKM_API int qkm_add_rms3(qkm_ctx *c, const float *a, const float *b, const float *c2, const float *w,
+                         float *s, float *xn, uint32_t n_rows, uint32_t n, float eps);
+/* add_rms3_grouped.comp:22-50: the routed stream as contrib [row][n_used][n], folded in
+ * slot order before the shared stream is added */
+QKM_API int qkm_add_rms3_grouped(qkm_ctx *c, const float *a, const float *routed, const float *c2,
+                                 const float *w, float *s, float *xn, uint32_t n_rows, uint32_t n,
+                                 uint32_t n_used, float eps);
+/* The feed-forward half of a decoder layer as the engine sequences it (src/main.cpp:4375-4404:
+ * add_rmsnorm, the MoE dispatches, add_rms3): resid_out = resid + attn_out + MoE(rmsnorm(resid +
+ * attn_out) * w_post); xn_next = rmsnorm(resid_out) * w_next.  resid_out may alias resid.
+ * n_tokens <= 64 takes the decode kernels, more the tensor-core path. */
+QKM_API int qkm_moe_layer_step(qkm_ctx *c, uint32_t layer, const float *resid, const float *attn_out,
+                               const float *w_post, const float *w_next, uint32_t n_tokens, float eps,
+                               float *resid_out, float *xn_next);
 
 /* ---- expert parallel (one context per GPU; no counterpart in the reference, which is
  * single-GPU: the arithmetic per (token, expert) is that of src/main.cpp:1351-1369) -------

@@ -175,6 +175,22 @@ class Oracle:
         return out
 
 
+def _add_rms(self, mode, a, b, c2, w, n_used=0, eps=1e-6):
+    a = np.ascontiguousarray(a, np.float32)
+    n_rows, n = a.shape
+    s, xn = np.empty_like(a), np.empty_like(a)
+    b = np.ascontiguousarray(b, np.float32)
+    c2 = None if c2 is None else np.ascontiguousarray(c2, np.float32)
+    w = np.ascontiguousarray(w, np.float32)
+    self.lib.orc_add_rms.argtypes = [C.c_int] + [C.c_void_p] * 6 + [C.c_uint32] * 3 + [C.c_float]
+    rc = self.lib.orc_add_rms(mode, _ptr(a), _ptr(b), _ptr(c2), _ptr(w), _ptr(s), _ptr(xn), n_rows, n, n_used, eps)
+    assert rc == 0
+    return s, xn
+
+
+Oracle.add_rms = _add_rms
+
+
 class Reference:
     """The reference's own src/quants.h functions (oracle/_ref/libqk_ref.so)."""
 

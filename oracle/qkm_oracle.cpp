@@ -469,3 +469,32 @@ ORC_API int orc_moe_layer(const qkm_dims* d, const qkm_layer_weights* L, const f
 }
 
 ORC_API int orc_hardware_threads(void) { return (int)std::thread::hardware_concurrency(); }
+
+// ---- residual adds + RMS norm (layer entry / tail) ------------------------------------------
+// shaders/add_rmsnorm.comp:22-40, add_rms3.comp:23-41, add_rms3_grouped.comp:22-50; the CPU
+// check of the reference accumulates the mean of squares in double (src/main.cpp:1688).
+// mode 0: s = a + b; 1: s = (a + b) + c2; 2: s = (a + sum_k routed[row][k][:]) + c2.
+// The sums are f32 in the shaders' order of additions; xn = s * scale * w with
+// scale = 1 / sqrt(mean(s^2) + eps), mean in double.
+ORC_API int orc_add_rms(int mode, const float* a, const float* b, const float* c2, const float* w, float* s,
+                        float* xn, uint32_t n_rows, uint32_t n, uint32_t n_used, float eps) {
+    for (uint32_t r = 0; r < n_rows; ++r) {
+        double ss = 0.0;
+        for (uint32_t i = 0; i < n; ++i) {
+            float v = a[(size_t)r * n + i];
+            if (mode == 2) {
+                float acc = 0.f;
+                for (uint32_t k = 0; k < n_used; ++k) acc += b[((size_t)r * n_used + k) * n + i];
+                v += acc;
+            } else {
+                v += b[(size_t)r * n + i];
+            }
+            if (mode >= 1) v += c2[(size_t)r * n + i];
+            s[(size_t)r * n + i] = v;
+            ss += (double)v * (double)v;
+        }
+        const double scale = 1.0 / std::sqrt(ss / (double)n + (double)eps);
+        for (uint32_t i = 0; i < n; ++i) xn[(size_t)r * n + i] = (float)((double)s[(size_t)r * n + i] * scale * (double)w[i]);
+    }
+    return 0;
+}

@@ -81,6 +81,20 @@ SIGNATURES = {
     "qkm_last_sel": (_I, [_VP, _VP, _U32]),
     "qkm_sel_device": (_VP, [_VP]),
     "qkm_h_device": (_VP, [_VP]),
+    "qkm_expert_range": (None, [_VP, C.POINTER(_U32), C.POINTER(_U32)]),
+    "qkm_gguf_open": (_VP, [C.c_char_p, C.c_char_p, _SZ]),
+    "qkm_gguf_close": (None, [_VP]),
+    "qkm_gguf_last_error": (C.c_char_p, [_VP]),
+    "qkm_gguf_tensor_count": (_U64, [_VP]),
+    "qkm_gguf_find": (_I, [_VP, C.c_char_p, C.POINTER(_U32), C.POINTER(_U64), C.POINTER(_VP), C.POINTER(_U64)]),
+    "qkm_gguf_kv_u64": (_U64, [_VP, C.c_char_p, _U64]),
+    "qkm_gguf_kv_str": (_I, [_VP, C.c_char_p, C.c_char_p, _SZ]),
+    "qkm_gguf_moe_layer": (_I, [_VP, _U32, C.POINTER(Dims), C.POINTER(LayerWeights)]),
+    "qkm_upload_layer_gguf": (_I, [_VP, _U32, _VP, _U32]),
+    "qkm_add_rmsnorm": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, C.c_float]),
+    "qkm_add_rms3": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, C.c_float]),
+    "qkm_add_rms3_grouped": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, _U32, C.c_float]),
+    "qkm_moe_layer_step": (_I, [_VP, _U32, _VP, _VP, _VP, _VP, _U32, C.c_float, _VP, _VP]),
     "qkm_ep_dispatch": (_I, [_VP, _U32, _VP, _U32, _U32, _VP, _VP, _VP]),
     "qkm_ep_dispatch_dev": (_I, [_VP, _U32, _VP, _U32, _U32, _VP, _VP, _VP]),
     "qkm_ep_shared": (_I, [_VP, _U32, _VP, _U32]),
@@ -279,6 +293,20 @@ class Context:
         y = np.empty_like(x)
         self.check(self.lib.qkm_moe_forward_host(self.h, layer_idx, mode, x.ctypes.data, x.shape[0], y.ctypes.data))
         return y
+
+    # -- layer entry / tail
+    def add_rmsnorm(self, a, b, w, y, xn, n_rows, n, eps=1e-6):
+        self.check(self.lib.qkm_add_rmsnorm(self.h, _p(a), _p(b), _p(w), _p(y), _p(xn), n_rows, n, eps))
+
+    def add_rms3(self, a, b, c2, w, s, xn, n_rows, n, eps=1e-6):
+        self.check(self.lib.qkm_add_rms3(self.h, _p(a), _p(b), _p(c2), _p(w), _p(s), _p(xn), n_rows, n, eps))
+
+    def add_rms3_grouped(self, a, routed, c2, w, s, xn, n_rows, n, n_used, eps=1e-6):
+        self.check(self.lib.qkm_add_rms3_grouped(self.h, _p(a), _p(routed), _p(c2), _p(w), _p(s), _p(xn), n_rows, n, n_used, eps))
+
+    def moe_layer_step(self, layer_idx, resid, attn_out, w_post, w_next, n, resid_out, xn_next, eps=1e-6):
+        self.check(self.lib.qkm_moe_layer_step(self.h, layer_idx, _p(resid), _p(attn_out), _p(w_post), _p(w_next), n, eps,
+                                               _p(resid_out), _p(xn_next)))
 
     # -- expert parallel (this context is one shard; see include/qk_moe.h)
     def ep_dispatch(self, layer_idx, x, n, n_ranks, xsend, selsend) -> list:

@@ -300,6 +300,10 @@ extern "C" QKM_API uint32_t qkm_n_expert(const qkm_ctx* c) { return c ? c->cfg.d
 extern "C" QKM_API uint32_t qkm_n_used(const qkm_ctx* c) { return c ? c->cfg.dims.n_used : 0; }
 extern "C" QKM_API uint32_t qkm_n_layer(const qkm_ctx* c) { return c ? c->cfg.n_layer : 0; }
 extern "C" QKM_API uint32_t qkm_max_tokens(const qkm_ctx* c) { return c ? c->cfg.max_tokens : 0; }
+extern "C" QKM_API void qkm_expert_range(const qkm_ctx* c, uint32_t* first, uint32_t* count) {
+    if (first) *first = c ? c->efirst : 0;
+    if (count) *count = c ? c->ecount : 0;
+}
 extern "C" QKM_API size_t qkm_row_bytes(uint32_t type, uint64_t ne0) {
     const uint32_t be = block_elems(type);
     if (be == 0 || ne0 % be) return 0;
@@ -794,6 +798,50 @@ extern "C" QKM_API int qkm_last_sel(qkm_ctx* c, qkm_sel* sel_host, uint32_t n) {
 }
 extern "C" QKM_API const qkm_sel* qkm_sel_device(const qkm_ctx* c) { return c ? c->sel : nullptr; }
 extern "C" QKM_API const float* qkm_h_device(const qkm_ctx* c) { return c ? c->h : nullptr; }
+
+// ---------------------------------------------------------------- layer entry / tail
+
+extern "C" QKM_API int qkm_add_rmsnorm(qkm_ctx* c, const float* a, const float* b, const float* w, float* y, float* xn,
+                                       uint32_t n_rows, uint32_t n, float eps) {
+    if (!c || !a || !b || !w || !y || !xn) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_add_rms(c->L(), 0, a, b, nullptr, w, y, xn, n_rows, n, 0, eps));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_add_rms3(qkm_ctx* c, const float* a, const float* b, const float* c2, const float* w,
+                                    float* s, float* xn, uint32_t n_rows, uint32_t n, float eps) {
+    if (!c || !a || !b || !c2 || !w || !s || !xn) return QKM_ERR_ARG;
+    QKM_LAUNCH(c, launch_add_rms(c->L(), 1, a, b, c2, w, s, xn, n_rows, n, 0, eps));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_add_rms3_grouped(qkm_ctx* c, const float* a, const float* routed, const float* c2,
+                                            const float* w, float* s, float* xn, uint32_t n_rows, uint32_t n,
+                                            uint32_t n_used, float eps) {
+    if (!c || !a || !routed || !c2 || !w || !s || !xn) return QKM_ERR_ARG;
+    if (n_used == 0 || n_used > 16) return fail(c, QKM_ERR_ARG, "qkm_add_rms3_grouped: n_used %u", n_used);
+    QKM_LAUNCH(c, launch_add_rms(c->L(), 2, a, routed, c2, w, s, xn, n_rows, n, n_used, eps));
+    return QKM_OK;
+}
+
+// One decoder layer's feed-forward half as the engine runs it (src/main.cpp:4375-4404):
+// resid2 = resid + attn_out, xn2 = rmsnorm(resid2) * w_post; y = MoE(xn2);
+// resid_out = resid2 + y, xn_next = rmsnorm(resid_out) * w_next.
+extern "C" QKM_API int qkm_moe_layer_step(qkm_ctx* c, uint32_t layer, const float* resid, const float* attn_out,
+                                          const float* w_post, const float* w_next, uint32_t n, float eps,
+                                          float* resid_out, float* xn_next) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (!resid || !attn_out || !w_post || !w_next || !resid_out || !xn_next) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    const qkm_dims& d = c->cfg.dims;
+    // x_stage / y_stage double as resid2 / MoE output scratch ([max_tokens][n_embd] each)
+    float* xn2 = c->x_stage;
+    QKM_LAUNCH(c, launch_add_rms(c->L(), 0, resid, attn_out, nullptr, w_post, resid_out, xn2, n, d.n_embd, 0, eps));
+    const int rc = n <= 64 ? qkm_moe_decode(c, layer, xn2, n, c->y_stage) : qkm_moe_prefill(c, layer, xn2, n, c->y_stage);
+    if (rc) return rc;
+    QKM_LAUNCH(c, launch_add_rms(c->L(), 0, resid_out, c->y_stage, nullptr, w_next, resid_out, xn_next, n, d.n_embd, 0, eps));
+    return QKM_OK;
+}
 
 // ---------------------------------------------------------------- expert parallel
 // One context per GPU, opened with expert_first/expert_count naming its shard.  Per layer:

@@ -169,6 +169,12 @@ cudaError_t launch_shared_down(const Launch& L, const qkm_dims& d, const void* d
 cudaError_t launch_fold_contrib(const Launch& L, const qkm_dims& d, const float* contrib, const float* y2,
                                 float* y, uint32_t n_tokens);
 
+// ---- residual adds fused with the RMS norm (qkm_tail.cu) ---------------------------------------
+// mode 0: s = a + b; 1: s = a + b + c2; 2: s = a + sum_k b[row][k][:] + c2 (b = per-slot contributions).
+// xn = s * w / sqrt(mean(s^2) + eps).
+cudaError_t launch_add_rms(const Launch& L, int mode, const float* a, const float* b, const float* c2, const float* w,
+                           float* s, float* xn, uint32_t n_rows, uint32_t n, uint32_t n_used, float eps);
+
 // ---- expert-parallel exchange helpers (qkm_ep.cu) --------------------------------------------
 // counts[0..n_ranks) rows per destination rank and counts[n_ranks] their sum; send_tok the
 // tokens in send order; send_pos[t][r] the row of token t among the rows sent (to rank r).

@@ -165,3 +165,21 @@ def test_gemv_oracle(orc, syn):
         np.testing.assert_allclose(y, want, rtol=1e-6, atol=1e-6 * np.abs(want).max())
         y32 = orc.gemv(ttype, W, x, M, K, acc=1, threads=3)
         assert syn.rel_err_rows(y32, y) < 1e-5
+
+
+def test_add_rms_oracle_matches_numpy(orc, syn):
+    """Layer entry / tail arithmetic (add_rmsnorm.comp, add_rms3.comp, add_rms3_grouped.comp)."""
+    n_rows, n, n_used = 4, 512, 3
+    a, c2 = syn.random_x(n_rows, n, 1), syn.random_x(n_rows, n, 2)
+    b3 = syn.random_x(n_rows * n_used, n, 3)
+    w = 1.0 + 0.1 * syn.random_x(1, n, 4).reshape(-1)
+    routed = b3.reshape(n_rows, n_used, n)
+    for mode, b, want_s in (
+        (0, b3[:n_rows], a + b3[:n_rows]),
+        (1, b3[:n_rows], (a + b3[:n_rows]) + c2),
+        (2, b3, (a + ((routed[:, 0] + routed[:, 1]) + routed[:, 2])) + c2),
+    ):
+        s, xn = orc.add_rms(mode, a, b, c2 if mode else None, w, n_used)
+        assert np.array_equal(s, want_s.astype(np.float32))
+        scale = 1.0 / np.sqrt((s.astype(np.float64) ** 2).mean(axis=1, keepdims=True) + 1e-6)
+        np.testing.assert_allclose(xn, (s * scale * w).astype(np.float32), rtol=1e-6)
