@@ -3,7 +3,7 @@
 // Some hosts hand a library a fixed set of device buffers and forbid anything that takes
 // memory from the driver while they run: an inference server that has already given all
 // free HBM to its own pool allocator, a real-time loop in which an allocation (which can
-// synchronise the whole device) would break its latency budget, or a plugin running inside
+// synchronise the whole device) would break its latency bound, or a plugin running inside
 // a process whose memory is accounted by someone else.  The context-based entry points
 // allocate their scratch when the context is opened.  This one needs no context and takes
 // no memory from the driver at all: its scratch is an array that is part of the library
