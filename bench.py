@@ -428,6 +428,8 @@ def run_gemv_sweep(args, pkg, syn, torch, R: Ranks, orc, peaks):
     torch.cuda.set_stream(stream)
     cases = [(t, m, k) for (m, k) in GEMV_SHAPES for t in (syn.Q8_0, syn.Q6_K, syn.IQ4_XS, syn.IQ3_XXS, syn.F16)]
     cases.append((syn.Q6_K, 151936, 2048))
+    # the reference quotes its GEMV bandwidths on matrices of 96 MB and more: the same per format
+    cases += [(t, 65536, 2048) for t in (syn.Q8_0, syn.Q6_K, syn.IQ4_XS, syn.IQ3_XXS, syn.F16)]
     names = {syn.Q8_0: "q8_0", syn.Q6_K: "q6_k", syn.IQ4_XS: "iq4_xs", syn.IQ3_XXS: "iq3_xxs", syn.F16: "f16"}
     out = {}
     for t, M, K in cases:

@@ -303,15 +303,16 @@ static cudaError_t gemv_stream_launch(const Launch& L, const uint8_t* W, const f
     // a tile must start and end on 16-byte boundaries: whole multiples of `gran` rows
     uint32_t gran = 1;
     while ((gran * rb) % 16) gran *= 2;
-    uint32_t rows_per_tile = (uint32_t)(gv::kStageBytes / rb) / gran * gran;
-    if (rows_per_tile == 0 || ((uintptr_t)W & 15u) || ((uintptr_t)x & 15u) || (size_t)n * K * 4 > 64 * 1024) return cudaSuccess;
-    if (rows_per_tile > 64) rows_per_tile = 64 / gran * gran;
-    if (rows_per_tile > 8 && gran <= 8) rows_per_tile &= ~7u;   // whole rounds of the eight warps
-    // small matrices: shorter tiles so that every SM gets a few
-    const uint32_t floor_rows = gran > 8 ? gran : 8 / gran * gran;
-    while (rows_per_tile > floor_rows && M / rows_per_tile < 4 * n_sms) rows_per_tile = (rows_per_tile / 2) / gran * gran;
-    if (rows_per_tile < floor_rows) rows_per_tile = floor_rows;
-    if ((size_t)rows_per_tile * rb > gv::kStageBytes) return cudaSuccess;
+    // whole rounds of the eight warps, about 20 KB per stage so that three blocks share an SM;
+    // wide rows take one round per tile even when that is more
+    uint32_t round = gran > 8 ? gran : 8;
+    if ((size_t)round * rb > gv::kStageBytes) round = gran;          // very wide rows: fewer than eight per tile
+    if (((uintptr_t)W & 15u) || ((uintptr_t)x & 15u) || (size_t)n * K * 4 > 64 * 1024 || (size_t)round * rb > gv::kStageBytes)
+        return cudaSuccess;
+    uint32_t rows_per_tile = (uint32_t)(20 * 1024 / rb) / round * round;
+    if (rows_per_tile < round) rows_per_tile = round;
+    if (rows_per_tile > 64) rows_per_tile = 64 / round * round;
+    (void)n_sms;
     const uint32_t n_tiles = M / rows_per_tile;
     if (n_tiles == 0) return cudaSuccess;
     const uint32_t stage_bytes = (uint32_t)((rows_per_tile * rb + 127) / 128 * 128);
