@@ -251,6 +251,15 @@ QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 QKM_API const qkm_sel *qkm_sel_device(const qkm_ctx *c);
 QKM_API const float   *qkm_h_device(const qkm_ctx *c);
 
+/* ---- dense quantised GEMM (gemm_q8_0*.comp, gemm_iq4_xs.comp; src/main.cpp:4806-4835) -----
+ * Y[n][M] = X[n][K] . W^T for a Q8_0 or IQ4_XS matrix W [M][K] (ggml rows), M % 128 == 0,
+ * K % 256 == 0.  qkm_dense_upload copies W (host pointer) into one of 16 slots; qkm_dense_gemm
+ * takes device x [n][K] / y [n][M] f32 and runs on the tensor cores with bf16 operands
+ * (the prefill tolerance applies).  Scratch grows to the largest n seen. */
+QKM_API int qkm_dense_upload(qkm_ctx *c, uint32_t slot, uint32_t type, const void *w_host,
+                             uint32_t M, uint32_t K);
+QKM_API int qkm_dense_gemm(qkm_ctx *c, uint32_t slot, const float *x, uint32_t n, float *y);
+
 /* ---- GGUF files (src/gguf.h:54-198; tensor set and checks of loadMoeT, src/main.cpp:1265-1308)
  * Read-only, memory-mapped; a split model is opened by its first shard
  * ("<prefix>-00001-of-000NN.gguf").  Every length in the file is bounds-checked; failures

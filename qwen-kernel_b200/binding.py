@@ -91,6 +91,8 @@ SIGNATURES = {
     "qkm_gguf_kv_str": (_I, [_VP, C.c_char_p, C.c_char_p, _SZ]),
     "qkm_gguf_moe_layer": (_I, [_VP, _U32, C.POINTER(Dims), C.POINTER(LayerWeights)]),
     "qkm_upload_layer_gguf": (_I, [_VP, _U32, _VP, _U32]),
+    "qkm_dense_upload": (_I, [_VP, _U32, _U32, _VP, _U32, _U32]),
+    "qkm_dense_gemm": (_I, [_VP, _U32, _VP, _U32, _VP]),
     "qkm_add_rmsnorm": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, C.c_float]),
     "qkm_add_rms3": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, C.c_float]),
     "qkm_add_rms3_grouped": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, _U32, C.c_float]),
@@ -293,6 +295,14 @@ class Context:
         y = np.empty_like(x)
         self.check(self.lib.qkm_moe_forward_host(self.h, layer_idx, mode, x.ctypes.data, x.shape[0], y.ctypes.data))
         return y
+
+    # -- dense quantised GEMM
+    def dense_upload(self, slot, ttype, W: np.ndarray, M, K):
+        W = np.ascontiguousarray(W)
+        self.check(self.lib.qkm_dense_upload(self.h, slot, ttype, W.ctypes.data, M, K))
+
+    def dense_gemm(self, slot, x, n, y):
+        self.check(self.lib.qkm_dense_gemm(self.h, slot, _p(x), n, _p(y)))
 
     # -- layer entry / tail
     def add_rmsnorm(self, a, b, w, y, xn, n_rows, n, eps=1e-6):

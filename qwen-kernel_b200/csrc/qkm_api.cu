@@ -71,6 +71,12 @@ struct qkm_ctx {
     MmaItem* mma_items[4] = {nullptr, nullptr, nullptr, nullptr};  // gate/up, down, shared gate/up, shared down
     uint32_t* pos_of = nullptr;       // [max_tokens*(n_used+1)]
     uint32_t* group_hist = nullptr;   // scratch of the multi-block grouping
+    // dense matrices for qkm_dense_gemm (tile-ordered copies) and its scratch, sized on demand
+    static constexpr int kDenseSlots = 16;
+    struct Dense { uint32_t type = 0, M = 0, K = 0; void* tiles = nullptr; } dense[kDenseSlots];
+    void* dense_xb = nullptr; uint32_t* dense_pairs = nullptr; qkm_sel* dense_sel = nullptr; MmaItem* dense_items = nullptr;
+    uint32_t* dense_n_items = nullptr;
+    size_t dense_cap_elems = 0, dense_cap_rows = 0, dense_cap_items = 0;
     // expert-parallel exchange plan of the last qkm_ep_dispatch, allocated on first use
     uint32_t ep_ranks = 0;
     uint32_t* ep_counts = nullptr;       // [n_ranks + 1] rows per destination rank, then their sum
@@ -276,7 +282,8 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
         for (void* p : l.allocs) if (p) cudaFree(p);
         for (void* p : l.tiles) if (p) cudaFree(p);
     }
-    void* scratch[] = {c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
+    for (auto& dm : c->dense) if (dm.tiles) cudaFree(dm.tiles);
+    void* scratch[] = {c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
@@ -798,6 +805,69 @@ extern "C" QKM_API int qkm_last_sel(qkm_ctx* c, qkm_sel* sel_host, uint32_t n) {
 }
 extern "C" QKM_API const qkm_sel* qkm_sel_device(const qkm_ctx* c) { return c ? c->sel : nullptr; }
 extern "C" QKM_API const float* qkm_h_device(const qkm_ctx* c) { return c ? c->h : nullptr; }
+
+// ---------------------------------------------------------------- dense quantised GEMM
+// The reference's batched-prefill projections (gemm_q8_0*.comp, gemm_iq4_xs.comp; dispatched at
+// src/main.cpp:4806-4835): Y[n][M] = X[n][K] . W^T with W a Q8_0 or IQ4_XS matrix.  The matrix is
+// uploaded once into a slot (copied and tile-ordered on the device); the GEMM runs on the same
+// dequantise-to-shared-memory + tcgen05 pipeline as the experts' down projection, bf16 operands.
+
+extern "C" QKM_API int qkm_dense_upload(qkm_ctx* c, uint32_t slot, uint32_t type, const void* w_host, uint32_t M, uint32_t K) {
+    if (!c || !w_host) return QKM_ERR_ARG;
+    if (slot >= qkm_ctx::kDenseSlots) return fail(c, QKM_ERR_BOUNDS, "dense slot %u out of range", slot);
+    if (type != QKM_TYPE_Q8_0 && type != QKM_TYPE_IQ4_XS) return fail(c, QKM_ERR_TYPE, "qkm_dense_upload: type %u (Q8_0 or IQ4_XS)", type);
+    if (M == 0 || M % 128 || K == 0 || K % 256) return fail(c, QKM_ERR_ARG, "qkm_dense_upload: M %% 128 and K %% 256 must be 0 (M=%u K=%u)", M, K);
+    auto& dm = c->dense[slot];
+    if (dm.tiles) { QKM_CUDA(c, cudaFree(dm.tiles)); dm = qkm_ctx::Dense{}; }
+    const size_t bytes = (size_t)M * row_bytes(type, K);
+    void* raw = nullptr;
+    QKM_CUDA(c, cudaMalloc(&raw, bytes + 256));
+    cudaError_t e = cudaMalloc(&dm.tiles, bytes + 256);
+    if (e == cudaSuccess) e = cudaMemcpyAsync(raw, w_host, bytes, cudaMemcpyHostToDevice, c->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync((uint8_t*)dm.tiles + bytes, 0, 256, c->stream);
+    if (e == cudaSuccess) e = launch_repack(c->L(), type, raw, dm.tiles, 1, M, K);
+    if (e == cudaSuccess) e = cudaStreamSynchronize(c->stream);
+    cudaFree(raw);
+    if (e != cudaSuccess) {
+        if (dm.tiles) cudaFree(dm.tiles);
+        dm = qkm_ctx::Dense{};
+        return fail(c, QKM_ERR_CUDA, "qkm_dense_upload: %s", cudaGetErrorString(e));
+    }
+    dm.type = type; dm.M = M; dm.K = K;
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_dense_gemm(qkm_ctx* c, uint32_t slot, const float* x, uint32_t n, float* y) {
+    if (!c || !x || !y) return QKM_ERR_ARG;
+    if (slot >= qkm_ctx::kDenseSlots || !c->dense[slot].tiles) return fail(c, QKM_ERR_BUSY, "dense slot %u holds no matrix", slot);
+    if (n == 0) return QKM_OK;
+    const auto& dm = c->dense[slot];
+    const uint32_t NT = prefill_pairs_per_block();
+    const size_t elems = (size_t)n * dm.K, items = (size_t)((n + NT - 1) / NT) * (dm.M / 128);
+    if (elems > c->dense_cap_elems) {
+        if (c->dense_xb) QKM_CUDA(c, cudaFree(c->dense_xb));
+        c->dense_xb = nullptr; c->dense_cap_elems = 0;
+        QKM_CUDA(c, cudaMalloc(&c->dense_xb, elems * 2));
+        c->dense_cap_elems = elems;
+    }
+    if (n > c->dense_cap_rows) {
+        if (c->dense_pairs) { cudaFree(c->dense_pairs); cudaFree(c->dense_sel); }
+        c->dense_pairs = nullptr; c->dense_sel = nullptr; c->dense_cap_rows = 0;
+        QKM_CUDA(c, cudaMalloc((void**)&c->dense_pairs, (size_t)n * sizeof(uint32_t)));
+        QKM_CUDA(c, cudaMalloc((void**)&c->dense_sel, (size_t)n * sizeof(qkm_sel)));
+        c->dense_cap_rows = n;
+    }
+    if (items > c->dense_cap_items) {
+        if (c->dense_items) cudaFree(c->dense_items);
+        c->dense_items = nullptr; c->dense_cap_items = 0;
+        QKM_CUDA(c, cudaMalloc((void**)&c->dense_items, items * sizeof(MmaItem)));
+        c->dense_cap_items = items;
+    }
+    if (!c->dense_n_items) QKM_CUDA(c, cudaMalloc((void**)&c->dense_n_items, sizeof(uint32_t)));
+    QKM_LAUNCH(c, launch_dense_gemm(c->L(), dm.type, dm.tiles, dm.M, dm.K, x, n, y, c->dense_xb, c->dense_pairs, c->dense_sel,
+                                    c->dense_items, c->dense_n_items, c->status));
+    return QKM_OK;
+}
 
 // ---------------------------------------------------------------- layer entry / tail
 

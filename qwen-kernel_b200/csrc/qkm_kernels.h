@@ -169,6 +169,13 @@ cudaError_t launch_shared_down(const Launch& L, const qkm_dims& d, const void* d
 cudaError_t launch_fold_contrib(const Launch& L, const qkm_dims& d, const float* contrib, const float* y2,
                                 float* y, uint32_t n_tokens);
 
+// Dense quantised GEMM Y[n][M] = X[n][K] . W^T on the tcgen05 pipeline (W tile-ordered Q8_0 / IQ4_XS,
+// M % 128 == 0, K % 256 == 0).  Scratch: xb n*K bf16, pairs n words, unit_sel n records,
+// items ceil(n/128) * M/128 entries, n_items one word.
+cudaError_t launch_dense_gemm(const Launch& L, uint32_t type, const void* tiles, uint32_t M, uint32_t K, const float* x,
+                              uint32_t n_rows, float* y, void* xb, uint32_t* pairs, qkm_sel* unit_sel, MmaItem* items,
+                              uint32_t* n_items, uint32_t* status);
+
 // ---- residual adds fused with the RMS norm (qkm_tail.cu) ---------------------------------------
 // mode 0: s = a + b; 1: s = a + b + c2; 2: s = a + sum_k b[row][k][:] + c2 (b = per-slot contributions).
 // xn = s * w / sqrt(mean(s^2) + eps).

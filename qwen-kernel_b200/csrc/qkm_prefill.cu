@@ -725,6 +725,58 @@ cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t route
     return cudaGetLastError();
 }
 
+// ---- dense quantised GEMM through the same pipeline ----------------------------------------------------
+// Y[n][M] = X[n][K] . W^T for one tile-ordered Q8_0 / IQ4_XS matrix: the matrix plays the part of a
+// single expert whose "pairs" are all n rows, so down_mma_kernel does the work.  These two kernels
+// prepare its inputs: X as bf16 rows, the identity pair list with unit weights, and the work list
+// (row tiles of one token tile are consecutive, as the kernel's row-tile walk expects).
+__global__ void __launch_bounds__(256)
+dense_prepare_kernel(const float* __restrict__ x, __nv_bfloat16* __restrict__ xb, uint64_t n_elems,
+                     uint32_t n_rows, uint32_t* __restrict__ pairs, qkm_sel* __restrict__ unit_sel) {
+    const uint64_t i = ((uint64_t)blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    if (i < n_elems) {
+        const float2 v = *reinterpret_cast<const float2*>(x + i);
+        *reinterpret_cast<__nv_bfloat162*>(xb + i) = __floats2bfloat162_rn(v.x, v.y);
+    }
+    const uint64_t t = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n_rows) {
+        pairs[t] = (uint32_t)t << 4;        // (row, slot 0)
+        unit_sel[t].ids[0] = 0;
+        unit_sel[t].w[0] = 1.0f;
+    }
+}
+
+__global__ void dense_plan_kernel(uint32_t n_rows, uint32_t row_tiles_total, MmaItem* __restrict__ items,
+                                  uint32_t* __restrict__ n_items) {
+    const uint32_t tiles = (n_rows + pf::kNT - 1) / pf::kNT;
+    for (uint32_t i = blockIdx.x * blockDim.x + threadIdx.x; i < tiles * row_tiles_total; i += gridDim.x * blockDim.x) {
+        MmaItem it;
+        it.expert = 0;
+        it.rt = (uint16_t)(i % row_tiles_total);
+        it.pair_off = (i / row_tiles_total) * pf::kNT;
+        it.n = min((uint32_t)pf::kNT, n_rows - it.pair_off);
+        items[i] = it;
+    }
+    if (blockIdx.x == 0 && threadIdx.x == 0) *n_items = tiles * row_tiles_total;
+}
+
+cudaError_t launch_dense_gemm(const Launch& L, uint32_t type, const void* tiles, uint32_t M, uint32_t K, const float* x,
+                              uint32_t n_rows, float* y, void* xb, uint32_t* pairs, qkm_sel* unit_sel, MmaItem* items,
+                              uint32_t* n_items, uint32_t* status) {
+    if (n_rows == 0) return cudaSuccess;
+    if (M % 128 || K % 256 || M / 128 > 65535) return cudaErrorInvalidValue;
+    const uint64_t n_elems = (uint64_t)n_rows * K;
+    dense_prepare_kernel<<<(unsigned)((n_elems / 2 + 255) / 256), 256, 0, L.stream>>>(x, (__nv_bfloat16*)xb, n_elems, n_rows, pairs, unit_sel);
+    const uint32_t total = (n_rows + pf::kNT - 1) / pf::kNT * (M / 128);
+    dense_plan_kernel<<<(total + 255) / 256, 256, 0, L.stream>>>(n_rows, M / 128, items, n_items);
+    L.count(2);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+    qkm_dims d;
+    d.n_embd = M; d.n_ff = K; d.n_expert = 1; d.n_used = 1;
+    return launch_down_mma(L, d, type, tiles, xb, unit_sel, pairs, items, n_items, total, y, status);
+}
+
 // ---- fold: y[t] = sum over slots (in order) of contrib[pos(t,s)], then the shared expert -----------------
 __global__ void fold_pairs_kernel(const float* __restrict__ contrib, const uint32_t* __restrict__ pos_of,
                                   float* __restrict__ y, uint32_t n_used, uint32_t n_embd) {
