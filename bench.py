@@ -465,6 +465,21 @@ def run_gemv_sweep(args, pkg, syn, torch, R: Ranks, orc, peaks):
                                       "frac_of_measured_copy": gb / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "copies": copies}
         del buf, w_dev
     torch.cuda.set_stream(torch.cuda.default_stream(dev))
+    ctx.set_stream(0)
+    # dense prefill projections on the tensor cores: Y[n][M] = X[n][K] . W^T (compute-bound at these
+    # n, so the matrix staying in L2 does not flatter the figure; the activations are 16-32 MB per call)
+    for t, M, K, n in ((syn.Q8_0, 4096, 2048, 2048), (syn.IQ4_XS, 4096, 2048, 2048), (syn.Q8_0, 8192, 2048, 512)):
+        W = syn.random_blocks(t, M, K, SEED_W + 6, "gemm")
+        ctx.dense_upload(0, t, W, M, K)
+        xg = torch.from_numpy(syn.random_x(n, K, SEED_X + 11)).to(dev)
+        yg = torch.empty((n, M), dtype=torch.float32, device=dev)
+        ctx.dense_gemm(0, xg, n, yg); R.barrier()
+        want = orc.gemv(t, W, xg[0].cpu().numpy(), M, K, threads=orc.hardware_threads())
+        err = syn.rel_err_rows(yg[:1].cpu().numpy(), want.reshape(1, -1))
+        assert err < 2e-2, f"dense gemm {names[t]} {M}x{K}: error {err}"
+        ms = timed(torch, R, torch.cuda.current_stream(dev), lambda: ctx.dense_gemm(0, xg, n, yg), 5, 3)
+        out[f"gemm_{names[t]}_{M}x{K}_n{n}"] = {"us": ms * 1e3, "tflops": 2.0 * n * M * K / (ms * 1e-3) / 1e12,
+                                                "frac_of_measured_bf16_burst": 2.0 * n * M * K / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"]}
     ctx.close()
     return out
 
