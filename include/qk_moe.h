@@ -292,6 +292,10 @@ QKM_API int qkm_add_rms3(qkm_ctx *c, const float *a, const float *b, const float
 QKM_API int qkm_add_rms3_grouped(qkm_ctx *c, const float *a, const float *routed, const float *c2,
                                  const float *w, float *s, float *xn, uint32_t n_rows, uint32_t n,
                                  uint32_t n_used, float eps);
+/* argmax1.comp:17-40 + argmax2.comp:16-32 (after the head GEMV, src/main.cpp:4406-4412): per row
+ * of n logits the index of the largest value, the lower index on ties; values must exceed
+ * -3.4e38 to count (NaN never wins; a row with nothing above the floor gives 0).  tok: device u32[n_rows]. */
+QKM_API int qkm_argmax(qkm_ctx *c, const float *logits, uint32_t n_rows, uint32_t n, uint32_t *tok);
 /* The feed-forward half of a decoder layer as the engine sequences it (src/main.cpp:4375-4404:
  * add_rmsnorm, the MoE dispatches, add_rms3): resid_out = resid + attn_out + MoE(rmsnorm(resid +
  * attn_out) * w_post); xn_next = rmsnorm(resid_out) * w_next.  resid_out may alias resid.

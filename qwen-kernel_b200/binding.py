@@ -93,6 +93,7 @@ SIGNATURES = {
     "qkm_upload_layer_gguf": (_I, [_VP, _U32, _VP, _U32]),
     "qkm_dense_upload": (_I, [_VP, _U32, _U32, _VP, _U32, _U32]),
     "qkm_dense_gemm": (_I, [_VP, _U32, _VP, _U32, _VP]),
+    "qkm_argmax": (_I, [_VP, _VP, _U32, _U32, _VP]),
     "qkm_add_rmsnorm": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, C.c_float]),
     "qkm_add_rms3": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, C.c_float]),
     "qkm_add_rms3_grouped": (_I, [_VP, _VP, _VP, _VP, _VP, _VP, _VP, _U32, _U32, _U32, C.c_float]),
@@ -313,6 +314,9 @@ class Context:
 
     def add_rms3_grouped(self, a, routed, c2, w, s, xn, n_rows, n, n_used, eps=1e-6):
         self.check(self.lib.qkm_add_rms3_grouped(self.h, _p(a), _p(routed), _p(c2), _p(w), _p(s), _p(xn), n_rows, n, n_used, eps))
+
+    def argmax(self, logits, n_rows, n, tok):
+        self.check(self.lib.qkm_argmax(self.h, _p(logits), n_rows, n, _p(tok)))
 
     def moe_layer_step(self, layer_idx, resid, attn_out, w_post, w_next, n, resid_out, xn_next, eps=1e-6):
         self.check(self.lib.qkm_moe_layer_step(self.h, layer_idx, _p(resid), _p(attn_out), _p(w_post), _p(w_next), n, eps,

@@ -71,6 +71,7 @@ struct qkm_ctx {
     MmaItem* mma_items[4] = {nullptr, nullptr, nullptr, nullptr};  // gate/up, down, shared gate/up, shared down
     uint32_t* pos_of = nullptr;       // [max_tokens*(n_used+1)]
     uint32_t* group_hist = nullptr;   // scratch of the multi-block grouping
+    void* argmax_scratch = nullptr; uint32_t argmax_rows = 0;
     // dense matrices for qkm_dense_gemm (tile-ordered copies) and its scratch, sized on demand
     static constexpr int kDenseSlots = 16;
     struct Dense { uint32_t type = 0, M = 0, K = 0; void* tiles = nullptr; } dense[kDenseSlots];
@@ -283,7 +284,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
         for (void* p : l.tiles) if (p) cudaFree(p);
     }
     for (auto& dm : c->dense) if (dm.tiles) cudaFree(dm.tiles);
-    void* scratch[] = {c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
+    void* scratch[] = {c->argmax_scratch, c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
@@ -891,6 +892,18 @@ extern "C" QKM_API int qkm_add_rms3_grouped(qkm_ctx* c, const float* a, const fl
     if (!c || !a || !routed || !c2 || !w || !s || !xn) return QKM_ERR_ARG;
     if (n_used == 0 || n_used > 16) return fail(c, QKM_ERR_ARG, "qkm_add_rms3_grouped: n_used %u", n_used);
     QKM_LAUNCH(c, launch_add_rms(c->L(), 2, a, routed, c2, w, s, xn, n_rows, n, n_used, eps));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_argmax(qkm_ctx* c, const float* logits, uint32_t n_rows, uint32_t n, uint32_t* tok) {
+    if (!c || !logits || !tok) return QKM_ERR_ARG;
+    if (n_rows > c->argmax_rows) {
+        if (c->argmax_scratch) QKM_CUDA(c, cudaFree(c->argmax_scratch));
+        c->argmax_scratch = nullptr; c->argmax_rows = 0;
+        QKM_CUDA(c, cudaMalloc(&c->argmax_scratch, argmax_scratch_bytes(n_rows)));
+        c->argmax_rows = n_rows;
+    }
+    QKM_LAUNCH(c, launch_argmax(c->L(), logits, n_rows, n, c->argmax_scratch, tok));
     return QKM_OK;
 }
 

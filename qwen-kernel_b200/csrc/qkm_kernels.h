@@ -182,6 +182,10 @@ cudaError_t launch_dense_gemm(const Launch& L, uint32_t type, const void* tiles,
 cudaError_t launch_add_rms(const Launch& L, int mode, const float* a, const float* b, const float* c2, const float* w,
                            float* s, float* xn, uint32_t n_rows, uint32_t n, uint32_t n_used, float eps);
 
+// greedy token per row of logits: largest value, lowest index on ties (scratch: argmax_scratch_bytes)
+size_t argmax_scratch_bytes(uint32_t n_rows);
+cudaError_t launch_argmax(const Launch& L, const float* logits, uint32_t n_rows, uint32_t n, void* scratch, uint32_t* tok);
+
 // ---- expert-parallel exchange helpers (qkm_ep.cu) --------------------------------------------
 // counts[0..n_ranks) rows per destination rank and counts[n_ranks] their sum; send_tok the
 // tokens in send order; send_pos[t][r] the row of token t among the rows sent (to rank r).

@@ -94,3 +94,76 @@ cudaError_t launch_add_rms(const Launch& L, int mode, const float* a, const floa
 }
 
 }  // namespace qkm
+
+// ---- greedy token: argmax over a row of logits ----------------------------------------------------
+// shaders/argmax1.comp:17-40 + argmax2.comp:16-32: the largest value wins, the lower index on
+// ties; a value must exceed -3.4e38 to be taken (so NaN never wins and an all-floor row gives 0).
+// Two launches as in the reference: up to 64 spans per row, then one block per row.
+namespace qkm {
+namespace {
+
+constexpr uint32_t kArgSpans = 64;
+
+__device__ __forceinline__ void arg_better(float& bv, uint32_t& bi, float v, uint32_t i) {
+    if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+}
+
+__device__ __forceinline__ void arg_block_reduce(float& bv, uint32_t& bi) {
+    __shared__ float s_v[8];
+    __shared__ uint32_t s_i[8];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float v = __shfl_xor_sync(0xFFFFFFFFu, bv, o);
+        const uint32_t i = __shfl_xor_sync(0xFFFFFFFFu, bi, o);
+        arg_better(bv, bi, v, i);
+    }
+    if ((threadIdx.x & 31u) == 0) { s_v[threadIdx.x >> 5] = bv; s_i[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0)
+        for (int w = 1; w < 8; ++w) arg_better(bv, bi, s_v[w], s_i[w]);
+}
+
+__global__ void __launch_bounds__(256)
+argmax_spans_kernel(const float* __restrict__ logits, uint32_t n, uint32_t span, float* __restrict__ vals,
+                    uint32_t* __restrict__ idxs) {
+    const uint32_t row = blockIdx.y, w = blockIdx.x;
+    const float* l = logits + (size_t)row * n;
+    const uint32_t start = w * span, end = min(start + span, n);
+    float bv = -3.4e38f;
+    uint32_t bi = 0xFFFFFFFFu;     // "nothing taken": loses every tie
+    for (uint32_t i = start + threadIdx.x; i < end; i += 256) {
+        const float v = l[i];
+        if (v > bv) { bv = v; bi = i; }
+    }
+    arg_block_reduce(bv, bi);
+    if (threadIdx.x == 0) { vals[row * kArgSpans + w] = bv; idxs[row * kArgSpans + w] = bi; }
+}
+
+__global__ void __launch_bounds__(256)
+argmax_final_kernel(const float* __restrict__ vals, const uint32_t* __restrict__ idxs, uint32_t m, uint32_t* __restrict__ tok) {
+    const uint32_t row = blockIdx.x, t = threadIdx.x;
+    float bv = t < m ? vals[row * kArgSpans + t] : -3.4e38f;
+    uint32_t bi = t < m ? idxs[row * kArgSpans + t] : 0xFFFFFFFFu;
+    arg_block_reduce(bv, bi);
+    if (t == 0) tok[row] = bi == 0xFFFFFFFFu ? 0u : bi;
+}
+
+}  // namespace
+
+size_t argmax_scratch_bytes(uint32_t n_rows) { return (size_t)n_rows * kArgSpans * 8; }
+
+cudaError_t launch_argmax(const Launch& L, const float* logits, uint32_t n_rows, uint32_t n, void* scratch, uint32_t* tok) {
+    if (n_rows == 0) return cudaSuccess;
+    if (n == 0) return cudaErrorInvalidValue;
+    uint32_t spans = (n + 4095) / 4096;
+    if (spans > kArgSpans) spans = kArgSpans;
+    const uint32_t span = (n + spans - 1) / spans;
+    float* vals = (float*)scratch;
+    uint32_t* idxs = (uint32_t*)(vals + (size_t)n_rows * kArgSpans);
+    argmax_spans_kernel<<<dim3(spans, n_rows), 256, 0, L.stream>>>(logits, n, span, vals, idxs);
+    argmax_final_kernel<<<n_rows, 256, 0, L.stream>>>(vals, idxs, spans, tok);
+    L.count(2);
+    return cudaGetLastError();
+}
+
+}  // namespace qkm

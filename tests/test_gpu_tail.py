@@ -73,3 +73,31 @@ def test_layer_step(ctx, orc, syn, T, tol):
     assert syn.rel_err_rows(got_xn, want_xn) < tol
     for t in d + [d_r, d_xn]:
         t.free()
+
+
+def _argmax_ref(rows):
+    """argmax1/argmax2 semantics: largest value above -3.4e38, lowest index on ties, else 0."""
+    out = []
+    for r in rows:
+        ok = r > np.float32(-3.4e38)          # False for NaN
+        if not ok.any():
+            out.append(0)
+            continue
+        m = r[ok].max()
+        out.append(int(np.nonzero(ok & (r == m))[0][0]))
+    return np.asarray(out, np.uint32)
+
+
+@pytest.mark.parametrize("n", [1, 255, 4096, 151936])
+def test_argmax(ctx, syn, n):
+    rows = syn.random_x(6, n, seed=12).copy()
+    if n > 300:
+        rows[1, 77] = rows[1, 300] = rows[1].max() + 1.0     # tie: lower index wins
+        rows[2, :] = -np.inf                                 # nothing above the floor
+        rows[3, 5] = np.nan; rows[3, n - 1] = np.inf         # NaN ignored, +inf wins
+        rows[4, :] = np.nan
+        rows[5, n - 1] = 1e30                                # last element
+    d_l, d_t = ctx.to_device(rows), ctx.alloc(4 * 6)
+    ctx.argmax(d_l, 6, n, d_t)
+    assert np.array_equal(d_t.download(np.uint32, 6), _argmax_ref(rows))
+    d_l.free(); d_t.free()
