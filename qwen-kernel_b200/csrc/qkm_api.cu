@@ -25,6 +25,7 @@ struct qkm_layer_dev {
     void* tiles[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool tiles_ok = false;   // routed gate/up and down both have tiles
     bool stream_ok = false;  // tiles, and every expert resident: the fused decode / prefill sequences apply
+    bool gu_only = false;    // as stream_ok for gate/up and the shared expert, but the down tensor (Q6_K) has no tiles
 };
 
 struct qkm_ctx {
@@ -396,7 +397,7 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
     }
     // tile-ordered copies for the streaming kernels (same bytes, re-ordered on the device)
     for (void*& p : l.tiles) { if (p) { QKM_CUDA(c, cudaFree(p)); p = nullptr; } }
-    l.stream_ok = l.tiles_ok = false;
+    l.stream_ok = l.tiles_ok = l.gu_only = false;
     if (c->shapes_stream_ok) {
         const qkm_dims& d = c->cfg.dims;
         struct { int idx; uint32_t type, mats, rows, K; } plan[] = {
@@ -405,16 +406,19 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
             {5, QKM_TYPE_Q8_0, 1, d.n_ff, d.n_embd}, {6, QKM_TYPE_Q8_0, 1, d.n_ff, d.n_embd},
             {7, QKM_TYPE_Q8_0, 1, d.n_embd, d.n_ff},
         };
-        bool ok = w->gateup_type == QKM_TYPE_IQ3_XXS && w->down_type == QKM_TYPE_IQ4_XS;
+        const bool gu = w->gateup_type == QKM_TYPE_IQ3_XXS, dn = w->down_type == QKM_TYPE_IQ4_XS;
         for (auto& t : plan) {
-            if (!ok) break;
+            if (!gu) break;                       // without streamed gate/up nothing else is used
+            if (t.idx == 4 && !dn) continue;      // Q6_K down: the f32 kernels read the raw layout
             const size_t bytes = tensor_bytes(c, t.idx, *w);
             QKM_CUDA(c, cudaMalloc(&l.tiles[t.idx], bytes + 256));
             cudaError_t e = launch_repack(c->L(), t.type, l.allocs[t.idx], l.tiles[t.idx], t.mats, t.rows, t.K);
             if (e != cudaSuccess) return fail(c, QKM_ERR_CUDA, "repack: %s", cudaGetErrorString(e));
         }
-        l.tiles_ok = ok;
-        l.stream_ok = ok && c->ecount == c->cfg.dims.n_expert;
+        const bool all_resident = c->ecount == c->cfg.dims.n_expert;
+        l.tiles_ok = gu && dn;
+        l.stream_ok = gu && dn && all_resident;
+        l.gu_only = gu && !dn && all_resident;
     }
     QKM_CUDA(c, cudaStreamSynchronize(c->stream));
     l.w = *w;
@@ -551,7 +555,7 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     c->prof_begin();
-    if (!ld.stream_ok) {  // generic kernels on the raw layout
+    if (!ld.stream_ok && !ld.gu_only) {  // generic kernels on the raw layout
         QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes));
         c->prof_mark("moe.route");
         QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
@@ -580,9 +584,11 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     QKM_LAUNCH(c, launch_gateup_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xplanes, c->xscale, c->pairs,
                                        c->items_sh_gu, c->n_items + 2, c->h, c->hpieces, nb, c->status));
     if (!fork) c->prof_mark("moe.shared_gu");
-    QKM_LAUNCH(c, launch_down_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, nullptr, c->pairs, c->items_sh_dn,
-                                     c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));   // unweighted: w_shared is applied by the routed down kernel
-    if (!fork) c->prof_mark("moe.shared_dn");
+    if (ld.stream_ok) {
+        QKM_LAUNCH(c, launch_down_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hpieces, nullptr, c->pairs, c->items_sh_dn,
+                                         c->n_items + 3, nullptr, c->y2, nullptr, nb, c->status));   // unweighted: w_shared is applied by the routed down kernel
+        if (!fork) c->prof_mark("moe.shared_dn");
+    }
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     // Router.  Decode-sized batches: the selection kernel's last block also groups the pairs and
     // cuts the work lists; otherwise a grouping launch follows.
@@ -603,7 +609,11 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
                                        c->items_gu, c->n_items, c->h, c->hpieces, nb, c->status));
     c->prof_mark("moe.gu");
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
-    QKM_LAUNCH(c, launch_down_tok(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->y2, y, n, nb, c->status));
+    if (ld.stream_ok) {
+        QKM_LAUNCH(c, launch_down_tok(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->y2, y, n, nb, c->status));
+    } else {   // Q6_K down: f32 kernel over h, routed slots and the shared expert in one pass
+        QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));
+    }
     c->prof_mark("moe.dn");
     return QKM_OK;
 }
@@ -653,7 +663,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     const qkm_layer_dev& ld = c->layers[layer];
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
-    if (!ld.stream_ok || n == 0) return prefill_generic(c, ld, x, n, y);
+    if ((!ld.stream_ok && !ld.gu_only) || n == 0) return prefill_generic(c, ld, x, n, y);
     // tensor-core path: tokens grouped by expert, expert GEMMs on tcgen05 with bf16 operands
     const uint32_t NT = prefill_pairs_per_block();
     const uint32_t rt_gu = d.n_ff / 128, rt_dn = d.n_embd / 128;
@@ -679,13 +689,27 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
                                     c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status));
     if (!fork) c->prof_mark("moe.shared_gu");
-    QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
-                                  c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
-    if (!fork) c->prof_mark("moe.shared_dn");
+    if (ld.stream_ok) {
+        QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
+                                      c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
+        if (!fork) c->prof_mark("moe.shared_dn");
+    }
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
                                     c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status));
     c->prof_mark("moe.gu");
+    if (!ld.stream_ok) {
+        // Q6_K down: the f32 kernels take over from h (per-pair contributions, shared down, fold)
+        if (!c->contrib) QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
+        if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
+        QKM_CUDA(c, cudaMemsetAsync(c->contrib, 0, (size_t)n * d.n_used * d.n_embd * sizeof(float), c->stream));
+        QKM_LAUNCH(c, launch_down_pairs(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, c->offsets, c->pairs, c->contrib, n, c->efirst, c->ecount));
+        QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, c->sel, c->y2, n));
+        c->prof_mark("moe.dn");
+        QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, c->y2, y, n));
+        c->prof_mark("moe.fold");
+        return QKM_OK;
+    }
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, c->sel, c->pairs, c->mma_items[1],
                                   c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status));
     c->prof_mark("moe.dn");

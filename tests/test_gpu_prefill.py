@@ -62,3 +62,13 @@ def test_prefill_matches_decode_path(pkg, syn):
         yd = ctx.moe_forward_host(0, x, mode=0)
         yp = ctx.moe_forward_host(0, x, mode=1)
     assert syn.rel_err_rows(yp, yd) < TOL_BF16
+
+
+@pytest.mark.parametrize("T", [70, 200])
+def test_prefill_q6k_down(pkg, orc, syn, T):
+    """Q6_K down tensors have no tile layout: gate/up runs on the tensor cores, the down
+    projection on the f32 kernels."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=46, router_type=syn.F32, down_type=syn.Q6_K)
+    x = syn.random_x(T, dims.n_embd, seed=78)
+    run_prefill(pkg, orc, syn, dims, layer, x)
