@@ -41,23 +41,25 @@ cudaError_t launch_encode_digits(const Launch& L, const float* x, int8_t* planes
 // ---- the streaming kernel ----------------------------------------------------------------------------------
 namespace gu {
 constexpr int kRowsPerItem = 128;
-constexpr int kUnitTiles = 2;                      // row tiles per unit (32 rows)
-constexpr int kUnitsPerItem = kRowsPerItem / (16 * kUnitTiles);
 constexpr int kStages = 2;
 constexpr uint32_t kGridLut = 32768;   // absolute shared-window addresses, 32 KB aligned so that
 constexpr uint32_t kSignLut = 65536;   // (index << shift) | lane offset needs no add
 constexpr uint32_t kLutEnd = 98304;
-constexpr int kRedFloats = kUnitTiles * 16 * 2 * 2;   // per warp: tile,row,token,matrix
 
 template <int FMT> struct Cfg;
+// kUnitTiles: row tiles per unit of work.  The routed experts take 64-row units (fewer
+// reductions and epilogues per weight); the shared expert has only n_ff rows per token pair and
+// keeps 32-row units so that its work still spreads over the SMs.
 template <> struct Cfg<QKM_TYPE_IQ3_XXS> {
-    static constexpr int kWarps = 16, kTile = kTileIq3, kLowRingWarps = 4;
+    static constexpr int kWarps = 16, kTile = kTileIq3, kLowRingWarps = 4, kUnitTiles = 4;
     static constexpr bool kLuts = true;
 };
 template <> struct Cfg<QKM_TYPE_Q8_0> {
-    static constexpr int kWarps = 8, kTile = kTileQ8, kLowRingWarps = 0;
+    static constexpr int kWarps = 8, kTile = kTileQ8, kLowRingWarps = 0, kUnitTiles = 2;
     static constexpr bool kLuts = false;
 };
+template <int FMT> constexpr int units_per_item() { return kRowsPerItem / (16 * Cfg<FMT>::kUnitTiles); }
+template <int FMT> constexpr int red_floats() { return Cfg<FMT>::kUnitTiles * 16 * 2 * 2; }   // per warp: tile,row,token,matrix
 }  // namespace gu
 
 // One 16-row x 256-column tile of one matrix against the warp's B operand.
@@ -190,7 +192,7 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
 
     // this team's contiguous share of the flat unit list
     const uint32_t teams_total = gridDim.x * n_teams, team_global = blockIdx.x * n_teams + team;
-    const uint64_t units_total = (uint64_t)n_items * gu::kUnitsPerItem;
+    const uint64_t units_total = (uint64_t)n_items * gu::units_per_item<FMT>();
     const uint32_t u_lo = (uint32_t)(units_total * team_global / teams_total);
     const uint32_t u_hi = (uint32_t)(units_total * (team_global + 1) / teams_total);
     const size_t mat_tiles = (size_t)KB * RT;
@@ -199,14 +201,14 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
     uint32_t p_unit = u_lo, p_tile = 0;
     auto issue = [&](uint32_t stage) {
         if (p_unit >= u_hi) return;
-        const StreamItem it = items[p_unit / gu::kUnitsPerItem];
-        const uint32_t rt = it.chunk * (gu::kRowsPerItem / 16) + (p_unit % gu::kUnitsPerItem) * gu::kUnitTiles + p_tile;
+        const StreamItem it = items[p_unit / gu::units_per_item<FMT>()];
+        const uint32_t rt = it.chunk * (gu::kRowsPerItem / 16) + (p_unit % gu::units_per_item<FMT>()) * gu::Cfg<FMT>::kUnitTiles + p_tile;
         const size_t tile = (size_t)it.expert * mat_tiles + (size_t)kb * RT + rt;
         const uint32_t bar = my_bar + 8 * stage, dst = ring + stage * kStageBytes;
         mbar_expect_tx(bar, kStageBytes);
         bulk_g2s(dst, gate_tiles + tile * C::kTile, C::kTile, bar);
         bulk_g2s(dst + C::kTile, up_tiles + tile * C::kTile, C::kTile, bar);
-        if (++p_tile == gu::kUnitTiles) { p_tile = 0; ++p_unit; }
+        if (++p_tile == gu::Cfg<FMT>::kUnitTiles) { p_tile = 0; ++p_unit; }
     };
     if (lane == 0)
         for (int s = 0; s < gu::kStages; ++s) issue(s);
@@ -220,7 +222,7 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
     uint32_t loaded_pair_off = 0xFFFFFFFFu, loaded_ntok = 0;
 
     for (uint32_t unit = u_lo; unit < u_hi; ++unit) {
-        const StreamItem it = items[unit / gu::kUnitsPerItem];
+        const StreamItem it = items[unit / gu::units_per_item<FMT>()];
         if (it.pair_off != loaded_pair_off || it.ntok != loaded_ntok) {
             // B operand: column g = (token slot g>>2, digit g&3); this warp's 256 columns
             loaded_pair_off = it.pair_off; loaded_ntok = it.ntok;
@@ -255,9 +257,9 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
                 wcol1 = sc * w0 * 128.f;
             }
         }
-        float* my_red = red + warp * gu::kRedFloats;
+        float* my_red = red + warp * gu::red_floats<FMT>();
 #pragma unroll 1
-        for (int tile = 0; tile < gu::kUnitTiles; ++tile, ++cnt) {
+        for (int tile = 0; tile < gu::Cfg<FMT>::kUnitTiles; ++tile, ++cnt) {
             const uint32_t stage = cnt % gu::kStages, parity = (cnt / gu::kStages) & 1u;
             if (!mbar_wait_bounded(my_bar + 8 * stage, parity)) timed_out = true;
             const uint32_t sbase = ring + stage * kStageBytes;
@@ -279,17 +281,17 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
         }
         // team-wide: sum the KB column-block partials, SwiGLU, store
         asm volatile("bar.sync %0, %1;" ::"r"(team + 1), "r"(team_threads) : "memory");
-        for (uint32_t j = lt; j < gu::kUnitTiles * 16 * 2; j += team_threads) {
+        for (uint32_t j = lt; j < gu::Cfg<FMT>::kUnitTiles * 16 * 2; j += team_threads) {
             const uint32_t ts = j & 1u, row = j >> 1;  // row within the unit
             if (ts < it.ntok) {
                 float gsum = 0.f, usum = 0.f;
                 for (uint32_t w = 0; w < KB; ++w) {
-                    const float* r = red + (team * KB + w) * gu::kRedFloats + (row * 2 + ts) * 2;
+                    const float* r = red + (team * KB + w) * gu::red_floats<FMT>() + (row * 2 + ts) * 2;
                     gsum += r[0]; usum += r[1];
                 }
                 const float hv = swiglu(gsum, usum);
                 const uint32_t pr = pairs[it.pair_off + ts], tok = pr >> 4, slot = pr & 15u;
-                const uint32_t r_ff = it.chunk * gu::kRowsPerItem + (unit % gu::kUnitsPerItem) * (16 * gu::kUnitTiles) + row;
+                const uint32_t r_ff = it.chunk * gu::kRowsPerItem + (unit % gu::units_per_item<FMT>()) * (16 * gu::Cfg<FMT>::kUnitTiles) + row;
                 h[((size_t)tok * (d.n_used + 1) + slot) * d.n_ff + r_ff] = hv;
                 // bf16 pieces in the down kernels' B-operand order: [token][slot][piece][sub-block][t][8]
                 // with the 8 = elements (4t, 16+4t, 4t+1, 17+4t, 4t+2, 18+4t, 4t+3, 19+4t)
@@ -317,8 +319,8 @@ static cudaError_t gateup_stream_launch(const Launch& L, const qkm_dims& d, cons
     // the dynamic area must reach from wherever it starts (a few KB at most) to the end of
     // the reduction scratch
     const size_t smem = C::kLuts ? (size_t)gu::kLutEnd + (size_t)(C::kWarps - C::kLowRingWarps) * gu::kStages * 2 * C::kTile +
-                                       (size_t)C::kWarps * gu::kRedFloats * 4
-                                 : 1024 + kRings + (size_t)C::kWarps * gu::kRedFloats * 4;
+                                       (size_t)C::kWarps * gu::red_floats<FMT>() * 4
+                                 : 1024 + kRings + (size_t)C::kWarps * gu::red_floats<FMT>() * 4;
     cudaError_t e = cudaFuncSetAttribute(gateup_stream_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     gateup_stream_kernel<FMT><<<n_blocks, C::kWarps * 32, smem, L.stream>>>(
