@@ -577,7 +577,9 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     }
-    QKM_LAUNCH(c, launch_xplanes(S, x, n, d.n_embd, c->xplanes, c->xscale));
+    // the shared gate too, when the selection kernel will not touch it (same condition as below)
+    const bool fused_plan = route_select_plans(d, n, c->route_scratch_bytes);
+    QKM_LAUNCH(c, launch_xplanes(S, x, n, d.n_embd, c->xplanes, c->xscale, fused_plan ? w.gate_inp_shexp : nullptr, c->sel));
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_planes, c->side));
     QKM_LAUNCH(c, launch_shared_plan(S, d, n, c->pairs, c->items_sh_gu, d.n_ff / gateup_stream_rows_per_item(),
                                      c->items_sh_dn, d.n_embd / down_stream_rows_per_item(), 2, c->n_items + 2));
@@ -592,9 +594,8 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     // Router.  Decode-sized batches: the selection kernel's last block also groups the pairs and
     // cuts the work lists; otherwise a grouping launch follows.
-    const bool fused_plan = route_select_plans(d, n, c->route_scratch_bytes);
     const RoutePlan rplan{c->route_counter, c->offsets, c->pairs, c->items_gu, c->items_dn, c->n_items,
-                          d.n_ff / gateup_stream_rows_per_item(), d.n_embd / down_stream_rows_per_item(), 2, c->efirst, c->ecount};
+                          d.n_ff / gateup_stream_rows_per_item(), d.n_embd / down_stream_rows_per_item(), 2, c->efirst, c->ecount, 1};
     QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
                                       nullptr, nullptr, nullptr, nullptr, nullptr, fused_plan ? &rplan : nullptr));
     c->prof_mark("moe.route");

@@ -88,7 +88,8 @@ cudaError_t launch_gemv_stream(const Launch& L, uint32_t type, const void* W, co
 
 // ---- qkm_route.cu
 // x rows as int8 digit planes + per-row scale (the selection kernel can write the same).
-cudaError_t launch_xplanes(const Launch& L, const float* x, uint32_t n_tokens, uint32_t n_embd, int8_t* xplanes, float* xscale);
+cudaError_t launch_xplanes(const Launch& L, const float* x, uint32_t n_tokens, uint32_t n_embd, int8_t* xplanes, float* xscale,
+                           const float* gis = nullptr, qkm_sel* sel = nullptr);   // gis given: also sel[t].w_shared = sigmoid(gis . x)
 // Optional tail of launch_route_select for decode-sized batches (<= 64 tokens, <= 1024 pairs,
 // f64-logit path): the selection kernel's last block also groups the pairs and cuts the
 // streaming kernels' work lists (what launch_group_plan does), saving a launch.  `counter` is a
@@ -102,6 +103,7 @@ struct RoutePlan {
     StreamItem* items_dn;
     uint32_t* n_items;
     uint32_t chunks_gu, chunks_dn, tok_per_item, expert_first, expert_count;
+    uint32_t shared_gate_elsewhere;   // 1: sel[t].w_shared is written by launch_xplanes (given gis); the selection kernel skips x
 };
 bool route_select_plans(const qkm_dims& d, uint32_t n_tokens, size_t scratch_bytes);
 // Scratch the refined router needs: n_tokens * n_expert f32 logits + n_expert f32 row norms,

@@ -327,13 +327,18 @@ cudaError_t launch_select(const Launch& L, const qkm_dims& d, const float* logit
 // layout [k-block][digit][256]; xscale = 2^-p.  A row with a non-finite value gets zero digits
 // and a NaN scale.  (The selection kernel can write the same planes; doing it here lets the
 // shared expert start before the routing is known.)
+// With gis != NULL it also evaluates the shared expert's gate, w_shared = sigmoid(gis . x) in
+// f64, into sel[t].w_shared - the selection kernel is then told to leave that field alone.
 __global__ void __launch_bounds__(256)
-xplanes_kernel(const float* __restrict__ x, uint32_t n_embd, int8_t* __restrict__ xplanes, float* __restrict__ xscale) {
+xplanes_kernel(const float* __restrict__ x, uint32_t n_embd, int8_t* __restrict__ xplanes, float* __restrict__ xscale,
+               const float* __restrict__ gis, qkm_sel* __restrict__ sel) {
     __shared__ float s_xm[8];
+    __shared__ double s_sg[8];
     const uint32_t t = blockIdx.x, tid = threadIdx.x, lane = tid & 31u, warp = tid >> 5;
     const float* xt = x + (size_t)t * n_embd;
     float v[16];   // n_embd <= 4096
     float xm = 0.f;
+    double dsg = 0.0;
     bool bad = false;
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
@@ -341,12 +346,20 @@ xplanes_kernel(const float* __restrict__ x, uint32_t n_embd, int8_t* __restrict_
         v[i] = k < n_embd ? xt[k] : 0.f;
         xm = fmaxf(xm, fabsf(v[i]));
         bad |= !(fabsf(v[i]) <= 3.0e38f);
+        if (gis != nullptr && k < n_embd) dsg += (double)gis[k] * (double)v[i];
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
+    if (gis != nullptr) dsg = warp_sum(dsg);
     const int any_bad = __syncthreads_or(bad ? 1 : 0);
-    if (lane == 0) s_xm[warp] = xm;
+    if (lane == 0) { s_xm[warp] = xm; s_sg[warp] = dsg; }
     __syncthreads();
+    if (gis != nullptr && tid == 0) {
+        double sg = 0.0;
+#pragma unroll
+        for (int w = 0; w < 8; ++w) sg += s_sg[w];
+        sel[t].w_shared = (float)(1.0 / (1.0 + exp(-sg)));
+    }
     float xmax = 0.f;
 #pragma unroll
     for (int w = 0; w < 8; ++w) xmax = fmaxf(xmax, s_xm[w]);
@@ -368,10 +381,11 @@ xplanes_kernel(const float* __restrict__ x, uint32_t n_embd, int8_t* __restrict_
     if (tid == 0) xscale[t] = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
 }
 
-cudaError_t launch_xplanes(const Launch& L, const float* x, uint32_t n_tokens, uint32_t n_embd, int8_t* xplanes, float* xscale) {
+cudaError_t launch_xplanes(const Launch& L, const float* x, uint32_t n_tokens, uint32_t n_embd, int8_t* xplanes, float* xscale,
+                           const float* gis, qkm_sel* sel) {
     if (n_tokens == 0) return cudaSuccess;
-    if (n_embd > 4096) return cudaErrorInvalidValue;
-    xplanes_kernel<<<n_tokens, 256, 0, L.stream>>>(x, n_embd, xplanes, xscale);
+    if (n_embd > 4096 || (gis != nullptr && sel == nullptr)) return cudaErrorInvalidValue;
+    xplanes_kernel<<<n_tokens, 256, 0, L.stream>>>(x, n_embd, xplanes, xscale, gis, sel);
     L.count();
     return cudaGetLastError();
 }
@@ -388,6 +402,7 @@ struct GroupTail {
     StreamItem* items_dn;
     uint32_t* n_items;       // [0] gate/up items, [1] down items
     uint32_t chunks_gu, chunks_dn, tok_per_item, n_tokens, expert_first, expert_count;
+    uint32_t shared_gate_elsewhere;   // sel[t].w_shared is written by another kernel: neither x nor the gate is touched here
 };
 static constexpr uint32_t kTailMaxPairs = 1024;
 
@@ -509,6 +524,13 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
     float xs = 0.f, xm = 0.f, rn = 0.f;
     double dsg = 0.0;
     bool bad = false;
+    // (skipped when the f64 logits are ranked as they are and the shared gate comes from
+    // elsewhere: nothing below needs x then)
+    const bool need_x = !EXACT || xplanes != nullptr || !tail.shared_gate_elsewhere;
+    float x2 = 0.f, r2 = 0.f, xmax = 0.f;
+    double sg = 0.0;
+    int any_bad = 0;
+    if (need_x) {
     for (uint32_t k = tid; k < d.n_embd; k += 256) {
         const float v = xt[k], gv = gis[k];
         s_x[k] = v;
@@ -528,14 +550,15 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
         rn = fmaxf(rn, __shfl_xor_sync(0xFFFFFFFFu, rn, o));
         xm = fmaxf(xm, __shfl_xor_sync(0xFFFFFFFFu, xm, o));
     }
-    const int any_bad = __syncthreads_or(bad ? 1 : 0);
+    any_bad = __syncthreads_or(bad ? 1 : 0);
     if (lane == 0) { s_f[warp] = xs; s_red[warp] = dsg; s_rn[warp] = rn; s_xm[warp] = xm; }
     if (tid == 0) s_ncand = 0;
     __syncthreads();
-    float x2 = 0.f, r2 = 0.f, xmax = 0.f;
-    double sg = 0.0;
 #pragma unroll
     for (int w = 0; w < 8; ++w) { x2 += s_f[w]; sg += s_red[w]; r2 = fmaxf(r2, s_rn[w]); xmax = fmaxf(xmax, s_xm[w]); }
+    } else {
+        __syncthreads();   // s_val is complete
+    }
     // the streaming expert kernels read x as int8 digit planes ([kb][digit][256] per row)
     if (xplanes != nullptr) {
         const int p = digit_exponent(xmax);
@@ -666,7 +689,7 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
             sel[t].ids[lane] = lane < d.n_used ? min(s_best_id[lane], d.n_expert - 1) : 0u;
             sel[t].w[lane] = lane < d.n_used ? (float)(wv / sum) : 0.f;
         } else if (lane == 16) {
-            sel[t].w_shared = (float)(1.0 / (1.0 + exp(-sg)));
+            if (need_x) sel[t].w_shared = (float)(1.0 / (1.0 + exp(-sg)));
             sel[t].route_done = 0;
         } else if (lane < 23) {
             sel[t].pad[lane - 17] = 0.f;
@@ -709,7 +732,7 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         uint32_t ef = plan->expert_first, ec = plan->expert_count;
         if (ec == 0) { ef = 0; ec = d.n_expert; }
         tail = GroupTail{plan->counter, plan->offsets, plan->pairs, plan->items_gu, plan->items_dn, plan->n_items,
-                         plan->chunks_gu, plan->chunks_dn, plan->tok_per_item, n_tokens, ef, ec};
+                         plan->chunks_gu, plan->chunks_dn, plan->tok_per_item, n_tokens, ef, ec, plan->shared_gate_elsewhere};
     }
     if (router_type != QKM_TYPE_F32 && router_type != QKM_TYPE_F16) return cudaErrorInvalidValue;
     if (n_tokens <= kExactMaxTokens && (size_t)n_tokens * d.n_expert * sizeof(double) <= scratch_bytes) {
