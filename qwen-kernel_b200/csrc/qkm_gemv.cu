@@ -286,9 +286,10 @@ gemv_direct_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, f
 
 template <int TYPE>
 static cudaError_t gemv_direct_launch(const Launch& L, const uint8_t* W, const float* x, float* y, uint32_t M, uint32_t K) {
-    // enough warps to fill the machine: a row is shared by up to eight warps when there are few rows
+    // one wave: as many warps as the machine holds at once (148 SMs x 64 warps), a row shared by
+    // up to eight warps when there are few rows
     uint32_t split = 1;
-    while (split < 8 && (uint64_t)M * split < 16384 && (K / 8) % (split * 2 * 32) == 0) split *= 2;
+    while (split < 8 && (uint64_t)M * split * 2 <= 148u * 64u && (K / 8) % (split * 2 * 32) == 0) split *= 2;
     const uint32_t rows_per_block = 8 / split;
     gemv_direct_kernel<TYPE><<<(M + rows_per_block - 1) / rows_per_block, 256, 0, L.stream>>>(W, x, y, M, K, split);
     L.count();
