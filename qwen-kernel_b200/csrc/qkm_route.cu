@@ -580,25 +580,40 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
     if (!EXACT) {
     // k-th largest f32 logit: the expert that exactly n_used-1 others precede
     {
-        // four logits per shared-memory load (n_expert is padded to 512 with the floor value)
-        const uint32_t n4 = (d.n_expert + 3u) & ~3u;
+        // Two levels: rank inside the warp's 32 experts by shuffles; an expert among the global
+        // top n_used is among its warp's top n_used, so only those survivors (n_used per warp and
+        // set) are ranked against each other.  Order: value descending, id ascending.
+        __shared__ float s_sv[2][8][16];
+        __shared__ uint32_t s_si[2][8][16];
         const bool two = d.n_expert > 256;       // the second expert of a thread exists only then
-        uint32_t c0 = 0, c1 = 0;
-        for (uint32_t j = 0; j < n4; j += 4) {
-            const float4 v = *reinterpret_cast<const float4*>(s_log + j);
-            c0 += (v.x > l0 || (v.x == l0 && j < id0)) ? 1u : 0u;
-            c0 += (v.y > l0 || (v.y == l0 && j + 1 < id0)) ? 1u : 0u;
-            c0 += (v.z > l0 || (v.z == l0 && j + 2 < id0)) ? 1u : 0u;
-            c0 += (v.w > l0 || (v.w == l0 && j + 3 < id0)) ? 1u : 0u;
+        uint32_t r0 = 0, r1 = 0;
+#pragma unroll 4
+        for (uint32_t sft = 1; sft < 32; ++sft) {
+            const uint32_t src = (lane + sft) & 31u;
+            const float o0 = __shfl_sync(0xFFFFFFFFu, l0, src);
+            r0 += (o0 > l0 || (o0 == l0 && src < lane)) ? 1u : 0u;
             if (two) {
-                c1 += (v.x > l1 || (v.x == l1 && j < id1)) ? 1u : 0u;
-                c1 += (v.y > l1 || (v.y == l1 && j + 1 < id1)) ? 1u : 0u;
-                c1 += (v.z > l1 || (v.z == l1 && j + 2 < id1)) ? 1u : 0u;
-                c1 += (v.w > l1 || (v.w == l1 && j + 3 < id1)) ? 1u : 0u;
+                const float o1 = __shfl_sync(0xFFFFFFFFu, l1, src);
+                r1 += (o1 > l1 || (o1 == l1 && src < lane)) ? 1u : 0u;
             }
         }
-        if (id0 < d.n_expert && c0 == d.n_used - 1) s_kth = l0;
-        if (two && id1 < d.n_expert && c1 == d.n_used - 1) s_kth = l1;
+        if (r0 < d.n_used) { s_sv[0][warp][r0] = l0; s_si[0][warp][r0] = id0; }
+        if (two && r1 < d.n_used) { s_sv[1][warp][r1] = l1; s_si[1][warp][r1] = id1; }
+        __syncthreads();
+        const uint32_t sets = two ? 2u : 1u;
+        if (r0 < d.n_used || (two && r1 < d.n_used)) {
+            uint32_t c0 = 0, c1 = 0;
+            for (uint32_t st = 0; st < sets; ++st)
+                for (uint32_t w = 0; w < 8; ++w)
+                    for (uint32_t q = 0; q < d.n_used; ++q) {
+                        const float v = s_sv[st][w][q];
+                        const uint32_t j = s_si[st][w][q];
+                        c0 += (v > l0 || (v == l0 && j < id0)) ? 1u : 0u;
+                        c1 += (v > l1 || (v == l1 && j < id1)) ? 1u : 0u;
+                    }
+            if (r0 < d.n_used && id0 < d.n_expert && c0 == d.n_used - 1) s_kth = l0;
+            if (two && r1 < d.n_used && id1 < d.n_expert && c1 == d.n_used - 1) s_kth = l1;
+        }
     }
     __syncthreads();
     const float kth = s_kth;

@@ -121,6 +121,43 @@ def test_route_select_ties_and_nonfinite(ctx, orc, syn):
         b.free()
 
 
+@pytest.mark.parametrize("T", [72, 160])
+def test_route_select_ties_large_batch(pkg, orc, syn, T):
+    """The same hazards on the large-batch paths (f32 logits below 128 tokens, tensor-core logits
+    above), where the boundary is re-evaluated in f64: ids must still equal the f64 router's."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=9, router_type=syn.F32)
+    r = layer.router.view(np.float32).reshape(256, 2048).copy()
+    r[200] = r[17]; r[90] = r[17]
+    r[3] = 0.0; r[4] = 0.0
+    layer.router = r.reshape(-1).view(np.uint8)
+    x = syn.random_x(T, 2048, seed=10)
+    x[2] = r[17] * 50.0
+    x[5, 100] = np.nan
+    x[6, 7] = np.inf
+    x[7] = 0.0
+    x[T - 1] = x[2]
+    want, w64 = orc.route(layer, x, threads=8)
+    with pkg.Context(dims, n_layer=1, max_tokens=T, device=0) as c:
+        c.upload_layer(0, layer)
+        c.moe_forward_host(0, np.where(np.isfinite(x), x, 0.0).astype(np.float32), mode=1)   # allocates the tensor-core scratch
+        d_r, d_g = c.to_device(layer.router), c.to_device(layer.gate_inp_shexp)
+        d_x, d_sel = c.to_device(x), c.alloc(T * 160)
+        c.moe_route_select(syn.F32, d_r, d_g, d_x, d_sel, T)
+        got = d_sel.download(pkg_sel(c), T)
+        for b in (d_r, d_g, d_x, d_sel):
+            b.free()
+        # and through the fused prefill call (tensor-core logits for T >= 128)
+        c.moe_forward_host(0, x, mode=1)
+        got_fused = c.last_sel(T)
+    for g in (got, got_fused):
+        assert np.array_equal(g["ids"], want["ids"])
+        assert list(g["ids"][2, :3]) == [17, 90, 200] and list(g["ids"][T - 1, :3]) == [17, 90, 200]
+        assert list(g["ids"][5, :8]) == list(range(8)) and list(g["ids"][7, :8]) == list(range(8))
+        ok = np.isfinite(w64[:, :8]).all(axis=1)
+        np.testing.assert_allclose(g["w"][ok, :8], w64[ok, :8], rtol=1e-5, atol=1e-7)
+
+
 def test_logits_and_select_from_f32(ctx, orc, syn):
     dims = syn.Dims()
     T = 16
