@@ -62,6 +62,7 @@ struct qkm_ctx {
     float* contrib_s = nullptr;       // [max_tokens][n_used+1][n_embd]
     uint32_t* arrivals = nullptr;     // [max_tokens][n_embd / unit rows]
     uint32_t* status = nullptr;       // kernel status word (device)
+    uint32_t shared_plan_n = 0;        // token count the shared expert's decode work lists were last cut for (0: stale)
     uint32_t* route_counter = nullptr; // ticket counter of the selection kernel's grouping tail (device, stays zero)
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
@@ -581,8 +582,13 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     const bool fused_plan = route_select_plans(d, n, c->route_scratch_bytes);
     QKM_LAUNCH(c, launch_xplanes(S, x, n, d.n_embd, c->xplanes, c->xscale, fused_plan ? w.gate_inp_shexp : nullptr, c->sel));
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_planes, c->side));
-    QKM_LAUNCH(c, launch_shared_plan(S, d, n, c->pairs, c->items_sh_gu, d.n_ff / gateup_stream_rows_per_item(),
-                                     c->items_sh_dn, d.n_embd / down_stream_rows_per_item(), 2, c->n_items + 2));
+    // the shared expert's work lists depend on the token count only and live in parts of the
+    // scratch the decode kernels never write: cut once, reused until another kind of call intervenes
+    if (c->shared_plan_n != n) {
+        QKM_LAUNCH(c, launch_shared_plan(S, d, n, c->pairs, c->items_sh_gu, d.n_ff / gateup_stream_rows_per_item(),
+                                         c->items_sh_dn, d.n_embd / down_stream_rows_per_item(), 2, c->n_items + 2));
+        c->shared_plan_n = n;
+    }
     QKM_LAUNCH(c, launch_gateup_stream(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xplanes, c->xscale, c->pairs,
                                        c->items_sh_gu, c->n_items + 2, c->h, c->hpieces, nb, c->status));
     if (!fork) c->prof_mark("moe.shared_gu");
@@ -664,6 +670,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     const qkm_layer_dev& ld = c->layers[layer];
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
+    c->shared_plan_n = 0;   // this call rewrites the scratch the decode work lists live in
     if ((!ld.stream_ok && !ld.gu_only) || n == 0) return prefill_generic(c, ld, x, n, y);
     // tensor-core path: tokens grouped by expert, expert GEMMs on tcgen05 with bf16 operands
     const uint32_t NT = prefill_pairs_per_block();
@@ -753,10 +760,13 @@ extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t
         if (int rc = layer_ready(c, first + l)) return rc;
     if (c->stream == nullptr || c->profiling || count < 2) return decode_stack_eager(c, first, count, x, n, y);
     auto& k = c->stack_key;
+    // (a stale shared-expert work list - another kind of call ran in between - also forces a new
+    // capture: the graph then contains the launch that cuts the list again)
     const bool same = c->stack_graph && k.first == first && k.count == count && k.n == n && k.x == x && k.y == y &&
-                      k.stream == c->stream;
+                      k.stream == c->stream && c->shared_plan_n == n;
     if (!same) {
         if (c->stack_graph) { cudaGraphExecDestroy(c->stack_graph); c->stack_graph = nullptr; }
+        c->shared_plan_n = 0;   // the captured sequence must cut the list itself
         const uint64_t before = c->launches;
         if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
             cudaGetLastError();
@@ -770,6 +780,7 @@ extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t
         if (rc != QKM_OK || e != cudaSuccess || !graph) {
             if (graph) cudaGraphDestroy(graph);
             cudaGetLastError();
+            c->shared_plan_n = 0;   // nothing captured has run
             return rc != QKM_OK ? rc : decode_stack_eager(c, first, count, x, n, y);
         }
         const cudaError_t ei = cudaGraphInstantiate(&c->stack_graph, graph, 0);
@@ -777,6 +788,7 @@ extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t
         if (ei != cudaSuccess) {
             c->stack_graph = nullptr;
             cudaGetLastError();
+            c->shared_plan_n = 0;
             return decode_stack_eager(c, first, count, x, n, y);
         }
         k.first = first; k.count = count; k.n = n; k.x = x; k.y = y; k.stream = c->stream;
@@ -964,6 +976,7 @@ extern "C" QKM_API int qkm_moe_layer_step(qkm_ctx* c, uint32_t layer, const floa
 
 static int ep_check(qkm_ctx* c, uint32_t n_ranks) {
     const qkm_dims& d = c->cfg.dims;
+    c->shared_plan_n = 0;
     if (n_ranks == 0 || n_ranks > 64 || d.n_expert % n_ranks) return fail(c, QKM_ERR_ARG, "n_ranks %u does not divide n_expert %u", n_ranks, d.n_expert);
     if (c->ecount != d.n_expert / n_ranks || c->efirst % c->ecount)
         return fail(c, QKM_ERR_MODE, "context holds experts [%u,%u): not one of %u equal shards", c->efirst, c->efirst + c->ecount, n_ranks);
@@ -1027,6 +1040,7 @@ extern "C" QKM_API int qkm_ep_dispatch_dev(qkm_ctx* c, uint32_t layer, const flo
 
 extern "C" QKM_API int qkm_ep_shared(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n) {
     if (int rc = layer_ready(c, layer)) return rc;
+    c->shared_plan_n = 0;
     if (!x) return QKM_ERR_ARG;
     if (int rc = check_tokens(c, n)) return rc;
     if (n == 0) return QKM_OK;
@@ -1066,6 +1080,7 @@ extern "C" QKM_API int qkm_ep_shared(qkm_ctx* c, uint32_t layer, const float* x,
 extern "C" QKM_API int qkm_ep_expert_forward(qkm_ctx* c, uint32_t layer, const float* xrecv, const qkm_sel* selrecv,
                                              uint32_t n_recv, float* partial) {
     if (int rc = layer_ready(c, layer)) return rc;
+    c->shared_plan_n = 0;
     if (n_recv == 0) return QKM_OK;
     if (!xrecv || !selrecv || !partial) return QKM_ERR_ARG;
     if (int rc = check_tokens(c, n_recv)) return rc;
