@@ -329,8 +329,8 @@ def run_ours(args, pkg, syn):
 # DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of
 # the decode stages on this workload; the captures are summarised under profiles/.
 NCU_TRAFFIC = {
-    "moe.gu": 84_650_000,   # gateup_stream_kernel<IQ3_XXS>: 82.32 MB read + 2.33 MB written at 102.5 experts' worth
-    "moe.dn": 58_170_000,   # down_tok_iq4_kernel: 57.37 MB read + 0.79 MB written
+    "moe.gu": 84_100_000,   # gateup_stream_kernel<IQ3_XXS>: 82.14 MB read + 1.96 MB written at 102.3 experts' worth
+    "moe.dn": 58_230_000,   # down_tok_iq4_kernel: 57.37 MB read + 0.86 MB written
 }
 
 PREFILL_CHUNKS = (128, 256, 512, 2048, 4096)
