@@ -660,37 +660,52 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
     {
         const double v0 = s_val[id0], v1 = s_val[id1];
         const bool m0 = v0 > ninf, m1 = v1 > ninf;
-        if (m0 || m1) {
-            uint32_t c0 = 0, c1 = 0;
-            if (EXACT || listed_all) {
-                // two values per shared-memory load (entries past n_expert hold -inf and never count)
-                const uint32_t n2 = (d.n_expert + 1u) & ~1u;
-                if (d.n_expert <= 256) {
-                    for (uint32_t j = 0; j < n2; j += 2) {
-                        const double2 vj = *reinterpret_cast<const double2*>(s_val + j);
-                        c0 += (vj.x > v0 || (vj.x == v0 && j < id0)) ? 1u : 0u;
-                        c0 += (vj.y > v0 || (vj.y == v0 && j + 1 < id0)) ? 1u : 0u;
-                    }
-                } else {
-                    for (uint32_t j = 0; j < n2; j += 2) {
-                        const double2 vj = *reinterpret_cast<const double2*>(s_val + j);
-                        c0 += (vj.x > v0 || (vj.x == v0 && j < id0)) ? 1u : 0u;
-                        c0 += (vj.y > v0 || (vj.y == v0 && j + 1 < id0)) ? 1u : 0u;
-                        c1 += (vj.x > v1 || (vj.x == v1 && j < id1)) ? 1u : 0u;
-                        c1 += (vj.y > v1 || (vj.y == v1 && j + 1 < id1)) ? 1u : 0u;
-                    }
-                }
-            } else {   // only the listed candidates hold values
-                for (uint32_t q = 0; q < n_listed; ++q) {
-                    const uint32_t j = s_cand[q];
-                    const double vj = s_val[j];
-                    c0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
-                    c1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
+        uint32_t c0 = d.n_used, c1 = d.n_used;   // "not among the first n_used" until shown otherwise
+        if (EXACT || listed_all) {   // block-uniform: every thread takes part in the shuffles and the barrier
+            // Two levels, as for the f32 k-th search: rank inside the warp's 32 experts by
+            // shuffles, then only each warp's first n_used are ranked against each other.
+            __shared__ double s_dv[2][8][16];
+            __shared__ uint32_t s_di[2][8][16];
+            const bool two = d.n_expert > 256;
+            uint32_t q0 = 0, q1 = 0;
+#pragma unroll 4
+            for (uint32_t sft = 1; sft < 32; ++sft) {
+                const uint32_t src = (lane + sft) & 31u;
+                const double o0 = __shfl_sync(0xFFFFFFFFu, v0, src);
+                q0 += (o0 > v0 || (o0 == v0 && src < lane)) ? 1u : 0u;
+                if (two) {
+                    const double o1 = __shfl_sync(0xFFFFFFFFu, v1, src);
+                    q1 += (o1 > v1 || (o1 == v1 && src < lane)) ? 1u : 0u;
                 }
             }
-            if (m0 && c0 < d.n_used) { s_best_id[c0] = id0; s_best_val[c0] = v0; }
-            if (m1 && c1 < d.n_used) { s_best_id[c1] = id1; s_best_val[c1] = v1; }
+            if (q0 < d.n_used) { s_dv[0][warp][q0] = v0; s_di[0][warp][q0] = id0; }
+            if (two && q1 < d.n_used) { s_dv[1][warp][q1] = v1; s_di[1][warp][q1] = id1; }
+            __syncthreads();
+            if (q0 < d.n_used || (two && q1 < d.n_used)) {
+                uint32_t k0 = 0, k1 = 0;
+                for (uint32_t st = 0; st < (two ? 2u : 1u); ++st)
+                    for (uint32_t w = 0; w < 8; ++w)
+                        for (uint32_t q = 0; q < d.n_used; ++q) {
+                            const double vj = s_dv[st][w][q];
+                            const uint32_t j = s_di[st][w][q];
+                            k0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
+                            k1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
+                        }
+                if (q0 < d.n_used) c0 = k0;
+                if (two && q1 < d.n_used) c1 = k1;
+            }
+        } else if (m0 || m1) {   // only the listed candidates hold values
+            uint32_t k0 = 0, k1 = 0;
+            for (uint32_t q = 0; q < n_listed; ++q) {
+                const uint32_t j = s_cand[q];
+                const double vj = s_val[j];
+                k0 += (vj > v0 || (vj == v0 && j < id0)) ? 1u : 0u;
+                k1 += (vj > v1 || (vj == v1 && j < id1)) ? 1u : 0u;
+            }
+            c0 = k0; c1 = k1;
         }
+        if (m0 && c0 < d.n_used) { s_best_id[c0] = id0; s_best_val[c0] = v0; }
+        if (m1 && c1 < d.n_used) { s_best_id[c1] = id1; s_best_val[c1] = v1; }
     }
     __syncthreads();
     if (warp == 0) {
