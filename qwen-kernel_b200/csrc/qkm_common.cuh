@@ -114,23 +114,26 @@ __device__ __forceinline__ void dequant8<QKM_TYPE_Q8_0>(const uint8_t* __restric
 }
 template <>
 __device__ __forceinline__ void dequant8<QKM_TYPE_Q6_K>(const uint8_t* __restrict__ row, uint32_t k, float* w) {
-    const uint8_t* b = row + (size_t)(k >> 8) * 210;
+    const uint8_t* b = row + (size_t)(k >> 8) * 210;   // blocks are 2-byte aligned
     const uint32_t n = k & 255u;          // element within the block
     const uint32_t half = n >> 7;         // which 128-element half
     const uint32_t quad = (n >> 5) & 3u;  // which 32-element quarter of the half
     const uint32_t l = n & 31u;           // multiple of 8
-    const uint8_t* ql = b + 64 * half + ((quad & 1u) ? 32 : 0) + l;
+    const uint8_t* ql = b + 64 * half + 32 * (quad & 1u) + l;
     const uint8_t* qh = b + 128 + 32 * half + l;
     const float d = f16_bits_to_f32(ld_u16(b + 208));
     const float sc = (float)(int8_t)b[192 + (n >> 4)];
     const float ds = d * sc;  // (d * sc) * q, left to right as the reference writes it
-    const uint32_t hs = 2 * quad;
-    const bool hi = quad >= 2;
+    const uint32_t nib = (quad >> 1) << 2, hs = 2 * quad;
+    // four values at a time: low nibbles (or high, for the upper quarters) and the two high
+    // bits are isolated with word-wide masks, then each byte is one 6-bit value
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-        const uint32_t lo4 = hi ? (uint32_t)(ql[i] >> 4) : (uint32_t)(ql[i] & 0xF);
-        const int q = (int)(lo4 | (((qh[i] >> hs) & 3u) << 4)) - 32;
-        w[i] = ds * (float)q;
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t lo = (ld_u32_a2(ql + 4 * h) >> nib) & 0x0F0F0F0Fu;
+        const uint32_t hi = ((ld_u32_a2(qh + 4 * h) >> hs) & 0x03030303u) << 4;
+        const uint32_t q = lo | hi;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) w[4 * h + i] = ds * (float)((int)((q >> (8 * i)) & 0xFFu) - 32);
     }
 }
 template <>

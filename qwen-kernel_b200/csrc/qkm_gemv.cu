@@ -156,23 +156,6 @@ __device__ __forceinline__ void unit8<QKM_TYPE_IQ3_XXS>(const uint8_t* __restric
         w[j + 4] = __uint_as_float(__float_as_uint(c) ^ ((sg << (27 - j)) & 0x80000000u));
     }
 }
-template <>
-__device__ __forceinline__ void unit8<QKM_TYPE_Q6_K>(const uint8_t* __restrict__ row, uint32_t k, float* w, const Luts& lut) {
-    const uint8_t* b = row + (size_t)(k >> 8) * 210;    // blocks are 2-byte aligned
-    const uint32_t n = k & 255u, half = n >> 7, quad = (n >> 5) & 3u, l = n & 31u;
-    const uint8_t* ql = b + 64 * half + 32 * (quad & 1u) + l;
-    const uint8_t* qh = b + 128 + 32 * half + l;
-    const float ds = f16_bits_to_f32(ld_u16(b + 208)) * (float)(int8_t)b[192 + (n >> 4)];
-    const uint32_t nib = (quad >> 1) << 2, hs = 2 * quad;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const uint32_t lo = (ld_u32_a2(ql + 4 * h) >> nib) & 0x0F0F0F0Fu;
-        const uint32_t hi = ((ld_u32_a2(qh + 4 * h) >> hs) & 0x03030303u) << 4;
-        const uint32_t q = lo | hi;                      // four 6-bit values, one per byte
-#pragma unroll
-        for (int i = 0; i < 4; ++i) w[4 * h + i] = ds * (float)((int)((q >> (8 * i)) & 0xFFu) - 32);
-    }
-}
 }  // namespace gv
 
 template <int TYPE>
