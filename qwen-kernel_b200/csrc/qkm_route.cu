@@ -1032,7 +1032,7 @@ __device__ __forceinline__ uint32_t gw_local_expert(const qkm_sel* __restrict__ 
 
 __global__ void __launch_bounds__(gw::kWarps * 32)
 group_count_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used, uint32_t n_expert,
-                   uint32_t expert_first, uint32_t expert_count, uint32_t* __restrict__ hist) {
+                   uint32_t expert_first, uint32_t expert_count, uint32_t n_runs, uint32_t* __restrict__ hist) {
     extern __shared__ uint32_t s_cnt[];   // [kWarps][expert_count]
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t run = blockIdx.x * gw::kWarps + warp;
@@ -1049,42 +1049,65 @@ group_count_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used
     }
     __syncwarp();
     if (p0 < np)
-        for (uint32_t e = lane; e < expert_count; e += 32) hist[(size_t)run * expert_count + e] = mine[e];
+        for (uint32_t e = lane; e < expert_count; e += 32) hist[(size_t)e * n_runs + run] = mine[e];
 }
 
-__global__ void __launch_bounds__(512)
-group_scan_kernel(uint32_t* __restrict__ hist, uint32_t n_runs, uint32_t expert_count, uint32_t* __restrict__ offsets) {
-    __shared__ uint32_t s_scan[512];
-    const uint32_t e = threadIdx.x;
-    uint32_t total = 0;
-    if (e < expert_count)
-        for (uint32_t r = 0; r < n_runs; ++r) {
-            const uint32_t v = hist[(size_t)r * expert_count + e];
-            hist[(size_t)r * expert_count + e] = total;
-            total += v;
+// hist is [expert][run]: one warp per expert turns its row of counts into exclusive prefix sums
+// (32 runs per step, coalesced) and leaves the expert's total in totals[e].
+__global__ void __launch_bounds__(256)
+group_scan_kernel(uint32_t* __restrict__ hist, uint32_t n_runs, uint32_t expert_count, uint32_t* __restrict__ totals) {
+    const uint32_t e = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31u;
+    if (e >= expert_count) return;
+    uint32_t* row = hist + (size_t)e * n_runs;
+    uint32_t run_total = 0;
+    for (uint32_t r0 = 0; r0 < n_runs; r0 += 32) {
+        const uint32_t r = r0 + lane;
+        const uint32_t v = r < n_runs ? row[r] : 0u;
+        uint32_t inc = v;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= (uint32_t)o) inc += up;
         }
-    s_scan[e] = total;
-    __syncthreads();
-    for (uint32_t o = 1; o < 512; o <<= 1) {
-        const uint32_t v = e >= o ? s_scan[e - o] : 0;
-        __syncthreads();
-        s_scan[e] += v;
-        __syncthreads();
+        if (r < n_runs) row[r] = run_total + inc - v;
+        run_total += __shfl_sync(0xFFFFFFFFu, inc, 31);
     }
-    if (e < expert_count) offsets[e] = s_scan[e] - total;
-    if (e == 511) offsets[expert_count] = s_scan[511];
+    if (lane == 0) totals[e] = run_total;
 }
 
 __global__ void __launch_bounds__(gw::kWarps * 32)
 group_place_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used, uint32_t n_expert,
-                   uint32_t expert_first, uint32_t expert_count, const uint32_t* __restrict__ hist,
-                   const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, uint32_t* __restrict__ pos_of) {
+                   uint32_t expert_first, uint32_t expert_count, uint32_t n_runs, const uint32_t* __restrict__ hist,
+                   const uint32_t* __restrict__ totals, uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs,
+                   uint32_t* __restrict__ pos_of) {
     extern __shared__ uint32_t s_cnt[];   // [kWarps][expert_count]: pairs of the run placed so far, per expert
+    __shared__ uint32_t s_off[513];       // exclusive scan of the expert totals (every block redoes it: 512 adds)
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t run = blockIdx.x * gw::kWarps + warp;
     uint32_t* mine = s_cnt + (size_t)warp * expert_count;
     for (uint32_t e = lane; e < expert_count; e += 32) mine[e] = 0;
-    __syncwarp();
+    {
+        const uint32_t e = threadIdx.x;   // 512 threads, expert_count <= 512
+        const uint32_t tot = e < expert_count ? totals[e] : 0u;
+        uint32_t inc = tot;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t up = __shfl_up_sync(0xFFFFFFFFu, inc, o);
+            if (lane >= (uint32_t)o) inc += up;
+        }
+        __shared__ uint32_t s_wtot[16];
+        if (lane == 31) s_wtot[warp] = inc;
+        __syncthreads();
+        uint32_t base = 0;
+        for (uint32_t w = 0; w < warp; ++w) base += s_wtot[w];
+        s_off[e] = base + inc - tot;
+        if (e == 511) s_off[512] = base + inc;
+        __syncthreads();
+        if (blockIdx.x == 0) {
+            if (e < expert_count) offsets[e] = s_off[e];
+            if (e == 0) offsets[expert_count] = s_off[512];
+        }
+    }
     const uint32_t p0 = run * gw::kRun;
     for (uint32_t i = 0; i < gw::kRun; i += 32) {
         const uint32_t p = p0 + i + lane;
@@ -1105,7 +1128,7 @@ group_place_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used
             const uint32_t t = p / n_used, s = p - t * n_used;
             uint32_t pos = gw::kInvalid;
             if (e != gw::kInvalid) {
-                pos = offsets[e] + hist[(size_t)run * expert_count + e] + before + rank;
+                pos = s_off[e] + hist[(size_t)e * n_runs + run] + before + rank;
                 pairs[pos] = (t << 4) | s;
             }
             if (pos_of) pos_of[t * (n_used + 1) + s] = pos;
@@ -1115,7 +1138,7 @@ group_place_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used
 
 size_t group_wide_scratch_bytes(uint32_t n_tokens, uint32_t n_used, uint32_t expert_count) {
     const size_t runs = ((size_t)n_tokens * n_used + gw::kRun - 1) / gw::kRun;
-    return (runs + gw::kWarps) * expert_count * sizeof(uint32_t);
+    return ((runs + gw::kWarps) * expert_count + 512) * sizeof(uint32_t);   // [expert][run] counts, then the expert totals
 }
 
 cudaError_t launch_group_pairs_wide(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
@@ -1130,10 +1153,11 @@ cudaError_t launch_group_pairs_wide(const Launch& L, const qkm_dims& d, const qk
         cudaError_t e = cudaMemsetAsync(offsets, 0, (expert_count + 1) * sizeof(uint32_t), L.stream);
         return e;
     }
-    group_count_kernel<<<blocks, gw::kWarps * 32, smem, L.stream>>>(sel, np, d.n_used, d.n_expert, expert_first, expert_count, hist);
-    group_scan_kernel<<<1, 512, 0, L.stream>>>(hist, n_runs, expert_count, offsets);
-    group_place_kernel<<<blocks, gw::kWarps * 32, smem, L.stream>>>(sel, np, d.n_used, d.n_expert, expert_first, expert_count,
-                                                                      hist, offsets, pairs, pos_of);
+    uint32_t* totals = hist + (size_t)n_runs * expert_count;
+    group_count_kernel<<<blocks, gw::kWarps * 32, smem, L.stream>>>(sel, np, d.n_used, d.n_expert, expert_first, expert_count, n_runs, hist);
+    group_scan_kernel<<<(expert_count + 7) / 8, 256, 0, L.stream>>>(hist, n_runs, expert_count, totals);
+    group_place_kernel<<<blocks, gw::kWarps * 32, smem, L.stream>>>(sel, np, d.n_used, d.n_expert, expert_first, expert_count, n_runs,
+                                                                      hist, totals, offsets, pairs, pos_of);
     L.count(3);
     return cudaGetLastError();
 }
