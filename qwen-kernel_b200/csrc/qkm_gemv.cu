@@ -158,7 +158,9 @@ __device__ __forceinline__ void unit8<QKM_TYPE_IQ3_XXS>(const uint8_t* __restric
 }
 }  // namespace gv
 
-template <int TYPE>
+// XREG: K == 2048 and one activation row - a lane always meets the same eight 8-column units, so
+// it keeps its 64 activation values in registers and shared memory carries weight bytes only.
+template <int TYPE, bool XREG>
 __global__ void __launch_bounds__(gv::kWarps * 32)
 gemv_stream_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, float* __restrict__ y,
                    uint32_t M, uint32_t K, uint32_t n, uint32_t rows_per_tile, uint32_t stage_bytes,
@@ -193,12 +195,34 @@ gemv_stream_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, f
     __syncthreads();
     bool timed_out = false;
     uint32_t cnt = 0;
+    float4 xr[XREG ? 16 : 1];
+    if (XREG) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            xr[2 * i] = *reinterpret_cast<const float4*>(s_x + (lane + 32 * i) * 8);
+            xr[2 * i + 1] = *reinterpret_cast<const float4*>(s_x + (lane + 32 * i) * 8 + 4);
+        }
+    }
     for (uint32_t tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++cnt) {
         const uint32_t stage = cnt % gv::kStages, parity = (cnt / gv::kStages) & 1u;
         if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), parity)) timed_out = true;
         const uint8_t* tb = ring_ptr + (size_t)stage * stage_bytes;
         for (uint32_t r = warp; r < rows_per_tile; r += gv::kWarps) {
             const uint8_t* row = tb + (size_t)r * rb;
+            if (XREG) {
+                float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float w[8];
+                    gv::unit8<TYPE>(row, (lane + 32 * i) * 8, w, s_lut);
+                    const float4 a = xr[2 * i], b = xr[2 * i + 1];
+                    acc0 += w[0] * a.x; acc1 += w[1] * a.y; acc0 += w[2] * a.z; acc1 += w[3] * a.w;
+                    acc0 += w[4] * b.x; acc1 += w[5] * b.y; acc0 += w[6] * b.z; acc1 += w[7] * b.w;
+                }
+                const float acc = warp_sum(acc0 + acc1);
+                if (lane == 0) y[(size_t)tile * rows_per_tile + r] = acc;
+                continue;
+            }
             for (uint32_t t = 0; t < n; ++t) {
                 const float* xt = s_x + (size_t)t * K;
                 float acc0 = 0.f, acc1 = 0.f;
@@ -301,11 +325,17 @@ static cudaError_t gemv_stream_launch(const Launch& L, const uint8_t* W, const f
     if (n_tiles == 0) return cudaSuccess;
     const uint32_t stage_bytes = (uint32_t)((rows_per_tile * rb + 127) / 128 * 128);
     const size_t smem = (size_t)n * K * 4 + (size_t)gv::kStages * stage_bytes;
-    cudaError_t e = cudaFuncSetAttribute(gemv_stream_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const bool xreg = K == 2048 && n == 1;
+    cudaError_t e = xreg ? cudaFuncSetAttribute(gemv_stream_kernel<TYPE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                         : cudaFuncSetAttribute(gemv_stream_kernel<TYPE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    const uint32_t per_sm = smem <= 72 * 1024 ? 3u : (smem <= 110 * 1024 ? 2u : 1u);
+    uint32_t per_sm = smem <= 72 * 1024 ? 3u : (smem <= 110 * 1024 ? 2u : 1u);
+    if (xreg && per_sm > 2) per_sm = 2;   // about 100 registers per thread: two blocks fit
     const uint32_t blocks = n_tiles < per_sm * n_sms ? n_tiles : per_sm * n_sms;
-    gemv_stream_kernel<TYPE><<<blocks, gv::kWarps * 32, smem, L.stream>>>(W, x, y, M, K, n, rows_per_tile, stage_bytes, status);
+    if (xreg)
+        gemv_stream_kernel<TYPE, true><<<blocks, gv::kWarps * 32, smem, L.stream>>>(W, x, y, M, K, n, rows_per_tile, stage_bytes, status);
+    else
+        gemv_stream_kernel<TYPE, false><<<blocks, gv::kWarps * 32, smem, L.stream>>>(W, x, y, M, K, n, rows_per_tile, stage_bytes, status);
     L.count();
     *rows_done = n_tiles * rows_per_tile;
     return cudaGetLastError();

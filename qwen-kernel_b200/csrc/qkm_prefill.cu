@@ -604,6 +604,16 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
 // * |w| * |x|, below 2^-9 * |w| * |x| for K <= 4096.
 // Block = 128 experts (M) x up to 128 tokens (N); 256 producer threads copy both operand tiles
 // into the swizzled layout, the ninth warp issues the MMAs.
+constexpr int kLgStages = 4;   // stages of the logits kernel (one block per SM: it is a small grid)
+constexpr int kLgDepth = 3;    // k-steps of asynchronous copies in flight
+
+__device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 struct LgRegs { uint4 a[4], b[4]; };
 
 template <int TYPE>
@@ -625,22 +635,22 @@ __device__ __forceinline__ void lg_fetch(LgRegs& r, const uint8_t* __restrict__ 
 }
 
 template <int TYPE>
-__global__ void __launch_bounds__(pf::kBlock, 2)
+__global__ void __launch_bounds__(pf::kBlock, 1)
 logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__ xh, const float* __restrict__ x_inv_scale,
                   float* __restrict__ logits, uint32_t n_expert, uint32_t K, uint32_t n_tokens, uint32_t* __restrict__ status) {
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
-    __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
+    __shared__ __align__(8) unsigned long long s_bar[2 * kLgStages + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const uint32_t t0 = blockIdx.x * 128u, e0 = blockIdx.y * 128u;
     const uint32_t n = min(128u, n_tokens - t0), n_mma = (n + 15u) & ~15u, KS = K / 64;
     if (tid == 0) {
-        for (int s = 0; s < pf::kStages; ++s) {
+        for (int s = 0; s < kLgStages; ++s) {
             mbar_init(smem_addr(&s_bar[s]), 1);
-            mbar_init(smem_addr(&s_bar[pf::kStages + s]), pf::kThreads);
+            mbar_init(smem_addr(&s_bar[kLgStages + s]), pf::kThreads);
         }
-        mbar_init(smem_addr(&s_bar[2 * pf::kStages]), 1);
+        mbar_init(smem_addr(&s_bar[2 * kLgStages]), 1);
         mbar_fence_init();
     }
     if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), 128); umma::tmem_relinquish(); }
@@ -653,24 +663,52 @@ logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__
     if (tid >= pf::kThreads) {
         if (lane == 0) {
             for (uint32_t ks = 0; ks < KS; ++ks) {
-                const uint32_t stage = ks % pf::kStages;
-                if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages + stage]), (ks / pf::kStages) & 1u)) timed_out = true;
+                const uint32_t stage = ks % kLgStages;
+                if (!mbar_wait_bounded(smem_addr(&s_bar[kLgStages + stage]), (ks / kLgStages) & 1u)) timed_out = true;
                 umma::fence_after_sync();
                 const uint32_t a = smem_addr(smem + stage * 2 * pf::kTileBytes), b = a + pf::kTileBytes;
 #pragma unroll
                 for (int j = 0; j < 4; ++j)
                     umma::mma_f16_ss(tmem, umma::smem_desc(a + 32 * j), umma::smem_desc(b + 32 * j), idesc, (ks | (uint32_t)j) != 0);
                 umma::commit(smem_addr(&s_bar[stage]));
-                if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[2 * pf::kStages]));
+                if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[2 * kLgStages]));
             }
         }
     } else {
+        if (TYPE == QKM_TYPE_F16) {
+            // Both operands are plain copies: 16-byte asynchronous copies straight into the
+            // swizzled tiles, kLgDepth k-steps in flight, so the global-load latency of a
+            // block that has the SM almost to itself (small batches) is hidden.
+            auto issue = [&](uint32_t ks) {
+                const uint32_t stage = ks % kLgStages;
+                if (ks >= (uint32_t)kLgStages)
+                    if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / kLgStages) - 1) & 1u)) timed_out = true;
+                const uint32_t st = smem_addr(smem + stage * 2 * pf::kTileBytes), k0 = ks * 64;
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const uint32_t qd = tid + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
+                    cp_async16(st + umma::sw128_chunk(row, c), router + ((size_t)(e0 + row) * K + k0 + 8 * c) * 2);
+                    if (qd < n_mma * 8) {
+                        const uint32_t src_row = row < n ? row : 0u;   // rows past n feed accumulator columns nobody reads
+                        cp_async16(st + pf::kTileBytes + umma::sw128_chunk(row, c), xh + (size_t)(t0 + src_row) * K + k0 + 8 * c);
+                    }
+                }
+                cp_async_commit();
+            };
+            for (uint32_t ks = 0; ks < (uint32_t)kLgDepth && ks < KS; ++ks) issue(ks);
+            for (uint32_t ks = 0; ks < KS; ++ks) {
+                if (ks + kLgDepth < KS) issue(ks + kLgDepth); else cp_async_commit();   // keep the group count in step
+                cp_async_wait<kLgDepth>();          // the copies of step ks have landed
+                umma::fence_smem_to_async();
+                mbar_arrive(smem_addr(&s_bar[kLgStages + ks % kLgStages]));
+            }
+        } else {
         LgRegs cur;
         lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K, 0);
         for (uint32_t ks = 0; ks < KS; ++ks) {
-            const uint32_t stage = ks % pf::kStages;
-            if (ks >= (uint32_t)pf::kStages)
-                if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
+            const uint32_t stage = ks % kLgStages;
+            if (ks >= (uint32_t)kLgStages)
+                if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / kLgStages) - 1) & 1u)) timed_out = true;
             uint8_t* st = smem + stage * 2 * pf::kTileBytes;
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
@@ -679,10 +717,11 @@ logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__
                 if (qd < n_mma * 8) *reinterpret_cast<uint4*>(st + pf::kTileBytes + umma::sw128_chunk(row, c)) = cur.b[i];
             }
             umma::fence_smem_to_async();
-            mbar_arrive(smem_addr(&s_bar[pf::kStages + stage]));
+            mbar_arrive(smem_addr(&s_bar[kLgStages + stage]));
             if (ks + 1 < KS) lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K, (ks + 1) * 64);
         }
-        if (!mbar_wait_bounded(smem_addr(&s_bar[2 * pf::kStages]), 0)) timed_out = true;
+        }
+        if (!mbar_wait_bounded(smem_addr(&s_bar[2 * kLgStages]), 0)) timed_out = true;
         umma::fence_after_sync();
         const uint32_t lg = warp & 3u, e = e0 + 32 * lg + lane;
         for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += 2) {
@@ -707,7 +746,7 @@ cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t route
                               uint32_t* status) {
     if (n_tokens == 0) return cudaSuccess;
     if (d.n_expert % 128 || d.n_embd % 64 || d.n_embd > 4096) return cudaErrorInvalidValue;
-    const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + 1024;
+    const size_t smem = (size_t)kLgStages * 2 * pf::kTileBytes + 1024;
     const dim3 grid((n_tokens + 127) / 128, d.n_expert / 128);
     cudaError_t e;
     if (router_type == QKM_TYPE_F16) {
