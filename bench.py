@@ -385,6 +385,22 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
         from qwen_kernel_b200.expert_parallel import ExpertParallel
         ep = ExpertParallel(ctx, dims.n_embd, dims.n_used, max_local_tokens=n_max, max_recv_rows=Tmax, device=dev)
     out = {"layers_rotated": PL, "chunks": {}}
+    # the peer-memory form (rows stored straight into the owners' buffers over NVLink, partial rows
+    # summed while read back): every rank must have mapped every peer, else all ranks leave it out
+    peer = None
+    if world > 1:
+        import torch.distributed as dist
+        from qwen_kernel_b200.expert_parallel import PeerExpertParallel
+        why = ""
+        try:
+            peer = PeerExpertParallel(ctx, max_local_tokens=n_max, device=dev)
+        except Exception as e:   # noqa: BLE001  (reported in the JSON line)
+            why = f"{type(e).__name__}: {e}"[:200]
+        ok = torch.tensor([0 if peer is None else 1], dtype=torch.int32, device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        if int(ok.item()) == 0:
+            peer = None
+            out["peer_memory_unavailable"] = why or "a peer rank could not map the buffers"
     steps, warm = max(3, args.steps // 4), 3
     for T in PREFILL_CHUNKS:
         n = T // world
@@ -414,6 +430,22 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             off = sum(send) - send[rank]
             entry_["rows_sent_off_gpu_per_rank"] = off
             entry_["nvlink_bytes_per_rank_per_layer"] = off * (dims.n_embd * 4 + 160) + off * dims.n_embd * 4
+            entry_["exchange"] = "NCCL all-to-all"
+        if peer:
+            def step_peer():
+                for l in range(PL):
+                    peer.forward(l, x[l], n, y[l], slot_rows=n)
+
+            y.zero_()
+            step_peer(); R.barrier()
+            err_p = syn.rel_err_rows(y[0, :k].cpu().numpy(), want)
+            assert err_p < 2e-2, f"peer-memory expert parallel T={T}: error {err_p}"
+            n0 = ctx.launch_count()
+            ms_p = timed(torch, R, stream, step_peer, steps, warm) / PL
+            entry_["peer_memory"] = {"us_per_layer": ms_p * 1e3, "tok_s": T / (ms_p * 1e-3),
+                                     "rel_err_vs_oracle": R.max_over_ranks(err_p),
+                                     "launches_per_layer": (ctx.launch_count() - n0) / ((steps + warm) * PL),
+                                     "exchange": "stores into / loads from peer-mapped buffers, two one-word all-reduces as barriers"}
         out["chunks"][str(T)] = entry_
     if world == 1:
         ctx.profile_enable(True)

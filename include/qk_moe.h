@@ -339,6 +339,39 @@ QKM_API int qkm_ep_expert_forward(qkm_ctx *c, uint32_t layer, const float *xrecv
 QKM_API int qkm_ep_combine(qkm_ctx *c, uint32_t n_tokens, uint32_t n_ranks, const float *back,
                            float *y);
 
+/* Expert parallel over peer memory (NVLink loads and stores), NO COUNTERPART IN THE
+ * REFERENCE.  The same layer without an all-to-all: each rank keeps receive buffers of
+ * n_ranks * slot_cap rows and has every peer's buffers mapped.  A token's row and record
+ * are stored by the push kernel straight into the buffers of the ranks that own its
+ * experts, at row (source rank * slot_rows + token), so no counts travel and nothing is
+ * packed; the pull kernel sums the partial rows while reading them from the owners.
+ *   qkm_ep_peer_setup(c, n_ranks, rank, slot_cap)  once; n_ranks * slot_cap <= max_tokens,
+ *                          n_ranks <= 16, the context opened on shard `rank`
+ *   qkm_ep_peer_export / qkm_ep_peer_import  QKM_EP_HANDLE_BYTES of CUDA IPC handles per
+ *                          rank, exchanged by the caller (processes of one node), or
+ *   qkm_ep_peer_buffers / qkm_ep_peer_set    raw device pointers (one process, several
+ *                          GPUs with peer access enabled)
+ * Per layer, all ranks with the same slot_rows (>= every rank's n_tokens, <= slot_cap):
+ *   qkm_ep_push(c, layer, x, n_tokens, slot_rows)   route + store rows into the owners
+ *   qkm_ep_shared(c, layer, x, n_tokens)
+ *   (caller)  barrier: any collective of the ranks enqueued on the context's stream
+ *   qkm_ep_forward_slots(c, layer, slot_rows)       resident experts over all slots
+ *   (caller)  barrier
+ *   qkm_ep_pull(c, n_tokens, slot_rows, y)          y = shared + partial rows of the owners
+ * The two barriers are all the ordering the buffers need from one layer to the next.
+ * No kernel waits on another GPU, nothing is read by the host. */
+#define QKM_EP_HANDLE_BYTES 192
+QKM_API int qkm_ep_peer_setup(qkm_ctx *c, uint32_t n_ranks, uint32_t rank, uint32_t slot_cap);
+QKM_API int qkm_ep_peer_buffers(qkm_ctx *c, void **xrecv, void **selrecv, void **partial);
+QKM_API int qkm_ep_peer_set(qkm_ctx *c, uint32_t peer, void *xrecv, void *selrecv,
+                            const void *partial);
+QKM_API int qkm_ep_peer_export(qkm_ctx *c, void *handles);
+QKM_API int qkm_ep_peer_import(qkm_ctx *c, uint32_t peer, const void *handles);
+QKM_API int qkm_ep_push(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
+                        uint32_t slot_rows);
+QKM_API int qkm_ep_forward_slots(qkm_ctx *c, uint32_t layer, uint32_t slot_rows);
+QKM_API int qkm_ep_pull(qkm_ctx *c, uint32_t n_tokens, uint32_t slot_rows, float *y);
+
 /* Router logits + selection WITHOUT any device allocation and without a context.
  * NO COUNTERPART IN THE REFERENCE: it exists for hosts that may not take memory from
  * the driver while they run (a server that already owns all free HBM through its own

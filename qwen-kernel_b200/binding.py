@@ -35,6 +35,7 @@ class LayerWeights(C.Structure):
                 ("gate_shexp", C.c_void_p), ("up_shexp", C.c_void_p), ("down_shexp", C.c_void_p)]
 
 
+EP_HANDLE_BYTES = 192   # QKM_EP_HANDLE_BYTES: three CUDA IPC handles
 SEL_DTYPE = np.dtype([("ids", np.uint32, 16), ("w", np.float32, 16), ("w_shared", np.float32),
                       ("route_done", np.uint32), ("pad", np.float32, 6)])
 assert SEL_DTYPE.itemsize == 160
@@ -103,6 +104,14 @@ SIGNATURES = {
     "qkm_ep_shared": (_I, [_VP, _U32, _VP, _U32]),
     "qkm_ep_expert_forward": (_I, [_VP, _U32, _VP, _VP, _U32, _VP]),
     "qkm_ep_combine": (_I, [_VP, _U32, _U32, _VP, _VP]),
+    "qkm_ep_peer_setup": (_I, [_VP, _U32, _U32, _U32]),
+    "qkm_ep_peer_buffers": (_I, [_VP, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), C.POINTER(C.c_void_p)]),
+    "qkm_ep_peer_set": (_I, [_VP, _U32, _VP, _VP, _VP]),
+    "qkm_ep_peer_export": (_I, [_VP, C.c_char_p]),
+    "qkm_ep_peer_import": (_I, [_VP, _U32, C.c_char_p]),
+    "qkm_ep_push": (_I, [_VP, _U32, _VP, _U32, _U32]),
+    "qkm_ep_forward_slots": (_I, [_VP, _U32, _U32]),
+    "qkm_ep_pull": (_I, [_VP, _U32, _U32, _VP]),
     "qkm_route_select_static": (_I, [_I, _VP, C.POINTER(Dims), _U32, _VP, _VP, _VP, _VP, _U32, C.c_char_p, _SZ]),
 }
 
@@ -341,6 +350,38 @@ class Context:
 
     def ep_combine(self, n, n_ranks, back, y):
         self.check(self.lib.qkm_ep_combine(self.h, n, n_ranks, _p(back), _p(y)))
+
+    # -- expert parallel over peer memory
+    def ep_peer_setup(self, n_ranks, rank, slot_cap):
+        self.check(self.lib.qkm_ep_peer_setup(self.h, n_ranks, rank, slot_cap))
+
+    def ep_peer_buffers(self):
+        """Device addresses (xrecv, selrecv, partial) of this rank's receive buffers."""
+        p = [C.c_void_p() for _ in range(3)]
+        self.check(self.lib.qkm_ep_peer_buffers(self.h, *[C.byref(v) for v in p]))
+        return tuple(int(v.value) for v in p)
+
+    def ep_peer_set(self, peer, xrecv, selrecv, partial):
+        self.check(self.lib.qkm_ep_peer_set(self.h, peer, _p(xrecv), _p(selrecv), _p(partial)))
+
+    def ep_peer_export(self) -> bytes:
+        buf = C.create_string_buffer(EP_HANDLE_BYTES)
+        self.check(self.lib.qkm_ep_peer_export(self.h, buf))
+        return buf.raw
+
+    def ep_peer_import(self, peer, handles: bytes):
+        if len(handles) != EP_HANDLE_BYTES:
+            raise ValueError(f"expected {EP_HANDLE_BYTES} bytes of handles, got {len(handles)}")
+        self.check(self.lib.qkm_ep_peer_import(self.h, peer, handles))
+
+    def ep_push(self, layer_idx, x, n, slot_rows):
+        self.check(self.lib.qkm_ep_push(self.h, layer_idx, _p(x), n, slot_rows))
+
+    def ep_forward_slots(self, layer_idx, slot_rows):
+        self.check(self.lib.qkm_ep_forward_slots(self.h, layer_idx, slot_rows))
+
+    def ep_pull(self, n, slot_rows, y):
+        self.check(self.lib.qkm_ep_pull(self.h, n, slot_rows, _p(y)))
 
     def profile_enable(self, on=True):
         self.check(self.lib.qkm_profile_enable(self.h, int(on)))

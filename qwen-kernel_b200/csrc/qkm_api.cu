@@ -86,6 +86,11 @@ struct qkm_ctx {
     uint32_t* ep_counts_host = nullptr;  // pinned mirror
     uint32_t* ep_send_tok = nullptr;     // [max_tokens * min(n_ranks, n_used)]
     uint32_t* ep_send_pos = nullptr;     // [max_tokens][n_ranks]
+    // peer-memory form of the exchange: this rank's receive buffers and every rank's as mapped here
+    uint32_t pm_ranks = 0, pm_rank = 0, pm_cap = 0;   // slot_cap rows per source rank
+    float* pm_xrecv = nullptr; qkm_sel* pm_selrecv = nullptr; float* pm_partial = nullptr;
+    EpPeerTable pm_peers{};
+    void* pm_opened[kMaxPeerRanks][3] = {};           // mappings this context opened from handles
     // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_planes = nullptr;
@@ -292,6 +297,8 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
+    for (auto& o : c->pm_opened) for (void* p : o) if (p) cudaIpcCloseMemHandle(p);
+    for (void* p : {(void*)c->pm_xrecv, (void*)c->pm_selrecv, (void*)c->pm_partial}) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->ep_counts_host) cudaFreeHost(c->ep_counts_host);
     if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
@@ -994,12 +1001,9 @@ static int ep_check(qkm_ctx* c, uint32_t n_ranks) {
     return QKM_OK;
 }
 
-static int ep_dispatch_launch(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t n_ranks,
-                              float* xsend, qkm_sel* selsend) {
-    if (int rc = layer_ready(c, layer)) return rc;
-    if (!x || !xsend || !selsend) return QKM_ERR_ARG;
-    if (int rc = check_tokens(c, n)) return rc;
-    if (int rc = ep_check(c, n_ranks)) return rc;
+// router logits and selection of the n local tokens into c->sel (digit planes / f16 rows as the
+// shared-expert kernels of that size want them)
+static int ep_route_local(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n) {
     const qkm_layer_dev& ld = c->layers[layer];
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
@@ -1012,6 +1016,17 @@ static int ep_dispatch_launch(qkm_ctx* c, uint32_t layer, const float* x, uint32
     QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
                                       planes ? c->xplanes : nullptr, planes ? c->xscale : nullptr, tc ? c->xb : nullptr,
                                       tc ? c->xscale : nullptr, c->status));
+    return QKM_OK;
+}
+
+static int ep_dispatch_launch(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t n_ranks,
+                              float* xsend, qkm_sel* selsend) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (!x || !xsend || !selsend) return QKM_ERR_ARG;
+    if (int rc = check_tokens(c, n)) return rc;
+    if (int rc = ep_check(c, n_ranks)) return rc;
+    if (int rc = ep_route_local(c, layer, x, n)) return rc;
+    const qkm_dims& d = c->cfg.dims;
     QKM_LAUNCH(c, launch_ep_plan(c->L(), d, c->sel, n, n_ranks, c->ep_counts, c->ep_send_tok, c->ep_send_pos));
     const uint32_t fan = n_ranks < d.n_used ? n_ranks : d.n_used;
     QKM_LAUNCH(c, launch_ep_pack(c->L(), d, x, c->sel, c->ep_send_tok, c->ep_counts + n_ranks, n * fan, xsend, selsend));
@@ -1117,5 +1132,126 @@ extern "C" QKM_API int qkm_ep_combine(qkm_ctx* c, uint32_t n, uint32_t n_ranks, 
     if (int rc = check_tokens(c, n)) return rc;
     if (c->ep_ranks != n_ranks || !c->ep_send_pos) return fail(c, QKM_ERR_MODE, "qkm_ep_combine without a matching qkm_ep_dispatch");
     QKM_LAUNCH(c, launch_ep_combine(c->L(), c->cfg.dims, back, c->ep_send_pos, c->y2, y, n, n_ranks));
+    return QKM_OK;
+}
+
+// ---------------------------------------------------------------- expert parallel over peer memory
+// The same layer without an all-to-all.  Every rank keeps three receive buffers of
+// n_ranks * slot_cap rows (x rows, selection records, partial rows) and maps every peer's:
+//   qkm_ep_peer_setup   : allocate this rank's buffers
+//   qkm_ep_peer_export / qkm_ep_peer_import : CUDA IPC handles between processes of one node,
+//   or qkm_ep_peer_buffers / qkm_ep_peer_set  : raw pointers (one process driving several GPUs)
+// and per layer, with slot_rows (>= every rank's token count, the same on all ranks):
+//   qkm_ep_push         : route the local tokens, store rows + records into the owners' buffers
+//   qkm_ep_shared       : the shared expert (no dependence on the peers)
+//   (host: barrier)     : all pushes have landed
+//   qkm_ep_forward_slots: resident experts over the n_ranks * slot_rows rows -> partial rows
+//   (host: barrier)     : all partial rows are written
+//   qkm_ep_pull         : y = shared + the partial rows, read from the owners' buffers
+// The two barriers also order the reuse of the buffers by the next layer: a rank pushes layer
+// l+1 after the second barrier of layer l, when every rank has finished reading the rows of l,
+// and overwrites its partial rows after the first barrier of l+1, which every rank enters
+// after its pull of l.  Kernels only store to and load from peer memory; none waits.
+
+static int pm_check(qkm_ctx* c, uint32_t slot_rows) {
+    if (!c) return QKM_ERR_ARG;
+    if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
+    if (slot_rows == 0 || slot_rows > c->pm_cap) return fail(c, QKM_ERR_BOUNDS, "slot_rows %u outside 1..%u", slot_rows, c->pm_cap);
+    for (uint32_t r = 0; r < c->pm_ranks; ++r)
+        if (!c->pm_peers.x[r] || !c->pm_peers.sel[r] || !c->pm_peers.partial[r])
+            return fail(c, QKM_ERR_MODE, "buffers of rank %u are not mapped (qkm_ep_peer_import / qkm_ep_peer_set)", r);
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_peer_setup(qkm_ctx* c, uint32_t n_ranks, uint32_t rank, uint32_t slot_cap) {
+    if (!c) return QKM_ERR_ARG;
+    const qkm_dims& d = c->cfg.dims;
+    if (c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup was already called on this context");
+    if (n_ranks == 0 || n_ranks > kMaxPeerRanks || d.n_expert % n_ranks || rank >= n_ranks)
+        return fail(c, QKM_ERR_ARG, "rank %u of %u ranks (at most %u, dividing n_expert %u)", rank, n_ranks, kMaxPeerRanks, d.n_expert);
+    if (c->ecount != d.n_expert / n_ranks || c->efirst != rank * c->ecount)
+        return fail(c, QKM_ERR_MODE, "context holds experts [%u,%u): not shard %u of %u", c->efirst, c->efirst + c->ecount, rank, n_ranks);
+    if (slot_cap == 0 || (uint64_t)slot_cap * n_ranks > c->cfg.max_tokens)
+        return fail(c, QKM_ERR_BOUNDS, "%u ranks x %u rows exceed max_tokens %u", n_ranks, slot_cap, c->cfg.max_tokens);
+    const size_t rows = (size_t)n_ranks * slot_cap;
+    QKM_CUDA(c, cudaMalloc((void**)&c->pm_xrecv, rows * d.n_embd * sizeof(float)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->pm_partial, rows * d.n_embd * sizeof(float)));
+    QKM_CUDA(c, cudaMemset(c->pm_xrecv, 0, rows * d.n_embd * sizeof(float)));
+    QKM_CUDA(c, cudaMemset(c->pm_selrecv, 0xFF, rows * sizeof(qkm_sel)));   // every record empty
+    QKM_CUDA(c, cudaMemset(c->pm_partial, 0, rows * d.n_embd * sizeof(float)));
+    c->pm_ranks = n_ranks; c->pm_rank = rank; c->pm_cap = slot_cap;
+    c->pm_peers.x[rank] = c->pm_xrecv; c->pm_peers.sel[rank] = c->pm_selrecv; c->pm_peers.partial[rank] = c->pm_partial;
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_peer_buffers(qkm_ctx* c, void** xrecv, void** selrecv, void** partial) {
+    if (!c || !xrecv || !selrecv || !partial) return QKM_ERR_ARG;
+    if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
+    *xrecv = c->pm_xrecv; *selrecv = c->pm_selrecv; *partial = c->pm_partial;
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_peer_set(qkm_ctx* c, uint32_t peer, void* xrecv, void* selrecv, const void* partial) {
+    if (!c || !xrecv || !selrecv || !partial) return QKM_ERR_ARG;
+    if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
+    if (peer >= c->pm_ranks || peer == c->pm_rank) return fail(c, QKM_ERR_ARG, "peer %u is not another rank of %u", peer, c->pm_ranks);
+    c->pm_peers.x[peer] = (float*)xrecv; c->pm_peers.sel[peer] = (qkm_sel*)selrecv; c->pm_peers.partial[peer] = (const float*)partial;
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_peer_export(qkm_ctx* c, void* handles) {
+    if (!c || !handles) return QKM_ERR_ARG;
+    if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
+    static_assert(sizeof(cudaIpcMemHandle_t) == QKM_EP_HANDLE_BYTES / 3, "handle size");
+    cudaIpcMemHandle_t h[3];
+    QKM_CUDA(c, cudaIpcGetMemHandle(&h[0], c->pm_xrecv));
+    QKM_CUDA(c, cudaIpcGetMemHandle(&h[1], c->pm_selrecv));
+    QKM_CUDA(c, cudaIpcGetMemHandle(&h[2], c->pm_partial));
+    memcpy(handles, h, sizeof h);
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_peer_import(qkm_ctx* c, uint32_t peer, const void* handles) {
+    if (!c || !handles) return QKM_ERR_ARG;
+    if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
+    if (peer >= c->pm_ranks || peer == c->pm_rank) return fail(c, QKM_ERR_ARG, "peer %u is not another rank of %u", peer, c->pm_ranks);
+    if (c->pm_opened[peer][0]) return fail(c, QKM_ERR_MODE, "buffers of rank %u are already mapped", peer);
+    cudaIpcMemHandle_t h[3];
+    memcpy(h, handles, sizeof h);
+    void* p[3] = {};
+    for (int i = 0; i < 3; ++i) {
+        const cudaError_t e = cudaIpcOpenMemHandle(&p[i], h[i], cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int j = 0; j < i; ++j) cudaIpcCloseMemHandle(p[j]);
+            cudaGetLastError();
+            return fail(c, QKM_ERR_CUDA, "mapping buffer %d of rank %u failed: %s", i, peer, cudaGetErrorString(e));
+        }
+    }
+    for (int i = 0; i < 3; ++i) c->pm_opened[peer][i] = p[i];
+    return qkm_ep_peer_set(c, peer, p[0], p[1], p[2]);
+}
+
+extern "C" QKM_API int qkm_ep_push(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t slot_rows) {
+    if (int rc = layer_ready(c, layer)) return rc;
+    if (int rc = pm_check(c, slot_rows)) return rc;
+    if (!x && n) return QKM_ERR_ARG;
+    if (n > slot_rows) return fail(c, QKM_ERR_BOUNDS, "%u tokens exceed slot_rows %u", n, slot_rows);
+    c->shared_plan_n = 0;
+    if (n) if (int rc = ep_route_local(c, layer, x, n)) return rc;
+    QKM_LAUNCH(c, launch_ep_push(c->L(), c->cfg.dims, x, c->sel, c->pm_peers, n, slot_rows, c->pm_rank, c->pm_ranks));
+    return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_forward_slots(qkm_ctx* c, uint32_t layer, uint32_t slot_rows) {
+    if (int rc = pm_check(c, slot_rows)) return rc;
+    return qkm_ep_expert_forward(c, layer, c->pm_xrecv, c->pm_selrecv, c->pm_ranks * slot_rows, c->pm_partial);
+}
+
+extern "C" QKM_API int qkm_ep_pull(qkm_ctx* c, uint32_t n, uint32_t slot_rows, float* y) {
+    if (int rc = pm_check(c, slot_rows)) return rc;
+    if (!y && n) return QKM_ERR_ARG;
+    if (n > slot_rows) return fail(c, QKM_ERR_BOUNDS, "%u tokens exceed slot_rows %u", n, slot_rows);
+    QKM_LAUNCH(c, launch_ep_pull(c->L(), c->cfg.dims, c->sel, c->pm_peers, c->y2, y, n, slot_rows, c->pm_rank, c->pm_ranks));
     return QKM_OK;
 }

@@ -7,6 +7,14 @@
 // experts over the received rows and returns one weighted partial row per received token.
 // The all-to-all itself is the host's (NCCL); these kernels only prepare and consume its
 // buffers, so nothing here waits on another GPU.
+//
+// Second form, without an all-to-all: every rank's receive buffers are mapped on every rank
+// (peer memory over NVLink).  The push kernel stores a token's row and selection record straight
+// into the buffers of each rank that owns one of its experts, at a row that depends only on
+// (source rank, token), so no counts are exchanged and nothing is packed; the pull kernel reads
+// the partial rows back from the peers' buffers while it sums them.  Only plain stores and
+// loads touch peer memory.  The host orders the phases with a barrier (any collective on the
+// stream); these kernels do not wait on anything either.
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -103,7 +111,90 @@ ep_combine_kernel(const float* __restrict__ back, const uint32_t* __restrict__ s
     *reinterpret_cast<float4*>(y + (size_t)t * n_embd + o) = v;
 }
 
+// One block per slot row i of this rank's region (slot_rows rows on every rank).  Rank d's
+// buffers get, at row rank * slot_rows + i: the selection record of token i and its x row if
+// token i selected an expert of d; otherwise a record whose ids are all past the expert table,
+// which the grouping kernels skip (rows i >= n_tokens are such records on every rank).
+__global__ void __launch_bounds__(256)
+ep_push_kernel(const float* __restrict__ x, const qkm_sel* __restrict__ sel, EpPeerTable peers, uint32_t n_tokens,
+               uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, uint32_t n_used, uint32_t experts_per_rank,
+               uint32_t n_embd) {
+    const uint32_t i = blockIdx.x, tid = threadIdx.x;
+    uint32_t need = 0;
+    if (i < n_tokens)
+        for (uint32_t s = 0; s < n_used; ++s) {
+            const uint32_t r = __ldg(&sel[i].ids[s]) / experts_per_rank;
+            if (r < n_ranks) need |= 1u << r;
+        }
+    const size_t row = (size_t)rank * slot_rows + i;
+    constexpr uint32_t kWords = sizeof(qkm_sel) / 4;
+    if (tid < kWords) {
+        const uint32_t mine = i < n_tokens ? reinterpret_cast<const uint32_t*>(sel + i)[tid] : 0u;
+        const uint32_t empty = tid < 16 ? kInvalid : 0u;
+        for (uint32_t d = 0; d < n_ranks; ++d)
+            reinterpret_cast<uint32_t*>(peers.sel[d] + row)[tid] = (need >> d & 1u) ? mine : empty;
+    }
+    if (!need) return;
+    const float4* src = reinterpret_cast<const float4*>(x + (size_t)i * n_embd);
+    for (uint32_t c = tid; c < n_embd / 4; c += blockDim.x) {
+        const float4 v = __ldg(src + c);
+        for (uint32_t d = 0; d < n_ranks; ++d)
+            if (need >> d & 1u) reinterpret_cast<float4*>(peers.x[d] + row * n_embd)[c] = v;
+    }
+}
+
+// y[t] = y2[t] + sum over the ranks that own one of t's experts, in rank order, of the partial
+// row that rank computed for (this rank, t), read from that rank's buffer.
+__global__ void __launch_bounds__(256)
+ep_pull_kernel(const qkm_sel* __restrict__ sel, EpPeerTable peers, const float* __restrict__ y2, float* __restrict__ y,
+               uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, uint32_t n_used, uint32_t experts_per_rank,
+               uint32_t n_embd) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (o >= n_embd) return;
+    uint32_t need = 0;
+    for (uint32_t s = 0; s < n_used; ++s) {
+        const uint32_t r = __ldg(&sel[t].ids[s]) / experts_per_rank;
+        if (r < n_ranks) need |= 1u << r;
+    }
+    const size_t row = (size_t)rank * slot_rows + t;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (uint32_t d = 0; d < n_ranks; ++d) {
+        if (!(need >> d & 1u)) continue;
+        const float4 c = *reinterpret_cast<const float4*>(peers.partial[d] + row * n_embd + o);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+    }
+    if (y2) {
+        const float4 c = *reinterpret_cast<const float4*>(y2 + (size_t)t * n_embd + o);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+    }
+    *reinterpret_cast<float4*>(y + (size_t)t * n_embd + o) = v;
+}
+
 }  // namespace
+
+cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel, const EpPeerTable& peers,
+                           uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks) {
+    if (n_ranks == 0 || n_ranks > kMaxPeerRanks || d.n_expert % n_ranks || rank >= n_ranks || n_tokens > slot_rows)
+        return cudaErrorInvalidValue;
+    if (slot_rows == 0) return cudaSuccess;
+    ep_push_kernel<<<slot_rows, 256, 0, L.stream>>>(x, sel, peers, n_tokens, slot_rows, rank, n_ranks, d.n_used,
+                                                    d.n_expert / n_ranks, d.n_embd);
+    L.count();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_ep_pull(const Launch& L, const qkm_dims& d, const qkm_sel* sel, const EpPeerTable& peers, const float* y2,
+                           float* y, uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks) {
+    if (n_ranks == 0 || n_ranks > kMaxPeerRanks || d.n_expert % n_ranks || rank >= n_ranks || n_tokens > slot_rows)
+        return cudaErrorInvalidValue;
+    if (n_tokens == 0) return cudaSuccess;
+    const dim3 grid((d.n_embd / 4 + 255) / 256, n_tokens);
+    ep_pull_kernel<<<grid, 256, 0, L.stream>>>(sel, peers, y2, y, slot_rows, rank, n_ranks, d.n_used, d.n_expert / n_ranks,
+                                               d.n_embd);
+    L.count();
+    return cudaGetLastError();
+}
 
 cudaError_t launch_ep_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens, uint32_t n_ranks,
                            uint32_t* counts, uint32_t* send_tok, uint32_t* send_pos) {

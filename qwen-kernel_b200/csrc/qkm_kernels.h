@@ -191,6 +191,17 @@ cudaError_t launch_argmax(const Launch& L, const float* logits, uint32_t n_rows,
 // ---- expert-parallel exchange helpers (qkm_ep.cu) --------------------------------------------
 // counts[0..n_ranks) rows per destination rank and counts[n_ranks] their sum; send_tok the
 // tokens in send order; send_pos[t][r] the row of token t among the rows sent (to rank r).
+// Receive buffers of every rank as this rank sees them (its own, and the peers' mapped ones).
+constexpr uint32_t kMaxPeerRanks = 16;
+struct EpPeerTable {
+    float* x[kMaxPeerRanks];          // [n_ranks * slot_rows][n_embd] rows pushed by the sources
+    qkm_sel* sel[kMaxPeerRanks];      // their selection records
+    const float* partial[kMaxPeerRanks];  // one weighted partial row per received row
+};
+cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel, const EpPeerTable& peers,
+                           uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
+cudaError_t launch_ep_pull(const Launch& L, const qkm_dims& d, const qkm_sel* sel, const EpPeerTable& peers, const float* y2,
+                           float* y, uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
 cudaError_t launch_ep_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens, uint32_t n_ranks,
                            uint32_t* counts, uint32_t* send_tok, uint32_t* send_pos);
 cudaError_t launch_ep_pack(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel,

@@ -857,13 +857,15 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
     if (stage_ids)
         for (uint32_t p = tid; p < np; p += 512) {
             const uint32_t t = p / n_used, s = p - t * n_used;
-            s_ids[p] = min(sel[t].ids[s], n_expert - 1) - expert_first;  // wraps when below
+            const uint32_t id = sel[t].ids[s];   // an id past the table marks an empty record
+            s_ids[p] = id < n_expert ? id - expert_first : 0xFFFFFFFFu;  // wraps when below
         }
     __syncthreads();
     auto local_expert = [&](uint32_t p) -> uint32_t {
         if (stage_ids) return s_ids[p];
         const uint32_t t = p / n_used, s = p - t * n_used;
-        return min(sel[t].ids[s], n_expert - 1) - expert_first;
+        const uint32_t id = sel[t].ids[s];
+        return id < n_expert ? id - expert_first : 0xFFFFFFFFu;
     };
     const uint32_t p0 = tid * chunk, p1 = min(np, p0 + chunk);
     if (tid < n_chunks) {
@@ -1027,7 +1029,8 @@ constexpr uint32_t kInvalid = 0xFFFFFFFFu;
 __device__ __forceinline__ uint32_t gw_local_expert(const qkm_sel* __restrict__ sel, uint32_t p, uint32_t n_used,
                                                     uint32_t n_expert, uint32_t expert_first) {
     const uint32_t t = p / n_used, s = p - t * n_used;
-    return min(sel[t].ids[s], n_expert - 1) - expert_first;   // wraps above expert_count when below the range
+    const uint32_t id = sel[t].ids[s];   // an id past the table marks an empty record: no expert takes it
+    return id < n_expert ? id - expert_first : 0xFFFFFFFFu;   // wraps above expert_count when below the range
 }
 
 __global__ void __launch_bounds__(gw::kWarps * 32)

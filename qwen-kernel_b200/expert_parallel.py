@@ -71,3 +71,50 @@ class ExpertParallel:
         eng.ep_expert_forward(layer, self.xrecv, self.selrecv, n_recv, self.partial)
         dist.all_to_all_single(self.back[:n_send], self.partial[:n_recv], send, recv, group=self.group)
         eng.ep_combine(n, W, self.back, y)
+
+
+class PeerExpertParallel:
+    """The same layer with no all-to-all: every rank's receive buffers are mapped on every
+    rank (CUDA IPC over NVLink), tokens' rows are stored straight into the owners' buffers by
+    the push kernel and the partial rows are summed while they are read back from them
+    (`qkm_ep_push` / `qkm_ep_forward_slots` / `qkm_ep_pull`).  Nothing comes to the host and
+    no counts travel; the only collectives are two barriers per layer (a one-word all-reduce
+    on the compute stream), which also order the reuse of the buffers by the next layer.
+
+    The engine must launch on the stream the process group's collectives synchronise with
+    (torch's current stream)."""
+
+    HANDLE_BYTES = 192
+
+    def __init__(self, engine, max_local_tokens: int, device, group=None):
+        self.engine, self.group = engine, group
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        self.max_local, self.device = max_local_tokens, device
+        engine.ep_peer_setup(self.world, self.rank, max_local_tokens)
+        mine = torch.frombuffer(bytearray(engine.ep_peer_export()), dtype=torch.uint8).to(device)
+        if mine.numel() != self.HANDLE_BYTES:
+            raise ValueError("engine exported handles of the wrong size")
+        every = [torch.empty_like(mine) for _ in range(self.world)]
+        dist.all_gather(every, mine, group=group)
+        for r, h in enumerate(every):
+            if r != self.rank:
+                engine.ep_peer_import(r, bytes(h.cpu().numpy().tobytes()))
+        self._word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.barrier()
+
+    def barrier(self) -> None:
+        dist.all_reduce(self._word, group=self.group)
+
+    def forward(self, layer: int, x: torch.Tensor, n: int, y: torch.Tensor, slot_rows: int | None = None) -> None:
+        """y[:n] = MoE layer `layer` of the n local rows x[:n].  All ranks call this together
+        with the same slot_rows (>= every rank's n; default: the size given at construction)."""
+        rows = self.max_local if slot_rows is None else slot_rows
+        if n > rows or rows > self.max_local:
+            raise ValueError(f"{n} local tokens / {rows} slot rows exceed the {self.max_local} this object was sized for")
+        eng = self.engine
+        eng.ep_push(layer, x, n, rows)
+        eng.ep_shared(layer, x, n)
+        self.barrier()                      # every rank's rows have landed
+        eng.ep_forward_slots(layer, rows)
+        self.barrier()                      # every rank's partial rows are written
+        eng.ep_pull(n, rows, y)

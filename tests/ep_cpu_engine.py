@@ -1,5 +1,7 @@
 """A CPU engine with the interface `ExpertParallel` drives (ep_dispatch / ep_shared /
-ep_expert_forward / ep_combine), computing with the oracle.  Test infrastructure only: it
+ep_expert_forward / ep_combine) and the one `PeerExpertParallel` drives (ep_peer_* / ep_push /
+ep_forward_slots / ep_pull, with POSIX shared memory standing in for peer-mapped device
+buffers), computing with the oracle.  Test infrastructure only: it
 lets the exchange logic (send order, split sizes, combine order) run as gloo ranks without a
 GPU, and documents the contract of the four calls in plain numpy."""
 import numpy as np
@@ -71,3 +73,82 @@ class OracleEngine:
                     out[t] += b[p]
         out += self.y2
         y.numpy()[:n] = out
+
+    # ---- peer-memory form: receive buffers live in shared memory, "handles" are their names
+    def ep_peer_setup(self, n_ranks, rank, slot_cap):
+        from multiprocessing import shared_memory
+        assert (n_ranks, rank) == (self.world, self.rank)
+        E, rows = self.dims.n_embd, n_ranks * slot_cap
+        self.cap = slot_cap
+        self.shm = [shared_memory.SharedMemory(create=True, size=max(nb, 1)) for nb in (rows * E * 4, rows * 160, rows * E * 4)]
+        self.peer_shm = {}
+        self.peers = {rank: self._views(self.shm, rows)}
+        self.peers[rank][1][:] = 0xFF
+
+    def _views(self, shm, rows):
+        E = self.dims.n_embd
+        return (np.ndarray((rows, E), np.float32, shm[0].buf), np.ndarray((rows, 160), np.uint8, shm[1].buf),
+                np.ndarray((rows, E), np.float32, shm[2].buf))
+
+    def ep_peer_export(self) -> bytes:
+        return b"".join(s.name.encode().ljust(64, b"\0") for s in self.shm)
+
+    def ep_peer_import(self, peer, handles: bytes):
+        from multiprocessing import shared_memory
+        names = [handles[64 * i:64 * i + 64].rstrip(b"\0").decode() for i in range(3)]
+        self.peer_shm[peer] = [shared_memory.SharedMemory(name=nm) for nm in names]
+        self.peers[peer] = self._views(self.peer_shm[peer], self.world * self.cap)
+
+    def _need(self, n):
+        owner = self.sel["ids"][:n, :self.dims.n_used] // self.per
+        return np.stack([(owner == r).any(axis=1) for r in range(self.world)], axis=1)   # [n][ranks]
+
+    def ep_push(self, layer, x, n, slot_rows):
+        xn = x.numpy()[:n]
+        self.sel, _ = self.orc.route(self.layers[layer], xn)
+        need = self._need(n) if n else np.zeros((0, self.world), bool)
+        empty = np.zeros(160, np.uint8)
+        empty[:64] = 0xFF
+        base = self.rank * slot_rows
+        for d in range(self.world):
+            xr, sr, _ = self.peers[d]
+            for i in range(slot_rows):
+                if i < n and need[i, d]:
+                    xr[base + i] = xn[i]
+                    sr[base + i] = self.sel[i:i + 1].view(np.uint8).reshape(160)
+                else:
+                    sr[base + i] = empty
+
+    def ep_forward_slots(self, layer, slot_rows):
+        from conftest import entry
+        xr, sr, pr = self.peers[self.rank]
+        rows = self.world * slot_rows
+        sel = sr[:rows].copy().reshape(-1).view(entry.package().SEL_DTYPE)
+        live = (sel["ids"][:, :self.dims.n_used] < self.dims.n_expert).any(axis=1)
+        pr[:rows] = 0
+        if live.any():
+            idx = np.nonzero(live)[0]
+            out = self.orc.moe_layer(self.slices[layer], np.ascontiguousarray(xr[idx]), sel_in=sel[idx].copy(), with_shared=False)
+            pr[idx] = out["y"]
+
+    def ep_pull(self, n, slot_rows, y):
+        if n == 0:
+            return
+        need = self._need(n)
+        out = np.zeros((n, self.dims.n_embd), np.float32)
+        for d in range(self.world):
+            pr = self.peers[d][2]
+            for t in range(n):
+                if need[t, d]:
+                    out[t] += pr[self.rank * slot_rows + t]
+        out += self.y2
+        y.numpy()[:n] = out
+
+    def close_peers(self):
+        self.peers = {}
+        for lst in self.peer_shm.values():
+            for s in lst:
+                s.close()
+        for s in getattr(self, "shm", []):
+            s.close()
+            s.unlink()

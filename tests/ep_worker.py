@@ -23,6 +23,7 @@ def main():
     ap.add_argument("--world", type=int, required=True)
     ap.add_argument("--port", type=int, required=True)
     ap.add_argument("--tokens", type=int, default=12)
+    ap.add_argument("--mode", choices=("alltoall", "peer"), default="alltoall")
     a = ap.parse_args()
     os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(a.port)
     dist.init_process_group("gloo", rank=a.rank, world_size=a.world)
@@ -31,7 +32,7 @@ def main():
     omod = entry.oracle_module()
     omod.build(ref=False)
     orc = omod.Oracle()
-    from qwen_kernel_b200.expert_parallel import ExpertParallel, shard_range
+    from qwen_kernel_b200.expert_parallel import ExpertParallel, PeerExpertParallel, shard_range
 
     dims = syn.Dims(n_embd=256, n_ff=256, n_expert=16, n_used=4)
     layers = [syn.make_layer(dims, seed=77, layer=l) for l in range(2)]
@@ -46,13 +47,20 @@ def main():
     x = torch.from_numpy(np.ascontiguousarray(x_all[lo:hi]).copy()) if n else torch.zeros((1, dims.n_embd))
     y = torch.zeros((max(n, 1), dims.n_embd))
     eng = OracleEngine(orc, layers, a.rank, a.world)
-    ep = ExpertParallel(eng, dims.n_embd, dims.n_used, max_local_tokens=T_all, max_recv_rows=T_all,
-                        device="cpu")
+    if a.mode == "peer":
+        ep = PeerExpertParallel(eng, max_local_tokens=T_all, device="cpu")
+    else:
+        ep = ExpertParallel(eng, dims.n_embd, dims.n_used, max_local_tokens=T_all, max_recv_rows=T_all,
+                            device="cpu")
     worst = 0.0
+    n_most = max(cut[r + 1] - cut[r] for r in range(a.world))
     for l in range(2):
-        ep.forward(l, x, n, y)
-        send, recv = ep.last_counts
-        assert len(send) == a.world and sum(send) <= n * min(a.world, dims.n_used)
+        if a.mode == "peer":
+            ep.forward(l, x, n, y, slot_rows=n_most if l else None)   # once with the full slots, once tight
+        else:
+            ep.forward(l, x, n, y)
+            send, recv = ep.last_counts
+            assert len(send) == a.world and sum(send) <= n * min(a.world, dims.n_used)
         if n:
             want = orc.moe_layer(layers[l], x_all[lo:hi])["y"]
             got = y.numpy()[:n]
@@ -65,6 +73,8 @@ def main():
     if a.rank == 0:
         print("EP_CPU", [tuple(g.tolist()) for g in gathered], flush=True)
     dist.barrier()
+    if a.mode == "peer":
+        eng.close_peers()
     dist.destroy_process_group()
     sys.exit(0 if worst <= 1e-5 else 1)
 

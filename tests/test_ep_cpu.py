@@ -20,11 +20,12 @@ def _free_port():
     return p
 
 
-@pytest.mark.parametrize("world,tokens", [(2, 12), (4, 9), (2, 1)])
-def test_expert_parallel_gloo(world, tokens, orc):  # `orc` builds the oracle once, before the ranks start
+@pytest.mark.parametrize("world,tokens,mode", [(2, 12, "alltoall"), (4, 9, "alltoall"), (2, 1, "alltoall"),
+                                               (2, 12, "peer"), (4, 9, "peer"), (2, 1, "peer")])
+def test_expert_parallel_gloo(world, tokens, mode, orc):  # `orc` builds the oracle once, before the ranks start
     port = _free_port()
     procs = [subprocess.Popen([sys.executable, os.path.join(HERE, "ep_worker.py"), "--rank", str(r), "--world",
-                               str(world), "--port", str(port), "--tokens", str(tokens)],
+                               str(world), "--port", str(port), "--tokens", str(tokens), "--mode", mode],
                               stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
              for r in range(world)]
     outs = []

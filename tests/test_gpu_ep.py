@@ -130,3 +130,152 @@ def test_ep_rejects_wrong_shard(pkg, syn):
         with pytest.raises(pkg.QkmError):
             c.ep_dispatch(0, d, 1, 8, d, d)      # 64 experts is a 4-way shard, not 8
         d.free()
+
+
+# ---- the peer-memory form (qkm_ep_push / qkm_ep_forward_slots / qkm_ep_pull) -------------------------
+def _download(c, ptr, dtype, shape):
+    out = np.empty(shape, dtype)
+    c.check(c.lib.qkm_d2h(c.h, out.ctypes.data, ptr, out.nbytes))
+    return out
+
+
+def run_ep_peer(pkg, orc, syn, dims, layer, x_parts, G, tol, slot_rows=None, cap_extra=0):
+    """G sharded contexts on one device; each has the others' receive buffers as raw pointers,
+    which is what a peer mapping is to the kernels.  Phases are separated by a sync of every
+    context (the barrier of the multi-GPU driver)."""
+    from qwen_kernel_b200 import SEL_DTYPE
+    per = dims.n_expert // G
+    E = dims.n_embd
+    most = max(p.shape[0] for p in x_parts)
+    cap = most + cap_extra
+    rows = cap if slot_rows is None else slot_rows
+    ctxs = []
+    for r in range(G):
+        c = pkg.Context(dims, n_layer=1, max_tokens=G * cap, device=0, expert_first=r * per, expert_count=per)
+        c.upload_layer(0, layer.expert_slice(r * per, per))
+        c.ep_peer_setup(G, r, cap)
+        ctxs.append(c)
+    bufs = [c.ep_peer_buffers() for c in ctxs]
+    for r, c in enumerate(ctxs):
+        for q in range(G):
+            if q != r:
+                c.ep_peer_set(q, *bufs[q])
+    d_xs, sels = [], []
+    for r, (c, xp) in enumerate(zip(ctxs, x_parts)):
+        n = xp.shape[0]
+        d_x = c.to_device(xp) if n else c.alloc(16)
+        c.ep_push(0, d_x, n, rows)
+        c.ep_shared(0, d_x, n)
+        d_xs.append(d_x)
+        sel = c.last_sel(n) if n else np.zeros(0, SEL_DTYPE)
+        if n:
+            assert np.array_equal(sel["ids"], orc.route(layer, xp)[0]["ids"])
+        sels.append(sel)
+    for c in ctxs:
+        c.sync()
+    # what landed: rank d holds source s's token i at row s * rows + i iff i selected an expert of d
+    for d, c in enumerate(ctxs):
+        xr = _download(c, bufs[d][0], np.float32, (G * rows, E))
+        sr = _download(c, bufs[d][1], np.uint8, (G * rows, 160)).reshape(-1).view(SEL_DTYPE)
+        for s in range(G):
+            n = x_parts[s].shape[0]
+            need = ((sels[s]["ids"][:, :dims.n_used] // per) == d).any(axis=1) if n else np.zeros(0, bool)
+            got = sr[s * rows:(s + 1) * rows]
+            assert np.array_equal(got["ids"][:n][need], sels[s]["ids"][need])
+            assert np.array_equal(xr[s * rows:s * rows + n][need], x_parts[s][need])
+            empty = np.ones(rows, bool)
+            empty[:n] = ~need
+            assert (got["ids"][empty][:, :dims.n_used] == 0xFFFFFFFF).all()
+    for c in ctxs:
+        c.ep_forward_slots(0, rows)
+    for c in ctxs:
+        c.sync()
+    worst = 0.0
+    for r, c in enumerate(ctxs):
+        n = x_parts[r].shape[0]
+        if n:
+            d_y = c.alloc(n * E * 4)
+            c.ep_pull(n, rows, d_y)
+            y = d_y.download(np.float32, (n, E))
+            want = orc.moe_layer(layer, x_parts[r], threads=orc.hardware_threads())["y"]
+            worst = max(worst, syn.rel_err_rows(y, want))
+            d_y.free()
+    for c, d_x in zip(ctxs, d_xs):
+        d_x.free()
+        c.close()
+    assert worst < tol, worst
+
+
+@pytest.mark.parametrize("G,T,extra", [(2, 24, 0), (4, 40, 5), (8, 200, 0), (2, 300, 0)])
+def test_ep_peer_full_size_shapes(pkg, orc, syn, G, T, extra):
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=46)
+    x = syn.random_x(T, dims.n_embd, seed=64)
+    cuts = np.linspace(0, T, G + 1).astype(int)
+    cuts[1] = min(T, cuts[1] + 3)                       # uneven shares
+    parts = [x[cuts[r]:cuts[r + 1]] for r in range(G)]
+    run_ep_peer(pkg, orc, syn, dims, layer, parts, G, TOL_BF16, cap_extra=extra)
+
+
+def test_ep_peer_rank_without_tokens_and_tight_slots(pkg, orc, syn):
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=47)
+    x = syn.random_x(5, dims.n_embd, seed=65)
+    run_ep_peer(pkg, orc, syn, dims, layer, [x, x[:0]], 2, TOL_BF16, slot_rows=5, cap_extra=3)
+
+
+def test_ep_peer_generic_kernels_f32(pkg, orc, syn):
+    dims = syn.Dims(n_embd=512, n_ff=256, n_expert=8, n_used=2)
+    layer = syn.make_layer(dims, seed=48, down_type=syn.Q6_K)
+    x = syn.random_x(10, dims.n_embd, seed=66)
+    run_ep_peer(pkg, orc, syn, dims, layer, [x[:6], x[6:]], 2, TOL_F32)
+
+
+def test_ep_peer_argument_checks(pkg, syn):
+    dims = syn.Dims()
+    with pkg.Context(dims, n_layer=1, max_tokens=16, device=0, expert_first=64, expert_count=64) as c:
+        c.upload_layer(0, syn.make_layer(dims, seed=45).expert_slice(64, 64))
+        d = c.alloc(1 << 16)
+        with pytest.raises(pkg.QkmError):
+            c.ep_push(0, d, 1, 4)                  # before qkm_ep_peer_setup
+        with pytest.raises(pkg.QkmError):
+            c.ep_peer_setup(4, 0, 4)               # the context holds shard 1, not 0
+        with pytest.raises(pkg.QkmError):
+            c.ep_peer_setup(4, 1, 5)               # 4 x 5 rows exceed max_tokens
+        c.ep_peer_setup(4, 1, 4)
+        with pytest.raises(pkg.QkmError):
+            c.ep_push(0, d, 1, 4)                  # peers not mapped yet
+        with pytest.raises(pkg.QkmError):
+            c.ep_peer_set(1, d, d, d)              # its own rank
+        d.free()
+
+
+def test_ep_peer_two_processes_over_ipc():
+    """Two processes, one GPU each: buffers mapped through CUDA IPC handles, NCCL barriers."""
+    import os
+    import socket
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    here = os.path.dirname(os.path.abspath(__file__))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    procs = [subprocess.Popen([sys.executable, os.path.join(here, "ep_gpu_worker.py"), "--rank", str(r), "--world", "2",
+                               "--port", str(port)], stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+             for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=600)
+        except subprocess.TimeoutExpired:
+            for q in procs:
+                q.kill()
+            raise
+        outs.append(out)
+    for r, (p, out) in enumerate(zip(procs, outs)):
+        assert p.returncode == 0, f"rank {r} failed:\n{out[-3000:]}"
+    assert "EP_GPU" in outs[0]
