@@ -393,7 +393,7 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
         from qwen_kernel_b200.expert_parallel import PeerExpertParallel
         why = ""
         try:
-            peer = PeerExpertParallel(ctx, max_local_tokens=n_max, device=dev)
+            peer = PeerExpertParallel(ctx, max_local_tokens=n_max, device=dev, device_barrier=True)
         except Exception as e:   # noqa: BLE001  (reported in the JSON line)
             why = f"{type(e).__name__}: {e}"[:200]
         ok = torch.tensor([0 if peer is None else 1], dtype=torch.int32, device=dev)
@@ -445,7 +445,12 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             entry_["peer_memory"] = {"us_per_layer": ms_p * 1e3, "tok_s": T / (ms_p * 1e-3),
                                      "rel_err_vs_oracle": R.max_over_ranks(err_p),
                                      "launches_per_layer": (ctx.launch_count() - n0) / ((steps + warm) * PL),
-                                     "exchange": "stores into / loads from peer-mapped buffers, two one-word all-reduces as barriers"}
+                                     "exchange": "stores into / loads from peer-mapped buffers, two flag barriers (own kernel) per layer, one library call per layer"}
+            ctx.sync()   # a barrier wait that ran out would surface here
+            peer.device_barrier = False
+            ms_n = timed(torch, R, stream, step_peer, steps, warm) / PL
+            peer.device_barrier = True
+            entry_["peer_memory"]["us_per_layer_with_nccl_barriers"] = ms_n * 1e3
         out["chunks"][str(T)] = entry_
     if world == 1:
         ctx.profile_enable(True)

@@ -371,6 +371,16 @@ QKM_API int qkm_ep_push(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_t
                         uint32_t slot_rows);
 QKM_API int qkm_ep_forward_slots(qkm_ctx *c, uint32_t layer, uint32_t slot_rows);
 QKM_API int qkm_ep_pull(qkm_ctx *c, uint32_t n_tokens, uint32_t slot_rows, float *y);
+/* The barrier as a kernel of the library: each rank stores a barrier number into a word of
+ * every peer's buffer and polls its own words.  Every rank issues the same sequence of
+ * barriers, each rank on its own GPU (two ranks' barriers on one device would wait on each
+ * other's launch).  The wait is bounded: after timeout_ms (> 0) the kernel gives up and the
+ * next qkm_sync returns QKM_ERR_TIMEOUT; the context stays usable.  slot_cap must be the
+ * same on all ranks.  qkm_ep_peer_layer is the whole per-layer sequence above with these
+ * barriers, one call per layer, nothing read by the host. */
+QKM_API int qkm_ep_barrier(qkm_ctx *c, uint32_t timeout_ms);
+QKM_API int qkm_ep_peer_layer(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
+                              uint32_t slot_rows, float *y, uint32_t timeout_ms);
 
 /* Router logits + selection WITHOUT any device allocation and without a context.
  * NO COUNTERPART IN THE REFERENCE: it exists for hosts that may not take memory from

@@ -112,6 +112,8 @@ SIGNATURES = {
     "qkm_ep_push": (_I, [_VP, _U32, _VP, _U32, _U32]),
     "qkm_ep_forward_slots": (_I, [_VP, _U32, _U32]),
     "qkm_ep_pull": (_I, [_VP, _U32, _U32, _VP]),
+    "qkm_ep_barrier": (_I, [_VP, _U32]),
+    "qkm_ep_peer_layer": (_I, [_VP, _U32, _VP, _U32, _U32, _VP, _U32]),
     "qkm_route_select_static": (_I, [_I, _VP, C.POINTER(Dims), _U32, _VP, _VP, _VP, _VP, _U32, C.c_char_p, _SZ]),
 }
 
@@ -382,6 +384,12 @@ class Context:
 
     def ep_pull(self, n, slot_rows, y):
         self.check(self.lib.qkm_ep_pull(self.h, n, slot_rows, _p(y)))
+
+    def ep_barrier(self, timeout_ms=2000):
+        self.check(self.lib.qkm_ep_barrier(self.h, timeout_ms))
+
+    def ep_peer_layer(self, layer_idx, x, n, slot_rows, y, timeout_ms=2000):
+        self.check(self.lib.qkm_ep_peer_layer(self.h, layer_idx, _p(x), n, slot_rows, _p(y), timeout_ms))
 
     def profile_enable(self, on=True):
         self.check(self.lib.qkm_profile_enable(self.h, int(on)))

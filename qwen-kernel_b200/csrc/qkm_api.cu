@@ -88,6 +88,7 @@ struct qkm_ctx {
     uint32_t* ep_send_pos = nullptr;     // [max_tokens][n_ranks]
     // peer-memory form of the exchange: this rank's receive buffers and every rank's as mapped here
     uint32_t pm_ranks = 0, pm_rank = 0, pm_cap = 0;   // slot_cap rows per source rank
+    uint32_t pm_epoch = 0;                            // barriers issued so far (qkm_ep_barrier)
     float* pm_xrecv = nullptr; qkm_sel* pm_selrecv = nullptr; float* pm_partial = nullptr;
     EpPeerTable pm_peers{};
     void* pm_opened[kMaxPeerRanks][3] = {};           // mappings this context opened from handles
@@ -1153,12 +1154,17 @@ extern "C" QKM_API int qkm_ep_combine(qkm_ctx* c, uint32_t n, uint32_t n_ranks, 
 // and overwrites its partial rows after the first barrier of l+1, which every rank enters
 // after its pull of l.  Kernels only store to and load from peer memory; none waits.
 
+constexpr size_t kPmFlagBytes = 256;
+static uint32_t* pm_flags_of(const qkm_ctx* c, void* selrecv) {
+    return (uint32_t*)((char*)selrecv + (size_t)c->pm_ranks * c->pm_cap * sizeof(qkm_sel));
+}
+
 static int pm_check(qkm_ctx* c, uint32_t slot_rows) {
     if (!c) return QKM_ERR_ARG;
     if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
     if (slot_rows == 0 || slot_rows > c->pm_cap) return fail(c, QKM_ERR_BOUNDS, "slot_rows %u outside 1..%u", slot_rows, c->pm_cap);
     for (uint32_t r = 0; r < c->pm_ranks; ++r)
-        if (!c->pm_peers.x[r] || !c->pm_peers.sel[r] || !c->pm_peers.partial[r])
+        if (!c->pm_peers.x[r] || !c->pm_peers.sel[r] || !c->pm_peers.partial[r] || !c->pm_peers.flags[r])
             return fail(c, QKM_ERR_MODE, "buffers of rank %u are not mapped (qkm_ep_peer_import / qkm_ep_peer_set)", r);
     return QKM_OK;
 }
@@ -1175,13 +1181,16 @@ extern "C" QKM_API int qkm_ep_peer_setup(qkm_ctx* c, uint32_t n_ranks, uint32_t 
         return fail(c, QKM_ERR_BOUNDS, "%u ranks x %u rows exceed max_tokens %u", n_ranks, slot_cap, c->cfg.max_tokens);
     const size_t rows = (size_t)n_ranks * slot_cap;
     QKM_CUDA(c, cudaMalloc((void**)&c->pm_xrecv, rows * d.n_embd * sizeof(float)));
-    QKM_CUDA(c, cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel)));
+    // the barrier words of qkm_ep_barrier sit behind the records, so three mappings carry everything
+    QKM_CUDA(c, cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel) + kPmFlagBytes));
+    QKM_CUDA(c, cudaMemset((char*)c->pm_selrecv + rows * sizeof(qkm_sel), 0, kPmFlagBytes));
     QKM_CUDA(c, cudaMalloc((void**)&c->pm_partial, rows * d.n_embd * sizeof(float)));
     QKM_CUDA(c, cudaMemset(c->pm_xrecv, 0, rows * d.n_embd * sizeof(float)));
     QKM_CUDA(c, cudaMemset(c->pm_selrecv, 0xFF, rows * sizeof(qkm_sel)));   // every record empty
     QKM_CUDA(c, cudaMemset(c->pm_partial, 0, rows * d.n_embd * sizeof(float)));
-    c->pm_ranks = n_ranks; c->pm_rank = rank; c->pm_cap = slot_cap;
+    c->pm_ranks = n_ranks; c->pm_rank = rank; c->pm_cap = slot_cap; c->pm_epoch = 0;
     c->pm_peers.x[rank] = c->pm_xrecv; c->pm_peers.sel[rank] = c->pm_selrecv; c->pm_peers.partial[rank] = c->pm_partial;
+    c->pm_peers.flags[rank] = pm_flags_of(c, c->pm_selrecv);
     return QKM_OK;
 }
 
@@ -1197,6 +1206,7 @@ extern "C" QKM_API int qkm_ep_peer_set(qkm_ctx* c, uint32_t peer, void* xrecv, v
     if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
     if (peer >= c->pm_ranks || peer == c->pm_rank) return fail(c, QKM_ERR_ARG, "peer %u is not another rank of %u", peer, c->pm_ranks);
     c->pm_peers.x[peer] = (float*)xrecv; c->pm_peers.sel[peer] = (qkm_sel*)selrecv; c->pm_peers.partial[peer] = (const float*)partial;
+    c->pm_peers.flags[peer] = pm_flags_of(c, selrecv);   // every rank uses the same slot_cap, hence the same offset
     return QKM_OK;
 }
 
@@ -1254,4 +1264,25 @@ extern "C" QKM_API int qkm_ep_pull(qkm_ctx* c, uint32_t n, uint32_t slot_rows, f
     if (n > slot_rows) return fail(c, QKM_ERR_BOUNDS, "%u tokens exceed slot_rows %u", n, slot_rows);
     QKM_LAUNCH(c, launch_ep_pull(c->L(), c->cfg.dims, c->sel, c->pm_peers, c->y2, y, n, slot_rows, c->pm_rank, c->pm_ranks));
     return QKM_OK;
+}
+
+// Barrier of the ranks as a kernel on the context's stream (ep_barrier_kernel): every rank must
+// issue the same sequence of barriers, each rank on its own GPU.  timeout_ms bounds the wait on
+// the device; a wait that ran out shows as QKM_ERR_TIMEOUT at the next qkm_sync.
+extern "C" QKM_API int qkm_ep_barrier(qkm_ctx* c, uint32_t timeout_ms) {
+    if (int rc = pm_check(c, 1)) return rc;
+    if (timeout_ms == 0) return fail(c, QKM_ERR_ARG, "the barrier needs a time limit");
+    QKM_LAUNCH(c, launch_ep_barrier(c->L(), c->pm_peers, c->pm_rank, c->pm_ranks, ++c->pm_epoch, (uint64_t)timeout_ms * 1000000ull, c->status));
+    return QKM_OK;
+}
+
+// The whole layer in one call: push, shared expert, barrier, resident experts, barrier, pull.
+extern "C" QKM_API int qkm_ep_peer_layer(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t slot_rows, float* y,
+                                         uint32_t timeout_ms) {
+    if (int rc = qkm_ep_push(c, layer, x, n, slot_rows)) return rc;
+    if (int rc = qkm_ep_shared(c, layer, x, n)) return rc;
+    if (int rc = qkm_ep_barrier(c, timeout_ms)) return rc;
+    if (int rc = qkm_ep_forward_slots(c, layer, slot_rows)) return rc;
+    if (int rc = qkm_ep_barrier(c, timeout_ms)) return rc;
+    return qkm_ep_pull(c, n, slot_rows, y);
 }

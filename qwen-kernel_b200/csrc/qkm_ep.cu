@@ -19,6 +19,7 @@
 #include <stdint.h>
 
 #include "qkm_kernels.h"
+#include "qkm_stream.cuh"
 
 namespace qkm {
 
@@ -171,7 +172,46 @@ ep_pull_kernel(const qkm_sel* __restrict__ sel, EpPeerTable peers, const float* 
     *reinterpret_cast<float4*>(y + (size_t)t * n_embd + o) = v;
 }
 
+// Barrier of the ranks, one launch per rank, each on its own GPU (never two of them on one
+// device: they wait for one another).  Barriers are numbered 1, 2, ... in the order every rank
+// issues them.  Lane d stores the number into word `rank` of rank d's flag array (release,
+// system scope: everything this rank's earlier kernels stored is visible before it); lane s
+// then polls word s of this rank's OWN array until rank s has reached the same barrier.  A
+// rank that has already gone on to a later barrier leaves a larger number, which also passes.
+// The wait is bounded by the device's nanosecond timer: when it runs out the kernel leaves
+// kStatusWaitTimeout in the status word and returns.
+__global__ void __launch_bounds__(32)
+ep_barrier_kernel(EpPeerTable peers, uint32_t rank, uint32_t n_ranks, uint32_t epoch, unsigned long long limit_ns,
+                  uint32_t* __restrict__ status) {
+    const uint32_t lane = threadIdx.x;
+    if (lane >= n_ranks) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peers.flags[lane] + rank), "r"(epoch) : "memory");
+    const uint32_t* mine = peers.flags[rank] + lane;
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t polls = 0;; ++polls) {
+        uint32_t v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if ((int32_t)(v - epoch) >= 0) break;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 > limit_ns) {
+            atomicExch(status, (uint32_t)kStatusWaitTimeout);
+            break;
+        }
+        __nanosleep(polls < 64 ? 32 : 256);
+    }
+}
+
 }  // namespace
+
+cudaError_t launch_ep_barrier(const Launch& L, const EpPeerTable& peers, uint32_t rank, uint32_t n_ranks, uint32_t epoch,
+                              uint64_t limit_ns, uint32_t* status) {
+    if (n_ranks == 0 || n_ranks > kMaxPeerRanks || rank >= n_ranks || !status) return cudaErrorInvalidValue;
+    ep_barrier_kernel<<<1, 32, 0, L.stream>>>(peers, rank, n_ranks, epoch, (unsigned long long)limit_ns, status);
+    L.count();
+    return cudaGetLastError();
+}
 
 cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel, const EpPeerTable& peers,
                            uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks) {

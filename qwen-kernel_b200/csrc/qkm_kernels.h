@@ -197,7 +197,10 @@ struct EpPeerTable {
     float* x[kMaxPeerRanks];          // [n_ranks * slot_rows][n_embd] rows pushed by the sources
     qkm_sel* sel[kMaxPeerRanks];      // their selection records
     const float* partial[kMaxPeerRanks];  // one weighted partial row per received row
+    uint32_t* flags[kMaxPeerRanks];   // [n_ranks] barrier words, word s written by rank s
 };
+cudaError_t launch_ep_barrier(const Launch& L, const EpPeerTable& peers, uint32_t rank, uint32_t n_ranks, uint32_t epoch,
+                              uint64_t limit_ns, uint32_t* status);
 cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel, const EpPeerTable& peers,
                            uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
 cudaError_t launch_ep_pull(const Launch& L, const qkm_dims& d, const qkm_sel* sel, const EpPeerTable& peers, const float* y2,

@@ -78,18 +78,24 @@ class PeerExpertParallel:
     rank (CUDA IPC over NVLink), tokens' rows are stored straight into the owners' buffers by
     the push kernel and the partial rows are summed while they are read back from them
     (`qkm_ep_push` / `qkm_ep_forward_slots` / `qkm_ep_pull`).  Nothing comes to the host and
-    no counts travel; the only collectives are two barriers per layer (a one-word all-reduce
-    on the compute stream), which also order the reuse of the buffers by the next layer.
+    no counts travel; the only synchronisation is two barriers per layer, which also order the
+    reuse of the buffers by the next layer.  With `device_barrier=True` the barriers are the
+    library's own kernel over the same peer mappings (`qkm_ep_barrier`, bounded wait) and a layer
+    is ONE call into the library (`qkm_ep_peer_layer`); otherwise each is a one-word all-reduce
+    of the process group on the compute stream.  The device barrier needs every rank on its own
+    GPU and all ranks issuing the same sequence of calls.
 
     The engine must launch on the stream the process group's collectives synchronise with
     (torch's current stream)."""
 
     HANDLE_BYTES = 192
 
-    def __init__(self, engine, max_local_tokens: int, device, group=None):
+    def __init__(self, engine, max_local_tokens: int, device, group=None, device_barrier: bool = False,
+                 timeout_ms: int = 2000):
         self.engine, self.group = engine, group
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.max_local, self.device = max_local_tokens, device
+        self.device_barrier, self.timeout_ms = device_barrier, timeout_ms
         engine.ep_peer_setup(self.world, self.rank, max_local_tokens)
         mine = torch.frombuffer(bytearray(engine.ep_peer_export()), dtype=torch.uint8).to(device)
         if mine.numel() != self.HANDLE_BYTES:
@@ -112,6 +118,9 @@ class PeerExpertParallel:
         if n > rows or rows > self.max_local:
             raise ValueError(f"{n} local tokens / {rows} slot rows exceed the {self.max_local} this object was sized for")
         eng = self.engine
+        if self.device_barrier:
+            eng.ep_peer_layer(layer, x, n, rows, y, self.timeout_ms)
+            return
         eng.ep_push(layer, x, n, rows)
         eng.ep_shared(layer, x, n)
         self.barrier()                      # every rank's rows have landed

@@ -57,10 +57,12 @@ def main():
         y2 = torch.zeros_like(x)
         for rep in range(3):              # back-to-back layers reuse the buffers
             for l in range(2):
+                peer.device_barrier = bool(rep & 1)          # all-reduce barriers, then the library's own
                 peer.forward(l, x, n, y, slot_rows=rows)
                 a2a.forward(l, x, n, y2)
                 want = orc.moe_layer(layers[l], x_all[lo:hi], threads=orc.hardware_threads())["y"]
                 worst = max(worst, syn.rel_err_rows(y.cpu().numpy(), want), syn.rel_err_rows(y2.cpu().numpy(), want))
+    ctx.sync()                                    # a device barrier that gave up would raise here
     ok = torch.tensor([worst], device=dev)
     dist.all_reduce(ok, op=dist.ReduceOp.MAX)
     if a.rank == 0:

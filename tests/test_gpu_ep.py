@@ -279,3 +279,45 @@ def test_ep_peer_two_processes_over_ipc():
     for r, (p, out) in enumerate(zip(procs, outs)):
         assert p.returncode == 0, f"rank {r} failed:\n{out[-3000:]}"
     assert "EP_GPU" in outs[0]
+
+
+def test_ep_peer_layer_single_rank_with_device_barrier(pkg, orc, syn):
+    """One rank: the barrier kernel signals and polls its own words; the fused call is the layer."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=49)
+    x = syn.random_x(140, dims.n_embd, seed=67)
+    with pkg.Context(dims, n_layer=1, max_tokens=160, device=0, expert_first=0, expert_count=dims.n_expert) as c:
+        c.upload_layer(0, layer)
+        c.ep_peer_setup(1, 0, 160)
+        d_x, d_y = c.to_device(x), c.alloc(x.nbytes)
+        for rows in (140, 160):
+            c.ep_peer_layer(0, d_x, 140, rows, d_y, timeout_ms=1000)
+            c.sync()
+            y = d_y.download(np.float32, x.shape)
+            want = orc.moe_layer(layer, x, threads=orc.hardware_threads())["y"]
+            assert syn.rel_err_rows(y, want) < TOL_BF16
+        d_x.free(); d_y.free()
+
+
+def test_ep_barrier_wait_runs_out(pkg, syn):
+    """A peer that never arrives: the bounded wait gives up after its limit, the next sync
+    reports QKM_ERR_TIMEOUT and the context keeps working."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=50)
+    c0 = pkg.Context(dims, n_layer=1, max_tokens=16, device=0, expert_first=0, expert_count=128)
+    c1 = pkg.Context(dims, n_layer=1, max_tokens=16, device=0, expert_first=128, expert_count=128)
+    c0.upload_layer(0, layer.expert_slice(0, 128))
+    c0.ep_peer_setup(2, 0, 8)
+    c1.ep_peer_setup(2, 1, 8)
+    c0.ep_peer_set(1, *c1.ep_peer_buffers())
+    c0.ep_barrier(timeout_ms=20)                 # rank 1 never issues its barrier
+    with pytest.raises(pkg.QkmError) as e:
+        c0.sync()
+    assert e.value.code == -7
+    c0.sync()                                    # the flag was cleared; the context is usable
+    x = syn.random_x(4, dims.n_embd, seed=68)
+    d_x = c0.to_device(x)
+    c0.ep_push(0, d_x, 4, 8)
+    c0.sync()
+    d_x.free()
+    c0.close(); c1.close()
