@@ -451,6 +451,21 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             ms_n = timed(torch, R, stream, step_peer, steps, warm) / PL
             peer.device_barrier = True
             entry_["peer_memory"]["us_per_layer_with_nccl_barriers"] = ms_n * 1e3
+            if T in (128, 4096):   # where the time goes: the six calls of one layer between events, mean over the layers
+                names = ("push", "barrier1", "experts", "barrier2", "pull")
+                acc = dict.fromkeys(names, 0.0)
+                for l in range(PL):
+                    ev = [torch.cuda.Event(enable_timing=True) for _ in range(6)]
+                    calls = (lambda: ctx.ep_push(l, x[l], n, n), ctx.ep_barrier,
+                             lambda: ctx.ep_forward_slots(l, n, n), ctx.ep_barrier, lambda: ctx.ep_pull(n, n, y[l]))
+                    ev[0].record(stream)
+                    for i, call in enumerate(calls):
+                        call()
+                        ev[i + 1].record(stream)
+                    torch.cuda.synchronize(dev)
+                    for i, nm in enumerate(names):
+                        acc[nm] += ev[i].elapsed_time(ev[i + 1]) * 1e3 / PL
+                entry_["peer_memory"]["stages_us"] = acc
         out["chunks"][str(T)] = entry_
     if world == 1:
         ctx.profile_enable(True)

@@ -344,7 +344,8 @@ QKM_API int qkm_ep_combine(qkm_ctx *c, uint32_t n_tokens, uint32_t n_ranks, cons
  * n_ranks * slot_cap rows and has every peer's buffers mapped.  A token's row and record
  * are stored by the push kernel straight into the buffers of the ranks that own its
  * experts, at row (source rank * slot_rows + token), so no counts travel and nothing is
- * packed; the pull kernel sums the partial rows while reading them from the owners.
+ * packed; the owners store their partial rows into the source's return buffer the same
+ * way, and the pull kernel sums them from local memory.
  *   qkm_ep_peer_setup(c, n_ranks, rank, slot_cap)  once; n_ranks * slot_cap <= max_tokens,
  *                          n_ranks <= 16, the context opened on shard `rank`
  *   qkm_ep_peer_export / qkm_ep_peer_import  QKM_EP_HANDLE_BYTES of CUDA IPC handles per
@@ -355,21 +356,25 @@ QKM_API int qkm_ep_combine(qkm_ctx *c, uint32_t n_tokens, uint32_t n_ranks, cons
  *   qkm_ep_push(c, layer, x, n_tokens, slot_rows)   route + store rows into the owners
  *   qkm_ep_shared(c, layer, x, n_tokens)
  *   (caller)  barrier: any collective of the ranks enqueued on the context's stream
- *   qkm_ep_forward_slots(c, layer, slot_rows)       resident experts over all slots
+ *   qkm_ep_forward_slots(c, layer, slot_rows, n_shared)  resident experts over all slots;
+ *             n_shared = QKM_EP_NO_SHARED after a qkm_ep_shared call, or n_tokens INSTEAD
+ *             of that call: the shared expert of this rank's tokens then runs beside the
+ *             resident experts and arrives with this rank's partial rows
  *   (caller)  barrier
- *   qkm_ep_pull(c, n_tokens, slot_rows, y)          y = shared + partial rows of the owners
+ *   qkm_ep_pull(c, n_tokens, slot_rows, y)          y = shared + the returned partial rows
  * The two barriers are all the ordering the buffers need from one layer to the next.
  * No kernel waits on another GPU, nothing is read by the host. */
 #define QKM_EP_HANDLE_BYTES 192
+#define QKM_EP_NO_SHARED 0xFFFFFFFFu
 QKM_API int qkm_ep_peer_setup(qkm_ctx *c, uint32_t n_ranks, uint32_t rank, uint32_t slot_cap);
-QKM_API int qkm_ep_peer_buffers(qkm_ctx *c, void **xrecv, void **selrecv, void **partial);
-QKM_API int qkm_ep_peer_set(qkm_ctx *c, uint32_t peer, void *xrecv, void *selrecv,
-                            const void *partial);
+QKM_API int qkm_ep_peer_buffers(qkm_ctx *c, void **xrecv, void **selrecv, void **back);
+QKM_API int qkm_ep_peer_set(qkm_ctx *c, uint32_t peer, void *xrecv, void *selrecv, void *back);
 QKM_API int qkm_ep_peer_export(qkm_ctx *c, void *handles);
 QKM_API int qkm_ep_peer_import(qkm_ctx *c, uint32_t peer, const void *handles);
 QKM_API int qkm_ep_push(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
                         uint32_t slot_rows);
-QKM_API int qkm_ep_forward_slots(qkm_ctx *c, uint32_t layer, uint32_t slot_rows);
+QKM_API int qkm_ep_forward_slots(qkm_ctx *c, uint32_t layer, uint32_t slot_rows,
+                                 uint32_t n_shared);
 QKM_API int qkm_ep_pull(qkm_ctx *c, uint32_t n_tokens, uint32_t slot_rows, float *y);
 /* The barrier as a kernel of the library: each rank stores a barrier number into a word of
  * every peer's buffer and polls its own words.  Every rank issues the same sequence of

@@ -110,7 +110,7 @@ SIGNATURES = {
     "qkm_ep_peer_export": (_I, [_VP, C.c_char_p]),
     "qkm_ep_peer_import": (_I, [_VP, _U32, C.c_char_p]),
     "qkm_ep_push": (_I, [_VP, _U32, _VP, _U32, _U32]),
-    "qkm_ep_forward_slots": (_I, [_VP, _U32, _U32]),
+    "qkm_ep_forward_slots": (_I, [_VP, _U32, _U32, _U32]),
     "qkm_ep_pull": (_I, [_VP, _U32, _U32, _VP]),
     "qkm_ep_barrier": (_I, [_VP, _U32]),
     "qkm_ep_peer_layer": (_I, [_VP, _U32, _VP, _U32, _U32, _VP, _U32]),
@@ -379,8 +379,10 @@ class Context:
     def ep_push(self, layer_idx, x, n, slot_rows):
         self.check(self.lib.qkm_ep_push(self.h, layer_idx, _p(x), n, slot_rows))
 
-    def ep_forward_slots(self, layer_idx, slot_rows):
-        self.check(self.lib.qkm_ep_forward_slots(self.h, layer_idx, slot_rows))
+    def ep_forward_slots(self, layer_idx, slot_rows, n_shared=None):
+        """n_shared=None: the shared expert was a separate ep_shared call; else this rank's token
+        count, and the shared expert runs beside the resident ones (no ep_shared call)."""
+        self.check(self.lib.qkm_ep_forward_slots(self.h, layer_idx, slot_rows, 0xFFFFFFFF if n_shared is None else n_shared))
 
     def ep_pull(self, n, slot_rows, y):
         self.check(self.lib.qkm_ep_pull(self.h, n, slot_rows, _p(y)))

@@ -89,7 +89,9 @@ struct qkm_ctx {
     // peer-memory form of the exchange: this rank's receive buffers and every rank's as mapped here
     uint32_t pm_ranks = 0, pm_rank = 0, pm_cap = 0;   // slot_cap rows per source rank
     uint32_t pm_epoch = 0;                            // barriers issued so far (qkm_ep_barrier)
-    float* pm_xrecv = nullptr; qkm_sel* pm_selrecv = nullptr; float* pm_partial = nullptr;
+    bool pm_shared_in_partial = false;                // the last qkm_ep_forward_slots included the shared expert
+    float* pm_xrecv = nullptr; qkm_sel* pm_selrecv = nullptr; float* pm_back = nullptr;   // mapped by the peers
+    float* pm_partial = nullptr;                      // local partial rows where the fold does not store to the peers
     EpPeerTable pm_peers{};
     void* pm_opened[kMaxPeerRanks][3] = {};           // mappings this context opened from handles
     // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
@@ -299,7 +301,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
     for (auto& o : c->pm_opened) for (void* p : o) if (p) cudaIpcCloseMemHandle(p);
-    for (void* p : {(void*)c->pm_xrecv, (void*)c->pm_selrecv, (void*)c->pm_partial}) if (p) cudaFree(p);
+    for (void* p : {(void*)c->pm_xrecv, (void*)c->pm_selrecv, (void*)c->pm_back, (void*)c->pm_partial}) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->ep_counts_host) cudaFreeHost(c->ep_counts_host);
     if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
@@ -1093,8 +1095,14 @@ extern "C" QKM_API int qkm_ep_shared(qkm_ctx* c, uint32_t layer, const float* x,
     return QKM_OK;
 }
 
-extern "C" QKM_API int qkm_ep_expert_forward(qkm_ctx* c, uint32_t layer, const float* xrecv, const qkm_sel* selrecv,
-                                             uint32_t n_recv, float* partial) {
+// Resident experts over n_recv rows -> partial.  with_shared: rows [sh_first, sh_first + sh_count)
+// are this rank's own tokens and also get the shared expert (its two GEMMs run beside the routed
+// ones on the side stream, as in qkm_moe_prefill), so their partial rows carry shared + routed.
+// slot_rows_peer != 0: the rows are slots of the peer-memory form and every live partial row is
+// stored into its source rank's return buffer instead of staying in `partial`.
+static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv, const qkm_sel* selrecv, uint32_t n_recv,
+                                  float* partial, bool with_shared, uint32_t sh_first, uint32_t sh_count,
+                                  uint32_t slot_rows_peer = 0) {
     if (int rc = layer_ready(c, layer)) return rc;
     c->shared_plan_n = 0;
     if (n_recv == 0) return QKM_OK;
@@ -1104,28 +1112,62 @@ extern "C" QKM_API int qkm_ep_expert_forward(qkm_ctx* c, uint32_t layer, const f
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     if (!ld.tiles_ok) {   // generic kernels on the raw layout
+        const float* y2 = nullptr;
+        if (with_shared && sh_count) {   // shared expert of the own rows first (it uses h too), added by the fold
+            const float* xo = xrecv + (size_t)sh_first * d.n_embd;
+            QKM_CUDA(c, cudaMemsetAsync(c->y2, 0, (size_t)n_recv * d.n_embd * sizeof(float), c->stream));
+            QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, xo, c->h, sh_count));
+            QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, selrecv + sh_first, c->y2 + (size_t)sh_first * d.n_embd, sh_count));
+            y2 = c->y2;
+        }
         QKM_LAUNCH(c, launch_group_pairs(c->L(), d, selrecv, n_recv, c->offsets, c->pairs, c->efirst, c->ecount));
         if (!c->contrib) QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
         QKM_LAUNCH(c, launch_gateup_pairs(c->L(), d, w.gateup_type, w.gate_exps, w.up_exps, xrecv, c->offsets, c->pairs, c->h, n_recv, c->efirst, c->ecount));
         QKM_CUDA(c, cudaMemsetAsync(c->contrib, 0, (size_t)n_recv * d.n_used * d.n_embd * sizeof(float), c->stream));
         QKM_LAUNCH(c, launch_down_pairs(c->L(), d, w.down_type, w.down_exps, c->h, selrecv, c->offsets, c->pairs, c->contrib, n_recv, c->efirst, c->ecount));
-        QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, nullptr, partial, n_recv));
+        QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, y2, partial, n_recv));
+        if (slot_rows_peer)
+            QKM_LAUNCH(c, launch_ep_return(c->L(), d, partial, selrecv, c->pm_peers, slot_rows_peer, c->pm_rank, c->pm_ranks,
+                                           with_shared ? sh_count : 0));
         return QKM_OK;
     }
     if (int rc = ensure_prefill_scratch(c)) return rc;
     const uint32_t NT = prefill_pairs_per_block();
     const uint32_t np_max = n_recv * d.n_used;
     const uint32_t tiles_now = c->ecount < np_max ? c->ecount + (np_max + NT - 1) / NT : np_max;
+    const uint32_t rt_gu = d.n_ff / 128, rt_dn = d.n_embd / 128;
     QKM_LAUNCH(c, launch_group_pairs_wide(c->L(), d, selrecv, n_recv, c->offsets, c->pairs, c->efirst, c->ecount, c->group_hist, c->pos_of));
     QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n_recv, c->mma_items[0], c->mma_items[1],
-                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of, false, true));
+                                  c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of, with_shared, true, sh_first,
+                                  with_shared ? sh_count : 0));
     QKM_LAUNCH(c, launch_to_f16_rows(c->L(), xrecv, c->xb, c->xscale, n_recv, d.n_embd));
+    const bool fork = with_shared && sh_count;
+    if (fork) {
+        const uint32_t sh_now = (sh_count + NT - 1) / NT;
+        Launch S{c->side, &c->launches};
+        QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
+        QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
+        QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
+                                        c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status));
+        QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, selrecv, c->pairs, c->mma_items[3],
+                                      c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
+        QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
+    }
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * (d.n_ff / 128), c->h, c->hb, c->status));
+                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
-                                  c->n_items + 1, tiles_now * (d.n_embd / 128), c->contrib_p, c->status));
-    QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, partial, n_recv));
+                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status));
+    if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
+    if (slot_rows_peer)
+        QKM_LAUNCH(c, launch_fold_pairs_peer(c->L(), d, c->contrib_p, c->pos_of, c->pm_peers, slot_rows_peer, c->pm_rank, c->pm_ranks));
+    else
+        QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, partial, n_recv));
     return QKM_OK;
+}
+
+extern "C" QKM_API int qkm_ep_expert_forward(qkm_ctx* c, uint32_t layer, const float* xrecv, const qkm_sel* selrecv,
+                                             uint32_t n_recv, float* partial) {
+    return ep_expert_forward_impl(c, layer, xrecv, selrecv, n_recv, partial, false, 0, 0);
 }
 
 extern "C" QKM_API int qkm_ep_combine(qkm_ctx* c, uint32_t n, uint32_t n_ranks, const float* back, float* y) {
@@ -1138,7 +1180,7 @@ extern "C" QKM_API int qkm_ep_combine(qkm_ctx* c, uint32_t n, uint32_t n_ranks, 
 
 // ---------------------------------------------------------------- expert parallel over peer memory
 // The same layer without an all-to-all.  Every rank keeps three receive buffers of
-// n_ranks * slot_cap rows (x rows, selection records, partial rows) and maps every peer's:
+// n_ranks * slot_cap rows (x rows, selection records, returned partial rows) and maps every peer's:
 //   qkm_ep_peer_setup   : allocate this rank's buffers
 //   qkm_ep_peer_export / qkm_ep_peer_import : CUDA IPC handles between processes of one node,
 //   or qkm_ep_peer_buffers / qkm_ep_peer_set  : raw pointers (one process driving several GPUs)
@@ -1146,13 +1188,14 @@ extern "C" QKM_API int qkm_ep_combine(qkm_ctx* c, uint32_t n, uint32_t n_ranks, 
 //   qkm_ep_push         : route the local tokens, store rows + records into the owners' buffers
 //   qkm_ep_shared       : the shared expert (no dependence on the peers)
 //   (host: barrier)     : all pushes have landed
-//   qkm_ep_forward_slots: resident experts over the n_ranks * slot_rows rows -> partial rows
-//   (host: barrier)     : all partial rows are written
-//   qkm_ep_pull         : y = shared + the partial rows, read from the owners' buffers
+//   qkm_ep_forward_slots: resident experts over the n_ranks * slot_rows rows; each partial row is
+//                         stored into its source rank's return buffer
+//   (host: barrier)     : all partial rows have landed
+//   qkm_ep_pull         : y = shared + the partial rows the owners returned
 // The two barriers also order the reuse of the buffers by the next layer: a rank pushes layer
 // l+1 after the second barrier of layer l, when every rank has finished reading the rows of l,
-// and overwrites its partial rows after the first barrier of l+1, which every rank enters
-// after its pull of l.  Kernels only store to and load from peer memory; none waits.
+// and stores partial rows of l+1 after the first barrier of l+1, which every rank enters after
+// its pull of l.  Kernels only store to and load from peer memory; none waits.
 
 constexpr size_t kPmFlagBytes = 256;
 static uint32_t* pm_flags_of(const qkm_ctx* c, void* selrecv) {
@@ -1164,7 +1207,7 @@ static int pm_check(qkm_ctx* c, uint32_t slot_rows) {
     if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
     if (slot_rows == 0 || slot_rows > c->pm_cap) return fail(c, QKM_ERR_BOUNDS, "slot_rows %u outside 1..%u", slot_rows, c->pm_cap);
     for (uint32_t r = 0; r < c->pm_ranks; ++r)
-        if (!c->pm_peers.x[r] || !c->pm_peers.sel[r] || !c->pm_peers.partial[r] || !c->pm_peers.flags[r])
+        if (!c->pm_peers.x[r] || !c->pm_peers.sel[r] || !c->pm_peers.back[r] || !c->pm_peers.flags[r])
             return fail(c, QKM_ERR_MODE, "buffers of rank %u are not mapped (qkm_ep_peer_import / qkm_ep_peer_set)", r);
     return QKM_OK;
 }
@@ -1185,27 +1228,29 @@ extern "C" QKM_API int qkm_ep_peer_setup(qkm_ctx* c, uint32_t n_ranks, uint32_t 
     QKM_CUDA(c, cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel) + kPmFlagBytes));
     QKM_CUDA(c, cudaMemset((char*)c->pm_selrecv + rows * sizeof(qkm_sel), 0, kPmFlagBytes));
     QKM_CUDA(c, cudaMalloc((void**)&c->pm_partial, rows * d.n_embd * sizeof(float)));
+    QKM_CUDA(c, cudaMalloc((void**)&c->pm_back, rows * d.n_embd * sizeof(float)));
+    QKM_CUDA(c, cudaMemset(c->pm_back, 0, rows * d.n_embd * sizeof(float)));
     QKM_CUDA(c, cudaMemset(c->pm_xrecv, 0, rows * d.n_embd * sizeof(float)));
     QKM_CUDA(c, cudaMemset(c->pm_selrecv, 0xFF, rows * sizeof(qkm_sel)));   // every record empty
     QKM_CUDA(c, cudaMemset(c->pm_partial, 0, rows * d.n_embd * sizeof(float)));
     c->pm_ranks = n_ranks; c->pm_rank = rank; c->pm_cap = slot_cap; c->pm_epoch = 0;
-    c->pm_peers.x[rank] = c->pm_xrecv; c->pm_peers.sel[rank] = c->pm_selrecv; c->pm_peers.partial[rank] = c->pm_partial;
+    c->pm_peers.x[rank] = c->pm_xrecv; c->pm_peers.sel[rank] = c->pm_selrecv; c->pm_peers.back[rank] = c->pm_back;
     c->pm_peers.flags[rank] = pm_flags_of(c, c->pm_selrecv);
     return QKM_OK;
 }
 
-extern "C" QKM_API int qkm_ep_peer_buffers(qkm_ctx* c, void** xrecv, void** selrecv, void** partial) {
-    if (!c || !xrecv || !selrecv || !partial) return QKM_ERR_ARG;
+extern "C" QKM_API int qkm_ep_peer_buffers(qkm_ctx* c, void** xrecv, void** selrecv, void** back) {
+    if (!c || !xrecv || !selrecv || !back) return QKM_ERR_ARG;
     if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
-    *xrecv = c->pm_xrecv; *selrecv = c->pm_selrecv; *partial = c->pm_partial;
+    *xrecv = c->pm_xrecv; *selrecv = c->pm_selrecv; *back = c->pm_back;
     return QKM_OK;
 }
 
-extern "C" QKM_API int qkm_ep_peer_set(qkm_ctx* c, uint32_t peer, void* xrecv, void* selrecv, const void* partial) {
-    if (!c || !xrecv || !selrecv || !partial) return QKM_ERR_ARG;
+extern "C" QKM_API int qkm_ep_peer_set(qkm_ctx* c, uint32_t peer, void* xrecv, void* selrecv, void* back) {
+    if (!c || !xrecv || !selrecv || !back) return QKM_ERR_ARG;
     if (!c->pm_ranks) return fail(c, QKM_ERR_MODE, "qkm_ep_peer_setup has not been called");
     if (peer >= c->pm_ranks || peer == c->pm_rank) return fail(c, QKM_ERR_ARG, "peer %u is not another rank of %u", peer, c->pm_ranks);
-    c->pm_peers.x[peer] = (float*)xrecv; c->pm_peers.sel[peer] = (qkm_sel*)selrecv; c->pm_peers.partial[peer] = (const float*)partial;
+    c->pm_peers.x[peer] = (float*)xrecv; c->pm_peers.sel[peer] = (qkm_sel*)selrecv; c->pm_peers.back[peer] = (float*)back;
     c->pm_peers.flags[peer] = pm_flags_of(c, selrecv);   // every rank uses the same slot_cap, hence the same offset
     return QKM_OK;
 }
@@ -1217,7 +1262,7 @@ extern "C" QKM_API int qkm_ep_peer_export(qkm_ctx* c, void* handles) {
     cudaIpcMemHandle_t h[3];
     QKM_CUDA(c, cudaIpcGetMemHandle(&h[0], c->pm_xrecv));
     QKM_CUDA(c, cudaIpcGetMemHandle(&h[1], c->pm_selrecv));
-    QKM_CUDA(c, cudaIpcGetMemHandle(&h[2], c->pm_partial));
+    QKM_CUDA(c, cudaIpcGetMemHandle(&h[2], c->pm_back));
     memcpy(handles, h, sizeof h);
     return QKM_OK;
 }
@@ -1253,16 +1298,21 @@ extern "C" QKM_API int qkm_ep_push(qkm_ctx* c, uint32_t layer, const float* x, u
     return QKM_OK;
 }
 
-extern "C" QKM_API int qkm_ep_forward_slots(qkm_ctx* c, uint32_t layer, uint32_t slot_rows) {
+extern "C" QKM_API int qkm_ep_forward_slots(qkm_ctx* c, uint32_t layer, uint32_t slot_rows, uint32_t n_shared) {
     if (int rc = pm_check(c, slot_rows)) return rc;
-    return qkm_ep_expert_forward(c, layer, c->pm_xrecv, c->pm_selrecv, c->pm_ranks * slot_rows, c->pm_partial);
+    if (n_shared != QKM_EP_NO_SHARED && n_shared > slot_rows) return fail(c, QKM_ERR_BOUNDS, "%u shared rows exceed slot_rows %u", n_shared, slot_rows);
+    const bool with_shared = n_shared != QKM_EP_NO_SHARED;
+    c->pm_shared_in_partial = with_shared;
+    return ep_expert_forward_impl(c, layer, c->pm_xrecv, c->pm_selrecv, c->pm_ranks * slot_rows, c->pm_partial, with_shared,
+                                  c->pm_rank * slot_rows, with_shared ? n_shared : 0, slot_rows);
 }
 
 extern "C" QKM_API int qkm_ep_pull(qkm_ctx* c, uint32_t n, uint32_t slot_rows, float* y) {
     if (int rc = pm_check(c, slot_rows)) return rc;
     if (!y && n) return QKM_ERR_ARG;
     if (n > slot_rows) return fail(c, QKM_ERR_BOUNDS, "%u tokens exceed slot_rows %u", n, slot_rows);
-    QKM_LAUNCH(c, launch_ep_pull(c->L(), c->cfg.dims, c->sel, c->pm_peers, c->y2, y, n, slot_rows, c->pm_rank, c->pm_ranks));
+    const bool own = c->pm_shared_in_partial;   // the shared expert came with this rank's partial rows
+    QKM_LAUNCH(c, launch_ep_pull(c->L(), c->cfg.dims, c->sel, c->pm_peers, own ? nullptr : c->y2, y, n, slot_rows, c->pm_rank, c->pm_ranks, own));
     return QKM_OK;
 }
 
@@ -1276,13 +1326,12 @@ extern "C" QKM_API int qkm_ep_barrier(qkm_ctx* c, uint32_t timeout_ms) {
     return QKM_OK;
 }
 
-// The whole layer in one call: push, shared expert, barrier, resident experts, barrier, pull.
+// The whole layer in one call: push, barrier, resident + shared experts, barrier, pull.
 extern "C" QKM_API int qkm_ep_peer_layer(qkm_ctx* c, uint32_t layer, const float* x, uint32_t n, uint32_t slot_rows, float* y,
                                          uint32_t timeout_ms) {
     if (int rc = qkm_ep_push(c, layer, x, n, slot_rows)) return rc;
-    if (int rc = qkm_ep_shared(c, layer, x, n)) return rc;
     if (int rc = qkm_ep_barrier(c, timeout_ms)) return rc;
-    if (int rc = qkm_ep_forward_slots(c, layer, slot_rows)) return rc;
+    if (int rc = qkm_ep_forward_slots(c, layer, slot_rows, n)) return rc;   // the shared expert rides with the resident ones
     if (int rc = qkm_ep_barrier(c, timeout_ms)) return rc;
     return qkm_ep_pull(c, n, slot_rows, y);
 }

@@ -11,8 +11,9 @@
 // Second form, without an all-to-all: every rank's receive buffers are mapped on every rank
 // (peer memory over NVLink).  The push kernel stores a token's row and selection record straight
 // into the buffers of each rank that owns one of its experts, at a row that depends only on
-// (source rank, token), so no counts are exchanged and nothing is packed; the pull kernel reads
-// the partial rows back from the peers' buffers while it sums them.  Only plain stores and
+// (source rank, token), so no counts are exchanged and nothing is packed; the owners store the
+// partial rows straight into the source's return buffer the same way (stores are posted, loads
+// from a peer are round trips), and the pull kernel sums them from local memory.  Only plain stores and
 // loads touch peer memory.  The host orders the phases with a barrier (any collective on the
 // stream); these kernels do not wait on anything either.
 #include <cuda_runtime.h>
@@ -115,7 +116,9 @@ ep_combine_kernel(const float* __restrict__ back, const uint32_t* __restrict__ s
 // One block per slot row i of this rank's region (slot_rows rows on every rank).  Rank d's
 // buffers get, at row rank * slot_rows + i: the selection record of token i and its x row if
 // token i selected an expert of d; otherwise a record whose ids are all past the expert table,
-// which the grouping kernels skip (rows i >= n_tokens are such records on every rank).
+// which the grouping kernels skip (rows i >= n_tokens are such records on every rank).  This
+// rank's own buffers always get the x row, and the weights of the record even when its ids are
+// blanked: the shared expert of the local tokens is computed from there.
 __global__ void __launch_bounds__(256)
 ep_push_kernel(const float* __restrict__ x, const qkm_sel* __restrict__ sel, EpPeerTable peers, uint32_t n_tokens,
                uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, uint32_t n_used, uint32_t experts_per_rank,
@@ -133,23 +136,40 @@ ep_push_kernel(const float* __restrict__ x, const qkm_sel* __restrict__ sel, EpP
         const uint32_t mine = i < n_tokens ? reinterpret_cast<const uint32_t*>(sel + i)[tid] : 0u;
         const uint32_t empty = tid < 16 ? kInvalid : 0u;
         for (uint32_t d = 0; d < n_ranks; ++d)
-            reinterpret_cast<uint32_t*>(peers.sel[d] + row)[tid] = (need >> d & 1u) ? mine : empty;
+            reinterpret_cast<uint32_t*>(peers.sel[d] + row)[tid] = (need >> d & 1u) ? mine : (d == rank && tid >= 16) ? mine : empty;
     }
-    if (!need) return;
+    if (i >= n_tokens) return;
+    const uint32_t dest = need | (1u << rank);
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)i * n_embd);
     for (uint32_t c = tid; c < n_embd / 4; c += blockDim.x) {
         const float4 v = __ldg(src + c);
         for (uint32_t d = 0; d < n_ranks; ++d)
-            if (need >> d & 1u) reinterpret_cast<float4*>(peers.x[d] + row * n_embd)[c] = v;
+            if (dest >> d & 1u) reinterpret_cast<float4*>(peers.x[d] + row * n_embd)[c] = v;
     }
 }
 
+// Slot row (source s, token i) of the local partial rows goes to rank s's return buffer at
+// (this rank, i), if a resident expert (or, for the first n_shared own rows, the shared expert)
+// contributed to it.  Used where the fold kernel does not store to the peers itself.
+__global__ void __launch_bounds__(256)
+ep_return_kernel(const float* __restrict__ partial, const qkm_sel* __restrict__ selrecv, EpPeerTable peers,
+                 uint32_t slot_rows, uint32_t rank, uint32_t n_used, uint32_t expert_first, uint32_t expert_count,
+                 uint32_t n_shared, uint32_t n_embd) {
+    const uint32_t r = blockIdx.x, src = r / slot_rows, i = r - src * slot_rows;
+    bool live = src == rank && i < n_shared;
+    for (uint32_t s = 0; s < n_used; ++s) live |= (__ldg(&selrecv[r].ids[s]) - expert_first) < expert_count;
+    if (!live) return;
+    const float4* from = reinterpret_cast<const float4*>(partial + (size_t)r * n_embd);
+    float4* to = reinterpret_cast<float4*>(peers.back[src] + ((size_t)rank * slot_rows + i) * n_embd);
+    for (uint32_t c = threadIdx.x; c < n_embd / 4; c += blockDim.x) to[c] = from[c];
+}
+
 // y[t] = y2[t] + sum over the ranks that own one of t's experts, in rank order, of the partial
-// row that rank computed for (this rank, t), read from that rank's buffer.
+// row that rank returned for t (row rank d * slot_rows + t of this rank's return buffer).
 __global__ void __launch_bounds__(256)
 ep_pull_kernel(const qkm_sel* __restrict__ sel, EpPeerTable peers, const float* __restrict__ y2, float* __restrict__ y,
                uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, uint32_t n_used, uint32_t experts_per_rank,
-               uint32_t n_embd) {
+               uint32_t n_embd, uint32_t own_always) {
     const uint32_t t = blockIdx.y;
     const uint32_t o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
     if (o >= n_embd) return;
@@ -158,11 +178,12 @@ ep_pull_kernel(const qkm_sel* __restrict__ sel, EpPeerTable peers, const float* 
         const uint32_t r = __ldg(&sel[t].ids[s]) / experts_per_rank;
         if (r < n_ranks) need |= 1u << r;
     }
-    const size_t row = (size_t)rank * slot_rows + t;
+    if (own_always) need |= 1u << rank;   // this rank's partial row carries the shared expert
+    const float* back = peers.back[rank];
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
     for (uint32_t d = 0; d < n_ranks; ++d) {
         if (!(need >> d & 1u)) continue;
-        const float4 c = *reinterpret_cast<const float4*>(peers.partial[d] + row * n_embd + o);
+        const float4 c = *reinterpret_cast<const float4*>(back + ((size_t)d * slot_rows + t) * n_embd + o);
         v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
     }
     if (y2) {
@@ -224,14 +245,24 @@ cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, c
     return cudaGetLastError();
 }
 
+cudaError_t launch_ep_return(const Launch& L, const qkm_dims& d, const float* partial, const qkm_sel* selrecv,
+                             const EpPeerTable& peers, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, uint32_t n_shared) {
+    if (slot_rows == 0 || n_ranks == 0 || n_ranks > kMaxPeerRanks || rank >= n_ranks || d.n_expert % n_ranks) return cudaErrorInvalidValue;
+    const uint32_t per = d.n_expert / n_ranks;
+    ep_return_kernel<<<n_ranks * slot_rows, 256, 0, L.stream>>>(partial, selrecv, peers, slot_rows, rank, d.n_used, rank * per, per,
+                                                                n_shared, d.n_embd);
+    L.count();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_ep_pull(const Launch& L, const qkm_dims& d, const qkm_sel* sel, const EpPeerTable& peers, const float* y2,
-                           float* y, uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks) {
+                           float* y, uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, bool own_always) {
     if (n_ranks == 0 || n_ranks > kMaxPeerRanks || d.n_expert % n_ranks || rank >= n_ranks || n_tokens > slot_rows)
         return cudaErrorInvalidValue;
     if (n_tokens == 0) return cudaSuccess;
     const dim3 grid((d.n_embd / 4 + 255) / 256, n_tokens);
     ep_pull_kernel<<<grid, 256, 0, L.stream>>>(sel, peers, y2, y, slot_rows, rank, n_ranks, d.n_used, d.n_expert / n_ranks,
-                                               d.n_embd);
+                                               d.n_embd, own_always ? 1u : 0u);
     L.count();
     return cudaGetLastError();
 }

@@ -42,7 +42,8 @@ cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float*
 cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
                             uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
                             MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of,
-                            bool with_shared = true, bool routed_pos_done = false);
+                            bool with_shared = true, bool routed_pos_done = false, uint32_t sh_first = 0,
+                            uint32_t sh_count = 0xFFFFFFFFu /* all rows */);
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
@@ -196,15 +197,20 @@ constexpr uint32_t kMaxPeerRanks = 16;
 struct EpPeerTable {
     float* x[kMaxPeerRanks];          // [n_ranks * slot_rows][n_embd] rows pushed by the sources
     qkm_sel* sel[kMaxPeerRanks];      // their selection records
-    const float* partial[kMaxPeerRanks];  // one weighted partial row per received row
+    float* back[kMaxPeerRanks];       // [n_ranks * slot_rows][n_embd] partial rows returned by the owners
     uint32_t* flags[kMaxPeerRanks];   // [n_ranks] barrier words, word s written by rank s
 };
 cudaError_t launch_ep_barrier(const Launch& L, const EpPeerTable& peers, uint32_t rank, uint32_t n_ranks, uint32_t epoch,
                               uint64_t limit_ns, uint32_t* status);
 cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel, const EpPeerTable& peers,
                            uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
+cudaError_t launch_fold_pairs_peer(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,
+                                   const EpPeerTable& peers, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
+cudaError_t launch_ep_return(const Launch& L, const qkm_dims& d, const float* partial, const qkm_sel* selrecv,
+                             const EpPeerTable& peers, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, uint32_t n_shared);
 cudaError_t launch_ep_pull(const Launch& L, const qkm_dims& d, const qkm_sel* sel, const EpPeerTable& peers, const float* y2,
-                           float* y, uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
+                           float* y, uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks,
+                           bool own_always);
 cudaError_t launch_ep_plan(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens, uint32_t n_ranks,
                            uint32_t* counts, uint32_t* send_tok, uint32_t* send_pos);
 cudaError_t launch_ep_pack(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel,

@@ -83,7 +83,7 @@ to_f16_rows_kernel(const float* __restrict__ x, __half* __restrict__ xh, float* 
 __global__ void __launch_bounds__(512)
 mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pairs, uint32_t n_expert_local,
                 uint32_t n_tokens, uint32_t n_used, uint32_t rt_gu, uint32_t rt_dn, uint32_t with_shared,
-                uint32_t routed_pos_done,
+                uint32_t routed_pos_done, uint32_t sh_first, uint32_t sh_count,
                 MmaItem* __restrict__ items_gu, MmaItem* __restrict__ items_dn, MmaItem* __restrict__ items_sh_gu,
                 MmaItem* __restrict__ items_sh_dn, uint32_t* __restrict__ n_items, uint32_t* __restrict__ pos_of) {
     __shared__ uint32_t s_scan[512];
@@ -110,12 +110,15 @@ mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pai
         for (uint32_t r = 0; r < rt_gu; ++r) { it.rt = (uint16_t)r; items_gu[(size_t)(first + ti) * rt_gu + r] = it; }
         for (uint32_t r = 0; r < rt_dn; ++r) { it.rt = (uint16_t)r; items_dn[(size_t)(first + ti) * rt_dn + r] = it; }
     }
-    const uint32_t sh_tiles = with_shared ? (n_tokens + pf::kNT - 1) / pf::kNT : 0;
+    // the shared expert takes rows [sh_first, sh_first + sh_count): all rows of a single-GPU
+    // chunk, this rank's own tokens among the received rows of an expert-parallel shard
+    const uint32_t sh_n = with_shared ? sh_count : 0;
+    const uint32_t sh_tiles = (sh_n + pf::kNT - 1) / pf::kNT;
     for (uint32_t ti = e; ti < sh_tiles; ti += 512) {
         MmaItem it;
         it.expert = 0;
         it.pair_off = np + ti * pf::kNT;
-        it.n = min((uint32_t)pf::kNT, n_tokens - ti * pf::kNT);
+        it.n = min((uint32_t)pf::kNT, sh_n - ti * pf::kNT);
         for (uint32_t r = 0; r < rt_gu; ++r) { it.rt = (uint16_t)r; items_sh_gu[(size_t)ti * rt_gu + r] = it; }
         for (uint32_t r = 0; r < rt_dn; ++r) { it.rt = (uint16_t)r; items_sh_dn[(size_t)ti * rt_dn + r] = it; }
     }
@@ -129,8 +132,10 @@ mma_plan_kernel(const uint32_t* __restrict__ offsets, uint32_t* __restrict__ pai
             pos_of[(pr >> 4) * (n_used + 1) + (pr & 15u)] = p;
         }
     for (uint32_t t = e; t < n_tokens; t += 512) {
-        if (with_shared) pairs[np + t] = (t << 4) | n_used;
-        pos_of[t * (n_used + 1) + n_used] = with_shared ? np + t : 0xFFFFFFFFu;
+        const uint32_t j = t - sh_first;          // wraps below the range
+        const bool in = j < sh_n;
+        if (in) pairs[np + j] = (t << 4) | n_used;
+        pos_of[t * (n_used + 1) + n_used] = in ? np + j : 0xFFFFFFFFu;
     }
 }
 
@@ -832,6 +837,29 @@ __global__ void fold_pairs_kernel(const float* __restrict__ contrib, const uint3
     *reinterpret_cast<float4*>(y + (size_t)t * n_embd + o) = v;
 }
 
+// The same sum for an expert-parallel shard whose rows are slots (source rank s, token i): the
+// row goes straight into rank s's return buffer, at (this rank, i), over the peer mapping; a
+// slot none of whose pairs ran here is not written (its owner does not read it).
+__global__ void fold_pairs_peer_kernel(const float* __restrict__ contrib, const uint32_t* __restrict__ pos_of,
+                                       EpPeerTable peers, uint32_t slot_rows, uint32_t rank, uint32_t n_used,
+                                       uint32_t n_embd) {
+    const uint32_t t = blockIdx.y;
+    const uint32_t o = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (o >= n_embd) return;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    bool any = false;
+    for (uint32_t s = 0; s <= n_used; ++s) {
+        const uint32_t p = pos_of[t * (n_used + 1) + s];
+        if (p == 0xFFFFFFFFu) continue;
+        any = true;
+        const float4 c = *reinterpret_cast<const float4*>(contrib + (size_t)p * n_embd + o);
+        v.x += c.x; v.y += c.y; v.z += c.z; v.w += c.w;
+    }
+    if (!any) return;
+    const uint32_t src = t / slot_rows, i = t - src * slot_rows;
+    *reinterpret_cast<float4*>(peers.back[src] + ((size_t)rank * slot_rows + i) * n_embd + o) = v;
+}
+
 // ---- launchers ---------------------------------------------------------------------------------------------
 uint32_t prefill_pairs_per_block() { return pf::kNT; }
 
@@ -845,10 +873,12 @@ cudaError_t launch_to_f16_rows(const Launch& L, const float* x, void* xh, float*
 cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* offsets, uint32_t* pairs,
                             uint32_t n_expert_local, uint32_t n_tokens, MmaItem* items_gu, MmaItem* items_dn,
                             MmaItem* items_sh_gu, MmaItem* items_sh_dn, uint32_t* n_items, uint32_t* pos_of,
-                            bool with_shared, bool routed_pos_done) {
+                            bool with_shared, bool routed_pos_done, uint32_t sh_first, uint32_t sh_count) {
     if (n_expert_local > 512) return cudaErrorInvalidValue;
+    if (sh_count == 0xFFFFFFFFu) { sh_first = 0; sh_count = n_tokens; }
+    if (sh_first > n_tokens || sh_count > n_tokens - sh_first) return cudaErrorInvalidValue;
     mma_plan_kernel<<<1, 512, 0, L.stream>>>(offsets, pairs, n_expert_local, n_tokens, d.n_used, d.n_ff / 128,
-                                             d.n_embd / 128, with_shared ? 1u : 0u, routed_pos_done ? 1u : 0u, items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, pos_of);
+                                             d.n_embd / 128, with_shared ? 1u : 0u, routed_pos_done ? 1u : 0u, sh_first, sh_count, items_gu, items_dn, items_sh_gu, items_sh_dn, n_items, pos_of);
     L.count();
     return cudaGetLastError();
 }
@@ -911,6 +941,15 @@ cudaError_t launch_fold_pairs(const Launch& L, const qkm_dims& d, const float* c
     if (n_tokens == 0) return cudaSuccess;
     const dim3 grid((d.n_embd / 4 + 255) / 256, n_tokens);
     fold_pairs_kernel<<<grid, 256, 0, L.stream>>>(contrib, pos_of, y, d.n_used, d.n_embd);
+    L.count();
+    return cudaGetLastError();
+}
+
+cudaError_t launch_fold_pairs_peer(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,
+                                   const EpPeerTable& peers, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks) {
+    if (slot_rows == 0 || n_ranks == 0 || n_ranks > kMaxPeerRanks || rank >= n_ranks) return cudaErrorInvalidValue;
+    const dim3 grid((d.n_embd / 4 + 255) / 256, n_ranks * slot_rows);
+    fold_pairs_peer_kernel<<<grid, 256, 0, L.stream>>>(contrib, pos_of, peers, slot_rows, rank, d.n_used, d.n_embd);
     L.count();
     return cudaGetLastError();
 }

@@ -122,8 +122,7 @@ class PeerExpertParallel:
             eng.ep_peer_layer(layer, x, n, rows, y, self.timeout_ms)
             return
         eng.ep_push(layer, x, n, rows)
-        eng.ep_shared(layer, x, n)
         self.barrier()                      # every rank's rows have landed
-        eng.ep_forward_slots(layer, rows)
+        eng.ep_forward_slots(layer, rows, n)   # the shared expert of the local rows rides along
         self.barrier()                      # every rank's partial rows are written
         eng.ep_pull(n, rows, y)

@@ -118,30 +118,48 @@ class OracleEngine:
                     sr[base + i] = self.sel[i:i + 1].view(np.uint8).reshape(160)
                 else:
                     sr[base + i] = empty
+                    if i < n and d == self.rank:      # own rows always travel: the shared expert reads them
+                        xr[base + i] = xn[i]
+                        sr[base + i, 64:] = self.sel[i:i + 1].view(np.uint8).reshape(160)[64:]
 
-    def ep_forward_slots(self, layer, slot_rows):
+    def ep_forward_slots(self, layer, slot_rows, n_shared=None):
         from conftest import entry
-        xr, sr, pr = self.peers[self.rank]
+        xr, sr, _ = self.peers[self.rank]
         rows = self.world * slot_rows
         sel = sr[:rows].copy().reshape(-1).view(entry.package().SEL_DTYPE)
         live = (sel["ids"][:, :self.dims.n_used] < self.dims.n_expert).any(axis=1)
-        pr[:rows] = 0
+        pr = np.zeros((rows, self.dims.n_embd), np.float32)
         if live.any():
             idx = np.nonzero(live)[0]
             out = self.orc.moe_layer(self.slices[layer], np.ascontiguousarray(xr[idx]), sel_in=sel[idx].copy(), with_shared=False)
             pr[idx] = out["y"]
+        self.shared_in_partial = n_shared is not None
+        if n_shared:
+            own = slice(self.rank * slot_rows, self.rank * slot_rows + n_shared)
+            sh = sel[own].copy()
+            sh["ids"][:, :self.dims.n_used] = 1       # experts outside the one-expert slice: shared only
+            lone = self.layers[layer].expert_slice(0, 1)
+            pr[own] += self.orc.moe_layer(lone, np.ascontiguousarray(xr[own]), sel_in=sh, with_shared=True)["y"]
+            live[own] = True
+        # every live partial row goes to its source rank's return buffer, at (this rank, token)
+        for r in np.nonzero(live)[0]:
+            src, i = divmod(int(r), slot_rows)
+            self.peers[src][2][self.rank * slot_rows + i] = pr[r]
 
     def ep_pull(self, n, slot_rows, y):
         if n == 0:
             return
         need = self._need(n)
+        if self.shared_in_partial:
+            need[:, self.rank] = True
+        back = self.peers[self.rank][2]
         out = np.zeros((n, self.dims.n_embd), np.float32)
         for d in range(self.world):
-            pr = self.peers[d][2]
             for t in range(n):
                 if need[t, d]:
-                    out[t] += pr[self.rank * slot_rows + t]
-        out += self.y2
+                    out[t] += back[d * slot_rows + t]
+        if not self.shared_in_partial:
+            out += self.y2
         y.numpy()[:n] = out
 
     def close_peers(self):

@@ -139,7 +139,7 @@ def _download(c, ptr, dtype, shape):
     return out
 
 
-def run_ep_peer(pkg, orc, syn, dims, layer, x_parts, G, tol, slot_rows=None, cap_extra=0):
+def run_ep_peer(pkg, orc, syn, dims, layer, x_parts, G, tol, slot_rows=None, cap_extra=0, merged=True):
     """G sharded contexts on one device; each has the others' receive buffers as raw pointers,
     which is what a peer mapping is to the kernels.  Phases are separated by a sync of every
     context (the barrier of the multi-GPU driver)."""
@@ -165,7 +165,8 @@ def run_ep_peer(pkg, orc, syn, dims, layer, x_parts, G, tol, slot_rows=None, cap
         n = xp.shape[0]
         d_x = c.to_device(xp) if n else c.alloc(16)
         c.ep_push(0, d_x, n, rows)
-        c.ep_shared(0, d_x, n)
+        if not merged:
+            c.ep_shared(0, d_x, n)
         d_xs.append(d_x)
         sel = c.last_sel(n) if n else np.zeros(0, SEL_DTYPE)
         if n:
@@ -186,8 +187,8 @@ def run_ep_peer(pkg, orc, syn, dims, layer, x_parts, G, tol, slot_rows=None, cap
             empty = np.ones(rows, bool)
             empty[:n] = ~need
             assert (got["ids"][empty][:, :dims.n_used] == 0xFFFFFFFF).all()
-    for c in ctxs:
-        c.ep_forward_slots(0, rows)
+    for c, xp in zip(ctxs, x_parts):
+        c.ep_forward_slots(0, rows, xp.shape[0] if merged else None)
     for c in ctxs:
         c.sync()
     worst = 0.0
@@ -206,15 +207,16 @@ def run_ep_peer(pkg, orc, syn, dims, layer, x_parts, G, tol, slot_rows=None, cap
     assert worst < tol, worst
 
 
+@pytest.mark.parametrize("merged", [True, False])
 @pytest.mark.parametrize("G,T,extra", [(2, 24, 0), (4, 40, 5), (8, 200, 0), (2, 300, 0)])
-def test_ep_peer_full_size_shapes(pkg, orc, syn, G, T, extra):
+def test_ep_peer_full_size_shapes(pkg, orc, syn, G, T, extra, merged):
     dims = syn.Dims()
     layer = syn.make_layer(dims, seed=46)
     x = syn.random_x(T, dims.n_embd, seed=64)
     cuts = np.linspace(0, T, G + 1).astype(int)
     cuts[1] = min(T, cuts[1] + 3)                       # uneven shares
     parts = [x[cuts[r]:cuts[r + 1]] for r in range(G)]
-    run_ep_peer(pkg, orc, syn, dims, layer, parts, G, TOL_BF16, cap_extra=extra)
+    run_ep_peer(pkg, orc, syn, dims, layer, parts, G, TOL_BF16, cap_extra=extra, merged=merged)
 
 
 def test_ep_peer_rank_without_tokens_and_tight_slots(pkg, orc, syn):
@@ -229,6 +231,7 @@ def test_ep_peer_generic_kernels_f32(pkg, orc, syn):
     layer = syn.make_layer(dims, seed=48, down_type=syn.Q6_K)
     x = syn.random_x(10, dims.n_embd, seed=66)
     run_ep_peer(pkg, orc, syn, dims, layer, [x[:6], x[6:]], 2, TOL_F32)
+    run_ep_peer(pkg, orc, syn, dims, layer, [x[:6], x[6:]], 2, TOL_F32, merged=False)
 
 
 def test_ep_peer_argument_checks(pkg, syn):
