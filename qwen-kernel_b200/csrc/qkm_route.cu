@@ -839,6 +839,17 @@ struct PlanArgs {
     uint32_t chunks_gu, chunks_dn, tok_per_item;
 };
 
+// Expert id -> index inside the resident range [expert_first, expert_first + expert_count);
+// a result >= expert_count means "not here" (the subtraction wraps for ids below the range).
+// With every expert resident an id past the table is clamped to the last expert, as the
+// reference's moe_group_pairs.comp does; on a shard it marks an empty record that no rank
+// takes (the peer-memory exchange fills unused slots with such records).
+__device__ __forceinline__ uint32_t local_expert_of(uint32_t id, uint32_t n_expert, uint32_t expert_first,
+                                                    uint32_t expert_count) {
+    if (expert_count >= n_expert) return min(id, n_expert - 1) - expert_first;
+    return id < n_expert ? id - expert_first : 0xFFFFFFFFu;
+}
+
 __global__ void __launch_bounds__(512)
 group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t n_expert, uint32_t n_used,
                    uint32_t expert_first, uint32_t expert_count, uint32_t n_chunks, uint32_t stage_ids,
@@ -857,15 +868,13 @@ group_pairs_kernel(const qkm_sel* __restrict__ sel, uint32_t n_tokens, uint32_t 
     if (stage_ids)
         for (uint32_t p = tid; p < np; p += 512) {
             const uint32_t t = p / n_used, s = p - t * n_used;
-            const uint32_t id = sel[t].ids[s];   // an id past the table marks an empty record
-            s_ids[p] = id < n_expert ? id - expert_first : 0xFFFFFFFFu;  // wraps when below
+            s_ids[p] = local_expert_of(sel[t].ids[s], n_expert, expert_first, expert_count);
         }
     __syncthreads();
     auto local_expert = [&](uint32_t p) -> uint32_t {
         if (stage_ids) return s_ids[p];
         const uint32_t t = p / n_used, s = p - t * n_used;
-        const uint32_t id = sel[t].ids[s];
-        return id < n_expert ? id - expert_first : 0xFFFFFFFFu;
+        return local_expert_of(sel[t].ids[s], n_expert, expert_first, expert_count);
     };
     const uint32_t p0 = tid * chunk, p1 = min(np, p0 + chunk);
     if (tid < n_chunks) {
@@ -1027,10 +1036,9 @@ constexpr uint32_t kInvalid = 0xFFFFFFFFu;
 }  // namespace gw
 
 __device__ __forceinline__ uint32_t gw_local_expert(const qkm_sel* __restrict__ sel, uint32_t p, uint32_t n_used,
-                                                    uint32_t n_expert, uint32_t expert_first) {
+                                                    uint32_t n_expert, uint32_t expert_first, uint32_t expert_count) {
     const uint32_t t = p / n_used, s = p - t * n_used;
-    const uint32_t id = sel[t].ids[s];   // an id past the table marks an empty record: no expert takes it
-    return id < n_expert ? id - expert_first : 0xFFFFFFFFu;   // wraps above expert_count when below the range
+    return local_expert_of(sel[t].ids[s], n_expert, expert_first, expert_count);
 }
 
 __global__ void __launch_bounds__(gw::kWarps * 32)
@@ -1046,7 +1054,7 @@ group_count_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used
     for (uint32_t i = 0; i < gw::kRun; i += 32) {
         const uint32_t p = p0 + i + lane;
         if (p < np) {
-            const uint32_t e = gw_local_expert(sel, p, n_used, n_expert, expert_first);
+            const uint32_t e = gw_local_expert(sel, p, n_used, n_expert, expert_first, expert_count);
             if (e < expert_count) atomicAdd(&mine[e], 1u);
         }
     }
@@ -1116,7 +1124,7 @@ group_place_kernel(const qkm_sel* __restrict__ sel, uint32_t np, uint32_t n_used
         const uint32_t p = p0 + i + lane;
         uint32_t e = gw::kInvalid;
         if (p < np) {
-            e = gw_local_expert(sel, p, n_used, n_expert, expert_first);
+            e = gw_local_expert(sel, p, n_used, n_expert, expert_first, expert_count);
             if (e >= expert_count) e = gw::kInvalid;
         }
         // lanes with the same expert: rank by lane, the lowest lane keeps the run's counter
