@@ -1223,6 +1223,7 @@ extern "C" QKM_API int qkm_ep_peer_setup(qkm_ctx* c, uint32_t n_ranks, uint32_t 
     if (slot_cap == 0 || (uint64_t)slot_cap * n_ranks > c->cfg.max_tokens)
         return fail(c, QKM_ERR_BOUNDS, "%u ranks x %u rows exceed max_tokens %u", n_ranks, slot_cap, c->cfg.max_tokens);
     const size_t rows = (size_t)n_ranks * slot_cap;
+    QKM_CUDA(c, cudaSetDevice(c->device));
     QKM_CUDA(c, cudaMalloc((void**)&c->pm_xrecv, rows * d.n_embd * sizeof(float)));
     // the barrier words of qkm_ep_barrier sit behind the records, so three mappings carry everything
     QKM_CUDA(c, cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel) + kPmFlagBytes));
@@ -1274,6 +1275,7 @@ extern "C" QKM_API int qkm_ep_peer_import(qkm_ctx* c, uint32_t peer, const void*
     if (c->pm_opened[peer][0]) return fail(c, QKM_ERR_MODE, "buffers of rank %u are already mapped", peer);
     cudaIpcMemHandle_t h[3];
     memcpy(h, handles, sizeof h);
+    QKM_CUDA(c, cudaSetDevice(c->device));   // the mappings belong to this context's device
     void* p[3] = {};
     for (int i = 0; i < 3; ++i) {
         const cudaError_t e = cudaIpcOpenMemHandle(&p[i], h[i], cudaIpcMemLazyEnablePeerAccess);
