@@ -503,6 +503,13 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
                     for i, nm in enumerate(names):
                         acc[nm] += ev[i].elapsed_time(ev[i + 1]) * 1e3 / PL
                 entry_["peer_memory"]["stages_us"] = acc
+            # the peer-memory form is the product path: its figures lead the entry, the all-to-all form sits beside them
+            pm = entry_.pop("peer_memory")
+            a2a = {k: entry_[k] for k in ("us_per_layer", "tok_s", "rel_err_vs_oracle", "launches_per_layer", "exchange")}
+            entry_.update(pm)
+            entry_["tensor_tflops"] = T * TENSOR_FLOPS_PER_TOKEN / (pm["us_per_layer"] * 1e-6) / 1e12
+            entry_["frac_of_measured_bf16_burst"] = entry_["tensor_tflops"] / peaks["bf16_tflops"]
+            entry_["nccl_all_to_all"] = a2a
         out["chunks"][str(T)] = entry_
     if world == 1:
         ctx.profile_enable(True)
@@ -522,7 +529,8 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
                                "frac": fl / (gu * 1e-6) / 1e12 / peaks["bf16_tflops"],
                                "peak_source": peaks["source"] + " cuBLAS bf16 burst", "traffic": None}
     out["workload"] = ("moe_prefill: one layer, chunks of T tokens, tcgen05 expert GEMMs" if world == 1 else
-                       f"expert-parallel moe layer: T tokens over {world} GPUs ({per} experts each), all-to-all over NVLink")
+                       f"expert-parallel moe layer: T tokens over {world} GPUs ({per} experts each), rows stored into the "
+                       "owners' peer-mapped buffers over NVLink (NCCL all-to-all form beside it)")
     out["scaling"] = "strong"
     R.barrier()
     ctx.close()

@@ -117,6 +117,11 @@ struct qkm_ctx {
         cudaEventRecord(prof_ev[++prof_n], stream);
     }
     Launch L() { return Launch{stream, &launches}; }
+    // decode chain (logits -> selection -> gate/up -> down -> next layer's logits): each kernel is
+    // launched as a programmatic dependent of the one before, so its scheduling and set-up overlap
+    // that kernel's tail.  Off unless QKM_PDL=1 is in the environment when the context is opened.
+    bool use_pdl = false;
+    Launch Lchain() { return Launch{stream, &launches, use_pdl && !profiling}; }
 };
 
 namespace {
@@ -207,6 +212,7 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
     if (!c) return bail("qkm_open: out of host memory", nullptr);
     c->cfg = *cfg;
     c->device = dev;
+    if (const char* v = getenv("QKM_PDL")) c->use_pdl = v[0] == '1';
     c->efirst = efirst;
     c->ecount = ecount;
     c->layers.resize(cfg->n_layer);
@@ -612,7 +618,7 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     // cuts the work lists; otherwise a grouping launch follows.
     const RoutePlan rplan{c->route_counter, c->offsets, c->pairs, c->items_gu, c->items_dn, c->n_items,
                           d.n_ff / gateup_stream_rows_per_item(), d.n_embd / down_stream_rows_per_item(), 2, c->efirst, c->ecount, 1};
-    QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
+    QKM_LAUNCH(c, launch_route_select(c->Lchain(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes,
                                       nullptr, nullptr, nullptr, nullptr, nullptr, fused_plan ? &rplan : nullptr));
     c->prof_mark("moe.route");
     if (!fused_plan) {
@@ -622,12 +628,12 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         c->prof_mark("moe.pairs");
     }
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_planes, 0));
-    QKM_LAUNCH(c, launch_gateup_stream(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xplanes, c->xscale, c->pairs,
+    QKM_LAUNCH(c, launch_gateup_stream(fused_plan ? c->Lchain() : c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xplanes, c->xscale, c->pairs,
                                        c->items_gu, c->n_items, c->h, c->hpieces, nb, c->status));
     c->prof_mark("moe.gu");
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     if (ld.stream_ok) {
-        QKM_LAUNCH(c, launch_down_tok(c->L(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->y2, y, n, nb, c->status));
+        QKM_LAUNCH(c, launch_down_tok(c->Lchain(), d, w.down_type, ld.tiles[4], c->hpieces, c->sel, c->y2, y, n, nb, c->status));
     } else {   // Q6_K down: f32 kernel over h, routed slots and the shared expert in one pass
         QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));
     }

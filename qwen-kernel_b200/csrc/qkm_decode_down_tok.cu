@@ -37,6 +37,7 @@ down_tok_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __re
     const uint32_t KB = d.n_ff / 256, n_teams = dt::kWarps / KB;
     const uint32_t team = warp / KB, kb = warp - team * KB;
     const uint32_t RT = d.n_embd / 16;  // row tiles = units per token
+    pdl_trigger();
 
     const uint32_t bar_base = (base + 15u) & ~15u;
     const uint32_t low_ring = (bar_base + dt::kWarps * dt::kStages * 8 + 127u) & ~127u;
@@ -65,6 +66,7 @@ down_tok_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __re
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();                         // the gate/up kernel's pieces and the selection are complete
 
     const uint32_t teams_total = gridDim.x * n_teams, team_global = blockIdx.x * n_teams + team;
     const uint64_t units_total = (uint64_t)n_tokens * RT;
@@ -193,10 +195,10 @@ cudaError_t launch_down_tok(const Launch& L, const qkm_dims& d, uint32_t type, c
                         (size_t)dt::kWarps * 128 * 4 + (size_t)dt::kWarps * 16 * 4 + 256;
     cudaError_t e = cudaFuncSetAttribute(down_tok_iq4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    down_tok_iq4_kernel<<<n_blocks, dt::kWarps * 32, smem, L.stream>>>(
-        (const uint8_t*)tiles, (const __nv_bfloat16*)hpieces, sel, y2, y, n_tokens, d, status);
+    e = launch_kernel(L, down_tok_iq4_kernel, dim3(n_blocks), dim3(dt::kWarps * 32), smem, (const uint8_t*)tiles,
+                      (const __nv_bfloat16*)hpieces, sel, y2, y, n_tokens, d, status);
     L.count();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 }  // namespace qkm

@@ -150,7 +150,7 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
     const uint32_t n_teams = C::kWarps / KB;
     const uint32_t team = warp / KB, kb = warp - team * KB;
     const uint32_t RT = d.n_ff / 16;             // row tiles per expert matrix
-    const uint32_t n_items = *n_items_ptr;
+    pdl_trigger();
 
     const uint32_t bar_base = (base + 15u) & ~15u;                      // kWarps * kStages barriers
     const uint32_t low_ring = (bar_base + C::kWarps * gu::kStages * 8 + 127u) & ~127u;
@@ -189,6 +189,8 @@ gateup_stream_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __re
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();                                  // tables and barriers are set up; now the work lists may be read
+    const uint32_t n_items = *n_items_ptr;
 
     // this team's contiguous share of the flat unit list
     const uint32_t teams_total = gridDim.x * n_teams, team_global = blockIdx.x * n_teams + team;
@@ -323,11 +325,11 @@ static cudaError_t gateup_stream_launch(const Launch& L, const qkm_dims& d, cons
                                  : 1024 + kRings + (size_t)C::kWarps * gu::red_floats<FMT>() * 4;
     cudaError_t e = cudaFuncSetAttribute(gateup_stream_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gateup_stream_kernel<FMT><<<n_blocks, C::kWarps * 32, smem, L.stream>>>(
-        (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, xplanes, xscale, pairs, items, n_items, h,
-        (__nv_bfloat16*)hpieces, d, status);
+    e = launch_kernel(L, gateup_stream_kernel<FMT>, dim3(n_blocks), dim3(C::kWarps * 32), smem,
+                      (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, xplanes, xscale, pairs, items, n_items, h,
+                      (__nv_bfloat16*)hpieces, d, status);
     L.count();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 cudaError_t launch_gateup_stream(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,

@@ -14,8 +14,31 @@ namespace qkm {
 struct Launch {
     cudaStream_t stream;
     uint64_t* launches;
+    // programmatic dependent launch: the kernel may be scheduled while the previous kernel of the
+    // stream is still running; it runs its set-up, then waits (pdl_wait) for that kernel's results
+    bool pdl = false;
     void count(int n = 1) const { if (launches) *launches += (uint64_t)n; }
 };
+
+// Launch with or without the programmatic-serialization attribute.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(const Launch& L, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = L.stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = L.pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
+#ifdef __CUDACC__
+// Both are no-ops in a kernel launched without the attribute.  pdl_wait: every kernel this one
+// depends on has finished and its stores are visible.  pdl_trigger: the next kernel of the
+// stream may be scheduled now (it still waits for this one's end in its own pdl_wait).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
 
 // One unit of work of a streaming kernel: an expert, a chunk of its rows and up to
 // tok_per_item of the tokens routed to it (pairs[pair_off .. pair_off + ntok)).

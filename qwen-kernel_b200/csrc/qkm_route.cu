@@ -42,6 +42,8 @@ __global__ void __launch_bounds__(256)
 logits_kernel(const uint8_t* __restrict__ router, const float* __restrict__ x, ACC* __restrict__ logits,
               float* __restrict__ row_norm2, uint32_t n_expert, uint32_t K, uint32_t n_tokens) {
     __shared__ ACC s_part[8][kTokPerBlock + 1];
+    pdl_trigger();
+    pdl_wait();   // the logits buffer is reused from layer to layer
     const uint32_t warp = threadIdx.x >> 5, lane = threadIdx.x & 31u;
     const uint32_t e = blockIdx.x * 2u + (warp >> 2), quarter = warp & 3u;
     const uint32_t t0 = blockIdx.y * kTokPerBlock;
@@ -124,12 +126,13 @@ static cudaError_t launch_logits64(const Launch& L, const qkm_dims& d, uint32_t 
                                    const float* x, double* logits, uint32_t n_tokens) {
     const dim3 grid((d.n_expert + 1) / 2, (n_tokens + kTokPerBlock - 1) / kTokPerBlock);
     const uint8_t* r = (const uint8_t*)router;
+    cudaError_t e;
     if (router_type == QKM_TYPE_F32)
-        logits_kernel<QKM_TYPE_F32, double><<<grid, 256, 0, L.stream>>>(r, x, logits, nullptr, d.n_expert, d.n_embd, n_tokens);
+        e = launch_kernel(L, logits_kernel<QKM_TYPE_F32, double>, grid, dim3(256), 0, r, x, logits, (float*)nullptr, d.n_expert, d.n_embd, n_tokens);
     else
-        logits_kernel<QKM_TYPE_F16, double><<<grid, 256, 0, L.stream>>>(r, x, logits, nullptr, d.n_expert, d.n_embd, n_tokens);
+        e = launch_kernel(L, logits_kernel<QKM_TYPE_F16, double>, grid, dim3(256), 0, r, x, logits, (float*)nullptr, d.n_expert, d.n_embd, n_tokens);
     L.count();
-    return cudaGetLastError();
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // ---- logits for many tokens: 64 x 64 output tiles, f32 FMA -------------------------------------
@@ -497,6 +500,8 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
     __shared__ uint32_t s_best_id[16];
     __shared__ double s_best_val[16];
     const uint32_t t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    pdl_trigger();
+    pdl_wait();   // the logits come from the kernel before
     const float* xt = x + (size_t)t * d.n_embd;
     const uint32_t id0 = tid, id1 = tid + 256u;
     const double ninf = -__longlong_as_double(0x7FF0000000000000ll);
@@ -771,11 +776,11 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         cudaError_t e = launch_logits64(L, d, router_type, router, x, l64, n_tokens);
         if (e != cudaSuccess) return e;
         if (router_type == QKM_TYPE_F32)
-            refine_select_kernel<QKM_TYPE_F32, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
+            e = launch_kernel(L, refine_select_kernel<QKM_TYPE_F32, true>, dim3(n_tokens), dim3(256), (size_t)d.n_embd * 4, (const uint8_t*)router, (const void*)l64, (const float*)nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
         else
-            refine_select_kernel<QKM_TYPE_F16, true><<<n_tokens, 256, d.n_embd * 4, L.stream>>>((const uint8_t*)router, l64, nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
+            e = launch_kernel(L, refine_select_kernel<QKM_TYPE_F16, true>, dim3(n_tokens), dim3(256), (size_t)d.n_embd * 4, (const uint8_t*)router, (const void*)l64, (const float*)nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
         L.count();
-        return cudaGetLastError();
+        return e != cudaSuccess ? e : cudaGetLastError();
     }
     if (((size_t)n_tokens * d.n_expert + d.n_expert) * sizeof(float) > scratch_bytes) return cudaErrorInvalidValue;
     float* logits = (float*)scratch;
