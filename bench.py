@@ -482,7 +482,7 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             entry_["peer_memory"] = {"us_per_layer": ms_p * 1e3, "tok_s": T / (ms_p * 1e-3),
                                      "rel_err_vs_oracle": R.max_over_ranks(err_p),
                                      "launches_per_layer": (ctx.launch_count() - n0) / ((steps + warm) * PL),
-                                     "exchange": "stores into / loads from peer-mapped buffers, two flag barriers (own kernel) per layer, one library call per layer"}
+                                     "exchange": "rows and partial rows stored into peer-mapped buffers over NVLink, two flag barriers (own kernel) per layer, one library call per layer"}
             ctx.sync()   # a barrier wait that ran out would surface here
             peer.device_barrier = False
             ms_n = timed(torch, R, stream, step_peer, steps, warm) / PL
