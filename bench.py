@@ -483,7 +483,10 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
                                      "rel_err_vs_oracle": R.max_over_ranks(err_p),
                                      "launches_per_layer": (ctx.launch_count() - n0) / ((steps + warm) * PL),
                                      "exchange": "rows and partial rows stored into peer-mapped buffers over NVLink, two flag barriers (own kernel) per layer, one library call per layer"}
-            ctx.sync()   # a barrier wait that ran out would surface here
+            try:
+                ctx.sync()   # a barrier wait that ran out surfaces here; every rank goes on with the same calls
+            except Exception as e:   # noqa: BLE001  (reported in the JSON line)
+                entry_["peer_memory"]["barrier_status"] = str(e)[:160]
             peer.device_barrier = False
             ms_n = timed(torch, R, stream, step_peer, steps, warm) / PL
             peer.device_barrier = True
