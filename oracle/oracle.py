@@ -227,3 +227,36 @@ class Reference:
         rc = self.lib.ref_dequant_row(ttype, _ptr(blocks), _ptr(out), n_elems)
         assert rc == 0, rc
         return out
+
+
+class ReferenceLayer:
+    """The reference's own CPU layer loop, `moeCpuRef` (src/main.cpp:1316-1387), compiled from
+    the span oracle/Makefile cuts out of the reference's source (oracle/_ref/libqk_ref_layer.so).
+    It accepts what `loadMoeT` accepts: F32 router and shared gate, IQ3_XXS / IQ4_XS gate/up,
+    IQ4_XS / Q6_K down, Q8_0 shared expert.  Single-threaded, one token at a time."""
+
+    PATH = os.path.join(HERE, "_ref", "libqk_ref_layer.so")
+
+    @classmethod
+    def available(cls) -> bool:
+        return os.path.exists(cls.PATH)
+
+    def __init__(self):
+        self.lib = L = C.CDLL(self.PATH)
+        L.ref_moe_layer.argtypes = [C.c_uint32] * 6 + [C.c_void_p] * 9 + [C.c_uint32] + [C.c_void_p] * 4
+
+    def moe_layer(self, layer, x):
+        """Returns dict(y f32 [T][n_embd], ids u32 [T][16], w f64 [T][16], w_shared f64 [T])."""
+        d = layer.dims
+        assert layer.router_type == 0, "the reference's loader accepts an F32 router only"
+        x = np.ascontiguousarray(x, np.float32).reshape(-1, d.n_embd)
+        T = x.shape[0]
+        y = np.zeros((T, d.n_embd), np.float32)
+        ids = np.zeros((T, 16), np.uint32)
+        w = np.zeros((T, 16), np.float64)
+        ws = np.zeros(T, np.float64)
+        t = layer.tensors()
+        rc = self.lib.ref_moe_layer(d.n_embd, d.n_ff, d.n_expert, d.n_used, layer.gateup_type, layer.down_type,
+                                    *[_ptr(a) for a in t], _ptr(x), T, _ptr(y), _ptr(ids), _ptr(w), _ptr(ws))
+        assert rc == 0, rc
+        return {"y": y, "ids": ids, "w": w, "w_shared": ws}

@@ -48,6 +48,14 @@ def ref(orc_mod):
 
 
 @pytest.fixture(scope="session")
+def ref_layer(orc_mod):
+    """The reference's own CPU layer loop (moeCpuRef), where oracle/_ref could be built."""
+    if not orc_mod.ReferenceLayer.available():
+        pytest.skip("reference source not found - restated layer loop only")
+    return orc_mod.ReferenceLayer()
+
+
+@pytest.fixture(scope="session")
 def golden():
     def load(name):
         return np.load(os.path.join(GOLDEN, name))

@@ -10,9 +10,13 @@ run where the reference tree does not exist.
   f16.npz             reference f16->f32 of all 65536 patterns, and f32->f16 of a
                       spread of floats (normals, halfway cases, under/overflow)
   tables.npz          the reference's codebooks (grid, sign bytes, iq4 values)
-  moe_small.npz       a small MoE layer through the oracle's f64 path, pinned after
-                      the oracle's dequantisers matched the reference bit-for-bit
-                      (regression pin for router/top-k/SwiGLU/down/shared logic)
+  moe_small_a.npz     a small MoE layer with an F16 router (which the reference's loader
+                      rejects) through the oracle's f64 path: a regression pin
+  moe_small_b.npz,    small MoE layers with the tensor types the reference's loader accepts
+  moe_small_c.npz     (F32 router; IQ4_XS + Q6_K and IQ3_XXS + IQ4_XS), outputs and selection
+                      produced by the REFERENCE's own moeCpuRef (src/main.cpp:1316-1387,
+                      compiled into oracle/_ref/libqk_ref_layer.so); h from the oracle after
+                      its y matched the reference's bit for bit
 """
 import os
 import sys
@@ -65,14 +69,22 @@ def main():
                         kvalues=np.array([ref.lib.ref_kvalues(i) for i in range(16)], np.int8),
                         block_bytes=np.array([ref.lib.ref_block_bytes(t) for t in (8, 14, 23, 18)], np.uint32))
 
+    assert om.ReferenceLayer.available(), "reference layer loop not built: cannot regenerate the layer fixtures"
+    ref_layer = om.ReferenceLayer()
     dims = syn.Dims(n_embd=512, n_ff=256, n_expert=16, n_used=4)
-    for tag, rt, gt, dt in (("a", syn.F16, syn.IQ3_XXS, syn.IQ4_XS), ("b", syn.F32, syn.IQ4_XS, syn.Q6_K)):
+    for tag, rt, gt, dt in (("a", syn.F16, syn.IQ3_XXS, syn.IQ4_XS), ("b", syn.F32, syn.IQ4_XS, syn.Q6_K),
+                            ("c", syn.F32, syn.IQ3_XXS, syn.IQ4_XS)):
         layer = syn.make_layer(dims, seed=1234, layer=3, router_type=rt, gateup_type=gt, down_type=dt)
         x = syn.random_x(3, dims.n_embd, seed=4321)
         out = orc.moe_layer(layer, x, want_h=True)
-        np.savez_compressed(os.path.join(HERE, f"moe_small_{tag}.npz"), x=x, y=out["y"], ids=out["sel"]["ids"],
-                            w=out["sel"]["w"], w_shared=out["sel"]["w_shared"], h=out["h"],
-                            types=np.array([rt, gt, dt]), dims=np.array([512, 256, 16, 4]))
+        y, ids, w, ws, source = out["y"], out["sel"]["ids"], out["sel"]["w"], out["sel"]["w_shared"], "oracle"
+        if rt == syn.F32:   # what the reference's loader accepts: its own loop produces the fixture
+            r = ref_layer.moe_layer(layer, x)
+            assert np.array_equal(r["y"].view(np.uint32), y.view(np.uint32)), "oracle and moeCpuRef disagree"
+            assert np.array_equal(r["ids"], ids)
+            y, ids, w, ws, source = r["y"], r["ids"], r["w"].astype(np.float32), r["w_shared"].astype(np.float32), "moeCpuRef"
+        np.savez_compressed(os.path.join(HERE, f"moe_small_{tag}.npz"), x=x, y=y, ids=ids, w=w, w_shared=ws, h=out["h"],
+                            types=np.array([rt, gt, dt]), dims=np.array([512, 256, 16, 4]), source=source)
     print("golden fixtures written to", HERE)
 
 

@@ -19,7 +19,7 @@ def check_layer(syn, got_y, got_sel, ref, n_used, tol=TOL_F32):
     assert np.array_equal(np.argmax(got_y, axis=1), np.argmax(ref["y"], axis=1))
 
 
-@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
 def test_golden_small_layer(pkg, syn, golden, tag):
     g = golden(f"moe_small_{tag}.npz")
     rt, gt, dt = (int(v) for v in g["types"])

@@ -69,7 +69,7 @@ def test_codebooks(orc, golden, syn):
     assert np.array_equal(y[3, 1].astype(np.int8), t["kvalues"])
 
 
-@pytest.mark.parametrize("tag", ["a", "b"])
+@pytest.mark.parametrize("tag", ["a", "b", "c"])
 def test_moe_layer_matches_golden(orc, syn, golden, tag):
     g = golden(f"moe_small_{tag}.npz")
     rt, gt, dt = (int(v) for v in g["types"])
@@ -82,6 +82,26 @@ def test_moe_layer_matches_golden(orc, syn, golden, tag):
     assert np.array_equal(out["y"].view(np.uint32), g["y"].view(np.uint32))
     assert np.array_equal(out["h"].view(np.uint32), g["h"].view(np.uint32))
     np.testing.assert_allclose(out["sel"]["w"], g["w"], rtol=0, atol=0)
+    np.testing.assert_allclose(out["sel"]["w_shared"], g["w_shared"], rtol=0, atol=0)
+    # fixtures b and c were produced by the reference's own moeCpuRef, a by the oracle
+    assert str(g["source"]) == ("oracle" if tag == "a" else "moeCpuRef")
+
+
+@pytest.mark.parametrize("gt,dt", [(18, 23), (18, 14), (23, 23), (23, 14)])
+def test_moe_layer_matches_reference_code(orc, ref_layer, syn, gt, dt):
+    """The restated layer loop against the reference's own moeCpuRef (src/main.cpp:1316-1387),
+    compiled from the reference's source: outputs, ids and selection weights bit for bit, for
+    every tensor-type combination its loader accepts (F32 router)."""
+    dims = syn.Dims(n_embd=512, n_ff=256, n_expert=32, n_used=8)
+    for seed in (1, 2):
+        layer = syn.make_layer(dims, seed=900 + seed, layer=seed, router_type=syn.F32, gateup_type=gt, down_type=dt)
+        x = syn.random_x(4, dims.n_embd, seed=950 + seed)
+        out = orc.moe_layer(layer, x, threads=2)
+        r = ref_layer.moe_layer(layer, x)
+        assert np.array_equal(out["sel"]["ids"], r["ids"])
+        assert np.array_equal(out["y"].view(np.uint32), r["y"].view(np.uint32))
+        assert np.array_equal(out["sel"]["w"], r["w"].astype(np.float32))
+        assert np.array_equal(out["sel"]["w_shared"], r["w_shared"].astype(np.float32))
 
 
 def test_moe_layer_properties(orc, syn):
