@@ -391,9 +391,13 @@ QKM_API int qkm_ep_peer_layer(qkm_ctx *c, uint32_t layer, const float *x, uint32
  * NO COUNTERPART IN THE REFERENCE: it exists for hosts that may not take memory from
  * the driver while they run (a server that already owns all free HBM through its own
  * pool, a latency-bound loop in which an allocation may stall the device, a plugin in
- * a process with externally accounted memory).  Same arithmetic and results as
- * qkm_moe_route_select.  Scratch is a fixed array inside the library image, one per
- * device, shared by all calls on that device:
+ * a process with externally accounted memory).  Same selection rules as
+ * qkm_moe_route_select and the same expert ids.  Up to 64 tokens the context call ranks
+ * f64 logits; this call does the same while n_tokens * n_expert * 8 bytes fit the array
+ * (then the weights are bit-identical), and otherwise ranks f32 logits and re-evaluates
+ * the boundary in f64 (e.g. 64 tokens x 512 experts: ids still equal, softmax weights
+ * equal to about 1e-6 relative).  Scratch is a fixed array inside the library image, one
+ * per device, shared by all calls on that device:
  *   - limits: n_tokens * n_expert <= QKM_STATIC_ROUTE_MAX_LOGITS and
  *     n_expert <= QKM_STATIC_ROUTE_MAX_EXPERTS; larger calls return QKM_ERR_ARG and
  *     write the reason to `err`;
@@ -402,7 +406,9 @@ QKM_API int qkm_ep_peer_layer(qkm_ctx *c, uint32_t layer, const float *x, uint32
  *     stream or order them with events;
  *   - the first call on a device looks up the array's address (and lets the runtime
  *     initialise the device if the process has not used it): make it during start-up,
- *     before any stream capture.
+ *     before any stream capture.  The address is cached for the life of the process
+ *     and does not survive a cudaDeviceReset;
+ *   - the caller's current device is left as it was.
  * `stream` is a cudaStream_t (NULL = default stream); all pointers are device memory. */
 #define QKM_STATIC_ROUTE_MAX_LOGITS  32768u
 #define QKM_STATIC_ROUTE_MAX_EXPERTS 512u

@@ -257,6 +257,15 @@ extern "C" QKM_API int qkm_gguf_moe_layer(qkm_gguf* g, uint32_t layer, qkm_dims*
         g->fail("layer %u: unexpected MoE tensor types", layer);
         return QKM_ERR_TYPE;
     }
+    // Dimensions are range-checked as 64-bit values before anything is narrowed or multiplied:
+    // a crafted header must not wrap a size computation (limits: what qkm_open accepts, with
+    // rows of at most 2^20 elements).
+    const uint64_t kMaxDim = 1u << 20;
+    if (t[2]->ne[0] < 256 || t[2]->ne[0] > kMaxDim || t[2]->ne[0] % 256 || t[2]->ne[1] < 256 || t[2]->ne[1] > kMaxDim ||
+        t[2]->ne[1] % 256 || t[2]->ne[2] < 1 || t[2]->ne[2] > 512) {
+        g->fail("layer %u: MoE tensor dims out of range (n_embd, n_ff multiples of 256 up to 2^20; at most 512 experts)", layer);
+        return QKM_ERR_BOUNDS;
+    }
     qkm_dims d;
     d.n_embd = (uint32_t)t[2]->ne[0];
     d.n_ff = (uint32_t)t[2]->ne[1];
@@ -265,14 +274,16 @@ extern "C" QKM_API int qkm_gguf_moe_layer(qkm_gguf* g, uint32_t layer, qkm_dims*
     const std::string key = (arch == g->kv_str.end() ? std::string() : arch->second) + ".expert_used_count";
     d.n_used = (uint32_t)qkm_gguf_kv_u64(g, key.c_str(), 8);
     if (d.n_used < 1 || d.n_used > 16 || d.n_used > d.n_expert) { g->fail("layer %u: expert_used_count %u unsupported", layer, d.n_used); return QKM_ERR_BOUNDS; }
-    auto shape = [&](int i, uint64_t a, uint64_t b, uint64_t c) { return t[i]->ne[0] == a && t[i]->ne[1] == b && t[i]->ne[2] == c; };
-    if (t[2]->ne[0] > 0xFFFFFFFFull || t[2]->ne[1] > 0xFFFFFFFFull || t[2]->ne[2] > 512 || d.n_embd % 256 || d.n_ff % 256 || !d.n_embd || !d.n_ff ||
-        !shape(0, d.n_embd, d.n_expert, 1) || t[1]->ne[0] != d.n_embd || !shape(3, d.n_embd, d.n_ff, d.n_expert) ||
-        !shape(4, d.n_ff, d.n_embd, d.n_expert) || !shape(5, d.n_embd, d.n_ff, 1) || !shape(6, d.n_embd, d.n_ff, 1) ||
-        !shape(7, d.n_ff, d.n_embd, 1)) {
+    auto shape = [&](int i, uint64_t a, uint64_t b, uint64_t c) {
+        return t[i]->ne[0] == a && t[i]->ne[1] == b && t[i]->ne[2] == c && t[i]->ne[3] == 1;
+    };
+    if (!shape(0, d.n_embd, d.n_expert, 1) || !shape(1, d.n_embd, 1, 1) || !shape(2, d.n_embd, d.n_ff, d.n_expert) ||
+        !shape(3, d.n_embd, d.n_ff, d.n_expert) || !shape(4, d.n_ff, d.n_embd, d.n_expert) || !shape(5, d.n_embd, d.n_ff, 1) ||
+        !shape(6, d.n_embd, d.n_ff, 1) || !shape(7, d.n_ff, d.n_embd, 1)) {
         g->fail("layer %u: inconsistent MoE tensor shapes", layer);
         return QKM_ERR_BOUNDS;
     }
+    // every extent is now <= 2^20 (ne[2] <= 512), so rb * ne[1] * ne[2] < 2^23 * 2^20 * 2^9 = 2^52
     for (int i = 0; i < 8; ++i) {
         const size_t rb = qkm_row_bytes(t[i]->type, t[i]->ne[0]);
         const uint64_t need = (uint64_t)rb * t[i]->ne[1] * t[i]->ne[2];

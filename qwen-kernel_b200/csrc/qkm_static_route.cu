@@ -22,6 +22,8 @@
 // The first call on a device looks the array's address up (and, if the process has not
 // used the device yet, lets the runtime create its context and load the module).  That is
 // set-up work: make one call per device during start-up, before any stream capture.
+// The address is cached per device for the life of the process; a cudaDeviceReset
+// invalidates it (a process that resets a device must not call this entry point again).
 #include <cuda_runtime.h>
 #include <stdint.h>
 #include <stdio.h>

@@ -106,6 +106,32 @@ def test_type_and_shape_checks(lib, syn, small_layer, tmp_path):
     lib.qkm_gguf_close(g)
 
 
+def test_oversized_dims_are_refused(lib, small_layer, tmp_path):
+    """A header whose extents would wrap the size computation (row bytes x rows x experts as a
+    64-bit product) or carry a fourth extent is refused before any size is computed."""
+    dims, layer = small_layer
+    ts = moe_layer_tensors(layer, 0)
+    huge = 0xFFFFFF00                                  # multiple of 256, fits u32: rb * ne[1] wraps u64
+    cases = {
+        "wide": (2, (huge, huge, 4)),                  # gate_exps: n_embd and n_ff near 2^32
+        "experts": (2, (256, 256, 1 << 40)),
+        "fourth_extent": (4, (256, 256, 4, 2)),        # down_exps with ne[3] = 2
+        "gis_rows": (1, (256, 3)),                     # shared gate must be one row
+    }
+    for name, (i, ne) in cases.items():
+        bad = list(ts)
+        bad[i] = (ts[i][0], ts[i][1], ne, ts[i][3])
+        if name in ("wide", "experts"):                # keep the other expert tensors consistent with the claim
+            bad[3] = (ts[3][0], ts[3][1], ne, ts[3][3])
+        write_gguf(tmp_path / f"{name}.gguf", {"general.architecture": "a", "a.expert_used_count": 2}, bad)
+        g, msg = _open(lib, tmp_path / f"{name}.gguf")
+        assert g, msg
+        rc, _, _ = _moe(lib, g, 0)
+        assert rc == -3, name
+        assert lib.qkm_gguf_last_error(g), name
+        lib.qkm_gguf_close(g)
+
+
 def test_damaged_files_are_refused(lib, small_layer, tmp_path):
     dims, layer = small_layer
     path = tmp_path / "ok.gguf"

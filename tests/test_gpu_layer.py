@@ -52,6 +52,21 @@ def test_decode_full_size_layer(pkg, orc, syn, router_type, gt, dt, T):
         assert np.array_equal(y, y2)
 
 
+@pytest.mark.parametrize("T", [16, 64])
+def test_decode_full_size_layer_batches(pkg, orc, syn, T):
+    """The bench batch (16 slots) and the largest decode-sized batch (64 tokens: the last one on
+    the streaming kernels; 65 is the first on the tensor cores, tests/test_gpu_prefill.py)."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=42)
+    x = syn.random_x(T, dims.n_embd, seed=47)
+    ref = orc.moe_layer(layer, x, threads=orc.hardware_threads())
+    with pkg.Context(dims, n_layer=1, max_tokens=T, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        y = ctx.moe_forward_host(0, x, mode=0)
+        check_layer(syn, y, ctx.last_sel(T), ref, 8)
+        assert np.array_equal(y, ctx.moe_forward_host(0, x, mode=0))
+
+
 def test_decode_stack_and_errors(pkg, orc, syn):
     dims = syn.Dims(n_embd=512, n_ff=256, n_expert=16, n_used=4)
     T, L = 6, 3

@@ -59,6 +59,25 @@ def test_gemv(ctx, orc, syn, ttype, M, K, n):
         b.free()
 
 
+@pytest.mark.parametrize("ttype,M,K", [(1, 65536, 2048), (8, 65536, 2048), (14, 65536, 2048), (23, 65536, 2048),
+                                       (18, 65536, 2048), (14, 151936, 2048), (8, 32768, 4096), (18, 40000, 4096)])
+def test_gemv_streamed_large_matrix(ctx, orc, syn, ttype, M, K):
+    """Matrices above 48 MB at n = 1 take the streamed (bulk-copy ring) kernels, for K = 2048 the
+    variant that keeps x in registers: the shapes the large-matrix bandwidth figures and the
+    151,936 x 2048 Q6_K head are quoted on.  Same tolerances as the small shapes."""
+    assert M * syn.row_bytes(ttype, K) > 48 << 20
+    W = syn.random_blocks(ttype, M, K, seed=11 * ttype + 3)
+    x = syn.random_x(1, K, seed=44)
+    d_w, d_x, d_y = ctx.to_device(W), ctx.to_device(x), ctx.alloc(M * 4)
+    ctx.gemv(ttype, d_w, d_x, d_y, M, K, 1)
+    got = d_y.download(np.float32, (1, M))
+    want = orc.gemv(ttype, W, x, M, K, threads=orc.hardware_threads())
+    assert syn.rel_err_reference(got, want) < TOL_REF_METRIC
+    assert syn.rel_err_rows(got, want) < TOL_F32
+    for b in (d_w, d_x, d_y):
+        b.free()
+
+
 def test_gemv_rejects_bad_shapes(ctx, pkg):
     d = ctx.alloc(4096)
     for ttype, K in ((8, 48), (14, 128), (18, 300), (99, 256)):
@@ -156,6 +175,44 @@ def test_route_select_ties_large_batch(pkg, orc, syn, T):
         assert list(g["ids"][5, :8]) == list(range(8)) and list(g["ids"][7, :8]) == list(range(8))
         ok = np.isfinite(w64[:, :8]).all(axis=1)
         np.testing.assert_allclose(g["w"][ok, :8], w64[ok, :8], rtol=1e-5, atol=1e-7)
+
+
+@pytest.mark.parametrize("T,router_type", [(1024, 0), (2048, 1)])
+def test_route_select_op_large_batch(pkg, orc, syn, T, router_type):
+    """The op-level call with >= 1024 tokens computes its f32 logits with the tiled GEMM kernel
+    and re-evaluates the boundary in f64: ids equal the f64 router's for EVERY token, including
+    tie / NaN / Inf / all-zero rows placed beyond row 1000."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=19, router_type=router_type)
+    if router_type == syn.F32:
+        r = layer.router.view(np.float32).reshape(256, 2048).copy()
+        r[200] = r[17]; r[90] = r[17]; r[3] = 0.0; r[4] = 0.0
+        layer.router = r.reshape(-1).view(np.uint8)
+        tie_row = r[17] * 50.0
+    else:
+        r = layer.router.view(np.float16).reshape(256, 2048).copy()
+        r[200] = r[17]; r[90] = r[17]; r[3] = 0.0; r[4] = 0.0
+        layer.router = r.reshape(-1).view(np.uint8)
+        tie_row = r[17].astype(np.float32) * 50.0
+    x = syn.random_x(T, 2048, seed=20)
+    x[1001] = tie_row; x[T - 1] = tie_row
+    x[1005, 100] = np.nan
+    x[1006, 7] = np.inf
+    x[1007] = 0.0
+    want, w64 = orc.route(layer, x, threads=orc.hardware_threads())
+    with pkg.Context(dims, n_layer=1, max_tokens=T, device=0) as c:
+        d_r, d_g = c.to_device(layer.router), c.to_device(layer.gate_inp_shexp)
+        d_x, d_sel = c.to_device(x), c.alloc(T * 160)
+        c.moe_route_select(router_type, d_r, d_g, d_x, d_sel, T)
+        got = d_sel.download(pkg_sel(c), T)
+        for b in (d_r, d_g, d_x, d_sel):
+            b.free()
+    assert np.array_equal(got["ids"], want["ids"])
+    assert list(got["ids"][1001, :3]) == [17, 90, 200] and list(got["ids"][T - 1, :3]) == [17, 90, 200]
+    assert list(got["ids"][1005, :8]) == list(range(8)) and list(got["ids"][1007, :8]) == list(range(8))
+    ok = np.isfinite(w64[:, :8]).all(axis=1)
+    np.testing.assert_allclose(got["w"][ok, :8], w64[ok, :8], rtol=1e-5, atol=1e-7)
+    np.testing.assert_allclose(got["w_shared"][ok], w64[ok, 16], rtol=1e-6)
 
 
 def test_logits_and_select_from_f32(ctx, orc, syn):
