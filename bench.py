@@ -43,7 +43,8 @@ SEED_W, SEED_X = 42, 43
 
 
 def measured_peaks():
-    """HBM GB/s and bf16 TF/s measured on this pool (driver-written), else the stated fallback."""
+    """HBM GB/s and bf16 TF/s from MEASURED_PEAKS.json (a copy benchmark and a cuBLAS GEMM run on the
+    target GPUs), else the stated fallback."""
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
@@ -155,7 +156,11 @@ def cpu_moe_sample(syn, orc_mod, dims, n_slots, layers_sample, threads, router_t
 
 
 def run_reference_arm(args, syn):
-    """The reference's CPU implementation of the path, timed on the host cores."""
+    """The reference's CPU implementation of the path (quants.h-style row dequantisation + scalar
+    f32 loop, restated in oracle/; its own moeCpuRef is single-threaded and f64), timed on the
+    host cores with all the threads the box has.  A step is the same workload as ours: n_slots
+    rows through `layers` layers.  All layers are timed when the whole run fits a few minutes
+    (N = 1); otherwise a step times a bounded sample of the layers and scales it, and says so."""
     rank, _, world = dist_env()
     if rank != 0:
         return
@@ -164,25 +169,36 @@ def run_reference_arm(args, syn):
     dims = syn.Dims()
     threads = orc_mod.Oracle().hardware_threads() or 1
     n_layers, n_slots = args.layers, args.slots * max(1, args.gpus)
-    sample_layers = 1
-    per_layer = []
-    for _ in range(args.warmup):
-        cpu_moe_sample(syn, orc_mod, dims, n_slots, sample_layers, threads, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)
-    for _ in range(args.steps):
-        per_layer.append(cpu_moe_sample(syn, orc_mod, dims, n_slots, sample_layers, threads, syn.F16, syn.IQ3_XXS, syn.IQ4_XS))
-    sec_per_step = float(np.mean(per_layer)) * n_layers
+    budget_s = 240.0
+    t_layer = cpu_moe_sample(syn, orc_mod, dims, n_slots, 1, threads, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)   # probe, untimed
+    total_steps = args.steps + args.warmup
+    sample_layers = n_layers if t_layer * n_layers * total_steps <= budget_s else max(1, int(budget_s / (t_layer * total_steps)))
+    sample_layers = min(sample_layers, n_layers)
+    per_step = []
+    for i in range(total_steps):
+        t = cpu_moe_sample(syn, orc_mod, dims, n_slots, sample_layers, threads, syn.F16, syn.IQ3_XXS, syn.IQ4_XS) * sample_layers
+        if i >= args.warmup:
+            per_step.append(t)
+    sec_per_step = float(np.mean(per_step)) * n_layers / sample_layers
     value = n_slots / sec_per_step
+    sample = (f"all {n_layers} layers x {n_slots} rows per step" if sample_layers == n_layers else
+              f"{sample_layers} of {n_layers} layers x {n_slots} rows per step, scaled by layers")
+    cfg = decode_config(args, n_slots)
+    cfg["parallelism"] = parallelism_label(max(1, args.gpus), args.slots)
     line = {
         "impl": "reference", "metric": "moe_decode_tok_s", "value": value, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec_per_step * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": decode_config(args, n_slots),
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
-                         "sample": f"{sample_layers} of {n_layers} layers x {n_slots} rows per step, scaled by layers"},
+        "config": cfg,
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "measured_all_layers": sample_layers == n_layers,
     }
     print(json.dumps(line), flush=True)
+
+
+def parallelism_label(world, slots):
+    return "1 GPU" if world == 1 else f"{world} replicas of the stack, {slots} slots each, no collective"
 
 
 def decode_config(args, n_slots):
@@ -265,10 +281,13 @@ def run_ours(args, pkg, syn):
     ctx.set_stream(stream.cuda_stream)
     layers_keep = []
     x_all = np.empty((L, S, dims.n_embd), np.float32)
+    ref_all = np.empty((L, S, dims.n_embd), np.float32)   # the oracle's output of every layer (checked below)
+    nthr = orc.hardware_threads() or 1
     for l in range(L):
         layer = syn.make_layer(dims, SEED_W, l, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)
         ctx.upload_layer(l, layer)
         x_all[l] = syn.random_x(S, dims.n_embd, SEED_X + 1000 * rank + l)
+        ref_all[l] = orc.moe_layer(layer, x_all[l], threads=nthr)["y"]
         if l < args.sub_layers:
             layers_keep.append(layer)
     with torch.cuda.stream(stream):
@@ -280,11 +299,13 @@ def run_ours(args, pkg, syn):
     def step():
         ctx.moe_decode_stack(0, L, x_dev, S, y_dev)
 
-    # correctness of what is being timed: layer 0 against the oracle
+    # correctness of what is being timed: every layer of the stack against the oracle
     step(); R.barrier()
-    ref0 = orc.moe_layer(layers_keep[0], x_all[0], threads=orc.hardware_threads())
-    err0 = syn.rel_err_rows(y_dev[0].cpu().numpy(), ref0["y"])
-    assert err0 < 1e-5, f"layer 0 output error {err0}"
+    y_host = y_dev.cpu().numpy()
+    errs = [syn.rel_err_rows(y_host[l], ref_all[l]) for l in range(L)]
+    err0 = float(max(errs))
+    assert err0 < 1e-5, f"layer {int(np.argmax(errs))} output error {err0}"
+    del ref_all
 
     # distinct experts per layer (for the algorithmic byte count), from the device's own routing
     distinct = []
@@ -329,9 +350,9 @@ def run_ours(args, pkg, syn):
         "us_per_layer": ms * 1e3 / L,
         "e2e": {"value": world * S / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": int(x_pin.numel() * 4) * world,
                 "d2h_bytes_per_step": int(y_pin.numel() * 4) * world, "ms_per_step": e2e_s * 1e3},
-        "gpu_launches": int(launches) * world, "clocks": clocks, "parity": {"layer0_rel_err": err0},
+        "gpu_launches": int(launches) * world, "clocks": clocks, "parity": {"max_rel_err_over_all_layers": err0, "layers_checked": L},
     }
-    line["config"]["parallelism"] = "1 GPU" if world == 1 else f"{world} replicas of the stack, {S} slots each, no collective"
+    line["config"]["parallelism"] = parallelism_label(world, S)
 
     # per-kernel timing of the dominant kernels over the same inputs (CUDA events, this stream)
     if rank == 0:
@@ -340,7 +361,7 @@ def run_ours(args, pkg, syn):
         line["roofline"] = {
             "bound": "hbm", "kernel": dom["name"], "achieved": dom["gbs"], "peak": peaks["hbm_gbs"], "unit": "GB/s",
             "frac": dom["gbs"] / peaks["hbm_gbs"], "peak_source": peaks["source"] + " copy bandwidth",
-            "frac_of_nominal_8TBs": dom["gbs"] / 8000.0, "traffic": NCU_TRAFFIC.get(dom["name"]),
+            "frac_of_nominal_8TBs": dom["gbs"] / 8000.0, "traffic": ncu_traffic(dom["name"]),
             "bytes_per_launch": dom["bytes_per_launch"], "ms_per_launch": dom["ms_per_layer"]}
         line["kernels"] = kern
         threads = orc.hardware_threads() or 1
@@ -348,6 +369,11 @@ def run_ours(args, pkg, syn):
             cpu_sec_layer = cpu_moe_sample(syn, orc_mod, dims, S, 2, threads, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)
             line["cpu_baseline"] = {"value": S / (cpu_sec_layer * L), "unit": "tok/s", "cores": threads, "kind": "port",
                                     "sample": f"2 of {L} layers x {S} rows on the host cores, scaled by layers"}
+            # the reference's own CPU loop is single-threaded: the same path on one thread (4 rows x 1 layer, scaled)
+            one = cpu_moe_sample(syn, orc_mod, dims, 4, 1, 1, syn.F16, syn.IQ3_XXS, syn.IQ4_XS)
+            line["cpu_baseline"]["single_thread"] = {"value": 4 / (one * L), "unit": "tok/s", "cores": 1,
+                                                     "sample": f"1 of {L} layers x 4 rows on one thread, scaled by layers"}
+            line["decode_batch1"] = run_batch1(ctx, syn, torch, R, stream, L, dims, x_all, peaks, orc, layers_keep)
     R.barrier()
     ctx.close()
     del x_dev, y_dev
@@ -388,12 +414,16 @@ def run_ours(args, pkg, syn):
     R.close()
 
 
-# DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of
-# the decode stages on this workload; the captures are summarised under profiles/.
-NCU_TRAFFIC = {
-    "moe.gu": 84_100_000,   # gateup_stream_kernel<IQ3_XXS>: 82.14 MB read + 1.96 MB written at 102.3 experts' worth
-    "moe.dn": 58_230_000,   # down_tok_iq4_kernel: 57.37 MB read + 0.86 MB written
-}
+def ncu_traffic(stage: str):
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of a decode stage's
+    kernel, from profiles/ncu_traffic.json - written when the ncu capture summarised under
+    profiles/ was taken, with the commit it was taken at.  None when the file has no entry."""
+    p = os.path.join(ROOT, "profiles", "ncu_traffic.json")
+    try:
+        return json.load(open(p)).get(stage, {}).get("dram_bytes_per_launch")
+    except Exception:
+        return None
+
 
 PREFILL_CHUNKS = (128, 256, 512, 2048, 4096)
 TENSOR_FLOPS_PER_TOKEN = 56_623_104   # routed 8 x (gate, up, down) + shared expert, 2 x MACs
@@ -452,7 +482,7 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
                     ctx.moe_prefill(l, x[l], n, y[l])
 
         step(); R.barrier()
-        k = min(n, 8)
+        k = min(n, 512) if rank == 0 else min(n, 8)   # rank 0 checks all of its rows (up to 512), the others a few
         want = orc.moe_layer(layers[0], x_np[0, :k], threads=orc.hardware_threads())["y"]
         err = syn.rel_err_rows(y[0, :k].cpu().numpy(), want)
         assert err < 2e-2, f"prefill T={T}: error {err}"
@@ -461,7 +491,8 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
         entry_ = {"us_per_layer": ms * 1e3, "tok_s": T / (ms * 1e-3), "rel_err_vs_oracle": R.max_over_ranks(err),
                   "tensor_tflops": T * TENSOR_FLOPS_PER_TOKEN / (ms * 1e-3) / 1e12,
                   "launches_per_layer": (ctx.launch_count() - n0) / ((steps + warm) * PL)}
-        entry_["frac_of_measured_bf16_burst"] = entry_["tensor_tflops"] / peaks["bf16_tflops"]
+        entry_["tensor_tflops_per_gpu"] = entry_["tensor_tflops"] / world
+        entry_["frac_of_measured_bf16_burst"] = entry_["tensor_tflops_per_gpu"] / peaks["bf16_tflops"]
         if ep:
             send, recv = ep.last_counts
             off = sum(send) - send[rank]
@@ -511,7 +542,8 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             a2a = {k: entry_[k] for k in ("us_per_layer", "tok_s", "rel_err_vs_oracle", "launches_per_layer", "exchange")}
             entry_.update(pm)
             entry_["tensor_tflops"] = T * TENSOR_FLOPS_PER_TOKEN / (pm["us_per_layer"] * 1e-6) / 1e12
-            entry_["frac_of_measured_bf16_burst"] = entry_["tensor_tflops"] / peaks["bf16_tflops"]
+            entry_["tensor_tflops_per_gpu"] = entry_["tensor_tflops"] / world
+            entry_["frac_of_measured_bf16_burst"] = entry_["tensor_tflops_per_gpu"] / peaks["bf16_tflops"]
             entry_["nccl_all_to_all"] = a2a
         out["chunks"][str(T)] = entry_
     if world == 1:
@@ -576,10 +608,9 @@ def run_gemv_sweep(args, pkg, syn, torch, R: Ranks, orc, peaks):
                 ctx.gemv(t, base + c * stride, x, y, M, K, 1)
 
         step(); R.barrier()
-        if M <= 8192:
-            want = orc.gemv(t, W, xv.reshape(-1), M, K, threads=orc.hardware_threads())
-            err = syn.rel_err_rows(y.cpu().numpy().reshape(1, -1), want.reshape(1, -1))
-            assert err < 1e-5, f"gemv {names[t]} {M}x{K}: error {err}"
+        want = orc.gemv(t, W, xv.reshape(-1), M, K, threads=orc.hardware_threads())
+        err = syn.rel_err_rows(y.cpu().numpy().reshape(1, -1), want.reshape(1, -1))
+        assert err < 1e-5, f"gemv {names[t]} {M}x{K}: error {err}"
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             step()
@@ -609,18 +640,38 @@ def run_gemv_sweep(args, pkg, syn, torch, R: Ranks, orc, peaks):
     return out
 
 
+def run_batch1(ctx, syn, torch, R, stream, L, dims, x_all, peaks, orc, layers_keep):
+    """BASELINE configuration 0: one MoE layer, decode batch 1 (the reference's `qk moe <layer>`
+    harness, src/main.cpp:1221-1243: us per layer and GB/s over the weight bytes one token
+    touches).  The call rotates over all L layers of the stack (one token through each, replayed
+    as a graph), so every layer's weights come from HBM, not from L2: a cold figure, as stated."""
+    dev = R.dev
+    with torch.cuda.stream(stream):
+        x1 = torch.from_numpy(np.ascontiguousarray(x_all[:, :1])).to(dev)
+        y1 = torch.empty_like(x1)
+    ctx.moe_decode_stack(0, L, x1, 1, y1); R.barrier()
+    ref = orc.moe_layer(layers_keep[0], x_all[0, :1])
+    err = syn.rel_err_rows(y1[0].cpu().numpy(), ref["y"])
+    assert err < 1e-5, f"batch-1 layer output error {err}"
+    ms = timed(torch, R, stream, lambda: ctx.moe_decode_stack(0, L, x1, 1, y1), 20, 3) / L
+    nbytes = syn.layer_touched_bytes(dims, syn.F16, syn.IQ3_XXS, syn.IQ4_XS, dims.n_used)
+    return {"workload": f"one layer, one token; rotating over {L} layers so weights stream from HBM (cold)",
+            "us_per_layer": ms * 1e3, "active_bytes_per_layer": nbytes, "gbs": nbytes / (ms * 1e-3) / 1e9,
+            "frac_of_measured_copy": nbytes / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "frac_of_nominal_8TBs": nbytes / (ms * 1e-3) / 8e12,
+            "rel_err_vs_oracle": err}
+
+
 def time_kernels(ctx, pkg, syn, torch, dev, stream, L, S, x_dev, distinct, dims, reps=5):
     """Average duration of every stage of the fused decode sequence (one launch per layer
     per pass), from CUDA events recorded on the launching stream between the stages
     (qkm_profile_*), with the algorithmic weight bytes each stage touches."""
     rb = syn.row_bytes
     mean_u = float(np.mean(distinct))
+    # the shared expert's matrices ride inside the routed kernels of the fused sequence
     stage_bytes = {
         "moe.route": dims.n_expert * rb(syn.F16, dims.n_embd) + dims.n_embd * 4,
-        "moe.shared_gu": 2 * dims.n_ff * rb(syn.Q8_0, dims.n_embd),
-        "moe.gu": mean_u * 2 * dims.n_ff * rb(syn.IQ3_XXS, dims.n_embd),
-        "moe.dn": mean_u * dims.n_embd * rb(syn.IQ4_XS, dims.n_ff),
-        "moe.shared_dn": dims.n_embd * rb(syn.Q8_0, dims.n_ff),
+        "moe.gu": mean_u * 2 * dims.n_ff * rb(syn.IQ3_XXS, dims.n_embd) + 2 * dims.n_ff * rb(syn.Q8_0, dims.n_embd),
+        "moe.dn": mean_u * dims.n_embd * rb(syn.IQ4_XS, dims.n_ff) + dims.n_embd * rb(syn.Q8_0, dims.n_ff),
     }
     y = torch.empty(S, dims.n_embd, device=dev)
     ctx.profile_enable(True)

@@ -64,6 +64,11 @@ struct qkm_ctx {
     uint32_t* status = nullptr;       // kernel status word (device)
     uint32_t shared_plan_n = 0;        // token count the shared expert's decode work lists were last cut for (0: stale)
     uint32_t* route_counter = nullptr; // ticket counter of the selection kernel's grouping tail (device, stays zero)
+    // fused decode sequence (router + grouping + planes -> gate/up -> down, three launches)
+    bool dec_ok = false;               // dims fit the fused decode kernels
+    int8_t* planes8 = nullptr;         // [max_tokens][n_embd/256][8][256]
+    uint8_t* lut_gu = nullptr;         // table images the decode kernels copy to shared memory
+    uint8_t* lut_dn = nullptr;
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
     // prefill (tcgen05) scratch, allocated on first use
@@ -268,11 +273,33 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
             }
         }
         cudaMemset(c->arrivals, 0, T * (d.n_embd / down_stream_unit_rows()) * sizeof(uint32_t));
+        c->dec_ok = decode_gateup_ok(d) && d.n_embd <= 4096;
+        if (c->dec_ok) {
+            struct { void** p; size_t bytes; } dec[] = {
+                {(void**)&c->planes8, T * 8 * d.n_embd},
+                {(void**)&c->lut_gu, decode_gateup_lut_bytes()},
+                {(void**)&c->lut_dn, decode_down_lut_bytes()},
+            };
+            for (auto& a : dec) {
+                if ((e = cudaMalloc(a.p, a.bytes)) != cudaSuccess) {
+                    bail("qkm_open: cudaMalloc of decode scratch", cudaGetErrorString(e));
+                    qkm_close(c);
+                    return nullptr;
+                }
+            }
+            const Launch L0{nullptr, nullptr};
+            if ((e = launch_decode_gateup_luts(L0, c->lut_gu)) != cudaSuccess || (e = launch_decode_down_lut(L0, c->lut_dn)) != cudaSuccess ||
+                (e = cudaDeviceSynchronize()) != cudaSuccess) {
+                bail("qkm_open: decode tables", cudaGetErrorString(e));
+                qkm_close(c);
+                return nullptr;
+            }
+        }
     }
     if ((e = cudaMalloc((void**)&c->status, sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMemset(c->status, 0, sizeof(uint32_t))) != cudaSuccess ||
-        (e = cudaMalloc((void**)&c->route_counter, sizeof(uint32_t))) != cudaSuccess ||
-        (e = cudaMemset(c->route_counter, 0, sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMalloc((void**)&c->route_counter, 16 * sizeof(uint32_t))) != cudaSuccess ||
+        (e = cudaMemset(c->route_counter, 0, 16 * sizeof(uint32_t))) != cudaSuccess ||
         (e = cudaMallocHost((void**)&c->status_host, sizeof(uint32_t))) != cudaSuccess) {
         bail("qkm_open: status word", cudaGetErrorString(e));
         qkm_close(c);
@@ -303,6 +330,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     void* scratch[] = {c->argmax_scratch, c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
+                       c->planes8, c->lut_gu, c->lut_dn,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
@@ -584,6 +612,39 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         return QKM_OK;
     }
     const uint32_t nb = (uint32_t)c->n_sms;
+    // Three launches for the whole layer: (1) router logits, selection and digit planes; (2) pair
+    // grouping (in every block's shared memory), then gate/up + SwiGLU of the routed experts and of
+    // the shared expert; (3) down
+    // projections of both and the weighted sum.  The shared expert rides inside (2) and (3): no
+    // side stream, and nothing runs beside the two persistent kernels that they would have to
+    // share the SMs with.
+    if (c->dec_ok && w.gateup_type == QKM_TYPE_IQ3_XXS && route_decode_ok(d, n, c->route_scratch_bytes) &&
+        (!ld.stream_ok || decode_down_ok(d))) {
+        RouteDecodeArgs ra{};
+        ra.router = (const uint8_t*)w.router; ra.gis = w.gate_inp_shexp; ra.x = x; ra.sel = c->sel;
+        ra.logits = (double*)c->route_scratch; ra.counter = c->route_counter; ra.planes = c->planes8; ra.xscale = c->xscale; ra.n_tokens = n; ra.d = d;
+        QKM_LAUNCH(c, launch_route_decode(c->Lchain(), w.router_type, ra));
+        c->prof_mark("moe.route");
+        GateupDecodeArgs ga{};
+        ga.gate_tiles = (const uint8_t*)ld.tiles[2]; ga.up_tiles = (const uint8_t*)ld.tiles[3];
+        ga.sh_gate_tiles = (const uint8_t*)ld.tiles[5]; ga.sh_up_tiles = (const uint8_t*)ld.tiles[6];
+        ga.luts = c->lut_gu; ga.planes = c->planes8; ga.xscale = c->xscale; ga.sel = c->sel;
+        ga.n_tokens = n; ga.expert_first = c->efirst; ga.expert_count = c->ecount; ga.with_shared = 1;
+        ga.h = c->h; ga.hpieces = c->hpieces; ga.status = c->status; ga.d = d;
+        QKM_LAUNCH(c, launch_decode_gateup(c->Lchain(), ga, nb));
+        c->prof_mark("moe.gu");
+        if (ld.stream_ok) {
+            DownDecodeArgs da{};
+            da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7]; da.lut = c->lut_dn;
+            da.hpieces = c->hpieces; da.h = c->h; da.sel = c->sel; da.y = y; da.n_tokens = n; da.status = c->status; da.d = d;
+            QKM_LAUNCH(c, launch_decode_down(c->Lchain(), da, nb));
+        } else {   // Q6_K down: f32 kernel over h, routed slots and the shared expert in one pass
+            QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));
+        }
+        c->prof_mark("moe.dn");
+        c->shared_plan_n = 0;   // pairs / work lists of the older sequence are overwritten
+        return QKM_OK;
+    }
     // Shared expert: depends on x only (as digit planes), so the whole of it - planes, gate/up,
     // down - runs on the side stream from the start of the layer, beside the router.  The main
     // stream needs the planes before the routed gate/up (ev_planes) and y2 before the routed

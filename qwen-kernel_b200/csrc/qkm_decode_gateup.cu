@@ -72,8 +72,8 @@ __device__ __forceinline__ void gu_tile(uint32_t tb, uint32_t lane, uint32_t g, 
     if (FMT == QKM_TYPE_IQ3_XXS) {
         const uint4 ia = lds128(tb + lane * 16);          // row g: 8 index pairs
         const uint4 ib_ = lds128(tb + 512 + lane * 16);   // row g+8
-        const uint4 xa0 = lds128(tb + 1024 + 32 * g), xa1 = lds128(tb + 1024 + 32 * g + 16);
-        const uint4 xb0 = lds128(tb + 1024 + 32 * (g + 8)), xb1 = lds128(tb + 1024 + 32 * (g + 8) + 16);
+        const uint4 xa0 = lds128(tb + 1024 + 16 * g), xa1 = lds128(tb + 1280 + 16 * g);
+        const uint4 xb0 = lds128(tb + 1152 + 16 * g), xb1 = lds128(tb + 1408 + 16 * g);
         const uint32_t idx_a[4] = {ia.x, ia.y, ia.z, ia.w}, idx_b[4] = {ib_.x, ib_.y, ib_.z, ib_.w};
         const uint32_t aux_a[8] = {xa0.x, xa0.y, xa0.z, xa0.w, xa1.x, xa1.y, xa1.z, xa1.w};
         const uint32_t aux_b[8] = {xb0.x, xb0.y, xb0.z, xb0.w, xb1.x, xb1.y, xb1.z, xb1.w};

@@ -58,6 +58,67 @@ struct MmaItem {
     uint32_t n;
 };
 
+// ---- fused decode sequence (qkm_dec_route.cu, qkm_dec_gateup.cu, qkm_dec_down.cu) ---------------
+// One expert (or the shared expert) with up to two of the tokens routed to it:
+// pairs[pair_off .. pair_off + ntok).  The gate/up kernel walks all n_ff rows of a group.
+struct DecodeGroup {
+    uint16_t expert;   // resident-expert index (kind 0)
+    uint8_t ntok;      // 1 or 2
+    uint8_t kind;      // 0 routed expert, 1 shared expert
+    uint32_t pair_off;
+};
+struct RouteDecodeArgs {
+    const uint8_t* router;     // [n_expert][n_embd] F32 or F16
+    const float* gis;          // [n_embd]
+    const float* x;            // [n_tokens][n_embd]
+    qkm_sel* sel;              // out [n_tokens]
+    double* logits;            // scratch [n_tokens][n_expert]
+    uint32_t* counter;         // ceil(n_tokens / 8) zero words; left at zero
+    int8_t* planes;            // out [n_tokens][n_embd/256][8][256]: digit planes 0..3 and their negatives 4..7
+    float* xscale;             // out [n_tokens] 2^-p
+    uint32_t n_tokens;
+    qkm_dims d;
+};
+bool route_decode_ok(const qkm_dims& d, uint32_t n_tokens, size_t scratch_bytes);
+cudaError_t launch_route_decode(const Launch& L, uint32_t router_type, const RouteDecodeArgs& a);
+// routed (IQ3_XXS) and shared (Q8_0) gate/up + SwiGLU over the groups; h as f32 and as bf16 pieces
+struct GateupDecodeArgs {
+    const uint8_t* gate_tiles;      // routed experts, IQ3_XXS tiles
+    const uint8_t* up_tiles;
+    const uint8_t* sh_gate_tiles;   // shared expert, Q8_0 tiles (may be NULL when no group has kind 1)
+    const uint8_t* sh_up_tiles;
+    const uint8_t* luts;            // decode_gateup_lut_bytes() bytes written by launch_decode_gateup_luts
+    const int8_t* planes;
+    const float* xscale;
+    const qkm_sel* sel;             // the selection (its pairs are grouped by expert in every block at its start)
+    uint32_t n_tokens, expert_first, expert_count, with_shared;
+    float* h;                       // [T][n_used+1][n_ff]
+    void* hpieces;                  // bf16 [T][n_used+1][3][n_ff] in the down kernel's operand order
+    uint32_t* status;
+    qkm_dims d;
+};
+size_t decode_gateup_lut_bytes();
+cudaError_t launch_decode_gateup_luts(const Launch& L, uint8_t* luts);
+bool decode_gateup_ok(const qkm_dims& d);
+cudaError_t launch_decode_gateup(const Launch& L, const GateupDecodeArgs& a, uint32_t n_blocks);
+// routed (IQ4_XS) down + shared (Q8_0) down + weighted sum: y[t] = sum_s w_s D[ids_s] h[t][s] + w_shared DS h[t][n_used]
+struct DownDecodeArgs {
+    const uint8_t* tiles;           // routed experts, IQ4_XS tiles
+    const uint8_t* sh_tiles;        // shared expert, Q8_0 tiles (NULL: no shared term)
+    const uint8_t* lut;             // decode_down_lut_bytes() bytes written by launch_decode_down_lut
+    const void* hpieces;
+    const float* h;                 // [T][n_used+1][n_ff] f32 (the shared expert's rows are encoded as digit planes in the kernel)
+    const qkm_sel* sel;
+    float* y;
+    uint32_t n_tokens;
+    uint32_t* status;
+    qkm_dims d;
+};
+size_t decode_down_lut_bytes();
+cudaError_t launch_decode_down_lut(const Launch& L, uint8_t* lut);
+bool decode_down_ok(const qkm_dims& d);
+cudaError_t launch_decode_down(const Launch& L, const DownDecodeArgs& a, uint32_t n_blocks);
+
 // ---- qkm_prefill.cu : tcgen05 expert GEMMs for batched prefill
 uint32_t prefill_pairs_per_block();
 // x rows as f16 scaled per row by a power of two (inv_scale[row] undoes it)

@@ -167,7 +167,7 @@ __device__ __forceinline__ Iq3Idx load_iq3_idx(const uint8_t* __restrict__ tile,
 }
 __device__ __forceinline__ Iq3Raw load_iq3(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q, const Iq3Idx& ix) {
     Iq3Raw r;
-    r.aux2 = *reinterpret_cast<const uint2*>(tile + 1024 + 32 * r16 + 8 * q);
+    r.aux2 = *reinterpret_cast<const uint2*>(tile + 1024 + 256 * (q >> 1) + 16 * r16 + 8 * (q & 1u));
     r.dbits = *reinterpret_cast<const uint16_t*>(tile + 1536 + 2 * r16);
 #pragma unroll
     for (int t = 0; t < 4; ++t) {

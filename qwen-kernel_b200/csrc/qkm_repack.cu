@@ -31,9 +31,10 @@ __global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restri
             const uint32_t g = lane >> 2, t = lane & 3u, ib = b >> 1;
             row_in_tile = g + 8 * h;
             off = 2 + 8 * ib + 2 * t + (b & 1u);
-        } else if (o < 1536) {
-            row_in_tile = (o - 1024) >> 5;
-            off = 2 + 64 + ((o - 1024) & 31u);
+        } else if (o < 1536) {   // aux words: [half of the sub-blocks][row][16 B]
+            const uint32_t q = o - 1024;
+            row_in_tile = (q >> 4) & 15u;
+            off = 2 + 64 + 16 * (q >> 8) + (q & 15u);
         } else {
             row_in_tile = (o - 1536) >> 1;
             off = (o - 1536) & 1u;

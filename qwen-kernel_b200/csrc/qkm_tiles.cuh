@@ -17,7 +17,10 @@
 //     [   0,1024)  index pairs: half h (row g + 8h), lane -> 16 B = for each of the 8
 //                  sub-blocks the two grid indices of 8-element group t
 //                  (raw qs[8*ib + 2*t], qs[8*ib + 2*t + 1]); address h*512 + lane*16
-//     [1024,1536)  aux words, row r at 1024 + 32*r, unchanged (4 x 7 sign bits + 4 scale bits)
+//     [1024,1536)  aux words (4 x 7 sign bits + 4 scale bits each), unchanged, as two halves:
+//                  words 4*hf .. 4*hf+3 (sub-blocks 4*hf .. 4*hf+3) of row r at
+//                  1024 + 256*hf + 16*r, so the 16-byte loads of eight rows g (or g+8) hit
+//                  eight consecutive 16-byte slots
 //     [1536,1568)  d[16] f16
 //   IQ4_XS (block: d f16 | scales_h u16 | scales_l[4] | qs[128], src/quants.h:107-113)
 //     [   0, 128)  headers: for g: 8 B of row g then 8 B of row g+8, each the raw first

@@ -67,6 +67,87 @@ def test_decode_full_size_layer_batches(pkg, orc, syn, T):
         assert np.array_equal(y, ctx.moe_forward_host(0, x, mode=0))
 
 
+@pytest.mark.parametrize("router_type", [0, 1])
+def test_decode_router_ties_and_nonfinite(pkg, orc, syn, router_type):
+    """The fused decode router (logits + ranking + grouping in one launch) on the hazards the
+    reference's selection rules cover: identical router rows (lowest id wins), all-zero rows,
+    NaN / Inf activations (logits at the floor: ids 0..7), an all-zero token.  Ids must equal the
+    f64 router's; finite tokens' outputs stay within the decode tolerance, and a second call is
+    bit-identical (the last-arriving block's ranking is deterministic)."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=9, router_type=router_type)
+    if router_type == syn.F32:
+        r = layer.router.view(np.float32).reshape(256, 2048).copy()
+    else:
+        r = layer.router.view(np.float16).reshape(256, 2048).copy()
+    r[200] = r[17]; r[90] = r[17]            # three identical rows: exact ties
+    r[3] = 0; r[4] = 0                       # two all-zero rows: logits exactly 0
+    layer.router = r.reshape(-1).view(np.uint8)
+    T = 12
+    x = syn.random_x(T, 2048, seed=10)
+    x[2] = r[17].astype(np.float32) * 50.0    # make the tied experts win for token 2
+    x[5, 100] = np.nan                        # every logit NaN
+    x[6, 7] = np.inf                          # logits +-inf / NaN
+    x[7] = 0.0                                # every logit 0: ids 0..7
+    x[T - 1] = x[2]
+    want, w64 = orc.route(layer, x)
+    finite = np.array([t for t in range(T) if t not in (5, 6)])
+    ref = orc.moe_layer(layer, x[finite], threads=orc.hardware_threads())
+    with pkg.Context(dims, n_layer=1, max_tokens=T, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        y = ctx.moe_forward_host(0, x, mode=0)
+        sel = ctx.last_sel(T)
+        y2 = ctx.moe_forward_host(0, x, mode=0)
+        sel2 = ctx.last_sel(T)
+    assert np.array_equal(sel["ids"][:, :8], want["ids"][:, :8])
+    assert list(sel["ids"][2, :3]) == [17, 90, 200] and list(sel["ids"][T - 1, :3]) == [17, 90, 200]
+    assert list(sel["ids"][5, :8]) == list(range(8)) and list(sel["ids"][7, :8]) == list(range(8))
+    ok = np.isfinite(w64[:, :8]).all(axis=1)
+    np.testing.assert_allclose(sel["w"][ok, :8], w64[ok, :8], rtol=1e-5, atol=1e-7)
+    assert syn.rel_err_rows(y[finite], ref["y"]) < TOL_F32
+    assert np.array_equal(sel["ids"], sel2["ids"]) and np.array_equal(y[finite], y2[finite])
+
+
+@pytest.mark.parametrize("T", [3, 33])
+def test_decode_512_experts(pkg, orc, syn, T):
+    """More than 256 experts: the ranking keeps two sorted key lists per lane (the 512-expert
+    variant of the model family); narrower rows (n_embd 1024: four column blocks per team)."""
+    dims = syn.Dims(n_embd=1024, n_ff=512, n_expert=512, n_used=8)
+    layer = syn.make_layer(dims, seed=14, router_type=syn.F32)
+    x = syn.random_x(T, dims.n_embd, seed=15)
+    ref = orc.moe_layer(layer, x, threads=orc.hardware_threads())
+    with pkg.Context(dims, n_layer=1, max_tokens=T, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        y = ctx.moe_forward_host(0, x, mode=0)
+        check_layer(syn, y, ctx.last_sel(T), ref, 8)
+        assert np.array_equal(y, ctx.moe_forward_host(0, x, mode=0))
+
+
+def test_decode_router_is_deterministic_over_many_calls(pkg, orc, syn):
+    """200 calls of the fused decode sequence on the same 16 rows: ids, weights and outputs are the
+    same bits every time (a last-arriving block ranks the logits; the reference removed such a
+    fusion on one backend because relaxed atomics made it non-deterministic)."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=12)
+    x = syn.random_x(16, dims.n_embd, seed=13)
+    want, _ = orc.route(layer, x, threads=orc.hardware_threads())
+    with pkg.Context(dims, n_layer=1, max_tokens=16, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        d_x, d_y = ctx.to_device(x), ctx.alloc(x.nbytes)
+        ctx.moe_decode(0, d_x, 16, d_y)
+        y0, s0 = d_y.download(np.float32, x.shape), ctx.last_sel(16)
+        assert np.array_equal(s0["ids"][:, :8], want["ids"][:, :8])
+        for _ in range(200):
+            ctx.moe_decode(0, d_x, 16, d_y)
+        y1, s1 = d_y.download(np.float32, x.shape), ctx.last_sel(16)
+        for i in range(50):
+            ctx.moe_decode(0, d_x, 16, d_y)
+            if i % 10 == 0:
+                s = ctx.last_sel(16)
+                assert np.array_equal(s["ids"], s0["ids"]) and np.array_equal(s["w"].view(np.uint32), s0["w"].view(np.uint32))
+    assert np.array_equal(s1["ids"], s0["ids"]) and np.array_equal(y1, y0)
+
+
 def test_decode_stack_and_errors(pkg, orc, syn):
     dims = syn.Dims(n_embd=512, n_ff=256, n_expert=16, n_used=4)
     T, L = 6, 3
