@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 
 #include <cstdarg>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 #include <new>
@@ -68,7 +69,6 @@ struct qkm_ctx {
     bool dec_ok = false;               // dims fit the fused decode kernels
     int8_t* planes8 = nullptr;         // [max_tokens][n_embd/256][8][256]
     uint8_t* lut_gu = nullptr;         // table images the decode kernels copy to shared memory
-    uint8_t* lut_dn = nullptr;
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
     // prefill (tcgen05) scratch, allocated on first use
@@ -278,7 +278,6 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
             struct { void** p; size_t bytes; } dec[] = {
                 {(void**)&c->planes8, T * 8 * d.n_embd},
                 {(void**)&c->lut_gu, decode_gateup_lut_bytes()},
-                {(void**)&c->lut_dn, decode_down_lut_bytes()},
             };
             for (auto& a : dec) {
                 if ((e = cudaMalloc(a.p, a.bytes)) != cudaSuccess) {
@@ -288,7 +287,7 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
                 }
             }
             const Launch L0{nullptr, nullptr};
-            if ((e = launch_decode_gateup_luts(L0, c->lut_gu)) != cudaSuccess || (e = launch_decode_down_lut(L0, c->lut_dn)) != cudaSuccess ||
+            if ((e = launch_decode_gateup_luts(L0, c->lut_gu)) != cudaSuccess ||
                 (e = cudaDeviceSynchronize()) != cudaSuccess) {
                 bail("qkm_open: decode tables", cudaGetErrorString(e));
                 qkm_close(c);
@@ -330,7 +329,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     void* scratch[] = {c->argmax_scratch, c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
-                       c->planes8, c->lut_gu, c->lut_dn,
+                       c->planes8, c->lut_gu,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
@@ -630,13 +629,13 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         ga.sh_gate_tiles = (const uint8_t*)ld.tiles[5]; ga.sh_up_tiles = (const uint8_t*)ld.tiles[6];
         ga.luts = c->lut_gu; ga.planes = c->planes8; ga.xscale = c->xscale; ga.sel = c->sel;
         ga.n_tokens = n; ga.expert_first = c->efirst; ga.expert_count = c->ecount; ga.with_shared = 1;
-        ga.h = c->h; ga.hpieces = c->hpieces; ga.status = c->status; ga.d = d;
+        ga.h = c->h; ga.status = c->status; ga.d = d;
         QKM_LAUNCH(c, launch_decode_gateup(c->Lchain(), ga, nb));
         c->prof_mark("moe.gu");
         if (ld.stream_ok) {
             DownDecodeArgs da{};
-            da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7]; da.lut = c->lut_dn;
-            da.hpieces = c->hpieces; da.h = c->h; da.sel = c->sel; da.y = y; da.n_tokens = n; da.status = c->status; da.d = d;
+            da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7];
+            da.h = c->h; da.sel = c->sel; da.y = y; da.n_tokens = n; da.status = c->status; da.d = d;
             QKM_LAUNCH(c, launch_decode_down(c->Lchain(), da, nb));
         } else {   // Q6_K down: f32 kernel over h, routed slots and the shared expert in one pass
             QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));

@@ -49,7 +49,7 @@ constexpr uint32_t kHigh = kTab + kTabBytes;
 constexpr uint32_t kRed = kHigh + (kWarps - kLowRingWarps) * kRingBytes;
 constexpr uint32_t kRank = kRed + kWarps * 2 * kRedFloats * 4;   // RankShared: selection scratch, group list, pairs
 constexpr uint32_t kEnd = kRank + ((sizeof(RankShared) + 127) / 128) * 128;
-constexpr int kQ8Quarter = 64 + 1024;               // d of two blocks x 16 rows, quants of two blocks x 16 rows
+constexpr int kQ8Quarter = 2 * 544;                 // two 32-column blocks of a Q8_0 tile: d and quants of 16 rows each
 constexpr uint32_t kCostRouted = 8, kCostShared = 11;   // relative time of a routed / a shared tile (measured)
 }  // namespace dg
 
@@ -117,17 +117,18 @@ __device__ __forceinline__ void iq3_tile(uint32_t tb, uint32_t lane, uint32_t g,
     }
 }
 
-// Two Q8_0 blocks (a quarter tile) of one matrix: q points at [d 64 B][quants 1024 B].
+// Two Q8_0 blocks (a quarter tile) of one matrix: q points at two 544-byte pieces [d 32 B][quants 512 B].
 __device__ __forceinline__ void q8_quarter(uint32_t q, uint32_t lane, uint32_t g, uint32_t b0a, uint32_t b1a, uint32_t b0b,
                                            uint32_t b1b, float wcol0, float wcol1, float& fa, float& fb) {
 #pragma unroll
     for (int bb = 0; bb < 2; ++bb) {
-        const uint2 qa = lds64(q + 64 + ((bb * 2 + 0) * 32 + lane) * 8);
-        const uint2 qb = lds64(q + 64 + ((bb * 2 + 1) * 32 + lane) * 8);
+        const uint32_t pb = q + 544 * bb;
+        const uint2 qa = lds64(pb + 32 + lane * 8);
+        const uint2 qb = lds64(pb + 32 + 256 + lane * 8);
         int c[4] = {0, 0, 0, 0};
         mma_s8(c, qa.x, qb.x, qa.y, qb.y, bb ? b0b : b0a, bb ? b1b : b1a);
-        const uint32_t dw = lds32(q + 2 * (16 * bb + (g & ~1u)));
-        const uint32_t dw8 = lds32(q + 2 * (16 * bb + 8 + (g & ~1u)));
+        const uint32_t dw = lds32(pb + 2 * (g & ~1u));
+        const uint32_t dw8 = lds32(pb + 2 * (8 + (g & ~1u)));
         const float da = f16_bits_to_f32((dw >> (16 * (g & 1u))) & 0xFFFFu);
         const float db = f16_bits_to_f32((dw8 >> (16 * (g & 1u))) & 0xFFFFu);
         fa += da * ((float)c[0] * wcol0 + (float)c[1] * wcol1);
@@ -218,11 +219,9 @@ decode_gateup_kernel(GateupDecodeArgs a) {
             p_g += kTileIq3; p_u += kTileIq3;
             ++p_tile; ++p_rt;
         } else {
-            mbar_expect_tx(bar, 2 * dg::kQ8Quarter);
-            bulk_g2s(dst, p_g + 64 * p_q, 64, bar);
-            bulk_g2s(dst + 64, p_g + 256 + 1024 * p_q, 1024, bar);
-            bulk_g2s(dst + dg::kQ8Quarter, p_u + 64 * p_q, 64, bar);
-            bulk_g2s(dst + dg::kQ8Quarter + 64, p_u + 256 + 1024 * p_q, 1024, bar);
+            mbar_expect_tx(bar, 2 * dg::kQ8Quarter);   // a quarter = two 32-column blocks = one 1088-byte piece
+            bulk_g2s(dst, p_g + dg::kQ8Quarter * p_q, dg::kQ8Quarter, bar);
+            bulk_g2s(dst + dg::kQ8Quarter, p_u + dg::kQ8Quarter * p_q, dg::kQ8Quarter, bar);
             if (++p_q == 4) { p_q = 0; p_g += kTileQ8; p_u += kTileQ8; ++p_tile; ++p_rt; }
         }
         if (p_rt >= RT) ++p_gi;
@@ -242,7 +241,7 @@ decode_gateup_kernel(GateupDecodeArgs a) {
     uint32_t gi = t_lo / RT, rt = t_lo - gi * RT;
     bool new_group = true;
     // where this thread's reduction outputs of the current group go: (token, slot) of token slot lt & 1
-    size_t h_base = 0, hp_base = 0;
+    size_t h_base = 0;
     bool ts_live = false;
 
     if (!mbar_wait_bounded(tab_bar, 0)) timed_out = true;   // every thread observes the table's arrival itself
@@ -257,7 +256,6 @@ decode_gateup_kernel(GateupDecodeArgs a) {
                 if (ts_live) {
                     const uint32_t pr = S.pairs[rec.pair_off + ets], tok = pr >> 4, slot = pr & 15u;
                     h_base = ((size_t)tok * (d.n_used + 1) + slot) * d.n_ff;
-                    hp_base = ((size_t)(tok * (d.n_used + 1) + slot) * 3) * d.n_ff;
                 }
             }
             // B operand: column g of the MMA = (token slot g >> 2, digit g & 3); this warp's 256 columns
@@ -348,14 +346,6 @@ decode_gateup_kernel(GateupDecodeArgs a) {
                     const float hv = swiglu(gsum, usum);
                     const uint32_t r_ff = e_first * 16 + row;
                     a.h[h_base + r_ff] = hv;
-                    // bf16 pieces in the down kernel's B-operand order: [token][slot][piece][sub-block][t][8]
-                    // with the 8 = elements (4t, 16+4t, 4t+1, 17+4t, 4t+2, 18+4t, 4t+3, 19+4t)
-                    __nv_bfloat16 p0, p1, p2;
-                    bf16_pieces(hv, p0, p1, p2);
-                    const uint32_t e32 = r_ff & 31u, tt = (e32 & 15u) >> 2, pos = 2 * (e32 & 3u) + (e32 >> 4);
-                    __nv_bfloat16* hp = reinterpret_cast<__nv_bfloat16*>(a.hpieces);
-                    const size_t o = hp_base + (r_ff & ~31u) + tt * 8 + pos;
-                    hp[o] = p0; hp[o + d.n_ff] = p1; hp[o + 2 * (size_t)d.n_ff] = p2;
                 }
             }
             e_n = 0;

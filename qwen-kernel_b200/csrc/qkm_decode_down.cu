@@ -199,8 +199,8 @@ down_stream_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __res
             } else {  // Q8_0: 8 blocks of 32 per row
 #pragma unroll
                 for (int blk = 0; blk < 8; ++blk) {
-                    const uint2 qa = lds64(tb + 256 + ((blk * 2 + 0) * 32 + lane) * 8);  // row g: qs[4t..], qs[16+4t..]
-                    const uint2 qb = lds64(tb + 256 + ((blk * 2 + 1) * 32 + lane) * 8);  // row g+8
+                    const uint2 qa = lds64(tb + 544 * blk + 32 + lane * 8);  // row g: qs[4t..], qs[16+4t..]
+                    const uint2 qb = lds64(tb + 544 * blk + 32 + 256 + lane * 8);  // row g+8
                     uint32_t ar[4], br[4];  // per byte j: (q[4t+j], q[16+4t+j]) as a bf16 pair
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
@@ -215,8 +215,8 @@ down_stream_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __res
                     float c[4] = {0.f, 0.f, 0.f, 0.f};
                     mma_bf16(c, ar[0], br[0], ar[1], br[1], bq[blk][0], bq[blk][1]);
                     mma_bf16(c, ar[2], br[2], ar[3], br[3], bq[blk][2], bq[blk][3]);
-                    const uint32_t dw = lds32(tb + 2 * (16 * blk + (g & ~1u)));
-                    const uint32_t dw8 = lds32(tb + 2 * (16 * blk + 8 + (g & ~1u)));
+                    const uint32_t dw = lds32(tb + 544 * blk + 2 * (g & ~1u));
+                    const uint32_t dw8 = lds32(tb + 544 * blk + 2 * (8 + (g & ~1u)));
                     const float da = f16_bits_to_f32((dw >> (16 * (g & 1u))) & 0xFFFFu);
                     const float db = f16_bits_to_f32((dw8 >> (16 * (g & 1u))) & 0xFFFFu);
                     acc[0] += da * c[0]; acc[1] += da * c[1];

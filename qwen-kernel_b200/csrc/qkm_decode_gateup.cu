@@ -111,12 +111,12 @@ __device__ __forceinline__ void gu_tile(uint32_t tb, uint32_t lane, uint32_t g, 
         float fa = 0.f, fb = 0.f;
 #pragma unroll
         for (int blk = 0; blk < 8; ++blk) {
-            const uint2 qa = lds64(tb + 256 + ((blk * 2 + 0) * 32 + lane) * 8);
-            const uint2 qb = lds64(tb + 256 + ((blk * 2 + 1) * 32 + lane) * 8);
+            const uint2 qa = lds64(tb + 544 * blk + 32 + lane * 8);
+            const uint2 qb = lds64(tb + 544 * blk + 32 + 256 + lane * 8);
             int c[4] = {0, 0, 0, 0};
             mma_s8(c, qa.x, qb.x, qa.y, qb.y, b0[blk], b1[blk]);
-            const uint32_t dw = lds32(tb + 2 * (16 * blk + (g & ~1u)));       // d of rows g&~1, (g&~1)+1
-            const uint32_t dw8 = lds32(tb + 2 * (16 * blk + 8 + (g & ~1u)));  // rows +8
+            const uint32_t dw = lds32(tb + 544 * blk + 2 * (g & ~1u));       // d of rows g&~1, (g&~1)+1
+            const uint32_t dw8 = lds32(tb + 544 * blk + 2 * (8 + (g & ~1u)));  // rows +8
             const float da = f16_bits_to_f32((dw >> (16 * (g & 1u))) & 0xFFFFu);
             const float db = f16_bits_to_f32((dw8 >> (16 * (g & 1u))) & 0xFFFFu);
             fa += da * ((float)c[0] * wcol0 + (float)c[1] * wcol1);

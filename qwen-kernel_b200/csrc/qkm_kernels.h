@@ -81,7 +81,7 @@ struct RouteDecodeArgs {
 };
 bool route_decode_ok(const qkm_dims& d, uint32_t n_tokens, size_t scratch_bytes);
 cudaError_t launch_route_decode(const Launch& L, uint32_t router_type, const RouteDecodeArgs& a);
-// routed (IQ3_XXS) and shared (Q8_0) gate/up + SwiGLU over the groups; h as f32 and as bf16 pieces
+// routed (IQ3_XXS) and shared (Q8_0) gate/up + SwiGLU over the groups
 struct GateupDecodeArgs {
     const uint8_t* gate_tiles;      // routed experts, IQ3_XXS tiles
     const uint8_t* up_tiles;
@@ -92,8 +92,7 @@ struct GateupDecodeArgs {
     const float* xscale;
     const qkm_sel* sel;             // the selection (its pairs are grouped by expert in every block at its start)
     uint32_t n_tokens, expert_first, expert_count, with_shared;
-    float* h;                       // [T][n_used+1][n_ff]
-    void* hpieces;                  // bf16 [T][n_used+1][3][n_ff] in the down kernel's operand order
+    float* h;                       // out [T][n_used+1][n_ff]
     uint32_t* status;
     qkm_dims d;
 };
@@ -105,17 +104,13 @@ cudaError_t launch_decode_gateup(const Launch& L, const GateupDecodeArgs& a, uin
 struct DownDecodeArgs {
     const uint8_t* tiles;           // routed experts, IQ4_XS tiles
     const uint8_t* sh_tiles;        // shared expert, Q8_0 tiles (NULL: no shared term)
-    const uint8_t* lut;             // decode_down_lut_bytes() bytes written by launch_decode_down_lut
-    const void* hpieces;
-    const float* h;                 // [T][n_used+1][n_ff] f32 (the shared expert's rows are encoded as digit planes in the kernel)
+    const float* h;                 // [T][n_used+1][n_ff] f32 (encoded as int8 digit planes inside the kernel)
     const qkm_sel* sel;
     float* y;
     uint32_t n_tokens;
     uint32_t* status;
     qkm_dims d;
 };
-size_t decode_down_lut_bytes();
-cudaError_t launch_decode_down_lut(const Launch& L, uint8_t* lut);
 bool decode_down_ok(const qkm_dims& d);
 cudaError_t launch_decode_down(const Launch& L, const DownDecodeArgs& a, uint32_t n_blocks);
 

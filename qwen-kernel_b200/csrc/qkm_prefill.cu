@@ -282,12 +282,12 @@ __device__ __forceinline__ void produce_q8(const uint8_t* __restrict__ tile, uin
 #pragma unroll
     for (int j = J0; j < J1; ++j) {
         const uint32_t blk = 2 * q + j;
-        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + 2 * (16 * blk + r16)));
+        const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + 544 * blk + 2 * r16));
         // lane slot (g, t): qs[4t..4t+3] then qs[16+4t..16+4t+3]
         uint2 w[4];
 #pragma unroll
         for (int t = 0; t < 4; ++t)
-            w[t] = *reinterpret_cast<const uint2*>(tile + 256 + ((blk * 2 + hf) * 32 + 4 * g + t) * 8);
+            w[t] = *reinterpret_cast<const uint2*>(tile + 544 * blk + 32 + (hf * 32 + 4 * g + t) * 8);
 #pragma unroll
         for (int p = 0; p < 4; ++p) {      // elements 8p..8p+7: words (2(p&1), 2(p&1)+1), .x below 16, .y above
             const uint32_t a = (p >> 1) ? w[2 * (p & 1)].y : w[2 * (p & 1)].x;

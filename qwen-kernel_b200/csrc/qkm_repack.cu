@@ -53,16 +53,13 @@ __global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restri
             off = 8 + 16 * ib + 4 * t + (b & 3u);
         }
         out[i] = m[(size_t)(rt * 16 + row_in_tile) * rb + (size_t)kb * 136 + off];
-    } else {  // Q8_0
-        uint32_t blk;
-        if (o < 256) {
-            blk = o >> 5;
-            row_in_tile = (o >> 1) & 15u;
-            off = o & 1u;
+    } else {  // Q8_0: per 32-column block, the 16 rows' d (32 B) then their quants (512 B)
+        const uint32_t blk = o / 544u, q = o - blk * 544u;
+        if (q < 32) {
+            row_in_tile = q >> 1;
+            off = q & 1u;
         } else {
-            const uint32_t q = o - 256;
-            blk = q >> 9;
-            const uint32_t h = (q >> 8) & 1u, lane = (q >> 3) & 31u, b = q & 7u;
+            const uint32_t v = q - 32, h = (v >> 8) & 1u, lane = (v >> 3) & 31u, b = v & 7u;
             const uint32_t g = lane >> 2, t = lane & 3u;
             row_in_tile = g + 8 * h;
             off = 2 + (b < 4 ? 4 * t + b : 16 + 4 * t + (b - 4));

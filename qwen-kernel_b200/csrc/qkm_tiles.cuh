@@ -29,10 +29,11 @@
 //                  c = 2*h + q: row g + 8h, sub-blocks 4q..4q+3, for each the raw qs word t
 //                  (bytes 4t..4t+3 of the sub-block's 16: low nibbles are elements
 //                  4t..4t+3, high nibbles elements 16+4t..16+4t+3)
-//   Q8_0 (block: d f16 | qs[32], src/quants.h:53-57), 8 blocks per row per tile
-//     [   0, 256)  d: row r, block b at 2*(16*b + r)  (16 consecutive rows per block)
-//     [ 256,4352)  quants: block b, half h (row g + 8h), lane -> 8 B at
-//                  256 + ((b*2 + h)*32 + lane)*8 = raw qs[4t..4t+3] then qs[16+4t..16+4t+3]
+//   Q8_0 (block: d f16 | qs[32], src/quants.h:53-57), 8 blocks per row per tile; block b of
+//   the 16 rows is one 544-byte piece at 544*b (so a run of blocks is one bulk copy):
+//     [  0, 32)  d: row r at 2*r
+//     [ 32,544)  quants: half h (row g + 8h), lane -> 8 B at 32 + (h*32 + lane)*8
+//                = raw qs[4t..4t+3] then qs[16+4t..16+4t+3]
 //
 // DIGIT PLANES.  An activation row x[K] is encoded as four int8 planes with one
 // power-of-two scale per row (or per 128-element chunk for the expert hidden rows):
