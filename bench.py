@@ -407,6 +407,9 @@ def run_ours(args, pkg, syn):
     # ---- the other configurations, as sub-objects of the same line
     if not args.no_sub:
         line["prefill"] = run_prefill_or_ep(args, pkg, syn, torch, R, orc, layers_keep, peaks)
+        if world > 1:
+            line["config"]["expert_parallel"] = {"ranks": world, "experts_per_rank": dims.n_expert // world,
+                                                 "tokens": line["prefill"].get("summary")}
         if world == 1:
             line["gemv"] = run_gemv_sweep(args, pkg, syn, torch, R, orc, peaks)
     if rank == 0:
@@ -469,6 +472,34 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             peer = None
             out["peer_memory_unavailable"] = why or "a peer rank could not map the buffers"
     steps, warm = max(3, args.steps // 4), 3
+    # the unsharded layer on ONE GPU at the same token counts, timed by rank 0 inside this run
+    # (the other ranks wait): the denominator of the expert-parallel speed-up
+    one_gpu_us = {}
+    if world > 1:
+        if rank == 0:
+            c1 = pkg.Context(dims, n_layer=PL, max_tokens=Tmax, device=R.local_rank)
+            for l, layer in enumerate(layers):
+                c1.upload_layer(l, layer)
+            x1 = torch.from_numpy(np.stack([syn.random_x(Tmax, dims.n_embd, SEED_X + 555 + l) for l in range(PL)])).to(dev)
+            y1 = torch.empty_like(x1)
+            for T1 in (128, 2048, 4096):
+                def step1():
+                    for l in range(PL):
+                        c1.moe_prefill(l, x1[l], T1, y1[l])
+                for _ in range(warm):
+                    step1()
+                torch.cuda.synchronize(dev)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record(stream)
+                for _ in range(steps):
+                    step1()
+                e1.record(stream)
+                torch.cuda.synchronize(dev)
+                one_gpu_us[T1] = e0.elapsed_time(e1) / steps / PL * 1e3
+            c1.close()
+            del x1, y1
+            torch.cuda.empty_cache()
+        R.barrier()
     for T in PREFILL_CHUNKS:
         n = T // world
         if n == 0:
@@ -545,6 +576,9 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             entry_["tensor_tflops_per_gpu"] = entry_["tensor_tflops"] / world
             entry_["frac_of_measured_bf16_burst"] = entry_["tensor_tflops_per_gpu"] / peaks["bf16_tflops"]
             entry_["nccl_all_to_all"] = a2a
+        if T in one_gpu_us:
+            entry_["us_per_layer_1gpu_same_run"] = one_gpu_us[T]
+            entry_["speedup_vs_1gpu"] = one_gpu_us[T] / entry_["us_per_layer"]
         out["chunks"][str(T)] = entry_
     if world == 1:
         ctx.profile_enable(True)
@@ -567,6 +601,10 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
                        f"expert-parallel moe layer: T tokens over {world} GPUs ({per} experts each), rows stored into the "
                        "owners' peer-mapped buffers over NVLink (NCCL all-to-all form beside it)")
     out["scaling"] = "strong"
+    if world > 1:   # the figures the scaling claim rests on, short enough to ride in the line's config object
+        out["summary"] = {str(T): {k: out["chunks"][str(T)].get(k) for k in
+                                   ("us_per_layer", "us_per_layer_1gpu_same_run", "speedup_vs_1gpu", "rel_err_vs_oracle", "stages_us")}
+                          for T in (128, 2048, 4096) if str(T) in out["chunks"]}
     R.barrier()
     ctx.close()
     return out

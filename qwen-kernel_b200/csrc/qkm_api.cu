@@ -771,7 +771,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     }
     QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
-                                    c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status));
+                                    c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms));
     if (!fork) c->prof_mark("moe.shared_gu");
     if (ld.stream_ok) {
         QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
@@ -1154,7 +1154,7 @@ extern "C" QKM_API int qkm_ep_shared(qkm_ctx* c, uint32_t layer, const float* x,
                                   c->mma_items[3], c->n_items, c->pos_of, true));
     QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
-                                    c->n_items + 2, sh_now * (d.n_ff / 128), c->h, c->hb, c->status));
+                                    c->n_items + 2, sh_now * (d.n_ff / 128), c->h, c->hb, c->status, sh_now * (d.n_ff / 128) <= 2u * (uint32_t)c->n_sms));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
                                   c->n_items + 3, sh_now * (d.n_embd / 128), c->contrib_p, c->status));
     QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, c->y2, n));
@@ -1214,15 +1214,17 @@ static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv
         QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
         QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
-                                        c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status));
+                                        c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms));
         QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, selrecv, c->pairs, c->mma_items[3],
                                       c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
         QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     }
+    // a shard of few experts launches fewer blocks than the machine holds: faster blocks instead (see the launchers)
+    const bool few_gu = c->ecount * rt_gu <= 2u * (uint32_t)c->n_sms, few_dn = c->ecount * rt_dn / 4 <= 2u * (uint32_t)c->n_sms;
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status));
+                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status, few_gu));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
-                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status));
+                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn));
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     if (slot_rows_peer)
         QKM_LAUNCH(c, launch_fold_pairs_peer(c->L(), d, c->contrib_p, c->pos_of, c->pm_peers, slot_rows_peer, c->pm_rank, c->pm_ranks));
@@ -1290,16 +1292,24 @@ extern "C" QKM_API int qkm_ep_peer_setup(qkm_ctx* c, uint32_t n_ranks, uint32_t 
         return fail(c, QKM_ERR_BOUNDS, "%u ranks x %u rows exceed max_tokens %u", n_ranks, slot_cap, c->cfg.max_tokens);
     const size_t rows = (size_t)n_ranks * slot_cap;
     QKM_CUDA(c, cudaSetDevice(c->device));
-    QKM_CUDA(c, cudaMalloc((void**)&c->pm_xrecv, rows * d.n_embd * sizeof(float)));
+    // all four buffers or none: a failure part way frees what was taken, so a retry starts clean
+    cudaError_t e = cudaMalloc((void**)&c->pm_xrecv, rows * d.n_embd * sizeof(float));
     // the barrier words of qkm_ep_barrier sit behind the records, so three mappings carry everything
-    QKM_CUDA(c, cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel) + kPmFlagBytes));
-    QKM_CUDA(c, cudaMemset((char*)c->pm_selrecv + rows * sizeof(qkm_sel), 0, kPmFlagBytes));
-    QKM_CUDA(c, cudaMalloc((void**)&c->pm_partial, rows * d.n_embd * sizeof(float)));
-    QKM_CUDA(c, cudaMalloc((void**)&c->pm_back, rows * d.n_embd * sizeof(float)));
-    QKM_CUDA(c, cudaMemset(c->pm_back, 0, rows * d.n_embd * sizeof(float)));
-    QKM_CUDA(c, cudaMemset(c->pm_xrecv, 0, rows * d.n_embd * sizeof(float)));
-    QKM_CUDA(c, cudaMemset(c->pm_selrecv, 0xFF, rows * sizeof(qkm_sel)));   // every record empty
-    QKM_CUDA(c, cudaMemset(c->pm_partial, 0, rows * d.n_embd * sizeof(float)));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel) + kPmFlagBytes);
+    if (e == cudaSuccess) e = cudaMemset((char*)c->pm_selrecv + rows * sizeof(qkm_sel), 0, kPmFlagBytes);
+    if (e == cudaSuccess) e = cudaMalloc((void**)&c->pm_partial, rows * d.n_embd * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&c->pm_back, rows * d.n_embd * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(c->pm_back, 0, rows * d.n_embd * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(c->pm_xrecv, 0, rows * d.n_embd * sizeof(float));
+    if (e == cudaSuccess) e = cudaMemset(c->pm_selrecv, 0xFF, rows * sizeof(qkm_sel));   // every record empty
+    if (e == cudaSuccess) e = cudaMemset(c->pm_partial, 0, rows * d.n_embd * sizeof(float));
+    if (e != cudaSuccess) {
+        for (void** p : {(void**)&c->pm_xrecv, (void**)&c->pm_selrecv, (void**)&c->pm_partial, (void**)&c->pm_back}) {
+            if (*p) cudaFree(*p);
+            *p = nullptr;
+        }
+        return fail(c, QKM_ERR_CUDA, "qkm_ep_peer_setup: %s", cudaGetErrorString(e));
+    }
     c->pm_ranks = n_ranks; c->pm_rank = rank; c->pm_cap = slot_cap; c->pm_epoch = 0;
     c->pm_peers.x[rank] = c->pm_xrecv; c->pm_peers.sel[rank] = c->pm_selrecv; c->pm_peers.back[rank] = c->pm_back;
     c->pm_peers.flags[rank] = pm_flags_of(c, c->pm_selrecv);

@@ -126,10 +126,10 @@ cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* 
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
-                              uint32_t* status);
+                              uint32_t* status, bool few_blocks = false);   // few_blocks: the grid will not fill the machine
 cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
                             const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
-                            uint32_t max_items, float* contrib, uint32_t* status);
+                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks = false);
 cudaError_t launch_fold_pairs(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,
                               float* y, uint32_t n_tokens);
 
@@ -202,7 +202,7 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
 // |error| <= 2^-9 * |router row| * |x|.  Needs n_expert % 128 == 0 and n_embd <= 4096.
 cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
                               const void* x_f16, const float* x_inv_scale, float* logits, uint32_t n_tokens,
-                              uint32_t* status);
+                              uint32_t* status, uint32_t splits = 1)   /* splits > 1: partial logits over column ranges, [splits][n_tokens][n_expert] */;
 cudaError_t launch_group_pairs(const Launch& L, const qkm_dims& d, const qkm_sel* sel, uint32_t n_tokens,
                                uint32_t* offsets, uint32_t* pairs, uint32_t expert_first,
                                uint32_t expert_count);

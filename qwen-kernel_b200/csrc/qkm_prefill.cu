@@ -181,12 +181,13 @@ __device__ __forceinline__ Iq3Raw load_iq3(const uint8_t* __restrict__ tile, uin
 // another the four sign masks of a 7-bit sign code; one packed multiply by the sub-block
 // scale (f16) and one XOR per pair.  Two roundings of 2^-12 each.
 //   s_grid: [256][kGridReplicas] u32 (four magnitudes)     s_sign: [128] sign bytes (code | parity << 7)
+template <int J0, int J1>
 __device__ __forceinline__ void produce_iq3(const Iq3Raw& raw, const uint32_t* __restrict__ s_grid,
                                             const uint8_t* __restrict__ s_sign, uint32_t lane, uint8_t* a_tile,
                                             uint32_t row) {
     const float d = f16_bits_to_f32(raw.dbits);
 #pragma unroll
-    for (int j = 0; j < 2; ++j) {          // sub-block 2q + j
+    for (int j = J0; j < J1; ++j) {        // sub-block 2q + j
         const uint32_t aux = j ? raw.aux2.y : raw.aux2.x;
         const __half2 db2 = __float2half2_rn(d * (0.5f + (float)(aux >> 28)) * 0.5f);
         const __half2 nb2 = __hmul2(db2, __float2half2_rn(-1024.f));
@@ -308,41 +309,47 @@ __device__ __forceinline__ void produce_q8(const uint8_t* __restrict__ tile, uin
 // `row_ptr[i]` is the activation row of pair i (element type: 2 bytes).
 struct BRegs { uint4 v[4]; };
 
-template <class T>
+template <class T, int PT = pf::kThreads>
 __device__ __forceinline__ BRegs fetch_b(const T* const* row_ptr, uint32_t n, uint32_t n_mma, uint32_t k0) {
     BRegs b;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t qd = threadIdx.x + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
+    for (int i = 0; i < 1024 / PT; ++i) {
+        const uint32_t qd = threadIdx.x + i * PT, row = qd >> 3, c = qd & 7u;
         b.v[i] = make_uint4(0, 0, 0, 0);
         if (qd < n_mma * 8 && row < n) b.v[i] = *reinterpret_cast<const uint4*>(row_ptr[row] + k0 + 8 * c);
     }
     return b;
 }
+template <int PT = pf::kThreads>
 __device__ __forceinline__ void store_b(uint8_t* b_tile, const BRegs& b, uint32_t n_mma) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const uint32_t qd = threadIdx.x + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
+    for (int i = 0; i < 1024 / PT; ++i) {
+        const uint32_t qd = threadIdx.x + i * PT, row = qd >> 3, c = qd & 7u;
         if (qd < n_mma * 8) *reinterpret_cast<uint4*>(b_tile + umma::sw128_chunk(row, c)) = b.v[i];
     }
 }
 
 // ---- gate/up + SwiGLU ------------------------------------------------------------------------------------
 // FMT: QKM_TYPE_IQ3_XXS (routed experts) or QKM_TYPE_Q8_0 (shared expert).
-template <int FMT>
-__global__ void __launch_bounds__(pf::kBlock, 2)
+// PT: producer threads.  256: a thread dequantises both 32-column sub-blocks of its row's k-step, two
+// blocks share an SM (big grids).  512: two threads share a row, one sub-block each, one block per
+// SM - for grids that do not fill the machine (a shard of few experts, the shared expert), where a
+// block's own speed is what counts.
+template <int FMT, int PT>
+__global__ void __launch_bounds__(PT + 32, PT == 256 ? 2 : 1)
 gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restrict__ up_tiles,
                   const __half* __restrict__ xb, const float* __restrict__ x_inv_scale,
                   const uint32_t* __restrict__ pairs, const MmaItem* __restrict__ items,
                   const uint32_t* __restrict__ n_items_ptr, float* __restrict__ h,
                   __nv_bfloat16* __restrict__ hb, qkm_dims d, uint32_t* __restrict__ status) {
     if (blockIdx.x >= *n_items_ptr) return;
+    constexpr int kSt = pf::kStages;
     constexpr int kTile = FMT == QKM_TYPE_IQ3_XXS ? kTileIq3 : kTileQ8;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
-    __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
+    __shared__ __align__(8) unsigned long long s_bar[2 * kSt + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + pf::kStages * 3 * pf::kTileBytes);
+    uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + kSt * 3 * pf::kTileBytes);
     uint8_t* s_sign = reinterpret_cast<uint8_t*>(s_grid + 256 * pf::kGridReplicas);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const MmaItem it = items[blockIdx.x];
@@ -350,15 +357,15 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     const uint32_t KB = d.n_embd / 256, RT16 = d.n_ff / 16, KS = d.n_embd / 64;
 
     if (FMT == QKM_TYPE_IQ3_XXS) {
-        for (uint32_t i = tid; i < 256 * pf::kGridReplicas; i += pf::kThreads) s_grid[i] = c_iq3_grid[i / pf::kGridReplicas];
+        for (uint32_t i = tid; i < 256 * pf::kGridReplicas; i += PT) s_grid[i] = c_iq3_grid[i / pf::kGridReplicas];
         if (tid < 128) s_sign[tid] = (uint8_t)signs8(tid);
     }
     if (tid == 0) {
-        for (int s = 0; s < pf::kStages; ++s) {
+        for (int s = 0; s < kSt; ++s) {
             mbar_init(smem_addr(&s_bar[s]), 1);                            // empty: one commit
-            mbar_init(smem_addr(&s_bar[pf::kStages + s]), pf::kThreads);   // full: every producer thread
+            mbar_init(smem_addr(&s_bar[kSt + s]), PT);   // full: every producer thread
         }
-        mbar_init(smem_addr(&s_bar[2 * pf::kStages]), 1);
+        mbar_init(smem_addr(&s_bar[2 * kSt]), 1);
         mbar_fence_init();
     }
     if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), 256); umma::tmem_relinquish(); }
@@ -369,8 +376,9 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     const uint32_t idesc = umma::instr_desc_f16(n_mma);
     bool timed_out = false;
 
-    // producer role of this thread: row r of the gate (threads 0..127) or up (128..255) tile
-    const uint32_t r = tid & 127u, mat = tid >> 7;
+    // producer role of this thread: row r of the gate (threads 0..127 of each 256) or up (128..255) tile;
+    // with 512 producers, threads 256.. take the second sub-block of the k-step
+    const uint32_t r = tid & 127u, mat = (tid >> 7) & 1u, half = tid >> 8;
     const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
     const uint8_t* wt = (mat ? up_tiles : gate_tiles) + (size_t)it.expert * KB * RT16 * kTile;
 
@@ -380,19 +388,19 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     __shared__ const __half* s_row[pf::kNT];
     __shared__ float s_inv[pf::kNT];
     __shared__ uint32_t s_hrow[pf::kNT];
-    for (uint32_t i = tid; i < n; i += pf::kBlock) {
+    for (uint32_t i = tid; i < n; i += PT + 32) {
         const uint32_t pr = pairs[it.pair_off + i], tok = pr >> 4;
         s_row[i] = xb + (size_t)tok * d.n_embd;
         s_inv[i] = x_inv_scale[tok];
         s_hrow[i] = tok * (d.n_used + 1) + (pr & 15u);
     }
     __syncthreads();
-    if (tid >= pf::kThreads) {
+    if (tid >= PT) {
         // ---- MMA issuer warp
         if (lane == 0) {
             for (uint32_t ks = 0; ks < KS; ++ks) {
-                const uint32_t stage = ks % pf::kStages;
-                if (!mbar_wait_bounded(smem_addr(&s_bar[pf::kStages + stage]), (ks / pf::kStages) & 1u)) timed_out = true;
+                const uint32_t stage = ks % kSt;
+                if (!mbar_wait_bounded(smem_addr(&s_bar[kSt + stage]), (ks / kSt) & 1u)) timed_out = true;
                 umma::fence_after_sync();
                 const uint32_t a_g = smem_addr(smem + stage * 3 * pf::kTileBytes), a_u = a_g + pf::kTileBytes, b = a_g + 2 * pf::kTileBytes;
 #pragma unroll
@@ -402,7 +410,7 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                     umma::mma_f16_ss(tmem + 128, umma::smem_desc(a_u + 32 * j), umma::smem_desc(b + 32 * j), idesc, acc);
                 }
                 umma::commit(smem_addr(&s_bar[stage]));
-                if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[2 * pf::kStages]));
+                if (ks + 1 == KS) umma::commit(smem_addr(&s_bar[2 * kSt]));
             }
         }
     } else {
@@ -413,9 +421,9 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
         ix = load_iq3_idx(wt + (size_t)rt16 * kTile, r16);
         raw = load_iq3(wt + (size_t)rt16 * kTile, r16, 0, ix);
     }
-    BRegs breg = fetch_b(s_row, n, n_mma, 0);
+    BRegs breg = fetch_b<__half, PT>(s_row, n, n_mma, 0);
     for (uint32_t ks = 0; ks < KS; ++ks) {
-        const uint32_t stage = ks % pf::kStages;
+        const uint32_t stage = ks % kSt;
         Iq3Raw next{};
         BRegs bnext{};
         if (ks + 1 < KS) {
@@ -424,27 +432,35 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                 if (((ks + 1) & 3u) == 0) ix = load_iq3_idx(ntile, r16);
                 next = load_iq3(ntile, r16, (ks + 1) & 3u, ix);
             }
-            bnext = fetch_b(s_row, n, n_mma, (ks + 1) * 64);
+            bnext = fetch_b<__half, PT>(s_row, n, n_mma, (ks + 1) * 64);
         }
-        if (ks >= (uint32_t)pf::kStages)
-            if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / pf::kStages) - 1) & 1u)) timed_out = true;
+        if (ks >= (uint32_t)kSt)
+            if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / kSt) - 1) & 1u)) timed_out = true;
         uint8_t* st = smem + stage * 3 * pf::kTileBytes;
         const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-        if (FMT == QKM_TYPE_IQ3_XXS) { produce_iq3(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r); raw = next; }
-        else produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
-        store_b(st + 2 * pf::kTileBytes, breg, n_mma);
+        if (FMT == QKM_TYPE_IQ3_XXS) {
+            if (PT == 256) produce_iq3<0, 2>(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r);
+            else if (half == 0) produce_iq3<0, 1>(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r);
+            else produce_iq3<1, 2>(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r);
+            raw = next;
+        } else {
+            if (PT == 256) produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+            else if (half == 0) produce_q8<true, 0, 1>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+            else produce_q8<true, 1, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+        }
+        store_b<PT>(st + 2 * pf::kTileBytes, breg, n_mma);
         breg = bnext;
         umma::fence_smem_to_async();
-        mbar_arrive(smem_addr(&s_bar[pf::kStages + stage]));
+        mbar_arrive(smem_addr(&s_bar[kSt + stage]));
     }
-    if (!mbar_wait_bounded(smem_addr(&s_bar[2 * pf::kStages]), 0)) timed_out = true;
+    if (!mbar_wait_bounded(smem_addr(&s_bar[2 * kSt]), 0)) timed_out = true;
     umma::fence_after_sync();
 
-    // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) and every other 16-column block
+    // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) and every (PT/128)-th 16-column block
     {
         const uint32_t lg = warp & 3u, row = 32 * lg + lane;
         const uint32_t r_ff = it.rt * 128u + row;
-        for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += 2) {
+        for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += PT / 128) {
             uint32_t vg[16], vu[16];
             umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, vg);
             umma::tmem_ld16(tmem + ((32 * lg) << 16) + 128 + cb * 16, vu);
@@ -463,9 +479,10 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     }
     }  // producer / epilogue warps
     umma::fence_before_sync();
-    __syncthreads();
+    // any thread's wait that ran out counts (the MMA issuer's too, not only thread 0's)
+    const int any_timed_out = __syncthreads_or(timed_out ? 1 : 0);
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
-    if (timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+    if (any_timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
 // ---- down -------------------------------------------------------------------------------------------------
@@ -595,9 +612,10 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     }  // row tiles
     }  // producer / epilogue warps
     umma::fence_before_sync();
-    __syncthreads();
+    // any thread's wait that ran out counts (the MMA issuer's too, not only thread 0's)
+    const int any_timed_out = __syncthreads_or(timed_out ? 1 : 0);
     if (warp == 0) umma::tmem_dealloc(tmem, 128);
-    if (timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+    if (any_timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
 // ---- router logits on the tensor cores -----------------------------------------------------------------
@@ -642,7 +660,12 @@ __device__ __forceinline__ void lg_fetch(LgRegs& r, const uint8_t* __restrict__ 
 template <int TYPE>
 __global__ void __launch_bounds__(pf::kBlock, 1)
 logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__ xh, const float* __restrict__ x_inv_scale,
-                  float* __restrict__ logits, uint32_t n_expert, uint32_t K, uint32_t n_tokens, uint32_t* __restrict__ status) {
+                  float* __restrict__ logits_all, uint32_t n_expert, uint32_t K_all, uint32_t n_tokens, uint32_t* __restrict__ status) {
+    // blockIdx.z: the column range [z, z+1) * K_all / gridDim.z; its partial logits go to part z of the output
+    const uint32_t K = K_all / gridDim.z;
+    float* __restrict__ logits = logits_all + (size_t)blockIdx.z * n_tokens * n_expert;
+    router += (size_t)blockIdx.z * K * (TYPE == QKM_TYPE_F16 ? 2 : 4);
+    xh += (size_t)blockIdx.z * K;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long s_bar[2 * kLgStages + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
@@ -692,10 +715,10 @@ logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
                     const uint32_t qd = tid + i * pf::kThreads, row = qd >> 3, c = qd & 7u;
-                    cp_async16(st + umma::sw128_chunk(row, c), router + ((size_t)(e0 + row) * K + k0 + 8 * c) * 2);
+                    cp_async16(st + umma::sw128_chunk(row, c), router + ((size_t)(e0 + row) * K_all + k0 + 8 * c) * 2);
                     if (qd < n_mma * 8) {
                         const uint32_t src_row = row < n ? row : 0u;   // rows past n feed accumulator columns nobody reads
-                        cp_async16(st + pf::kTileBytes + umma::sw128_chunk(row, c), xh + (size_t)(t0 + src_row) * K + k0 + 8 * c);
+                        cp_async16(st + pf::kTileBytes + umma::sw128_chunk(row, c), xh + (size_t)(t0 + src_row) * K_all + k0 + 8 * c);
                     }
                 }
                 cp_async_commit();
@@ -709,7 +732,7 @@ logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__
             }
         } else {
         LgRegs cur;
-        lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K, 0);
+        lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K_all, 0);
         for (uint32_t ks = 0; ks < KS; ++ks) {
             const uint32_t stage = ks % kLgStages;
             if (ks >= (uint32_t)kLgStages)
@@ -723,7 +746,7 @@ logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__
             }
             umma::fence_smem_to_async();
             mbar_arrive(smem_addr(&s_bar[kLgStages + stage]));
-            if (ks + 1 < KS) lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K, (ks + 1) * 64);
+            if (ks + 1 < KS) lg_fetch<TYPE>(cur, router, xh, e0, t0, n, n_mma, K_all, (ks + 1) * 64);
         }
         }
         if (!mbar_wait_bounded(smem_addr(&s_bar[2 * kLgStages]), 0)) timed_out = true;
@@ -741,18 +764,19 @@ logits_mma_kernel(const uint8_t* __restrict__ router, const __half* __restrict__
         }
     }
     umma::fence_before_sync();
-    __syncthreads();
+    // any thread's wait that ran out counts (the MMA issuer's too, not only thread 0's)
+    const int any_timed_out = __syncthreads_or(timed_out ? 1 : 0);
     if (warp == 0) umma::tmem_dealloc(tmem, 128);
-    if (timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+    if (any_timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
 cudaError_t launch_logits_mma(const Launch& L, const qkm_dims& d, uint32_t router_type, const void* router,
                               const void* x_f16, const float* x_inv_scale, float* logits, uint32_t n_tokens,
-                              uint32_t* status) {
+                              uint32_t* status, uint32_t splits) {
     if (n_tokens == 0) return cudaSuccess;
-    if (d.n_expert % 128 || d.n_embd % 64 || d.n_embd > 4096) return cudaErrorInvalidValue;
+    if (d.n_expert % 128 || d.n_embd % 64 || d.n_embd > 4096 || splits == 0 || (d.n_embd / 64) % splits) return cudaErrorInvalidValue;
     const size_t smem = (size_t)kLgStages * 2 * pf::kTileBytes + 1024;
-    const dim3 grid((n_tokens + 127) / 128, d.n_expert / 128);
+    const dim3 grid((n_tokens + 127) / 128, d.n_expert / 128, splits);
     cudaError_t e;
     if (router_type == QKM_TYPE_F16) {
         e = cudaFuncSetAttribute(logits_mma_kernel<QKM_TYPE_F16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -883,14 +907,14 @@ cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* 
     return cudaGetLastError();
 }
 
-template <int FMT>
+template <int FMT, int PT>
 static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
                                      const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
                                      const uint32_t* n_items, uint32_t max_items, float* h, void* hb, uint32_t* status) {
     const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 256 * pf::kGridReplicas * 4 + 128 + 1024;
-    cudaError_t e = cudaFuncSetAttribute(gateup_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gateup_mma_kernel<FMT, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    gateup_mma_kernel<FMT><<<max_items, pf::kBlock, smem, L.stream>>>(
+    gateup_mma_kernel<FMT, PT><<<max_items, PT + 32, smem, L.stream>>>(
         (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, (const __half*)xb, x_inv_scale, pairs, items, n_items, h,
         (__nv_bfloat16*)hb, d, status);
     L.count();
@@ -900,24 +924,28 @@ static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const v
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
-                              uint32_t* status) {
+                              uint32_t* status, bool few_blocks) {
     if (max_items == 0) return cudaSuccess;
     if (type == QKM_TYPE_IQ3_XXS)
-        return gateup_mma_launch<QKM_TYPE_IQ3_XXS>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
+        // (512 producer threads do not help this format: its unpacking waits on table look-ups, not on issue slots)
+        return gateup_mma_launch<QKM_TYPE_IQ3_XXS, 256>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
     if (type == QKM_TYPE_Q8_0)
-        return gateup_mma_launch<QKM_TYPE_Q8_0>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
+        return few_blocks ? gateup_mma_launch<QKM_TYPE_Q8_0, 512>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status)
+                          : gateup_mma_launch<QKM_TYPE_Q8_0, 256>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
     return cudaErrorInvalidValue;
 }
 
 template <int FMT>
 static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const void* tiles, const void* hb,
                                    const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items,
-                                   const uint32_t* n_items, uint32_t max_items, float* contrib, uint32_t* status) {
+                                   const uint32_t* n_items, uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks) {
     const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + (FMT == QKM_TYPE_IQ4_XS ? 256 * 32 * 4 : 0) + 1024;
     cudaError_t e = cudaFuncSetAttribute(down_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     // routed experts: four row tiles per block (set-up amortised); the shared expert has few blocks, one each
+    // (a shard of few experts: one row tile per block as well, so that its blocks fill the machine)
     uint32_t row_tiles = FMT == QKM_TYPE_IQ4_XS ? 4u : 1u;
+    (void)few_blocks;
     while (row_tiles > 1 && (d.n_embd / 128) % row_tiles) row_tiles >>= 1;
     down_mma_kernel<FMT><<<(max_items + row_tiles - 1) / row_tiles, pf::kBlock, smem, L.stream>>>(
         (const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items, n_items, contrib, d, row_tiles, status);
@@ -927,12 +955,12 @@ static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const voi
 
 cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
                             const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
-                            uint32_t max_items, float* contrib, uint32_t* status) {
+                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks) {
     if (max_items == 0) return cudaSuccess;
     if (type == QKM_TYPE_IQ4_XS)
-        return down_mma_launch<QKM_TYPE_IQ4_XS>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status);
+        return down_mma_launch<QKM_TYPE_IQ4_XS>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status, few_blocks);
     if (type == QKM_TYPE_Q8_0)
-        return down_mma_launch<QKM_TYPE_Q8_0>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status);
+        return down_mma_launch<QKM_TYPE_Q8_0>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status, few_blocks);
     return cudaErrorInvalidValue;
 }
 

@@ -488,7 +488,7 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
                      const float* __restrict__ row_norm2, const float* __restrict__ gis,
                      const float* __restrict__ x, qkm_sel* __restrict__ sel, qkm_dims d,
                      int8_t* __restrict__ xplanes, float* __restrict__ xscale, float eps_terms, float eps_abs,
-                     GroupTail tail) {
+                     GroupTail tail, uint32_t n_parts, size_t part_stride) {
     extern __shared__ float s_x[];  // n_embd floats
     __shared__ __align__(16) double s_val[512];   // f64 logit of every candidate, -inf elsewhere
     __shared__ __align__(16) float s_log[512];
@@ -515,8 +515,14 @@ refine_select_kernel(const uint8_t* __restrict__ router, const void* __restrict_
         s_val[id1] = v1;
     } else {
         const float* lt = reinterpret_cast<const float*>(logits_any) + (size_t)t * d.n_expert;
-        l0 = (id0 < d.n_expert ? sane(lt[id0]) : kFloor) + 0.0f;  // + 0: -0 and +0 tie
-        l1 = (id1 < d.n_expert ? sane(lt[id1]) : kFloor) + 0.0f;
+        // the logits may arrive as n_parts partial sums over column ranges (split-K GEMM): added in order
+        float a0 = 0.f, a1 = 0.f;
+        for (uint32_t p = 0; p < n_parts; ++p) {
+            if (id0 < d.n_expert) a0 += lt[p * part_stride + id0];
+            if (id1 < d.n_expert) a1 += lt[p * part_stride + id1];
+        }
+        l0 = (id0 < d.n_expert ? sane(a0) : kFloor) + 0.0f;  // + 0: -0 and +0 tie
+        l1 = (id1 < d.n_expert ? sane(a1) : kFloor) + 0.0f;
         s_log[id0] = l0;
         s_log[id1] = l1;
         s_val[id0] = ninf;
@@ -752,7 +758,9 @@ bool route_select_plans(const qkm_dims& d, uint32_t n_tokens, size_t scratch_byt
 }
 
 size_t route_scratch_bytes(uint32_t n_tokens, uint32_t n_expert) {
-    const size_t f32_path = ((size_t)n_tokens * n_expert + n_expert) * sizeof(float);
+    // f32 logits (up to 8 partial sums over column ranges when the batch is small enough to split) + row norms
+    const size_t parts = n_tokens >= 128 && n_tokens <= 4096 ? 8 : 1;
+    const size_t f32_path = ((size_t)n_tokens * n_expert * parts + n_expert) * sizeof(float);
     const size_t f64_path = (size_t)(n_tokens < kExactMaxTokens ? n_tokens : kExactMaxTokens) * n_expert * sizeof(double);
     return f32_path > f64_path ? f32_path : f64_path;
 }
@@ -776,9 +784,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         cudaError_t e = launch_logits64(L, d, router_type, router, x, l64, n_tokens);
         if (e != cudaSuccess) return e;
         if (router_type == QKM_TYPE_F32)
-            e = launch_kernel(L, refine_select_kernel<QKM_TYPE_F32, true>, dim3(n_tokens), dim3(256), (size_t)d.n_embd * 4, (const uint8_t*)router, (const void*)l64, (const float*)nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
+            e = launch_kernel(L, refine_select_kernel<QKM_TYPE_F32, true>, dim3(n_tokens), dim3(256), (size_t)d.n_embd * 4, (const uint8_t*)router, (const void*)l64, (const float*)nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail, 1u, (size_t)0);
         else
-            e = launch_kernel(L, refine_select_kernel<QKM_TYPE_F16, true>, dim3(n_tokens), dim3(256), (size_t)d.n_embd * 4, (const uint8_t*)router, (const void*)l64, (const float*)nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail);
+            e = launch_kernel(L, refine_select_kernel<QKM_TYPE_F16, true>, dim3(n_tokens), dim3(256), (size_t)d.n_embd * 4, (const uint8_t*)router, (const void*)l64, (const float*)nullptr, gis, x, sel, d, xplanes, xscale, 0.f, 0.f, tail, 1u, (size_t)0);
         L.count();
         return e != cudaSuccess ? e : cudaGetLastError();
     }
@@ -787,16 +795,25 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
     float* norm2 = logits + (size_t)n_tokens * d.n_expert;
     const uint8_t* r = (const uint8_t*)router;
     float eps_terms, eps_abs = 0.f;
+    uint32_t n_parts = 1;
     if (x_f16 && x_f16_inv && status && n_tokens >= 128 && d.n_expert % 128 == 0 && d.n_embd <= 4096) {
-        // tensor cores, f16 operands: |error| <= 2^-9 |w| |x|, plus the flush of tiny router values
+        // tensor cores, f16 operands: |error| <= 2^-9 |w| |x|, plus the flush of tiny router values.
+        // Few output tiles: the columns are split over more blocks, partial logits side by side
+        // (summed by the selection kernel).
+        const uint32_t tiles = ((n_tokens + 127) / 128) * (d.n_expert / 128);
+        uint32_t splits = 1;
+        while (splits < 8 && tiles * splits * 2 <= 148u && (d.n_embd / 64) % (splits * 2) == 0 &&
+               ((size_t)n_tokens * d.n_expert * (splits * 2) + d.n_expert) * sizeof(float) <= scratch_bytes) splits *= 2;
+        norm2 = logits + (size_t)n_tokens * d.n_expert * splits;
         if (router_type == QKM_TYPE_F32)
             row_norm2_kernel<QKM_TYPE_F32><<<(d.n_expert + 7) / 8, 256, 0, L.stream>>>(r, norm2, d.n_expert, d.n_embd);
         else
             row_norm2_kernel<QKM_TYPE_F16><<<(d.n_expert + 7) / 8, 256, 0, L.stream>>>(r, norm2, d.n_expert, d.n_embd);
         L.count();
-        cudaError_t e = launch_logits_mma(L, d, router_type, router, x_f16, x_f16_inv, logits, n_tokens, status);
+        cudaError_t e = launch_logits_mma(L, d, router_type, router, x_f16, x_f16_inv, logits, n_tokens, status, splits);
         if (e != cudaSuccess) return e;
-        eps_terms = 32768.f;                       // 2^-9 / 2^-24
+        n_parts = splits;
+        eps_terms = 32768.f + (float)splits;       // 2^-9 / 2^-24, plus the additions of the partial sums
         eps_abs = 2.f * sqrtf((float)d.n_embd);    // 2^-25 per router element that f16 flushes
     } else if (n_tokens >= 1024) {   // many tokens: tiled GEMM, one chain of n_embd additions per logit
         const dim3 grid((d.n_expert + 63) / 64, (n_tokens + 63) / 64);
@@ -817,9 +834,9 @@ cudaError_t launch_route_select(const Launch& L, const qkm_dims& d, uint32_t rou
         eps_terms = (float)(d.n_embd / 32 + 8);
     }
     if (router_type == QKM_TYPE_F32)
-        refine_select_kernel<QKM_TYPE_F32, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs, GroupTail{});
+        refine_select_kernel<QKM_TYPE_F32, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs, GroupTail{}, n_parts, (size_t)n_tokens * d.n_expert);
     else
-        refine_select_kernel<QKM_TYPE_F16, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs, GroupTail{});
+        refine_select_kernel<QKM_TYPE_F16, false><<<n_tokens, 256, d.n_embd * 4, L.stream>>>(r, logits, norm2, gis, x, sel, d, xplanes, xscale, eps_terms, eps_abs, GroupTail{}, n_parts, (size_t)n_tokens * d.n_expert);
     L.count();
     return cudaGetLastError();
 }

@@ -60,8 +60,13 @@ class ExpertParallel:
         both = [int(v) for v in self.counts_dev.tolist()]
         send, recv = both[:W], both[W:]
         n_send, n_recv = sum(send), sum(recv)
-        if n_recv > self.max_recv:
-            raise RuntimeError(f"rank {self.rank}: {n_recv} rows arrive but buffers hold {self.max_recv}")
+        # an overflow is decided by all ranks together: a rank that raised alone would leave its
+        # peers blocked in the next collective
+        over = torch.tensor([max(0, n_recv - self.max_recv)], dtype=torch.int32, device=self.device)
+        dist.all_reduce(over, op=dist.ReduceOp.MAX, group=self.group)
+        if int(over.item()) > 0:
+            raise RuntimeError(f"rank {self.rank}: {n_recv} rows arrive here, the buffers hold {self.max_recv}; "
+                               f"the fullest rank is {int(over.item())} rows over (every rank raises)")
         self.last_counts = (send, recv)
         w1 = dist.all_to_all_single(self.xrecv[:n_recv], self.xsend[:n_send], recv, send, group=self.group, async_op=True)
         w2 = dist.all_to_all_single(self.selrecv[:n_recv], self.selsend[:n_send], recv, send, group=self.group, async_op=True)
@@ -86,7 +91,10 @@ class PeerExpertParallel:
     GPU and all ranks issuing the same sequence of calls.
 
     The engine must launch on the stream the process group's collectives synchronise with
-    (torch's current stream)."""
+    (torch's current stream): the constructor and every forward() point the engine at it.
+    After a device barrier's bounded wait has run out, y is undefined from that layer on until
+    the engine's sync() has reported the timeout; with `device_barrier=True` call `sync()` at the
+    end of a step (see `end_step`)."""
 
     HANDLE_BYTES = 192
 
@@ -96,6 +104,7 @@ class PeerExpertParallel:
         self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
         self.max_local, self.device = max_local_tokens, device
         self.device_barrier, self.timeout_ms = device_barrier, timeout_ms
+        self._follow_current_stream()
         engine.ep_peer_setup(self.world, self.rank, max_local_tokens)
         mine = torch.frombuffer(bytearray(engine.ep_peer_export()), dtype=torch.uint8).to(device)
         if mine.numel() != self.HANDLE_BYTES:
@@ -108,8 +117,20 @@ class PeerExpertParallel:
         self._word = torch.zeros(1, dtype=torch.int32, device=device)
         self.barrier()
 
+    def _follow_current_stream(self) -> None:
+        """The one-word all-reduces that order the phases run on torch's current stream; the
+        engine's kernels must run there too, or the barriers order nothing."""
+        if hasattr(self.engine, "set_stream") and torch.cuda.is_available() and torch.device(self.device).type == "cuda":
+            self.engine.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+
     def barrier(self) -> None:
         dist.all_reduce(self._word, group=self.group)
+
+    def end_step(self) -> None:
+        """End of a step with the library's own barriers: brings a barrier wait that ran out to
+        the host (raises the engine's timeout error); outputs since that layer are invalid."""
+        if self.device_barrier:
+            self.engine.sync()
 
     def forward(self, layer: int, x: torch.Tensor, n: int, y: torch.Tensor, slot_rows: int | None = None) -> None:
         """y[:n] = MoE layer `layer` of the n local rows x[:n].  All ranks call this together
@@ -118,6 +139,7 @@ class PeerExpertParallel:
         if n > rows or rows > self.max_local:
             raise ValueError(f"{n} local tokens / {rows} slot rows exceed the {self.max_local} this object was sized for")
         eng = self.engine
+        self._follow_current_stream()
         if self.device_barrier:
             eng.ep_peer_layer(layer, x, n, rows, y, self.timeout_ms)
             return
