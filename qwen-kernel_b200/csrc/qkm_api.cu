@@ -69,6 +69,7 @@ struct qkm_ctx {
     bool dec_ok = false;               // dims fit the fused decode kernels
     int8_t* planes8 = nullptr;         // [max_tokens][n_embd/256][8][256]
     uint8_t* lut_gu = nullptr;         // table images the decode kernels copy to shared memory
+    uint8_t* lut_pf = nullptr;         // table image of the prefill IQ3_XXS gate/up kernel
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
     // prefill (tcgen05) scratch, allocated on first use
@@ -124,7 +125,10 @@ struct qkm_ctx {
     Launch L() { return Launch{stream, &launches}; }
     // decode chain (logits -> selection -> gate/up -> down -> next layer's logits): each kernel is
     // launched as a programmatic dependent of the one before, so its scheduling and set-up overlap
-    // that kernel's tail.  Off unless QKM_PDL=1 is in the environment when the context is opened.
+    // that kernel's tail.  Off unless QKM_PDL=1 is in the environment when the context is opened:
+    // inside the captured decode graph the kernels already follow one another without a gap, and the
+    // persistent blocks leave an early block no room on an SM, so it measured no gain (75.5 us per
+    // layer at 16 slots either way).
     bool use_pdl = false;
     Launch Lchain() { return Launch{stream, &launches, use_pdl && !profiling}; }
 };
@@ -305,6 +309,15 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
         return nullptr;
     }
     *c->status_host = 0;
+    {
+        const Launch L0{nullptr, nullptr};
+        if ((e = cudaMalloc((void**)&c->lut_pf, gateup_iq3_table_bytes())) != cudaSuccess ||
+            (e = launch_gateup_iq3_table(L0, c->lut_pf)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
+            bail("qkm_open: prefill tables", cudaGetErrorString(e));
+            qkm_close(c);
+            return nullptr;
+        }
+    }
     if (cudaStreamCreateWithFlags(&c->side, cudaStreamNonBlocking) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_fork, cudaEventDisableTiming) != cudaSuccess ||
         cudaEventCreateWithFlags(&c->ev_join, cudaEventDisableTiming) != cudaSuccess ||
@@ -329,7 +342,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     void* scratch[] = {c->argmax_scratch, c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
-                       c->planes8, c->lut_gu,
+                       c->planes8, c->lut_gu, c->lut_pf,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
@@ -780,7 +793,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     }
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status));
+                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status, false, c->lut_pf));
     c->prof_mark("moe.gu");
     if (!ld.stream_ok) {
         // Q6_K down: the f32 kernels take over from h (per-pair contributions, shared down, fold)
@@ -1222,7 +1235,7 @@ static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv
     // a shard of few experts launches fewer blocks than the machine holds: faster blocks instead (see the launchers)
     const bool few_gu = c->ecount * rt_gu <= 2u * (uint32_t)c->n_sms, few_dn = c->ecount * rt_dn / 4 <= 2u * (uint32_t)c->n_sms;
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status, few_gu));
+                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status, few_gu, c->lut_pf));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
                                   c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn));
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));

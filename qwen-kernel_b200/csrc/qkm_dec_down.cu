@@ -130,7 +130,7 @@ decode_down_kernel(DownDecodeArgs a) {
         if (p_u >= u_hi) return;
         if (p_new_tok) {
             p_new_tok = false;
-            const uint32_t e = min(a.sel[p_tok].ids[slot], d.n_expert - 1);
+            const uint32_t e = min(__ldcg(&a.sel[p_tok].ids[slot]), d.n_expert - 1);   // (read before the wait below: L2, not a stale L1 line)
             p_src = a.tiles + ((size_t)e * mat_tiles + (size_t)kb * RT + 2 * p_pr) * kTileIq4;
             if (with_shared) p_sh = a.sh_tiles + ((size_t)(warp >> 3) * RT + 2 * p_pr) * kTileQ8 + dd::kShBlock * (warp & 7u);
         }
@@ -148,6 +148,10 @@ decode_down_kernel(DownDecodeArgs a) {
     };
     if (lane == 0)
         for (int s = 0; s < dd::kStages; ++s) issue(s);
+    // The first weight tiles are on their way (they depend on the selection only, which was final
+    // before the gate/up kernel released this one); h is that kernel's output.
+    pdl_wait();
+    pdl_trigger();
 
     // the codebook in four registers (kvalues_iq4nl as int8)
     const uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;

@@ -101,11 +101,11 @@ __device__ __forceinline__ void iq3_tile(uint32_t tb, uint32_t lane, uint32_t g,
     acc[0] = acc[1] = acc[2] = acc[3] = 0;
 #pragma unroll
     for (int sb = 0; sb < 8; ++sb) {
-        const uint32_t wa = idx_a[sb >> 1], wb = idx_b[sb >> 1];
-        const uint32_t s_lo = (sb & 1) ? 0x7624u : 0x7604u, s_hi = (sb & 1) ? 0x7634u : 0x7614u;
+        const uint32_t wa = idx_a[2 * (sb & 1) + (sb >> 2)], wb = idx_b[2 * (sb & 1) + (sb >> 2)];   // even sub-blocks in words 0,1; odd in 2,3
+        const uint32_t s_lo = (sb & 2) ? 0x7624u : 0x7604u, s_hi = (sb & 2) ? 0x7634u : 0x7614u;
         const uint32_t ga0 = lds32(prmt(wa, grid_c, s_lo)), ga1 = lds32(prmt(wa, grid_c, s_hi));
         const uint32_t gb0 = lds32(prmt(wb, grid_c, s_lo)), gb1 = lds32(prmt(wb, grid_c, s_hi));
-        const uint32_t xa = aux_a[sb], xb = aux_b[sb];
+        const uint32_t xa = aux_a[4 * (sb & 1) + (sb >> 1)], xb = aux_b[4 * (sb & 1) + (sb >> 1)];
         const uint2 ma = lds64((__funnelshift_l(xa, xa, rot) & 0xFE00u) | sign_c);
         const uint2 mb = lds64((__funnelshift_l(xb, xb, rot) & 0xFE00u) | sign_c);
         int c[4] = {0, 0, 0, 0};
@@ -170,6 +170,12 @@ decode_gateup_kernel(GateupDecodeArgs a) {
         mbar_expect_tx(tab_bar, dg::kTabBytes);
         for (uint32_t i = 0; i < 4; ++i) bulk_g2s(dg::kTab + i * 16384u, a.luts + i * 16384u, 16384u, tab_bar);
     }
+
+    // Up to here nothing depended on the router kernel, so a block scheduled early (programmatic
+    // dependent launch) has its barriers and table copy under way while that kernel's tail runs.  The
+    // next kernel is released only now: what it reads before its own wait (the selection) is then final.
+    pdl_wait();
+    pdl_trigger();
 
     // Every block groups the selection's pairs by expert itself (same lists everywhere).
     RankShared& S = *reinterpret_cast<RankShared*>(smem_raw + (dg::kRank - base));

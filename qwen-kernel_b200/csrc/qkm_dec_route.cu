@@ -43,6 +43,11 @@ route_decode_kernel(RouteDecodeArgs a) {
     const uint32_t n_pair_blocks = (d.n_expert + 1) / 2;                              // blocks along the experts
     const uint32_t n_logit_blocks = n_pair_blocks * ((T + rd::kTok - 1) / rd::kTok);  // times the token groups
 
+    // x is the output of the kernel before; the selection, planes and logits written here are still
+    // read by the previous layer's kernels until that kernel has ended
+    pdl_wait();
+    pdl_trigger();
+
     if (blockIdx.x >= n_logit_blocks) {
         // ---- one token: digit planes + shared gate ----------------------------------------------
         __shared__ float s_xm[8];

@@ -80,9 +80,9 @@ __device__ __forceinline__ void gu_tile(uint32_t tb, uint32_t lane, uint32_t g, 
         int acc[4] = {0, 0, 0, 0};
 #pragma unroll
         for (int sb = 0; sb < 8; ++sb) {
-            const uint32_t wa = idx_a[sb >> 1], wb = idx_b[sb >> 1];
+            const uint32_t wa = idx_a[2 * (sb & 1) + (sb >> 2)], wb = idx_b[2 * (sb & 1) + (sb >> 2)];   // even sub-blocks in words 0,1; odd in 2,3
             uint32_t a_lo, a_hi, b_lo, b_hi;  // table addresses of the two grid entries per row
-            if (sb & 1) {
+            if (sb & 2) {
                 a_lo = ((wa >> 9) & 0x7F80u) | grid_c;  a_hi = ((wa >> 17) & 0x7F80u) | grid_c;
                 b_lo = ((wb >> 9) & 0x7F80u) | grid_c;  b_hi = ((wb >> 17) & 0x7F80u) | grid_c;
             } else {
@@ -90,7 +90,7 @@ __device__ __forceinline__ void gu_tile(uint32_t tb, uint32_t lane, uint32_t g, 
                 b_lo = ((wb << 7) & 0x7F80u) | grid_c;  b_hi = ((wb >> 1) & 0x7F80u) | grid_c;
             }
             const uint32_t ga0 = lds32(a_lo), ga1 = lds32(a_hi), gb0 = lds32(b_lo), gb1 = lds32(b_hi);
-            const uint32_t xa = aux_a[sb], xb = aux_b[sb];
+            const uint32_t xa = aux_a[4 * (sb & 1) + (sb >> 1)], xb = aux_b[4 * (sb & 1) + (sb >> 1)];
             const uint2 ma = lds64((((xa >> (7 * t)) & 127u) << 8) | sign_c);
             const uint2 mb = lds64((((xb >> (7 * t)) & 127u) << 8) | sign_c);
             int c[4] = {0, 0, 0, 0};

@@ -126,7 +126,10 @@ cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* 
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
-                              uint32_t* status, bool few_blocks = false);   // few_blocks: the grid will not fill the machine
+                              uint32_t* status, bool few_blocks = false,   // few_blocks: the grid will not fill the machine
+                              const uint8_t* iq3_table = nullptr);         // IQ3_XXS: the table image (launch_gateup_iq3_table) selects the table-driven kernel
+size_t gateup_iq3_table_bytes();
+cudaError_t launch_gateup_iq3_table(const Launch& L, uint8_t* out);
 cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
                             const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
                             uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks = false);

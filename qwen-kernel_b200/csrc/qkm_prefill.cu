@@ -152,73 +152,6 @@ __device__ __forceinline__ uint32_t pack16(float a, float b) {
 }
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) { return pack16<false>(a, b); }
 
-// IQ3_XXS raw bytes of one thread's row.  The index pairs are fetched once per 256-column
-// block with full 16-byte loads (every fetched sector is used); the two aux words and the
-// scale per k-step.
-struct Iq3Idx { uint4 t[4]; };                       // group t: index pairs of sub-blocks 0..7
-struct Iq3Raw { uint32_t idxw[4]; uint2 aux2; uint32_t dbits; };
-
-__device__ __forceinline__ Iq3Idx load_iq3_idx(const uint8_t* __restrict__ tile, uint32_t r16) {
-    const uint32_t g = r16 & 7u, hf = r16 >> 3;
-    Iq3Idx r;
-#pragma unroll
-    for (int t = 0; t < 4; ++t) r.t[t] = *reinterpret_cast<const uint4*>(tile + hf * 512 + (4 * g + t) * 16);
-    return r;
-}
-__device__ __forceinline__ Iq3Raw load_iq3(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q, const Iq3Idx& ix) {
-    Iq3Raw r;
-    r.aux2 = *reinterpret_cast<const uint2*>(tile + 1024 + 256 * (q >> 1) + 16 * r16 + 8 * (q & 1u));
-    r.dbits = *reinterpret_cast<const uint16_t*>(tile + 1536 + 2 * r16);
-#pragma unroll
-    for (int t = 0; t < 4; ++t) {
-        const uint32_t w[4] = {ix.t[t].x, ix.t[t].y, ix.t[t].z, ix.t[t].w};
-        r.idxw[t] = q == 0 ? w[0] : q == 1 ? w[1] : q == 2 ? w[2] : w[3];
-    }
-    return r;
-}
-
-// Dequantise to f16: a table gives the four magnitudes of a grid entry as two f16 pairs,
-// another the four sign masks of a 7-bit sign code; one packed multiply by the sub-block
-// scale (f16) and one XOR per pair.  Two roundings of 2^-12 each.
-//   s_grid: [256][kGridReplicas] u32 (four magnitudes)     s_sign: [128] sign bytes (code | parity << 7)
-template <int J0, int J1>
-__device__ __forceinline__ void produce_iq3(const Iq3Raw& raw, const uint32_t* __restrict__ s_grid,
-                                            const uint8_t* __restrict__ s_sign, uint32_t lane, uint8_t* a_tile,
-                                            uint32_t row) {
-    const float d = f16_bits_to_f32(raw.dbits);
-#pragma unroll
-    for (int j = J0; j < J1; ++j) {        // sub-block 2q + j
-        const uint32_t aux = j ? raw.aux2.y : raw.aux2.x;
-        const __half2 db2 = __float2half2_rn(d * (0.5f + (float)(aux >> 28)) * 0.5f);
-        const __half2 nb2 = __hmul2(db2, __float2half2_rn(-1024.f));
-#pragma unroll
-        for (int t = 0; t < 4; ++t) {      // 8-element group t -> chunk 4j + t
-            const uint32_t pr = (raw.idxw[t] >> (16 * j)) & 0xFFFFu;
-            // four u8 magnitudes per grid word; byte b becomes the f16 1024 + b by placing it under
-            // the exponent byte 0x64, and one fused multiply-add scales it and removes the 1024
-            const uint32_t g0 = s_grid[(pr & 0xFFu) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
-            const uint32_t g1 = s_grid[(pr >> 8) * pf::kGridReplicas + (lane & (pf::kGridReplicas - 1))];
-            // sign byte of the 7-bit code (128-byte table: one word per bank, never a conflict),
-            // then bit i -> bit 7 of byte i by one multiply (the partial products do not overlap)
-            const uint32_t s8 = s_sign[(aux >> (7 * t)) & 127u];
-            const uint32_t m_lo = ((s8 & 0xFu) * 0x10204080u) & 0x80808080u;
-            const uint32_t m_hi = ((s8 >> 4) * 0x10204080u) & 0x80808080u;
-            uint4 o;
-            __half2 v;
-            uint32_t h;
-            h = __byte_perm(g0, 0x64646464u, 0x5140); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
-            o.x = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_lo, 0u, 0x1404);
-            h = __byte_perm(g0, 0x64646464u, 0x7362); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
-            o.y = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_lo, 0u, 0x3424);
-            h = __byte_perm(g1, 0x64646464u, 0x5140); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
-            o.z = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_hi, 0u, 0x1404);
-            h = __byte_perm(g1, 0x64646464u, 0x7362); v = __hfma2(*reinterpret_cast<__half2*>(&h), db2, nb2);
-            o.w = *reinterpret_cast<uint32_t*>(&v) ^ __byte_perm(m_hi, 0u, 0x3424);
-            *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + t)) = o;
-        }
-    }
-}
-
 // IQ4_XS: a quant byte holds two weights 16 columns apart (low and high nibble).  The table
 // maps a byte to both values as a bf16 pair; it is replicated per lane ([256][32] words, lane
 // = bank) so lookups never conflict.  s_pair_lane already points at this lane's column.
@@ -344,22 +277,17 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                   __nv_bfloat16* __restrict__ hb, qkm_dims d, uint32_t* __restrict__ status) {
     if (blockIdx.x >= *n_items_ptr) return;
     constexpr int kSt = pf::kStages;
-    constexpr int kTile = FMT == QKM_TYPE_IQ3_XXS ? kTileIq3 : kTileQ8;
+    static_assert(FMT == QKM_TYPE_Q8_0, "IQ3_XXS has its own kernel (gateup_iq3_kernel)");
+    constexpr int kTile = kTileQ8;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long s_bar[2 * kSt + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
     uint8_t* smem = reinterpret_cast<uint8_t*>(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
-    uint32_t* s_grid = reinterpret_cast<uint32_t*>(smem + kSt * 3 * pf::kTileBytes);
-    uint8_t* s_sign = reinterpret_cast<uint8_t*>(s_grid + 256 * pf::kGridReplicas);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     const MmaItem it = items[blockIdx.x];
     const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
     const uint32_t KB = d.n_embd / 256, RT16 = d.n_ff / 16, KS = d.n_embd / 64;
 
-    if (FMT == QKM_TYPE_IQ3_XXS) {
-        for (uint32_t i = tid; i < 256 * pf::kGridReplicas; i += PT) s_grid[i] = c_iq3_grid[i / pf::kGridReplicas];
-        if (tid < 128) s_sign[tid] = (uint8_t)signs8(tid);
-    }
     if (tid == 0) {
         for (int s = 0; s < kSt; ++s) {
             mbar_init(smem_addr(&s_bar[s]), 1);                            // empty: one commit
@@ -415,39 +343,18 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
         }
     } else {
     // ---- producer warps
-    Iq3Raw raw{};   // this thread's quant bytes of the current k-step, fetched one step ahead
-    Iq3Idx ix{};    // index pairs of the current 256-column block
-    if (FMT == QKM_TYPE_IQ3_XXS) {
-        ix = load_iq3_idx(wt + (size_t)rt16 * kTile, r16);
-        raw = load_iq3(wt + (size_t)rt16 * kTile, r16, 0, ix);
-    }
     BRegs breg = fetch_b<__half, PT>(s_row, n, n_mma, 0);
     for (uint32_t ks = 0; ks < KS; ++ks) {
         const uint32_t stage = ks % kSt;
-        Iq3Raw next{};
         BRegs bnext{};
-        if (ks + 1 < KS) {
-            if (FMT == QKM_TYPE_IQ3_XXS) {
-                const uint8_t* ntile = wt + ((size_t)((ks + 1) >> 2) * RT16 + rt16) * kTile;
-                if (((ks + 1) & 3u) == 0) ix = load_iq3_idx(ntile, r16);
-                next = load_iq3(ntile, r16, (ks + 1) & 3u, ix);
-            }
-            bnext = fetch_b<__half, PT>(s_row, n, n_mma, (ks + 1) * 64);
-        }
+        if (ks + 1 < KS) bnext = fetch_b<__half, PT>(s_row, n, n_mma, (ks + 1) * 64);
         if (ks >= (uint32_t)kSt)
             if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / kSt) - 1) & 1u)) timed_out = true;
         uint8_t* st = smem + stage * 3 * pf::kTileBytes;
         const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-        if (FMT == QKM_TYPE_IQ3_XXS) {
-            if (PT == 256) produce_iq3<0, 2>(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r);
-            else if (half == 0) produce_iq3<0, 1>(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r);
-            else produce_iq3<1, 2>(raw, s_grid, s_sign, lane, st + mat * pf::kTileBytes, r);
-            raw = next;
-        } else {
-            if (PT == 256) produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
-            else if (half == 0) produce_q8<true, 0, 1>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
-            else produce_q8<true, 1, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
-        }
+        if (PT == 256) produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+        else if (half == 0) produce_q8<true, 0, 1>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+        else produce_q8<true, 1, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
         store_b<PT>(st + 2 * pf::kTileBytes, breg, n_mma);
         breg = bnext;
         umma::fence_smem_to_async();
@@ -483,6 +390,354 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     const int any_timed_out = __syncthreads_or(timed_out ? 1 : 0);
     if (warp == 0) umma::tmem_dealloc(tmem, 256);
     if (any_timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+}
+
+// ---- gate/up + SwiGLU, IQ3_XXS, table-driven producers -------------------------------------------------
+// The same GEMM as gateup_mma_kernel<QKM_TYPE_IQ3_XXS>, same operands and the same bits out, with the
+// dequantisation cut to about two instructions per weight:
+//   * one 64 KB table image at shared address 0x10000, 256 rows of 256 bytes.  Bytes [0,128) of row i:
+//     the four magnitudes of grid entry i as f16, once per lane column (16 columns of 8 bytes: a
+//     64-bit load of a half-warp never conflicts).  Bytes [128,256) of row i: the sign masks of the
+//     8-weight sign code i & 127 - four words, bit 15 / bit 31 set for a negative weight - once per
+//     lane column (8 columns of 16 bytes: a 128-bit load of a quarter-warp never conflicts).
+//   * a look-up address is one byte permute: [column byte, index byte, 0x01, 0x00]; no shifts, masks
+//     or adds (the sign code's eighth bit is whatever follows it in the aux word: rows 128..255
+//     repeat the masks of rows 0..127).
+//   * per 8 weights: 3 permutes, 3 loads, 4 packed multiplies by the sub-block scale, 4 XORs, 1 store.
+//   * the dequantised weights never touch shared memory: a producer thread owns one weight row (one
+//     tensor-memory lane) and writes its 32 columns of the k-step with two tcgen05.st; the MMA takes
+//     its A operand from tensor memory (lane = row, two f16 per 32-bit column) and only the x tile
+//     (B) from shared memory.  Shared-memory bandwidth is then spent on the table look-ups and on B,
+//     not on writing and re-reading the 32 KB of A per k-step.
+// 512 producer threads (row, matrix, 32-column half of the k-step), one block per SM, three stages
+// of (gate and up weights: 64 tensor-memory columns; x tile: 16 KB of shared memory); a block walks
+// items blockIdx.x, + gridDim.x, ... and keeps the table.  The accumulators of the next item are
+// written only after every producer has read the previous item's (its arrival on the first
+// k-step's barrier comes after its epilogue).
+namespace pq {
+constexpr int kProducers = 512;
+constexpr int kBlock = kProducers + 32;
+constexpr int kStages = 3;
+constexpr uint32_t kTab = 0x10000u, kTabBytes = 0x10000u;
+constexpr uint32_t kStage0 = 0x20000u;                                   // x tiles follow the table
+constexpr uint32_t kEnd = kStage0 + kStages * pf::kTileBytes;
+constexpr uint32_t kTmemCols = 512, kTmemA = 256;                        // accumulators [0,256), A stages [256,448)
+__device__ __forceinline__ uint32_t stage_addr(uint32_t s) { return kStage0 + s * pf::kTileBytes; }
+}  // namespace pq
+
+size_t gateup_iq3_table_bytes() { return pq::kTabBytes; }
+
+__global__ void gateup_iq3_table_kernel(uint8_t* __restrict__ out) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;   // one 4-byte word each
+    if (i >= pq::kTabBytes / 4) return;
+    const uint32_t row = i >> 6, w = i & 63u;
+    uint32_t v;
+    if (w < 32) {   // column w / 2, magnitudes 2 (w & 1) and 2 (w & 1) + 1
+        const uint32_t g = c_iq3_grid[row] >> (16 * (w & 1u));
+        const __half2 m = __floats2half2_rn((float)(g & 0xFFu), (float)((g >> 8) & 0xFFu));
+        v = *reinterpret_cast<const uint32_t*>(&m);
+    } else {        // column (w - 32) / 4, weights 2j and 2j + 1 of the group
+        const uint32_t sg = signs8(row & 127u), j = w & 3u;
+        v = (((sg >> (2 * j)) & 1u) ? 0x8000u : 0u) | (((sg >> (2 * j + 1)) & 1u) ? 0x80000000u : 0u);
+    }
+    reinterpret_cast<uint32_t*>(out)[i] = v;
+}
+
+cudaError_t launch_gateup_iq3_table(const Launch& L, uint8_t* out) {
+    gateup_iq3_table_kernel<<<pq::kTabBytes / 4 / 256, 256, 0, L.stream>>>(out);
+    L.count();
+    return cudaGetLastError();
+}
+
+__device__ __forceinline__ uint32_t prmt_b32(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+__device__ __forceinline__ void named_sync(uint32_t id, uint32_t n_threads) {
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+__device__ __forceinline__ uint32_t hmul2_bits(uint32_t a, __half2 b) {
+    const __half2 v = __hmul2(*reinterpret_cast<const __half2*>(&a), b);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// 32 lanes x 8 consecutive 32-bit columns of tensor memory: thread i of the warp writes lane (base lane + i)
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t (&v)[8]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(taddr), "r"(v[0]), "r"(v[1]),
+                 "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// D[tmem] (+)= A[tmem] * B[smem]: A is 128 lanes (rows) x 8 columns (16 f16), B a K-major shared-memory tile
+__device__ __forceinline__ void mma_f16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+    const uint32_t acc = accumulate ? 1u : 0u;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(acc)
+        : "memory");
+}
+
+// The quant bytes one thread needs of its row's 256-column block, packed: ix[t][p] holds the index
+// pairs of group t for k-steps 2p (low half) and 2p + 1 (high half) of the thread's 32-column
+// half j; ax[q] is the aux word of sub-block 2q + j.
+struct Iq3Block { uint32_t ix[4][2]; uint32_t ax[4]; uint32_t dbits; };
+__device__ __forceinline__ Iq3Block load_iq3_block(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t j) {
+    const uint32_t g = r16 & 7u, hf = r16 >> 3;
+    Iq3Block b;
+#pragma unroll
+    for (int t = 0; t < 4; ++t) {   // the tile keeps the even sub-blocks' pairs in the first 8 bytes, the odd ones' in the last 8
+        const uint2 v = *reinterpret_cast<const uint2*>(tile + hf * 512 + (4 * g + t) * 16 + 8 * j);
+        b.ix[t][0] = v.x; b.ix[t][1] = v.y;
+    }
+    const uint4 a = *reinterpret_cast<const uint4*>(tile + 1024 + 256 * j + 16 * r16);
+    b.ax[0] = a.x; b.ax[1] = a.y; b.ax[2] = a.z; b.ax[3] = a.w;
+    b.dbits = *reinterpret_cast<const uint16_t*>(tile + 1536 + 2 * r16);
+    return b;
+}
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, uint32_t src_bytes) {   // src_bytes 0: zero fill
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cp_async_wait_all_but_one() { asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+
+__global__ void __launch_bounds__(pq::kBlock, 1)
+gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restrict__ up_tiles,
+                  const __half* __restrict__ xb, const float* __restrict__ x_inv_scale,
+                  const uint32_t* __restrict__ pairs, const MmaItem* __restrict__ items,
+                  const uint32_t* __restrict__ n_items_ptr, float* __restrict__ h,
+                  __nv_bfloat16* __restrict__ hb, qkm_dims d, const uint8_t* __restrict__ table,
+                  uint32_t* __restrict__ status) {
+    constexpr int kSt = pq::kStages, PT = pq::kProducers;
+    const uint32_t n_items = *n_items_ptr;
+    if (blockIdx.x >= n_items) return;
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    __shared__ __align__(8) unsigned long long s_bar[2 * kSt + 2];  // empty[stage], full[stage], done, table
+    __shared__ uint32_t s_tmem;
+    __shared__ float s_inv[pf::kNT];
+    __shared__ uint32_t s_hrow[pf::kNT];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    {   // the fixed addresses must lie inside the dynamic area
+        const uint32_t dyn_base = smem_addr(smem_dyn);
+        uint32_t dyn_size;
+        asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+        if (dyn_base > pq::kTab || dyn_base + dyn_size < pq::kEnd) {
+            if (tid == 0) atomicExch(status, (uint32_t)kStatusBadLayout);
+            return;
+        }
+    }
+    const uint32_t KB = d.n_embd / 256, RT16 = d.n_ff / 16, KS = d.n_embd / 64;
+    const uint32_t bar_empty = smem_addr(&s_bar[0]), bar_full = smem_addr(&s_bar[kSt]);
+    const uint32_t bar_done = smem_addr(&s_bar[2 * kSt]), bar_tab = smem_addr(&s_bar[2 * kSt + 1]);
+
+    if (tid == 0) {
+        for (int s = 0; s < kSt; ++s) {
+            mbar_init(bar_empty + 8 * s, 1);     // one commit
+            mbar_init(bar_full + 8 * s, PT / 32); // one arrival per producer warp
+        }
+        mbar_init(bar_done, 1);
+        mbar_init(bar_tab, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), pq::kTmemCols); umma::tmem_relinquish(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    if (tid == 0) {
+        mbar_expect_tx(bar_tab, pq::kTabBytes);
+        for (uint32_t i = 0; i < 4; ++i) bulk_g2s(pq::kTab + i * 16384u, table + i * 16384u, 16384u, bar_tab);
+    }
+    const uint32_t tmem = s_tmem;
+    bool timed_out = false;
+
+    if (tid >= PT) {
+        // ---- MMA issuer warp: the whole warp walks the loop (addresses stay warp-uniform), one
+        // elected lane issues
+        {
+            const bool leader = umma::elect_one();
+            uint32_t stage = 0, phase = 0;
+            for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x) {
+                const uint32_t idesc = umma::instr_desc_f16((items[item].n + 15u) & ~15u);
+                for (uint32_t ks = 0; ks < KS; ++ks) {
+                    if (!mbar_wait_bounded(bar_full + 8 * stage, phase)) timed_out = true;
+                    umma::fence_after_sync();
+                    const uint64_t d_b = umma::smem_desc(pq::stage_addr(stage));
+                    const uint32_t t_g = tmem + pq::kTmemA + stage * 64u, t_u = t_g + 32u;
+                    if (leader) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {   // 16 columns of K further: 8 tensor-memory columns, 32 bytes of the x tile
+                            const bool acc = (ks | (uint32_t)j) != 0;
+                            mma_f16_ts(tmem, t_g + 8 * j, d_b + 2 * j, idesc, acc);
+                            mma_f16_ts(tmem + 128, t_u + 8 * j, d_b + 2 * j, idesc, acc);
+                        }
+                        umma::commit(bar_empty + 8 * stage);
+                        if (ks + 1 == KS) umma::commit(bar_done);
+                    }
+                    __syncwarp();
+                    if (++stage == (uint32_t)kSt) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else {
+    // ---- producer warps: thread = (row r, matrix, 32-column half j of each k-step)
+    const uint32_t r = tid & 127u, mat = (tid >> 7) & 1u, j = tid >> 8;
+    const uint32_t mconst = 0x00010000u | ((lane & 15u) * 8u);
+    const uint32_t sconst = 0x00010000u | (128u + (lane & 7u) * 16u);
+    // this thread's 16 columns of its tensor-memory lane (row r): matrix, then the 32-column half
+    const uint32_t a_lane = tmem + ((r & ~31u) << 16) + pq::kTmemA + mat * 32u + j * 16u;
+    // N operand: chunks tid and tid + 512 of the x tile (row = chunk / 8), copied asynchronously
+    const uint32_t b_row0 = tid >> 3, b_row1 = b_row0 + 64, b_c = tid & 7u;
+    const uint32_t b_off0 = umma::sw128_chunk(b_row0, b_c), b_off1 = umma::sw128_chunk(b_row1, b_c);
+    if (!mbar_wait_bounded(bar_tab, 0)) timed_out = true;
+
+    uint32_t stage = 0, phase = 0, gs = 0, iter = 0;
+    for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
+        const MmaItem it = items[item];
+        const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
+        const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
+        const uint8_t* wt = (mat ? up_tiles : gate_tiles) + ((size_t)it.expert * KB * RT16 + rt16) * kTileIq3;
+        Iq3Block cur = load_iq3_block(wt, r16, j);
+        // the x rows of this thread's two chunks (rows >= n are zero-filled, rows >= n_mma not written)
+        const __half* b_src0 = xb + 8 * b_c;
+        const __half* b_src1 = b_src0;
+        if (b_row0 < n) b_src0 += (size_t)(pairs[it.pair_off + b_row0] >> 4) * d.n_embd;
+        if (b_row1 < n) b_src1 += (size_t)(pairs[it.pair_off + b_row1] >> 4) * d.n_embd;
+        const uint32_t b_sz0 = b_row0 < n ? 16u : 0u, b_sz1 = b_row1 < n ? 16u : 0u;
+        const bool b_do0 = b_row0 < n_mma, b_do1 = b_row1 < n_mma;
+        // per column (pair) of this item: the scale that undoes its row's power-of-two scaling,
+        // and where its h row goes in the [token][slot] layout
+        named_sync(1, PT);   // the previous item's epilogue has read these
+        for (uint32_t i = tid; i < n; i += PT) {
+            const uint32_t pr = pairs[it.pair_off + i], tok = pr >> 4;
+            s_inv[i] = x_inv_scale[tok];
+            s_hrow[i] = tok * (d.n_used + 1) + (pr & 15u);
+        }
+        named_sync(1, PT);
+        // the first k-step's x tile
+        if (gs >= (uint32_t)kSt)
+            if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u)) timed_out = true;
+        {
+            const uint32_t st = pq::stage_addr(stage);
+            if (b_do0) cp_async16(st + b_off0, b_src0, b_sz0);
+            if (b_do1) cp_async16(st + b_off1, b_src1, b_sz1);
+            cp_async_commit();
+        }
+        for (uint32_t kb = 0; kb < KB; ++kb) {
+            Iq3Block nxt = cur;
+            if (kb + 1 < KB) nxt = load_iq3_block(wt + (size_t)(kb + 1) * RT16 * kTileIq3, r16, j);
+            const float dd = f16_bits_to_f32(cur.dbits);
+            const float d2 = dd * 0.5f, d4 = dd * 0.25f;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t ks = kb * 4 + q;
+                const uint32_t st = pq::stage_addr(stage);
+                // the next k-step's x tile goes to the next stage, once the MMAs that read it are done
+                uint32_t stage1 = stage + 1, phase1 = phase;
+                if (stage1 == (uint32_t)kSt) { stage1 = 0; phase1 ^= 1u; }
+                if (ks + 1 < KS) {
+                    if (gs + 1 >= (uint32_t)kSt)
+                        if (!mbar_wait_bounded(bar_empty + 8 * stage1, phase1 ^ 1u)) timed_out = true;
+                    const uint32_t st1 = pq::stage_addr(stage1);
+                    if (b_do0) cp_async16(st1 + b_off0, b_src0 + (ks + 1) * 64, b_sz0);
+                    if (b_do1) cp_async16(st1 + b_off1, b_src1 + (ks + 1) * 64, b_sz1);
+                }
+                cp_async_commit();
+                // sub-block 2q + j: scale d (2s + 1) / 4, exact in f32, one rounding to f16
+                const uint32_t aux = cur.ax[q];
+                const float sf = __uint_as_float(0x4B000000u | (aux >> 28)) - 8388608.f;
+                const __half2 db2 = __float2half2_rn(fmaf(sf, d2, d4));
+                const uint32_t sel_a = (q & 1) ? 0x7624u : 0x7604u, sel_b = (q & 1) ? 0x7634u : 0x7614u;
+#pragma unroll
+                for (int tp = 0; tp < 4; tp += 2) {   // two 8-weight groups at a time: all six look-ups first
+                    uint2 m0[2], m1[2];
+                    uint4 sg[2];
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        const int t = tp + u;
+                        const uint32_t w = cur.ix[t][q >> 1];
+                        m0[u] = lds64(prmt_b32(w, mconst, sel_a));
+                        m1[u] = lds64(prmt_b32(w, mconst, sel_b));
+                        sg[u] = lds128(prmt_b32(t ? aux >> (7 * t) : aux, sconst, 0x7604u));
+                    }
+                    uint32_t o[8];   // groups tp, tp + 1 -> columns 4 tp .. 4 tp + 7 of the thread's 16
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        o[4 * u + 0] = hmul2_bits(m0[u].x, db2) ^ sg[u].x;
+                        o[4 * u + 1] = hmul2_bits(m0[u].y, db2) ^ sg[u].y;
+                        o[4 * u + 2] = hmul2_bits(m1[u].x, db2) ^ sg[u].z;
+                        o[4 * u + 3] = hmul2_bits(m1[u].y, db2) ^ sg[u].w;
+                    }
+                    tmem_st8(a_lane + stage * 64u + 4 * tp, o);
+                }
+                tmem_st_wait();
+                cp_async_wait_all_but_one();   // this k-step's x tile has landed (the next one's may be in flight)
+                umma::fence_smem_to_async();   // the x tile (generic-proxy writes) before the tensor core reads it
+                umma::fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_full + 8 * stage);
+                ++gs;
+                stage = stage1; phase = phase1;
+            }
+            cur = nxt;
+        }
+        if (!mbar_wait_bounded(bar_done, iter & 1u)) timed_out = true;
+        umma::fence_after_sync();
+
+        // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) and every fourth 16-column block
+        {
+            const uint32_t lg = warp & 3u, row = 32 * lg + lane;
+            const uint32_t r_ff = it.rt * 128u + row;
+            for (uint32_t cb = warp >> 2; cb < n_mma / 16; cb += PT / 128) {
+                uint32_t vg[16], vu[16];
+                umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, vg);
+                umma::tmem_ld16(tmem + ((32 * lg) << 16) + 128 + cb * 16, vu);
+                umma::tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t col = cb * 16 + i;
+                    if (col < n) {
+                        const float us = s_inv[col];   // undo the per-token power-of-two scale of x
+                        const float hv = swiglu(__uint_as_float(vg[i]) * us, __uint_as_float(vu[i]) * us);
+                        hb[(size_t)(it.pair_off + col) * d.n_ff + r_ff] = __float2bfloat16_rn(hv);
+                        h[(size_t)s_hrow[col] * d.n_ff + r_ff] = hv;
+                    }
+                }
+            }
+            umma::fence_before_sync();   // the accumulators are read before this thread's next arrival
+        }
+    }
+    }  // producer / epilogue warps
+    umma::fence_before_sync();
+    const int any_timed_out = __syncthreads_or(timed_out ? 1 : 0);
+    if (warp == 0) umma::tmem_dealloc(tmem, pq::kTmemCols);
+    if (any_timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+}
+
+static cudaError_t gateup_iq3_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
+                                     const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
+                                     const uint32_t* n_items, uint32_t max_items, float* h, void* hb, const uint8_t* table,
+                                     uint32_t* status) {
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n_sms = v;
+    }
+    const size_t smem = pq::kEnd;   // reaches from wherever the dynamic area starts to the end of the fixed layout
+    cudaError_t e = cudaFuncSetAttribute(gateup_iq3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const uint32_t grid = max_items < (uint32_t)n_sms ? max_items : (uint32_t)n_sms;
+    gateup_iq3_kernel<<<grid, pq::kBlock, smem, L.stream>>>(
+        (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, (const __half*)xb, x_inv_scale, pairs, items, n_items, h,
+        (__nv_bfloat16*)hb, d, table, status);
+    L.count();
+    return cudaGetLastError();
 }
 
 // ---- down -------------------------------------------------------------------------------------------------
@@ -633,7 +888,6 @@ constexpr int kLgDepth = 3;    // k-steps of asynchronous copies in flight
 __device__ __forceinline__ void cp_async16(uint32_t smem_dst, const void* gsrc) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_dst), "l"(gsrc) : "memory");
 }
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -911,7 +1165,7 @@ template <int FMT, int PT>
 static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
                                      const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
                                      const uint32_t* n_items, uint32_t max_items, float* h, void* hb, uint32_t* status) {
-    const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 256 * pf::kGridReplicas * 4 + 128 + 1024;
+    const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 1024;
     cudaError_t e = cudaFuncSetAttribute(gateup_mma_kernel<FMT, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     gateup_mma_kernel<FMT, PT><<<max_items, PT + 32, smem, L.stream>>>(
@@ -924,11 +1178,12 @@ static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const v
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
-                              uint32_t* status, bool few_blocks) {
+                              uint32_t* status, bool few_blocks, const uint8_t* iq3_table) {
     if (max_items == 0) return cudaSuccess;
-    if (type == QKM_TYPE_IQ3_XXS)
-        // (512 producer threads do not help this format: its unpacking waits on table look-ups, not on issue slots)
-        return gateup_mma_launch<QKM_TYPE_IQ3_XXS, 256>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
+    if (type == QKM_TYPE_IQ3_XXS) {
+        if (!iq3_table) return cudaErrorInvalidValue;
+        return gateup_iq3_launch(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, iq3_table, status);
+    }
     if (type == QKM_TYPE_Q8_0)
         return few_blocks ? gateup_mma_launch<QKM_TYPE_Q8_0, 512>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status)
                           : gateup_mma_launch<QKM_TYPE_Q8_0, 256>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);

@@ -28,13 +28,15 @@ __global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restri
     if (TYPE == QKM_TYPE_IQ3_XXS) {
         if (o < 1024) {
             const uint32_t h = o >> 9, lane = (o >> 4) & 31u, b = o & 15u;
-            const uint32_t g = lane >> 2, t = lane & 3u, ib = b >> 1;
+            const uint32_t g = lane >> 2, t = lane & 3u;
+            const uint32_t ib = 2 * ((b & 7u) >> 1) + (b >> 3);   // even sub-blocks first, then the odd ones
             row_in_tile = g + 8 * h;
             off = 2 + 8 * ib + 2 * t + (b & 1u);
-        } else if (o < 1536) {   // aux words: [half of the sub-blocks][row][16 B]
+        } else if (o < 1536) {   // aux words: [parity of the sub-block][row][4 words]
             const uint32_t q = o - 1024;
+            const uint32_t ib = 2 * ((q & 15u) >> 2) + (q >> 8);
             row_in_tile = (q >> 4) & 15u;
-            off = 2 + 64 + 16 * (q >> 8) + (q & 15u);
+            off = 2 + 64 + 4 * ib + (q & 3u);
         } else {
             row_in_tile = (o - 1536) >> 1;
             off = (o - 1536) & 1u;

@@ -16,10 +16,13 @@
 //   IQ3_XXS (block: d f16 | qs[64] grid indices | 8 aux words, src/quants.h:115-119)
 //     [   0,1024)  index pairs: half h (row g + 8h), lane -> 16 B = for each of the 8
 //                  sub-blocks the two grid indices of 8-element group t
-//                  (raw qs[8*ib + 2*t], qs[8*ib + 2*t + 1]); address h*512 + lane*16
+//                  (raw qs[8*ib + 2*t], qs[8*ib + 2*t + 1]), the even sub-blocks 0,2,4,6 in
+//                  the first 8 bytes and the odd ones in the last 8 (a prefill thread owns one
+//                  32-column half of every 64-column k-step: one 8-byte load); address
+//                  h*512 + lane*16
 //     [1024,1536)  aux words (4 x 7 sign bits + 4 scale bits each), unchanged, as two halves:
-//                  words 4*hf .. 4*hf+3 (sub-blocks 4*hf .. 4*hf+3) of row r at
-//                  1024 + 256*hf + 16*r, so the 16-byte loads of eight rows g (or g+8) hit
+//                  the words of sub-blocks par, 2+par, 4+par, 6+par of row r at
+//                  1024 + 256*par + 16*r, so the 16-byte loads of eight rows g (or g+8) hit
 //                  eight consecutive 16-byte slots
 //     [1536,1568)  d[16] f16
 //   IQ4_XS (block: d f16 | scales_h u16 | scales_l[4] | qs[128], src/quants.h:107-113)

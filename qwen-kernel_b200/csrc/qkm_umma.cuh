@@ -32,6 +32,19 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t smem_byte_addr) {
     return d;
 }
 
+// true in exactly one lane of the (converged) warp
+__device__ __forceinline__ bool elect_one() {
+    uint32_t p;
+    asm volatile(
+        "{\n"
+        ".reg .pred P1;\n"
+        "elect.sync _|P1, 0xFFFFFFFF;\n"
+        "selp.u32 %0, 1, 0, P1;\n"
+        "}\n"
+        : "=r"(p));
+    return p != 0;
+}
+
 // instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n (multiple of 16)
 __device__ __forceinline__ uint32_t instr_desc_bf16(uint32_t n) {
     uint32_t d = 0;
