@@ -793,7 +793,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     }
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status, false, c->lut_pf));
+                                    c->n_items, tiles_now * rt_gu, ld.stream_ok ? nullptr : c->h, c->hb, c->status, false, c->lut_pf));   // f32 h only where the f32 down kernels follow
     c->prof_mark("moe.gu");
     if (!ld.stream_ok) {
         // Q6_K down: the f32 kernels take over from h (per-pair contributions, shared down, fold)
@@ -1235,7 +1235,7 @@ static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv
     // a shard of few experts launches fewer blocks than the machine holds: faster blocks instead (see the launchers)
     const bool few_gu = c->ecount * rt_gu <= 2u * (uint32_t)c->n_sms, few_dn = c->ecount * rt_dn / 4 <= 2u * (uint32_t)c->n_sms;
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, c->h, c->hb, c->status, few_gu, c->lut_pf));
+                                    c->n_items, tiles_now * rt_gu, ld.stream_ok ? nullptr : c->h, c->hb, c->status, few_gu, c->lut_pf));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
                                   c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn));
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));

@@ -520,8 +520,8 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long s_bar[2 * kSt + 2];  // empty[stage], full[stage], done, table
     __shared__ uint32_t s_tmem;
-    __shared__ float s_inv[pf::kNT];
-    __shared__ uint32_t s_hrow[pf::kNT];
+    __shared__ float s_inv[2][pf::kNT];
+    __shared__ uint32_t s_hrow[2][pf::kNT];
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
     {   // the fixed addresses must lie inside the dynamic area
         const uint32_t dyn_base = smem_addr(smem_dyn);
@@ -596,29 +596,50 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
     const uint32_t b_off0 = umma::sw128_chunk(b_row0, b_c), b_off1 = umma::sw128_chunk(b_row1, b_c);
     if (!mbar_wait_bounded(bar_tab, 0)) timed_out = true;
 
+    // What an item needs before its first k-step - its record, the first weight bytes, the x rows of
+    // this thread's two chunks, the per-column scale and h offset - is fetched while the item
+    // before it drains (MMA tail and epilogue); s_inv / s_hrow are double-buffered for that.
+    struct ItemHead {
+        MmaItem it;
+        Iq3Block blk;
+        const uint8_t* wt;
+        const __half* b_src0;
+        const __half* b_src1;
+        uint32_t r16;
+    };
+    auto fetch_head = [&](uint32_t item, uint32_t buf) -> ItemHead {
+        ItemHead hd;
+        hd.it = items[item];
+        const uint32_t rowidx = hd.it.rt * 128u + r;
+        hd.r16 = rowidx & 15u;
+        hd.wt = (mat ? up_tiles : gate_tiles) + ((size_t)hd.it.expert * KB * RT16 + (rowidx >> 4)) * kTileIq3;
+        hd.blk = load_iq3_block(hd.wt, hd.r16, j);
+        // rows >= n are zero-filled, rows >= n_mma not written
+        hd.b_src0 = xb + 8 * b_c;
+        hd.b_src1 = hd.b_src0;
+        if (b_row0 < hd.it.n) hd.b_src0 += (size_t)(pairs[hd.it.pair_off + b_row0] >> 4) * d.n_embd;
+        if (b_row1 < hd.it.n) hd.b_src1 += (size_t)(pairs[hd.it.pair_off + b_row1] >> 4) * d.n_embd;
+        for (uint32_t i = tid; i < hd.it.n; i += PT) {
+            const uint32_t pr = pairs[hd.it.pair_off + i], tok = pr >> 4;
+            s_inv[buf][i] = x_inv_scale[tok];
+            s_hrow[buf][i] = (tok * (d.n_used + 1) + (pr & 15u)) * d.n_ff;   // element offset of the pair's h row
+        }
+        return hd;
+    };
     uint32_t stage = 0, phase = 0, gs = 0, iter = 0;
+    ItemHead head = fetch_head(blockIdx.x, 0);
+    named_sync(1, PT);
     for (uint32_t item = blockIdx.x; item < n_items; item += gridDim.x, ++iter) {
-        const MmaItem it = items[item];
+        const MmaItem it = head.it;
         const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
-        const uint32_t rowidx = it.rt * 128u + r, rt16 = rowidx >> 4, r16 = rowidx & 15u;
-        const uint8_t* wt = (mat ? up_tiles : gate_tiles) + ((size_t)it.expert * KB * RT16 + rt16) * kTileIq3;
-        Iq3Block cur = load_iq3_block(wt, r16, j);
-        // the x rows of this thread's two chunks (rows >= n are zero-filled, rows >= n_mma not written)
-        const __half* b_src0 = xb + 8 * b_c;
-        const __half* b_src1 = b_src0;
-        if (b_row0 < n) b_src0 += (size_t)(pairs[it.pair_off + b_row0] >> 4) * d.n_embd;
-        if (b_row1 < n) b_src1 += (size_t)(pairs[it.pair_off + b_row1] >> 4) * d.n_embd;
+        const uint32_t r16 = head.r16;
+        const uint8_t* wt = head.wt;
+        Iq3Block cur = head.blk;
+        const __half* b_src0 = head.b_src0;
+        const __half* b_src1 = head.b_src1;
         const uint32_t b_sz0 = b_row0 < n ? 16u : 0u, b_sz1 = b_row1 < n ? 16u : 0u;
         const bool b_do0 = b_row0 < n_mma, b_do1 = b_row1 < n_mma;
-        // per column (pair) of this item: the scale that undoes its row's power-of-two scaling,
-        // and where its h row goes in the [token][slot] layout
-        named_sync(1, PT);   // the previous item's epilogue has read these
-        for (uint32_t i = tid; i < n; i += PT) {
-            const uint32_t pr = pairs[it.pair_off + i], tok = pr >> 4;
-            s_inv[i] = x_inv_scale[tok];
-            s_hrow[i] = tok * (d.n_used + 1) + (pr & 15u);
-        }
-        named_sync(1, PT);
+        const uint32_t buf = iter & 1u;
         // the first k-step's x tile
         if (gs >= (uint32_t)kSt)
             if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u)) timed_out = true;
@@ -686,10 +707,13 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
             }
             cur = nxt;
         }
+        if (item + gridDim.x < n_items) head = fetch_head(item + gridDim.x, buf ^ 1u);
         if (!mbar_wait_bounded(bar_done, iter & 1u)) timed_out = true;
         umma::fence_after_sync();
 
-        // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) and every fourth 16-column block
+        // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) and every fourth 16-column block.
+        // silu with the fast exponential and division: their error (a few ulp) is far below the f16
+        // rounding of the operands, and the epilogue is a fifth of the kernel's instructions otherwise
         {
             const uint32_t lg = warp & 3u, row = 32 * lg + lane;
             const uint32_t r_ff = it.rt * 128u + row;
@@ -698,19 +722,22 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                 umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, vg);
                 umma::tmem_ld16(tmem + ((32 * lg) << 16) + 128 + cb * 16, vu);
                 umma::tmem_ld_wait();
+                __nv_bfloat16* hbp = hb + (size_t)(it.pair_off + cb * 16) * d.n_ff + r_ff;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const uint32_t col = cb * 16 + i;
                     if (col < n) {
-                        const float us = s_inv[col];   // undo the per-token power-of-two scale of x
-                        const float hv = swiglu(__uint_as_float(vg[i]) * us, __uint_as_float(vu[i]) * us);
-                        hb[(size_t)(it.pair_off + col) * d.n_ff + r_ff] = __float2bfloat16_rn(hv);
-                        h[(size_t)s_hrow[col] * d.n_ff + r_ff] = hv;
+                        const float us = s_inv[buf][col];   // undo the per-token power-of-two scale of x
+                        const float g = __uint_as_float(vg[i]) * us, u = __uint_as_float(vu[i]) * us;
+                        const float hv = __fdividef(g, 1.0f + __expf(-g)) * u;
+                        hbp[(size_t)i * d.n_ff] = __float2bfloat16_rn(hv);
+                        if (h) h[(size_t)s_hrow[buf][col] + r_ff] = hv;
                     }
                 }
             }
             umma::fence_before_sync();   // the accumulators are read before this thread's next arrival
         }
+        named_sync(1, PT);   // the next item's columns are written, this item's are read
     }
     }  // producer / epilogue warps
     umma::fence_before_sync();
