@@ -70,6 +70,7 @@ struct qkm_ctx {
     int8_t* planes8 = nullptr;         // [max_tokens][n_embd/256][8][256]
     uint8_t* lut_gu = nullptr;         // table images the decode kernels copy to shared memory
     uint8_t* lut_pf = nullptr;         // table image of the prefill IQ3_XXS gate/up kernel
+    uint8_t* lut_dn = nullptr;         // table image of the prefill IQ4_XS down kernel
     uint32_t* status_host = nullptr;  // pinned mirror
     bool shapes_stream_ok = false;
     // prefill (tcgen05) scratch, allocated on first use
@@ -312,7 +313,9 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
     {
         const Launch L0{nullptr, nullptr};
         if ((e = cudaMalloc((void**)&c->lut_pf, gateup_iq3_table_bytes())) != cudaSuccess ||
-            (e = launch_gateup_iq3_table(L0, c->lut_pf)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
+            (e = launch_gateup_iq3_table(L0, c->lut_pf)) != cudaSuccess ||
+            (e = cudaMalloc((void**)&c->lut_dn, down_iq4_table_bytes())) != cudaSuccess ||
+            (e = launch_down_iq4_table(L0, c->lut_dn)) != cudaSuccess || (e = cudaDeviceSynchronize()) != cudaSuccess) {
             bail("qkm_open: prefill tables", cudaGetErrorString(e));
             qkm_close(c);
             return nullptr;
@@ -342,7 +345,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     void* scratch[] = {c->argmax_scratch, c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
-                       c->planes8, c->lut_gu, c->lut_pf,
+                       c->planes8, c->lut_gu, c->lut_pf, c->lut_dn,
                        c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
@@ -808,7 +811,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
         return QKM_OK;
     }
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, c->sel, c->pairs, c->mma_items[1],
-                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status));
+                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, false, c->lut_dn));
     c->prof_mark("moe.dn");
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, y, n));
@@ -1237,7 +1240,7 @@ static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
                                     c->n_items, tiles_now * rt_gu, ld.stream_ok ? nullptr : c->h, c->hb, c->status, few_gu, c->lut_pf));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
-                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn));
+                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn, c->lut_dn));
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     if (slot_rows_peer)
         QKM_LAUNCH(c, launch_fold_pairs_peer(c->L(), d, c->contrib_p, c->pos_of, c->pm_peers, slot_rows_peer, c->pm_rank, c->pm_ranks));

@@ -132,7 +132,10 @@ size_t gateup_iq3_table_bytes();
 cudaError_t launch_gateup_iq3_table(const Launch& L, uint8_t* out);
 cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
                             const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
-                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks = false);
+                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks = false,
+                            const uint8_t* iq4_table = nullptr);   // IQ4_XS: the table image (launch_down_iq4_table) selects the table-driven kernel
+size_t down_iq4_table_bytes();
+cudaError_t launch_down_iq4_table(const Launch& L, uint8_t* out);
 cudaError_t launch_fold_pairs(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,
                               float* y, uint32_t n_tokens);
 

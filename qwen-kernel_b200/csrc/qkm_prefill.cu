@@ -1217,6 +1217,290 @@ cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type,
     return cudaErrorInvalidValue;
 }
 
+// ---- down, IQ4_XS, table-driven producers, A operand in tensor memory -------------------------------------
+// The same GEMM, operands and bits as down_mma_kernel<QKM_TYPE_IQ4_XS>, built like gateup_iq3_kernel:
+// 512 producer threads = (row of 128, row tile 2u or 2u+1 of the unit, 32-column half of the k-step);
+// a unit is one (expert, pair tile) times two consecutive 128-row tiles of the down matrix, so the
+// two accumulators share the h tile (B).  The table maps a quant byte to (kvalues[lo], kvalues[hi])
+// as a bf16 pair, once per lane (a row of the 64 KB image is 32 x 4 bytes: a look-up never
+// conflicts and its address is one byte permute).  The sub-block scale d * (ls - 32) is applied in
+// two bf16 pieces, so a stored weight carries one bf16 rounding of the exact product.
+namespace pd {
+constexpr uint32_t kTab = pq::kTab, kTabBytes = pq::kTabBytes;
+}
+size_t down_iq4_table_bytes() { return pd::kTabBytes; }
+
+__global__ void down_iq4_table_kernel(uint8_t* __restrict__ out) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;   // one 4-byte word each
+    if (i >= pd::kTabBytes / 4) return;
+    const uint32_t row = i >> 6, w = i & 63u;
+    uint32_t v = 0;
+    if (w < 32) {
+        const __nv_bfloat162 m = __floats2bfloat162_rn((float)c_iq4_values[row & 15u], (float)c_iq4_values[row >> 4]);
+        v = *reinterpret_cast<const uint32_t*>(&m);
+    }
+    reinterpret_cast<uint32_t*>(out)[i] = v;
+}
+
+cudaError_t launch_down_iq4_table(const Launch& L, uint8_t* out) {
+    down_iq4_table_kernel<<<pd::kTabBytes / 4 / 256, 256, 0, L.stream>>>(out);
+    L.count();
+    return cudaGetLastError();
+}
+
+// the bytes one thread needs for (row, k-step q of the 256-column block, 32-column half j)
+struct Iq4Step { uint32_t w[4]; };
+__device__ __forceinline__ Iq4Step load_iq4_step(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q, uint32_t j) {
+    const uint32_t g = r16 & 7u, hf = r16 >> 3, sb = 2 * q + j;
+    Iq4Step r;
+#pragma unroll
+    for (int t = 0; t < 4; ++t)
+        r.w[t] = *reinterpret_cast<const uint32_t*>(tile + 128 + ((2 * hf + (sb >> 2)) * 32 + 4 * g + t) * 16 + 4 * (sb & 3u));
+    return r;
+}
+
+__global__ void __launch_bounds__(pq::kBlock, 1)
+down_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restrict__ hb,
+                const qkm_sel* __restrict__ sel, const uint32_t* __restrict__ pairs,
+                const MmaItem* __restrict__ items, const uint32_t* __restrict__ n_items_ptr,
+                float* __restrict__ contrib, qkm_dims d, const uint8_t* __restrict__ table,
+                uint32_t* __restrict__ status) {
+    constexpr int kSt = pq::kStages, PT = pq::kProducers;
+    const uint32_t n_units = *n_items_ptr / 2;   // items of one (expert, pair tile) are consecutive row tiles, an even number
+    if (blockIdx.x >= n_units) return;
+    extern __shared__ __align__(1024) uint8_t smem_dyn[];
+    __shared__ __align__(8) unsigned long long s_bar[2 * kSt + 2];  // empty[stage], full[stage], done, table
+    __shared__ uint32_t s_tmem;
+    __shared__ float s_wgt[2][pf::kNT];
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u;
+    {   // the fixed addresses must lie inside the dynamic area
+        const uint32_t dyn_base = smem_addr(smem_dyn);
+        uint32_t dyn_size;
+        asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(dyn_size));
+        if (dyn_base > pq::kTab || dyn_base + dyn_size < pq::kEnd) {
+            if (tid == 0) atomicExch(status, (uint32_t)kStatusBadLayout);
+            return;
+        }
+    }
+    const uint32_t KB = d.n_ff / 256, RT16 = d.n_embd / 16, KS = d.n_ff / 64;
+    const uint32_t bar_empty = smem_addr(&s_bar[0]), bar_full = smem_addr(&s_bar[kSt]);
+    const uint32_t bar_done = smem_addr(&s_bar[2 * kSt]), bar_tab = smem_addr(&s_bar[2 * kSt + 1]);
+
+    if (tid == 0) {
+        for (int s = 0; s < kSt; ++s) {
+            mbar_init(bar_empty + 8 * s, 1);      // one commit
+            mbar_init(bar_full + 8 * s, PT / 32); // one arrival per producer warp
+        }
+        mbar_init(bar_done, 1);
+        mbar_init(bar_tab, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) { umma::tmem_alloc(smem_addr(&s_tmem), pq::kTmemCols); umma::tmem_relinquish(); }
+    umma::fence_before_sync();
+    __syncthreads();
+    umma::fence_after_sync();
+    if (tid == 0) {
+        mbar_expect_tx(bar_tab, pd::kTabBytes);
+        for (uint32_t i = 0; i < 4; ++i) bulk_g2s(pd::kTab + i * 16384u, table + i * 16384u, 16384u, bar_tab);
+    }
+    const uint32_t tmem = s_tmem;
+    bool timed_out = false;
+
+    if (tid >= PT) {
+        // ---- MMA issuer warp: the whole warp walks the loop, one elected lane issues
+        const bool leader = umma::elect_one();
+        uint32_t stage = 0, phase = 0;
+        for (uint32_t unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
+            const uint32_t idesc = umma::instr_desc_bf16((items[2 * unit].n + 15u) & ~15u);
+            for (uint32_t ks = 0; ks < KS; ++ks) {
+                if (!mbar_wait_bounded(bar_full + 8 * stage, phase)) timed_out = true;
+                umma::fence_after_sync();
+                const uint64_t d_b = umma::smem_desc(pq::stage_addr(stage));
+                const uint32_t t_0 = tmem + pq::kTmemA + stage * 64u, t_1 = t_0 + 32u;
+                if (leader) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const bool acc = (ks | (uint32_t)j) != 0;
+                        mma_f16_ts(tmem, t_0 + 8 * j, d_b + 2 * j, idesc, acc);
+                        mma_f16_ts(tmem + 128, t_1 + 8 * j, d_b + 2 * j, idesc, acc);
+                    }
+                    umma::commit(bar_empty + 8 * stage);
+                    if (ks + 1 == KS) umma::commit(bar_done);
+                }
+                __syncwarp();
+                if (++stage == (uint32_t)kSt) { stage = 0; phase ^= 1u; }
+            }
+        }
+    } else {
+    // ---- producer warps: thread = (row r, row tile `mat` of the unit, 32-column half j of each k-step)
+    const uint32_t r = tid & 127u, mat = (tid >> 7) & 1u, j = tid >> 8;
+    const uint32_t tconst = 0x00010000u | (lane * 4u);
+    const uint32_t a_lane = tmem + ((r & ~31u) << 16) + pq::kTmemA + mat * 32u + j * 16u;
+    // N operand: chunks tid and tid + 512 of the h tile (row = chunk / 8), copied asynchronously
+    const uint32_t b_row0 = tid >> 3, b_row1 = b_row0 + 64, b_c = tid & 7u;
+    const uint32_t b_off0 = umma::sw128_chunk(b_row0, b_c), b_off1 = umma::sw128_chunk(b_row1, b_c);
+    if (!mbar_wait_bounded(bar_tab, 0)) timed_out = true;
+
+    struct UnitHead {
+        MmaItem it;            // the unit's first item (row tile it.rt, the second is it.rt + 1)
+        const uint8_t* wt;     // this thread's 16-row tile of column block 0
+        uint32_t r16;
+        uint2 hd;              // block header of column block 0
+        Iq4Step first;         // quant words of k-step 0
+    };
+    auto fetch_head = [&](uint32_t unit, uint32_t buf) -> UnitHead {
+        UnitHead hd;
+        hd.it = items[2 * unit];
+        const uint32_t rowidx = (hd.it.rt + mat) * 128u + r;
+        hd.r16 = rowidx & 15u;
+        hd.wt = tiles + ((size_t)hd.it.expert * KB * RT16 + (rowidx >> 4)) * kTileIq4;
+        hd.hd = *reinterpret_cast<const uint2*>(hd.wt + 16 * (hd.r16 & 7u) + 8 * (hd.r16 >> 3));
+        hd.first = load_iq4_step(hd.wt, hd.r16, 0, j);
+        for (uint32_t i = tid; i < hd.it.n; i += PT) {   // routing weight of the unit's columns (pairs)
+            const uint32_t pr = pairs[hd.it.pair_off + i], tok = pr >> 4, slot = pr & 15u;
+            s_wgt[buf][i] = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
+        }
+        return hd;
+    };
+    uint32_t stage = 0, phase = 0, gs = 0, iter = 0;
+    UnitHead head = fetch_head(blockIdx.x, 0);
+    named_sync(1, PT);
+    for (uint32_t unit = blockIdx.x; unit < n_units; unit += gridDim.x, ++iter) {
+        const MmaItem it = head.it;
+        const uint32_t n = it.n, n_mma = (n + 15u) & ~15u;
+        const uint32_t r16 = head.r16;
+        const uint8_t* wt = head.wt;
+        uint2 hdr = head.hd;
+        Iq4Step cur = head.first;
+        const uint32_t buf = iter & 1u;
+        // the h rows of this thread's two chunks: the unit's pairs are consecutive rows of hb
+        const __nv_bfloat16* b_src0 = hb + (size_t)(it.pair_off + (b_row0 < n ? b_row0 : 0u)) * d.n_ff + 8 * b_c;
+        const __nv_bfloat16* b_src1 = hb + (size_t)(it.pair_off + (b_row1 < n ? b_row1 : 0u)) * d.n_ff + 8 * b_c;
+        const uint32_t b_sz0 = b_row0 < n ? 16u : 0u, b_sz1 = b_row1 < n ? 16u : 0u;
+        const bool b_do0 = b_row0 < n_mma, b_do1 = b_row1 < n_mma;
+        // the first k-step's h tile
+        if (gs >= (uint32_t)kSt)
+            if (!mbar_wait_bounded(bar_empty + 8 * stage, phase ^ 1u)) timed_out = true;
+        {
+            const uint32_t st = pq::stage_addr(stage);
+            if (b_do0) cp_async16(st + b_off0, b_src0, b_sz0);
+            if (b_do1) cp_async16(st + b_off1, b_src1, b_sz1);
+            cp_async_commit();
+        }
+        for (uint32_t ks = 0; ks < KS; ++ks) {
+            const uint32_t q = ks & 3u;
+            // the next k-step's bytes (and the next column block's header) are fetched one step ahead
+            Iq4Step nxt = cur;
+            uint2 hdr_n = hdr;
+            if (ks + 1 < KS) {
+                const uint8_t* ntile = wt + (size_t)((ks + 1) >> 2) * RT16 * kTileIq4;
+                nxt = load_iq4_step(ntile, r16, (ks + 1) & 3u, j);
+                if (((ks + 1) & 3u) == 0) hdr_n = *reinterpret_cast<const uint2*>(ntile + 16 * (r16 & 7u) + 8 * (r16 >> 3));
+            }
+            // the next k-step's h tile goes to the next stage, once the MMAs that read it are done
+            uint32_t stage1 = stage + 1, phase1 = phase;
+            if (stage1 == (uint32_t)kSt) { stage1 = 0; phase1 ^= 1u; }
+            if (ks + 1 < KS) {
+                if (gs + 1 >= (uint32_t)kSt)
+                    if (!mbar_wait_bounded(bar_empty + 8 * stage1, phase1 ^ 1u)) timed_out = true;
+                const uint32_t st1 = pq::stage_addr(stage1);
+                if (b_do0) cp_async16(st1 + b_off0, b_src0 + (ks + 1) * 64, b_sz0);
+                if (b_do1) cp_async16(st1 + b_off1, b_src1 + (ks + 1) * 64, b_sz1);
+            }
+            cp_async_commit();
+            // sub-block 2q + j: scale d * (ls - 32) in two bf16 pieces
+            const uint32_t sb = 2 * q + j;
+            const float dd = f16_bits_to_f32(hdr.x & 0xFFFFu);
+            const int ls = (int)(((hdr.y >> (4 * sb)) & 0xFu) | ((((hdr.x >> 16) >> (2 * sb)) & 3u) << 4)) - 32;
+            const float dl = dd * (float)ls;
+            const __nv_bfloat16 dhi = __float2bfloat16_rn(dl);
+            const __nv_bfloat162 s_hi = __bfloat162bfloat162(dhi);
+            const __nv_bfloat162 s_lo = __bfloat162bfloat162(__float2bfloat16_rn(dl - __bfloat162float(dhi)));
+            auto scale = [&](uint32_t x) -> uint32_t {
+                const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&x);
+                const __nv_bfloat162 o = __hfma2(v, s_hi, __hmul2(v, s_lo));
+                return *reinterpret_cast<const uint32_t*>(&o);
+            };
+            // all sixteen look-ups first: byte i of the sub-block -> (element i, element 16 + i)
+            uint32_t l[16];
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                l[4 * t + 0] = lds32(prmt_b32(cur.w[t], tconst, 0x7604u));
+                l[4 * t + 1] = lds32(prmt_b32(cur.w[t], tconst, 0x7614u));
+                l[4 * t + 2] = lds32(prmt_b32(cur.w[t], tconst, 0x7624u));
+                l[4 * t + 3] = lds32(prmt_b32(cur.w[t], tconst, 0x7634u));
+            }
+            uint32_t lo[8], hi[8];   // columns 0..7: elements 0..15 (low nibbles); columns 8..15: elements 16..31
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+                lo[c] = scale(__byte_perm(l[2 * c], l[2 * c + 1], 0x5410));
+                hi[c] = scale(__byte_perm(l[2 * c], l[2 * c + 1], 0x7632));
+            }
+            tmem_st8(a_lane + stage * 64u, lo);
+            tmem_st8(a_lane + stage * 64u + 8, hi);
+            tmem_st_wait();
+            cp_async_wait<1>();            // this k-step's h tile has landed (the next one's may be in flight)
+            umma::fence_smem_to_async();   // the h tile (generic-proxy writes) before the tensor core reads it
+            umma::fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_full + 8 * stage);
+            ++gs;
+            stage = stage1; phase = phase1;
+            cur = nxt; hdr = hdr_n;
+        }
+        if (unit + gridDim.x < n_units) head = fetch_head(unit + gridDim.x, buf ^ 1u);
+        if (!mbar_wait_bounded(bar_done, iter & 1u)) timed_out = true;
+        umma::fence_after_sync();
+
+        // epilogue: warp w reads TMEM lanes 32*(w&3).. (rows) of accumulator (w >> 2) & 1 and every other
+        // 16-column block; the routing weight is applied after the full K reduction
+        {
+            const uint32_t lg = warp & 3u, acc = (warp >> 2) & 1u;
+            const uint32_t o = (it.rt + acc) * 128u + 32 * lg + lane;
+            for (uint32_t cb = warp >> 3; cb < n_mma / 16; cb += 2) {
+                uint32_t v[16];
+                umma::tmem_ld16(tmem + ((32 * lg) << 16) + acc * 128u + cb * 16, v);
+                umma::tmem_ld_wait();
+                float* cp = contrib + (size_t)(it.pair_off + cb * 16) * d.n_embd + o;
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    const uint32_t col = cb * 16 + i;
+                    if (col < n) cp[(size_t)i * d.n_embd] = s_wgt[buf][col] * __uint_as_float(v[i]);
+                }
+            }
+            umma::fence_before_sync();   // the accumulators are read before this thread's next arrival
+        }
+        named_sync(1, PT);   // the next unit's columns are written, this unit's are read
+    }
+    }  // producer / epilogue warps
+    umma::fence_before_sync();
+    const int any_timed_out = __syncthreads_or(timed_out ? 1 : 0);
+    if (warp == 0) umma::tmem_dealloc(tmem, pq::kTmemCols);
+    if (any_timed_out && tid == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+}
+
+static cudaError_t down_iq4_launch(const Launch& L, const qkm_dims& d, const void* tiles, const void* hb,
+                                   const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items,
+                                   const uint32_t* n_items, uint32_t max_items, float* contrib, const uint8_t* table,
+                                   uint32_t* status) {
+    static int n_sms = 0;
+    if (n_sms == 0) {
+        int dev = 0, v = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        n_sms = v;
+    }
+    const size_t smem = pq::kEnd;
+    cudaError_t e = cudaFuncSetAttribute(down_iq4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const uint32_t units = max_items / 2;
+    const uint32_t grid = units < (uint32_t)n_sms ? units : (uint32_t)n_sms;
+    if (grid == 0) return cudaSuccess;
+    down_iq4_kernel<<<grid, pq::kBlock, smem, L.stream>>>((const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items,
+                                                          n_items, contrib, d, table, status);
+    L.count();
+    return cudaGetLastError();
+}
+
 template <int FMT>
 static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const void* tiles, const void* hb,
                                    const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items,
@@ -1237,8 +1521,10 @@ static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const voi
 
 cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
                             const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
-                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks) {
+                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks, const uint8_t* iq4_table) {
     if (max_items == 0) return cudaSuccess;
+    if (type == QKM_TYPE_IQ4_XS && iq4_table && (d.n_embd / 128) % 2 == 0)   // row tiles in pairs
+        return down_iq4_launch(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, iq4_table, status);
     if (type == QKM_TYPE_IQ4_XS)
         return down_mma_launch<QKM_TYPE_IQ4_XS>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status, few_blocks);
     if (type == QKM_TYPE_Q8_0)
