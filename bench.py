@@ -482,7 +482,7 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
                 c1.upload_layer(l, layer)
             x1 = torch.from_numpy(np.stack([syn.random_x(Tmax, dims.n_embd, SEED_X + 555 + l) for l in range(PL)])).to(dev)
             y1 = torch.empty_like(x1)
-            for T1 in (128, 2048, 4096):
+            for T1 in (t for t in (128, 2048, 4096) if t in PREFILL_CHUNKS):
                 def step1():
                     for l in range(PL):
                         c1.moe_prefill(l, x1[l], T1, y1[l])
@@ -580,7 +580,7 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
             entry_["us_per_layer_1gpu_same_run"] = one_gpu_us[T]
             entry_["speedup_vs_1gpu"] = one_gpu_us[T] / entry_["us_per_layer"]
         out["chunks"][str(T)] = entry_
-    if world == 1:
+    if world == 1 and Tmax >= 2048:
         ctx.profile_enable(True)
         T = 2048
         acc = {}
@@ -593,7 +593,7 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
         gu = acc.get("moe.gu", 0.0)
         if gu > 0:
             fl = T * dims.n_used * 2 * 2 * dims.n_ff * dims.n_embd
-            out["roofline"] = {"bound": "tensor", "kernel": "gateup_mma_kernel<IQ3_XXS> at 2048 tokens",
+            out["roofline"] = {"bound": "tensor", "kernel": "gateup_iq3_kernel at 2048 tokens",
                                "achieved": fl / (gu * 1e-6) / 1e12, "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                                "frac": fl / (gu * 1e-6) / 1e12 / peaks["bf16_tflops"],
                                "peak_source": peaks["source"] + " cuBLAS bf16 burst", "traffic": None}
@@ -738,8 +738,13 @@ def main():
     ap.add_argument("--slots", type=int, default=16, help="decode slots per GPU")
     ap.add_argument("--sub-layers", type=int, default=8, help="distinct layers the prefill / expert-parallel cases rotate over")
     ap.add_argument("--no-sub", action="store_true", help="only the headline decode workload")
+    ap.add_argument("--prefill-tokens", default="", help="comma-separated chunk sizes of the prefill / expert-parallel cases "
+                    "(default: 128,256,512,2048,4096); a single size keeps a profiler capture of their kernels small")
     args = ap.parse_args()
     args.sub_layers = max(1, min(args.sub_layers, args.layers))
+    if args.prefill_tokens:
+        global PREFILL_CHUNKS
+        PREFILL_CHUNKS = tuple(sorted(int(v) for v in args.prefill_tokens.split(",") if v))
     pkg = entry.package()
     syn = pkg.synth
     if args.impl == "reference":

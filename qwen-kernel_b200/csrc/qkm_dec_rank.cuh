@@ -47,7 +47,8 @@ __device__ __forceinline__ void rank_tokens_impl(const double* __restrict__ logi
     // eight, with a sorting network; then each of the n_used rounds compares only list heads:
     // the warp finds the largest head with three hardware reductions (high word, low word among
     // the lanes that hold it, lowest id among those - lowest id wins ties) and the winning lane
-    // pops its list.  Integer arithmetic only: f64 instructions are slow on this part.
+    // pops its list.  Integer arithmetic only: a serial chain of f64 compares and selects is latency-
+    // bound (f64 adds and multiplies run at half the f32 rate here, f32<->f64 conversions at an eighth).
     const uint32_t per_lane = (d.n_expert + 31) / 32;   // <= 16
     const unsigned long long kFloorBits = (unsigned long long)__double_as_longlong((double)rk::kFloor);
     for (uint32_t t = t_first + warp; t < t_first + t_count; t += n_warps) {
