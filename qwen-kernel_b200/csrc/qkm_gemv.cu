@@ -358,6 +358,12 @@ cudaError_t launch_gemv_stream(const Launch& L, uint32_t type, const void* W, co
             default: return cudaErrorInvalidValue;
         }
     }
+    if (n == 1 && aligned) {   // large matrices in the formats the integer tensor-core form takes
+        e = launch_gemv_mma(L, type, w, x, y, M, K, n_sms, status, &done);
+        if (e != cudaSuccess) return e;
+        if (done == M) return cudaSuccess;
+        if (done) return launch_gemv_tail(L, type, w + (size_t)done * row_bytes(type, K), x, y + done, M - done, K, n, M);
+    }
     switch (type) {
         case QKM_TYPE_F32: e = gemv_stream_launch<QKM_TYPE_F32>(L, w, x, y, M, K, n, n_sms, status, &done); break;
         case QKM_TYPE_F16: e = gemv_stream_launch<QKM_TYPE_F16>(L, w, x, y, M, K, n, n_sms, status, &done); break;

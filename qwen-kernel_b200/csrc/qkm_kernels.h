@@ -169,6 +169,8 @@ cudaError_t launch_gemv(const Launch& L, uint32_t type, const void* W, const flo
                         uint32_t M, uint32_t K, uint32_t n);
 
 // streamed form (bulk-copy ring) with the generic kernel for tail rows / unaligned tensors
+cudaError_t launch_gemv_mma(const Launch& L, uint32_t type, const void* W, const float* x, float* y, uint32_t M,
+                            uint32_t K, uint32_t n_sms, uint32_t* status, uint32_t* rows_done);
 cudaError_t launch_gemv_stream(const Launch& L, uint32_t type, const void* W, const float* x, float* y,
                                uint32_t M, uint32_t K, uint32_t n, uint32_t n_sms, uint32_t* status);
 
