@@ -9,13 +9,15 @@
 //
 // A block has one warp per 256 columns of K, and every warp streams its own slice: for a tile of 16
 // rows the 8 blocks x 34 bytes of each row that fall into its columns (272 contiguous bytes per
-// row), copied asynchronously (cp.async, 16 bytes per lane and instruction) into its own ring of
-// stages.  A slice row is 68 words long, so the A-fragment loads of the eight row groups fall into
+// row), fetched as one two-dimensional TMA copy (a tensor map over the matrix as [row][byte pair], box
+// = 16 rows x 272 bytes; no multicast) into its own ring of stages.  A slice row is 68 words long, so the A-fragment loads of the eight row groups fall into
 // different banks without padding, and no warp waits for another until the partial sums of eight
 // tiles meet in shared memory.  (Bulk copies of whole rows into a padded block-wide stage moved
-// 3.8 TB/s at most: sixteen 2 KB copies per tile.)  A warp multiplies its 256 columns of the 16
+// 3.8 TB/s at most - sixteen 2 KB copies per tile - and 16-byte cp.async pieces 4.5 TB/s.)  A warp multiplies its 256 columns of the 16
 // rows (eight MMAs), scales each 32-column block's integer sums by the block's f16 scale and keeps
 // f32 partial sums.
+#include <cuda.h>
+
 #include "qkm_common.cuh"
 #include "qkm_kernels.h"
 #include "qkm_stream.cuh"
@@ -30,54 +32,55 @@ constexpr int kMaxStages = 6;
 constexpr int kSlice = 8 * 34;     // bytes of one row inside a warp's 256 columns (Q8_0)
 }  // namespace gm
 
-// Q8_0: 16 rows x 32 columns of block `bi` of the tile at `st` (row stride S) against one k32 B operand.
-// Returns in f0 / f1 the contribution to rows g / g+8 of this lane's two digit planes.
+// Q8_0: 16 rows x 32 columns of block `bi` of the tile at `st` (row stride S).  Loading a block's
+// words and multiplying them are separate so that the next block's loads are in flight meanwhile.
+struct Q8Frag { uint32_t w[8]; uint32_t d0, d1; };
 template <bool EVEN>
-__device__ __forceinline__ void q8_block_mma(uint32_t st, uint32_t S, uint32_t bi, uint32_t g, uint32_t t, uint32_t b0,
-                                             uint32_t b1, float plane_w, float& f0, float& f1) {
+__device__ __forceinline__ Q8Frag q8_block_load(uint32_t st, uint32_t S, uint32_t bi, uint32_t g, uint32_t t) {
     const uint32_t r0 = st + g * S + 34u * bi, r1 = r0 + 8u * S;
-    uint32_t a0, a1, a2, a3;
-    if (EVEN) {   // the quants start two bytes into a word: two aligned words and a funnel shift each
-        a0 = __funnelshift_r(lds32(r0 + 4 * t), lds32(r0 + 4 * t + 4), 16);
-        a1 = __funnelshift_r(lds32(r1 + 4 * t), lds32(r1 + 4 * t + 4), 16);
-        a2 = __funnelshift_r(lds32(r0 + 16 + 4 * t), lds32(r0 + 20 + 4 * t), 16);
-        a3 = __funnelshift_r(lds32(r1 + 16 + 4 * t), lds32(r1 + 20 + 4 * t), 16);
+    Q8Frag f;
+    if (EVEN) {   // the quants start two bytes into a word: two aligned words per fragment register
+        f.w[0] = lds32(r0 + 4 * t);      f.w[1] = lds32(r0 + 4 * t + 4);
+        f.w[2] = lds32(r1 + 4 * t);      f.w[3] = lds32(r1 + 4 * t + 4);
+        f.w[4] = lds32(r0 + 16 + 4 * t); f.w[5] = lds32(r0 + 20 + 4 * t);
+        f.w[6] = lds32(r1 + 16 + 4 * t); f.w[7] = lds32(r1 + 20 + 4 * t);
+        f.d0 = lds32(r0); f.d1 = lds32(r1);             // the block scale (f16) sits in the low half
     } else {
-        a0 = lds32(r0 + 2 + 4 * t); a1 = lds32(r1 + 2 + 4 * t);
-        a2 = lds32(r0 + 18 + 4 * t); a3 = lds32(r1 + 18 + 4 * t);
+        f.w[0] = lds32(r0 + 2 + 4 * t);  f.w[2] = lds32(r1 + 2 + 4 * t);
+        f.w[4] = lds32(r0 + 18 + 4 * t); f.w[6] = lds32(r1 + 18 + 4 * t);
+        f.w[1] = f.w[3] = f.w[5] = f.w[7] = 0;
+        f.d0 = lds32(r0 - 2); f.d1 = lds32(r1 - 2);     // ... in the high half
+    }
+    return f;
+}
+// Adds to f0 / f1 the contribution to rows g / g+8 of this lane's two digit planes.
+template <bool EVEN>
+__device__ __forceinline__ void q8_block_mma(const Q8Frag& f, uint32_t b0, uint32_t b1, float plane_w, float& f0, float& f1) {
+    uint32_t a0, a1, a2, a3;
+    if (EVEN) {
+        a0 = __funnelshift_r(f.w[0], f.w[1], 16); a1 = __funnelshift_r(f.w[2], f.w[3], 16);
+        a2 = __funnelshift_r(f.w[4], f.w[5], 16); a3 = __funnelshift_r(f.w[6], f.w[7], 16);
+    } else {
+        a0 = f.w[0]; a1 = f.w[2]; a2 = f.w[4]; a3 = f.w[6];
     }
     int c[4] = {0, 0, 0, 0};
     mma_s8(c, a0, a1, a2, a3, b0, b1);
-    // the block scales (f16 at the head of each block); an even block's sits in the low half of its word
-    const uint32_t w0 = lds32(EVEN ? r0 : r0 - 2), w1 = lds32(EVEN ? r1 : r1 - 2);
-    const float d0 = f16_bits_to_f32(EVEN ? (w0 & 0xFFFFu) : (w0 >> 16));
-    const float d1 = f16_bits_to_f32(EVEN ? (w1 & 0xFFFFu) : (w1 >> 16));
+    const float d0 = f16_bits_to_f32(EVEN ? (f.d0 & 0xFFFFu) : (f.d0 >> 16));
+    const float d1 = f16_bits_to_f32(EVEN ? (f.d1 & 0xFFFFu) : (f.d1 >> 16));
     // digits 2t (weight 1) and 2t+1 (weight 128) of this lane's pair, exact in int32
     f0 = fmaf((float)(c[0] + (c[1] << 7)) * plane_w, d0, f0);
     f1 = fmaf((float)(c[2] + (c[3] << 7)) * plane_w, d1, f1);
 }
 
-template <int N>
-__device__ __forceinline__ void cp_async_wait_n() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void cp_async_wait_dyn(uint32_t n) {   // at most n groups still in flight
-    switch (n) {
-        case 0: cp_async_wait_n<0>(); break;
-        case 1: cp_async_wait_n<1>(); break;
-        case 2: cp_async_wait_n<2>(); break;
-        case 3: cp_async_wait_n<3>(); break;
-        case 4: cp_async_wait_n<4>(); break;
-        default: cp_async_wait_n<5>(); break;
-    }
-}
-
 template <int TYPE>
 __global__ void __launch_bounds__(gm::kMaxWarps * 32)
-gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, uint32_t n_tiles,
-                uint32_t K, uint32_t rb, uint32_t n_stages) {
+gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restrict__ x, float* __restrict__ y,
+                uint32_t n_tiles, uint32_t K, uint32_t n_stages, uint32_t* __restrict__ status) {
     static_assert(TYPE == QKM_TYPE_Q8_0, "formats: Q8_0");
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ float s_max[gm::kMaxWarps];
     __shared__ float s_scale;
+    __shared__ __align__(8) unsigned long long s_bar[gm::kMaxWarps][gm::kMaxStages];   // a stage of a warp's ring has landed
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const uint32_t KB = K / 256, n_threads = KB * 32;
     constexpr uint32_t S = gm::kSlice, kStage = gm::kRows * gm::kSlice;   // 272-byte slice rows, 4352 bytes per stage
@@ -87,27 +90,24 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, floa
     const uint32_t red_floats = KB * gm::kGroup * gm::kRows;
     const uint32_t ring = ((smem_addr(smem_raw) + K * 4 + 2 * red_floats * 4 + 127u) & ~127u) + warp * n_stages * kStage;
 
-    // this block's tiles: blockIdx.x, + gridDim.x, ...; a lane's chunks of a tile: c = lane + 32 k < 272,
-    // row c / 17, 16-byte piece c % 17 of the slice row - the same for every tile
+    // this block's tiles: blockIdx.x, + gridDim.x, ...
     const uint32_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
-    uint32_t c_src[9], c_dst[9];
-#pragma unroll
-    for (int k = 0; k < 9; ++k) {
-        const uint32_t c = lane + 32u * k, row = c / 17u, j = c - row * 17u;
-        c_src[k] = row * rb + warp * S + 16u * j;
-        c_dst[k] = row * S + 16u * j;
+    const uint32_t my_bar = smem_addr(&s_bar[warp][0]);
+    bool timed_out = false;
+    if (lane == 0) {
+        for (uint32_t s = 0; s < n_stages; ++s) mbar_init(my_bar + 8 * s, 1);
+        mbar_fence_init();
     }
-    auto issue = [&](uint32_t i) {   // tile number i of this block into stage i % n_stages of this warp's ring
-        const uint32_t dst = ring + (i % n_stages) * kStage;
-        const uint8_t* src = W + (size_t)(blockIdx.x + i * gridDim.x) * gm::kRows * rb;
-#pragma unroll
-        for (int k = 0; k < 9; ++k)
-            if (k < 8 || lane < 16u) asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst + c_dst[k]), "l"(src + c_src[k]) : "memory");
+    __syncwarp();
+    auto issue = [&](uint32_t i) {   // tile number i of this block into stage i % n_stages of this warp's ring; lane 0
+        const uint32_t s = i % n_stages, dst = ring + s * kStage, bar = my_bar + 8 * s;
+        const uint32_t cx = warp * (S / 2), cy = (blockIdx.x + i * gridDim.x) * gm::kRows;   // byte pairs, rows
+        mbar_expect_tx(bar, kStage);
+        asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                     ::"r"(dst), "l"(&tmap), "r"(cx), "r"(cy), "r"(bar) : "memory");
     };
-    for (uint32_t i = 0; i + 1 < n_stages; ++i) {
-        if (i < my_tiles) issue(i);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-    }
+    if (lane == 0)
+        for (uint32_t i = 0; i + 2 < n_stages && i < my_tiles; ++i) issue(i);   // n_stages - 2 tiles ahead; two more per pair below
 
     // x as digit planes (the first tiles are on their way meanwhile)
     {
@@ -156,24 +156,35 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, floa
         const uint32_t in_group = min((uint32_t)gm::kGroup, my_tiles - i0);
         float acc[gm::kGroup][2];
 #pragma unroll
-        for (int q = 0; q < gm::kGroup; ++q) {
-            acc[q][0] = acc[q][1] = 0.f;
+        for (int q = 0; q < gm::kGroup; q += 2) {   // two tiles at a time: their dependent chains interleave
+            acc[q][0] = acc[q][1] = acc[q + 1][0] = acc[q + 1][1] = 0.f;
             const uint32_t i = i0 + q;
             if (i < my_tiles) {   // block-uniform
-                // refill the stage this warp read one tile ago (its loads have returned), then wait for tile i
+                // refill the two stages this warp read one pair ago (its loads have returned), then wait for the pair
                 __syncwarp();
-                if (i + n_stages - 1 < my_tiles) issue(i + n_stages - 1);
-                asm volatile("cp.async.commit_group;" ::: "memory");
-                cp_async_wait_dyn(n_stages - 1);   // every lane's pieces of tile i
-                __syncwarp();
-                const uint32_t st = ring + (i % n_stages) * kStage;
-                float f0 = 0.f, f1 = 0.f;
-#pragma unroll
-                for (int sb = 0; sb < 8; ++sb) {
-                    if (sb & 1) q8_block_mma<false>(st, S, sb, g, t, b0[sb], b1[sb], plane_w, f0, f1);
-                    else q8_block_mma<true>(st, S, sb, g, t, b0[sb], b1[sb], plane_w, f0, f1);
+                if (lane == 0) {
+                    if (i + n_stages - 2 < my_tiles) issue(i + n_stages - 2);
+                    if (i + n_stages - 1 < my_tiles) issue(i + n_stages - 1);
                 }
-                acc[q][0] = f0; acc[q][1] = f1;
+                const bool two = i + 1 < my_tiles;
+                if (!mbar_wait_bounded(my_bar + 8 * (i % n_stages), (i / n_stages) & 1u)) timed_out = true;
+                if (two && !mbar_wait_bounded(my_bar + 8 * ((i + 1) % n_stages), ((i + 1) / n_stages) & 1u)) timed_out = true;
+                const uint32_t sa = ring + (i % n_stages) * kStage, sb_ = two ? ring + ((i + 1) % n_stages) * kStage : sa;
+                float fa0 = 0.f, fa1 = 0.f, fb0 = 0.f, fb1 = 0.f;
+                Q8Frag ca = q8_block_load<true>(sa, S, 0, g, t), cb = q8_block_load<true>(sb_, S, 0, g, t);
+#pragma unroll
+                for (int sb = 0; sb < 8; ++sb) {   // block sb + 1 is loaded while block sb is multiplied
+                    Q8Frag na = ca, nb = cb;
+                    if (sb + 1 < 8) {
+                        na = (sb & 1) ? q8_block_load<true>(sa, S, sb + 1, g, t) : q8_block_load<false>(sa, S, sb + 1, g, t);
+                        nb = (sb & 1) ? q8_block_load<true>(sb_, S, sb + 1, g, t) : q8_block_load<false>(sb_, S, sb + 1, g, t);
+                    }
+                    if (sb & 1) { q8_block_mma<false>(ca, b0[sb], b1[sb], plane_w, fa0, fa1); q8_block_mma<false>(cb, b0[sb], b1[sb], plane_w, fb0, fb1); }
+                    else { q8_block_mma<true>(ca, b0[sb], b1[sb], plane_w, fa0, fa1); q8_block_mma<true>(cb, b0[sb], b1[sb], plane_w, fb0, fb1); }
+                    ca = na; cb = nb;
+                }
+                acc[q][0] = fa0; acc[q][1] = fa1;
+                if (two) { acc[q + 1][0] = fb0; acc[q + 1][1] = fb1; }
             }
         }
         // the two digit-plane pairs of a row sit in lanes t = 0 and t = 1; then the warps' column blocks
@@ -195,6 +206,7 @@ gemv_mma_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, floa
         }
         buf ^= 1u;
     }
+    if (timed_out && lane == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
 // Rows [0, *rows_done) are computed here; the caller finishes the rest.  Shapes this form does not take
@@ -203,8 +215,7 @@ cudaError_t launch_gemv_mma(const Launch& L, uint32_t type, const void* W, const
                             uint32_t K, uint32_t n_sms, uint32_t* status, uint32_t* rows_done) {
     *rows_done = 0;
     if (type != QKM_TYPE_Q8_0 || K % 256 != 0 || K < 512 || K > 256u * gm::kMaxWarps || M < (uint32_t)gm::kRows) return cudaSuccess;
-    (void)status;   // no device-side wait in this form
-    if (((uintptr_t)W & 15u) || ((uintptr_t)x & 3u)) return cudaSuccess;
+    if (((uintptr_t)W & 15u) || ((uintptr_t)x & 3u) || status == nullptr) return cudaSuccess;
     const uint32_t rb = (uint32_t)row_bytes(type, K);   // a multiple of 16 for K % 256 == 0
     if (rb % 16) return cudaSuccess;
     const uint32_t KB = K / 256;
@@ -212,14 +223,32 @@ cudaError_t launch_gemv_mma(const Launch& L, uint32_t type, const void* W, const
     const size_t stage = (size_t)KB * gm::kRows * gm::kSlice;   // one stage of every warp's ring
     // one block per SM with as deep a ring as fits: the bytes in flight, not the warps, carry the bandwidth
     uint32_t n_stages = gm::kMaxStages;
-    while (n_stages > 2 && fixed + n_stages * stage > 200u * 1024u) --n_stages;
+    while (n_stages > 3 && fixed + n_stages * stage > 200u * 1024u) --n_stages;
     const size_t smem = fixed + n_stages * stage;
-    if (smem > 220u * 1024u) return cudaSuccess;
+    if (smem > 220u * 1024u || n_stages < 3) return cudaSuccess;
+    // the matrix as [M rows][rb / 2 byte pairs]; a box is one warp's slice of a tile
+    typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                 const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                 CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres) != cudaSuccess || !fn) return cudaSuccess;
+        encode = (EncodeFn)fn;
+    }
+    CUtensorMap tmap;
+    const cuuint64_t gdim[2] = {rb / 2, M}, gstride[1] = {rb};
+    const cuuint32_t box[2] = {gm::kSlice / 2, gm::kRows}, estride[2] = {1, 1};
+    if (encode(&tmap, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(W), gdim, gstride, box, estride, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return cudaSuccess;   // the other kernels take the call
     cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<QKM_TYPE_Q8_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const uint32_t n_tiles = M / gm::kRows;
-    const uint32_t blocks = n_tiles < n_sms ? n_tiles : n_sms;
-    gemv_mma_kernel<QKM_TYPE_Q8_0><<<blocks, KB * 32, smem, L.stream>>>((const uint8_t*)W, x, y, n_tiles, K, rb, n_stages);
+    const uint32_t per_sm = smem <= 110u * 1024u ? 2u : 1u;
+    const uint32_t blocks = n_tiles < per_sm * n_sms ? n_tiles : per_sm * n_sms;
+    gemv_mma_kernel<QKM_TYPE_Q8_0><<<blocks, KB * 32, smem, L.stream>>>(tmap, x, y, n_tiles, K, n_stages, status);
     L.count();
     *rows_done = n_tiles * gm::kRows;
     return cudaGetLastError();
