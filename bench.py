@@ -548,6 +548,8 @@ def run_prefill_or_ep(args, pkg, syn, torch, R: Ranks, orc, layers, peaks):
                                      "rel_err_vs_oracle": R.max_over_ranks(err_p),
                                      "launches_per_layer": (ctx.launch_count() - n0) / ((steps + warm) * PL),
                                      "exchange": "rows and partial rows stored into peer-mapped buffers over NVLink, two flag barriers (own kernel) per layer, one library call per layer"}
+            if ep:   # same rows as the all-to-all form, but f16 on the way out (f32 partial rows on the way back)
+                entry_["peer_memory"]["nvlink_bytes_per_rank_per_layer"] = off * (dims.n_embd * 2 + 160) + off * dims.n_embd * 4
             try:
                 ctx.sync()   # a barrier wait that ran out surfaces here; every rank goes on with the same calls
             except Exception as e:   # noqa: BLE001  (reported in the JSON line)

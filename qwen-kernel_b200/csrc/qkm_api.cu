@@ -97,8 +97,10 @@ struct qkm_ctx {
     uint32_t pm_ranks = 0, pm_rank = 0, pm_cap = 0;   // slot_cap rows per source rank
     uint32_t pm_epoch = 0;                            // barriers issued so far (qkm_ep_barrier)
     bool pm_shared_in_partial = false;                // the last qkm_ep_forward_slots included the shared expert
+    bool pm_rows_f16 = false;                         // the last qkm_ep_push sent f16 rows (layers on the tensor-core path)
     float* pm_xrecv = nullptr; qkm_sel* pm_selrecv = nullptr; float* pm_back = nullptr;   // mapped by the peers
     float* pm_partial = nullptr;                      // local partial rows where the fold does not store to the peers
+    float* pm_xscale = nullptr;                       // [slot_cap] scales of the local rows sent as f16 (small batches)
     EpPeerTable pm_peers{};
     void* pm_opened[kMaxPeerRanks][3] = {};           // mappings this context opened from handles
     // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
@@ -350,7 +352,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
     for (auto& o : c->pm_opened) for (void* p : o) if (p) cudaIpcCloseMemHandle(p);
-    for (void* p : {(void*)c->pm_xrecv, (void*)c->pm_selrecv, (void*)c->pm_back, (void*)c->pm_partial}) if (p) cudaFree(p);
+    for (void* p : {(void*)c->pm_xrecv, (void*)c->pm_selrecv, (void*)c->pm_back, (void*)c->pm_partial, (void*)c->pm_xscale}) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->ep_counts_host) cudaFreeHost(c->ep_counts_host);
     if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
@@ -1184,7 +1186,7 @@ extern "C" QKM_API int qkm_ep_shared(qkm_ctx* c, uint32_t layer, const float* x,
 // stored into its source rank's return buffer instead of staying in `partial`.
 static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv, const qkm_sel* selrecv, uint32_t n_recv,
                                   float* partial, bool with_shared, uint32_t sh_first, uint32_t sh_count,
-                                  uint32_t slot_rows_peer = 0) {
+                                  uint32_t slot_rows_peer = 0, bool rows_f16 = false) {
     if (int rc = layer_ready(c, layer)) return rc;
     c->shared_plan_n = 0;
     if (n_recv == 0) return QKM_OK;
@@ -1222,14 +1224,21 @@ static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv
     QKM_LAUNCH(c, launch_mma_plan(c->L(), d, c->offsets, c->pairs, c->ecount, n_recv, c->mma_items[0], c->mma_items[1],
                                   c->mma_items[2], c->mma_items[3], c->n_items, c->pos_of, with_shared, true, sh_first,
                                   with_shared ? sh_count : 0));
-    QKM_LAUNCH(c, launch_to_f16_rows(c->L(), xrecv, c->xb, c->xscale, n_recv, d.n_embd));
+    // the rows as scaled f16: converted here, or already so on arrival (then only their scales are gathered)
+    const void* xb_rows = c->xb;
+    if (rows_f16) {
+        xb_rows = xrecv;
+        QKM_LAUNCH(c, launch_ep_row_scales(c->L(), selrecv, c->xscale, n_recv));
+    } else {
+        QKM_LAUNCH(c, launch_to_f16_rows(c->L(), xrecv, c->xb, c->xscale, n_recv, d.n_embd));
+    }
     const bool fork = with_shared && sh_count;
     if (fork) {
         const uint32_t sh_now = (sh_count + NT - 1) / NT;
         Launch S{c->side, &c->launches};
         QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
-        QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
+        QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], xb_rows, c->xscale, c->pairs, c->mma_items[2],
                                         c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms));
         QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, selrecv, c->pairs, c->mma_items[3],
                                       c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
@@ -1237,7 +1246,7 @@ static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv
     }
     // a shard of few experts launches fewer blocks than the machine holds: faster blocks instead (see the launchers)
     const bool few_gu = c->ecount * rt_gu <= 2u * (uint32_t)c->n_sms, few_dn = c->ecount * rt_dn / 4 <= 2u * (uint32_t)c->n_sms;
-    QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
+    QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], xb_rows, c->xscale, c->pairs, c->mma_items[0],
                                     c->n_items, tiles_now * rt_gu, ld.stream_ok ? nullptr : c->h, c->hb, c->status, few_gu, c->lut_pf));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
                                   c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn, c->lut_dn));
@@ -1308,19 +1317,20 @@ extern "C" QKM_API int qkm_ep_peer_setup(qkm_ctx* c, uint32_t n_ranks, uint32_t 
         return fail(c, QKM_ERR_BOUNDS, "%u ranks x %u rows exceed max_tokens %u", n_ranks, slot_cap, c->cfg.max_tokens);
     const size_t rows = (size_t)n_ranks * slot_cap;
     QKM_CUDA(c, cudaSetDevice(c->device));
-    // all four buffers or none: a failure part way frees what was taken, so a retry starts clean
+    // all five buffers or none: a failure part way frees what was taken, so a retry starts clean
     cudaError_t e = cudaMalloc((void**)&c->pm_xrecv, rows * d.n_embd * sizeof(float));
     // the barrier words of qkm_ep_barrier sit behind the records, so three mappings carry everything
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->pm_selrecv, rows * sizeof(qkm_sel) + kPmFlagBytes);
     if (e == cudaSuccess) e = cudaMemset((char*)c->pm_selrecv + rows * sizeof(qkm_sel), 0, kPmFlagBytes);
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->pm_partial, rows * d.n_embd * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc((void**)&c->pm_back, rows * d.n_embd * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc((void**)&c->pm_xscale, (size_t)slot_cap * sizeof(float));
     if (e == cudaSuccess) e = cudaMemset(c->pm_back, 0, rows * d.n_embd * sizeof(float));
     if (e == cudaSuccess) e = cudaMemset(c->pm_xrecv, 0, rows * d.n_embd * sizeof(float));
     if (e == cudaSuccess) e = cudaMemset(c->pm_selrecv, 0xFF, rows * sizeof(qkm_sel));   // every record empty
     if (e == cudaSuccess) e = cudaMemset(c->pm_partial, 0, rows * d.n_embd * sizeof(float));
     if (e != cudaSuccess) {
-        for (void** p : {(void**)&c->pm_xrecv, (void**)&c->pm_selrecv, (void**)&c->pm_partial, (void**)&c->pm_back}) {
+        for (void** p : {(void**)&c->pm_xrecv, (void**)&c->pm_selrecv, (void**)&c->pm_partial, (void**)&c->pm_back, (void**)&c->pm_xscale}) {
             if (*p) cudaFree(*p);
             *p = nullptr;
         }
@@ -1388,7 +1398,22 @@ extern "C" QKM_API int qkm_ep_push(qkm_ctx* c, uint32_t layer, const float* x, u
     if (n > slot_rows) return fail(c, QKM_ERR_BOUNDS, "%u tokens exceed slot_rows %u", n, slot_rows);
     c->shared_plan_n = 0;
     if (n) if (int rc = ep_route_local(c, layer, x, n)) return rc;
-    QKM_LAUNCH(c, launch_ep_push(c->L(), c->cfg.dims, x, c->sel, c->pm_peers, n, slot_rows, c->pm_rank, c->pm_ranks));
+    // Layers whose resident experts run on the tensor cores consume the rows as scaled f16: then those
+    // travel (half the bytes; every rank decides the same from the layer's types).  The router above
+    // has made them already for 128 tokens and more.
+    const qkm_layer_dev& ld = c->layers[layer];
+    c->pm_rows_f16 = ld.tiles_ok && c->cfg.dims.n_embd % 8 == 0;
+    if (c->pm_rows_f16 && n) {
+        const float* inv = c->xscale;
+        if (n < 128) {   // (the router made digit planes, whose scales sit in xscale for the streamed shared expert)
+            if (int rc = ensure_prefill_scratch(c)) return rc;
+            QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->pm_xscale, n, c->cfg.dims.n_embd));
+            inv = c->pm_xscale;
+        }
+        QKM_LAUNCH(c, launch_ep_push(c->L(), c->cfg.dims, x, c->sel, c->pm_peers, n, slot_rows, c->pm_rank, c->pm_ranks, c->xb, inv));
+    } else {
+        QKM_LAUNCH(c, launch_ep_push(c->L(), c->cfg.dims, x, c->sel, c->pm_peers, n, slot_rows, c->pm_rank, c->pm_ranks));
+    }
     return QKM_OK;
 }
 
@@ -1398,7 +1423,8 @@ extern "C" QKM_API int qkm_ep_forward_slots(qkm_ctx* c, uint32_t layer, uint32_t
     const bool with_shared = n_shared != QKM_EP_NO_SHARED;
     c->pm_shared_in_partial = with_shared;
     return ep_expert_forward_impl(c, layer, c->pm_xrecv, c->pm_selrecv, c->pm_ranks * slot_rows, c->pm_partial, with_shared,
-                                  c->pm_rank * slot_rows, with_shared ? n_shared : 0, slot_rows);
+                                  c->pm_rank * slot_rows, with_shared ? n_shared : 0, slot_rows,
+                                  c->pm_rows_f16 && c->layers[layer].tiles_ok);
 }
 
 extern "C" QKM_API int qkm_ep_pull(qkm_ctx* c, uint32_t n, uint32_t slot_rows, float* y) {

@@ -16,6 +16,7 @@
 // from a peer are round trips), and the pull kernel sums them from local memory.  Only plain stores and
 // loads touch peer memory.  The host orders the phases with a barrier (any collective on the
 // stream); these kernels do not wait on anything either.
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -119,8 +120,13 @@ ep_combine_kernel(const float* __restrict__ back, const uint32_t* __restrict__ s
 // which the grouping kernels skip (rows i >= n_tokens are such records on every rank).  This
 // rank's own buffers always get the x row, and the weights of the record even when its ids are
 // blanked: the shared expert of the local tokens is computed from there.
+// With xh (the rows as f16, each scaled by a power of two) the f16 row travels instead - half the
+// bytes; it lands at the head of the same row buffer (row r at byte r * n_embd * 2) and the scale
+// that undoes the scaling rides in the record's first padding word.  The owner would make exactly
+// this conversion from the f32 row, so its results do not change.
 __global__ void __launch_bounds__(256)
-ep_push_kernel(const float* __restrict__ x, const qkm_sel* __restrict__ sel, EpPeerTable peers, uint32_t n_tokens,
+ep_push_kernel(const float* __restrict__ x, const __half* __restrict__ xh, const float* __restrict__ x_inv_scale,
+               const qkm_sel* __restrict__ sel, EpPeerTable peers, uint32_t n_tokens,
                uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, uint32_t n_used, uint32_t experts_per_rank,
                uint32_t n_embd) {
     const uint32_t i = blockIdx.x, tid = threadIdx.x;
@@ -133,19 +139,35 @@ ep_push_kernel(const float* __restrict__ x, const qkm_sel* __restrict__ sel, EpP
     const size_t row = (size_t)rank * slot_rows + i;
     constexpr uint32_t kWords = sizeof(qkm_sel) / 4;
     if (tid < kWords) {
-        const uint32_t mine = i < n_tokens ? reinterpret_cast<const uint32_t*>(sel + i)[tid] : 0u;
+        uint32_t mine = i < n_tokens ? reinterpret_cast<const uint32_t*>(sel + i)[tid] : 0u;
+        if (xh != nullptr && tid == kSelScaleWord && i < n_tokens) mine = __float_as_uint(x_inv_scale[i]);
         const uint32_t empty = tid < 16 ? kInvalid : 0u;
         for (uint32_t d = 0; d < n_ranks; ++d)
             reinterpret_cast<uint32_t*>(peers.sel[d] + row)[tid] = (need >> d & 1u) ? mine : (d == rank && tid >= 16) ? mine : empty;
     }
     if (i >= n_tokens) return;
     const uint32_t dest = need | (1u << rank);
+    if (xh != nullptr) {
+        const uint4* src = reinterpret_cast<const uint4*>(xh + (size_t)i * n_embd);
+        for (uint32_t c = tid; c < n_embd / 8; c += blockDim.x) {
+            const uint4 v = __ldg(src + c);
+            for (uint32_t d = 0; d < n_ranks; ++d)
+                if (dest >> d & 1u) reinterpret_cast<uint4*>(reinterpret_cast<__half*>(peers.x[d]) + row * n_embd)[c] = v;
+        }
+        return;
+    }
     const float4* src = reinterpret_cast<const float4*>(x + (size_t)i * n_embd);
     for (uint32_t c = tid; c < n_embd / 4; c += blockDim.x) {
         const float4 v = __ldg(src + c);
         for (uint32_t d = 0; d < n_ranks; ++d)
             if (dest >> d & 1u) reinterpret_cast<float4*>(peers.x[d] + row * n_embd)[c] = v;
     }
+}
+
+// x_inv_scale[r] = the scale that came with row r's record (f16 rows on the wire)
+__global__ void ep_row_scales_kernel(const qkm_sel* __restrict__ selrecv, float* __restrict__ x_inv_scale, uint32_t n_rows) {
+    const uint32_t r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r < n_rows) x_inv_scale[r] = __uint_as_float(reinterpret_cast<const uint32_t*>(selrecv + r)[kSelScaleWord]);
 }
 
 // Slot row (source s, token i) of the local partial rows goes to rank s's return buffer at
@@ -234,12 +256,21 @@ cudaError_t launch_ep_barrier(const Launch& L, const EpPeerTable& peers, uint32_
     return cudaGetLastError();
 }
 
+cudaError_t launch_ep_row_scales(const Launch& L, const qkm_sel* selrecv, float* x_inv_scale, uint32_t n_rows) {
+    if (n_rows == 0) return cudaSuccess;
+    ep_row_scales_kernel<<<(n_rows + 255) / 256, 256, 0, L.stream>>>(selrecv, x_inv_scale, n_rows);
+    L.count();
+    return cudaGetLastError();
+}
+
 cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel, const EpPeerTable& peers,
-                           uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks) {
+                           uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, const void* xh,
+                           const float* x_inv_scale) {
     if (n_ranks == 0 || n_ranks > kMaxPeerRanks || d.n_expert % n_ranks || rank >= n_ranks || n_tokens > slot_rows)
         return cudaErrorInvalidValue;
     if (slot_rows == 0) return cudaSuccess;
-    ep_push_kernel<<<slot_rows, 256, 0, L.stream>>>(x, sel, peers, n_tokens, slot_rows, rank, n_ranks, d.n_used,
+    if ((xh != nullptr) != (x_inv_scale != nullptr) || (xh && d.n_embd % 8)) return cudaErrorInvalidValue;
+    ep_push_kernel<<<slot_rows, 256, 0, L.stream>>>(x, (const __half*)xh, x_inv_scale, sel, peers, n_tokens, slot_rows, rank, n_ranks, d.n_used,
                                                     d.n_expert / n_ranks, d.n_embd);
     L.count();
     return cudaGetLastError();

@@ -289,8 +289,12 @@ struct EpPeerTable {
 };
 cudaError_t launch_ep_barrier(const Launch& L, const EpPeerTable& peers, uint32_t rank, uint32_t n_ranks, uint32_t epoch,
                               uint64_t limit_ns, uint32_t* status);
+// xh / x_inv_scale: the rows as scaled f16 (to_f16_rows_kernel) - then those travel instead of the f32 rows
 cudaError_t launch_ep_push(const Launch& L, const qkm_dims& d, const float* x, const qkm_sel* sel, const EpPeerTable& peers,
-                           uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
+                           uint32_t n_tokens, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks, const void* xh = nullptr,
+                           const float* x_inv_scale = nullptr);
+cudaError_t launch_ep_row_scales(const Launch& L, const qkm_sel* selrecv, float* x_inv_scale, uint32_t n_rows);
+constexpr uint32_t kSelScaleWord = 34;   // first padding word of a selection record (ids 0-15, w 16-31, w_shared, route_done, pad)
 cudaError_t launch_fold_pairs_peer(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,
                                    const EpPeerTable& peers, uint32_t slot_rows, uint32_t rank, uint32_t n_ranks);
 cudaError_t launch_ep_return(const Launch& L, const qkm_dims& d, const float* partial, const qkm_sel* selrecv,

@@ -183,7 +183,18 @@ def run_ep_peer(pkg, orc, syn, dims, layer, x_parts, G, tol, slot_rows=None, cap
             need = ((sels[s]["ids"][:, :dims.n_used] // per) == d).any(axis=1) if n else np.zeros(0, bool)
             got = sr[s * rows:(s + 1) * rows]
             assert np.array_equal(got["ids"][:n][need], sels[s]["ids"][need])
-            assert np.array_equal(xr[s * rows:s * rows + n][need], x_parts[s][need])
+            if n and need.any():
+                inv = got["pad"][:n, 0][need]
+                if (inv != 0).all():
+                    # rows travel as f16, scaled per row by a power of two (max|x| lands in [2^13, 2^14)), at the
+                    # head of the row buffer; the scale that undoes it rides in the record's first padding word
+                    xh = xr.view(np.float16).reshape(-1)[:G * rows * E].reshape(G * rows, E)[s * rows:s * rows + n][need]
+                    xs = x_parts[s][need]
+                    up = np.float32(2.0) ** (14 - (np.frexp(np.abs(xs).max(axis=1))[1]))
+                    assert np.array_equal(inv, (1.0 / up).astype(np.float32))
+                    assert np.array_equal(xh, (xs * up[:, None]).astype(np.float16))
+                else:
+                    assert np.array_equal(xr[s * rows:s * rows + n][need], x_parts[s][need])
             empty = np.ones(rows, bool)
             empty[:n] = ~need
             assert (got["ids"][empty][:, :dims.n_used] == 0xFFFFFFFF).all()
