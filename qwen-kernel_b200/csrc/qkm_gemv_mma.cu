@@ -209,11 +209,229 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restric
     if (timed_out && lane == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
+// ---- Q6_K ------------------------------------------------------------------------------------------------
+// Rows of a Q6_K matrix are 210 bytes per 256 columns, so a warp's column block is not 16-byte
+// aligned inside the row and cannot be fetched on its own; but a tile of 16 rows is one contiguous,
+// 16-byte aligned run of the matrix, and for K = 2048 its row stride (420 words) spreads the eight row
+// groups over different banks as it is.  So the whole tile comes in with ONE bulk copy into a
+// block-wide ring, and every warp reads its block from there.  Inside a block the 6-bit values are
+// put together from ql (low nibbles) and qh (two high bits) four at a time, turned into int8 q - 32,
+// and multiplied 16 columns at a time (mma.sync.m16n8k16.s8: one int8 scale per 16 columns, applied
+// to the integer sums), then by the block's f16 scale.
+namespace gq {
+constexpr int kRows = 16;
+constexpr int kGroup = 4;          // tiles between two reductions over the warps
+constexpr int kMaxStages = 8;
+}  // namespace gq
+
+__device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
+}
+// a 32-bit word at a 2-byte aligned shared address (ODD: the address is 2 mod 4)
+template <bool ODD>
+__device__ __forceinline__ uint32_t lds32_a2(uint32_t addr) {
+    if (!ODD) return lds32(addr);
+    return __funnelshift_r(lds32(addr - 2), lds32(addr + 2), 16);
+}
+// four 6-bit values (ql nibbles | qh bit pairs << 4) as int8 q - 32
+__device__ __forceinline__ uint32_t q6_to_s8(uint32_t wl, uint32_t wh, int nib_hi, int hshift) {
+    const uint32_t q = ((wl >> (4 * nib_hi)) & 0x0F0F0F0Fu) | (((wh >> hshift) & 0x03030303u) << 4);
+    const uint32_t v = q ^ 0x20202020u;          // q < 32: v = q + 32 (bit 5 set), and q - 32 = v - 64 = v | 0xC0 as int8
+    const uint32_t n = v & 0x20202020u;          // q >= 32: v = q - 32 already
+    return v | (n << 1) | (n << 2);
+}
+
+template <bool ODD>
+__device__ __forceinline__ void q6k_tile(uint32_t blk0, uint32_t blk1, uint32_t t, const uint32_t (&bq)[16], float plane_w,
+                                         float& f0, float& f1) {
+    // blk0 / blk1: this warp's block of rows g / g+8 in the stage.  The sixteen scales of each row as four words.
+    uint32_t sc0[4], sc1[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) { sc0[k] = lds32_a2<ODD>(blk0 + 192 + 4 * k); sc1[k] = lds32_a2<ODD>(blk1 + 192 + 4 * k); }
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int G0 = 0; G0 < 16; G0 += 4) {   // four groups of 16 columns: all their words are requested first
+        uint32_t wl0[4], wh0[4], wl1[4], wh1[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int G = G0 + u, hf = G >> 3, qd = (G & 7) >> 1, lofs = 16 * (G & 1);
+            const uint32_t ql = 64 * hf + 32 * (qd & 1) + lofs + 4 * t, qh = 128 + 32 * hf + lofs + 4 * t;
+            wl0[u] = lds32_a2<ODD>(blk0 + ql); wh0[u] = lds32_a2<ODD>(blk0 + qh);
+            wl1[u] = lds32_a2<ODD>(blk1 + ql); wh1[u] = lds32_a2<ODD>(blk1 + qh);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int G = G0 + u, qd = (G & 7) >> 1;
+            int c[4] = {0, 0, 0, 0};
+            mma_s8_k16(c, q6_to_s8(wl0[u], wh0[u], qd >> 1, 2 * qd), q6_to_s8(wl1[u], wh1[u], qd >> 1, 2 * qd), bq[G]);
+            const int a = (int)(int8_t)(sc0[G >> 2] >> (8 * (G & 3))), b = (int)(int8_t)(sc1[G >> 2] >> (8 * (G & 3)));
+            s0 += (float)((c[0] + (c[1] << 7)) * a);
+            s1 += (float)((c[2] + (c[3] << 7)) * b);
+        }
+    }
+    uint32_t d0, d1;
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d0) : "r"(blk0 + 208));
+    asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d1) : "r"(blk1 + 208));
+    f0 = s0 * plane_w * f16_bits_to_f32(d0);
+    f1 = s1 * plane_w * f16_bits_to_f32(d1);
+}
+
+__global__ void __launch_bounds__(gm::kMaxWarps * 32)
+gemv_q6k_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, uint32_t n_tiles,
+                uint32_t K, uint32_t rb, uint32_t n_stages, uint32_t* __restrict__ status) {
+    extern __shared__ __align__(128) uint8_t smem_raw[];
+    __shared__ __align__(8) unsigned long long s_bar[2 * gq::kMaxStages];   // full[stage], empty[stage]
+    __shared__ float s_max[gm::kMaxWarps];
+    __shared__ float s_scale;
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
+    const uint32_t KB = K / 256, n_threads = KB * 32;
+    // layout: digit planes [KB][4][256] | partial sums [2][KB][kGroup * 16] | stages [n_stages][16 rows][rb]
+    int8_t* planes = reinterpret_cast<int8_t*>(smem_raw);
+    float* red = reinterpret_cast<float*>(smem_raw + (size_t)K * 4);
+    const uint32_t red_floats = KB * gq::kGroup * gq::kRows;
+    const uint32_t stage0 = (smem_addr(smem_raw) + K * 4 + 2 * red_floats * 4 + 127u) & ~127u;
+    const uint32_t stage_bytes = (gq::kRows * rb + 127u) & ~127u;
+    const uint32_t bar_full = smem_addr(&s_bar[0]), bar_empty = smem_addr(&s_bar[gq::kMaxStages]);
+    bool timed_out = false;
+
+    if (tid == 0) {
+        for (uint32_t s = 0; s < n_stages; ++s) { mbar_init(bar_full + 8 * s, 1); mbar_init(bar_empty + 8 * s, KB); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    const uint32_t my_tiles = blockIdx.x < n_tiles ? (n_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0u;
+    auto issue = [&](uint32_t i) {   // tile number i of this block into stage i % n_stages: one copy; thread 0
+        const uint32_t s = i % n_stages;
+        mbar_expect_tx(bar_full + 8 * s, gq::kRows * rb);
+        bulk_g2s(stage0 + s * stage_bytes, W + (size_t)(blockIdx.x + i * gridDim.x) * gq::kRows * rb, gq::kRows * rb, bar_full + 8 * s);
+    };
+    if (tid == 0)
+        for (uint32_t i = 0; i + 1 < n_stages && i < my_tiles; ++i) issue(i);
+
+    // x as digit planes (the first tiles are on their way meanwhile)
+    {
+        float m = 0.f;
+        bool bad = false;
+        for (uint32_t k = tid; k < K; k += n_threads) {
+            const float v = x[k];
+            bad |= !(fabsf(v) <= 3.0e38f);
+            m = fmaxf(m, fabsf(v));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        const int any_bad = __syncthreads_or(bad ? 1 : 0);
+        if (lane == 0) s_max[warp] = m;
+        __syncthreads();
+        m = 0.f;
+        for (uint32_t w = 0; w < KB; ++w) m = fmaxf(m, s_max[w]);
+        const int p = digit_exponent(m);
+        const float up = ldexpf(1.0f, p);
+        for (uint32_t k = tid; k < K; k += n_threads) {
+            const uint32_t dgt = any_bad ? 0u : digits4(__float2int_rn(x[k] * up));
+            int8_t* q = planes + (size_t)(k >> 8) * 1024 + (k & 255u);
+            q[0] = (int8_t)(dgt & 255u);
+            q[256] = (int8_t)((dgt >> 8) & 255u);
+            q[512] = (int8_t)((dgt >> 16) & 255u);
+            q[768] = (int8_t)(dgt >> 24);
+        }
+        if (tid == 0) s_scale = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
+        __syncthreads();
+    }
+    // B operands of this warp's 256 columns, 16 columns each: column n = g is digit plane g (g < 4), k = 4t..4t+3
+    uint32_t bq[16];
+    {
+        const uint32_t pl = smem_addr(planes) + warp * 1024u;
+#pragma unroll
+        for (int G = 0; G < 16; ++G) bq[G] = g < 4 ? lds32(pl + g * 256 + G * 16 + t * 4) : 0u;
+    }
+    const float plane_w = t == 0 ? 1.f : (t == 1 ? 16384.f : 0.f);
+    const float xscale = s_scale;
+    const bool odd = (warp & 1u) != 0;   // 210 * warp is 2 mod 4 for odd warps (K / 256 is even: rows start on word boundaries)
+
+    uint32_t buf = 0;
+    for (uint32_t i0 = 0; i0 < my_tiles; i0 += gq::kGroup) {
+        const uint32_t in_group = min((uint32_t)gq::kGroup, my_tiles - i0);
+        float acc[gq::kGroup][2];
+#pragma unroll
+        for (int q = 0; q < gq::kGroup; ++q) {
+            acc[q][0] = acc[q][1] = 0.f;
+            const uint32_t i = i0 + q;
+            if (i < my_tiles) {   // block-uniform
+                const uint32_t s = i % n_stages;
+                if (tid == 0 && i + n_stages - 1 < my_tiles) {   // refill the stage the block left one tile ago
+                    const uint32_t j = i + n_stages - 1, sj = j % n_stages;
+                    if (j >= n_stages && !mbar_wait_bounded(bar_empty + 8 * sj, ((j / n_stages) - 1) & 1u)) timed_out = true;
+                    issue(j);
+                }
+                if (!mbar_wait_bounded(bar_full + 8 * s, (i / n_stages) & 1u)) timed_out = true;
+                const uint32_t blk0 = stage0 + s * stage_bytes + g * rb + 210u * warp, blk1 = blk0 + 8u * rb;
+                float f0, f1;
+                if (odd) q6k_tile<true>(blk0, blk1, t, bq, plane_w, f0, f1);
+                else q6k_tile<false>(blk0, blk1, t, bq, plane_w, f0, f1);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+                acc[q][0] = f0; acc[q][1] = f1;
+            }
+        }
+        float* rw = red + (size_t)buf * red_floats + (size_t)warp * gq::kGroup * gq::kRows;
+#pragma unroll
+        for (int q = 0; q < gq::kGroup; ++q) {
+            float v0 = acc[q][0], v1 = acc[q][1];
+            v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 1); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 1);
+            if (t == 0) { rw[q * gq::kRows + g] = v0; rw[q * gq::kRows + g + 8] = v1; }
+        }
+        __syncthreads();
+        for (uint32_t o = tid; o < in_group * gq::kRows; o += n_threads) {
+            const float* rr = red + (size_t)buf * red_floats + o;
+            float v = 0.f;
+            for (uint32_t w = 0; w < KB; ++w) v += rr[(size_t)w * gq::kGroup * gq::kRows];
+            const uint32_t q = o / gq::kRows, r = o - q * gq::kRows;
+            const uint32_t tile = blockIdx.x + (i0 + q) * gridDim.x;
+            y[(size_t)tile * gq::kRows + r] = v * xscale;
+        }
+        buf ^= 1u;
+    }
+    if (timed_out && lane == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
+}
+
+static cudaError_t gemv_q6k_launch(const Launch& L, const void* W, const float* x, float* y, uint32_t M, uint32_t K,
+                                   uint32_t n_sms, uint32_t* status, uint32_t* rows_done) {
+    const uint32_t KB = K / 256;
+    if (K % 512 != 0 || KB > (uint32_t)gm::kMaxWarps || M < (uint32_t)gq::kRows) return cudaSuccess;   // an even number of blocks per row
+    const uint32_t rb = 210u * KB;
+    const size_t fixed = (size_t)K * 4 + 2 * (size_t)KB * gq::kGroup * gq::kRows * 4 + 256;
+    const size_t stage = ((size_t)gq::kRows * rb + 127) / 128 * 128;
+    // two blocks per SM with three stages each where that fits (the kernel is bound by its own instructions,
+    // so warps count), else one block with as many stages as fit
+    uint32_t n_stages = 3;
+    uint32_t per_sm = 2;
+    if (fixed + 3 * stage > 110u * 1024u) {
+        per_sm = 1;
+        n_stages = gq::kMaxStages;
+        while (n_stages > 2 && fixed + n_stages * stage > 200u * 1024u) --n_stages;
+    }
+    const size_t smem = fixed + n_stages * stage;
+    if (smem > 220u * 1024u) return cudaSuccess;
+    cudaError_t e = cudaFuncSetAttribute(gemv_q6k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+    const uint32_t n_tiles = M / gq::kRows;
+    const uint32_t blocks = n_tiles < per_sm * n_sms ? n_tiles : per_sm * n_sms;
+    gemv_q6k_kernel<<<blocks, KB * 32, smem, L.stream>>>((const uint8_t*)W, x, y, n_tiles, K, rb, n_stages, status);
+    L.count();
+    *rows_done = n_tiles * gq::kRows;
+    return cudaGetLastError();
+}
+
 // Rows [0, *rows_done) are computed here; the caller finishes the rest.  Shapes this form does not take
 // leave *rows_done at 0.
 cudaError_t launch_gemv_mma(const Launch& L, uint32_t type, const void* W, const float* x, float* y, uint32_t M,
                             uint32_t K, uint32_t n_sms, uint32_t* status, uint32_t* rows_done) {
     *rows_done = 0;
+    if (type == QKM_TYPE_Q6_K) {
+        if (((uintptr_t)W & 15u) || ((uintptr_t)x & 3u) || status == nullptr) return cudaSuccess;
+        return gemv_q6k_launch(L, W, x, y, M, K, n_sms, status, rows_done);
+    }
     if (type != QKM_TYPE_Q8_0 || K % 256 != 0 || K < 512 || K > 256u * gm::kMaxWarps || M < (uint32_t)gm::kRows) return cudaSuccess;
     if (((uintptr_t)W & 15u) || ((uintptr_t)x & 3u) || status == nullptr) return cudaSuccess;
     const uint32_t rb = (uint32_t)row_bytes(type, K);   // a multiple of 16 for K % 256 == 0
