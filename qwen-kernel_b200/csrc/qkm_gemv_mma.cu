@@ -236,10 +236,12 @@ __device__ __forceinline__ uint32_t lds32_a2(uint32_t addr) {
 }
 // four 6-bit values (ql nibbles | qh bit pairs << 4) as int8 q - 32
 __device__ __forceinline__ uint32_t q6_to_s8(uint32_t wl, uint32_t wh, int nib_hi, int hshift) {
-    const uint32_t q = ((wl >> (4 * nib_hi)) & 0x0F0F0F0Fu) | (((wh >> hshift) & 0x03030303u) << 4);
+    const uint32_t lo = nib_hi ? wl >> 4 : wl;
+    const uint32_t hi = hshift < 4 ? wh << (4 - hshift) : wh >> (hshift - 4);   // the bit pair to bits 4, 5 of each byte
+    const uint32_t q = (hi & 0x30303030u) | (lo & 0x0F0F0F0Fu);
     const uint32_t v = q ^ 0x20202020u;          // q < 32: v = q + 32 (bit 5 set), and q - 32 = v - 64 = v | 0xC0 as int8
     const uint32_t n = v & 0x20202020u;          // q >= 32: v = q - 32 already
-    return v | (n << 1) | (n << 2);
+    return v + n * 6u;                           // | (n << 1) | (n << 2): no bits overlap, one multiply-add
 }
 
 template <bool ODD>
