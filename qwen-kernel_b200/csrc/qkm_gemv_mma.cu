@@ -209,7 +209,7 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restric
     if (timed_out && lane == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
-// ---- Q6_K ------------------------------------------------------------------------------------------------
+// ---- Q6_K and IQ4_XS: a block-wide ring of whole tiles -----------------------------------------------------
 // Rows of a Q6_K matrix are 210 bytes per 256 columns, so a warp's column block is not 16-byte
 // aligned inside the row and cannot be fetched on its own; but a tile of 16 rows is one contiguous,
 // 16-byte aligned run of the matrix, and for K = 2048 its row stride (420 words) spreads the eight row
@@ -279,8 +279,66 @@ __device__ __forceinline__ void q6k_tile(uint32_t blk0, uint32_t blk1, uint32_t 
     f1 = s1 * plane_w * f16_bits_to_f32(d1);
 }
 
-__global__ void __launch_bounds__(gm::kMaxWarps * 32)
-gemv_q6k_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, uint32_t n_tiles,
+// ---- IQ4_XS (in the same block-wide ring) -------------------------------------------------------------------
+// A row is 136 bytes per 256 columns (d, scales_h, scales_l, 128 quant bytes), always word aligned.  A quant
+// word holds elements 4t..4t+3 (low nibbles) and 16+4t..16+4t+3 (high nibbles) of a 32-column sub-block;
+// the 16-entry codebook sits in four registers and is looked up with byte permutes, which leaves the
+// values in the order (e, 16+e, e+1, 16+e+1 | e+2, ...): the B operand is loaded in that order too.
+__device__ __forceinline__ uint32_t prmt_r(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+__device__ __forceinline__ void iq4_codebook_word(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;   // kvalues_iq4nl as int8
+    const uint32_t s = w & 0x77777777u, s2 = s >> 16, w4 = w << 4;
+    // byte j of a mask is 0xFF when nibble j (of the low / high half-word) has its top bit set
+    const uint32_t m_lo = prmt_r(w4, w, 0xD9C8u), m_hi = prmt_r(w4, w, 0xFBEAu);
+    const uint32_t a_lo = prmt_r(T0, T1, s), b_lo = prmt_r(T2, T3, s);
+    const uint32_t a_hi = prmt_r(T0, T1, s2), b_hi = prmt_r(T2, T3, s2);
+    lo = (a_lo & ~m_lo) | (b_lo & m_lo);
+    hi = (a_hi & ~m_hi) | (b_hi & m_hi);
+}
+// the eight sub-block scales ls - 32 of one row as int8: sub-blocks 0,2,4,6 in ev, 1,3,5,7 in od
+// (scales_l: eight 4-bit fields, scales_h: eight 2-bit fields; src/quants.h:107-113, :139-146)
+__device__ __forceinline__ void iq4_row_scales(uint32_t sl, uint32_t sh, uint32_t& ev, uint32_t& od) {
+    const uint32_t r = prmt_r(sh, 0u, 0x1100u);                        // bytes (B0, B0, B1, B1) of scales_h
+    const uint32_t he = ((r << 4) & 0x00300030u) | (r & 0x30003000u);  // top two bits of sub-blocks 0,2,4,6 at bits 4..5
+    const uint32_t ho = ((r << 2) & 0x00300030u) | ((r >> 2) & 0x30003000u);
+    const uint32_t te = ((sl & 0x0F0F0F0Fu) | he) ^ 0x20202020u;       // ls ^ 32 per byte
+    const uint32_t to = (((sl >> 4) & 0x0F0F0F0Fu) | ho) ^ 0x20202020u;
+    ev = (te & 0x20202020u) * 6u + te;                                 // ls - 32 as int8 (bit 5 extended into bits 6..7)
+    od = (to & 0x20202020u) * 6u + to;
+}
+__device__ __forceinline__ void iq4_tile(uint32_t blk0, uint32_t blk1, uint32_t t, const uint32_t (&b0)[8], const uint32_t (&b1)[8],
+                                         float plane_w, float& f0, float& f1) {
+    const uint32_t h0 = lds32(blk0), h1 = lds32(blk1);   // d | scales_h << 16
+    uint32_t ev0, od0, ev1, od1;
+    iq4_row_scales(lds32(blk0 + 4), h0 >> 16, ev0, od0);
+    iq4_row_scales(lds32(blk1 + 4), h1 >> 16, ev1, od1);
+    uint32_t w0[8], w1[8];
+#pragma unroll
+    for (int sb = 0; sb < 8; ++sb) { w0[sb] = lds32(blk0 + 8 + 16 * sb + 4 * t); w1[sb] = lds32(blk1 + 8 + 16 * sb + 4 * t); }
+    float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+    for (int sb = 0; sb < 8; ++sb) {
+        uint32_t a0, a1, a2, a3;
+        iq4_codebook_word(w0[sb], a0, a2);
+        iq4_codebook_word(w1[sb], a1, a3);
+        int c[4] = {0, 0, 0, 0};
+        mma_s8(c, a0, a1, a2, a3, b0[sb], b1[sb]);
+        const int l0 = (int)(int8_t)(((sb & 1) ? od0 : ev0) >> (8 * (sb >> 1)));
+        const int l1 = (int)(int8_t)(((sb & 1) ? od1 : ev1) >> (8 * (sb >> 1)));
+        s0 += (float)((c[0] + (c[1] << 7)) * l0);
+        s1 += (float)((c[2] + (c[3] << 7)) * l1);
+    }
+    f0 = s0 * plane_w * f16_bits_to_f32(h0 & 0xFFFFu);
+    f1 = s1 * plane_w * f16_bits_to_f32(h1 & 0xFFFFu);
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(gm::kMaxWarps * 32, 1)
+gemv_tile_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, float* __restrict__ y, uint32_t n_tiles,
                 uint32_t K, uint32_t rb, uint32_t n_stages, uint32_t* __restrict__ status) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
     __shared__ __align__(8) unsigned long long s_bar[2 * gq::kMaxStages];   // full[stage], empty[stage]
@@ -340,16 +398,29 @@ gemv_q6k_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, floa
         if (tid == 0) s_scale = any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p);
         __syncthreads();
     }
-    // B operands of this warp's 256 columns, 16 columns each: column n = g is digit plane g (g < 4), k = 4t..4t+3
+    static_assert(TYPE == QKM_TYPE_Q6_K || TYPE == QKM_TYPE_IQ4_XS, "formats: Q6_K, IQ4_XS");
+    constexpr uint32_t kBlockBytes = TYPE == QKM_TYPE_Q6_K ? 210u : 136u;
+    // B operands of this warp's 256 columns: column n = g is digit plane g (g < 4).  Q6_K: 16 columns each,
+    // k = 4t..4t+3.  IQ4_XS: 32 columns each in the codebook look-up's element order (see iq4_codebook_word).
     uint32_t bq[16];
     {
         const uint32_t pl = smem_addr(planes) + warp * 1024u;
+        if (TYPE == QKM_TYPE_Q6_K) {
 #pragma unroll
-        for (int G = 0; G < 16; ++G) bq[G] = g < 4 ? lds32(pl + g * 256 + G * 16 + t * 4) : 0u;
+            for (int G = 0; G < 16; ++G) bq[G] = g < 4 ? lds32(pl + g * 256 + G * 16 + t * 4) : 0u;
+        } else {
+#pragma unroll
+            for (int sb = 0; sb < 8; ++sb) {
+                const uint32_t wa = g < 4 ? lds32(pl + g * 256 + sb * 32 + t * 4) : 0u;        // elements 4t .. 4t+3
+                const uint32_t wb = g < 4 ? lds32(pl + g * 256 + sb * 32 + 16 + t * 4) : 0u;   // elements 16+4t ..
+                bq[sb] = prmt_r(wa, wb, 0x5140u);       // e, 16+e, e+1, 16+e+1
+                bq[8 + sb] = prmt_r(wa, wb, 0x7362u);   // e+2, 16+e+2, e+3, 16+e+3
+            }
+        }
     }
     const float plane_w = t == 0 ? 1.f : (t == 1 ? 16384.f : 0.f);
     const float xscale = s_scale;
-    const bool odd = (warp & 1u) != 0;   // 210 * warp is 2 mod 4 for odd warps (K / 256 is even: rows start on word boundaries)
+    const bool odd = TYPE == QKM_TYPE_Q6_K && (warp & 1u) != 0;   // 210 * warp is 2 mod 4 for odd warps (K / 256 is even: rows start on word boundaries)
 
     uint32_t buf = 0;
     for (uint32_t i0 = 0; i0 < my_tiles; i0 += gq::kGroup) {
@@ -367,10 +438,18 @@ gemv_q6k_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, floa
                     issue(j);
                 }
                 if (!mbar_wait_bounded(bar_full + 8 * s, (i / n_stages) & 1u)) timed_out = true;
-                const uint32_t blk0 = stage0 + s * stage_bytes + g * rb + 210u * warp, blk1 = blk0 + 8u * rb;
+                const uint32_t blk0 = stage0 + s * stage_bytes + g * rb + kBlockBytes * warp, blk1 = blk0 + 8u * rb;
                 float f0, f1;
-                if (odd) q6k_tile<true>(blk0, blk1, t, bq, plane_w, f0, f1);
-                else q6k_tile<false>(blk0, blk1, t, bq, plane_w, f0, f1);
+                if (TYPE == QKM_TYPE_IQ4_XS) {
+                    uint32_t b0[8], b1[8];
+#pragma unroll
+                    for (int sb = 0; sb < 8; ++sb) { b0[sb] = bq[sb]; b1[sb] = bq[8 + sb]; }
+                    iq4_tile(blk0, blk1, t, b0, b1, plane_w, f0, f1);
+                } else if (odd) {
+                    q6k_tile<true>(blk0, blk1, t, bq, plane_w, f0, f1);
+                } else {
+                    q6k_tile<false>(blk0, blk1, t, bq, plane_w, f0, f1);
+                }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * s);
                 acc[q][0] = f0; acc[q][1] = f1;
@@ -397,11 +476,12 @@ gemv_q6k_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, floa
     if (timed_out && lane == 0) atomicExch(status, (uint32_t)kStatusWaitTimeout);
 }
 
-static cudaError_t gemv_q6k_launch(const Launch& L, const void* W, const float* x, float* y, uint32_t M, uint32_t K,
-                                   uint32_t n_sms, uint32_t* status, uint32_t* rows_done) {
+template <int TYPE>
+static cudaError_t gemv_tile_launch(const Launch& L, const void* W, const float* x, float* y, uint32_t M, uint32_t K,
+                                    uint32_t n_sms, uint32_t* status, uint32_t* rows_done) {
     const uint32_t KB = K / 256;
     if (K % 512 != 0 || KB > (uint32_t)gm::kMaxWarps || M < (uint32_t)gq::kRows) return cudaSuccess;   // an even number of blocks per row
-    const uint32_t rb = 210u * KB;
+    const uint32_t rb = (TYPE == QKM_TYPE_Q6_K ? 210u : 136u) * KB;
     const size_t fixed = (size_t)K * 4 + 2 * (size_t)KB * gq::kGroup * gq::kRows * 4 + 256;
     const size_t stage = ((size_t)gq::kRows * rb + 127) / 128 * 128;
     // two blocks per SM with three stages each where that fits (the kernel is bound by its own instructions,
@@ -415,11 +495,11 @@ static cudaError_t gemv_q6k_launch(const Launch& L, const void* W, const float* 
     }
     const size_t smem = fixed + n_stages * stage;
     if (smem > 220u * 1024u) return cudaSuccess;
-    cudaError_t e = cudaFuncSetAttribute(gemv_q6k_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(gemv_tile_kernel<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const uint32_t n_tiles = M / gq::kRows;
     const uint32_t blocks = n_tiles < per_sm * n_sms ? n_tiles : per_sm * n_sms;
-    gemv_q6k_kernel<<<blocks, KB * 32, smem, L.stream>>>((const uint8_t*)W, x, y, n_tiles, K, rb, n_stages, status);
+    gemv_tile_kernel<TYPE><<<blocks, KB * 32, smem, L.stream>>>((const uint8_t*)W, x, y, n_tiles, K, rb, n_stages, status);
     L.count();
     *rows_done = n_tiles * gq::kRows;
     return cudaGetLastError();
@@ -430,9 +510,10 @@ static cudaError_t gemv_q6k_launch(const Launch& L, const void* W, const float* 
 cudaError_t launch_gemv_mma(const Launch& L, uint32_t type, const void* W, const float* x, float* y, uint32_t M,
                             uint32_t K, uint32_t n_sms, uint32_t* status, uint32_t* rows_done) {
     *rows_done = 0;
-    if (type == QKM_TYPE_Q6_K) {
+    if (type == QKM_TYPE_Q6_K || type == QKM_TYPE_IQ4_XS) {
         if (((uintptr_t)W & 15u) || ((uintptr_t)x & 3u) || status == nullptr) return cudaSuccess;
-        return gemv_q6k_launch(L, W, x, y, M, K, n_sms, status, rows_done);
+        return type == QKM_TYPE_Q6_K ? gemv_tile_launch<QKM_TYPE_Q6_K>(L, W, x, y, M, K, n_sms, status, rows_done)
+                                     : gemv_tile_launch<QKM_TYPE_IQ4_XS>(L, W, x, y, M, K, n_sms, status, rows_done);
     }
     if (type != QKM_TYPE_Q8_0 || K % 256 != 0 || K < 512 || K > 256u * gm::kMaxWarps || M < (uint32_t)gm::kRows) return cudaSuccess;
     if (((uintptr_t)W & 15u) || ((uintptr_t)x & 3u) || status == nullptr) return cudaSuccess;
