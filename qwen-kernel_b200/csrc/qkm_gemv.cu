@@ -348,7 +348,9 @@ cudaError_t launch_gemv_stream(const Launch& L, uint32_t type, const void* W, co
     uint32_t done = 0;
     cudaError_t e;
     const bool aligned = !((uintptr_t)W & 15u) && !((uintptr_t)x & 15u) && (type != QKM_TYPE_IQ4_XS || K % 256 == 0);
-    if (n == 1 && aligned && (size_t)M * row_bytes(type, K) <= kDirectMaxBytes && type != QKM_TYPE_F32) {
+    // (the integer tensor-core kernels win from about 8192 rows on for the two formats whose unpacking is costly)
+    const bool try_mma_small = M >= 8192 && (type == QKM_TYPE_Q6_K || type == QKM_TYPE_IQ4_XS);
+    if (n == 1 && aligned && (size_t)M * row_bytes(type, K) <= kDirectMaxBytes && type != QKM_TYPE_F32 && !try_mma_small) {
         switch (type) {
             case QKM_TYPE_F16: return gemv_direct_launch<QKM_TYPE_F16>(L, w, x, y, M, K);
             case QKM_TYPE_Q8_0: return gemv_direct_launch<QKM_TYPE_Q8_0>(L, w, x, y, M, K);
