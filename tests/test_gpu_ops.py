@@ -78,6 +78,24 @@ def test_gemv_streamed_large_matrix(ctx, orc, syn, ttype, M, K):
         b.free()
 
 
+@pytest.mark.parametrize("ttype,M,K", [(14, 8192, 2048), (23, 8192, 2048), (14, 8200, 4096), (23, 8208, 1024), (8, 40000, 2048),
+                                       (14, 40016, 512), (8, 30008, 3072)])
+def test_gemv_tensor_core_forms(ctx, orc, syn, ttype, M, K):
+    """The integer tensor-core GEMV kernels (digit planes x quantised weights): Q6_K and IQ4_XS from
+    8192 rows on, Q8_0 above 48 MB; row counts that leave a tail of fewer than 16 rows, and other K."""
+    W = syn.random_blocks(ttype, M, K, seed=7 * ttype + 1)
+    x = syn.random_x(1, K, seed=45)
+    x[0, 5] = 40.0          # one large element: the small ones keep fewer bits of the fixed-point planes
+    d_w, d_x, d_y = ctx.to_device(W), ctx.to_device(x), ctx.alloc(M * 4)
+    ctx.gemv(ttype, d_w, d_x, d_y, M, K, 1)
+    got = d_y.download(np.float32, (1, M))
+    want = orc.gemv(ttype, W, x, M, K, threads=orc.hardware_threads())
+    assert syn.rel_err_reference(got, want) < TOL_REF_METRIC
+    assert syn.rel_err_rows(got, want) < TOL_F32
+    for b in (d_w, d_x, d_y):
+        b.free()
+
+
 def test_gemv_rejects_bad_shapes(ctx, pkg):
     d = ctx.alloc(4096)
     for ttype, K in ((8, 48), (14, 128), (18, 300), (99, 256)):
