@@ -75,7 +75,8 @@ struct qkm_ctx {
     bool shapes_stream_ok = false;
     // prefill (tcgen05) scratch, allocated on first use
     void* xb = nullptr;               // [max_tokens][n_embd] f16, rows scaled by powers of two (xscale undoes it)
-    void* hb = nullptr;               // [max_tokens*(n_used+1)][n_ff] bf16
+    void* hb = nullptr;               // [max_tokens*(n_used+1)][n_ff] hidden rows by pair position: f16 scaled per row (bf16 on the f32-down path)
+    float* hscale = nullptr;          // [max_tokens*(n_used+1)] the scales that undo the rows' scaling
     float* contrib_p = nullptr;       // [max_tokens*(n_used+1)][n_embd]
     MmaItem* mma_items[4] = {nullptr, nullptr, nullptr, nullptr};  // gate/up, down, shared gate/up, shared down
     uint32_t* pos_of = nullptr;       // [max_tokens*(n_used+1)]
@@ -348,7 +349,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
                        c->planes8, c->lut_gu, c->lut_pf, c->lut_dn,
-                       c->xb, c->hb, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
+                       c->xb, c->hb, c->hscale, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
     for (auto& o : c->pm_opened) for (void* p : o) if (p) cudaIpcCloseMemHandle(p);
@@ -747,6 +748,7 @@ static int ensure_prefill_scratch(qkm_ctx* c) {
     const size_t max_tiles = d.n_expert + (T * d.n_used + NT - 1) / NT, max_sh = (T + NT - 1) / NT;
     QKM_CUDA(c, cudaMalloc(&c->xb, T * d.n_embd * 2));
     QKM_CUDA(c, cudaMalloc(&c->hb, rows * d.n_ff * 2));
+    QKM_CUDA(c, cudaMalloc((void**)&c->hscale, rows * sizeof(float)));
     QKM_CUDA(c, cudaMalloc((void**)&c->contrib_p, rows * d.n_embd * sizeof(float)));
     QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[0], max_tiles * rt_gu * sizeof(MmaItem)));
     QKM_CUDA(c, cudaMalloc((void**)&c->mma_items[1], max_tiles * rt_dn * sizeof(MmaItem)));
@@ -788,17 +790,24 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
         QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     }
+    // Tensor-core down GEMMs take the hidden rows as f16 scaled per row by a power of two: the gate/up kernels
+    // store them in f32 by pair position (in c->h), a conversion pass finds each row's scale.  Layers whose
+    // down tensor takes the f32 kernels keep h in the reference's layout.
+    float* const h_ref = ld.stream_ok ? nullptr : c->h;
+    float* const h_pos = ld.stream_ok ? c->h : nullptr;
     QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
-                                    c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms));
+                                    c->n_items + 2, sh_now * rt_gu, h_ref, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms, nullptr, h_pos));
     if (!fork) c->prof_mark("moe.shared_gu");
     if (ld.stream_ok) {
+        // the shared expert's rows follow the routed pairs (their number is offsets[ecount], known on the device)
+        QKM_LAUNCH(c, launch_h_rows_to_f16(S, c->h, c->hb, c->hscale, d.n_ff, c->offsets + c->ecount, 0, nullptr, n));
         QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
-                                      c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
+                                      c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status, false, nullptr, c->hscale));
         if (!fork) c->prof_mark("moe.shared_dn");
     }
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, ld.stream_ok ? nullptr : c->h, c->hb, c->status, false, c->lut_pf));   // f32 h only where the f32 down kernels follow
+                                    c->n_items, tiles_now * rt_gu, h_ref, c->hb, c->status, false, c->lut_pf, h_pos));
     c->prof_mark("moe.gu");
     if (!ld.stream_ok) {
         // Q6_K down: the f32 kernels take over from h (per-pair contributions, shared down, fold)
@@ -812,8 +821,9 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
         c->prof_mark("moe.fold");
         return QKM_OK;
     }
+    QKM_LAUNCH(c, launch_h_rows_to_f16(c->L(), c->h, c->hb, c->hscale, d.n_ff, nullptr, 0, c->offsets + c->ecount, n * d.n_used));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, c->sel, c->pairs, c->mma_items[1],
-                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, false, c->lut_dn));
+                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, false, c->lut_dn, c->hscale));
     c->prof_mark("moe.dn");
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, y, n));
@@ -1172,9 +1182,11 @@ extern "C" QKM_API int qkm_ep_shared(qkm_ctx* c, uint32_t layer, const float* x,
                                   c->mma_items[3], c->n_items, c->pos_of, true));
     QKM_LAUNCH(c, launch_to_f16_rows(c->L(), x, c->xb, c->xscale, n, d.n_embd));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
-                                    c->n_items + 2, sh_now * (d.n_ff / 128), c->h, c->hb, c->status, sh_now * (d.n_ff / 128) <= 2u * (uint32_t)c->n_sms));
+                                    c->n_items + 2, sh_now * (d.n_ff / 128), nullptr, c->hb, c->status, sh_now * (d.n_ff / 128) <= 2u * (uint32_t)c->n_sms,
+                                    nullptr, c->h));
+    QKM_LAUNCH(c, launch_h_rows_to_f16(c->L(), c->h, c->hb, c->hscale, d.n_ff, nullptr, 0, nullptr, n));   // the routed list is empty: rows 0 .. n-1
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
-                                  c->n_items + 3, sh_now * (d.n_embd / 128), c->contrib_p, c->status));
+                                  c->n_items + 3, sh_now * (d.n_embd / 128), c->contrib_p, c->status, false, nullptr, c->hscale));
     QKM_LAUNCH(c, launch_fold_pairs(c->L(), d, c->contrib_p, c->pos_of, c->y2, n));
     return QKM_OK;
 }
@@ -1239,17 +1251,20 @@ static int ep_expert_forward_impl(qkm_ctx* c, uint32_t layer, const float* xrecv
         QKM_CUDA(c, cudaEventRecord(c->ev_fork, c->stream));
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
         QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], xb_rows, c->xscale, c->pairs, c->mma_items[2],
-                                        c->n_items + 2, sh_now * rt_gu, c->h, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms));
+                                        c->n_items + 2, sh_now * rt_gu, nullptr, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms,
+                                        nullptr, c->h));
+        QKM_LAUNCH(c, launch_h_rows_to_f16(S, c->h, c->hb, c->hscale, d.n_ff, c->offsets + c->ecount, 0, nullptr, sh_count));
         QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, selrecv, c->pairs, c->mma_items[3],
-                                      c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status));
+                                      c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status, false, nullptr, c->hscale));
         QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     }
     // a shard of few experts launches fewer blocks than the machine holds: faster blocks instead (see the launchers)
     const bool few_gu = c->ecount * rt_gu <= 2u * (uint32_t)c->n_sms, few_dn = c->ecount * rt_dn / 4 <= 2u * (uint32_t)c->n_sms;
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], xb_rows, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, ld.stream_ok ? nullptr : c->h, c->hb, c->status, few_gu, c->lut_pf));
+                                    c->n_items, tiles_now * rt_gu, nullptr, c->hb, c->status, few_gu, c->lut_pf, c->h));
+    QKM_LAUNCH(c, launch_h_rows_to_f16(c->L(), c->h, c->hb, c->hscale, d.n_ff, nullptr, 0, c->offsets + c->ecount, n_recv * d.n_used));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, selrecv, c->pairs, c->mma_items[1],
-                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn, c->lut_dn));
+                                  c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, few_dn, c->lut_dn, c->hscale));
     if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
     if (slot_rows_peer)
         QKM_LAUNCH(c, launch_fold_pairs_peer(c->L(), d, c->contrib_p, c->pos_of, c->pm_peers, slot_rows_peer, c->pm_rank, c->pm_ranks));

@@ -127,13 +127,19 @@ cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
                               uint32_t* status, bool few_blocks = false,   // few_blocks: the grid will not fill the machine
-                              const uint8_t* iq3_table = nullptr);         // IQ3_XXS: the table image (launch_gateup_iq3_table) selects the table-driven kernel
+                              const uint8_t* iq3_table = nullptr,          // IQ3_XXS: the table image (launch_gateup_iq3_table) selects the table-driven kernel
+                              float* hp = nullptr);                        // f32 rows by pair position instead of the bf16 rows in hb (see launch_h_rows_to_f16)
+// rows [first, first + count) of hp (f32, K wide) -> f16 rows scaled per row by a power of two + the inverse scales;
+// first = *first_ptr + first_add (first_ptr may be null), count = min(*count_ptr, count_max) (count_ptr may be null)
+cudaError_t launch_h_rows_to_f16(const Launch& L, const float* hp, void* hh, float* inv_scale, uint32_t K,
+                                 const uint32_t* first_ptr, uint32_t first_add, const uint32_t* count_ptr, uint32_t count_max);
 size_t gateup_iq3_table_bytes();
 cudaError_t launch_gateup_iq3_table(const Launch& L, uint8_t* out);
 cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
                             const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
                             uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks = false,
-                            const uint8_t* iq4_table = nullptr);   // IQ4_XS: the table image (launch_down_iq4_table) selects the table-driven kernel
+                            const uint8_t* iq4_table = nullptr,    // IQ4_XS: the table image (launch_down_iq4_table) selects the table-driven kernel
+                            const float* h_inv_scale = nullptr);   // hb holds scaled f16 rows (launch_h_rows_to_f16): f16 operands
 size_t down_iq4_table_bytes();
 cudaError_t launch_down_iq4_table(const Launch& L, uint8_t* out);
 cudaError_t launch_fold_pairs(const Launch& L, const qkm_dims& d, const float* contrib, const uint32_t* pos_of,

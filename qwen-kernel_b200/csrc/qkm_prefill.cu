@@ -73,6 +73,66 @@ to_f16_rows_kernel(const float* __restrict__ x, __half* __restrict__ xh, float* 
     if (tid == 0) inv_scale[t] = ldexpf(1.0f, -p);
 }
 
+// The hidden rows for the down GEMM: f32 rows by pair position -> f16, each row scaled by a power of two so
+// that max|h| lands in [2^13, 2^14) (exact), and the scale that undoes it.  Rows [first, first + count) with
+// first = *first_ptr + first_add when first_ptr is given (the shared expert's rows start where the routed
+// pairs end, a count only the device knows) and count = *count_ptr when count_ptr is given.  Persistent
+// blocks: the row count is an upper bound on the host.
+__global__ void __launch_bounds__(256)
+h_rows_to_f16_kernel(const float* __restrict__ hp, __half* __restrict__ hh, float* __restrict__ inv_scale, uint32_t K,
+                     const uint32_t* __restrict__ first_ptr, uint32_t first_add, const uint32_t* __restrict__ count_ptr,
+                     uint32_t count_max) {
+    // one warp per row, 4-element pieces: a row's values stay in registers between the maximum and the conversion
+    const uint32_t lane = threadIdx.x & 31u, warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, n_warps = (gridDim.x * blockDim.x) >> 5;
+    const uint32_t first = (first_ptr ? *first_ptr : 0u) + first_add;
+    const uint32_t count = count_ptr ? min(*count_ptr, count_max) : count_max;
+    constexpr int kPieces = 8;   // K <= 1024 in registers; wider rows are read twice
+    for (uint32_t r = warp; r < count; r += n_warps) {
+        const float4* src = reinterpret_cast<const float4*>(hp + (size_t)(first + r) * K);
+        const uint32_t n4 = K / 4;
+        float4 v[kPieces];
+        float m = 0.f;
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const uint32_t c = lane + 32u * i;
+            v[i] = c < n4 ? src[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(v[i].x), fabsf(v[i].y)), fmaxf(fabsf(v[i].z), fabsf(v[i].w))));
+        }
+        for (uint32_t c = lane + 32u * kPieces; c < n4; c += 32) {
+            const float4 w = src[c];
+            m = fmaxf(m, fmaxf(fmaxf(fabsf(w.x), fabsf(w.y)), fmaxf(fabsf(w.z), fabsf(w.w))));
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+        int p = 0;
+        if (m > 0.f && m <= 3.0e38f) { int e; frexpf(m, &e); p = 14 - e; }
+        const float up = ldexpf(1.0f, p);
+        uint2* dst = reinterpret_cast<uint2*>(hh + (size_t)(first + r) * K);
+        auto pack = [&](const float4& w) -> uint2 {
+            const __half2 a = __floats2half2_rn(w.x * up, w.y * up), b = __floats2half2_rn(w.z * up, w.w * up);
+            return make_uint2(*reinterpret_cast<const uint32_t*>(&a), *reinterpret_cast<const uint32_t*>(&b));
+        };
+#pragma unroll
+        for (int i = 0; i < kPieces; ++i) {
+            const uint32_t c = lane + 32u * i;
+            if (c < n4) dst[c] = pack(v[i]);
+        }
+        for (uint32_t c = lane + 32u * kPieces; c < n4; c += 32) dst[c] = pack(src[c]);
+        if (lane == 0) inv_scale[first + r] = ldexpf(1.0f, -p);
+    }
+}
+
+cudaError_t launch_h_rows_to_f16(const Launch& L, const float* hp, void* hh, float* inv_scale, uint32_t K,
+                                 const uint32_t* first_ptr, uint32_t first_add, const uint32_t* count_ptr, uint32_t count_max) {
+    if (count_max == 0) return cudaSuccess;
+    if (K % 4) return cudaErrorInvalidValue;
+    const uint32_t want = (count_max + 7) / 8;   // eight rows per block at a time
+    const uint32_t blocks = want < 148u * 8u ? want : 148u * 8u;
+    h_rows_to_f16_kernel<<<blocks, 256, 0, L.stream>>>(hp, (__half*)hh, inv_scale, K, first_ptr, first_add, count_ptr, count_max);
+    L.count();
+    return cudaGetLastError();
+}
+
 // ---- work list ------------------------------------------------------------------------------------------
 // For every expert with pairs: its pairs in tiles of kNT, times the 128-row tiles of the
 // gate/up matrices (items_gu) and of the down matrix (items_dn).  Index n_expert_local is
@@ -274,7 +334,7 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                   const __half* __restrict__ xb, const float* __restrict__ x_inv_scale,
                   const uint32_t* __restrict__ pairs, const MmaItem* __restrict__ items,
                   const uint32_t* __restrict__ n_items_ptr, float* __restrict__ h,
-                  __nv_bfloat16* __restrict__ hb, qkm_dims d, uint32_t* __restrict__ status) {
+                  __nv_bfloat16* __restrict__ hb, float* __restrict__ hp, qkm_dims d, uint32_t* __restrict__ status) {
     if (blockIdx.x >= *n_items_ptr) return;
     constexpr int kSt = pf::kStages;
     static_assert(FMT == QKM_TYPE_Q8_0, "IQ3_XXS has its own kernel (gateup_iq3_kernel)");
@@ -378,8 +438,9 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                 if (col < n) {
                     const float us = s_inv[col];   // undo the per-token power-of-two scale of x
                     const float hv = swiglu(__uint_as_float(vg[i]) * us, __uint_as_float(vu[i]) * us);
-                    hb[(size_t)(it.pair_off + col) * d.n_ff + r_ff] = __float2bfloat16_rn(hv);
-                    h[(size_t)s_hrow[col] * d.n_ff + r_ff] = hv;
+                    if (hp) hp[(size_t)(it.pair_off + col) * d.n_ff + r_ff] = hv;   // f32 by pair position: converted to scaled f16 rows later
+                    else hb[(size_t)(it.pair_off + col) * d.n_ff + r_ff] = __float2bfloat16_rn(hv);
+                    if (h) h[(size_t)s_hrow[col] * d.n_ff + r_ff] = hv;
                 }
             }
         }
@@ -512,7 +573,7 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                   const __half* __restrict__ xb, const float* __restrict__ x_inv_scale,
                   const uint32_t* __restrict__ pairs, const MmaItem* __restrict__ items,
                   const uint32_t* __restrict__ n_items_ptr, float* __restrict__ h,
-                  __nv_bfloat16* __restrict__ hb, qkm_dims d, const uint8_t* __restrict__ table,
+                  __nv_bfloat16* __restrict__ hb, float* __restrict__ hp, qkm_dims d, const uint8_t* __restrict__ table,
                   uint32_t* __restrict__ status) {
     constexpr int kSt = pq::kStages, PT = pq::kProducers;
     const uint32_t n_items = *n_items_ptr;
@@ -722,7 +783,7 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                 umma::tmem_ld16(tmem + ((32 * lg) << 16) + cb * 16, vg);
                 umma::tmem_ld16(tmem + ((32 * lg) << 16) + 128 + cb * 16, vu);
                 umma::tmem_ld_wait();
-                __nv_bfloat16* hbp = hb + (size_t)(it.pair_off + cb * 16) * d.n_ff + r_ff;
+                const size_t hoff = (size_t)(it.pair_off + cb * 16) * d.n_ff + r_ff;
 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
                     const uint32_t col = cb * 16 + i;
@@ -730,7 +791,8 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                         const float us = s_inv[buf][col];   // undo the per-token power-of-two scale of x
                         const float g = __uint_as_float(vg[i]) * us, u = __uint_as_float(vu[i]) * us;
                         const float hv = __fdividef(g, 1.0f + __expf(-g)) * u;
-                        hbp[(size_t)i * d.n_ff] = __float2bfloat16_rn(hv);
+                        if (hp) hp[hoff + (size_t)i * d.n_ff] = hv;   // f32 by pair position: converted to scaled f16 rows later
+                        else hb[hoff + (size_t)i * d.n_ff] = __float2bfloat16_rn(hv);
                         if (h) h[(size_t)s_hrow[buf][col] + r_ff] = hv;
                     }
                 }
@@ -748,7 +810,7 @@ gateup_iq3_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
 
 static cudaError_t gateup_iq3_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
                                      const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
-                                     const uint32_t* n_items, uint32_t max_items, float* h, void* hb, const uint8_t* table,
+                                     const uint32_t* n_items, uint32_t max_items, float* h, void* hb, float* hp, const uint8_t* table,
                                      uint32_t* status) {
     static int n_sms = 0;
     if (n_sms == 0) {
@@ -762,19 +824,23 @@ static cudaError_t gateup_iq3_launch(const Launch& L, const qkm_dims& d, const v
     const uint32_t grid = max_items < (uint32_t)n_sms ? max_items : (uint32_t)n_sms;
     gateup_iq3_kernel<<<grid, pq::kBlock, smem, L.stream>>>(
         (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, (const __half*)xb, x_inv_scale, pairs, items, n_items, h,
-        (__nv_bfloat16*)hb, d, table, status);
+        (__nv_bfloat16*)hb, hp, d, table, status);
     L.count();
     return cudaGetLastError();
 }
 
 // ---- down -------------------------------------------------------------------------------------------------
 // FMT: QKM_TYPE_IQ4_XS (routed) or QKM_TYPE_Q8_0 (shared).  contrib[pair position][n_embd].
-template <int FMT>
+// F16H: the hidden rows are f16, each scaled by a power of two (h_inv_scale undoes it in the epilogue), and the
+// weights are dequantised to f16 as well (Q8_0 only); else both are bf16.
+template <int FMT, bool F16H = false>
 __global__ void __launch_bounds__(pf::kBlock, 2)
 down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restrict__ hb,
                 const qkm_sel* __restrict__ sel, const uint32_t* __restrict__ pairs,
                 const MmaItem* __restrict__ items, const uint32_t* __restrict__ n_items_ptr,
-                float* __restrict__ contrib, qkm_dims d, uint32_t row_tiles, uint32_t* __restrict__ status) {
+                float* __restrict__ contrib, qkm_dims d, uint32_t row_tiles, uint32_t* __restrict__ status,
+                const float* __restrict__ h_inv_scale = nullptr) {
+    static_assert(!F16H || FMT == QKM_TYPE_Q8_0, "f16 hidden rows: Q8_0 weights here, IQ4_XS in down_iq4_kernel");
     if (blockIdx.x * row_tiles >= *n_items_ptr) return;
     constexpr int kTile = FMT == QKM_TYPE_IQ4_XS ? kTileIq4 : kTileQ8;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
@@ -807,7 +873,7 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     __syncthreads();
     umma::fence_after_sync();
     const uint32_t tmem = s_tmem;
-    const uint32_t idesc = umma::instr_desc_bf16(n_mma);
+    const uint32_t idesc = F16H ? umma::instr_desc_f16(n_mma) : umma::instr_desc_bf16(n_mma);
     bool timed_out = false;
 
     // producer role: thread -> row (tid & 127), 32-column half (tid >> 7) of the A tile; all threads help with B
@@ -820,7 +886,7 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     for (uint32_t i = tid; i < n; i += pf::kBlock) {
         s_row[i] = hb + (size_t)(it.pair_off + i) * d.n_ff;
         const uint32_t pr = pairs[it.pair_off + i], tok = pr >> 4, slot = pr & 15u;
-        s_wgt[i] = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
+        s_wgt[i] = (slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared) * (F16H ? h_inv_scale[it.pair_off + i] : 1.0f);
     }
     __syncthreads();
     // The block walks `row_tiles` consecutive 128-row tiles of the same expert and pairs: tables,
@@ -865,8 +931,8 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
             raw = next;
         } else {
             const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-            if (tid < 128) produce_q8<false, 0, 1>(tile, r16, ks & 3u, st, r);
-            else produce_q8<false, 1, 2>(tile, r16, ks & 3u, st, r);
+            if (tid < 128) produce_q8<F16H, 0, 1>(tile, r16, ks & 3u, st, r);
+            else produce_q8<F16H, 1, 2>(tile, r16, ks & 3u, st, r);
         }
         store_b(st + pf::kTileBytes, breg, n_mma);
         breg = bnext;
@@ -1191,13 +1257,13 @@ cudaError_t launch_mma_plan(const Launch& L, const qkm_dims& d, const uint32_t* 
 template <int FMT, int PT>
 static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const void* gate_tiles, const void* up_tiles,
                                      const void* xb, const float* x_inv_scale, const uint32_t* pairs, const MmaItem* items,
-                                     const uint32_t* n_items, uint32_t max_items, float* h, void* hb, uint32_t* status) {
+                                     const uint32_t* n_items, uint32_t max_items, float* h, void* hb, float* hp, uint32_t* status) {
     const size_t smem = (size_t)pf::kStages * 3 * pf::kTileBytes + 1024;
     cudaError_t e = cudaFuncSetAttribute(gateup_mma_kernel<FMT, PT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     gateup_mma_kernel<FMT, PT><<<max_items, PT + 32, smem, L.stream>>>(
         (const uint8_t*)gate_tiles, (const uint8_t*)up_tiles, (const __half*)xb, x_inv_scale, pairs, items, n_items, h,
-        (__nv_bfloat16*)hb, d, status);
+        (__nv_bfloat16*)hb, hp, d, status);
     L.count();
     return cudaGetLastError();
 }
@@ -1205,15 +1271,15 @@ static cudaError_t gateup_mma_launch(const Launch& L, const qkm_dims& d, const v
 cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* gate_tiles,
                               const void* up_tiles, const void* xb, const float* x_inv_scale, const uint32_t* pairs,
                               const MmaItem* items, const uint32_t* n_items, uint32_t max_items, float* h, void* hb,
-                              uint32_t* status, bool few_blocks, const uint8_t* iq3_table) {
+                              uint32_t* status, bool few_blocks, const uint8_t* iq3_table, float* hp) {
     if (max_items == 0) return cudaSuccess;
     if (type == QKM_TYPE_IQ3_XXS) {
         if (!iq3_table) return cudaErrorInvalidValue;
-        return gateup_iq3_launch(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, iq3_table, status);
+        return gateup_iq3_launch(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, hp, iq3_table, status);
     }
     if (type == QKM_TYPE_Q8_0)
-        return few_blocks ? gateup_mma_launch<QKM_TYPE_Q8_0, 512>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status)
-                          : gateup_mma_launch<QKM_TYPE_Q8_0, 256>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, status);
+        return few_blocks ? gateup_mma_launch<QKM_TYPE_Q8_0, 512>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, hp, status)
+                          : gateup_mma_launch<QKM_TYPE_Q8_0, 256>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, hp, status);
     return cudaErrorInvalidValue;
 }
 
@@ -1234,9 +1300,12 @@ __global__ void down_iq4_table_kernel(uint8_t* __restrict__ out) {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;   // one 4-byte word each
     if (i >= pd::kTabBytes / 4) return;
     const uint32_t row = i >> 6, w = i & 63u;
-    uint32_t v = 0;
-    if (w < 32) {
+    uint32_t v;
+    if (w < 32) {    // bf16 pairs, one per lane
         const __nv_bfloat162 m = __floats2bfloat162_rn((float)c_iq4_values[row & 15u], (float)c_iq4_values[row >> 4]);
+        v = *reinterpret_cast<const uint32_t*>(&m);
+    } else {         // the same as f16 pairs
+        const __half2 m = __floats2half2_rn((float)c_iq4_values[row & 15u], (float)c_iq4_values[row >> 4]);
         v = *reinterpret_cast<const uint32_t*>(&m);
     }
     reinterpret_cast<uint32_t*>(out)[i] = v;
@@ -1259,12 +1328,16 @@ __device__ __forceinline__ Iq4Step load_iq4_step(const uint8_t* __restrict__ til
     return r;
 }
 
+// F16H: the hidden rows are f16, each scaled by a power of two (h_inv_scale undoes it in the epilogue, with
+// the routing weight), and the weights are dequantised to f16 with one multiply by the f16 sub-block scale
+// (two roundings of 2^-12); else both operands are bf16 and the scale is applied in two bf16 pieces.
+template <bool F16H>
 __global__ void __launch_bounds__(pq::kBlock, 1)
 down_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restrict__ hb,
                 const qkm_sel* __restrict__ sel, const uint32_t* __restrict__ pairs,
                 const MmaItem* __restrict__ items, const uint32_t* __restrict__ n_items_ptr,
                 float* __restrict__ contrib, qkm_dims d, const uint8_t* __restrict__ table,
-                uint32_t* __restrict__ status) {
+                uint32_t* __restrict__ status, const float* __restrict__ h_inv_scale) {
     constexpr int kSt = pq::kStages, PT = pq::kProducers;
     const uint32_t n_units = *n_items_ptr / 2;   // items of one (expert, pair tile) are consecutive row tiles, an even number
     if (blockIdx.x >= n_units) return;
@@ -1311,7 +1384,8 @@ down_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
         const bool leader = umma::elect_one();
         uint32_t stage = 0, phase = 0;
         for (uint32_t unit = blockIdx.x; unit < n_units; unit += gridDim.x) {
-            const uint32_t idesc = umma::instr_desc_bf16((items[2 * unit].n + 15u) & ~15u);
+            const uint32_t nn = (items[2 * unit].n + 15u) & ~15u;
+            const uint32_t idesc = F16H ? umma::instr_desc_f16(nn) : umma::instr_desc_bf16(nn);
             for (uint32_t ks = 0; ks < KS; ++ks) {
                 if (!mbar_wait_bounded(bar_full + 8 * stage, phase)) timed_out = true;
                 umma::fence_after_sync();
@@ -1334,7 +1408,7 @@ down_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
     } else {
     // ---- producer warps: thread = (row r, row tile `mat` of the unit, 32-column half j of each k-step)
     const uint32_t r = tid & 127u, mat = (tid >> 7) & 1u, j = tid >> 8;
-    const uint32_t tconst = 0x00010000u | (lane * 4u);
+    const uint32_t tconst = 0x00010000u | ((F16H ? 128u : 0u) + lane * 4u);   // the f16 pairs sit in the upper half of a table row
     const uint32_t a_lane = tmem + ((r & ~31u) << 16) + pq::kTmemA + mat * 32u + j * 16u;
     // N operand: chunks tid and tid + 512 of the h tile (row = chunk / 8), copied asynchronously
     const uint32_t b_row0 = tid >> 3, b_row1 = b_row0 + 64, b_c = tid & 7u;
@@ -1358,7 +1432,7 @@ down_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
         hd.first = load_iq4_step(hd.wt, hd.r16, 0, j);
         for (uint32_t i = tid; i < hd.it.n; i += PT) {   // routing weight of the unit's columns (pairs)
             const uint32_t pr = pairs[hd.it.pair_off + i], tok = pr >> 4, slot = pr & 15u;
-            s_wgt[buf][i] = slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared;
+            s_wgt[buf][i] = (slot < d.n_used ? sel[tok].w[slot] : sel[tok].w_shared) * (F16H ? h_inv_scale[hd.it.pair_off + i] : 1.0f);
         }
         return hd;
     };
@@ -1416,7 +1490,12 @@ down_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
             const __nv_bfloat16 dhi = __float2bfloat16_rn(dl);
             const __nv_bfloat162 s_hi = __bfloat162bfloat162(dhi);
             const __nv_bfloat162 s_lo = __bfloat162bfloat162(__float2bfloat16_rn(dl - __bfloat162float(dhi)));
+            const __half2 s_h = __float2half2_rn(dl);
             auto scale = [&](uint32_t x) -> uint32_t {
+                if (F16H) {
+                    const __half2 o = __hmul2(*reinterpret_cast<const __half2*>(&x), s_h);
+                    return *reinterpret_cast<const uint32_t*>(&o);
+                }
                 const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(&x);
                 const __nv_bfloat162 o = __hfma2(v, s_hi, __hmul2(v, s_lo));
                 return *reinterpret_cast<const uint32_t*>(&o);
@@ -1482,7 +1561,7 @@ down_iq4_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
 static cudaError_t down_iq4_launch(const Launch& L, const qkm_dims& d, const void* tiles, const void* hb,
                                    const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items,
                                    const uint32_t* n_items, uint32_t max_items, float* contrib, const uint8_t* table,
-                                   uint32_t* status) {
+                                   uint32_t* status, const float* h_inv_scale) {
     static int n_sms = 0;
     if (n_sms == 0) {
         int dev = 0, v = 0;
@@ -1490,41 +1569,52 @@ static cudaError_t down_iq4_launch(const Launch& L, const qkm_dims& d, const voi
         n_sms = v;
     }
     const size_t smem = pq::kEnd;
-    cudaError_t e = cudaFuncSetAttribute(down_iq4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = h_inv_scale ? cudaFuncSetAttribute(down_iq4_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                                : cudaFuncSetAttribute(down_iq4_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     const uint32_t units = max_items / 2;
     const uint32_t grid = units < (uint32_t)n_sms ? units : (uint32_t)n_sms;
     if (grid == 0) return cudaSuccess;
-    down_iq4_kernel<<<grid, pq::kBlock, smem, L.stream>>>((const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items,
-                                                          n_items, contrib, d, table, status);
+    if (h_inv_scale)
+        down_iq4_kernel<true><<<grid, pq::kBlock, smem, L.stream>>>((const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items,
+                                                                    n_items, contrib, d, table, status, h_inv_scale);
+    else
+        down_iq4_kernel<false><<<grid, pq::kBlock, smem, L.stream>>>((const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items,
+                                                                     n_items, contrib, d, table, status, h_inv_scale);
     L.count();
     return cudaGetLastError();
 }
 
-template <int FMT>
+template <int FMT, bool F16H = false>
 static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const void* tiles, const void* hb,
                                    const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items,
-                                   const uint32_t* n_items, uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks) {
+                                   const uint32_t* n_items, uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks,
+                                   const float* h_inv_scale = nullptr) {
     const size_t smem = (size_t)pf::kStages * 2 * pf::kTileBytes + (FMT == QKM_TYPE_IQ4_XS ? 256 * 32 * 4 : 0) + 1024;
-    cudaError_t e = cudaFuncSetAttribute(down_mma_kernel<FMT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(down_mma_kernel<FMT, F16H>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     // routed experts: four row tiles per block (set-up amortised); the shared expert has few blocks, one each
     // (a shard of few experts: one row tile per block as well, so that its blocks fill the machine)
     uint32_t row_tiles = FMT == QKM_TYPE_IQ4_XS ? 4u : 1u;
     (void)few_blocks;
     while (row_tiles > 1 && (d.n_embd / 128) % row_tiles) row_tiles >>= 1;
-    down_mma_kernel<FMT><<<(max_items + row_tiles - 1) / row_tiles, pf::kBlock, smem, L.stream>>>(
-        (const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items, n_items, contrib, d, row_tiles, status);
+    down_mma_kernel<FMT, F16H><<<(max_items + row_tiles - 1) / row_tiles, pf::kBlock, smem, L.stream>>>(
+        (const uint8_t*)tiles, (const __nv_bfloat16*)hb, sel, pairs, items, n_items, contrib, d, row_tiles, status, h_inv_scale);
     L.count();
     return cudaGetLastError();
 }
 
 cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, const void* tiles, const void* hb,
                             const qkm_sel* sel, const uint32_t* pairs, const MmaItem* items, const uint32_t* n_items,
-                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks, const uint8_t* iq4_table) {
+                            uint32_t max_items, float* contrib, uint32_t* status, bool few_blocks, const uint8_t* iq4_table,
+                            const float* h_inv_scale) {
     if (max_items == 0) return cudaSuccess;
     if (type == QKM_TYPE_IQ4_XS && iq4_table && (d.n_embd / 128) % 2 == 0)   // row tiles in pairs
-        return down_iq4_launch(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, iq4_table, status);
+        return down_iq4_launch(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, iq4_table, status, h_inv_scale);
+    if (h_inv_scale) {   // f16 hidden rows: only the two kernels above and below take them
+        if (type != QKM_TYPE_Q8_0) return cudaErrorInvalidValue;
+        return down_mma_launch<QKM_TYPE_Q8_0, true>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status, few_blocks, h_inv_scale);
+    }
     if (type == QKM_TYPE_IQ4_XS)
         return down_mma_launch<QKM_TYPE_IQ4_XS>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status, few_blocks);
     if (type == QKM_TYPE_Q8_0)
