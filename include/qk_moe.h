@@ -222,7 +222,8 @@ QKM_API int qkm_dequant(qkm_ctx *c, uint32_t type, const void *blocks, float *y,
 QKM_API int qkm_moe_decode(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
                            float *y);
 /* Batched-prefill sequence (src/main.cpp:5050-5198): grouped by expert, expert
- * GEMMs on the tensor cores with bf16 operands and f32 accumulation. */
+ * GEMMs on the tensor cores with f16 operands (x and h rows scaled per row by a power of
+ * two) and f32 accumulation. */
 QKM_API int qkm_moe_prefill(qkm_ctx *c, uint32_t layer, const float *x, uint32_t n_tokens,
                             float *y);
 /* Same two calls with HOST buffers: copies x in, runs, copies y out, syncs.
@@ -249,7 +250,7 @@ QKM_API int qkm_profile_read(qkm_ctx *c, char *labels, float *ms, uint32_t max_s
 QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 /* Device address of the context's selection / h scratch of the last fused call (h in f32 is
  * written by the decode calls and by the prefill calls of layers whose down tensor has no
- * tile layout; the tensor-core prefill keeps h in bf16 only). */
+ * tile layout; the tensor-core prefill writes f32 rows by pair position there, not [T][slot]). */
 QKM_API const qkm_sel *qkm_sel_device(const qkm_ctx *c);
 QKM_API const float   *qkm_h_device(const qkm_ctx *c);
 
