@@ -249,8 +249,8 @@ QKM_API int qkm_profile_read(qkm_ctx *c, char *labels, float *ms, uint32_t max_s
 /* Selection records of the last fused call (device -> host copy, syncs). */
 QKM_API int qkm_last_sel(qkm_ctx *c, qkm_sel *sel_host, uint32_t n_tokens);
 /* Device address of the context's selection / h scratch of the last fused call (h in f32 is
- * written by the decode calls and by the prefill calls of layers whose down tensor has no
- * tile layout; the tensor-core prefill writes f32 rows by pair position there, not [T][slot]). */
+ * written by the decode calls and by the prefill calls that take the f32 kernels; the tensor-core
+ * prefill writes f32 rows by pair position there, not [T][slot]). */
 QKM_API const qkm_sel *qkm_sel_device(const qkm_ctx *c);
 QKM_API const float   *qkm_h_device(const qkm_ctx *c);
 

@@ -26,7 +26,7 @@ struct qkm_layer_dev {
     void* tiles[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
     bool tiles_ok = false;   // routed gate/up and down both have tiles
     bool stream_ok = false;  // tiles, and every expert resident: the fused decode / prefill sequences apply
-    bool gu_only = false;    // as stream_ok for gate/up and the shared expert, but the down tensor (Q6_K) has no tiles
+    bool gu_only = false;    // as stream_ok for gate/up and the shared expert; the down tensor is Q6_K (tiles[4] holds Q6_K tiles)
 };
 
 struct qkm_ctx {
@@ -472,7 +472,6 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
         const bool gu = w->gateup_type == QKM_TYPE_IQ3_XXS, dn = w->down_type == QKM_TYPE_IQ4_XS;
         for (auto& t : plan) {
             if (!gu) break;                       // without streamed gate/up nothing else is used
-            if (t.idx == 4 && !dn) continue;      // Q6_K down: the f32 kernels read the raw layout
             const size_t bytes = tensor_bytes(c, t.idx, *w);
             QKM_CUDA(c, cudaMalloc(&l.tiles[t.idx], bytes + 256));
             cudaError_t e = launch_repack(c->L(), t.type, l.allocs[t.idx], l.tiles[t.idx], t.mats, t.rows, t.K);
@@ -637,7 +636,7 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     // side stream, and nothing runs beside the two persistent kernels that they would have to
     // share the SMs with.
     if (c->dec_ok && w.gateup_type == QKM_TYPE_IQ3_XXS && route_decode_ok(d, n, c->route_scratch_bytes) &&
-        (!ld.stream_ok || decode_down_ok(d))) {
+        decode_down_ok(d)) {
         RouteDecodeArgs ra{};
         ra.router = (const uint8_t*)w.router; ra.gis = w.gate_inp_shexp; ra.x = x; ra.sel = c->sel;
         ra.logits = (double*)c->route_scratch; ra.counter = c->route_counter; ra.planes = c->planes8; ra.xscale = c->xscale; ra.n_tokens = n; ra.d = d;
@@ -656,8 +655,11 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
             da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7];
             da.h = c->h; da.sel = c->sel; da.y = y; da.n_tokens = n; da.status = c->status; da.d = d;
             QKM_LAUNCH(c, launch_decode_down(c->Lchain(), da, nb));
-        } else {   // Q6_K down: f32 kernel over h, routed slots and the shared expert in one pass
-            QKM_LAUNCH(c, launch_down_tokens(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, y, n, c->efirst, c->ecount, w.down_shexp));
+        } else {   // Q6_K down
+            DownDecodeArgs da{};
+            da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7];
+            da.h = c->h; da.sel = c->sel; da.y = y; da.n_tokens = n; da.status = c->status; da.d = d;
+            QKM_LAUNCH(c, launch_decode_down_q6k(c->Lchain(), da, nb));
         }
         c->prof_mark("moe.dn");
         c->shared_plan_n = 0;   // pairs / work lists of the older sequence are overwritten
@@ -791,36 +793,19 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
         QKM_CUDA(c, cudaStreamWaitEvent(c->side, c->ev_fork, 0));
     }
     // Tensor-core down GEMMs take the hidden rows as f16 scaled per row by a power of two: the gate/up kernels
-    // store them in f32 by pair position (in c->h), a conversion pass finds each row's scale.  Layers whose
-    // down tensor takes the f32 kernels keep h in the reference's layout.
-    float* const h_ref = ld.stream_ok ? nullptr : c->h;
-    float* const h_pos = ld.stream_ok ? c->h : nullptr;
+    // store them in f32 by pair position (in c->h), a conversion pass finds each row's scale.
     QKM_LAUNCH(c, launch_gateup_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[5], ld.tiles[6], c->xb, c->xscale, c->pairs, c->mma_items[2],
-                                    c->n_items + 2, sh_now * rt_gu, h_ref, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms, nullptr, h_pos));
+                                    c->n_items + 2, sh_now * rt_gu, nullptr, c->hb, c->status, sh_now * rt_gu <= 2u * (uint32_t)c->n_sms, nullptr, c->h));
     if (!fork) c->prof_mark("moe.shared_gu");
-    if (ld.stream_ok) {
-        // the shared expert's rows follow the routed pairs (their number is offsets[ecount], known on the device)
-        QKM_LAUNCH(c, launch_h_rows_to_f16(S, c->h, c->hb, c->hscale, d.n_ff, c->offsets + c->ecount, 0, nullptr, n));
-        QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
-                                      c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status, false, nullptr, c->hscale));
-        if (!fork) c->prof_mark("moe.shared_dn");
-    }
+    // the shared expert's rows follow the routed pairs (their number is offsets[ecount], known on the device)
+    QKM_LAUNCH(c, launch_h_rows_to_f16(S, c->h, c->hb, c->hscale, d.n_ff, c->offsets + c->ecount, 0, nullptr, n));
+    QKM_LAUNCH(c, launch_down_mma(S, d, QKM_TYPE_Q8_0, ld.tiles[7], c->hb, c->sel, c->pairs, c->mma_items[3],
+                                  c->n_items + 3, sh_now * rt_dn, c->contrib_p, c->status, false, nullptr, c->hscale));
+    if (!fork) c->prof_mark("moe.shared_dn");
     if (fork) QKM_CUDA(c, cudaEventRecord(c->ev_join, c->side));
     QKM_LAUNCH(c, launch_gateup_mma(c->L(), d, w.gateup_type, ld.tiles[2], ld.tiles[3], c->xb, c->xscale, c->pairs, c->mma_items[0],
-                                    c->n_items, tiles_now * rt_gu, h_ref, c->hb, c->status, false, c->lut_pf, h_pos));
+                                    c->n_items, tiles_now * rt_gu, nullptr, c->hb, c->status, false, c->lut_pf, c->h));
     c->prof_mark("moe.gu");
-    if (!ld.stream_ok) {
-        // Q6_K down: the f32 kernels take over from h (per-pair contributions, shared down, fold)
-        if (!c->contrib) QKM_CUDA(c, cudaMalloc((void**)&c->contrib, (size_t)c->cfg.max_tokens * d.n_used * d.n_embd * sizeof(float)));
-        if (fork) QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_join, 0));
-        QKM_CUDA(c, cudaMemsetAsync(c->contrib, 0, (size_t)n * d.n_used * d.n_embd * sizeof(float), c->stream));
-        QKM_LAUNCH(c, launch_down_pairs(c->L(), d, w.down_type, w.down_exps, c->h, c->sel, c->offsets, c->pairs, c->contrib, n, c->efirst, c->ecount));
-        QKM_LAUNCH(c, launch_shared_down(c->L(), d, w.down_shexp, c->h, c->sel, c->y2, n));
-        c->prof_mark("moe.dn");
-        QKM_LAUNCH(c, launch_fold_contrib(c->L(), d, c->contrib, c->y2, y, n));
-        c->prof_mark("moe.fold");
-        return QKM_OK;
-    }
     QKM_LAUNCH(c, launch_h_rows_to_f16(c->L(), c->h, c->hb, c->hscale, d.n_ff, nullptr, 0, c->offsets + c->ecount, n * d.n_used));
     QKM_LAUNCH(c, launch_down_mma(c->L(), d, w.down_type, ld.tiles[4], c->hb, c->sel, c->pairs, c->mma_items[1],
                                   c->n_items + 1, tiles_now * rt_dn, c->contrib_p, c->status, false, c->lut_dn, c->hscale));

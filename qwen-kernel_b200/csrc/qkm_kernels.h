@@ -113,6 +113,8 @@ struct DownDecodeArgs {
 };
 bool decode_down_ok(const qkm_dims& d);
 cudaError_t launch_decode_down(const Launch& L, const DownDecodeArgs& a, uint32_t n_blocks);
+// the same with the routed experts as Q6_K tiles
+cudaError_t launch_decode_down_q6k(const Launch& L, const DownDecodeArgs& a, uint32_t n_blocks);
 
 // ---- qkm_prefill.cu : tcgen05 expert GEMMs for batched prefill
 uint32_t prefill_pairs_per_block();

@@ -296,6 +296,37 @@ __device__ __forceinline__ void produce_q8(const uint8_t* __restrict__ tile, uin
     }
 }
 
+// Q6_K (tile layout of qkm_tiles.cuh): the 32 columns of 128-column half hf = q / 2, quarter
+// qd = 2 (q & 1) + j - nibble qd / 2 of the (qd & 1)-th 32-byte run of ql, bit pair qd of qh, scales
+// 2 (4 hf + qd) and the one after it (src/quants.h:148-163).  One rounding: d * scale * (q - 32) -> 16 bit.
+template <bool F16>
+__device__ __forceinline__ void produce_q6k(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q, uint32_t j,
+                                            uint8_t* a_tile, uint32_t row) {
+    const uint32_t g = r16 & 7u, h = r16 >> 3, hf = q >> 1, qd = 2 * (q & 1u) + j;
+    const float d = f16_bits_to_f32(*reinterpret_cast<const uint16_t*>(tile + 3328 + 2 * r16));
+    const float s0 = d * (float)(int8_t)tile[16 * r16 + 4 * hf + qd], s1 = d * (float)(int8_t)tile[16 * r16 + 8 + 4 * hf + qd];
+    const uint8_t* ql = tile + 256 + ((3 * h + hf) * 32 + 4 * g) * 16 + 8 * (qd & 1u);
+    const uint8_t* qh = tile + 256 + ((3 * h + 2) * 32 + 4 * g) * 16 + 8 * hf;
+    uint32_t v[8];   // word m: elements 4m .. 4m+3 as bytes q (0..63)
+#pragma unroll
+    for (int m = 0; m < 8; ++m) {
+        const uint32_t wl = *reinterpret_cast<const uint32_t*>(ql + 16 * (m & 3) + 4 * (m >> 2));
+        const uint32_t wh = *reinterpret_cast<const uint32_t*>(qh + 16 * (m & 3) + 4 * (m >> 2));
+        v[m] = (((qd >> 1) ? wl >> 4 : wl) & 0x0F0F0F0Fu) | (((wh >> (2 * qd)) & 0x03030303u) << 4);
+    }
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {      // elements 8p .. 8p+7
+        const float s = p < 2 ? s0 : s1;
+        const uint32_t a = v[2 * p], b = v[2 * p + 1];
+        uint4 o;
+        o.x = pack16<F16>(s * (float)((int)(a & 0xFF) - 32), s * (float)((int)((a >> 8) & 0xFF) - 32));
+        o.y = pack16<F16>(s * (float)((int)((a >> 16) & 0xFF) - 32), s * (float)((int)(a >> 24) - 32));
+        o.z = pack16<F16>(s * (float)((int)(b & 0xFF) - 32), s * (float)((int)((b >> 8) & 0xFF) - 32));
+        o.w = pack16<F16>(s * (float)((int)((b >> 16) & 0xFF) - 32), s * (float)((int)(b >> 24) - 32));
+        *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + p)) = o;
+    }
+}
+
 // N operand: rows [0, n_mma) of the block's pairs, 64 columns at k0; rows >= n are zero.
 // Split in two so the global loads of the next k-step can be in flight during this one:
 // fetch_b reads this thread's (at most 4) 16-byte chunks, store_b writes them swizzled.
@@ -830,9 +861,9 @@ static cudaError_t gateup_iq3_launch(const Launch& L, const qkm_dims& d, const v
 }
 
 // ---- down -------------------------------------------------------------------------------------------------
-// FMT: QKM_TYPE_IQ4_XS (routed) or QKM_TYPE_Q8_0 (shared).  contrib[pair position][n_embd].
+// FMT: QKM_TYPE_IQ4_XS or QKM_TYPE_Q6_K (routed), QKM_TYPE_Q8_0 (shared).  contrib[pair position][n_embd].
 // F16H: the hidden rows are f16, each scaled by a power of two (h_inv_scale undoes it in the epilogue), and the
-// weights are dequantised to f16 as well (Q8_0 only); else both are bf16.
+// weights are dequantised to f16 as well (Q8_0, Q6_K); else both are bf16.
 template <int FMT, bool F16H = false>
 __global__ void __launch_bounds__(pf::kBlock, 2)
 down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restrict__ hb,
@@ -840,9 +871,9 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
                 const MmaItem* __restrict__ items, const uint32_t* __restrict__ n_items_ptr,
                 float* __restrict__ contrib, qkm_dims d, uint32_t row_tiles, uint32_t* __restrict__ status,
                 const float* __restrict__ h_inv_scale = nullptr) {
-    static_assert(!F16H || FMT == QKM_TYPE_Q8_0, "f16 hidden rows: Q8_0 weights here, IQ4_XS in down_iq4_kernel");
+    static_assert(!F16H || FMT != QKM_TYPE_IQ4_XS, "f16 hidden rows: Q8_0 / Q6_K weights here, IQ4_XS in down_iq4_kernel");
     if (blockIdx.x * row_tiles >= *n_items_ptr) return;
-    constexpr int kTile = FMT == QKM_TYPE_IQ4_XS ? kTileIq4 : kTileQ8;
+    constexpr int kTile = FMT == QKM_TYPE_IQ4_XS ? kTileIq4 : FMT == QKM_TYPE_Q6_K ? kTileQ6 : kTileQ8;
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long s_bar[2 * pf::kStages + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
@@ -929,6 +960,8 @@ down_mma_kernel(const uint8_t* __restrict__ tiles, const __nv_bfloat16* __restri
         if (FMT == QKM_TYPE_IQ4_XS) {
             produce_iq4(raw, ks & 3u, jhalf, s_pair_lane, st, r);
             raw = next;
+        } else if (FMT == QKM_TYPE_Q6_K) {
+            produce_q6k<F16H>(wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile, r16, ks & 3u, jhalf, st, r);
         } else {
             const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
             if (tid < 128) produce_q8<F16H, 0, 1>(tile, r16, ks & 3u, st, r);
@@ -1595,7 +1628,7 @@ static cudaError_t down_mma_launch(const Launch& L, const qkm_dims& d, const voi
     if (e != cudaSuccess) return e;
     // routed experts: four row tiles per block (set-up amortised); the shared expert has few blocks, one each
     // (a shard of few experts: one row tile per block as well, so that its blocks fill the machine)
-    uint32_t row_tiles = FMT == QKM_TYPE_IQ4_XS ? 4u : 1u;
+    uint32_t row_tiles = FMT == QKM_TYPE_Q8_0 ? 1u : 4u;
     (void)few_blocks;
     while (row_tiles > 1 && (d.n_embd / 128) % row_tiles) row_tiles >>= 1;
     down_mma_kernel<FMT, F16H><<<(max_items + row_tiles - 1) / row_tiles, pf::kBlock, smem, L.stream>>>(
@@ -1612,6 +1645,8 @@ cudaError_t launch_down_mma(const Launch& L, const qkm_dims& d, uint32_t type, c
     if (type == QKM_TYPE_IQ4_XS && iq4_table && (d.n_embd / 128) % 2 == 0)   // row tiles in pairs
         return down_iq4_launch(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, iq4_table, status, h_inv_scale);
     if (h_inv_scale) {   // f16 hidden rows: only the two kernels above and below take them
+        if (type == QKM_TYPE_Q6_K)
+            return down_mma_launch<QKM_TYPE_Q6_K, true>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status, few_blocks, h_inv_scale);
         if (type != QKM_TYPE_Q8_0) return cudaErrorInvalidValue;
         return down_mma_launch<QKM_TYPE_Q8_0, true>(L, d, tiles, hb, sel, pairs, items, n_items, max_items, contrib, status, few_blocks, h_inv_scale);
     }

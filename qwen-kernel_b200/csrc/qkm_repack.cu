@@ -13,7 +13,7 @@ namespace qkm {
 template <int TYPE>
 __global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restrict__ out, uint32_t rows,
                               uint32_t K, uint64_t total_bytes) {
-    constexpr int kTile = TYPE == QKM_TYPE_IQ3_XXS ? kTileIq3 : TYPE == QKM_TYPE_IQ4_XS ? kTileIq4 : kTileQ8;
+    constexpr int kTile = TYPE == QKM_TYPE_IQ3_XXS ? kTileIq3 : TYPE == QKM_TYPE_IQ4_XS ? kTileIq4 : TYPE == QKM_TYPE_Q6_K ? kTileQ6 : kTileQ8;
     const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total_bytes) return;
     const uint32_t KB = K / 256, RT = rows / 16;
@@ -55,6 +55,22 @@ __global__ void repack_kernel(const uint8_t* __restrict__ raw, uint8_t* __restri
             off = 8 + 16 * ib + 4 * t + (b & 3u);
         }
         out[i] = m[(size_t)(rt * 16 + row_in_tile) * rb + (size_t)kb * 136 + off];
+    } else if (TYPE == QKM_TYPE_Q6_K) {
+        if (o < 256) {
+            const uint32_t b = o & 15u;
+            row_in_tile = o >> 4;
+            off = 192 + (b < 8 ? 2 * b : 2 * (b - 8) + 1);
+        } else if (o < 3328) {
+            const uint32_t q = o - 256, c = q >> 9, lane = (q >> 4) & 31u, b = q & 15u;
+            const uint32_t g = lane >> 2, t = lane & 3u, h = c / 3, k = c - 3 * h, w = b >> 2;
+            const uint32_t wm = (w & 1u) ? 4 + t : t;
+            row_in_tile = g + 8 * h;
+            off = k < 2 ? 64 * k + 32 * (w >> 1) + 4 * wm + (b & 3u) : 128 + 32 * (w >> 1) + 4 * wm + (b & 3u);
+        } else {
+            row_in_tile = (o - 3328) >> 1;
+            off = 208 + (o & 1u);
+        }
+        out[i] = m[(size_t)(rt * 16 + row_in_tile) * rb + (size_t)kb * 210 + off];
     } else {  // Q8_0: per 32-column block, the 16 rows' d (32 B) then their quants (512 B)
         const uint32_t blk = o / 544u, q = o - blk * 544u;
         if (q < 32) {
@@ -81,6 +97,7 @@ cudaError_t launch_repack(const Launch& L, uint32_t type, const void* raw, void*
     switch (type) {
         case QKM_TYPE_IQ3_XXS: repack_kernel<QKM_TYPE_IQ3_XXS><<<grid, 256, 0, L.stream>>>(r, o, rows, K, total); break;
         case QKM_TYPE_IQ4_XS: repack_kernel<QKM_TYPE_IQ4_XS><<<grid, 256, 0, L.stream>>>(r, o, rows, K, total); break;
+        case QKM_TYPE_Q6_K: repack_kernel<QKM_TYPE_Q6_K><<<grid, 256, 0, L.stream>>>(r, o, rows, K, total); break;
         case QKM_TYPE_Q8_0: repack_kernel<QKM_TYPE_Q8_0><<<grid, 256, 0, L.stream>>>(r, o, rows, K, total); break;
         default: return cudaErrorInvalidValue;
     }

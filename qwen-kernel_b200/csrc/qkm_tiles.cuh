@@ -6,7 +6,7 @@
 // needs for 16 rows x 256 columns with one bulk copy and read it back from shared
 // memory with aligned, conflict-free 128-bit loads.  A tile holds exactly the bytes
 // of its 16 row-blocks (no padding, nothing recomputed), so tile bytes = 16 x
-// block bytes x (256 / block elements): IQ3_XXS 1568, IQ4_XS 2176, Q8_0 4352.
+// block bytes x (256 / block elements): IQ3_XXS 1568, IQ4_XS 2176, Q6_K 3360, Q8_0 4352.
 // Tiles of one matrix [rows][K] are ordered [kb = K/256][rt = rows/16]: a warp that
 // owns column block kb walks consecutive memory as it moves down the rows.
 //
@@ -32,6 +32,16 @@
 //                  c = 2*h + q: row g + 8h, sub-blocks 4q..4q+3, for each the raw qs word t
 //                  (bytes 4t..4t+3 of the sub-block's 16: low nibbles are elements
 //                  4t..4t+3, high nibbles elements 16+4t..16+4t+3)
+//   Q6_K (block: ql[128] | qh[64] | scales[16] int8 | d f16, src/quants.h:98-103).  A 128-column
+//   half hf of a block packs element l + 32*qd (l < 32, qd < 4) as nibble (qd >> 1) of
+//   ql[64*hf + 32*(qd & 1) + l] and bit pair qd of qh[32*hf + l]; its scale is scales[8*hf + 2*qd + l/16].
+//   Word m (0..7) of a 32-byte run holds l = 4m..4m+3.  Lane (g,t) multiplies, for every (hf, qd),
+//   the elements l = 4t..4t+3 (16-column group 2*(4*hf+qd)) and l = 16+4t..16+4t+3 (the group after it):
+//     [   0, 256)  scales: row r at 16*r, the eight even groups 0,2,..,14 then the eight odd ones
+//     [ 256,3328)  quants: chunk c (0..5), lane -> 16 B at 256 + (c*32 + lane)*16; c = 3*h + k, row g + 8h:
+//                  k = 0, 1: half hf = k: ql words t and 4+t of the first 32-byte run, then of the second
+//                  k = 2:    qh words t and 4+t of half 0, then of half 1
+//     [3328,3360)  d[16] f16
 //   Q8_0 (block: d f16 | qs[32], src/quants.h:53-57), 8 blocks per row per tile; block b of
 //   the 16 rows is one 544-byte piece at 544*b (so a run of blocks is one bulk copy):
 //     [  0, 32)  d: row r at 2*r
@@ -52,12 +62,14 @@ namespace qkm {
 
 static constexpr int kTileIq3 = 1568;
 static constexpr int kTileIq4 = 2176;
+static constexpr int kTileQ6 = 3360;
 static constexpr int kTileQ8 = 4352;
 
 __host__ __device__ inline int tile_bytes(uint32_t type) {
     switch (type) {
         case QKM_TYPE_IQ3_XXS: return kTileIq3;
         case QKM_TYPE_IQ4_XS: return kTileIq4;
+        case QKM_TYPE_Q6_K: return kTileQ6;
         case QKM_TYPE_Q8_0: return kTileQ8;
         default: return 0;
     }

@@ -67,6 +67,29 @@ def test_decode_full_size_layer_batches(pkg, orc, syn, T):
         assert np.array_equal(y, ctx.moe_forward_host(0, x, mode=0))
 
 
+@pytest.mark.parametrize("T", [3, 16, 64])
+def test_decode_q6k_down_batches(pkg, orc, syn, T):
+    """Layers whose routed down tensor is Q6_K take the fused decode sequence with the Q6_K form of
+    the down kernel (integer tensor-core arithmetic on Q6_K tiles): the decode tolerance holds,
+    a row with a NaN stays confined to its token, and a second call is bit-identical."""
+    dims = syn.Dims()
+    layer = syn.make_layer(dims, seed=44, down_type=syn.Q6_K)
+    x = syn.random_x(T, dims.n_embd, seed=48)
+    x[T // 2] *= 1e-3
+    if T > 3:
+        x[1, 7] = np.nan
+    ref = orc.moe_layer(layer, x, threads=orc.hardware_threads())
+    with pkg.Context(dims, n_layer=1, max_tokens=T, device=0) as ctx:
+        ctx.upload_layer(0, layer)
+        y = ctx.moe_forward_host(0, x, mode=0)
+        sel = ctx.last_sel(T)
+        assert np.array_equal(sel["ids"][:, :8], ref["sel"]["ids"][:, :8])
+        ok = np.isfinite(x).all(axis=1)
+        assert syn.rel_err_rows(y[ok], ref["y"][ok]) < TOL_F32
+        assert np.isnan(y[~ok]).all()
+        assert np.array_equal(y, ctx.moe_forward_host(0, x, mode=0), equal_nan=True)
+
+
 @pytest.mark.parametrize("router_type", [0, 1])
 def test_decode_router_ties_and_nonfinite(pkg, orc, syn, router_type):
     """The fused decode router (logits + ranking + grouping in one launch) on the hazards the

@@ -139,8 +139,8 @@ def test_prefill_matches_decode_path(pkg, syn):
 
 @pytest.mark.parametrize("T", [70, 200])
 def test_prefill_q6k_down(pkg, orc, syn, T):
-    """Q6_K down tensors have no tile layout: gate/up runs on the tensor cores, the down
-    projection on the f32 kernels."""
+    """Q6_K down tensors: both expert GEMMs on the tensor cores (the down kernel dequantises
+    Q6_K tiles to f16)."""
     dims = syn.Dims()
     layer = syn.make_layer(dims, seed=46, router_type=syn.F32, down_type=syn.Q6_K)
     x = syn.random_x(T, dims.n_embd, seed=78)
