@@ -27,6 +27,8 @@ struct qkm_layer_dev {
     bool tiles_ok = false;   // routed gate/up and down both have tiles
     bool stream_ok = false;  // tiles, and every expert resident: the fused decode / prefill sequences apply
     bool gu_only = false;    // as stream_ok for gate/up and the shared expert; the down tensor is Q6_K (tiles[4] holds Q6_K tiles)
+    bool fused_ok = false;   // every tensor has tiles and every expert is resident (any supported type mix): the
+                             // three-kernel decode sequence and the tensor-core prefill apply
 };
 
 struct qkm_ctx {
@@ -460,7 +462,7 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
     }
     // tile-ordered copies for the streaming kernels (same bytes, re-ordered on the device)
     for (void*& p : l.tiles) { if (p) { QKM_CUDA(c, cudaFree(p)); p = nullptr; } }
-    l.stream_ok = l.tiles_ok = l.gu_only = false;
+    l.stream_ok = l.tiles_ok = l.gu_only = l.fused_ok = false;
     if (c->shapes_stream_ok) {
         const qkm_dims& d = c->cfg.dims;
         struct { int idx; uint32_t type, mats, rows, K; } plan[] = {
@@ -471,7 +473,6 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
         };
         const bool gu = w->gateup_type == QKM_TYPE_IQ3_XXS, dn = w->down_type == QKM_TYPE_IQ4_XS;
         for (auto& t : plan) {
-            if (!gu) break;                       // without streamed gate/up nothing else is used
             const size_t bytes = tensor_bytes(c, t.idx, *w);
             QKM_CUDA(c, cudaMalloc(&l.tiles[t.idx], bytes + 256));
             cudaError_t e = launch_repack(c->L(), t.type, l.allocs[t.idx], l.tiles[t.idx], t.mats, t.rows, t.K);
@@ -481,6 +482,7 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
         l.tiles_ok = gu && dn;
         l.stream_ok = gu && dn && all_resident;
         l.gu_only = gu && !dn && all_resident;
+        l.fused_ok = all_resident;
     }
     QKM_CUDA(c, cudaStreamSynchronize(c->stream));
     l.w = *w;
@@ -617,7 +619,8 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     c->prof_begin();
-    if (!ld.stream_ok && !ld.gu_only) {  // generic kernels on the raw layout
+    const bool fused = ld.fused_ok && c->dec_ok && route_decode_ok(d, n, c->route_scratch_bytes) && decode_down_ok(d);
+    if (!fused && !ld.stream_ok && !ld.gu_only) {  // generic kernels on the raw layout
         QKM_LAUNCH(c, launch_route_select(c->L(), d, w.router_type, w.router, w.gate_inp_shexp, x, c->sel, n, c->route_scratch, c->route_scratch_bytes));
         c->prof_mark("moe.route");
         QKM_LAUNCH(c, launch_shared_gateup(c->L(), d, w.gate_shexp, w.up_shexp, x, c->h, n));
@@ -635,8 +638,7 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
     // projections of both and the weighted sum.  The shared expert rides inside (2) and (3): no
     // side stream, and nothing runs beside the two persistent kernels that they would have to
     // share the SMs with.
-    if (c->dec_ok && w.gateup_type == QKM_TYPE_IQ3_XXS && route_decode_ok(d, n, c->route_scratch_bytes) &&
-        decode_down_ok(d)) {
+    if (fused) {
         RouteDecodeArgs ra{};
         ra.router = (const uint8_t*)w.router; ra.gis = w.gate_inp_shexp; ra.x = x; ra.sel = c->sel;
         ra.logits = (double*)c->route_scratch; ra.counter = c->route_counter; ra.planes = c->planes8; ra.xscale = c->xscale; ra.n_tokens = n; ra.d = d;
@@ -647,10 +649,11 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         ga.sh_gate_tiles = (const uint8_t*)ld.tiles[5]; ga.sh_up_tiles = (const uint8_t*)ld.tiles[6];
         ga.luts = c->lut_gu; ga.planes = c->planes8; ga.xscale = c->xscale; ga.sel = c->sel;
         ga.n_tokens = n; ga.expert_first = c->efirst; ga.expert_count = c->ecount; ga.with_shared = 1;
+        ga.gateup_type = w.gateup_type;
         ga.h = c->h; ga.status = c->status; ga.d = d;
         QKM_LAUNCH(c, launch_decode_gateup(c->Lchain(), ga, nb));
         c->prof_mark("moe.gu");
-        if (ld.stream_ok) {
+        if (w.down_type == QKM_TYPE_IQ4_XS) {
             DownDecodeArgs da{};
             da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7];
             da.h = c->h; da.sel = c->sel; da.y = y; da.n_tokens = n; da.status = c->status; da.d = d;
@@ -769,7 +772,7 @@ extern "C" QKM_API int qkm_moe_prefill(qkm_ctx* c, uint32_t layer, const float* 
     const qkm_layer_weights& w = ld.w;
     const qkm_dims& d = c->cfg.dims;
     c->shared_plan_n = 0;   // this call rewrites the scratch the decode work lists live in
-    if ((!ld.stream_ok && !ld.gu_only) || n == 0) return prefill_generic(c, ld, x, n, y);
+    if (!ld.fused_ok || n == 0) return prefill_generic(c, ld, x, n, y);
     // tensor-core path: tokens grouped by expert, expert GEMMs on tcgen05 with bf16 operands
     const uint32_t NT = prefill_pairs_per_block();
     const uint32_t rt_gu = d.n_ff / 128, rt_dn = d.n_embd / 128;

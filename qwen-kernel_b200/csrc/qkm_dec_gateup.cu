@@ -29,6 +29,11 @@
 //     partial sums; d * 0.25 and the digit weights are applied once per tile in f32.
 // Q8_0 tiles are cut into quarters (two 32-column blocks) so that a stage of the same ring
 // holds them.
+//
+// IQ4_XS gate/up tensors (moe_gateup_iq4.comp) take the same kernel, instantiated with the inner
+// step of the decode down kernel: the 16-entry codebook in four registers, looked up with byte
+// permutes, the 6-bit sub-block scales as integers.  No table image: the rings (4352 bytes per
+// stage) lie in one run at the start of shared memory.
 #include "qkm_dec_rank.cuh"
 #include "qkm_kernels.h"
 #include "qkm_stream.cuh"
@@ -41,6 +46,8 @@ constexpr int kWarps = 16;
 constexpr int kStages = 2;
 constexpr int kStageBytes = 2 * kTileIq3;          // gate tile + up tile (3136); a Q8_0 quarter pair needs 2176
 constexpr int kRingBytes = kStages * kStageBytes;
+constexpr int kStageBytes4 = 2 * kTileIq4;         // the IQ4_XS form: 4352
+constexpr int kRingBytes4 = kStages * kStageBytes4;
 constexpr uint32_t kTab = 65536, kTabBytes = 65536;   // absolute shared-window address (64 KB aligned) and size
 constexpr int kLowRingWarps = 10;                   // rings below the table; the others above it
 constexpr int kGroupTiles = 4;                      // tiles between two team-wide reductions
@@ -49,6 +56,11 @@ constexpr uint32_t kHigh = kTab + kTabBytes;
 constexpr uint32_t kRed = kHigh + (kWarps - kLowRingWarps) * kRingBytes;
 constexpr uint32_t kRank = kRed + kWarps * 2 * kRedFloats * 4;   // RankShared: selection scratch, group list, pairs
 constexpr uint32_t kEnd = kRank + ((sizeof(RankShared) + 127) / 128) * 128;
+// IQ4_XS form, offsets from the (128-byte aligned) start of the dynamic area: barriers, rings, scratch
+constexpr uint32_t kRings4 = 1024;
+constexpr uint32_t kRed4 = kRings4 + kWarps * kRingBytes4;
+constexpr uint32_t kRank4 = kRed4 + kWarps * 2 * kRedFloats * 4;
+constexpr uint32_t kEnd4 = kRank4 + ((sizeof(RankShared) + 127) / 128) * 128 + 128;
 constexpr int kQ8Quarter = 2 * 544;                 // two 32-column blocks of a Q8_0 tile: d and quants of 16 rows each
 constexpr uint32_t kCostRouted = 8, kCostShared = 11;   // relative time of a routed / a shared tile (measured)
 }  // namespace dg
@@ -117,6 +129,55 @@ __device__ __forceinline__ void iq3_tile(uint32_t tb, uint32_t lane, uint32_t g,
     }
 }
 
+// Eight IQ4_XS weights of one quant word (low nibbles: elements 4t..4t+3, high nibbles: 16+4t..16+4t+3) as
+// two int8 A-operand registers: lo = elements (4t, 16+4t, 4t+1, 17+4t), hi = (4t+2, 18+4t, 4t+3, 19+4t).
+__device__ __forceinline__ void iq4_word_gu(uint32_t w, uint32_t& lo, uint32_t& hi) {
+    const uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;   // kvalues_iq4nl as int8
+    const uint32_t s = w & 0x77777777u, s2 = s >> 16, w4 = w << 4;
+    const uint32_t m_lo = prmt(w4, w, 0xD9C8u), m_hi = prmt(w4, w, 0xFBEAu);   // 0xFF where a nibble's top bit is set
+    const uint32_t a_lo = prmt(T0, T1, s), b_lo = prmt(T2, T3, s);
+    const uint32_t a_hi = prmt(T0, T1, s2), b_hi = prmt(T2, T3, s2);
+    lo = (a_lo & ~m_lo) | (b_lo & m_lo);
+    hi = (a_hi & ~m_hi) | (b_hi & m_hi);
+}
+// the eight sub-block scales ls - 32 of one row as int8: sub-blocks 0,2,4,6 in ev, 1,3,5,7 in od
+__device__ __forceinline__ void iq4_scales_gu(uint32_t sl, uint32_t sh, uint32_t& ev, uint32_t& od) {
+    const uint32_t r = prmt(sh, 0u, 0x1100u);
+    const uint32_t he = ((r << 4) & 0x00300030u) | (r & 0x30003000u);
+    const uint32_t ho = ((r << 2) & 0x00300030u) | ((r >> 2) & 0x30003000u);
+    const uint32_t te = ((sl & 0x0F0F0F0Fu) | he) ^ 0x20202020u;
+    const uint32_t to = (((sl >> 4) & 0x0F0F0F0Fu) | ho) ^ 0x20202020u;
+    ev = (te & 0x20202020u) * 6u + te;
+    od = (to & 0x20202020u) * 6u + to;
+}
+// One IQ4_XS tile against the warp's B operand (elements in iq4_word_gu's order).  acc as in iq3_tile;
+// hd: the headers of rows g (x: d | scales_h << 16, y: scales_l) and g+8 (z, w).
+__device__ __forceinline__ void iq4_tile_gu(uint32_t tb, uint32_t lane, uint32_t g, const uint32_t (&b0)[8],
+                                            const uint32_t (&b1)[8], int (&acc)[4], uint4& hd) {
+    hd = lds128(tb + 16 * g);
+    uint32_t ea, oa, eb, ob;
+    iq4_scales_gu(hd.y, hd.x >> 16, ea, oa);
+    iq4_scales_gu(hd.w, hd.z >> 16, eb, ob);
+    acc[0] = acc[1] = acc[2] = acc[3] = 0;
+#pragma unroll
+    for (int hf = 0; hf < 2; ++hf) {
+        const uint4 qa4 = lds128(tb + 128 + (hf * 32 + lane) * 16), qb4 = lds128(tb + 128 + ((2 + hf) * 32 + lane) * 16);
+        const uint32_t wa[4] = {qa4.x, qa4.y, qa4.z, qa4.w}, wb[4] = {qb4.x, qb4.y, qb4.z, qb4.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int sb = 4 * hf + j;
+            uint32_t a0, a1, a2, a3;
+            iq4_word_gu(wa[j], a0, a2);
+            iq4_word_gu(wb[j], a1, a3);
+            int c[4] = {0, 0, 0, 0};
+            mma_s8(c, a0, a1, a2, a3, b0[sb], b1[sb]);
+            const uint32_t sel = 0x8880u + (uint32_t)(sb >> 1) * 0x1111u;   // byte sb / 2, sign-extended
+            const int la = (int)prmt((sb & 1) ? oa : ea, 0u, sel), lb = (int)prmt((sb & 1) ? ob : eb, 0u, sel);
+            acc[0] += la * c[0]; acc[1] += la * c[1]; acc[2] += lb * c[2]; acc[3] += lb * c[3];
+        }
+    }
+}
+
 // Two Q8_0 blocks (a quarter tile) of one matrix: q points at two 544-byte pieces [d 32 B][quants 512 B].
 __device__ __forceinline__ void q8_quarter(uint32_t q, uint32_t lane, uint32_t g, uint32_t b0a, uint32_t b1a, uint32_t b0b,
                                            uint32_t b1b, float wcol0, float wcol1, float& fa, float& fb) {
@@ -136,8 +197,11 @@ __device__ __forceinline__ void q8_quarter(uint32_t q, uint32_t lane, uint32_t g
     }
 }
 
+template <bool IQ4>
 __global__ void __launch_bounds__(dg::kWarps * 32, 1)
 decode_gateup_kernel(GateupDecodeArgs a) {
+    constexpr int kTileR = IQ4 ? kTileIq4 : kTileIq3;                       // routed tile bytes
+    constexpr int kStageB = IQ4 ? dg::kStageBytes4 : dg::kStageBytes, kRingB = IQ4 ? dg::kRingBytes4 : dg::kRingBytes;
     extern __shared__ __align__(128) uint8_t smem_raw[];
     const uint32_t base = smem_addr(smem_raw);
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
@@ -147,16 +211,18 @@ decode_gateup_kernel(GateupDecodeArgs a) {
     const uint32_t team = warp / KB, kb = warp - team * KB;
     const uint32_t RT = d.n_ff / 16;              // tiles per group
 
-    const uint32_t bar_base = (base + 15u) & ~15u;                       // kWarps * kStages ring barriers, then the table's
+    const uint32_t base4 = (base + 127u) & ~127u;                        // IQ4_XS form: everything relative to here
+    const uint32_t bar_base = IQ4 ? base4 : (base + 15u) & ~15u;         // kWarps * kStages ring barriers, then the table's
     const uint32_t tab_bar = bar_base + dg::kWarps * dg::kStages * 8;
     const uint32_t low_ring = (tab_bar + 8 + 127u) & ~127u;
-    if (low_ring + dg::kLowRingWarps * dg::kRingBytes > dg::kTab) {      // layout assumption broken
+    if (!IQ4 && low_ring + dg::kLowRingWarps * dg::kRingBytes > dg::kTab) {   // layout assumption broken
         if (tid == 0) atomicExch(a.status, (uint32_t)kStatusBadLayout);
         return;
     }
-    const uint32_t ring = warp < (uint32_t)dg::kLowRingWarps ? low_ring + warp * dg::kRingBytes
+    const uint32_t ring = IQ4 ? base4 + dg::kRings4 + warp * kRingB
+                        : warp < (uint32_t)dg::kLowRingWarps ? low_ring + warp * dg::kRingBytes
                                                              : dg::kHigh + (warp - dg::kLowRingWarps) * dg::kRingBytes;
-    float* red = reinterpret_cast<float*>(smem_raw + (dg::kRed - base));
+    float* red = reinterpret_cast<float*>(smem_raw + ((IQ4 ? base4 + dg::kRed4 : dg::kRed) - base));
     const uint32_t my_bar = bar_base + warp * dg::kStages * 8;
     bool timed_out = false;
 
@@ -166,7 +232,7 @@ decode_gateup_kernel(GateupDecodeArgs a) {
         mbar_fence_init();
     }
     __syncthreads();
-    if (tid == 0) {   // the 64 KB table image comes from global memory (L2 after the first block) in four bulk copies
+    if (!IQ4 && tid == 0) {   // the 64 KB table image comes from global memory (L2 after the first block) in four bulk copies
         mbar_expect_tx(tab_bar, dg::kTabBytes);
         for (uint32_t i = 0; i < 4; ++i) bulk_g2s(dg::kTab + i * 16384u, a.luts + i * 16384u, 16384u, tab_bar);
     }
@@ -178,7 +244,7 @@ decode_gateup_kernel(GateupDecodeArgs a) {
     pdl_trigger();
 
     // Every block groups the selection's pairs by expert itself (same lists everywhere).
-    RankShared& S = *reinterpret_cast<RankShared*>(smem_raw + (dg::kRank - base));
+    RankShared& S = *reinterpret_cast<RankShared*>(smem_raw + ((IQ4 ? base4 + dg::kRank4 : dg::kRank) - base));
     group_pairs_shared(S, a.sel, d, a.n_tokens, a.expert_first, a.expert_count, a.with_shared != 0, dg::kWarps);
 
     // This team's contiguous share of the flat tile list.  A shared-expert (Q8_0) tile takes longer
@@ -211,18 +277,18 @@ decode_gateup_kernel(GateupDecodeArgs a) {
             p_kind = r.kind;
             if (p_kind == 0) {
                 const size_t tile = (size_t)r.expert * mat_tiles + (size_t)kb * RT + p_rt;
-                p_g = a.gate_tiles + tile * kTileIq3; p_u = a.up_tiles + tile * kTileIq3;
+                p_g = a.gate_tiles + tile * kTileR; p_u = a.up_tiles + tile * kTileR;
             } else {
                 const size_t tile = (size_t)kb * RT + p_rt;
                 p_g = a.sh_gate_tiles + tile * kTileQ8; p_u = a.sh_up_tiles + tile * kTileQ8;
             }
         }
-        const uint32_t bar = my_bar + 8 * stage, dst = ring + stage * dg::kStageBytes;
+        const uint32_t bar = my_bar + 8 * stage, dst = ring + stage * kStageB;
         if (p_kind == 0) {
-            mbar_expect_tx(bar, 2 * kTileIq3);
-            bulk_g2s(dst, p_g, kTileIq3, bar);
-            bulk_g2s(dst + kTileIq3, p_u, kTileIq3, bar);
-            p_g += kTileIq3; p_u += kTileIq3;
+            mbar_expect_tx(bar, 2 * kTileR);
+            bulk_g2s(dst, p_g, kTileR, bar);
+            bulk_g2s(dst + kTileR, p_u, kTileR, bar);
+            p_g += kTileR; p_u += kTileR;
             ++p_tile; ++p_rt;
         } else {
             mbar_expect_tx(bar, 2 * dg::kQ8Quarter);   // a quarter = two 32-column blocks = one 1088-byte piece
@@ -250,7 +316,7 @@ decode_gateup_kernel(GateupDecodeArgs a) {
     size_t h_base = 0;
     bool ts_live = false;
 
-    if (!mbar_wait_bounded(tab_bar, 0)) timed_out = true;   // every thread observes the table's arrival itself
+    if (!IQ4 && !mbar_wait_bounded(tab_bar, 0)) timed_out = true;   // every thread observes the table's arrival itself
 
     for (uint32_t tile = t_lo; tile < t_hi; ++tile) {
         if (new_group) {
@@ -271,7 +337,11 @@ decode_gateup_kernel(GateupDecodeArgs a) {
                 const int8_t* pl = a.planes + (((size_t)tok * KB + kb) * 8 + dgt) * 256;
 #pragma unroll
                 for (int sb = 0; sb < 8; ++sb) {
-                    if (rec.kind == 0) {   // lane t owns elements 8t .. 8t+7 of each sub-block
+                    if (IQ4 && rec.kind == 0) {   // iq4_word_gu's order: (4t, 16+4t, 4t+1, 17+4t | 4t+2, 18+4t, 4t+3, 19+4t)
+                        const uint32_t v = *reinterpret_cast<const uint32_t*>(pl + 32 * sb + 4 * t);
+                        const uint32_t u = *reinterpret_cast<const uint32_t*>(pl + 32 * sb + 16 + 4 * t);
+                        b0[sb] = prmt(v, u, 0x5140u); b1[sb] = prmt(v, u, 0x7362u);
+                    } else if (rec.kind == 0) {   // lane t owns elements 8t .. 8t+7 of each sub-block
                         const uint2 v = *reinterpret_cast<const uint2*>(pl + 32 * sb + 8 * t);
                         const uint2 n = *reinterpret_cast<const uint2*>(pl + 1024 + 32 * sb + 8 * t);
                         b0[sb] = v.x; b1[sb] = v.y; n0[sb] = n.x; n1[sb] = n.y;
@@ -298,8 +368,20 @@ decode_gateup_kernel(GateupDecodeArgs a) {
         if (rec.kind == 0) {
             const uint32_t stage = cnt % dg::kStages, parity = (cnt / dg::kStages) & 1u;
             if (!mbar_wait_bounded(my_bar + 8 * stage, parity)) timed_out = true;
-            const uint32_t sbase = ring + stage * dg::kStageBytes;
+            const uint32_t sbase = ring + stage * kStageB;
             int ig[4], iu[4];
+            if (IQ4) {
+                uint4 hg, hu;
+                iq4_tile_gu(sbase, lane, g, b0, b1, ig, hg);
+                iq4_tile_gu(sbase + kTileIq4, lane, g, b0, b1, iu, hu);
+                __syncwarp();
+                if (lane == 0) issue(stage);
+                ++cnt;
+                ga = f16_bits_to_f32(hg.x & 0xFFFFu) * ((float)ig[0] * wcol0 + (float)ig[1] * wcol1);
+                gb = f16_bits_to_f32(hg.z & 0xFFFFu) * ((float)ig[2] * wcol0 + (float)ig[3] * wcol1);
+                ua = f16_bits_to_f32(hu.x & 0xFFFFu) * ((float)iu[0] * wcol0 + (float)iu[1] * wcol1);
+                ub = f16_bits_to_f32(hu.z & 0xFFFFu) * ((float)iu[2] * wcol0 + (float)iu[3] * wcol1);
+            } else {
             iq3_tile(sbase, lane, g, grid_c, sign_c, rot, b0, b1, n0, n1, ig);
             iq3_tile(sbase + kTileIq3, lane, g, grid_c, sign_c, rot, b0, b1, n0, n1, iu);
             const uint32_t dwa = lds32(sbase + 1536 + 2 * (g & ~1u)), dwb = lds32(sbase + 1536 + 2 * ((g + 8) & ~1u));
@@ -313,13 +395,14 @@ decode_gateup_kernel(GateupDecodeArgs a) {
             gb = (f16_bits_to_f32((dwb >> sh) & 0xFFFFu) * 0.25f) * ((float)ig[2] * wcol0 + (float)ig[3] * wcol1);
             ua = (f16_bits_to_f32((uwa >> sh) & 0xFFFFu) * 0.25f) * ((float)iu[0] * wcol0 + (float)iu[1] * wcol1);
             ub = (f16_bits_to_f32((uwb >> sh) & 0xFFFFu) * 0.25f) * ((float)iu[2] * wcol0 + (float)iu[3] * wcol1);
+            }
         } else {
             ga = gb = ua = ub = 0.f;
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
                 const uint32_t stage = cnt % dg::kStages, parity = (cnt / dg::kStages) & 1u;
                 if (!mbar_wait_bounded(my_bar + 8 * stage, parity)) timed_out = true;
-                const uint32_t sbase = ring + stage * dg::kStageBytes;
+                const uint32_t sbase = ring + stage * kStageB;
                 q8_quarter(sbase, lane, g, b0[2 * q], b1[2 * q], b0[2 * q + 1], b1[2 * q + 1], wcol0, wcol1, ga, gb);
                 q8_quarter(sbase + dg::kQ8Quarter, lane, g, b0[2 * q], b1[2 * q], b0[2 * q + 1], b1[2 * q + 1], wcol0, wcol1, ua, ub);
                 __syncwarp();
@@ -369,10 +452,19 @@ bool decode_gateup_ok(const qkm_dims& d) {
 
 cudaError_t launch_decode_gateup(const Launch& L, const GateupDecodeArgs& a, uint32_t n_blocks) {
     if (!decode_gateup_ok(a.d)) return cudaErrorInvalidValue;
+    if (a.gateup_type == QKM_TYPE_IQ4_XS) {
+        const size_t smem4 = dg::kEnd4;
+        cudaError_t e4 = cudaFuncSetAttribute(decode_gateup_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem4);
+        if (e4 != cudaSuccess) return e4;
+        e4 = launch_kernel(L, decode_gateup_kernel<true>, dim3(n_blocks), dim3(dg::kWarps * 32), smem4, a);
+        L.count();
+        return e4 != cudaSuccess ? e4 : cudaGetLastError();
+    }
+    if (a.gateup_type != QKM_TYPE_IQ3_XXS) return cudaErrorInvalidValue;
     const size_t smem = dg::kEnd;   // the dynamic area must reach from wherever it starts to the end of the scratch
-    cudaError_t e = cudaFuncSetAttribute(decode_gateup_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(decode_gateup_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
-    e = launch_kernel(L, decode_gateup_kernel, dim3(n_blocks), dim3(dg::kWarps * 32), smem, a);
+    e = launch_kernel(L, decode_gateup_kernel<false>, dim3(n_blocks), dim3(dg::kWarps * 32), smem, a);
     L.count();
     return e != cudaSuccess ? e : cudaGetLastError();
 }

@@ -83,7 +83,7 @@ bool route_decode_ok(const qkm_dims& d, uint32_t n_tokens, size_t scratch_bytes)
 cudaError_t launch_route_decode(const Launch& L, uint32_t router_type, const RouteDecodeArgs& a);
 // routed (IQ3_XXS) and shared (Q8_0) gate/up + SwiGLU over the groups
 struct GateupDecodeArgs {
-    const uint8_t* gate_tiles;      // routed experts, IQ3_XXS tiles
+    const uint8_t* gate_tiles;      // routed experts, IQ3_XXS or IQ4_XS tiles (gateup_type)
     const uint8_t* up_tiles;
     const uint8_t* sh_gate_tiles;   // shared expert, Q8_0 tiles (may be NULL when no group has kind 1)
     const uint8_t* sh_up_tiles;
@@ -92,6 +92,7 @@ struct GateupDecodeArgs {
     const float* xscale;
     const qkm_sel* sel;             // the selection (its pairs are grouped by expert in every block at its start)
     uint32_t n_tokens, expert_first, expert_count, with_shared;
+    uint32_t gateup_type;           // QKM_TYPE_IQ3_XXS or QKM_TYPE_IQ4_XS
     float* h;                       // out [T][n_used+1][n_ff]
     uint32_t* status;
     qkm_dims d;

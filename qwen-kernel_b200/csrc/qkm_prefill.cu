@@ -269,6 +269,27 @@ __device__ __forceinline__ void produce_iq4(const Iq4Raw& raw, uint32_t q, uint3
     }
 }
 
+// IQ4_XS to f16 without the pair table (the gate/up kernel's form): the codebook times the sub-block
+// scale as sixteen floats in shared memory (sixteen banks: look-ups of different entries never
+// conflict, equal ones broadcast), one rounding of d * (ls - 32) * kvalue to f16.
+__device__ __forceinline__ void produce_iq4_f16(const Iq4Raw& raw, uint32_t q, uint32_t j, const float* __restrict__ s_kv,
+                                                uint8_t* a_tile, uint32_t row) {
+    const uint32_t sb = 2 * q + j, sh = raw.hd.x >> 16;
+    const int ls = (int)(((raw.hd.y >> (4 * sb)) & 0xFu) | (((sh >> (2 * sb)) & 3u) << 4)) - 32;
+    const float dl = f16_bits_to_f32(raw.hd.x & 0xFFFFu) * (float)ls;
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {      // elements 8p .. 8p+7: low nibbles of words 2p, 2p+1 (p < 2), high nibbles of words 2p-4, 2p-3
+        const uint32_t sft = (p >> 1) ? 4u : 0u;
+        const uint32_t a = raw.w[2 * (p & 1)] >> sft, b = raw.w[2 * (p & 1) + 1] >> sft;
+        uint4 o;
+        o.x = pack16<true>(dl * s_kv[a & 15u], dl * s_kv[(a >> 8) & 15u]);
+        o.y = pack16<true>(dl * s_kv[(a >> 16) & 15u], dl * s_kv[(a >> 24) & 15u]);
+        o.z = pack16<true>(dl * s_kv[b & 15u], dl * s_kv[(b >> 8) & 15u]);
+        o.w = pack16<true>(dl * s_kv[(b >> 16) & 15u], dl * s_kv[(b >> 24) & 15u]);
+        *reinterpret_cast<uint4*>(a_tile + umma::sw128_chunk(row, 4 * j + p)) = o;
+    }
+}
+
 template <bool F16, int J0, int J1>
 __device__ __forceinline__ void produce_q8(const uint8_t* __restrict__ tile, uint32_t r16, uint32_t q,
                                            uint8_t* a_tile, uint32_t row) {
@@ -354,7 +375,8 @@ __device__ __forceinline__ void store_b(uint8_t* b_tile, const BRegs& b, uint32_
 }
 
 // ---- gate/up + SwiGLU ------------------------------------------------------------------------------------
-// FMT: QKM_TYPE_IQ3_XXS (routed experts) or QKM_TYPE_Q8_0 (shared expert).
+// FMT: QKM_TYPE_Q8_0 (shared expert) or QKM_TYPE_IQ4_XS (routed experts of layers whose gate/up tensors are
+// IQ4_XS; 512 producers only).  IQ3_XXS routed experts have their own kernel below.
 // PT: producer threads.  256: a thread dequantises both 32-column sub-blocks of its row's k-step, two
 // blocks share an SM (big grids).  512: two threads share a row, one sub-block each, one block per
 // SM - for grids that do not fill the machine (a shard of few experts, the shared expert), where a
@@ -368,8 +390,10 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
                   __nv_bfloat16* __restrict__ hb, float* __restrict__ hp, qkm_dims d, uint32_t* __restrict__ status) {
     if (blockIdx.x >= *n_items_ptr) return;
     constexpr int kSt = pf::kStages;
-    static_assert(FMT == QKM_TYPE_Q8_0, "IQ3_XXS has its own kernel (gateup_iq3_kernel)");
-    constexpr int kTile = kTileQ8;
+    static_assert(FMT == QKM_TYPE_Q8_0 || (FMT == QKM_TYPE_IQ4_XS && PT == 512), "IQ3_XXS has its own kernel (gateup_iq3_kernel)");
+    constexpr int kTile = FMT == QKM_TYPE_IQ4_XS ? kTileIq4 : kTileQ8;
+    __shared__ float s_kv[16];
+    if (FMT == QKM_TYPE_IQ4_XS && threadIdx.x < 16) s_kv[threadIdx.x] = (float)c_iq4_values[threadIdx.x];
     extern __shared__ __align__(1024) uint8_t smem_dyn[];
     __shared__ __align__(8) unsigned long long s_bar[2 * kSt + 1];  // empty[stage], full[stage], done
     __shared__ uint32_t s_tmem;
@@ -443,7 +467,8 @@ gateup_mma_kernel(const uint8_t* __restrict__ gate_tiles, const uint8_t* __restr
             if (!mbar_wait_bounded(smem_addr(&s_bar[stage]), ((ks / kSt) - 1) & 1u)) timed_out = true;
         uint8_t* st = smem + stage * 3 * pf::kTileBytes;
         const uint8_t* tile = wt + ((size_t)(ks >> 2) * RT16 + rt16) * kTile;
-        if (PT == 256) produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
+        if (FMT == QKM_TYPE_IQ4_XS) produce_iq4_f16(load_iq4(tile, r16, ks & 3u, half), ks & 3u, half, s_kv, st + mat * pf::kTileBytes, r);
+        else if (PT == 256) produce_q8<true, 0, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
         else if (half == 0) produce_q8<true, 0, 1>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
         else produce_q8<true, 1, 2>(tile, r16, ks & 3u, st + mat * pf::kTileBytes, r);
         store_b<PT>(st + 2 * pf::kTileBytes, breg, n_mma);
@@ -1310,6 +1335,8 @@ cudaError_t launch_gateup_mma(const Launch& L, const qkm_dims& d, uint32_t type,
         if (!iq3_table) return cudaErrorInvalidValue;
         return gateup_iq3_launch(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, hp, iq3_table, status);
     }
+    if (type == QKM_TYPE_IQ4_XS)
+        return gateup_mma_launch<QKM_TYPE_IQ4_XS, 512>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, hp, status);
     if (type == QKM_TYPE_Q8_0)
         return few_blocks ? gateup_mma_launch<QKM_TYPE_Q8_0, 512>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, hp, status)
                           : gateup_mma_launch<QKM_TYPE_Q8_0, 256>(L, d, gate_tiles, up_tiles, xb, x_inv_scale, pairs, items, n_items, max_items, h, hb, hp, status);

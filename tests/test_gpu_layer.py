@@ -67,13 +67,15 @@ def test_decode_full_size_layer_batches(pkg, orc, syn, T):
         assert np.array_equal(y, ctx.moe_forward_host(0, x, mode=0))
 
 
+@pytest.mark.parametrize("gt,dt", [(18, 14), (23, 23), (23, 14)])
 @pytest.mark.parametrize("T", [3, 16, 64])
-def test_decode_q6k_down_batches(pkg, orc, syn, T):
-    """Layers whose routed down tensor is Q6_K take the fused decode sequence with the Q6_K form of
-    the down kernel (integer tensor-core arithmetic on Q6_K tiles): the decode tolerance holds,
+def test_decode_other_type_mixes_batches(pkg, orc, syn, T, gt, dt):
+    """Layers whose routed down tensor is Q6_K (14) and / or whose gate/up tensors are IQ4_XS (23)
+    take the fused decode sequence too, with the Q6_K form of the down kernel and the IQ4_XS form of
+    the gate/up kernel (integer tensor-core arithmetic on their tiles): the decode tolerance holds,
     a row with a NaN stays confined to its token, and a second call is bit-identical."""
     dims = syn.Dims()
-    layer = syn.make_layer(dims, seed=44, down_type=syn.Q6_K)
+    layer = syn.make_layer(dims, seed=44, gateup_type=gt, down_type=dt)
     x = syn.random_x(T, dims.n_embd, seed=48)
     x[T // 2] *= 1e-3
     if T > 3:

@@ -137,11 +137,12 @@ def test_prefill_matches_decode_path(pkg, syn):
     assert syn.rel_err_rows(yp, yd) < TOL_BF16
 
 
+@pytest.mark.parametrize("gt,dt", [(18, 14), (23, 23), (23, 14)])
 @pytest.mark.parametrize("T", [70, 200])
-def test_prefill_q6k_down(pkg, orc, syn, T):
-    """Q6_K down tensors: both expert GEMMs on the tensor cores (the down kernel dequantises
-    Q6_K tiles to f16)."""
+def test_prefill_other_type_mixes(pkg, orc, syn, T, gt, dt):
+    """Q6_K (14) down tensors and IQ4_XS (23) gate/up tensors: both expert GEMMs on the tensor cores
+    (kernels that dequantise Q6_K / IQ4_XS tiles to f16 in shared memory)."""
     dims = syn.Dims()
-    layer = syn.make_layer(dims, seed=46, router_type=syn.F32, down_type=syn.Q6_K)
+    layer = syn.make_layer(dims, seed=46, router_type=syn.F32, gateup_type=gt, down_type=dt)
     x = syn.random_x(T, dims.n_embd, seed=78)
     run_prefill(pkg, orc, syn, dims, layer, x)
