@@ -215,68 +215,85 @@ gemv_mma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restric
 // 16-byte aligned run of the matrix, and for K = 2048 its row stride (420 words) spreads the eight row
 // groups over different banks as it is.  So the whole tile comes in with ONE bulk copy into a
 // block-wide ring, and every warp reads its block from there.  Inside a block the 6-bit values are
-// put together from ql (low nibbles) and qh (two high bits) four at a time, turned into int8 q - 32,
-// and multiplied 16 columns at a time (mma.sync.m16n8k16.s8: one int8 scale per 16 columns, applied
-// to the integer sums), then by the block's f16 scale.
+// put together from ql (low nibbles) and qh (two high bits) four at a time as int8 4 * (q - 32),
+// and multiplied 32 columns at a time (mma.sync.m16n8k32.s8, the two 16-column groups of an MMA against
+// different B columns: one int8 scale per 16 columns, applied to the integer sums), then by the
+// block's f16 scale.
 namespace gq {
 constexpr int kRows = 16;
 constexpr int kGroup = 4;          // tiles between two reductions over the warps
 constexpr int kMaxStages = 8;
 }  // namespace gq
 
-__device__ __forceinline__ void mma_s8_k16(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t b0) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5}, {%6}, {%0,%1,%2,%3};"
-                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(b0));
-}
 // a 32-bit word at a 2-byte aligned shared address (ODD: the address is 2 mod 4)
 template <bool ODD>
 __device__ __forceinline__ uint32_t lds32_a2(uint32_t addr) {
     if (!ODD) return lds32(addr);
     return __funnelshift_r(lds32(addr - 2), lds32(addr + 2), 16);
 }
-// four 6-bit values (ql nibbles | qh bit pairs << 4) as int8 q - 32
-__device__ __forceinline__ uint32_t q6_to_s8(uint32_t wl, uint32_t wh, int nib_hi, int hshift) {
-    const uint32_t lo = nib_hi ? wl >> 4 : wl;
-    const uint32_t hi = hshift < 4 ? wh << (4 - hshift) : wh >> (hshift - 4);   // the bit pair to bits 4, 5 of each byte
-    const uint32_t q = (hi & 0x30303030u) | (lo & 0x0F0F0F0Fu);
-    const uint32_t v = q ^ 0x20202020u;          // q < 32: v = q + 32 (bit 5 set), and q - 32 = v - 64 = v | 0xC0 as int8
-    const uint32_t n = v & 0x20202020u;          // q >= 32: v = q - 32 already
-    return v + n * 6u;                           // | (n << 1) | (n << 2): no bits overlap, one multiply-add
+__device__ __forceinline__ uint32_t prmt_q6(uint32_t a, uint32_t b, uint32_t sel) {
+    uint32_t r;
+    asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
+    return r;
+}
+// Sixteen Q6_K weights as four int8 A-operand registers, each 4 * (q - 32): the 6-bit value sits in the top
+// six bits of its byte with its top bit flipped, so no sign extension is computed.  w1 / w2: the ql words
+// of elements l..l+3 in the first / second 32-byte run of a 128-column half, hq: the qh word of the same l;
+// r[qd] = elements l + 32 qd .. + 3  (src/quants.h:148-163).
+__device__ __forceinline__ void q6_words_x4(uint32_t w1, uint32_t w2, uint32_t hq, uint32_t (&r)[4]) {
+    const uint32_t hx = hq ^ 0xAAAAAAAAu;
+    const uint32_t lo1 = w1 & 0x0F0F0F0Fu, hi1 = w1 & 0xF0F0F0F0u;
+    const uint32_t lo2 = w2 & 0x0F0F0F0Fu, hi2 = w2 & 0xF0F0F0F0u;
+    r[0] = ((hx << 6) & 0xC0C0C0C0u) | (lo1 << 2);
+    r[1] = ((hx << 4) & 0xC0C0C0C0u) | (lo2 << 2);
+    r[2] = ((hx << 2) & 0xC0C0C0C0u) | (hi1 >> 2);
+    r[3] = (hx & 0xC0C0C0C0u) | (hi2 >> 2);
 }
 
+// One 16-row x 256-column tile.  MMA j = 4 hf + qd multiplies two 16-column groups at once (m16n8k32): the
+// first against B columns 0..3 (the four digit planes; zero over the second group's k range), the second
+// against columns 4..7, so lane t holds the sums of group 2j + t/2 for digits 2 (t & 1), 2 (t & 1) + 1 and
+// multiplies them by that group's int8 scale as integers.  f0 / f1: rows g / g+8, this lane's share
+// (the four lanes t of a row add up to the row's sum).
 template <bool ODD>
-__device__ __forceinline__ void q6k_tile(uint32_t blk0, uint32_t blk1, uint32_t t, const uint32_t (&bq)[16], float plane_w,
+__device__ __forceinline__ void q6k_tile(uint32_t blk0, uint32_t blk1, uint32_t t, const uint32_t (&b0)[8], const uint32_t (&b1)[8],
                                          float& f0, float& f1) {
-    // blk0 / blk1: this warp's block of rows g / g+8 in the stage.  The sixteen scales of each row as four words.
+    // blk0 / blk1: this warp's block of rows g / g+8 in the stage: ql[128] | qh[64] | scales[16] | d
     uint32_t sc0[4], sc1[4];
 #pragma unroll
     for (int k = 0; k < 4; ++k) { sc0[k] = lds32_a2<ODD>(blk0 + 192 + 4 * k); sc1[k] = lds32_a2<ODD>(blk1 + 192 + 4 * k); }
-    float s0 = 0.f, s1 = 0.f;
+    const uint32_t sel_e = 0x8880u + (t >> 1) * 0x1111u, sel_o = sel_e + 0x2222u;   // byte t/2 (+2), sign-extended
+    int acc[4] = {0, 0, 0, 0};
 #pragma unroll
-    for (int G0 = 0; G0 < 16; G0 += 4) {   // four groups of 16 columns: all their words are requested first
-        uint32_t wl0[4], wh0[4], wl1[4], wh1[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int G = G0 + u, hf = G >> 3, qd = (G & 7) >> 1, lofs = 16 * (G & 1);
-            const uint32_t ql = 64 * hf + 32 * (qd & 1) + lofs + 4 * t, qh = 128 + 32 * hf + lofs + 4 * t;
-            wl0[u] = lds32_a2<ODD>(blk0 + ql); wh0[u] = lds32_a2<ODD>(blk0 + qh);
-            wl1[u] = lds32_a2<ODD>(blk1 + ql); wh1[u] = lds32_a2<ODD>(blk1 + qh);
+    for (int hf = 0; hf < 2; ++hf) {
+        uint32_t a0[4], a1[4], a2[4], a3[4];
+        {
+            const uint32_t q0 = blk0 + 64 * hf + 4 * t, h0 = blk0 + 128 + 32 * hf + 4 * t;
+            const uint32_t q1 = blk1 + 64 * hf + 4 * t, h1 = blk1 + 128 + 32 * hf + 4 * t;
+            const uint32_t w0a = lds32_a2<ODD>(q0), w0b = lds32_a2<ODD>(q0 + 16), w0c = lds32_a2<ODD>(q0 + 32), w0d = lds32_a2<ODD>(q0 + 48);
+            const uint32_t w1a = lds32_a2<ODD>(q1), w1b = lds32_a2<ODD>(q1 + 16), w1c = lds32_a2<ODD>(q1 + 32), w1d = lds32_a2<ODD>(q1 + 48);
+            const uint32_t g0a = lds32_a2<ODD>(h0), g0b = lds32_a2<ODD>(h0 + 16), g1a = lds32_a2<ODD>(h1), g1b = lds32_a2<ODD>(h1 + 16);
+            q6_words_x4(w0a, w0c, g0a, a0);   // row g, l = 4t ..
+            q6_words_x4(w0b, w0d, g0b, a2);   // row g, l = 16 + 4t ..
+            q6_words_x4(w1a, w1c, g1a, a1);   // row g + 8
+            q6_words_x4(w1b, w1d, g1b, a3);
         }
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int G = G0 + u, qd = (G & 7) >> 1;
+        for (int qd = 0; qd < 4; ++qd) {
+            const int j = 4 * hf + qd;
             int c[4] = {0, 0, 0, 0};
-            mma_s8_k16(c, q6_to_s8(wl0[u], wh0[u], qd >> 1, 2 * qd), q6_to_s8(wl1[u], wh1[u], qd >> 1, 2 * qd), bq[G]);
-            const int a = (int)(int8_t)(sc0[G >> 2] >> (8 * (G & 3))), b = (int)(int8_t)(sc1[G >> 2] >> (8 * (G & 3)));
-            s0 += (float)((c[0] + (c[1] << 7)) * a);
-            s1 += (float)((c[2] + (c[3] << 7)) * b);
+            mma_s8(c, a0[qd], a1[qd], a2[qd], a3[qd], b0[j], b1[j]);
+            const uint32_t sel = (j & 1) ? sel_o : sel_e;
+            const int sa = (int)prmt_q6(sc0[j >> 1], 0u, sel), sb = (int)prmt_q6(sc1[j >> 1], 0u, sel);
+            acc[0] += sa * c[0]; acc[1] += sa * c[1]; acc[2] += sb * c[2]; acc[3] += sb * c[3];
         }
     }
     uint32_t d0, d1;
     asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d0) : "r"(blk0 + 208));
     asm volatile("ld.shared.u16 %0, [%1];" : "=r"(d1) : "r"(blk1 + 208));
-    f0 = s0 * plane_w * f16_bits_to_f32(d0);
-    f1 = s1 * plane_w * f16_bits_to_f32(d1);
+    const float dw0 = (t & 1u) ? 4096.f : 0.25f, dw1 = dw0 * 128.f;   // 128^(2 (t & 1)) / 4: the weights are 4 (q - 32)
+    f0 = f16_bits_to_f32(d0) * ((float)acc[0] * dw0 + (float)acc[1] * dw1);
+    f1 = f16_bits_to_f32(d1) * ((float)acc[2] * dw0 + (float)acc[3] * dw1);
 }
 
 // ---- IQ4_XS (in the same block-wide ring) -------------------------------------------------------------------
@@ -400,14 +417,18 @@ gemv_tile_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, flo
     }
     static_assert(TYPE == QKM_TYPE_Q6_K || TYPE == QKM_TYPE_IQ4_XS, "formats: Q6_K, IQ4_XS");
     constexpr uint32_t kBlockBytes = TYPE == QKM_TYPE_Q6_K ? 210u : 136u;
-    // B operands of this warp's 256 columns: column n = g is digit plane g (g < 4).  Q6_K: 16 columns each,
-    // k = 4t..4t+3.  IQ4_XS: 32 columns each in the codebook look-up's element order (see iq4_codebook_word).
+    // B operands of this warp's 256 columns.  IQ4_XS: column n = g is digit plane g (g < 4), 32 columns each in the
+    // codebook look-up's element order (see iq4_codebook_word).  Q6_K: see q6k_tile.
     uint32_t bq[16];
     {
         const uint32_t pl = smem_addr(planes) + warp * 1024u;
         if (TYPE == QKM_TYPE_Q6_K) {
 #pragma unroll
-            for (int G = 0; G < 16; ++G) bq[G] = g < 4 ? lds32(pl + g * 256 + G * 16 + t * 4) : 0u;
+            for (int j = 0; j < 8; ++j) {   // lanes g < 4: digit g of the first group of MMA j; g >= 4: digit g - 4 of the second
+                const uint32_t v = lds32(pl + (g & 3u) * 256 + j * 32 + (g >> 2) * 16 + t * 4);
+                bq[j] = g < 4 ? v : 0u;
+                bq[8 + j] = g < 4 ? 0u : v;
+            }
         } else {
 #pragma unroll
             for (int sb = 0; sb < 8; ++sb) {
@@ -440,15 +461,15 @@ gemv_tile_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, flo
                 if (!mbar_wait_bounded(bar_full + 8 * s, (i / n_stages) & 1u)) timed_out = true;
                 const uint32_t blk0 = stage0 + s * stage_bytes + g * rb + kBlockBytes * warp, blk1 = blk0 + 8u * rb;
                 float f0, f1;
-                if (TYPE == QKM_TYPE_IQ4_XS) {
-                    uint32_t b0[8], b1[8];
+                uint32_t b0[8], b1[8];
 #pragma unroll
-                    for (int sb = 0; sb < 8; ++sb) { b0[sb] = bq[sb]; b1[sb] = bq[8 + sb]; }
+                for (int sb = 0; sb < 8; ++sb) { b0[sb] = bq[sb]; b1[sb] = bq[8 + sb]; }
+                if (TYPE == QKM_TYPE_IQ4_XS) {
                     iq4_tile(blk0, blk1, t, b0, b1, plane_w, f0, f1);
                 } else if (odd) {
-                    q6k_tile<true>(blk0, blk1, t, bq, plane_w, f0, f1);
+                    q6k_tile<true>(blk0, blk1, t, b0, b1, f0, f1);
                 } else {
-                    q6k_tile<false>(blk0, blk1, t, bq, plane_w, f0, f1);
+                    q6k_tile<false>(blk0, blk1, t, b0, b1, f0, f1);
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(bar_empty + 8 * s);
@@ -460,6 +481,9 @@ gemv_tile_kernel(const uint8_t* __restrict__ W, const float* __restrict__ x, flo
         for (int q = 0; q < gq::kGroup; ++q) {
             float v0 = acc[q][0], v1 = acc[q][1];
             v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 1); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 1);
+            if (TYPE == QKM_TYPE_Q6_K) {   // all four lanes of a row hold a share
+                v0 += __shfl_xor_sync(0xFFFFFFFFu, v0, 2); v1 += __shfl_xor_sync(0xFFFFFFFFu, v1, 2);
+            }
             if (t == 0) { rw[q * gq::kRows + g] = v0; rw[q * gq::kRows + g + 8] = v1; }
         }
         __syncthreads();
