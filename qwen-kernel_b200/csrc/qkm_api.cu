@@ -71,6 +71,7 @@ struct qkm_ctx {
     bool dec_ok = false;               // dims fit the fused decode kernels
     int8_t* planes8 = nullptr;         // [max_tokens][n_embd/256][8][256]
     uint8_t* lut_gu = nullptr;         // table images the decode kernels copy to shared memory
+    uint8_t* lut_dd = nullptr;         // table image of the decode IQ4_XS down kernel
     uint8_t* lut_pf = nullptr;         // table image of the prefill IQ3_XXS gate/up kernel
     uint8_t* lut_dn = nullptr;         // table image of the prefill IQ4_XS down kernel
     uint32_t* status_host = nullptr;  // pinned mirror
@@ -288,6 +289,7 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
             struct { void** p; size_t bytes; } dec[] = {
                 {(void**)&c->planes8, T * 8 * d.n_embd},
                 {(void**)&c->lut_gu, decode_gateup_lut_bytes()},
+                {(void**)&c->lut_dd, decode_down_lut_bytes()},
             };
             for (auto& a : dec) {
                 if ((e = cudaMalloc(a.p, a.bytes)) != cudaSuccess) {
@@ -298,6 +300,7 @@ extern "C" QKM_API qkm_ctx* qkm_open(const qkm_config* cfg, char* err, size_t er
             }
             const Launch L0{nullptr, nullptr};
             if ((e = launch_decode_gateup_luts(L0, c->lut_gu)) != cudaSuccess ||
+                (e = launch_decode_down_lut(L0, c->lut_dd)) != cudaSuccess ||
                 (e = cudaDeviceSynchronize()) != cudaSuccess) {
                 bail("qkm_open: decode tables", cudaGetErrorString(e));
                 qkm_close(c);
@@ -350,7 +353,7 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     void* scratch[] = {c->argmax_scratch, c->dense_xb, c->dense_pairs, c->dense_sel, c->dense_items, c->dense_n_items, c->sel, c->h, c->route_scratch, c->offsets, c->pairs, c->contrib, c->y2, c->x_stage, c->y_stage,
                        c->stack_x, c->stack_y, c->xplanes, c->xscale, c->hpieces, c->items_gu, c->items_dn,
                        c->items_sh_gu, c->items_sh_dn, c->n_items, c->contrib_s, c->arrivals, c->status, c->route_counter,
-                       c->planes8, c->lut_gu, c->lut_pf, c->lut_dn,
+                       c->planes8, c->lut_gu, c->lut_dd, c->lut_pf, c->lut_dn,
                        c->xb, c->hb, c->hscale, c->contrib_p, c->mma_items[0], c->mma_items[1], c->mma_items[2], c->mma_items[3],
                        c->pos_of, c->group_hist, c->ep_counts, c->ep_send_tok, c->ep_send_pos};
     for (void* p : scratch) if (p) cudaFree(p);
@@ -655,7 +658,7 @@ extern "C" QKM_API int qkm_moe_decode(qkm_ctx* c, uint32_t layer, const float* x
         c->prof_mark("moe.gu");
         if (w.down_type == QKM_TYPE_IQ4_XS) {
             DownDecodeArgs da{};
-            da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7];
+            da.tiles = (const uint8_t*)ld.tiles[4]; da.sh_tiles = (const uint8_t*)ld.tiles[7]; da.lut = c->lut_dd;
             da.h = c->h; da.sel = c->sel; da.y = y; da.n_tokens = n; da.status = c->status; da.d = d;
             QKM_LAUNCH(c, launch_decode_down(c->Lchain(), da, nb));
         } else {   // Q6_K down

@@ -4,28 +4,31 @@
 //
 // Replaces moe_down_iq4.comp + moe_down_q8b.comp + the "routed + shared" add.  A unit of work
 // is (token, 16 output rows) and belongs to a whole block: warp (slot s, column block kb)
-// streams the 16-row tiles of expert ids_s, two at a time (they are consecutive in memory: one
-// bulk copy), through a private two-stage ring of bulk copies (TMA, no tensor map, no
-// multicast), so the eight slots of a token are worked on at once and are added in slot order
-// by the block - no per-slot scratch in global memory, no atomics, the same bits on every run.
-// The two tiles of a step are worked on side by side, so their dependent chains (table
-// look-ups, MMA, scale) overlap.  Tile pairs are cut evenly and contiguously over the blocks
-// (one pair of imbalance in ~7); a block sums once per chunk of up to two pairs.
+// streams the 16-row tiles of expert ids_s through a private three-stage ring of bulk copies
+// (TMA, no tensor map, no multicast), so the eight slots of a token are worked on at once and
+// are added in slot order by the block - no per-slot scratch in global memory, no atomics, the
+// same bits on every run.  The flat list of (token, tile) is cut evenly and contiguously over
+// the blocks; a block sums once per chunk of up to four tiles.
 //
 // Arithmetic: exact integers until the last step.  When its token changes, a warp encodes the
 // 256 values of h[t][s] it multiplies with as four int8 digit planes (28-bit fixed point
 // relative to the largest of the 256, one power-of-two scale) and keeps them in registers as
-// the B operand of int8 MMAs.  IQ4_XS inner step: the sixteen codebook values live in four
-// registers; a byte-permute with the quant nibbles as selectors looks up the lower and the
-// upper half of the codebook, a sign-replicating byte-permute of the nibbles' top bits picks
-// between them - eight weights per eleven instructions, no shared-memory table, no bank
-// conflicts.  The 6-bit sub-block scales (ls - 32) are unpacked eight at a time with word-wide
-// masks and multiply the int32 partial sums as integers; d, the digit weights, the plane scale
-// and the routing weight are applied once per tile in f32.
+// the B operand of int8 MMAs.  IQ4_XS inner step: a quant byte holds two weights 16 columns
+// apart; a 64 KB table image at shared address 0x10000 maps the byte to both codebook values
+// (row = byte value, 256-byte stride, one 4-byte entry per lane: bank = lane, no conflicts),
+// and a look-up address is one byte permute [lane * 4, byte, 0x01, 0x00].  Eight weights cost
+// four permutes, four loads and one more permute that packs the operand register - the
+// kernel is bound by the integer pipe, and this is half the work of looking the codebook up
+// with permutes of four constant registers.  The 6-bit sub-block scales (ls - 32) are unpacked
+// eight at a time with word-wide masks and multiply the int32 partial sums as integers; d, the
+// digit weights, the plane scale and the routing weight are applied once per tile in f32.
 //
 // Shared expert: warp w also takes 32-column block w of the Q8_0 matrix for the tile's rows:
 // raw int8 weights against h[t][n_used] as digit planes, which the block encodes in shared
 // memory whenever its token changes.
+//
+// Shared memory: the table occupies [0x10000, 0x20000) of the shared window; barriers, the first
+// rings and the shared row's planes lie below it, the other rings and the scratch above.
 #include "qkm_kernels.h"
 #include "qkm_stream.cuh"
 #include "qkm_tiles.cuh"
@@ -34,42 +37,49 @@ namespace qkm {
 
 namespace dd {
 constexpr int kWarps = 16;
-constexpr int kStages = 2;
+constexpr int kStages = 3;
 constexpr int kShBlock = 544;                       // one Q8_0 block column of a 16-row tile: d, quants
-constexpr int kStageBytes = 2 * kTileIq4 + 2 * kShBlock;   // two tiles, two shared blocks: 5440
-constexpr int kRingBytes = kStages * kStageBytes;
-constexpr int kChunk = 4;                           // tiles (two steps) between two block-wide sums
+constexpr int kStageBytes = kTileIq4 + kShBlock;    // 2720
+constexpr int kRingBytes = kStages * kStageBytes;   // 8160
+constexpr int kChunk = 4;                           // tiles between two block-wide sums
 constexpr uint32_t kMaxFf = 512;
-// dynamic shared memory, offsets from a 128-byte aligned base
-constexpr uint32_t kBars = 0;                                              // kWarps * kStages mbarriers
-constexpr uint32_t kRings = 1024;
-constexpr uint32_t kDig = kRings + kWarps * kRingBytes;                    // per warp: 4 digit planes x 256 B, operand order
+constexpr uint32_t kTab = 0x10000u, kTabBytes = 0x10000u;   // absolute shared-window address (64 KB aligned) and size
+constexpr int kLowRingWarps = 7;                    // rings below the table; the others above it
+// absolute shared-window addresses above the table
+constexpr uint32_t kHigh = kTab + kTabBytes;
+constexpr uint32_t kDig = kHigh + (kWarps - kLowRingWarps) * kRingBytes;   // per warp: 4 digit planes x 256 B, operand order
 constexpr uint32_t kRed = kDig + kWarps * 1024;                            // [2 buffers][16 warps][kChunk tiles][16 rows]
-constexpr uint32_t kHd = kRed + 2 * kWarps * kChunk * 16 * 4;              // 4 digit planes x 512 of h[t][n_used]
-constexpr uint32_t kMisc = kHd + 4 * kMaxFf;                               // 16 warp maxima
-constexpr uint32_t kEnd = kMisc + 128;
+constexpr uint32_t kEnd = kRed + 2 * kWarps * kChunk * 16 * 4;
+// below the table, offsets from the (128-byte aligned) start of the dynamic area
+constexpr uint32_t kBars = 0;                                              // kWarps * kStages ring barriers, then the table's
+constexpr uint32_t kMisc = 512;                                            // 16 warp maxima
+constexpr uint32_t kHd = 640;                                              // 4 digit planes x 512 of h[t][n_used]
+constexpr uint32_t kLowRings = kHd + 4 * kMaxFf;                           // 2688
 }  // namespace dd
 
+size_t decode_down_lut_bytes() { return dd::kTabBytes; }
+
+// The table image: row b (256 B) = for each of 32 lanes the 4-byte entry (kvalues[b & 15], kvalues[b >> 4], 0, 0)
+// as int8 (src/quant_tables.h: kvalues_iq4nl); the upper 128 bytes of a row are unused.
+__global__ void decode_down_lut_kernel(uint8_t* __restrict__ out) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;   // one 4-byte word each
+    if (i >= dd::kTabBytes / 4) return;
+    const uint32_t row = i >> 6, w = i & 63u;
+    uint32_t v = 0;
+    if (w < 32) v = (uint32_t)(uint8_t)c_iq4_values[row & 15u] | ((uint32_t)(uint8_t)c_iq4_values[row >> 4] << 8);
+    reinterpret_cast<uint32_t*>(out)[i] = v;
+}
+
+cudaError_t launch_decode_down_lut(const Launch& L, uint8_t* lut) {
+    decode_down_lut_kernel<<<dd::kTabBytes / 4 / 256, 256, 0, L.stream>>>(lut);
+    L.count();
+    return cudaGetLastError();
+}
 
 __device__ __forceinline__ uint32_t prmt_dd(uint32_t a, uint32_t b, uint32_t sel) {
     uint32_t r;
     asm("prmt.b32 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(sel));
     return r;
-}
-
-// Eight IQ4_XS weights of one quant word (bytes 4t..4t+3 of a sub-block's sixteen: the low nibbles
-// are elements 4t..4t+3, the high nibbles elements 16+4t..16+4t+3) as two int8 MMA A-operand
-// registers: lo = elements (4t, 16+4t, 4t+1, 17+4t), hi = elements (4t+2, 18+4t, 4t+3, 19+4t).
-// T0..T3: the codebook kvalues_iq4nl (src/quant_tables.h), four int8 per register.
-__device__ __forceinline__ void iq4_word(uint32_t w, uint32_t T0, uint32_t T1, uint32_t T2, uint32_t T3,
-                                         uint32_t& lo, uint32_t& hi) {
-    const uint32_t s = w & 0x77777777u, s2 = s >> 16, w4 = w << 4;
-    // byte j of a mask is 0xFF when nibble j (of the low / high half-word) has its top bit set
-    const uint32_t m_lo = prmt_dd(w4, w, 0xD9C8u), m_hi = prmt_dd(w4, w, 0xFBEAu);
-    const uint32_t a_lo = prmt_dd(T0, T1, s), b_lo = prmt_dd(T2, T3, s);
-    const uint32_t a_hi = prmt_dd(T0, T1, s2), b_hi = prmt_dd(T2, T3, s2);
-    lo = (a_lo & ~m_lo) | (b_lo & m_lo);
-    hi = (a_hi & ~m_hi) | (b_hi & m_hi);
 }
 
 // The eight sub-block scales ls - 32 of one row as int8: even sub-blocks 0,2,4,6 in ev, odd 1,3,5,7 in od.
@@ -85,11 +95,22 @@ __device__ __forceinline__ void iq4_scales(uint32_t sl, uint32_t sh, uint32_t& e
     od = (to & 0x20202020u) * 6u + to;
 }
 
+// Eight IQ4_XS weights of one quant word (bytes 4t..4t+3 of a sub-block's sixteen: the low nibbles are
+// elements 4t..4t+3, the high nibbles elements 16+4t..16+4t+3) as two int8 MMA A-operand registers:
+// lo = elements (4t, 16+4t, 4t+1, 17+4t), hi = elements (4t+2, 18+4t, 4t+3, 19+4t).
+// tab_c: bytes (lane * 4, -, 0x01, 0x00): with a quant byte in byte 1 it is that byte's table entry for this lane.
+__device__ __forceinline__ void iq4_word(uint32_t w, uint32_t tab_c, uint32_t& lo, uint32_t& hi) {
+    const uint32_t e0 = lds32(prmt_dd(w, tab_c, 0x7604u)), e1 = lds32(prmt_dd(w, tab_c, 0x7614u));
+    const uint32_t e2 = lds32(prmt_dd(w, tab_c, 0x7624u)), e3 = lds32(prmt_dd(w, tab_c, 0x7634u));
+    lo = prmt_dd(e0, e1, 0x5410u);
+    hi = prmt_dd(e2, e3, 0x5410u);
+}
+
 __global__ void __launch_bounds__(dd::kWarps * 32, 1)
 decode_down_kernel(DownDecodeArgs a) {
     extern __shared__ __align__(128) uint8_t smem_raw[];
-    uint8_t* sm = reinterpret_cast<uint8_t*>(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
-    const uint32_t base = smem_addr(sm);
+    const uint32_t win0 = smem_addr(smem_raw);                     // where the dynamic area starts in the shared window
+    const uint32_t base = (win0 + 127u) & ~127u;
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, g = lane >> 2, t = lane & 3u;
     const qkm_dims d = a.d;
     const uint32_t KB = d.n_ff / 256;               // 2
@@ -98,53 +119,61 @@ decode_down_kernel(DownDecodeArgs a) {
     const uint32_t n_slots = d.n_used + 1;
     const bool with_shared = a.sh_tiles != nullptr;
 
-    const uint32_t ring = base + dd::kRings + warp * dd::kRingBytes;
+    if (base + dd::kLowRings + dd::kLowRingWarps * dd::kRingBytes > dd::kTab) {   // layout assumption broken
+        if (tid == 0) atomicExch(a.status, (uint32_t)kStatusBadLayout);
+        return;
+    }
+    auto at = [&](uint32_t window_addr) -> uint8_t* { return smem_raw + (window_addr - win0); };
+    const uint32_t ring = warp < (uint32_t)dd::kLowRingWarps ? base + dd::kLowRings + warp * dd::kRingBytes
+                                                             : dd::kHigh + (warp - dd::kLowRingWarps) * dd::kRingBytes;
     const uint32_t my_bar = base + dd::kBars + warp * dd::kStages * 8;
-    const uint32_t my_dig = base + dd::kDig + warp * 1024;
-    uint8_t* dig = sm + dd::kDig + warp * 1024;
-    float* red = reinterpret_cast<float*>(sm + dd::kRed);
-    int8_t* s_hd = reinterpret_cast<int8_t*>(sm + dd::kHd);
-    float* s_misc = reinterpret_cast<float*>(sm + dd::kMisc);
+    const uint32_t tab_bar = base + dd::kBars + dd::kWarps * dd::kStages * 8;
+    const uint32_t my_dig = dd::kDig + warp * 1024;
+    uint8_t* dig = at(my_dig);
+    float* red = reinterpret_cast<float*>(at(dd::kRed));
+    int8_t* s_hd = reinterpret_cast<int8_t*>(at(base + dd::kHd));
+    float* s_misc = reinterpret_cast<float*>(at(base + dd::kMisc));
     bool timed_out = false;
 
     if (lane == 0) {
         for (int s = 0; s < dd::kStages; ++s) mbar_init(my_bar + 8 * s, 1);
+        if (warp == 0) mbar_init(tab_bar, 1);
         mbar_fence_init();
     }
     __syncthreads();
+    if (tid == 0) {   // the 64 KB table image comes from global memory (L2 after the first block) in four bulk copies
+        mbar_expect_tx(tab_bar, dd::kTabBytes);
+        for (uint32_t i = 0; i < 4; ++i) bulk_g2s(dd::kTab + i * 16384u, a.lut + i * 16384u, 16384u, tab_bar);
+    }
 
-    // Work: the flat list of (token, pair of 16-row tiles) is cut evenly and contiguously over the
-    // blocks; a block walks its range in chunks of up to two pairs of one token, sums once per chunk.
-    const uint32_t PT = RT / 2;                     // tile pairs per token
-    const uint64_t pairs_total = (uint64_t)a.n_tokens * PT;
-    const uint32_t u_lo = (uint32_t)(pairs_total * blockIdx.x / gridDim.x);
-    const uint32_t u_hi = (uint32_t)(pairs_total * (blockIdx.x + 1) / gridDim.x);
+    const uint64_t tiles_total = (uint64_t)a.n_tokens * RT;
+    const uint32_t u_lo = (uint32_t)(tiles_total * blockIdx.x / gridDim.x);
+    const uint32_t u_hi = (uint32_t)(tiles_total * (blockIdx.x + 1) / gridDim.x);
     const size_t mat_tiles = (size_t)KB * RT;
 
     // producer cursor; lane 0 only
-    uint32_t p_u = u_lo, p_tok = u_lo / PT, p_pr = u_lo - p_tok * PT;
+    uint32_t p_u = u_lo, p_tok = u_lo / RT, p_rt = u_lo - p_tok * RT;
     bool p_new_tok = true;
-    const uint8_t* p_src = nullptr;     // next tile pair of expert ids[slot]
+    const uint8_t* p_src = nullptr;     // next tile of expert ids[slot]
     const uint8_t* p_sh = nullptr;      // block column `warp` of the next tile of the shared matrix
     auto issue = [&](uint32_t stage) {
         if (p_u >= u_hi) return;
         if (p_new_tok) {
             p_new_tok = false;
-            const uint32_t e = min(__ldcg(&a.sel[p_tok].ids[slot]), d.n_expert - 1);   // (read before the wait below: L2, not a stale L1 line)
-            p_src = a.tiles + ((size_t)e * mat_tiles + (size_t)kb * RT + 2 * p_pr) * kTileIq4;
-            if (with_shared) p_sh = a.sh_tiles + ((size_t)(warp >> 3) * RT + 2 * p_pr) * kTileQ8 + dd::kShBlock * (warp & 7u);
+            const uint32_t e = min(__ldcg(&a.sel[p_tok].ids[slot]), d.n_expert - 1);
+            p_src = a.tiles + ((size_t)e * mat_tiles + (size_t)kb * RT + p_rt) * kTileIq4;
+            if (with_shared) p_sh = a.sh_tiles + ((size_t)(warp >> 3) * RT + p_rt) * kTileQ8 + dd::kShBlock * (warp & 7u);
         }
         const uint32_t bar = my_bar + 8 * stage, dst = ring + stage * dd::kStageBytes;
-        mbar_expect_tx(bar, 2 * kTileIq4 + (with_shared ? 2 * dd::kShBlock : 0));
-        bulk_g2s(dst, p_src, 2 * kTileIq4, bar);
-        p_src += 2 * kTileIq4;
-        if (with_shared) {   // block column `warp` of the shared matrix (column block warp / 8, block warp % 8), both tiles
-            bulk_g2s(dst + 2 * kTileIq4, p_sh, dd::kShBlock, bar);
-            bulk_g2s(dst + 2 * kTileIq4 + dd::kShBlock, p_sh + kTileQ8, dd::kShBlock, bar);
-            p_sh += 2 * kTileQ8;
+        mbar_expect_tx(bar, kTileIq4 + (with_shared ? dd::kShBlock : 0));
+        bulk_g2s(dst, p_src, kTileIq4, bar);
+        p_src += kTileIq4;
+        if (with_shared) {
+            bulk_g2s(dst + kTileIq4, p_sh, dd::kShBlock, bar);
+            p_sh += kTileQ8;
         }
         ++p_u;
-        if (++p_pr == PT) { p_pr = 0; ++p_tok; p_new_tok = true; }
+        if (++p_rt == RT) { p_rt = 0; ++p_tok; p_new_tok = true; }
     };
     if (lane == 0)
         for (int s = 0; s < dd::kStages; ++s) issue(s);
@@ -153,26 +182,25 @@ decode_down_kernel(DownDecodeArgs a) {
     pdl_wait();
     pdl_trigger();
 
-    // the codebook in four registers (kvalues_iq4nl as int8)
-    const uint32_t T0 = 0xBFAD9881u, T1 = 0xF6EADDCFu, T2 = 0x26190D01u, T3 = 0x71594535u;
     uint32_t cnt = 0, buf = 0;
     float w_s = 0.f, w_sh = 0.f;   // routing weight x plane scale of this warp's slot; w_shared x 2^-p of the shared row's digits
     uint32_t b0[8], b1[8];         // B operand: digit g (g < 4) of the token's h values, in the A operand's element order
     // digit weights: C columns 2t, 2t+1 are digits 2t, 2t+1 (t < 2); the other columns are zero
     const float dw0 = t == 0 ? 1.f : (t == 1 ? 16384.f : 0.f), dw1 = dw0 * 128.f;
+    const uint32_t tab_c = dd::kTab + lane * 4;
 
-    uint32_t tok = u_lo / PT, pr = u_lo - tok * PT;
+    if (!mbar_wait_bounded(tab_bar, 0)) timed_out = true;   // every thread observes the table's arrival itself
+
+    uint32_t tok = u_lo / RT, rt = u_lo - tok * RT;
     bool new_tok = true;
     for (uint32_t u = u_lo; u < u_hi;) {
         if (new_tok) {   // block-uniform
             new_tok = false;
-            // every global load of the switch is issued first, so their round trips overlap
             const float* hs = a.h + ((size_t)tok * n_slots + slot) * d.n_ff + 256 * kb + 8 * lane;
             const float4 v0 = *reinterpret_cast<const float4*>(hs), v1 = *reinterpret_cast<const float4*>(hs + 4);
             const float w_slot = a.sel[tok].w[slot];
             w_sh = a.sel[tok].w_shared;
             const float hv_sh = (with_shared && tid < d.n_ff) ? a.h[((size_t)tok * n_slots + d.n_used) * d.n_ff + tid] : 0.f;
-            // ---- this warp's B operand: h[tok][slot][256 kb .. 256 kb + 256) as digit planes -----------
             {
                 const float hv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
                 float m = 0.f;
@@ -205,7 +233,6 @@ decode_down_kernel(DownDecodeArgs a) {
                 w_s = w_slot * (any_bad ? __int_as_float(0x7FC00000) : ldexpf(1.0f, -p));
             }
             if (with_shared) {
-                // h[t][n_used] as four int8 digit planes in shared memory, one power-of-two scale
                 const float hv = hv_sh;
                 float m = fabsf(hv);
                 const bool bad = !(m <= 3.0e38f);
@@ -229,7 +256,7 @@ decode_down_kernel(DownDecodeArgs a) {
                 __syncthreads();
             }
         }
-        const uint32_t n_c = min(2u, min(u_hi - u, PT - pr));   // steps (tile pairs) of this chunk
+        const uint32_t n_c = min((uint32_t)dd::kChunk, min(u_hi - u, RT - rt));   // tiles of this chunk
         uint32_t hb0 = 0, hb1 = 0;   // the shared expert's B operand: digit g of block column `warp`
         if (with_shared && g < 4) {
             const int8_t* hp = s_hd + g * dd::kMaxFf + 32 * warp;
@@ -240,85 +267,66 @@ decode_down_kernel(DownDecodeArgs a) {
         for (uint32_t i = 0; i < n_c; ++i, ++cnt) {
             const uint32_t stage = cnt % dd::kStages, parity = (cnt / dd::kStages) & 1u;
             if (!mbar_wait_bounded(my_bar + 8 * stage, parity)) timed_out = true;
-            const uint32_t tb = ring + stage * dd::kStageBytes, qb = tb + 2 * kTileIq4;
-            // headers of both tiles: row g (d | scales_h << 16, scales_l), row g+8
-            const uint4 hdA = lds128(tb + 16 * g), hdB = lds128(tb + kTileIq4 + 16 * g);
-            uint32_t eaA, oaA, ebA, obA, eaB, oaB, ebB, obB;   // ls - 32 of the even / odd sub-blocks, rows g and g+8
-            iq4_scales(hdA.y, hdA.x >> 16, eaA, oaA);
-            iq4_scales(hdA.w, hdA.z >> 16, ebA, obA);
-            iq4_scales(hdB.y, hdB.x >> 16, eaB, oaB);
-            iq4_scales(hdB.w, hdB.z >> 16, ebB, obB);
-            int accA[4] = {0, 0, 0, 0}, accB[4] = {0, 0, 0, 0};
+            const uint32_t tb = ring + stage * dd::kStageBytes, qb = tb + kTileIq4;
+            // headers: row g (x: d | scales_h << 16, y: scales_l), row g+8 (z, w)
+            const uint4 hd = lds128(tb + 16 * g);
+            uint32_t ea, oa, eb, ob;   // ls - 32 of the even / odd sub-blocks, rows g and g+8
+            iq4_scales(hd.y, hd.x >> 16, ea, oa);
+            iq4_scales(hd.w, hd.z >> 16, eb, ob);
+            int acc[4] = {0, 0, 0, 0};
 #pragma unroll
             for (int hf = 0; hf < 2; ++hf) {
-                // quant word t of sub-blocks 4hf..4hf+3: rows g and g+8 of tile A, then of tile B
+                // quant word t of sub-blocks 4hf..4hf+3: rows g and g+8
                 const uint4 qa4 = lds128(tb + 128 + (hf * 32 + lane) * 16), qb4 = lds128(tb + 128 + ((2 + hf) * 32 + lane) * 16);
-                const uint4 qc4 = lds128(tb + kTileIq4 + 128 + (hf * 32 + lane) * 16), qd4 = lds128(tb + kTileIq4 + 128 + ((2 + hf) * 32 + lane) * 16);
                 const uint32_t wa[4] = {qa4.x, qa4.y, qa4.z, qa4.w}, wb[4] = {qb4.x, qb4.y, qb4.z, qb4.w};
-                const uint32_t wc[4] = {qc4.x, qc4.y, qc4.z, qc4.w}, wd[4] = {qd4.x, qd4.y, qd4.z, qd4.w};
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
                     const int sb = 4 * hf + j;
-                    uint32_t a0, a1, a2, a3, e0, e1, e2, e3;
-                    iq4_word(wa[j], T0, T1, T2, T3, a0, a2);
-                    iq4_word(wb[j], T0, T1, T2, T3, a1, a3);
-                    iq4_word(wc[j], T0, T1, T2, T3, e0, e2);
-                    iq4_word(wd[j], T0, T1, T2, T3, e1, e3);
-                    int cA[4] = {0, 0, 0, 0}, cB[4] = {0, 0, 0, 0};
-                    mma_s8(cA, a0, a1, a2, a3, b0[sb], b1[sb]);
-                    mma_s8(cB, e0, e1, e2, e3, b0[sb], b1[sb]);
-                    // byte (sb / 2) of the even or odd word, sign-extended
-                    const uint32_t sel = 0x8880u + (uint32_t)(sb >> 1) * 0x1111u;
-                    const int laA = (int)prmt_dd((sb & 1) ? oaA : eaA, 0u, sel), lbA = (int)prmt_dd((sb & 1) ? obA : ebA, 0u, sel);
-                    const int laB = (int)prmt_dd((sb & 1) ? oaB : eaB, 0u, sel), lbB = (int)prmt_dd((sb & 1) ? obB : ebB, 0u, sel);
-                    accA[0] += laA * cA[0]; accA[1] += laA * cA[1]; accA[2] += lbA * cA[2]; accA[3] += lbA * cA[3];
-                    accB[0] += laB * cB[0]; accB[1] += laB * cB[1]; accB[2] += lbB * cB[2]; accB[3] += lbB * cB[3];
+                    uint32_t a0, a1, a2, a3;
+                    iq4_word(wa[j], tab_c, a0, a2);
+                    iq4_word(wb[j], tab_c, a1, a3);
+                    int c[4] = {0, 0, 0, 0};
+                    mma_s8(c, a0, a1, a2, a3, b0[sb], b1[sb]);
+                    const uint32_t sel = 0x8880u + (uint32_t)(sb >> 1) * 0x1111u;   // byte sb / 2, sign-extended
+                    const int la = (int)prmt_dd((sb & 1) ? oa : ea, 0u, sel), lb = (int)prmt_dd((sb & 1) ? ob : eb, 0u, sel);
+                    acc[0] += la * c[0]; acc[1] += la * c[1]; acc[2] += lb * c[2]; acc[3] += lb * c[3];
                 }
             }
-            float vaA = w_s * (f16_bits_to_f32(hdA.x & 0xFFFFu) * ((float)accA[0] * dw0 + (float)accA[1] * dw1));
-            float vbA = w_s * (f16_bits_to_f32(hdA.z & 0xFFFFu) * ((float)accA[2] * dw0 + (float)accA[3] * dw1));
-            float vaB = w_s * (f16_bits_to_f32(hdB.x & 0xFFFFu) * ((float)accB[0] * dw0 + (float)accB[1] * dw1));
-            float vbB = w_s * (f16_bits_to_f32(hdB.z & 0xFFFFu) * ((float)accB[2] * dw0 + (float)accB[3] * dw1));
-            // shared expert: one Q8_0 block (32 columns) of each tile's 16 rows against the digit planes
+            float va = w_s * (f16_bits_to_f32(hd.x & 0xFFFFu) * ((float)acc[0] * dw0 + (float)acc[1] * dw1));
+            float vb = w_s * (f16_bits_to_f32(hd.z & 0xFFFFu) * ((float)acc[2] * dw0 + (float)acc[3] * dw1));
             if (with_shared) {
-#pragma unroll
-                for (int k = 0; k < 2; ++k) {
-                    const uint32_t pb = qb + dd::kShBlock * k;
-                    const uint2 qa = lds64(pb + 32 + lane * 8);            // row g: qs[4t..4t+3], qs[16+4t..16+4t+3]
-                    const uint2 qc = lds64(pb + 32 + 256 + lane * 8);      // row g+8
-                    int c[4] = {0, 0, 0, 0};
-                    mma_s8(c, qa.x, qc.x, qa.y, qc.y, hb0, hb1);
-                    const uint32_t dw = lds32(pb + 2 * (g & ~1u)), dw8 = lds32(pb + 2 * (8 + (g & ~1u)));
-                    const float sda = f16_bits_to_f32((dw >> (16 * (g & 1u))) & 0xFFFFu);
-                    const float sdb = f16_bits_to_f32((dw8 >> (16 * (g & 1u))) & 0xFFFFu);
-                    const float sa = w_sh * (sda * ((float)c[0] * dw0 + (float)c[1] * dw1));
-                    const float sb_ = w_sh * (sdb * ((float)c[2] * dw0 + (float)c[3] * dw1));
-                    if (k == 0) { vaA += sa; vbA += sb_; } else { vaB += sa; vbB += sb_; }
-                }
+                const uint2 qa = lds64(qb + 32 + lane * 8);            // row g: qs[4t..4t+3], qs[16+4t..16+4t+3]
+                const uint2 qc = lds64(qb + 32 + 256 + lane * 8);      // row g+8
+                int c[4] = {0, 0, 0, 0};
+                mma_s8(c, qa.x, qc.x, qa.y, qc.y, hb0, hb1);
+                const uint32_t dw = lds32(qb + 2 * (g & ~1u)), dw8 = lds32(qb + 2 * (8 + (g & ~1u)));
+                const float sda = f16_bits_to_f32((dw >> (16 * (g & 1u))) & 0xFFFFu);
+                const float sdb = f16_bits_to_f32((dw8 >> (16 * (g & 1u))) & 0xFFFFu);
+                va += w_sh * (sda * ((float)c[0] * dw0 + (float)c[1] * dw1));
+                vb += w_sh * (sdb * ((float)c[2] * dw0 + (float)c[3] * dw1));
             }
             __syncwarp();
             if (lane == 0) issue(stage);
             // digits 0, 1 sit in lane t = 0 and 2, 3 in t = 1
-            vaA += __shfl_xor_sync(0xFFFFFFFFu, vaA, 1); vbA += __shfl_xor_sync(0xFFFFFFFFu, vbA, 1);
-            vaB += __shfl_xor_sync(0xFFFFFFFFu, vaB, 1); vbB += __shfl_xor_sync(0xFFFFFFFFu, vbB, 1);
+            va += __shfl_xor_sync(0xFFFFFFFFu, va, 1); vb += __shfl_xor_sync(0xFFFFFFFFu, vb, 1);
             if (t == 0) {
-                float* r = red + ((buf * dd::kWarps + warp) * dd::kChunk + 2 * i) * 16;
-                r[g] = vaA; r[g + 8] = vbA; r[16 + g] = vaB; r[24 + g] = vbB;
+                float* r = red + ((buf * dd::kWarps + warp) * dd::kChunk + i) * 16;
+                r[g] = va; r[g + 8] = vb;
             }
         }
         __syncthreads();
-        if (tid < 32 * n_c) {
+        if (tid < 16 * n_c) {
             const uint32_t i = tid >> 4, r = tid & 15u;   // tile i of the chunk
             float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < dd::kWarps; ++w)   // slot order, column blocks inside a slot
                 sum += red[((buf * dd::kWarps + w) * dd::kChunk + i) * 16 + r];
-            a.y[(size_t)tok * d.n_embd + (2 * pr + i) * 16 + r] = sum;
+            a.y[(size_t)tok * d.n_embd + (rt + i) * 16 + r] = sum;
         }
         buf ^= 1u;
         u += n_c;
-        pr += n_c;
-        if (pr == PT) { pr = 0; ++tok; new_tok = true; }
+        rt += n_c;
+        if (rt == RT) { rt = 0; ++tok; new_tok = true; }
     }
     if (timed_out && lane == 0) atomicExch(a.status, (uint32_t)kStatusWaitTimeout);
 }
@@ -328,9 +336,9 @@ bool decode_down_ok(const qkm_dims& d) {
 }
 
 cudaError_t launch_decode_down(const Launch& L, const DownDecodeArgs& a, uint32_t n_blocks) {
-    if (!decode_down_ok(a.d)) return cudaErrorInvalidValue;
+    if (!decode_down_ok(a.d) || !a.lut) return cudaErrorInvalidValue;
     if (a.n_tokens == 0) return cudaSuccess;
-    const size_t smem = dd::kEnd + 128;
+    const size_t smem = dd::kEnd;   // the dynamic area must reach from wherever it starts to the end of the scratch
     cudaError_t e = cudaFuncSetAttribute(decode_down_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
     e = launch_kernel(L, decode_down_kernel, dim3(n_blocks), dim3(dd::kWarps * 32), smem, a);

@@ -105,6 +105,7 @@ cudaError_t launch_decode_gateup(const Launch& L, const GateupDecodeArgs& a, uin
 struct DownDecodeArgs {
     const uint8_t* tiles;           // routed experts, IQ4_XS tiles
     const uint8_t* sh_tiles;        // shared expert, Q8_0 tiles (NULL: no shared term)
+    const uint8_t* lut;             // IQ4_XS form: decode_down_lut_bytes() bytes written by launch_decode_down_lut
     const float* h;                 // [T][n_used+1][n_ff] f32 (encoded as int8 digit planes inside the kernel)
     const qkm_sel* sel;
     float* y;
@@ -113,6 +114,8 @@ struct DownDecodeArgs {
     qkm_dims d;
 };
 bool decode_down_ok(const qkm_dims& d);
+size_t decode_down_lut_bytes();
+cudaError_t launch_decode_down_lut(const Launch& L, uint8_t* lut);
 cudaError_t launch_decode_down(const Launch& L, const DownDecodeArgs& a, uint32_t n_blocks);
 // the same with the routed experts as Q6_K tiles
 cudaError_t launch_decode_down_q6k(const Launch& L, const DownDecodeArgs& a, uint32_t n_blocks);
