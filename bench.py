@@ -390,30 +390,33 @@ def run_ours(args, pkg, syn):
     del x_dev, y_dev
     torch.cuda.empty_cache()
 
-    # ---- the Q6_K-down variant of the layer (some layers of the real model carry it): streamed
-    # router / shared / gate-up kernels, f32 down kernel.  Four rotating layers, same 16 slots.
+    # ---- the other type mixes the reference loads (src/main.cpp:1283-1291): a Q6_K down tensor, IQ4_XS
+    # gate/up tensors.  Same three-kernel decode sequence on their own tile layouts.  Four rotating
+    # layers, same 16 slots.
     if not args.no_sub and world == 1:
         QL = 4
-        cq = pkg.Context(dims, n_layer=QL, max_tokens=S, device=R.local_rank)
-        sq = torch.cuda.Stream(dev)
-        cq.set_stream(sq.cuda_stream)
-        q_layers = [syn.make_layer(dims, SEED_W, 100 + l, syn.F16, syn.IQ3_XXS, syn.Q6_K) for l in range(QL)]
-        for l, ly in enumerate(q_layers):
-            cq.upload_layer(l, ly)
-        with torch.cuda.stream(sq):
-            xq = torch.from_numpy(x_all[:QL].copy()).to(dev)
-            yq = torch.empty_like(xq)
-        cq.moe_decode_stack(0, QL, xq, S, yq); R.barrier()
-        refq = orc.moe_layer(q_layers[0], x_all[0], threads=orc.hardware_threads())
-        errq = syn.rel_err_rows(yq[0].cpu().numpy(), refq["y"])
-        assert errq < 1e-5, f"Q6_K-down layer output error {errq}"
-        msq = timed(torch, R, sq, lambda: cq.moe_decode_stack(0, QL, xq, S, yq), args.steps, 3) / QL
-        line["decode_q6k_down"] = {"us_per_layer": msq * 1e3, "tok_s_through_40_layers": S / (msq * 40e-3),
-                                   "rel_err_vs_oracle": errq, "layers_rotated": QL,
-                                   "note": "working set 4 x 0.45 GB > L2; down projection on the f32 kernel (no tile layout yet)"}
-        cq.close()
-        del xq, yq
-        torch.cuda.empty_cache()
+        for key, gt, dt, what in (("decode_q6k_down", syn.IQ3_XXS, syn.Q6_K, "Q6_K down tensors (decode_down_q6k_kernel)"),
+                                  ("decode_iq4_gateup", syn.IQ4_XS, syn.IQ4_XS, "IQ4_XS gate/up tensors (decode_gateup_kernel<IQ4_XS>)")):
+            cq = pkg.Context(dims, n_layer=QL, max_tokens=S, device=R.local_rank)
+            sq = torch.cuda.Stream(dev)
+            cq.set_stream(sq.cuda_stream)
+            q_layers = [syn.make_layer(dims, SEED_W, 100 + l, syn.F16, gt, dt) for l in range(QL)]
+            for l, ly in enumerate(q_layers):
+                cq.upload_layer(l, ly)
+            with torch.cuda.stream(sq):
+                xq = torch.from_numpy(x_all[:QL].copy()).to(dev)
+                yq = torch.empty_like(xq)
+            cq.moe_decode_stack(0, QL, xq, S, yq); R.barrier()
+            refq = orc.moe_layer(q_layers[0], x_all[0], threads=orc.hardware_threads())
+            errq = syn.rel_err_rows(yq[0].cpu().numpy(), refq["y"])
+            assert errq < 1e-5, f"{key}: layer output error {errq}"
+            msq = timed(torch, R, sq, lambda: cq.moe_decode_stack(0, QL, xq, S, yq), args.steps, 3) / QL
+            line[key] = {"us_per_layer": msq * 1e3, "tok_s_through_40_layers": S / (msq * 40e-3),
+                         "rel_err_vs_oracle": errq, "layers_rotated": QL,
+                         "note": f"working set {QL} layers x 0.4-0.5 GB > L2; {what}"}
+            cq.close()
+            del xq, yq, cq
+            torch.cuda.empty_cache()
 
     # ---- the other configurations, as sub-objects of the same line
     if not args.no_sub:
