@@ -110,10 +110,27 @@ struct qkm_ctx {
     // the shared expert's kernels run on a side stream, beside the routing/grouping kernels
     cudaStream_t side = nullptr;
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr, ev_planes = nullptr;
-    // the decode stack as a CUDA graph: captured on first use for a given argument set
-    cudaGraphExec_t stack_graph = nullptr;
-    struct { uint32_t first, count, n; const float* x; float* y; cudaStream_t stream; } stack_key{};
-    uint64_t stack_graph_launches = 0;
+    // the decode stack as CUDA graphs: captured on first use of an argument set, a few sets kept
+    // (the host-buffer form runs the stack in chunks of layers, each its own graph)
+    static constexpr int kStackGraphs = 8;
+    struct StackGraph {
+        cudaGraphExec_t exec = nullptr;
+        uint32_t first = 0, count = 0, n = 0;
+        const float* x = nullptr;
+        float* y = nullptr;
+        cudaStream_t stream = nullptr;
+        uint64_t launches = 0;       // kernels one replay launches
+        uint32_t plan_after = 0;     // shared_plan_n once the sequence has run
+        uint64_t used = 0;           // for least-recently-used replacement
+    } stack_graphs[kStackGraphs];
+    uint64_t stack_clock = 0;
+    // the host-buffer form of the stack copies chunk k+1 in and chunk k-1 out while chunk k computes
+    static constexpr int kStackChunks = 4;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;
+    cudaEvent_t ev_in[kStackChunks] = {}, ev_out[kStackChunks] = {}, ev_copies = nullptr;
+    void drop_stack_graphs() {
+        for (auto& g : stack_graphs) if (g.exec) { cudaGraphExecDestroy(g.exec); g.exec = nullptr; }
+    }
     // per-stage profiling of the fused calls
     static constexpr int kMaxStages = 16;
     bool profiling = false;
@@ -361,7 +378,12 @@ extern "C" QKM_API void qkm_close(qkm_ctx* c) {
     for (void* p : {(void*)c->pm_xrecv, (void*)c->pm_selrecv, (void*)c->pm_back, (void*)c->pm_partial, (void*)c->pm_xscale}) if (p) cudaFree(p);
     if (c->status_host) cudaFreeHost(c->status_host);
     if (c->ep_counts_host) cudaFreeHost(c->ep_counts_host);
-    if (c->stack_graph) cudaGraphExecDestroy(c->stack_graph);
+    c->drop_stack_graphs();
+    for (cudaEvent_t ev : c->ev_in) if (ev) cudaEventDestroy(ev);
+    for (cudaEvent_t ev : c->ev_out) if (ev) cudaEventDestroy(ev);
+    if (c->ev_copies) cudaEventDestroy(c->ev_copies);
+    if (c->copy_in) cudaStreamDestroy(c->copy_in);
+    if (c->copy_out) cudaStreamDestroy(c->copy_out);
     if (c->ev_fork) cudaEventDestroy(c->ev_fork);
     if (c->ev_join) cudaEventDestroy(c->ev_join);
     if (c->ev_planes) cudaEventDestroy(c->ev_planes);
@@ -453,7 +475,7 @@ extern "C" QKM_API int qkm_upload_layer(qkm_ctx* c, uint32_t layer, const qkm_la
                           w->gate_shexp, w->up_shexp, w->down_shexp};
     for (const void* p : src) if (!p) return fail(c, QKM_ERR_ARG, "layer %u: NULL tensor pointer", layer);
     QKM_CUDA(c, cudaSetDevice(c->device));
-    if (c->stack_graph) { cudaGraphExecDestroy(c->stack_graph); c->stack_graph = nullptr; }
+    c->drop_stack_graphs();
     qkm_layer_dev& l = c->layers[layer];
     for (int i = 0; i < 8; ++i) {
         const size_t bytes = tensor_bytes(c, i, *w);
@@ -854,13 +876,18 @@ extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t
     for (uint32_t l = 0; l < count; ++l)
         if (int rc = layer_ready(c, first + l)) return rc;
     if (c->stream == nullptr || c->profiling || count < 2) return decode_stack_eager(c, first, count, x, n, y);
-    auto& k = c->stack_key;
-    // (a stale shared-expert work list - another kind of call ran in between - also forces a new
-    // capture: the graph then contains the launch that cuts the list again)
-    const bool same = c->stack_graph && k.first == first && k.count == count && k.n == n && k.x == x && k.y == y &&
-                      k.stream == c->stream && c->shared_plan_n == n;
-    if (!same) {
-        if (c->stack_graph) { cudaGraphExecDestroy(c->stack_graph); c->stack_graph = nullptr; }
+    // A captured sequence always cuts the shared expert's work lists itself (shared_plan_n is cleared
+    // before the capture), so a replay never depends on what ran in between.
+    qkm_ctx::StackGraph* g = nullptr;
+    for (auto& e : c->stack_graphs)
+        if (e.exec && e.first == first && e.count == count && e.n == n && e.x == x && e.y == y && e.stream == c->stream) g = &e;
+    if (!g) {
+        qkm_ctx::StackGraph* slot = &c->stack_graphs[0];
+        for (auto& e : c->stack_graphs) {
+            if (!e.exec) { slot = &e; break; }
+            if (e.used < slot->used) slot = &e;
+        }
+        if (slot->exec) { cudaGraphExecDestroy(slot->exec); slot->exec = nullptr; }
         c->shared_plan_n = 0;   // the captured sequence must cut the list itself
         const uint64_t before = c->launches;
         if (cudaStreamBeginCapture(c->stream, cudaStreamCaptureModeThreadLocal) != cudaSuccess) {
@@ -870,26 +897,29 @@ extern "C" QKM_API int qkm_moe_decode_stack(qkm_ctx* c, uint32_t first, uint32_t
         const int rc = decode_stack_eager(c, first, count, x, n, y);
         cudaGraph_t graph = nullptr;
         const cudaError_t e = cudaStreamEndCapture(c->stream, &graph);
-        c->stack_graph_launches = c->launches - before;
+        slot->launches = c->launches - before;
+        slot->plan_after = c->shared_plan_n;
         c->launches = before;
+        c->shared_plan_n = 0;   // nothing captured has run
         if (rc != QKM_OK || e != cudaSuccess || !graph) {
             if (graph) cudaGraphDestroy(graph);
             cudaGetLastError();
-            c->shared_plan_n = 0;   // nothing captured has run
             return rc != QKM_OK ? rc : decode_stack_eager(c, first, count, x, n, y);
         }
-        const cudaError_t ei = cudaGraphInstantiate(&c->stack_graph, graph, 0);
+        const cudaError_t ei = cudaGraphInstantiate(&slot->exec, graph, 0);
         cudaGraphDestroy(graph);
         if (ei != cudaSuccess) {
-            c->stack_graph = nullptr;
+            slot->exec = nullptr;
             cudaGetLastError();
-            c->shared_plan_n = 0;
             return decode_stack_eager(c, first, count, x, n, y);
         }
-        k.first = first; k.count = count; k.n = n; k.x = x; k.y = y; k.stream = c->stream;
+        slot->first = first; slot->count = count; slot->n = n; slot->x = x; slot->y = y; slot->stream = c->stream;
+        g = slot;
     }
-    QKM_CUDA(c, cudaGraphLaunch(c->stack_graph, c->stream));
-    c->launches += c->stack_graph_launches;
+    g->used = ++c->stack_clock;
+    QKM_CUDA(c, cudaGraphLaunch(g->exec, c->stream));
+    c->launches += g->launches;
+    c->shared_plan_n = g->plan_after;
     return QKM_OK;
 }
 
@@ -903,10 +933,45 @@ extern "C" QKM_API int qkm_moe_decode_stack_host(qkm_ctx* c, uint32_t first, uin
         QKM_CUDA(c, cudaMalloc((void**)&c->stack_x, cap));
         QKM_CUDA(c, cudaMalloc((void**)&c->stack_y, cap));
     }
-    const size_t bytes = (size_t)count * n * c->cfg.dims.n_embd * sizeof(float);
-    QKM_CUDA(c, cudaMemcpyAsync(c->stack_x, x_host, bytes, cudaMemcpyHostToDevice, c->stream));
-    if (int rc = qkm_moe_decode_stack(c, first, count, c->stack_x, n, c->stack_y)) return rc;
-    QKM_CUDA(c, cudaMemcpyAsync(y_host, c->stack_y, bytes, cudaMemcpyDeviceToHost, c->stream));
+    const size_t layer_elems = (size_t)n * c->cfg.dims.n_embd;
+    const size_t bytes = (size_t)count * layer_elems * sizeof(float);
+    if (c->stream == nullptr || c->profiling || count < 2u * qkm_ctx::kStackChunks) {
+        QKM_CUDA(c, cudaMemcpyAsync(c->stack_x, x_host, bytes, cudaMemcpyHostToDevice, c->stream));
+        if (int rc = qkm_moe_decode_stack(c, first, count, c->stack_x, n, c->stack_y)) return rc;
+        QKM_CUDA(c, cudaMemcpyAsync(y_host, c->stack_y, bytes, cudaMemcpyDeviceToHost, c->stream));
+        return check_status(c);
+    }
+    // Chunks of layers: all input copies are queued on their own stream at once, chunk k computes as soon
+    // as its rows are there, and its outputs leave on a third stream while chunk k+1 computes.  Only the
+    // first chunk's copy in and the last chunk's copy out are not hidden.
+    if (!c->copy_in) {
+        QKM_CUDA(c, cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
+        QKM_CUDA(c, cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
+        for (cudaEvent_t& ev : c->ev_in) QKM_CUDA(c, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        for (cudaEvent_t& ev : c->ev_out) QKM_CUDA(c, cudaEventCreateWithFlags(&ev, cudaEventDisableTiming));
+        QKM_CUDA(c, cudaEventCreateWithFlags(&c->ev_copies, cudaEventDisableTiming));
+    }
+    constexpr uint32_t K = qkm_ctx::kStackChunks;
+    uint32_t lo[K + 1];
+    for (uint32_t k = 0; k <= K; ++k) lo[k] = (uint32_t)((uint64_t)count * k / K);
+    // whatever the stream still holds (it reads or writes the staging buffers) comes first
+    QKM_CUDA(c, cudaEventRecord(c->ev_copies, c->stream));
+    QKM_CUDA(c, cudaStreamWaitEvent(c->copy_in, c->ev_copies, 0));
+    for (uint32_t k = 0; k < K; ++k) {
+        const size_t off = lo[k] * layer_elems, len = (size_t)(lo[k + 1] - lo[k]) * layer_elems * sizeof(float);
+        QKM_CUDA(c, cudaMemcpyAsync(c->stack_x + off, x_host + off, len, cudaMemcpyHostToDevice, c->copy_in));
+        QKM_CUDA(c, cudaEventRecord(c->ev_in[k], c->copy_in));
+    }
+    for (uint32_t k = 0; k < K; ++k) {
+        const size_t off = lo[k] * layer_elems, len = (size_t)(lo[k + 1] - lo[k]) * layer_elems * sizeof(float);
+        QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_in[k], 0));
+        if (int rc = qkm_moe_decode_stack(c, first + lo[k], lo[k + 1] - lo[k], c->stack_x + off, n, c->stack_y + off)) return rc;
+        QKM_CUDA(c, cudaEventRecord(c->ev_out[k], c->stream));
+        QKM_CUDA(c, cudaStreamWaitEvent(c->copy_out, c->ev_out[k], 0));
+        QKM_CUDA(c, cudaMemcpyAsync(y_host + off, c->stack_y + off, len, cudaMemcpyDeviceToHost, c->copy_out));
+    }
+    QKM_CUDA(c, cudaEventRecord(c->ev_copies, c->copy_out));
+    QKM_CUDA(c, cudaStreamWaitEvent(c->stream, c->ev_copies, 0));   // the stream's synchronise below covers the copies
     return check_status(c);
 }
 

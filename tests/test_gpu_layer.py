@@ -198,6 +198,43 @@ def test_decode_stack_and_errors(pkg, orc, syn):
         assert ctx.launch_count() > 0
 
 
+def test_decode_stack_host_buffers_in_chunks(pkg, orc, syn):
+    """The host-buffer form of the stack (copies inside): nine layers run as chunks of layers, each
+    its own graph, with the copies on their own streams; three layers take the plain form.  Both equal
+    the layer-by-layer calls bit for bit, on a repeated call (graphs replayed) and after a call with
+    another token count and with device buffers in between (more argument sets than one graph)."""
+    import torch
+    dims = syn.Dims(n_embd=512, n_ff=256, n_expert=16, n_used=4)
+    T, L = 5, 9
+    layers = [syn.make_layer(dims, seed=52, layer=l) for l in range(L)]
+    x = np.stack([syn.random_x(T, dims.n_embd, seed=80 + l) for l in range(L)])
+    with pkg.Context(dims, n_layer=L, max_tokens=T, device=0) as ctx:
+        for l in range(L):
+            ctx.upload_layer(l, layers[l])
+        want = np.stack([ctx.moe_forward_host(l, x[l], mode=0) for l in range(L)])
+        stream = torch.cuda.Stream(torch.device("cuda", 0))
+        ctx.set_stream(stream.cuda_stream)
+        y = np.zeros_like(x)
+        for _ in range(3):
+            y[:] = 0
+            ctx.moe_decode_stack_host(0, L, x.ctypes.data, T, y.ctypes.data)
+            assert np.array_equal(y, want)
+        x3 = np.ascontiguousarray(x[:, :3])
+        y3 = np.zeros_like(x3)
+        ctx.moe_decode_stack_host(0, L, x3.ctypes.data, 3, y3.ctypes.data)
+        assert max(syn.rel_err_rows(y3[l], want[l, :3]) for l in range(L)) < 1e-6   # (another batch: not held to the same bits)
+        d_x, d_y = ctx.to_device(x), ctx.alloc(x.nbytes)
+        ctx.moe_decode_stack(0, L, d_x, T, d_y)
+        assert np.array_equal(d_y.download(np.float32, x.shape), want)
+        y[:] = 0
+        ctx.moe_decode_stack_host(0, L, x.ctypes.data, T, y.ctypes.data)
+        assert np.array_equal(y, want)
+        y2 = np.zeros_like(x[:3])
+        ctx.moe_decode_stack_host(2, 3, x[2:5].ctypes.data, T, y2.ctypes.data)   # fewer layers than chunks: one copy each way
+        assert np.array_equal(y2, want[2:5])
+        ctx.set_stream(0)
+
+
 def test_expert_parallel_view_partial_sums(pkg, orc, syn):
     """A context that holds experts [4,8) only returns that shard's partial sum."""
     dims = syn.Dims(n_embd=512, n_ff=256, n_expert=8, n_used=3)
