@@ -234,8 +234,11 @@ QKM_API int qkm_moe_forward_host(qkm_ctx *c, uint32_t layer, int mode, const flo
  * per-layer input rows x[l] (device [n_layer][T][n_embd]); y likewise. */
 QKM_API int qkm_moe_decode_stack(qkm_ctx *c, uint32_t layer_first, uint32_t layer_count,
                                  const float *x, uint32_t n_tokens, float *y);
-/* The same with HOST buffers [layer_count][T][n_embd]: one copy in, the stack, one
- * copy out, then a stream synchronise.  Pinned host memory makes the copies async. */
+/* The same with HOST buffers [layer_count][T][n_embd], then a stream synchronise.  From eight
+ * layers on (and on a stream of the caller's) the stack runs in four chunks of layers: all input
+ * copies are queued at once on a copy stream, a chunk starts when its rows have arrived and its
+ * outputs leave on a third stream while the next chunk computes.  Pinned host memory makes the
+ * copies asynchronous. */
 QKM_API int qkm_moe_decode_stack_host(qkm_ctx *c, uint32_t layer_first, uint32_t layer_count,
                                       const float *x_host, uint32_t n_tokens, float *y_host);
 /* Per-stage device timing of the fused calls (the reference's QK_STEP_PROF,
