@@ -4,7 +4,8 @@ kernel waits on another, so running the ranks one after the other is safe on one
 
 Tolerance: the expert GEMMs run on the tensor cores (bf16/f16 operands), so outputs are held
 to the prefill tolerance 2e-2 (row-scaled) against the f64 oracle; ids, send order and split
-sizes are exact.  Shapes without tiles take the f32 kernels and are held to 1e-5."""
+sizes are exact.  Shapes and type mixes outside the shard's tensor-core path take the f32 kernels and are
+held to 1e-5."""
 import numpy as np
 import pytest
 
@@ -115,7 +116,8 @@ def test_ep_rank_without_tokens(pkg, orc, syn):
 
 
 def test_ep_generic_kernels_f32(pkg, orc, syn):
-    """Q6_K down has no tile layout: the f32 kernels serve the shard, 1e-5 applies."""
+    """A shard's tensor-core path is wired for IQ3_XXS gate/up + IQ4_XS down tiles; a layer with a Q6_K
+    down tensor is served by the f32 kernels, and 1e-5 applies."""
     dims = syn.Dims(n_embd=512, n_ff=256, n_expert=8, n_used=2)
     layer = syn.make_layer(dims, seed=44, down_type=syn.Q6_K)
     x = syn.random_x(10, dims.n_embd, seed=63)
