@@ -235,7 +235,8 @@ QKM_API int qkm_moe_forward_host(qkm_ctx *c, uint32_t layer, int mode, const flo
 QKM_API int qkm_moe_decode_stack(qkm_ctx *c, uint32_t layer_first, uint32_t layer_count,
                                  const float *x, uint32_t n_tokens, float *y);
 /* The same with HOST buffers [layer_count][T][n_embd], then a stream synchronise.  From eight
- * layers on (and on a stream of the caller's) the stack runs in four chunks of layers: all input
+ * layers on (and on a stream of the caller's) the stack runs in four chunks of layers (two layers,
+ * two halves of the rest, two layers): all input
  * copies are queued at once on a copy stream, a chunk starts when its rows have arrived and its
  * outputs leave on a third stream while the next chunk computes.  Pinned host memory makes the
  * copies asynchronous. */

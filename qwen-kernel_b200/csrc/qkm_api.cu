@@ -943,7 +943,7 @@ extern "C" QKM_API int qkm_moe_decode_stack_host(qkm_ctx* c, uint32_t first, uin
     }
     // Chunks of layers: all input copies are queued on their own stream at once, chunk k computes as soon
     // as its rows are there, and its outputs leave on a third stream while chunk k+1 computes.  Only the
-    // first chunk's copy in and the last chunk's copy out are not hidden.
+    // first chunk's copy in and the last chunk's copy out are not hidden, so these two chunks are short.
     if (!c->copy_in) {
         QKM_CUDA(c, cudaStreamCreateWithFlags(&c->copy_in, cudaStreamNonBlocking));
         QKM_CUDA(c, cudaStreamCreateWithFlags(&c->copy_out, cudaStreamNonBlocking));
@@ -952,8 +952,9 @@ extern "C" QKM_API int qkm_moe_decode_stack_host(qkm_ctx* c, uint32_t first, uin
         QKM_CUDA(c, cudaEventCreateWithFlags(&c->ev_copies, cudaEventDisableTiming));
     }
     constexpr uint32_t K = qkm_ctx::kStackChunks;
-    uint32_t lo[K + 1];
-    for (uint32_t k = 0; k <= K; ++k) lo[k] = (uint32_t)((uint64_t)count * k / K);
+    // two layers first and two last (what is not hidden is their copy in and copy out), the rest in halves
+    static_assert(K == 4, "chunk boundaries below are written for four chunks");
+    const uint32_t lo[K + 1] = {0u, 2u, 2u + (count - 4u) / 2u, count - 2u, count};
     // whatever the stream still holds (it reads or writes the staging buffers) comes first
     QKM_CUDA(c, cudaEventRecord(c->ev_copies, c->stream));
     QKM_CUDA(c, cudaStreamWaitEvent(c->copy_in, c->ev_copies, 0));
