@@ -45,7 +45,6 @@ constexpr int kBlock = kThreads + 32;
 constexpr int kStages = 2;
 constexpr int kNT = 128;                       // pairs per block (N tile)
 constexpr int kTileBytes = 128 * 128;          // 128 rows x 64 bf16
-constexpr int kGridReplicas = 8;
 }  // namespace pf
 
 // ---- x -> f16 rows, each scaled by a power of two so that max|x| lands in [2^13, 2^14) -----------
